@@ -1,0 +1,88 @@
+"""Seeded synthetic inputs for the quantized-linear path.
+
+The benchmark configurations describe their inputs as distributions, not data sets:
+block scales are |N(0,1)| times a constant stored as fp16, quantised codes are uniform
+over their range, activations are N(0,1).  These generators draw exactly that, on the
+host with numpy's PCG64, so the same bytes can be handed to the CUDA library and to the
+CPU checker.  Scale/min packing for Q4_K inverts the 6-bit unpack of
+``unpack_q4k_q5k_scales`` (src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:108-122).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .format import QuantFormat
+
+SEED_BASE = 0xB2000000
+
+
+def rng_for(config: int, tensor_index: int = 0) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(SEED_BASE + 16 * config + tensor_index))
+
+
+def activations(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
+    return rng.standard_normal((m, k), dtype=np.float32)
+
+
+def _fp16_scale_bytes(rng: np.random.Generator, nblocks: int, mult: float) -> np.ndarray:
+    d = (np.abs(rng.standard_normal(nblocks, dtype=np.float32)) * np.float32(mult)).astype(np.float16)
+    return d.view(np.uint8).reshape(nblocks, 2)
+
+
+def q4_0_blocks(rng, nblocks: int, scale: float = 0.02) -> np.ndarray:
+    out = np.empty((nblocks, 18), dtype=np.uint8)
+    out[:, 0:2] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 2:18] = rng.integers(0, 256, size=(nblocks, 16), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def q8_0_blocks(rng, nblocks: int, scale: float = 0.004) -> np.ndarray:
+    out = np.empty((nblocks, 34), dtype=np.uint8)
+    out[:, 0:2] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 2:34] = rng.integers(-127, 128, size=(nblocks, 32), dtype=np.int8).view(np.uint8)
+    return out.reshape(-1)
+
+
+def pack_q4k_scales(scales: np.ndarray, mins: np.ndarray) -> np.ndarray:
+    """[nb,8] 6-bit scales and mins -> [nb,12] packed bytes."""
+    s = scales.astype(np.uint8)
+    m = mins.astype(np.uint8)
+    out = np.empty((s.shape[0], 12), dtype=np.uint8)
+    out[:, 0:4] = (s[:, 0:4] & 63) | ((s[:, 4:8] >> 4) << 6)
+    out[:, 4:8] = (m[:, 0:4] & 63) | ((m[:, 4:8] >> 4) << 6)
+    out[:, 8:12] = (s[:, 4:8] & 15) | ((m[:, 4:8] & 15) << 4)
+    return out
+
+
+def q4_k_blocks(rng, nblocks: int, scale: float = 0.002) -> np.ndarray:
+    out = np.empty((nblocks, 144), dtype=np.uint8)
+    out[:, 0:2] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 2:4] = _fp16_scale_bytes(rng, nblocks, scale)
+    sc = rng.integers(0, 64, size=(nblocks, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, size=(nblocks, 8), dtype=np.uint8)
+    out[:, 4:16] = pack_q4k_scales(sc, mn)
+    out[:, 16:144] = rng.integers(0, 256, size=(nblocks, 128), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def q6_k_blocks(rng, nblocks: int, scale: float = 0.0005) -> np.ndarray:
+    out = np.empty((nblocks, 210), dtype=np.uint8)
+    out[:, 0:192] = rng.integers(0, 256, size=(nblocks, 192), dtype=np.uint8)
+    out[:, 192:208] = rng.integers(-64, 64, size=(nblocks, 16), dtype=np.int8).view(np.uint8)
+    out[:, 208:210] = _fp16_scale_bytes(rng, nblocks, scale)
+    return out.reshape(-1)
+
+
+_GEN = {
+    QuantFormat.Q4_0: q4_0_blocks,
+    QuantFormat.Q8_0: q8_0_blocks,
+    QuantFormat.Q4_K: q4_k_blocks,
+    QuantFormat.Q6_K: q6_k_blocks,
+}
+
+
+def weight_bytes(fmt: QuantFormat, rng, n: int, k: int) -> np.ndarray:
+    """Packed [N,K] weight (blocks along K) with the benchmark's value distribution."""
+    fmt = QuantFormat.parse(fmt)
+    assert k % fmt.block_size == 0
+    return _GEN[fmt](rng, n * (k // fmt.block_size))
