@@ -1,0 +1,273 @@
+// C ABI of the library (declared in include/b200q.h): argument validation with the same rules
+// as boostr's QuantTensor::from_bytes / quant_matmul checks, kernel-family dispatch, and a
+// thread-local error string in place of Error::QuantError { reason }.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200q.h"
+#include "common.cuh"
+
+namespace b200q {
+cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, int out_dtype, cudaStream_t st, int sm_count);
+cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
+                        size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
+                        unsigned int* status, bool* ws_too_small);
+size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count);
+bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
+size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N);
+cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
+                           size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
+                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len);
+cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
+                               cudaStream_t st);
+}  // namespace b200q
+
+using namespace b200q;
+
+// One status word per device image of this library; kernels receive its address.
+__device__ unsigned int g_status_word = 0;
+
+namespace {
+
+// Device address of g_status_word on the current device, looked up once per device.
+// (The symbol's name in host code is only a handle; kernels need the address.)
+unsigned int* status_ptr_current() {
+    static unsigned int* cached[64];
+    static std::once_flag once[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::call_once(once[dev], [dev] {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) p = nullptr;
+        cached[dev] = static_cast<unsigned int*>(p);
+    });
+    return cached[dev];
+}
+
+thread_local char t_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+bool known_format(int f) { return f == FMT_Q4_0 || f == FMT_Q8_0 || f == FMT_Q4_K || f == FMT_Q6_K; }
+const char* format_name(int f) {
+    switch (f) {
+    case FMT_Q4_0: return "Q4_0";
+    case FMT_Q8_0: return "Q8_0";
+    case FMT_Q4_K: return "Q4_K";
+    case FMT_Q6_K: return "Q6_K";
+    default: return "?";
+    }
+}
+
+// SM count of the current device, looked up once per device.
+int sm_count_current() {
+    static int cached[64];
+    static std::once_flag once[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::call_once(once[dev], [dev] {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    });
+    return cached[dev];
+}
+
+int check_matmul_args(const char* op, int format, const void* act, int act_dtype, const void* w, const void* out,
+                      int out_dtype, size_t M, size_t K, size_t N) {
+    if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "%s: unsupported format id %d", op, format);
+    if (act_dtype != DT_F32 && act_dtype != DT_BF16)
+        return fail(B200Q_ERR_UNSUPPORTED_DTYPE, "%s activation must be F32 (or BF16), got dtype id %d", op, act_dtype);
+    if (out_dtype != DT_F32 && out_dtype != DT_BF16 && out_dtype != DT_F16)
+        return fail(B200Q_ERR_UNSUPPORTED_DTYPE, "%s output must be F32, BF16 or F16, got dtype id %d", op, out_dtype);
+    if (M == 0 || K == 0 || N == 0) return fail(B200Q_ERR_BAD_SHAPE, "%s: M, K, N must be positive (M=%zu K=%zu N=%zu)", op, M, K, N);
+    if (K % fmt_block_size(format))
+        return fail(B200Q_ERR_BAD_SHAPE, "last dimension %zu is not a multiple of %s's block_size %d", K, format_name(format),
+                    fmt_block_size(format));
+    if (M > 0x7FFFFFFFull / 2 || K > 0x7FFFFFFFull / 2 || N > 0x7FFFFFFFull / 2 ||
+        (K / fmt_block_size(format)) * (size_t)fmt_block_bytes(format) > 0x7FFFFFFFull)
+        return fail(B200Q_ERR_BAD_SHAPE, "%s: dimension too large (M=%zu K=%zu N=%zu)", op, M, K, N);
+    if (!act || !w || !out) return fail(B200Q_ERR_INVALID_ARG, "%s: null pointer", op);
+    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(B200Q_ERR_INVALID_ARG, "%s: weight pointer must be 16-byte aligned", op);
+    if (reinterpret_cast<uintptr_t>(act) & 15) return fail(B200Q_ERR_INVALID_ARG, "%s: activation pointer must be 16-byte aligned", op);
+    if (reinterpret_cast<uintptr_t>(out) & 3) return fail(B200Q_ERR_INVALID_ARG, "%s: output pointer must be 4-byte aligned", op);
+    return B200Q_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200q_version(void) { return 100; }
+
+const char* b200q_last_error(void) { return t_err; }
+
+size_t b200q_block_size(int format) { return known_format(format) ? (size_t)fmt_block_size(format) : 0; }
+size_t b200q_block_bytes(int format) { return known_format(format) ? (size_t)fmt_block_bytes(format) : 0; }
+
+int b200q_storage_bytes(int format, size_t numel, size_t* out_bytes) {
+    if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "unsupported format id %d", format);
+    if (!out_bytes) return fail(B200Q_ERR_INVALID_ARG, "out_bytes is null");
+    size_t bs = fmt_block_size(format);
+    if (numel % bs)
+        return fail(B200Q_ERR_BAD_SHAPE, "%s: element count %zu is not a multiple of block_size %zu", format_name(format), numel, bs);
+    *out_bytes = numel / bs * fmt_block_bytes(format);
+    return B200Q_OK;
+}
+
+int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int out_dtype, void* stream) {
+    if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "dequantize: unsupported format id %d", format);
+    if (out_dtype != DT_F32 && out_dtype != DT_BF16 && out_dtype != DT_F16 && out_dtype != DT_F64)
+        return fail(B200Q_ERR_UNSUPPORTED_DTYPE, "dequantize target must be float, got dtype id %d", out_dtype);
+    if (nblocks == 0) return B200Q_OK;
+    if (!w || !out) return fail(B200Q_ERR_INVALID_ARG, "dequantize: null pointer");
+    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(B200Q_ERR_INVALID_ARG, "dequantize: weight pointer must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(out) & 15) return fail(B200Q_ERR_INVALID_ARG, "dequantize: output pointer must be 16-byte aligned");
+    cudaError_t e = launch_dequant(format, w, nblocks, out, out_dtype, static_cast<cudaStream_t>(stream), sm_count_current());
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA dequant kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N) {
+    if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
+    const bool swiglu = op == B200Q_OP_QUANT_SWIGLU;
+    size_t need = gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
+    if (!swiglu && prefill_supported(format, M, K, N)) {
+        size_t a = prefill_workspace_bytes(format, DT_F32, M, K, N);
+        if (a > need) need = a;
+    }
+    if (swiglu && prefill_supported(format, M, K, N)) {
+        // large-M SwiGLU = two prefill GEMMs into scratch, then the gate
+        size_t a = prefill_workspace_bytes(format, DT_F32, M, K, N) + 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255);
+        if (a > need) need = a;
+    }
+    return need;
+}
+
+int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
+                       size_t K, size_t N, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_matmul_args("quant_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul: cannot resolve the device status word");
+    bool small = false;
+    cudaError_t e;
+    if (prefill_supported(format, M, K, N)) {
+        char msg[256] = "";
+        e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
+                           status, &small, msg, sizeof(msg));
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
+    } else {
+        e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
+                        st, status, &small);
+    }
+    if (small)
+        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_matmul: workspace of %zu bytes is too small, need %zu", ws_bytes,
+                    b200q_workspace_bytes(B200Q_OP_QUANT_MATMUL, format, M, K, N));
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_matmul kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
+                             const void* act, int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes,
+                             void* stream) {
+    if (n_weights < 0) return fail(B200Q_ERR_INVALID_ARG, "quant_matmul_batch: negative weight count");
+    if (n_weights == 0) return B200Q_OK;
+    if (!formats || !w || !N || !out) return fail(B200Q_ERR_INVALID_ARG, "quant_matmul_batch: null array");
+    for (int i = 0; i < n_weights; ++i) {
+        int rc = b200q_quant_matmul(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream);
+        if (rc) return rc;
+    }
+    return B200Q_OK;
+}
+
+int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w_gate, const void* w_up, void* out,
+                       int out_dtype, size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, void* stream) {
+    int rc = check_matmul_args("quant_swiglu", format, act, act_dtype, w_gate, out, out_dtype, M, K, N);
+    if (rc) return rc;
+    if (!w_up) return fail(B200Q_ERR_INVALID_ARG, "quant_swiglu: null pointer");
+    if (reinterpret_cast<uintptr_t>(w_up) & 15) return fail(B200Q_ERR_INVALID_ARG, "quant_swiglu: weight pointer must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "quant_swiglu: cannot resolve the device status word");
+    const size_t need = b200q_workspace_bytes(B200Q_OP_QUANT_SWIGLU, format, M, K, N);
+    if (need > ws_bytes || (need && !ws))
+        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_swiglu: workspace of %zu bytes is too small, need %zu", ws_bytes, need);
+    bool small = false;
+    cudaError_t e;
+    if (prefill_supported(format, M, K, N)) {
+        // two tensor-core GEMMs into f32 scratch, then silu(gate) * up
+        const size_t mn = (M * N * sizeof(float) + 255) & ~(size_t)255;
+        float* g = static_cast<float*>(ws);
+        float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + mn);
+        uint8_t* rest = static_cast<uint8_t*>(ws) + 2 * mn;
+        const size_t rest_bytes = ws_bytes - 2 * mn;
+        char msg[256] = "";
+        e = launch_prefill(format, act, act_dtype, w_gate, g, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, status,
+                           &small, msg, sizeof(msg));
+        if (e == cudaSuccess && !small)
+            e = launch_prefill(format, act, act_dtype, w_up, u, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st,
+                               status, &small, msg, sizeof(msg));
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_swiglu: %s", msg);
+        if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
+    } else {
+        e = launch_gemv(format, act, act_dtype, w_gate, w_up, out, out_dtype, M, K, N, ws, ws_bytes, true, sm_count_current(),
+                        st, status, &small);
+    }
+    if (small) return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_swiglu: workspace of %zu bytes is too small, need %zu", ws_bytes, need);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_swiglu kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, int rank, int world, void* dst,
+                     size_t dst_bytes) {
+    if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "shard_pack: unsupported format id %d", format);
+    if (!src || !dst) return fail(B200Q_ERR_INVALID_ARG, "shard_pack: null pointer");
+    if (world <= 0 || rank < 0 || rank >= world) return fail(B200Q_ERR_INVALID_ARG, "shard_pack: rank %d out of range for world size %d", rank, world);
+    const size_t bs = fmt_block_size(format), bb = fmt_block_bytes(format);
+    if (K % bs) return fail(B200Q_ERR_BAD_SHAPE, "last dimension %zu is not a multiple of %s's block_size %zu", K, format_name(format), bs);
+    const size_t row_bytes = K / bs * bb;
+    const uint8_t* s = static_cast<const uint8_t*>(src);
+    uint8_t* d = static_cast<uint8_t*>(dst);
+    if (dim == 0) {
+        if (N % (size_t)world) return fail(B200Q_ERR_BAD_SHAPE, "out_features %zu not divisible by world_size %d", N, world);
+        const size_t rows = N / world, bytes = rows * row_bytes;
+        if (dst_bytes < bytes) return fail(B200Q_ERR_INVALID_ARG, "shard_pack: destination holds %zu bytes, need %zu", dst_bytes, bytes);
+        memcpy(d, s + (size_t)rank * bytes, bytes);
+        return B200Q_OK;
+    }
+    if (dim == 1) {
+        if (K % (size_t)world) return fail(B200Q_ERR_BAD_SHAPE, "in_features %zu not divisible by world_size %d", K, world);
+        const size_t kl = K / world;
+        if (kl % bs) return fail(B200Q_ERR_BAD_SHAPE, "in_features per rank %zu is not a multiple of %s's block_size %zu", kl, format_name(format), bs);
+        const size_t lrow = kl / bs * bb, bytes = N * lrow;
+        if (dst_bytes < bytes) return fail(B200Q_ERR_INVALID_ARG, "shard_pack: destination holds %zu bytes, need %zu", dst_bytes, bytes);
+        for (size_t r = 0; r < N; ++r) memcpy(d + r * lrow, s + r * row_bytes + (size_t)rank * lrow, lrow);
+        return B200Q_OK;
+    }
+    return fail(B200Q_ERR_INVALID_ARG, "shard_pack: dim must be 0 or 1, got %d", dim);
+}
+
+int b200q_check_device_status(void* stream) {
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "stream synchronize failed: %s", cudaGetErrorString(e));
+    unsigned int word = 0, zero = 0;
+    e = cudaMemcpyFromSymbol(&word, g_status_word, sizeof(word));
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "status read failed: %s", cudaGetErrorString(e));
+    if (word) {
+        cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero));
+        return fail(B200Q_ERR_TIMEOUT, "a kernel gave up on a bounded wait (status 0x%x)", word);
+    }
+    return B200Q_OK;
+}
+
+}  // extern "C"

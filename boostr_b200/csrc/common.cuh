@@ -1,0 +1,167 @@
+// Shared device helpers for the sm_100a quantized-linear kernels: mbarrier and bulk-copy
+// (TMA) wrappers with bounded waits, legacy-tensor-core MMA wrappers for the memory-bound
+// small-M kernels, unaligned shared-memory loads for the 2-byte-aligned GGUF blocks.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200q {
+
+// Block formats (QuantFormat::format_id of the reference).
+enum : int { FMT_Q4_0 = 0, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q6_K = 10 };
+enum : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_F64 = 3 };
+
+// Device status word (one per device, owned by the C-ABI translation unit and handed to
+// kernels as a pointer): a kernel that gives up on a bounded wait ORs a code in here and
+// finishes without touching the data it waited for.
+enum : unsigned { STATUS_TIMEOUT_FULL = 1u, STATUS_TIMEOUT_EMPTY = 2u, STATUS_TIMEOUT_MMA = 4u, STATUS_TIMEOUT_TMEM = 8u };
+
+__host__ __device__ constexpr int fmt_block_size(int f) { return (f == FMT_Q4_0 || f == FMT_Q8_0) ? 32 : 256; }
+__host__ __device__ constexpr int fmt_block_bytes(int f) {
+    return f == FMT_Q4_0 ? 18 : f == FMT_Q8_0 ? 34 : f == FMT_Q4_K ? 144 : f == FMT_Q6_K ? 210 : 0;
+}
+// Bytes of one 256-element run of a row ("slice"): the unit one warp of the small-M kernel owns.
+__host__ __device__ constexpr int fmt_slice_bytes(int f) { return fmt_block_bytes(f) * (256 / fmt_block_size(f)); }
+
+// ---------------------------------------------------------------- shared memory / mbarrier
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after two seconds of wall time, in which case the caller records a
+// status code and stops using the data it waited for.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > 2000000000ull) return false;
+        __nanosleep(40);
+    }
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ------------------------------------------------------------------- shared-memory loads
+
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+// 32-bit word at a 2-byte-aligned shared address.
+__device__ __forceinline__ uint32_t lds32_u(uint32_t a) {
+    uint32_t base = a & ~3u;
+    uint32_t sh = (a & 3u) * 8u;
+    uint32_t w0 = lds32(base), w1 = lds32(base + 4);
+    return __funnelshift_r(w0, w1, sh);
+}
+// Two consecutive 32-bit words at a 2-byte-aligned shared address.
+__device__ __forceinline__ uint2 lds64_u(uint32_t a) {
+    uint32_t base = a & ~3u;
+    uint32_t sh = (a & 3u) * 8u;
+    uint32_t w0 = lds32(base), w1 = lds32(base + 4), w2 = lds32(base + 8);
+    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
+}
+
+// ------------------------------------------------------------------------------- MMA
+
+// D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col) + C
+__device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1, const int (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// D(16x8,s32) = A(16x16,s8,row) * B(16x8,s8,col) + C
+__device__ __forceinline__ void mma_s8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// D(16x8,s32) = A(16x16,u8,row) * B(16x8,u8,col) + C
+__device__ __forceinline__ void mma_u8u8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+// D(16x8,f32) = A(16x16,f16,row) * B(16x8,f16,col) + C
+__device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1, const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+// ---------------------------------------------------------------------------- numerics
+
+__device__ __forceinline__ float f16bits_to_f32(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+}  // namespace b200q

@@ -1,0 +1,851 @@
+// Memory-bound quantized GEMV / small-M kernel (M <= 16 per launch) for Q4_0, Q8_0, Q4_K, Q6_K.
+//
+// Stands in for boostr's quant_gemv_*_q8_1_mwr / quant_gemv_*_f32 / fused_swiglu_*_mwr kernels
+// (src/quant/cuda/kernels/quant_gemv.cu:43-1215) and its separate activation-quantise launch
+// (src/quant/cuda/kernels/quant_act.cu:17-69).
+//
+// Shape of the kernel
+//   * Persistent CTAs, one per SM, 16 warps each (four per scheduler, so every warp may use 128
+//     registers).  Warp 0 streams slabs of packed weight rows into a ring of shared-memory
+//     stages with 1-D bulk copies (cp.async.bulk + mbarrier byte counts), running nstages-1
+//     fills ahead; with 3-5 stages of 37-70 KB each SM keeps over 100 KB of HBM reads in flight.
+//   * Each compute warp owns one 256-wide run of K (a "slice": one Q4_K/Q6_K block or eight
+//     Q4_0/Q8_0 blocks) of a K-chunk of up to 16 slices.  The activations of that run are
+//     prepared ONCE per launch and kept in registers as MMA B-fragments, so the only
+//     shared-memory traffic in the loop is the packed weights themselves.
+//   * Dot products run on the tensor cores through mma.sync (16 weight rows x 8 activation
+//     rows per instruction).  The tensor pipe is nearly idle at these shapes; the point is that
+//     one instruction replaces 128 dp4a/FFMA lanes of work, which keeps the integer ALUs (nibble
+//     and 6-bit unpacking) under the HBM rate.
+//   * Q4_K / Q6_K reproduce boostr's CPU numerics: the activation run is quantised to Q8_K
+//     (amax/127 scale, round-half-even, src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98)
+//     inside the kernel, integer dots are exact, and each block contributes
+//     (d*d8)*sumi - (dmin*d8)*sumi_mins without FMA contraction
+//     (src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172, fused_q6k_q8k_dot.rs:170-224).
+//     Blocks are summed in K order, so for K <= 4096 the result is bit-identical to the CPU path.
+//   * Q4_0 / Q8_0 keep full activation precision as the CPU path does
+//     (src/quant/cpu/kernels/quant_matmul.rs:193-209): each run is scaled by a power of two and
+//     split into fp16 hi + lo parts (M <= 8), or rounded once to fp16 (M 9..16, relative error
+//     2^-12); codes are exact in fp16 and products accumulate in f32.
+//   * Partial sums of the warps of a CTA meet in shared memory and are added in slice order.
+//     When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks
+//     are spread over gridDim.y and a second small kernel adds the partials.
+#include "common.cuh"
+
+namespace b200q {
+
+struct GemvParams {
+    const uint8_t* w[2];  // [1] = up-projection weight in SwiGLU mode
+    const void* act;
+    void* out;
+    float* partial;       // [nmat][ksplit][M][N] f32 when ksplit > 1
+    uint32_t M, K, N;
+    uint32_t m0;          // first activation row of this launch (M tiles of 16)
+    uint32_t mcount;      // activation rows handled by this launch (<= 8*MT)
+    uint32_t row_bytes;
+    uint32_t nslices;     // ceil(K / 256)
+    uint32_t spc;         // slices per chunk (<= 16) == compute warps per row group
+    uint32_t nchunks;     // ceil(nslices / spc)
+    uint32_t ksplit;      // gridDim.y
+    uint32_t rgs;         // 16-row groups per slab
+    uint32_t srow;        // shared-memory row stride (bytes, multiple of 16, odd multiple of 16)
+    uint32_t stage_bytes;
+    uint32_t nstages;
+    uint32_t total_units; // slabs
+    uint32_t red_off;     // byte offset of the reduction buffer in dynamic smem
+    uint32_t stage_off;   // byte offset of stage 0
+    int act_dtype, out_dtype;
+    unsigned long long w_bytes;  // bytes of each weight tensor
+    unsigned int* status;        // device status word (bounded-wait timeouts)
+};
+
+namespace {
+
+constexpr int MAX_STAGES = 8;
+
+// ---------------------------------------------------------------- activation access
+
+__device__ __forceinline__ void load_act8(const void* act, int dt, size_t idx, float (&v)[8]) {
+    if (dt == DT_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(act) + idx);
+        float4 a = __ldg(p), b = __ldg(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(act) + idx));
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ void load_act4(const void* act, int dt, size_t idx, float (&v)[4]) {
+    if (dt == DT_F32) {
+        float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(act) + idx));
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else {
+        uint2 r = __ldg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(act) + idx));
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+    }
+}
+
+// Q8_K code of one activation: rint(x * id) clamped to [-128, 127] (round half to even).
+__device__ __forceinline__ int q8k_code(float x, float id) {
+    int q = __float2int_rn(__fmul_rn(x, id));
+    return max(-128, min(127, q));
+}
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xFF) | ((uint32_t)(b & 0xFF) << 8) | ((uint32_t)(c & 0xFF) << 16) | ((uint32_t)(d & 0xFF) << 24);
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
+}
+__device__ __forceinline__ int quad_sum(int v) {
+    v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+    return v + __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+}
+
+// ------------------------------------------------------------------ per-format state
+//
+// Lane naming follows the MMA fragment layout: g = lane / 4 (weight row within the 16-row
+// group, and activation row within an 8-row tile), t = lane % 4 (position along K).
+
+template <int FMT, int MT, bool HILO>
+struct SliceB;
+
+// ---- Q4_K: int8 activations; sub-block j (32 wide) uses elements 8t..8t+7 of the lane ----
+template <int MT, bool HILO>
+struct SliceB<FMT_Q4_K, MT, HILO> {
+    uint32_t q[MT][16];   // [2*j + half]: k32 B fragment of sub-block j
+    uint32_t bs_lo[MT];   // bytes: (bsum_j + 4096) & 127 for j = 4t..4t+3 (t < 2), else 0
+    uint32_t bs_hi[MT];   // bytes: (bsum_j + 4096) >> 7
+    float d8[MT][2];      // Q8_K scale of activation rows 2t, 2t+1 of the tile
+
+    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
+#pragma unroll
+        for (int tl = 0; tl < MT; ++tl) {
+            uint32_t m = tl * 8 + g;
+            bool on = valid && m < p.mcount;
+            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 8 * t;
+            float amax = 0.f;
+            if (on) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float v[8];
+                    load_act8(p.act, p.act_dtype, base + 32 * j, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                }
+            }
+            amax = quad_max(amax);
+            float d = __fdiv_rn(amax, 127.0f);
+            float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+            uint32_t lo[2] = {0, 0}, hi[2] = {0, 0};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (on) {
+                    float v[8];
+                    load_act8(p.act, p.act_dtype, base + 32 * j, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) c[i] = q8k_code(v[i], id);
+                }
+                q[tl][2 * j] = pack4(c[0], c[1], c[2], c[3]);
+                q[tl][2 * j + 1] = pack4(c[4], c[5], c[6], c[7]);
+                int bsum = quad_sum(c[0] + c[1] + c[2] + c[3] + c[4] + c[5] + c[6] + c[7]) + 4096;
+                lo[j >> 2] |= (uint32_t)(bsum & 127) << (8 * (j & 3));
+                hi[j >> 2] |= (uint32_t)(bsum >> 7) << (8 * (j & 3));
+            }
+            bs_lo[tl] = !on ? 0u : t == 0 ? lo[0] : t == 1 ? lo[1] : 0u;
+            bs_hi[tl] = !on ? 0u : t == 0 ? hi[0] : t == 1 ? hi[1] : 0u;
+            float dd = on ? d : 0.f;
+            d8[tl][0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
+            d8[tl][1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+        }
+    }
+};
+
+// ---- Q6_K: int8 activations; sub-block sb (16 wide) uses elements 4t..4t+3 ----
+template <int MT, bool HILO>
+struct SliceB<FMT_Q6_K, MT, HILO> {
+    uint32_t q[MT][16];  // [sb]: k16 B fragment of 16-wide sub-block sb
+    float d8[MT][2];
+
+    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
+#pragma unroll
+        for (int tl = 0; tl < MT; ++tl) {
+            uint32_t m = tl * 8 + g;
+            bool on = valid && m < p.mcount;
+            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 4 * t;
+            float amax = 0.f;
+            if (on) {
+#pragma unroll
+                for (int sb = 0; sb < 16; ++sb) {
+                    float v[4];
+                    load_act4(p.act, p.act_dtype, base + 16 * sb, v);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                }
+            }
+            amax = quad_max(amax);
+            float d = __fdiv_rn(amax, 127.0f);
+            float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+#pragma unroll
+            for (int sb = 0; sb < 16; ++sb) {
+                uint32_t r = 0;
+                if (on) {
+                    float v[4];
+                    load_act4(p.act, p.act_dtype, base + 16 * sb, v);
+                    r = pack4(q8k_code(v[0], id), q8k_code(v[1], id), q8k_code(v[2], id), q8k_code(v[3], id));
+                }
+                q[tl][sb] = r;
+            }
+            float dd = on ? d : 0.f;
+            d8[tl][0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
+            d8[tl][1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+        }
+    }
+};
+
+// ---- Q8_0 / Q4_0: fp16 activations scaled by a power of two per (row, slice) ----
+template <int FMT, int MT, bool HILO>
+struct SliceBF16 {
+    uint32_t h[MT][8][4];                 // [block][step*2 + {b0,b1}] half2 fragments
+    uint32_t l[HILO ? MT : 1][8][4];      // low parts * 2048 (HILO only)
+    float inv[MT][2];                     // 1 / scale of activation rows 2t, 2t+1
+
+    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
+        const uint32_t kleft = valid ? p.K - slice * 256 : 0;  // elements of this slice that exist
+#pragma unroll
+        for (int tl = 0; tl < MT; ++tl) {
+            uint32_t m = tl * 8 + g;
+            bool on = valid && m < p.mcount;
+            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 8 * t;
+            float amax = 0.f;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                if (on && 32u * b < kleft) {
+                    float v[8];
+                    load_act8(p.act, p.act_dtype, base + 32 * b, v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+                }
+            }
+            amax = quad_max(amax);
+            uint32_t e = __float_as_uint(amax) >> 23;  // biased exponent (amax >= 0)
+            e = e == 0 ? 127u : (e > 253u ? 253u : e);
+            float sc = __uint_as_float((254u - e) << 23);  // 2^(127-e): amax*sc in [1,2)
+            float isc = __uint_as_float(e << 23);
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                if (on && 32u * b < kleft) load_act8(p.act, p.act_dtype, base + 32 * b, v);
+                __half hi[8], lo[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float x = v[i] * sc;
+                    hi[i] = __float2half_rn(x);
+                    lo[i] = __float2half_rn((x - __half2float(hi[i])) * 2048.0f);
+                }
+                // K order inside a 32-block follows what the weight side can unpack cheaply:
+                //   Q8_0: byte pairs   -> (0,1) (2,3) | (4,5) (6,7)
+                //   Q4_0: byte i holds elements 2i, 2i+1 -> lop3 yields (0,4) (1,5) | (2,6) (3,7)
+                constexpr int P8[8] = {0, 1, 2, 3, 4, 5, 6, 7};
+                constexpr int P4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    int i0 = FMT == FMT_Q8_0 ? P8[2 * r] : P4[2 * r];
+                    int i1 = FMT == FMT_Q8_0 ? P8[2 * r + 1] : P4[2 * r + 1];
+                    h[tl][b][r] = h2_as_u32(__halves2half2(hi[i0], hi[i1]));
+                    if (HILO) l[tl][b][r] = h2_as_u32(__halves2half2(lo[i0], lo[i1]));
+                }
+            }
+            float ii = on ? isc : 0.f;
+            inv[tl][0] = __shfl_sync(0xFFFFFFFFu, ii, (2 * t) * 4);
+            inv[tl][1] = __shfl_sync(0xFFFFFFFFu, ii, (2 * t + 1) * 4);
+        }
+    }
+};
+template <int MT, bool HILO>
+struct SliceB<FMT_Q8_0, MT, HILO> : SliceBF16<FMT_Q8_0, MT, HILO> {};
+template <int MT, bool HILO>
+struct SliceB<FMT_Q4_0, MT, HILO> : SliceBF16<FMT_Q4_0, MT, HILO> {};
+
+// ------------------------------------------------------------------ slice x 16 rows
+
+// Adds the contribution of one slice (K run of 256) of weight rows g and g+8 to acc.
+// ra / rb: shared-memory byte address of the slice in row g / g+8.
+
+template <int MT, bool HILO>
+__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, uint32_t ra, uint32_t rb, int t,
+                                          float (&acc)[MT][4]) {
+    const int zero[4] = {0, 0, 0, 0};
+    uint4 ha = lds128(ra), hb = lds128(rb);
+    // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
+    uint32_t sA[2], mA[2], sB[2], mB[2];
+    sA[0] = ha.y & 0x3F3F3F3Fu;
+    mA[0] = ha.z & 0x3F3F3F3Fu;
+    sA[1] = (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u);
+    mA[1] = ((ha.w >> 4) & 0x0F0F0F0Fu) | ((ha.z >> 2) & 0x30303030u);
+    sB[0] = hb.y & 0x3F3F3F3Fu;
+    mB[0] = hb.z & 0x3F3F3F3Fu;
+    sB[1] = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
+    mB[1] = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
+
+    int isum_lo[MT][4], isum_hi[MT][4];  // hi: 16x too large (high nibbles are used unshifted)
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) isum_lo[tl][i] = isum_hi[tl][i] = 0;
+
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
+        uint2 qa = lds64(ra + 16 + 32 * jj + 8 * t), qb = lds64(rb + 16 + 32 * jj + 8 * t);
+        const int sh = 8 * ((2 * jj) & 3);
+        const int scA0 = (sA[jj >> 1] >> sh) & 0xFF, scA1 = (sA[jj >> 1] >> (sh + 8)) & 0xFF;
+        const int scB0 = (sB[jj >> 1] >> sh) & 0xFF, scB1 = (sB[jj >> 1] >> (sh + 8)) & 0xFF;
+#pragma unroll
+        for (int tl = 0; tl < MT; ++tl) {
+            int d[4];
+            mma_u8s8_k32(d, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu,
+                         B.q[tl][4 * jj], B.q[tl][4 * jj + 1], zero);
+            isum_lo[tl][0] += scA0 * d[0];
+            isum_lo[tl][1] += scA0 * d[1];
+            isum_lo[tl][2] += scB0 * d[2];
+            isum_lo[tl][3] += scB0 * d[3];
+            mma_u8s8_k32(d, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u,
+                         B.q[tl][4 * jj + 2], B.q[tl][4 * jj + 3], zero);
+            isum_hi[tl][0] += scA1 * d[0];
+            isum_hi[tl][1] += scA1 * d[1];
+            isum_hi[tl][2] += scB1 * d[2];
+            isum_hi[tl][3] += scB1 * d[3];
+        }
+    }
+    // sum_j mins_j * bsum_j as two tiny u8 MMAs over (bsum + 4096) = hi * 128 + lo
+    const uint32_t am0 = t == 0 ? mA[0] : t == 1 ? mA[1] : 0u;
+    const uint32_t am1 = t == 0 ? mB[0] : t == 1 ? mB[1] : 0u;
+    const int sumA = __dp4a(mA[0], 0x01010101u, __dp4a(mA[1], 0x01010101u, 0u));
+    const int sumB = __dp4a(mB[0], 0x01010101u, __dp4a(mB[1], 0x01010101u, 0u));
+    const float dA = f16bits_to_f32(ha.x & 0xFFFF), dminA = f16bits_to_f32(ha.x >> 16);
+    const float dB = f16bits_to_f32(hb.x & 0xFFFF), dminB = f16bits_to_f32(hb.x >> 16);
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl) {
+        int ml[4], mh[4];
+        mma_u8u8_k16(ml, am0, am1, B.bs_lo[tl], zero);
+        mma_u8u8_k16(mh, am0, am1, B.bs_hi[tl], zero);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sumi = isum_lo[tl][i] + (isum_hi[tl][i] >> 4);
+            const int summ = ml[i] + 128 * mh[i] - 4096 * (i < 2 ? sumA : sumB);
+            const float d8 = B.d8[tl][i & 1];
+            const float dall = __fmul_rn(i < 2 ? dA : dB, d8);
+            const float dmall = __fmul_rn(i < 2 ? dminA : dminB, d8);
+            const float term = __fsub_rn(__fmul_rn(dall, (float)sumi), __fmul_rn(dmall, (float)summ));
+            acc[tl][i] = __fadd_rn(acc[tl][i], term);
+        }
+    }
+}
+
+template <int MT, bool HILO>
+__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, uint32_t ra, uint32_t rb, int t,
+                                          float (&acc)[MT][4]) {
+    const int zero[4] = {0, 0, 0, 0};
+    int isum[MT][4];
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) isum[tl][i] = 0;
+    uint32_t scA[4], scB[4];  // 16 signed 8-bit scales per row
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        scA[i] = lds32_u(ra + 192 + 4 * i);
+        scB[i] = lds32_u(rb + 192 + 4 * i);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int is = 0; is < 2; ++is) {
+            const uint32_t o = 64 * n + 16 * is + 4 * t;
+            const uint32_t la0 = lds32_u(ra + o), la1 = lds32_u(ra + o + 32), hA = lds32_u(ra + 128 + 32 * n + 16 * is + 4 * t);
+            const uint32_t lb0 = lds32_u(rb + o), lb1 = lds32_u(rb + o + 32), hB = lds32_u(rb + 128 + 32 * n + 16 * is + 4 * t);
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+                // int8 value 4*(q-32): nibble -> bits 5..2, two high bits -> bits 7..6, flip bit 7
+                const uint32_t qla = (gq & 1) ? la1 : la0, qlb = (gq & 1) ? lb1 : lb0;
+                const uint32_t na = (gq < 2 ? (qla << 2) : (qla >> 2)) & 0x3C3C3C3Cu;
+                const uint32_t nb = (gq < 2 ? (qlb << 2) : (qlb >> 2)) & 0x3C3C3C3Cu;
+                const uint32_t ua = ((hA << (6 - 2 * gq)) & 0xC0C0C0C0u) ^ 0x80808080u;
+                const uint32_t ub = ((hB << (6 - 2 * gq)) & 0xC0C0C0C0u) ^ 0x80808080u;
+                const int sb = 8 * n + 2 * gq + is;
+                const int sA_ = (int)(signed char)((scA[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
+                const int sB_ = (int)(signed char)((scB[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
+#pragma unroll
+                for (int tl = 0; tl < MT; ++tl) {
+                    int d[4];
+                    mma_s8s8_k16(d, na | ua, nb | ub, B.q[tl][sb], zero);
+                    isum[tl][0] += sA_ * d[0];
+                    isum[tl][1] += sA_ * d[1];
+                    isum[tl][2] += sB_ * d[2];
+                    isum[tl][3] += sB_ * d[3];
+                }
+            }
+        }
+    }
+    const float dA = f16bits_to_f32(lds16(ra + 208)), dB = f16bits_to_f32(lds16(rb + 208));
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float dall = __fmul_rn(i < 2 ? dA : dB, B.d8[tl][i & 1]);
+            acc[tl][i] = __fadd_rn(acc[tl][i], __fmul_rn(dall, (float)(isum[tl][i] >> 2)));
+        }
+}
+
+// int8 x4 (as stored, two's complement) -> two half2 holding the exact integers
+__device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x = w ^ 0x80808080u;  // q + 128 in 0..255
+    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 (magic) + 128
+    lo = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4140)), bias));
+    hi = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4342)), bias));
+}
+
+template <int FMT, int MT, bool HILO>
+__device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, uint32_t ra, uint32_t rb, int t, uint32_t nblk,
+                                          float (&acc)[MT][4]) {
+    constexpr int BB = fmt_block_bytes(FMT);
+    const float zf[4] = {0.f, 0.f, 0.f, 0.f};
+    float sacc[MT][4];
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sacc[tl][i] = 0.f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        if ((uint32_t)b < nblk) {  // warp-uniform: ragged last slice when K % 256 != 0
+            uint32_t a[2][4];  // [row][step*2 + {k 2t.., k 2t+8..}]
+            if constexpr (FMT == FMT_Q8_0) {
+                // block = f16 d | 32 x i8 ; lane uses bytes 8t..8t+7
+                uint2 wa = lds64_u(ra + BB * b + 2 + 8 * t), wb = lds64_u(rb + BB * b + 2 + 8 * t);
+                s8x4_to_h2(wa.x, a[0][0], a[0][1]);
+                s8x4_to_h2(wa.y, a[0][2], a[0][3]);
+                s8x4_to_h2(wb.x, a[1][0], a[1][1]);
+                s8x4_to_h2(wb.y, a[1][2], a[1][3]);
+            } else {
+                // Q4_0 block = f16 d | 16 B ; byte i = elements 2i (low nibble), 2i+1 (high); lane uses bytes 4t..4t+3
+                const __half2 b8 = __floats2half2_rn(1032.f, 1032.f);              // 1024 + 8
+                const __half2 s16 = __floats2half2_rn(0.0625f, 0.0625f), b72 = __floats2half2_rn(-72.f, -72.f);
+                uint32_t wv[2] = {lds32_u(ra + BB * b + 2 + 4 * t), lds32_u(rb + BB * b + 2 + 4 * t)};
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint32_t w0 = wv[r], w1 = wv[r] >> 8;
+                    a[r][0] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w0, 0x000F000Fu, 0x64006400u)), b8));        // e0,e4
+                    a[r][1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w0, 0x00F000F0u, 0x64006400u)), s16, b72));  // e1,e5
+                    a[r][2] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w1, 0x000F000Fu, 0x64006400u)), b8));        // e2,e6
+                    a[r][3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w1, 0x00F000F0u, 0x64006400u)), s16, b72));  // e3,e7
+                }
+            }
+            const float dA = f16bits_to_f32(lds16(ra + BB * b)), dB = f16bits_to_f32(lds16(rb + BB * b));
+#pragma unroll
+            for (int tl = 0; tl < MT; ++tl) {
+                float d[4];
+                mma_f16_k16(d, a[0][0], a[1][0], a[0][1], a[1][1], B.h[tl][b][0], B.h[tl][b][1], zf);
+                mma_f16_k16(d, a[0][2], a[1][2], a[0][3], a[1][3], B.h[tl][b][2], B.h[tl][b][3], d);
+                if constexpr (HILO) {
+                    float e[4];
+                    mma_f16_k16(e, a[0][0], a[1][0], a[0][1], a[1][1], B.l[tl][b][0], B.l[tl][b][1], zf);
+                    mma_f16_k16(e, a[0][2], a[1][2], a[0][3], a[1][3], B.l[tl][b][2], B.l[tl][b][3], e);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) d[i] = fmaf(e[i], 1.0f / 2048.0f, d[i]);
+                }
+                sacc[tl][0] = fmaf(dA, d[0], sacc[tl][0]);
+                sacc[tl][1] = fmaf(dA, d[1], sacc[tl][1]);
+                sacc[tl][2] = fmaf(dB, d[2], sacc[tl][2]);
+                sacc[tl][3] = fmaf(dB, d[3], sacc[tl][3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[tl][i] = fmaf(sacc[tl][i], B.inv[tl][i & 1], acc[tl][i]);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ void store_out(void* out, int dt, size_t idx, float v) {
+    if (dt == DT_F32) static_cast<float*>(out)[idx] = v;
+    else if (dt == DT_BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+    else static_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+// ------------------------------------------------------------------------- the kernel
+//
+// FMT    block format
+// MT     8-row activation tiles per launch (1 or 2)
+// SL     K-chunks (of up to 16 slices) one CTA walks per slab; its activation fragments for all
+//        of them stay in registers
+// HILO   fp16 hi+lo activation split (Q4_0 / Q8_0 only)
+// SWIGLU two weights (gate, up) and out = silu(gate) * up
+// Cursor over the sequence of stage fills of one CTA: slab -> matrix -> K-chunk.
+struct FillCursor {
+    uint32_t unit;
+    int mat, c;
+    uint32_t it;  // running fill index: stage = it % nstages, parity = (it / nstages) & 1
+};
+
+template <int FMT, int MT, int SL, bool HILO, bool SWIGLU>
+__global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NMAT = SWIGLU ? 2 : 1;
+    constexpr int SLICE_B = fmt_slice_bytes(FMT);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwc = (int)(p.spc * p.rgs);  // warps in the CTA; warp 0 also issues the copies
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 8 * MAX_STAGES;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + 16 * MAX_STAGES);
+    float* red = reinterpret_cast<float*>(smem + p.red_off);
+    const uint32_t stage0 = smem_u32(smem + p.stage_off);
+    const uint32_t rps = 16 * p.rgs;  // rows per slab
+    const uint32_t ks = blockIdx.y;
+    const int nch = (int)min((uint32_t)SL, p.nchunks - ks * SL);  // K-chunks this CTA walks (>= 1)
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.nstages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, nwc);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // Issues the copies of the fill at `cur` (warp 0 only) and advances the cursor.
+    auto produce = [&](FillCursor& cur) {
+        if (cur.unit >= p.total_units) return;
+        const uint32_t stage = cur.it % p.nstages, par = (cur.it / p.nstages) & 1;
+        const uint32_t r0 = cur.unit * rps;
+        const uint32_t nrows = min(rps, p.N - r0);
+        const uint8_t* wbase = p.w[cur.mat];
+        const uint8_t* wend = wbase + p.w_bytes;
+        const uint32_t gc = ks * SL + cur.c;
+        // wait until every warp has released the stage (first trip round the ring passes at once)
+        if (!*abort_flag && !mbar_wait(bar_empty + 8 * stage, par ^ 1)) {
+            *abort_flag = 1;
+            atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+        }
+        if (!*abort_flag) {
+            const uint32_t coff = gc * p.spc * SLICE_B;
+            const uint32_t cbytes = min(p.spc * SLICE_B, p.row_bytes - coff);
+            const uint32_t sdst = stage0 + stage * p.stage_bytes;
+            uint32_t tx = 0;
+            // Each row's chunk is copied as the enclosing 16-byte-aligned range.  Only the last
+            // row of the tensor can have a range that would end past the buffer: its final <16
+            // bytes are moved with plain loads instead.
+            for (uint32_t r = lane; r < nrows; r += 32) {
+                const uint8_t* gsrc = wbase + (size_t)(r0 + r) * p.row_bytes + coff;
+                const uint8_t* gs = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(gsrc) & ~(uintptr_t)15);
+                const uint8_t* ge = gsrc + cbytes;
+                const uint8_t* e16 = reinterpret_cast<const uint8_t*>((reinterpret_cast<uintptr_t>(ge) + 15) & ~(uintptr_t)15);
+                if (e16 > wend) {
+                    e16 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(ge) & ~(uintptr_t)15);
+                    uint8_t* sd = smem + p.stage_off + stage * p.stage_bytes + r * p.srow;
+                    for (const uint8_t* q = e16; q < ge; ++q) sd[q - gs] = __ldg(q);
+                }
+                tx += (uint32_t)(e16 - gs);
+            }
+            tx = __reduce_add_sync(0xFFFFFFFFu, tx);
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(bar_full + 8 * stage, tx);
+            __syncwarp();
+            for (uint32_t r = lane; r < nrows; r += 32) {
+                const uint8_t* gsrc = wbase + (size_t)(r0 + r) * p.row_bytes + coff;
+                const uint8_t* gs = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(gsrc) & ~(uintptr_t)15);
+                const uint8_t* ge = gsrc + cbytes;
+                const uint8_t* e16 = reinterpret_cast<const uint8_t*>((reinterpret_cast<uintptr_t>(ge) + 15) & ~(uintptr_t)15);
+                if (e16 > wend) e16 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(ge) & ~(uintptr_t)15);
+                const uint32_t n = (uint32_t)(e16 - gs);
+                if (n) bulk_g2s(sdst + r * p.srow, gs, n, bar_full + 8 * stage);
+            }
+        }
+        ++cur.it;
+        if (++cur.c >= nch) {
+            cur.c = 0;
+            if (++cur.mat >= NMAT) {
+                cur.mat = 0;
+                cur.unit += gridDim.x;
+            }
+        }
+    };
+
+    // Warp 0 runs nstages-1 fills ahead of the computation.
+    FillCursor pc{blockIdx.x, 0, 0, 0};
+    if (warp == 0)
+        for (uint32_t i = 0; i + 1 < p.nstages; ++i) produce(pc);
+
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t s = warp % p.spc;   // slice within a chunk
+    const uint32_t rg = warp / p.spc;  // row group within a slab
+    const int nthr = nwc * 32;
+
+    SliceB<FMT, MT, HILO> B[SL];
+#pragma unroll
+    for (int c = 0; c < SL; ++c) {
+        const uint32_t gc = ks * SL + c;
+        const uint32_t slice = gc * p.spc + s;
+        B[c].build(p, slice, c < nch && slice < p.nslices, g, t);
+    }
+
+    uint32_t it = 0, buf = 0;
+    for (uint32_t unit = blockIdx.x; unit < p.total_units; unit += gridDim.x, buf ^= 1) {
+        const uint32_t r0 = unit * rps;
+        const uint32_t rowA = rg * 16 + g, rowB = rowA + 8;  // rows of the slab
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+            float acc[MT][4];
+#pragma unroll
+            for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[tl][i] = 0.f;
+            // phase of a row inside its 16-byte-aligned copy (0 whenever row_bytes % 16 == 0)
+            const uint32_t phA = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowA) * p.row_bytes) & 15);
+            const uint32_t phB = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowB) * p.row_bytes) & 15);
+#pragma unroll
+            for (int c = 0; c < SL; ++c) {
+                if (c < nch) {
+                    if (warp == 0) produce(pc);  // refills the stage every warp released one fill ago
+                    const uint32_t gc = ks * SL + c;
+                    const uint32_t stage = it % p.nstages, par = (it / p.nstages) & 1;
+                    ++it;
+                    if (!*abort_flag && !mbar_wait(bar_full + 8 * stage, par)) {
+                        *abort_flag = 1;
+                        atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                    }
+                    const uint32_t slice = gc * p.spc + s;
+                    if (!*abort_flag && slice < p.nslices) {
+                        const uint32_t coff = gc * p.spc * SLICE_B;
+                        const uint32_t sb = stage0 + stage * p.stage_bytes + s * SLICE_B;
+                        const uint32_t ra = sb + rowA * p.srow + ((phA + coff) & 15);
+                        const uint32_t rb = sb + rowB * p.srow + ((phB + coff) & 15);
+                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, HILO>(B[c], ra, rb, t, acc);
+                        else if constexpr (FMT == FMT_Q6_K) slice_q6k<MT, HILO>(B[c], ra, rb, t, acc);
+                        else {
+                            const uint32_t kl = p.K - slice * 256;
+                            slice_f16<FMT, MT, HILO>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                }
+            }
+            float* rdst = red + ((size_t)(buf * NMAT + mat) * nwc + warp) * (MT * 4 * 32);
+#pragma unroll
+            for (int tl = 0; tl < MT; ++tl)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rdst[(tl * 4 + i) * 32 + lane] = acc[tl][i];
+        }
+        __syncthreads();
+        // cross-warp sum in slice order, then store
+        const int per_rg = MT * 4 * 32;
+        for (int e = threadIdx.x; e < (int)p.rgs * per_rg; e += nthr) {
+            const int rgi = e / per_rg, rem = e % per_rg, i = rem >> 5, ln = rem & 31;
+            float v[NMAT];
+#pragma unroll
+            for (int mat = 0; mat < NMAT; ++mat) {
+                const float* src = red + ((size_t)(buf * NMAT + mat) * nwc + rgi * p.spc) * per_rg + i * 32 + ln;
+                float sum = 0.f;
+                for (uint32_t ss = 0; ss < p.spc; ++ss) sum = __fadd_rn(sum, src[(size_t)ss * per_rg]);
+                v[mat] = sum;
+            }
+            const int ci = i & 3;
+            const uint32_t row = r0 + rgi * 16 + (ln >> 2) + (ci >= 2 ? 8 : 0);
+            const uint32_t col = (i >> 2) * 8 + 2 * (ln & 3) + (ci & 1);
+            if (row < p.N && col < p.mcount) {
+                if (p.ksplit == 1) {
+                    float r = v[0];
+                    if constexpr (SWIGLU) r = silu_f(v[0]) * v[1];
+                    store_out(p.out, p.out_dtype, (size_t)(p.m0 + col) * p.N + row, r);
+                } else {
+#pragma unroll
+                    for (int mat = 0; mat < NMAT; ++mat)
+                        p.partial[((size_t)(mat * p.ksplit + ks) * p.M + p.m0 + col) * p.N + row] = v[mat];
+                }
+            }
+        }
+    }
+}
+
+// Adds split-K partials [nmat][ksplit][M][N] in K order and applies the SwiGLU gate.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, void* out, int out_dtype,
+                                                            size_t mn, uint32_t ksplit, int swiglu) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (size_t)gridDim.x * blockDim.x) {
+        float a = 0.f, b = 0.f;
+        for (uint32_t k = 0; k < ksplit; ++k) a = __fadd_rn(a, partial[(size_t)k * mn + i]);
+        if (swiglu) {
+            for (uint32_t k = 0; k < ksplit; ++k) b = __fadd_rn(b, partial[(size_t)(ksplit + k) * mn + i]);
+            a = silu_f(a) * b;
+        }
+        store_out(out, out_dtype, i, a);
+    }
+}
+
+template <int FMT, int MT, int SL, bool HILO, bool SWIGLU>
+cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    auto k = gemv_kernel<FMT, MT, SL, HILO, SWIGLU>;
+    static bool attr_set[64] = {};  // per device; setting the attribute is idempotent, races are harmless
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    k<<<grid, threads, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int FMT, bool SWIGLU>
+cudaError_t launch_gemv_fmt(const GemvParams& p, int mt, int sl, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
+    if constexpr (KQ) {
+        if (mt == 1 && sl == 1) return launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 2) return launch_one<FMT, 1, 2, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 4) return launch_one<FMT, 1, 4, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, grid, threads, smem, st);
+    } else {
+        if (mt == 1 && sl == 1) return launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// Largest number of K-chunks a CTA may keep activation fragments for, per format and tile count.
+int gemv_max_sl(int fmt, int mt) {
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    if (kq) return mt == 1 ? 4 : 2;
+    return 1;
+}
+
+struct GemvPlan {
+    uint32_t spc, nslices, nchunks, sl, ksplit, rgs, srow, stage_bytes, nstages, total_units, red_off, stage_off;
+    size_t smem;
+    int threads;
+    dim3 grid;
+};
+
+// Shape-dependent launch geometry, shared by the launcher and the workspace query.
+bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_count, GemvPlan& pl) {
+    const uint32_t slice_b = fmt_slice_bytes(fmt);
+    const uint32_t row_bytes = K / fmt_block_size(fmt) * fmt_block_bytes(fmt);
+    pl.nslices = (K + 255) / 256;
+    pl.spc = pl.nslices < 16 ? pl.nslices : 16;
+    pl.nchunks = (pl.nslices + pl.spc - 1) / pl.spc;
+    const uint32_t maxsl = gemv_max_sl(fmt, mt);
+    uint32_t sl = pl.nchunks < maxsl ? pl.nchunks : maxsl;
+    if (sl == 3) sl = 4;  // instantiated values: 1, 2, 4
+    pl.sl = sl;
+    pl.ksplit = (pl.nchunks + sl - 1) / sl;
+    pl.rgs = 16 / pl.spc;
+    if (pl.rgs < 1) pl.rgs = 1;
+    // never stage more row groups than the tensor has
+    const uint32_t need_rg = (N + 15) / 16;
+    if (pl.rgs > need_rg) pl.rgs = need_rg;
+    uint32_t cmax = pl.spc * slice_b < row_bytes ? pl.spc * slice_b : row_bytes;
+    uint32_t srow = (cmax + 19 + 15) & ~15u;
+    if ((srow & 31) == 0) srow += 16;  // odd multiple of 16: 8 rows x 4 lanes hit 32 distinct banks
+    pl.srow = srow;
+    pl.stage_bytes = 16 * pl.rgs * srow;
+    const int nwc = pl.spc * pl.rgs;
+    const uint32_t red_bytes = 2u * (swiglu ? 2 : 1) * nwc * mt * 4 * 32 * 4;
+    pl.red_off = 256;
+    pl.stage_off = (pl.red_off + red_bytes + 127) & ~127u;
+    const uint32_t budget = 232448 - 1024;
+    if (pl.stage_off + 2 * pl.stage_bytes > budget) return false;
+    uint32_t ns = (budget - pl.stage_off) / pl.stage_bytes;
+    if (ns > MAX_STAGES) ns = MAX_STAGES;
+    pl.nstages = ns;
+    pl.smem = pl.stage_off + (size_t)ns * pl.stage_bytes;
+    pl.total_units = (N + 16 * pl.rgs - 1) / (16 * pl.rgs);
+    pl.threads = nwc * 32;
+    uint32_t gx = sm_count / pl.ksplit;
+    if (gx < 1) gx = 1;
+    if (gx > pl.total_units) gx = pl.total_units;
+    pl.grid = dim3(gx, pl.ksplit, 1);
+    return true;
+}
+
+size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count) {
+    size_t need = 0;
+    for (int mt = 1; mt <= 2; ++mt) {
+        if (mt == 2 && M <= 8) break;
+        GemvPlan pl;
+        if (!gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl)) continue;
+        if (pl.ksplit > 1) {
+            size_t b = (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float);
+            if (b > need) need = b;
+        }
+    }
+    return need;
+}
+
+// out[M,N] = act[M,K] x W^T for any M, in passes of up to 16 activation rows.
+cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
+                        size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
+                        unsigned int* status, bool* ws_too_small) {
+    *ws_too_small = false;
+    bool need_reduce = false;
+    uint32_t red_ksplit = 1;
+    for (size_t m0 = 0; m0 < M; m0 += 16) {
+        const uint32_t mc = (uint32_t)(M - m0 < 16 ? M - m0 : 16);
+        const int mt = M <= 8 ? 1 : 2;  // one geometry for every pass, so split-K partials line up
+        GemvPlan pl;
+        if (!gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl)) return cudaErrorInvalidConfiguration;
+        GemvParams p{};
+        p.w[0] = static_cast<const uint8_t*>(w0);
+        p.w[1] = static_cast<const uint8_t*>(w1 ? w1 : w0);
+        p.act = act;
+        p.out = out;
+        p.partial = static_cast<float*>(ws);
+        p.M = (uint32_t)M; p.K = (uint32_t)K; p.N = (uint32_t)N;
+        p.m0 = (uint32_t)m0; p.mcount = mc;
+        p.row_bytes = (uint32_t)(K / fmt_block_size(fmt) * fmt_block_bytes(fmt));
+        p.nslices = pl.nslices; p.spc = pl.spc; p.nchunks = pl.nchunks; p.ksplit = pl.ksplit; p.rgs = pl.rgs;
+        p.srow = pl.srow; p.stage_bytes = pl.stage_bytes; p.nstages = pl.nstages; p.total_units = pl.total_units;
+        p.red_off = pl.red_off; p.stage_off = pl.stage_off;
+        p.act_dtype = act_dtype; p.out_dtype = out_dtype;
+        p.w_bytes = (unsigned long long)N * p.row_bytes;
+        p.status = status;
+        if (pl.ksplit > 1) {
+            size_t need = (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float);
+            if (!ws || ws_bytes < need) { *ws_too_small = true; return cudaSuccess; }
+            need_reduce = true;
+            red_ksplit = pl.ksplit;
+        }
+        cudaError_t e;
+        switch (fmt) {
+        case FMT_Q4_0: e = swiglu ? launch_gemv_fmt<FMT_Q4_0, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q4_0, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q8_0: e = swiglu ? launch_gemv_fmt<FMT_Q8_0, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q8_0, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q4_K: e = swiglu ? launch_gemv_fmt<FMT_Q4_K, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q4_K, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q6_K: e = swiglu ? launch_gemv_fmt<FMT_Q6_K, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q6_K, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        default: return cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    if (need_reduce) {
+        size_t mn = M * N;
+        int grid = (int)((mn + 255) / 256);
+        if (grid > sm_count * 8) grid = sm_count * 8;
+        splitk_reduce_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(ws), out, out_dtype, mn, red_ksplit, swiglu ? 1 : 0);
+        return cudaGetLastError();
+    }
+    return cudaSuccess;
+}
+
+}  // namespace b200q

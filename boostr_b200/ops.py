@@ -1,0 +1,144 @@
+"""Host-side mirror of boostr's quantized ops, bound to the sm_100a library.
+
+``dequantize`` ~ DequantOps::dequantize (src/quant/traits/dequant.rs:15),
+``quant_matmul`` / ``quant_matmul_batch`` / ``quant_swiglu`` ~ QuantMatmulOps
+(src/quant/traits/quant_matmul.rs:22-39,122-127).  Same argument meaning, same shape rules
+and the same error texts as the reference's CUDA implementation
+(src/quant/cuda/quant_matmul/impl_ops.rs:112-172, src/quant/cuda/dequant.rs:74-146).  The
+calls enqueue on torch's current stream and do not synchronise.  torch supplies device
+memory and the stream handle only; all arithmetic happens in ``libb200q.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Sequence
+
+import torch
+
+from . import _cabi
+from .format import QuantError
+from .tensor import QuantTensor
+
+_DT = {torch.float32: _cabi.DT_F32, torch.bfloat16: _cabi.DT_BF16, torch.float16: _cabi.DT_F16,
+       torch.float64: _cabi.DT_F64}
+
+_workspaces: dict = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise QuantError(f"{what} must live on a CUDA device: this library has no CPU path")
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    """Scratch buffer reused across calls on one device (grown on demand, never shrunk)."""
+    key = (torch.device(device).index, torch.cuda.current_stream().cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def dequantize(qt: QuantTensor, target_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    if target_dtype not in _DT:
+        raise QuantError(f"dequantize target must be float, got {target_dtype}")
+    _require_cuda(qt.storage, "QuantTensor")
+    out = torch.empty(qt.shape, dtype=target_dtype, device=qt.device)
+    with torch.cuda.device(qt.device):
+        _cabi.check(_cabi.lib().b200q_dequantize(qt.format.format_id, qt.storage.data_ptr(), qt.num_blocks(),
+                                                 out.data_ptr(), _DT[target_dtype], _stream()))
+    return out
+
+
+def _check_act(op: str, activation: torch.Tensor, weight: QuantTensor, allow_bf16: bool):
+    ok = (torch.float32, torch.bfloat16) if allow_bf16 else (torch.float32,)
+    if activation.dtype not in ok:
+        raise QuantError(f"{op} activation must be F32, got {activation.dtype}")
+    if len(weight.shape) != 2:
+        raise QuantError(f"{op} weight must be 2D [N, K], got {list(weight.shape)}")
+    n, k = weight.shape
+    if activation.dim() == 0:
+        raise QuantError(f"{op} activation must be at least 1D")
+    if activation.shape[-1] != k:
+        raise QuantError(f"{op} dimension mismatch: activation K={activation.shape[-1]}, weight K={k}")
+    _require_cuda(activation, "activation")
+    _require_cuda(weight.storage, "QuantTensor")
+    act = activation.contiguous()
+    if act.data_ptr() % 16:
+        act = act.clone()
+    m = act.numel() // k
+    return act, m, k, n
+
+
+def quant_matmul(activation: torch.Tensor, weight: QuantTensor, out_dtype: torch.dtype = torch.float32,
+                 allow_bf16_activation: bool = True) -> torch.Tensor:
+    """activation [..., M, K] x weight [N, K] -> [..., M, N] (F32 unless out_dtype says otherwise)."""
+    act, m, k, n = _check_act("quant_matmul", activation, weight, allow_bf16_activation)
+    out = torch.empty((*activation.shape[:-1], n), dtype=out_dtype, device=act.device)
+    if m == 0:
+        return out
+    L = _cabi.lib()
+    with torch.cuda.device(act.device):
+        need = L.b200q_workspace_bytes(_cabi.OP_QUANT_MATMUL, weight.format.format_id, m, k, n)
+        ws = workspace(need, act.device) if need else None
+        _cabi.check(L.b200q_quant_matmul(weight.format.format_id, act.data_ptr(), _DT[act.dtype],
+                                         weight.storage.data_ptr(), out.data_ptr(), _DT[out_dtype], m, k, n,
+                                         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                         _stream()))
+    return out
+
+
+def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
+                       out_dtype: torch.dtype = torch.float32) -> List[torch.Tensor]:
+    """One activation against several weights sharing K (q/k/v, gate/up)."""
+    if not weights:
+        return []
+    acts = [_check_act("quant_matmul", activation, w, True) for w in weights]
+    act, m, k, _ = acts[0]
+    outs = [torch.empty((*activation.shape[:-1], a[3]), dtype=out_dtype, device=act.device) for a in acts]
+    if m == 0:
+        return outs
+    L = _cabi.lib()
+    nw = len(weights)
+    fmts = (ctypes.c_int * nw)(*[w.format.format_id for w in weights])
+    wptr = (ctypes.c_void_p * nw)(*[w.storage.data_ptr() for w in weights])
+    ns = (ctypes.c_size_t * nw)(*[a[3] for a in acts])
+    optr = (ctypes.c_void_p * nw)(*[o.data_ptr() for o in outs])
+    with torch.cuda.device(act.device):
+        need = max(L.b200q_workspace_bytes(_cabi.OP_QUANT_MATMUL, w.format.format_id, m, k, a[3])
+                   for w, a in zip(weights, acts))
+        ws = workspace(need, act.device) if need else None
+        _cabi.check(L.b200q_quant_matmul_batch(nw, fmts, wptr, ns, optr, act.data_ptr(), _DT[act.dtype],
+                                               _DT[out_dtype], m, k, ws.data_ptr() if ws is not None else None,
+                                               ws.numel() if ws is not None else 0, _stream()))
+    return outs
+
+
+def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: QuantTensor,
+                 out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """silu(activation x gate^T) * (activation x up^T); gate and up share N, K and format."""
+    if gate_weight.format != up_weight.format or tuple(gate_weight.shape) != tuple(up_weight.shape):
+        raise QuantError("quant_swiglu: gate and up weights must have the same format and shape")
+    act, m, k, n = _check_act("quant_swiglu", activation, gate_weight, True)
+    out = torch.empty((*activation.shape[:-1], n), dtype=out_dtype, device=act.device)
+    if m == 0:
+        return out
+    L = _cabi.lib()
+    with torch.cuda.device(act.device):
+        need = L.b200q_workspace_bytes(_cabi.OP_QUANT_SWIGLU, gate_weight.format.format_id, m, k, n)
+        ws = workspace(need, act.device) if need else None
+        _cabi.check(L.b200q_quant_swiglu(gate_weight.format.format_id, act.data_ptr(), _DT[act.dtype],
+                                         gate_weight.storage.data_ptr(), up_weight.storage.data_ptr(), out.data_ptr(),
+                                         _DT[out_dtype], m, k, n, ws.data_ptr() if ws is not None else None,
+                                         ws.numel() if ws is not None else 0, _stream()))
+    return out
+
+
+def check_device_status() -> None:
+    """Synchronises the current stream and raises if a kernel gave up on a bounded wait."""
+    _cabi.check(_cabi.lib().b200q_check_device_status(_stream()))

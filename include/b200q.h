@@ -1,0 +1,158 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) quantized-linear library.
+ *
+ * This is the boundary a boostr maintainer binds from Rust (`extern "C"`) in place of
+ * the PTX modules boostr's CUDA backend loads today.  Every entry point names the
+ * boostr interface it stands in for (paths are relative to the boostr repository).
+ *
+ * Conventions (same as boostr's CUDA backend, src/quant/cuda/quant_matmul/impl_ops.rs:112-172):
+ *   - all `const void* w / act`, `void* out / ws` arguments are DEVICE pointers
+ *     (boostr passes `Tensor::ptr()` / `Storage::ptr()` as u64);
+ *   - the caller allocates outputs and scratch; the library never allocates or frees;
+ *   - work is enqueued on `stream` (a CUstream / cudaStream_t, may be NULL for the
+ *     default stream) and the call returns without synchronising;
+ *   - weights are packed blocks, row-major [N, K] with blocks along K and no row
+ *     padding (src/quant/format.rs:5-20); `w` must be 16-byte aligned;
+ *   - activations are contiguous row-major [M, K]; outputs are row-major [M, N];
+ *   - every function returns a b200q_status; on failure `b200q_last_error()` gives the
+ *     reason for the calling thread (the counterpart of Error::QuantError { reason },
+ *     src/error.rs:22-27).  Nothing aborts, traps or throws.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200Q_API
+#else
+#define B200Q_API __attribute__((visibility("default")))
+#endif
+
+typedef enum b200q_status {
+    B200Q_OK = 0,
+    B200Q_ERR_INVALID_ARG = 1,
+    B200Q_ERR_UNSUPPORTED_FORMAT = 2,
+    B200Q_ERR_BAD_SHAPE = 3,
+    B200Q_ERR_WORKSPACE_TOO_SMALL = 4,
+    B200Q_ERR_CUDA = 5,
+    B200Q_ERR_TIMEOUT = 6,
+    B200Q_ERR_UNSUPPORTED_DTYPE = 7
+} b200q_status;
+
+/* Block formats; values are QuantFormat::format_id (src/quant/format.rs:204-230). */
+typedef enum b200q_format {
+    B200Q_Q4_0 = 0,
+    B200Q_Q8_0 = 4,
+    B200Q_Q4_K = 8,
+    B200Q_Q6_K = 10
+} b200q_format;
+
+/* Element types of activations / outputs (numr DType subset). */
+typedef enum b200q_dtype {
+    B200Q_F32 = 0,
+    B200Q_BF16 = 1,
+    B200Q_F16 = 2,
+    B200Q_F64 = 3 /* dequantize target only */
+} b200q_dtype;
+
+/* Operations that may need scratch memory; argument of b200q_workspace_bytes. */
+typedef enum b200q_op {
+    B200Q_OP_QUANT_MATMUL = 0,
+    B200Q_OP_QUANT_SWIGLU = 1
+} b200q_op;
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+B200Q_API int b200q_version(void);
+
+/* Message of the last failed call made by this thread ("" if none). */
+B200Q_API const char* b200q_last_error(void);
+
+/* QuantFormat::block_size / block_bytes (src/quant/format.rs:81-140); 0 for an unknown format. */
+B200Q_API size_t b200q_block_size(int format);
+B200Q_API size_t b200q_block_bytes(int format);
+
+/* QuantFormat::storage_bytes (src/quant/format.rs:142-157): bytes of `numel` elements;
+ * B200Q_ERR_BAD_SHAPE when numel is not a multiple of the block size. */
+B200Q_API int b200q_storage_bytes(int format, size_t numel, size_t* out_bytes);
+
+/*
+ * DequantOps::dequantize (src/quant/traits/dequant.rs:15; CUDA impl
+ * src/quant/cuda/dequant.rs:74-146, kernels src/quant/cuda/kernels/dequant.cu:18-206).
+ * Decodes `nblocks` packed blocks at `w` into nblocks * block_size elements of
+ * `out_dtype` at `out` (F32, BF16, F16 or F64).  16-bit targets are one
+ * round-to-nearest-even rounding of the exact f32 value; there is no intermediate
+ * f32 tensor and no second cast pass.
+ */
+B200Q_API int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int out_dtype, void* stream);
+
+/*
+ * Scratch bytes b200q_quant_matmul / b200q_quant_swiglu need for this shape (0 for most
+ * decode shapes).  Scratch contents need no initialisation and carry nothing between calls.
+ * Returns 0 as well when the arguments are invalid; the op itself reports the error.
+ */
+B200Q_API size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N);
+
+/*
+ * QuantMatmulOps::quant_matmul (src/quant/traits/quant_matmul.rs:23; CUDA impl
+ * src/quant/cuda/quant_matmul/impl_ops.rs:112-172, kernels
+ * src/quant/cuda/kernels/quant_gemv.cu and quant_matmul.cu):
+ *     out[M,N] = act[M,K] x dequant(w[N,K])^T
+ * act_dtype: F32 (what boostr accepts) or BF16 (extension); out_dtype: F32 (what boostr
+ * returns), BF16 or F16.  Requires M, K, N > 0 and K a multiple of the block size.
+ * Q4_K / Q6_K follow boostr's CPU numerics: each 256-wide run of an activation row is
+ * quantised to int8 with one f32 scale (Q8_K) and the dot products are integer
+ * (src/quant/cpu/kernels/quant_matmul.rs:107-158); Q4_0 / Q8_0 keep the activation
+ * precision (f32 there, :193-209).
+ */
+B200Q_API int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype,
+                                 size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * QuantMatmulOps::quant_matmul_batch (src/quant/traits/quant_matmul.rs:30-39; CUDA impl
+ * src/quant/cuda/quant_matmul/impl_ops.rs:174-335): one activation against `n_weights`
+ * weights that share K.  formats[i], w[i], N[i], out[i] describe weight i; out[i] is [M, N[i]].
+ * `ws` must hold the largest b200q_workspace_bytes over the weights.
+ */
+B200Q_API int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N,
+                                       void* const* out, const void* act, int act_dtype, int out_dtype, size_t M,
+                                       size_t K, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * QuantMatmulOps::quant_swiglu (src/quant/traits/quant_matmul.rs:122-127; CUDA impl
+ * src/quant/cuda/quant_matmul/impl_ops.rs:337-441):
+ *     out[M,N] = silu(act x Wg^T) * (act x Wu^T),   silu(x) = x / (1 + exp(-x))
+ * Wg and Wu share format, N and K.
+ */
+B200Q_API int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w_gate, const void* w_up,
+                                 void* out, int out_dtype, size_t M, size_t K, size_t N, void* ws, size_t ws_bytes,
+                                 void* stream);
+
+/*
+ * Tensor-parallel shard extraction, HOST memory to HOST memory.  boostr shards dense
+ * weights with scatter_to_rank (src/distributed/tensor_parallel.rs:258-300) and has no
+ * quantised counterpart; this cuts rank `rank` of `world` out of a packed [N,K] weight:
+ *   dim 0 (column-parallel): rows [rank*N/world, (rank+1)*N/world) — a contiguous byte range;
+ *   dim 1 (row-parallel):   columns [rank*K/world, ...) of every row, repacked tightly;
+ *                           K/world must be a multiple of the block size.
+ * `dst` receives (N/world)*K or N*(K/world) elements' worth of blocks.
+ */
+B200Q_API int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, int rank, int world,
+                               void* dst, size_t dst_bytes);
+
+/*
+ * Waits for `stream` and reports whether any kernel of this library gave up on a
+ * bounded wait since the last call (B200Q_ERR_TIMEOUT) — the library never spins
+ * without a limit.  Diagnostic; not needed in normal operation.
+ */
+B200Q_API int b200q_check_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

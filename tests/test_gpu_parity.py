@@ -1,0 +1,293 @@
+"""GPU parity: the CUDA library (through its C ABI) against the CPU oracle on the same seeded bytes.
+
+Bars: dequantised weights bit-exact; matmul max|y - y_ref| / max|y_ref| <= 1e-3 for the
+fp32-accumulate kernels (the tighter per-family bounds asserted below are what the design
+is expected to reach) and <= 1e-2 for the bf16 tensor-core prefill path.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from boostr_b200 import synth
+from boostr_b200.format import QuantError, QuantFormat as F
+from util import describe_mismatch, rel_err, seed_of
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+FMTS = ["Q4_0", "Q8_0", "Q4_K", "Q6_K"]
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "dequant_witness.npz")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from boostr_b200 import ops as o
+
+    return o
+
+
+def _qt(fmt, wbytes, n, k):
+    from boostr_b200.tensor import QuantTensor
+
+    return QuantTensor.from_bytes(wbytes, fmt, (n, k), device="cuda")
+
+
+# ------------------------------------------------------------------ dequantize
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("nblk", [1, 3, 8, 17, 1000])
+def test_dequant_f32_bit_exact(ops, oracle, fmt, nblk):
+    f = F.parse(fmt)
+    rng = synth.rng_for(20, f.value * 100 + nblk % 97)
+    blocks = synth._GEN[f](rng, nblk)
+    from boostr_b200.tensor import QuantTensor
+
+    qt = QuantTensor.from_bytes(blocks, f, (nblk * f.block_size,), device="cuda")
+    got = ops.dequantize(qt, torch.float32).cpu().numpy()
+    want = oracle.dequantize_f32(fmt, blocks)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), describe_mismatch(got, want)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequant_16bit_and_f64(ops, oracle, fmt):
+    f = F.parse(fmt)
+    nblk = 64 * (256 // f.block_size) + (3 if f.block_size == 32 else 0)
+    rng = synth.rng_for(21, f.value)
+    blocks = synth._GEN[f](rng, nblk)
+    from boostr_b200.tensor import QuantTensor
+
+    qt = QuantTensor.from_bytes(blocks, f, (nblk * f.block_size,), device="cuda")
+    bf = ops.dequantize(qt, torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(bf, oracle.dequantize_16(fmt, blocks, "bf16"))
+    fh = ops.dequantize(qt, torch.float16).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(fh, oracle.dequantize_16(fmt, blocks, "f16"))
+    f64 = ops.dequantize(qt, torch.float64).cpu().numpy()
+    assert np.array_equal(f64, oracle.dequantize_f32(fmt, blocks).astype(np.float64))
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_dequant_golden_witness(ops, fmt):
+    g = np.load(GOLD)
+    f = F.parse(fmt)
+    blocks = g[f"{fmt}_blocks"]
+    from boostr_b200.tensor import QuantTensor
+
+    qt = QuantTensor.from_bytes(blocks, f, (blocks.size // f.block_bytes * f.block_size,), device="cuda")
+    got = ops.dequantize(qt, torch.float32).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), g[f"{fmt}_f32"].view(np.uint32))
+
+
+def test_dequant_full_size_checksum(ops, oracle):
+    # Q4_K weight of BASELINE config 3 (14336 x 4096): every 997th block against the oracle,
+    # plus linearity of the whole output in the block scale (size-independent property).
+    f = F.Q4_K
+    n, k = 14336, 4096
+    rng = synth.rng_for(3, 1)
+    w = synth.weight_bytes(f, rng, n, k)
+    qt = _qt(f, w, n, k)
+    got = ops.dequantize(qt, torch.bfloat16)
+    blocks = w.reshape(-1, 144)
+    pick = np.arange(0, blocks.shape[0], 997)
+    want = oracle.dequantize_16("Q4_K", np.ascontiguousarray(blocks[pick]).reshape(-1), "bf16").reshape(len(pick), 256)
+    g = got.view(torch.int16).reshape(-1, 256)[torch.from_numpy(pick).cuda()].cpu().numpy().view(np.uint16)
+    assert np.array_equal(g, want)
+
+
+def test_dequant_rejects_bad_target(ops):
+    qt = _qt("Q8_0", synth.q8_0_blocks(synth.rng_for(22), 2), 2, 32)
+    with pytest.raises(QuantError):
+        ops.dequantize(qt, torch.int32)
+
+
+# ------------------------------------------------------------------ quant_matmul (GEMV / small M)
+
+SHAPES = [
+    # (M, N, K)
+    (1, 1, 256), (1, 17, 512), (2, 33, 256), (3, 64, 1024), (1, 257, 2304), (5, 100, 4096), (8, 48, 4096),
+    (9, 40, 512), (16, 130, 4096), (1, 96, 8192), (4, 70, 14336), (12, 35, 14336), (17, 50, 1024), (33, 20, 512),
+]
+
+
+def _bound(fmt, m):
+    if fmt in ("Q4_K", "Q6_K"):
+        return 2e-6  # integer dots are exact; only the order of <= 56 f32 block terms differs
+    return 1e-5 if m <= 8 else 1e-3  # fp16 hi+lo split / single fp16 rounding of activations
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_quant_matmul_small_m(ops, oracle, fmt, m, n, k):
+    rng = synth.rng_for(23, (seed_of(fmt, m, n, k)))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    canary = torch.full((m * n + 64,), 12345.0, device="cuda")
+    got_t = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k))
+    ops.check_device_status()
+    got = got_t.cpu().numpy()
+    want = oracle.quant_matmul(fmt, act, w, n, threads=8)
+    e_max, e_rms = rel_err(got, want)
+    assert got.shape == (m, n)
+    assert np.isfinite(got).all()
+    assert e_max <= _bound(fmt, m), f"{fmt} M={m} N={n} K={k}: max-norm err {e_max:.3e} rms {e_rms:.3e}\n" + describe_mismatch(got, want)
+    assert torch.all(canary == 12345.0)
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q6_K"])
+def test_kquant_bit_exact_when_k_fits_one_chunk(ops, oracle, fmt):
+    # K <= 4096: block terms are added in K order exactly as the CPU loop does
+    rng = synth.rng_for(24, F.parse(fmt).value)
+    m, n, k = 3, 77, 4096
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k)).cpu().numpy()
+    want = oracle.quant_matmul(fmt, act, w, n, threads=4)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), describe_mismatch(got, want)
+
+
+@pytest.mark.parametrize("fmt", ["Q4_0", "Q8_0"])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (2, 5, 96), (1, 40, 288), (9, 33, 4128)])
+def test_ragged_k_for_32_blocks(ops, oracle, fmt, m, n, k):
+    rng = synth.rng_for(25, k % 89 + m)
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul(fmt, act, w, n)
+    e_max, _ = rel_err(got, want)
+    assert e_max <= _bound(fmt, m), f"err {e_max:.3e}\n" + describe_mismatch(got, want)
+
+
+def test_known_answers(ops):
+    # the reference's closed-form cases (src/quant/cpu/kernels/quant_matmul.rs:415-510)
+    def f16b(x):
+        return np.array([x], np.float16).view(np.uint8)
+
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = f16b(2.0)
+    blk[2:] = 0x99
+    out = ops.quant_matmul(torch.ones(1, 32, device="cuda"), _qt("Q4_0", blk, 1, 32))
+    assert out.shape == (1, 1) and abs(out.item() - 64.0) < 1e-4
+    b8 = np.zeros(34, np.uint8)
+    b8[0:2] = f16b(0.5)
+    b8[2:] = 4
+    act = torch.ones(2, 32, device="cuda")
+    act[1] = 0.5
+    out = ops.quant_matmul(act, _qt("Q8_0", b8, 1, 32)).cpu().numpy()
+    assert abs(out[0, 0] - 64.0) < 1e-4 and abs(out[1, 0] - 32.0) < 1e-4
+    b1 = blk.copy()
+    b1[0:2] = f16b(1.0)
+    b3 = blk.copy()
+    b3[0:2] = f16b(3.0)
+    out = ops.quant_matmul(torch.ones(1, 32, device="cuda"), _qt("Q4_0", np.concatenate([b1, b3]), 2, 32)).cpu().numpy()
+    assert abs(out[0, 0] - 32.0) < 1e-4 and abs(out[0, 1] - 96.0) < 1e-4
+
+
+def test_zero_activation_and_leading_dims(ops, oracle):
+    rng = synth.rng_for(26)
+    n, k = 40, 512
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    qt = _qt("Q4_K", w, n, k)
+    z = ops.quant_matmul(torch.zeros(2, k, device="cuda"), qt)
+    assert torch.all(z == 0)
+    act = synth.activations(rng, 6, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda().reshape(2, 3, k), qt)
+    assert got.shape == (2, 3, n)
+    want = oracle.quant_matmul("Q4_K", act, w, n)
+    assert rel_err(got.reshape(6, n).cpu().numpy(), want)[0] < 2e-6
+
+
+def test_bf16_activation_extension(ops, oracle):
+    rng = synth.rng_for(27)
+    m, n, k = 4, 64, 1024
+    act = synth.activations(rng, m, k)
+    a_bf = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(act)).reshape(m, k)
+    for fmt in FMTS:
+        w = synth.weight_bytes(fmt, rng, n, k)
+        got = ops.quant_matmul(torch.from_numpy(a_bf).cuda().to(torch.bfloat16), _qt(fmt, w, n, k)).cpu().numpy()
+        want = oracle.quant_matmul(fmt, a_bf, w, n)  # oracle upcasts bf16 -> f32 exactly
+        assert rel_err(got, want)[0] <= _bound(fmt, m), fmt
+
+
+def test_run_twice_is_bitwise_identical(ops):
+    rng = synth.rng_for(28)
+    m, n, k = 7, 300, 4096
+    act = torch.from_numpy(synth.activations(rng, m, k)).cuda()
+    for fmt in FMTS:
+        qt = _qt(fmt, synth.weight_bytes(fmt, rng, n, k), n, k)
+        a = ops.quant_matmul(act, qt)
+        b = ops.quant_matmul(act, qt)
+        assert torch.equal(a, b), fmt
+
+
+def test_argument_errors(ops):
+    rng = synth.rng_for(29)
+    qt = _qt("Q8_0", synth.weight_bytes("Q8_0", rng, 4, 64), 4, 64)
+    with pytest.raises(QuantError, match="dimension mismatch"):
+        ops.quant_matmul(torch.ones(2, 32, device="cuda"), qt)
+    with pytest.raises(QuantError, match="must be F32"):
+        ops.quant_matmul(torch.ones(2, 64, device="cuda", dtype=torch.float16), qt)
+    from boostr_b200.tensor import QuantTensor
+
+    with pytest.raises(QuantError, match="not a multiple"):
+        QuantTensor.from_bytes(np.zeros(34, np.uint8), "Q8_0", (1, 33))
+    with pytest.raises(QuantError, match="expected 34 bytes"):
+        QuantTensor.from_bytes(np.zeros(35, np.uint8), "Q8_0", (1, 32))
+
+
+# ------------------------------------------------------------------ swiglu / batch
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,n,k", [(1, 48, 512), (3, 130, 4096), (10, 64, 1024), (2, 40, 14336)])
+def test_quant_swiglu(ops, oracle, fmt, m, n, k):
+    rng = synth.rng_for(30, seed_of(fmt, m, n, k))
+    act = synth.activations(rng, m, k)
+    wg = synth.weight_bytes(fmt, rng, n, k)
+    wu = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt(fmt, wg, n, k), _qt(fmt, wu, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_swiglu(fmt, act, wg, wu, n, threads=4)
+    e_max, _ = rel_err(got, want)
+    assert e_max <= max(_bound(fmt, m) * 4, 1e-5), f"err {e_max:.3e}\n" + describe_mismatch(got, want)
+
+
+def test_quant_matmul_batch_mixed_formats(ops, oracle):
+    rng = synth.rng_for(31)
+    m, k = 2, 1024
+    act = synth.activations(rng, m, k)
+    specs = [("Q4_K", 64), ("Q4_K", 32), ("Q6_K", 32)]
+    ws = [synth.weight_bytes(f, rng, n, k) for f, n in specs]
+    outs = ops.quant_matmul_batch(torch.from_numpy(act).cuda(), [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)])
+    for (f, n), w, o in zip(specs, ws, outs):
+        want = oracle.quant_matmul(f, act, w, n)
+        assert rel_err(o.cpu().numpy(), want)[0] < 2e-6
+
+
+# ------------------------------------------------------------------ BASELINE shapes
+
+
+@pytest.mark.parametrize("fmt,m,n,k", [
+    ("Q4_0", 1, 4096, 4096),      # config 1
+    ("Q8_0", 1, 11008, 4096),     # config 2
+    ("Q8_0", 8, 11008, 4096),
+    ("Q6_K", 1, 128256, 4096),    # config 4
+    ("Q6_K", 16, 128256, 4096),
+    ("Q4_K", 1, 14336, 4096),     # config 5 layer shapes
+    ("Q6_K", 1, 4096, 14336),
+    ("Q4_K", 16, 4096, 4096),
+    ("Q6_K", 16, 4096, 14336),
+])
+def test_baseline_shapes(ops, oracle, fmt, m, n, k):
+    rng = synth.rng_for(2, seed_of(fmt, m, n))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul(fmt, act, w, n, threads=os.cpu_count() or 8)
+    e_max, e_rms = rel_err(got, want)
+    print(f"{fmt} M={m} N={n} K={k}: max-norm {e_max:.2e} rms {e_rms:.2e}")
+    assert e_max <= _bound(fmt, m), describe_mismatch(got, want)
