@@ -36,6 +36,7 @@ SIGNATURES = {
                                    c_size_t, c_void_p, c_size_t, c_void_p]),
     "b200q_shard_pack": (c_int, [c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_int, c_void_p, c_size_t]),
     "b200q_check_device_status": (c_int, [c_void_p]),
+    "b200q_launch_count": (ctypes.c_ulonglong, []),
 }
 
 _lib = None

@@ -3,6 +3,7 @@
 // thread-local error string in place of Error::QuantError { reason }.
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -25,6 +26,13 @@ cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, in
 }  // namespace b200q
 
 using namespace b200q;
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+namespace b200q {
+void note_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+}  // namespace b200q
 
 // One status word per device image of this library; kernels receive its address.
 __device__ unsigned int g_status_word = 0;
@@ -256,6 +264,8 @@ int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, i
     }
     return fail(B200Q_ERR_INVALID_ARG, "shard_pack: dim must be 0 or 1, got %d", dim);
 }
+
+unsigned long long b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int b200q_check_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

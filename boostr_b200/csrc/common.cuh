@@ -26,6 +26,9 @@ __host__ __device__ constexpr int fmt_block_bytes(int f) {
 // Bytes of one 256-element run of a row ("slice"): the unit one warp of the small-M kernel owns.
 __host__ __device__ constexpr int fmt_slice_bytes(int f) { return fmt_block_bytes(f) * (256 / fmt_block_size(f)); }
 
+// Host-side count of kernel launches issued by the library (see b200q_launch_count).
+void note_launch(unsigned n = 1);
+
 // ---------------------------------------------------------------- shared memory / mbarrier
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -166,6 +166,7 @@ cudaError_t launch_dequant_fmt(const void* w, size_t nblocks, void* out, int out
     case DT_F64: dequant_kernel<FMT, double><<<grid, 256, 0, st>>>(wp, static_cast<double*>(out), nunits, tail); break;
     default: return cudaErrorInvalidValue;
     }
+    note_launch();
     return cudaGetLastError();
 }
 

@@ -701,6 +701,7 @@ cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem,
         attr_set[dev] = true;
     }
     k<<<grid, threads, smem, st>>>(p);
+    note_launch();
     return cudaGetLastError();
 }
 
@@ -843,6 +844,7 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         int grid = (int)((mn + 255) / 256);
         if (grid > sm_count * 8) grid = sm_count * 8;
         splitk_reduce_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(ws), out, out_dtype, mn, red_ksplit, swiglu ? 1 : 0);
+        note_launch();
         return cudaGetLastError();
     }
     return cudaSuccess;

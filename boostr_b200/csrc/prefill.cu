@@ -30,6 +30,7 @@ cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, in
     int grid = (int)(want < (size_t)sm_count * 8 ? want : (size_t)sm_count * 8);
     if (grid < 1) grid = 1;
     swiglu_gate_kernel<<<grid, 256, 0, st>>>(gate, up, out, out_dtype, n);
+    note_launch();
     return cudaGetLastError();
 }
 

@@ -75,11 +75,22 @@ def _check_act(op: str, activation: torch.Tensor, weight: QuantTensor, allow_bf1
     return act, m, k, n
 
 
+def _out_buffer(out, shape, dtype, device):
+    if out is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or not out.is_contiguous() or out.device != device:
+        raise QuantError(f"out must be a contiguous {dtype} tensor of shape {list(shape)} on {device}")
+    return out
+
+
 def quant_matmul(activation: torch.Tensor, weight: QuantTensor, out_dtype: torch.dtype = torch.float32,
-                 allow_bf16_activation: bool = True) -> torch.Tensor:
-    """activation [..., M, K] x weight [N, K] -> [..., M, N] (F32 unless out_dtype says otherwise)."""
+                 allow_bf16_activation: bool = True, out: torch.Tensor = None) -> torch.Tensor:
+    """activation [..., M, K] x weight [N, K] -> [..., M, N] (F32 unless out_dtype says otherwise).
+
+    ``out`` lets the caller supply the result buffer (as boostr's CUDA backend allocates the
+    output before the launch); with it the call allocates nothing, which CUDA-graph capture needs."""
     act, m, k, n = _check_act("quant_matmul", activation, weight, allow_bf16_activation)
-    out = torch.empty((*activation.shape[:-1], n), dtype=out_dtype, device=act.device)
+    out = _out_buffer(out, (*activation.shape[:-1], n), out_dtype, act.device)
     if m == 0:
         return out
     L = _cabi.lib()
@@ -94,13 +105,14 @@ def quant_matmul(activation: torch.Tensor, weight: QuantTensor, out_dtype: torch
 
 
 def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
-                       out_dtype: torch.dtype = torch.float32) -> List[torch.Tensor]:
+                       out_dtype: torch.dtype = torch.float32, outs: Sequence[torch.Tensor] = None) -> List[torch.Tensor]:
     """One activation against several weights sharing K (q/k/v, gate/up)."""
     if not weights:
         return []
     acts = [_check_act("quant_matmul", activation, w, True) for w in weights]
     act, m, k, _ = acts[0]
-    outs = [torch.empty((*activation.shape[:-1], a[3]), dtype=out_dtype, device=act.device) for a in acts]
+    outs = [_out_buffer(None if outs is None else outs[i], (*activation.shape[:-1], a[3]), out_dtype, act.device)
+            for i, a in enumerate(acts)]
     if m == 0:
         return outs
     L = _cabi.lib()
@@ -120,12 +132,12 @@ def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
 
 
 def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: QuantTensor,
-                 out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                 out_dtype: torch.dtype = torch.float32, out: torch.Tensor = None) -> torch.Tensor:
     """silu(activation x gate^T) * (activation x up^T); gate and up share N, K and format."""
     if gate_weight.format != up_weight.format or tuple(gate_weight.shape) != tuple(up_weight.shape):
         raise QuantError("quant_swiglu: gate and up weights must have the same format and shape")
     act, m, k, n = _check_act("quant_swiglu", activation, gate_weight, True)
-    out = torch.empty((*activation.shape[:-1], n), dtype=out_dtype, device=act.device)
+    out = _out_buffer(out, (*activation.shape[:-1], n), out_dtype, act.device)
     if m == 0:
         return out
     L = _cabi.lib()
@@ -137,6 +149,11 @@ def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: 
                                          _DT[out_dtype], m, k, n, ws.data_ptr() if ws is not None else None,
                                          ws.numel() if ws is not None else 0, _stream()))
     return out
+
+
+def launch_count() -> int:
+    """Kernel launches issued by the library so far in this process."""
+    return int(_cabi.lib().b200q_launch_count())
 
 
 def check_device_status() -> None:

@@ -152,6 +152,13 @@ B200Q_API int b200q_shard_pack(int format, const void* src, size_t N, size_t K, 
  */
 B200Q_API int b200q_check_device_status(void* stream);
 
+/*
+ * Number of kernel launches this library has issued in the calling process (all threads,
+ * all devices).  Launches recorded while a stream is being captured count once, at capture.
+ * Diagnostic: lets a harness state how many of this library's kernels ran in a timed region.
+ */
+B200Q_API unsigned long long b200q_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif
