@@ -54,6 +54,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase (try_wait may suspend the thread for a while when it fails).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -63,7 +75,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // status code and stops using the data it waited for.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
-    for (int i = 0; i < 16; ++i)
+    for (int i = 0; i < 128; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
@@ -89,40 +101,18 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------- shared-memory loads
+// Plain C++ loads (not asm) so the compiler can schedule them freely between the barrier
+// operations, whose asm statements carry memory clobbers.
 
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-    return v;
-}
+__device__ __forceinline__ uint32_t lds32(const uint8_t* a) { return *reinterpret_cast<const uint32_t*>(a); }
+__device__ __forceinline__ uint2 lds64(const uint8_t* a) { return *reinterpret_cast<const uint2*>(a); }
+__device__ __forceinline__ uint4 lds128(const uint8_t* a) { return *reinterpret_cast<const uint4*>(a); }
+__device__ __forceinline__ uint32_t lds16(const uint8_t* a) { return *reinterpret_cast<const unsigned short*>(a); }
 // 32-bit word at a 2-byte-aligned shared address.
-__device__ __forceinline__ uint32_t lds32_u(uint32_t a) {
-    uint32_t base = a & ~3u;
-    uint32_t sh = (a & 3u) * 8u;
-    uint32_t w0 = lds32(base), w1 = lds32(base + 4);
-    return __funnelshift_r(w0, w1, sh);
-}
-// Two consecutive 32-bit words at a 2-byte-aligned shared address.
-__device__ __forceinline__ uint2 lds64_u(uint32_t a) {
-    uint32_t base = a & ~3u;
-    uint32_t sh = (a & 3u) * 8u;
-    uint32_t w0 = lds32(base), w1 = lds32(base + 4), w2 = lds32(base + 8);
-    return make_uint2(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh));
+__device__ __forceinline__ uint32_t lds32_u(const uint8_t* a) {
+    const uintptr_t v = reinterpret_cast<uintptr_t>(a);
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(v & ~(uintptr_t)3);
+    return __funnelshift_r(base[0], base[1], (uint32_t)(v & 3u) * 8u);
 }
 
 // ------------------------------------------------------------------------------- MMA
@@ -130,27 +120,27 @@ __device__ __forceinline__ uint2 lds64_u(uint32_t a) {
 // D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col) + C
 __device__ __forceinline__ void mma_u8s8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1, const int (&c)[4]) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 // D(16x8,s32) = A(16x16,s8,row) * B(16x8,s8,col) + C
 __device__ __forceinline__ void mma_s8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 // D(16x8,s32) = A(16x16,u8,row) * B(16x8,u8,col) + C
 __device__ __forceinline__ void mma_u8u8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 // D(16x8,f32) = A(16x16,f16,row) * B(16x8,f16,col) + C
 __device__ __forceinline__ void mma_f16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                             uint32_t b1, const float (&c)[4]) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));

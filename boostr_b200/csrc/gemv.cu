@@ -6,9 +6,14 @@
 //
 // Shape of the kernel
 //   * Persistent CTAs, one per SM, 16 warps each (four per scheduler, so every warp may use 128
-//     registers).  Warp 0 streams slabs of packed weight rows into a ring of shared-memory
-//     stages with 1-D bulk copies (cp.async.bulk + mbarrier byte counts), running nstages-1
-//     fills ahead; with 3-5 stages of 37-70 KB each SM keeps over 100 KB of HBM reads in flight.
+//     registers).  Slabs of packed weight rows stream into a ring of shared-memory stages
+//     through 1-D bulk copies (cp.async.bulk + mbarrier byte counts); the warps take turns
+//     requesting the next fill of the stage they have just released, so no warp is "the
+//     producer"; 3-5 stages of 37-70 KB keep over 100 KB of HBM reads in flight per SM.
+//   * There is no block-wide barrier in the steady state: stages are handed over through
+//     full/empty mbarriers and the per-slab partial sums through a second ring of mbarrier-
+//     guarded slots; the warps take turns adding up a slab published two slabs earlier, so
+//     nobody waits for the slowest warp and warps drift apart freely.
 //   * Each compute warp owns one 256-wide run of K (a "slice": one Q4_K/Q6_K block or eight
 //     Q4_0/Q8_0 blocks) of a K-chunk of up to 16 slices.  The activations of that run are
 //     prepared ONCE per launch and kept in registers as MMA B-fragments, so the only
@@ -30,6 +35,8 @@
 //   * Partial sums of the warps of a CTA meet in shared memory and are added in slice order.
 //     When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks
 //     are spread over gridDim.y and a second small kernel adds the partials.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -52,12 +59,28 @@ struct GemvParams {
     uint32_t stage_bytes;
     uint32_t nstages;
     uint32_t total_units; // slabs
-    uint32_t red_off;     // byte offset of the reduction buffer in dynamic smem
+    uint32_t red_off;     // byte offset of the reduction ring in dynamic smem
+    uint32_t red_slot_bytes;
+    uint32_t red_slots;   // slots in the reduction ring (3 or 4)
     uint32_t stage_off;   // byte offset of stage 0
+    uint32_t rows_aligned;  // 1 when every row chunk starts and ends on a 16-byte boundary
+    uint32_t contig;        // experiment: one linear copy per stage, rows unpadded
     int act_dtype, out_dtype;
     unsigned long long w_bytes;  // bytes of each weight tensor
     unsigned int* status;        // device status word (bounded-wait timeouts)
 };
+
+#ifdef B200Q_TRACE
+// Debug build only: per-CTA timeline of warps 0/7/15 (nanosecond stamps), read back by the host.
+__device__ unsigned long long g_trace[148 * 3 * 64];
+#define TRACE(slot)                                                                                          \
+    do {                                                                                                     \
+        if (lane == 0 && (warp == 0 || warp == 7 || warp == 15) && (slot) < 64 && blockIdx.x < 148)          \
+            g_trace[(blockIdx.x * 3 + (warp == 0 ? 0 : warp == 7 ? 1 : 2)) * 64 + (slot)] = global_timer_ns(); \
+    } while (0)
+#else
+#define TRACE(slot) do {} while (0)
+#endif
 
 namespace {
 
@@ -129,29 +152,29 @@ struct SliceB<FMT_Q4_K, MT, HILO> {
             uint32_t m = tl * 8 + g;
             bool on = valid && m < p.mcount;
             size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 8 * t;
-            float amax = 0.f;
-            if (on) {
+            // one round of loads: the lane's 64 activations stay in registers for both passes
+            float v[8][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float v[8];
-                    load_act8(p.act, p.act_dtype, base + 32 * j, v);
+            for (int j = 0; j < 8; ++j) {
+                if (on) load_act8(p.act, p.act_dtype, base + 32 * j, v[j]);
+                else
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-                }
+                    for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
             }
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
             amax = quad_max(amax);
             float d = __fdiv_rn(amax, 127.0f);
             float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
             uint32_t lo[2] = {0, 0}, hi[2] = {0, 0};
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                int c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                if (on) {
-                    float v[8];
-                    load_act8(p.act, p.act_dtype, base + 32 * j, v);
+                int c[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) c[i] = q8k_code(v[i], id);
-                }
+                for (int i = 0; i < 8; ++i) c[i] = q8k_code(v[j][i], id);
                 q[tl][2 * j] = pack4(c[0], c[1], c[2], c[3]);
                 q[tl][2 * j + 1] = pack4(c[4], c[5], c[6], c[7]);
                 int bsum = quad_sum(c[0] + c[1] + c[2] + c[3] + c[4] + c[5] + c[6] + c[7]) + 4096;
@@ -179,29 +202,25 @@ struct SliceB<FMT_Q6_K, MT, HILO> {
             uint32_t m = tl * 8 + g;
             bool on = valid && m < p.mcount;
             size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 4 * t;
-            float amax = 0.f;
-            if (on) {
+            float v[16][4];
 #pragma unroll
-                for (int sb = 0; sb < 16; ++sb) {
-                    float v[4];
-                    load_act4(p.act, p.act_dtype, base + 16 * sb, v);
+            for (int sb = 0; sb < 16; ++sb) {
+                if (on) load_act4(p.act, p.act_dtype, base + 16 * sb, v[sb]);
+                else
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[i]));
-                }
+                    for (int i = 0; i < 4; ++i) v[sb][i] = 0.f;
             }
+            float amax = 0.f;
+#pragma unroll
+            for (int sb = 0; sb < 16; ++sb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[sb][i]));
             amax = quad_max(amax);
             float d = __fdiv_rn(amax, 127.0f);
             float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
 #pragma unroll
-            for (int sb = 0; sb < 16; ++sb) {
-                uint32_t r = 0;
-                if (on) {
-                    float v[4];
-                    load_act4(p.act, p.act_dtype, base + 16 * sb, v);
-                    r = pack4(q8k_code(v[0], id), q8k_code(v[1], id), q8k_code(v[2], id), q8k_code(v[3], id));
-                }
-                q[tl][sb] = r;
-            }
+            for (int sb = 0; sb < 16; ++sb)
+                q[tl][sb] = pack4(q8k_code(v[sb][0], id), q8k_code(v[sb][1], id), q8k_code(v[sb][2], id), q8k_code(v[sb][3], id));
             float dd = on ? d : 0.f;
             d8[tl][0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
             d8[tl][1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
@@ -222,17 +241,32 @@ struct SliceBF16 {
         for (int tl = 0; tl < MT; ++tl) {
             uint32_t m = tl * 8 + g;
             bool on = valid && m < p.mcount;
-            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 8 * t;
-            float amax = 0.f;
+            // elements of a 32-block held by this lane: Q4_0 8t..8t+7; Q8_0 4t..4t+3 and 16+4t..16+4t+3
+            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + (FMT == FMT_Q8_0 ? 4 : 8) * t;
+            auto load_blk = [&](int b, float (&v)[8]) {
+                if constexpr (FMT == FMT_Q8_0) {
+                    float lo4[4], hi4[4];
+                    load_act4(p.act, p.act_dtype, base + 32 * b, lo4);
+                    load_act4(p.act, p.act_dtype, base + 32 * b + 16, hi4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { v[i] = lo4[i]; v[4 + i] = hi4[i]; }
+                } else {
+                    load_act8(p.act, p.act_dtype, base + 32 * b, v);
+                }
+            };
+            float v[8][8];
 #pragma unroll
             for (int b = 0; b < 8; ++b) {
-                if (on && 32u * b < kleft) {
-                    float v[8];
-                    load_act8(p.act, p.act_dtype, base + 32 * b, v);
+                if (on && 32u * b < kleft) load_blk(b, v[b]);
+                else
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-                }
+                    for (int i = 0; i < 8; ++i) v[b][i] = 0.f;
             }
+            float amax = 0.f;
+#pragma unroll
+            for (int b = 0; b < 8; ++b)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[b][i]));
             amax = quad_max(amax);
             uint32_t e = __float_as_uint(amax) >> 23;  // biased exponent (amax >= 0)
             e = e == 0 ? 127u : (e > 253u ? 253u : e);
@@ -240,17 +274,15 @@ struct SliceBF16 {
             float isc = __uint_as_float(e << 23);
 #pragma unroll
             for (int b = 0; b < 8; ++b) {
-                float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                if (on && 32u * b < kleft) load_act8(p.act, p.act_dtype, base + 32 * b, v);
                 __half hi[8], lo[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    float x = v[i] * sc;
+                    float x = v[b][i] * sc;
                     hi[i] = __float2half_rn(x);
                     lo[i] = __float2half_rn((x - __half2float(hi[i])) * 2048.0f);
                 }
                 // K order inside a 32-block follows what the weight side can unpack cheaply:
-                //   Q8_0: byte pairs   -> (0,1) (2,3) | (4,5) (6,7)
+                //   Q8_0: byte pairs of the lane's two words -> (0,1) (2,3) | (4,5) (6,7)
                 //   Q4_0: byte i holds elements 2i, 2i+1 -> lop3 yields (0,4) (1,5) | (2,6) (3,7)
                 constexpr int P8[8] = {0, 1, 2, 3, 4, 5, 6, 7};
                 constexpr int P4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
@@ -277,9 +309,22 @@ struct SliceB<FMT_Q4_0, MT, HILO> : SliceBF16<FMT_Q4_0, MT, HILO> {};
 
 // Adds the contribution of one slice (K run of 256) of weight rows g and g+8 to acc.
 // ra / rb: shared-memory byte address of the slice in row g / g+8.
+// M1: only activation row 0 exists, so accumulator columns 1 and 3 (odd activation rows) are
+// never stored and their scaling work is skipped.
 
-template <int MT, bool HILO>
-__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, uint32_t ra, uint32_t rb, int t,
+// byte i of x, zero-extended / sign-extended, in one PRMT
+template <int I>
+__device__ __forceinline__ int byte_u(uint32_t x) { return (int)__byte_perm(x, 0u, 0x4440 | I); }
+template <int I>
+__device__ __forceinline__ int byte_s(uint32_t x) {
+    // prmt selector nibble: bits 2..0 pick a byte, bit 3 replicates that byte's sign bit instead
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0u), "n"(((I | 8) << 12) | ((I | 8) << 8) | ((I | 8) << 4) | I));
+    return r;
+}
+
+template <int MT, bool HILO, bool M1>
+__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t,
                                           float (&acc)[MT][4]) {
     const int zero[4] = {0, 0, 0, 0};
     uint4 ha = lds128(ra), hb = lds128(rb);
@@ -303,24 +348,33 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, u
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
         uint2 qa = lds64(ra + 16 + 32 * jj + 8 * t), qb = lds64(rb + 16 + 32 * jj + 8 * t);
-        const int sh = 8 * ((2 * jj) & 3);
-        const int scA0 = (sA[jj >> 1] >> sh) & 0xFF, scA1 = (sA[jj >> 1] >> (sh + 8)) & 0xFF;
-        const int scB0 = (sB[jj >> 1] >> sh) & 0xFF, scB1 = (sB[jj >> 1] >> (sh + 8)) & 0xFF;
+        int scA0, scA1, scB0, scB1;
+        if ((jj & 1) == 0) {
+            scA0 = byte_u<0>(sA[jj >> 1]); scA1 = byte_u<1>(sA[jj >> 1]);
+            scB0 = byte_u<0>(sB[jj >> 1]); scB1 = byte_u<1>(sB[jj >> 1]);
+        } else {
+            scA0 = byte_u<2>(sA[jj >> 1]); scA1 = byte_u<3>(sA[jj >> 1]);
+            scB0 = byte_u<2>(sB[jj >> 1]); scB1 = byte_u<3>(sB[jj >> 1]);
+        }
 #pragma unroll
         for (int tl = 0; tl < MT; ++tl) {
             int d[4];
             mma_u8s8_k32(d, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu,
                          B.q[tl][4 * jj], B.q[tl][4 * jj + 1], zero);
             isum_lo[tl][0] += scA0 * d[0];
-            isum_lo[tl][1] += scA0 * d[1];
             isum_lo[tl][2] += scB0 * d[2];
-            isum_lo[tl][3] += scB0 * d[3];
+            if (!M1) {
+                isum_lo[tl][1] += scA0 * d[1];
+                isum_lo[tl][3] += scB0 * d[3];
+            }
             mma_u8s8_k32(d, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u,
                          B.q[tl][4 * jj + 2], B.q[tl][4 * jj + 3], zero);
             isum_hi[tl][0] += scA1 * d[0];
-            isum_hi[tl][1] += scA1 * d[1];
             isum_hi[tl][2] += scB1 * d[2];
-            isum_hi[tl][3] += scB1 * d[3];
+            if (!M1) {
+                isum_hi[tl][1] += scA1 * d[1];
+                isum_hi[tl][3] += scB1 * d[3];
+            }
         }
     }
     // sum_j mins_j * bsum_j as two tiny u8 MMAs over (bsum + 4096) = hi * 128 + lo
@@ -337,6 +391,7 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, u
         mma_u8u8_k16(mh, am0, am1, B.bs_hi[tl], zero);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
+            if (M1 && (i & 1)) continue;
             const int sumi = isum_lo[tl][i] + (isum_hi[tl][i] >> 4);
             const int summ = ml[i] + 128 * mh[i] - 4096 * (i < 2 ? sumA : sumB);
             const float d8 = B.d8[tl][i & 1];
@@ -348,9 +403,27 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, u
     }
 }
 
-template <int MT, bool HILO>
-__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, uint32_t ra, uint32_t rb, int t,
+// Sign-extended byte `sb` (0..15) of four words; sb is a constant after unrolling.
+__device__ __forceinline__ int byte_s_dyn(const uint32_t (&sc)[4], int sb) {
+    const uint32_t w = sc[sb >> 2];
+    switch (sb & 3) {
+    case 0: return byte_s<0>(w);
+    case 1: return byte_s<1>(w);
+    case 2: return byte_s<2>(w);
+    default: return byte_s<3>(w);
+    }
+}
+
+// Signed scale sb (0..15) of a row from its four scale words.
+template <int SB>
+__device__ __forceinline__ int q6k_scale(const uint32_t (&sc)[4]) { return byte_s<SB & 3>(sc[SB >> 2]); }
+
+// ALIGNED: both slices start on a 4-byte boundary (plain 32-bit loads); otherwise they are only
+// 2-byte aligned and every word is assembled from two.
+template <int MT, bool HILO, bool M1, bool ALIGNED>
+__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t,
                                           float (&acc)[MT][4]) {
+    auto ld = [](const uint8_t* a) { return ALIGNED ? lds32(a) : lds32_u(a); };
     const int zero[4] = {0, 0, 0, 0};
     int isum[MT][4];
 #pragma unroll
@@ -360,35 +433,36 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, u
     uint32_t scA[4], scB[4];  // 16 signed 8-bit scales per row
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        scA[i] = lds32_u(ra + 192 + 4 * i);
-        scB[i] = lds32_u(rb + 192 + 4 * i);
+        scA[i] = ld(ra + 192 + 4 * i);
+        scB[i] = ld(rb + 192 + 4 * i);
     }
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
 #pragma unroll
         for (int is = 0; is < 2; ++is) {
             const uint32_t o = 64 * n + 16 * is + 4 * t;
-            const uint32_t la0 = lds32_u(ra + o), la1 = lds32_u(ra + o + 32), hA = lds32_u(ra + 128 + 32 * n + 16 * is + 4 * t);
-            const uint32_t lb0 = lds32_u(rb + o), lb1 = lds32_u(rb + o + 32), hB = lds32_u(rb + 128 + 32 * n + 16 * is + 4 * t);
+            const uint32_t la0 = ld(ra + o), la1 = ld(ra + o + 32), hA = ld(ra + 128 + 32 * n + 16 * is + 4 * t);
+            const uint32_t lb0 = ld(rb + o), lb1 = ld(rb + o + 32), hB = ld(rb + 128 + 32 * n + 16 * is + 4 * t);
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
                 // int8 value 4*(q-32): nibble -> bits 5..2, two high bits -> bits 7..6, flip bit 7
                 const uint32_t qla = (gq & 1) ? la1 : la0, qlb = (gq & 1) ? lb1 : lb0;
-                const uint32_t na = (gq < 2 ? (qla << 2) : (qla >> 2)) & 0x3C3C3C3Cu;
-                const uint32_t nb = (gq < 2 ? (qlb << 2) : (qlb >> 2)) & 0x3C3C3C3Cu;
                 const uint32_t ua = ((hA << (6 - 2 * gq)) & 0xC0C0C0C0u) ^ 0x80808080u;
                 const uint32_t ub = ((hB << (6 - 2 * gq)) & 0xC0C0C0C0u) ^ 0x80808080u;
+                const uint32_t va = lop3_and_or(gq < 2 ? (qla << 2) : (qla >> 2), 0x3C3C3C3Cu, ua);
+                const uint32_t vb = lop3_and_or(gq < 2 ? (qlb << 2) : (qlb >> 2), 0x3C3C3C3Cu, ub);
                 const int sb = 8 * n + 2 * gq + is;
-                const int sA_ = (int)(signed char)((scA[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
-                const int sB_ = (int)(signed char)((scB[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
+                const int sA_ = byte_s_dyn(scA, sb), sB_ = byte_s_dyn(scB, sb);
 #pragma unroll
                 for (int tl = 0; tl < MT; ++tl) {
                     int d[4];
-                    mma_s8s8_k16(d, na | ua, nb | ub, B.q[tl][sb], zero);
+                    mma_s8s8_k16(d, va, vb, B.q[tl][sb], zero);
                     isum[tl][0] += sA_ * d[0];
-                    isum[tl][1] += sA_ * d[1];
                     isum[tl][2] += sB_ * d[2];
-                    isum[tl][3] += sB_ * d[3];
+                    if (!M1) {
+                        isum[tl][1] += sA_ * d[1];
+                        isum[tl][3] += sB_ * d[3];
+                    }
                 }
             }
         }
@@ -398,6 +472,7 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, u
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
+            if (M1 && (i & 1)) continue;
             const float dall = __fmul_rn(i < 2 ? dA : dB, B.d8[tl][i & 1]);
             acc[tl][i] = __fadd_rn(acc[tl][i], __fmul_rn(dall, (float)(isum[tl][i] >> 2)));
         }
@@ -411,8 +486,8 @@ __device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t& lo, uint32_t& h
     hi = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4342)), bias));
 }
 
-template <int FMT, int MT, bool HILO>
-__device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, uint32_t ra, uint32_t rb, int t, uint32_t nblk,
+template <int FMT, int MT, bool HILO, bool M1>
+__device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t, uint32_t nblk,
                                           float (&acc)[MT][4]) {
     constexpr int BB = fmt_block_bytes(FMT);
     const float zf[4] = {0.f, 0.f, 0.f, 0.f};
@@ -426,12 +501,12 @@ __device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, uint32
         if ((uint32_t)b < nblk) {  // warp-uniform: ragged last slice when K % 256 != 0
             uint32_t a[2][4];  // [row][step*2 + {k 2t.., k 2t+8..}]
             if constexpr (FMT == FMT_Q8_0) {
-                // block = f16 d | 32 x i8 ; lane uses bytes 8t..8t+7
-                uint2 wa = lds64_u(ra + BB * b + 2 + 8 * t), wb = lds64_u(rb + BB * b + 2 + 8 * t);
-                s8x4_to_h2(wa.x, a[0][0], a[0][1]);
-                s8x4_to_h2(wa.y, a[0][2], a[0][3]);
-                s8x4_to_h2(wb.x, a[1][0], a[1][1]);
-                s8x4_to_h2(wb.y, a[1][2], a[1][3]);
+                // block = f16 d | 32 x i8 ; lane uses bytes 4t..4t+3 and 16+4t..16+4t+3, so the four
+                // lanes of a row read 16 contiguous bytes per load
+                s8x4_to_h2(lds32_u(ra + BB * b + 2 + 4 * t), a[0][0], a[0][1]);
+                s8x4_to_h2(lds32_u(ra + BB * b + 18 + 4 * t), a[0][2], a[0][3]);
+                s8x4_to_h2(lds32_u(rb + BB * b + 2 + 4 * t), a[1][0], a[1][1]);
+                s8x4_to_h2(lds32_u(rb + BB * b + 18 + 4 * t), a[1][2], a[1][3]);
             } else {
                 // Q4_0 block = f16 d | 16 B ; byte i = elements 2i (low nibble), 2i+1 (high); lane uses bytes 4t..4t+3
                 const __half2 b8 = __floats2half2_rn(1032.f, 1032.f);              // 1024 + 8
@@ -457,12 +532,15 @@ __device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, uint32
                     mma_f16_k16(e, a[0][0], a[1][0], a[0][1], a[1][1], B.l[tl][b][0], B.l[tl][b][1], zf);
                     mma_f16_k16(e, a[0][2], a[1][2], a[0][3], a[1][3], B.l[tl][b][2], B.l[tl][b][3], e);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) d[i] = fmaf(e[i], 1.0f / 2048.0f, d[i]);
+                    for (int i = 0; i < 4; ++i)
+                        if (!(M1 && (i & 1))) d[i] = fmaf(e[i], 1.0f / 2048.0f, d[i]);
                 }
                 sacc[tl][0] = fmaf(dA, d[0], sacc[tl][0]);
-                sacc[tl][1] = fmaf(dA, d[1], sacc[tl][1]);
                 sacc[tl][2] = fmaf(dB, d[2], sacc[tl][2]);
-                sacc[tl][3] = fmaf(dB, d[3], sacc[tl][3]);
+                if (!M1) {
+                    sacc[tl][1] = fmaf(dA, d[1], sacc[tl][1]);
+                    sacc[tl][3] = fmaf(dB, d[3], sacc[tl][3]);
+                }
             }
         }
     }
@@ -492,19 +570,28 @@ __device__ __forceinline__ void store_out(void* out, int dt, size_t idx, float v
 struct FillCursor {
     uint32_t unit;
     int mat, c;
-    uint32_t it;  // running fill index: stage = it % nstages, parity = (it / nstages) & 1
+    uint32_t it;     // running fill index
+    uint32_t stage;  // it % nstages
+    uint32_t par;    // (it / nstages) & 1
 };
 
-template <int FMT, int MT, int SL, bool HILO, bool SWIGLU>
+constexpr int RED_SLOTS = 4;  // upper bound; p.red_slots (3 or 4) are used
+// dynamic shared memory header: full[8] | empty[8] | abort | red_full[4] | red_empty[4]
+constexpr int OFF_EMPTY = 8 * MAX_STAGES, OFF_ABORT = 16 * MAX_STAGES, OFF_RFULL = OFF_ABORT + 8,
+              OFF_REMPTY = OFF_RFULL + 8 * RED_SLOTS;
+
+template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
 __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool HILO = (FMT == FMT_Q4_0 || FMT == FMT_Q8_0) && MT == 1;
     constexpr int NMAT = SWIGLU ? 2 : 1;
     constexpr int SLICE_B = fmt_slice_bytes(FMT);
+    constexpr int PER_RG = MT * 4 * 32;  // floats one warp contributes per row group
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nwc = (int)(p.spc * p.rgs);  // warps in the CTA; warp 0 also issues the copies
-    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 8 * MAX_STAGES;
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + 16 * MAX_STAGES);
-    float* red = reinterpret_cast<float*>(smem + p.red_off);
+    const int nwc = (int)(p.spc * p.rgs);  // warps in the CTA
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + OFF_EMPTY;
+    const uint32_t bar_rfull = bar_full + OFF_RFULL, bar_rempty = bar_full + OFF_REMPTY;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_ABORT);
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
     const uint32_t rps = 16 * p.rgs;  // rows per slab
     const uint32_t ks = blockIdx.y;
@@ -515,33 +602,48 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, nwc);
         }
+        for (int s = 0; s < RED_SLOTS; ++s) {
+            mbar_init(bar_rfull + 8 * s, nwc);
+            mbar_init(bar_rempty + 8 * s, 1);
+        }
         *abort_flag = 0;
         mbar_fence_init();
     }
     __syncthreads();
 
-    // Issues the copies of the fill at `cur` (warp 0 only) and advances the cursor.
-    auto produce = [&](FillCursor& cur) {
-        if (cur.unit >= p.total_units) return;
-        const uint32_t stage = cur.it % p.nstages, par = (cur.it / p.nstages) & 1;
+    // A warp that gives up on a wait marks the CTA dead; the others notice at their next slab.
+    // Dead warps keep walking the loops (so every barrier still gets its arrivals) but skip
+    // waits and arithmetic.
+    bool dead = false;
+    auto give_up = [&](unsigned code) {
+        dead = true;
+        *abort_flag = 1;
+        atomicOr(p.status, code);
+    };
+
+    // Requests the fill at `cur`: the calling warp copies all rows of the stage, one row per
+    // lane and pass.  The stage must have been released by every warp.
+    auto issue_fill = [&](const FillCursor& cur) {
+        const uint32_t stage = cur.stage;
         const uint32_t r0 = cur.unit * rps;
         const uint32_t nrows = min(rps, p.N - r0);
         const uint8_t* wbase = p.w[cur.mat];
-        const uint8_t* wend = wbase + p.w_bytes;
         const uint32_t gc = ks * SL + cur.c;
-        // wait until every warp has released the stage (first trip round the ring passes at once)
-        if (!*abort_flag && !mbar_wait(bar_empty + 8 * stage, par ^ 1)) {
-            *abort_flag = 1;
-            atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-        }
-        if (!*abort_flag) {
-            const uint32_t coff = gc * p.spc * SLICE_B;
-            const uint32_t cbytes = min(p.spc * SLICE_B, p.row_bytes - coff);
-            const uint32_t sdst = stage0 + stage * p.stage_bytes;
-            uint32_t tx = 0;
+        const uint32_t coff = gc * p.spc * SLICE_B;
+        const uint32_t cbytes = min(p.spc * SLICE_B, p.row_bytes - coff);
+        const uint32_t sdst = stage0 + stage * p.stage_bytes;
+        const uint32_t bar = bar_full + 8 * stage;
+        if (p.rows_aligned) {
+            if (lane == 0) mbar_expect_tx(bar, nrows * cbytes);
+            __syncwarp();
+            for (uint32_t r = lane; r < nrows; r += 32)
+                bulk_g2s(sdst + r * p.srow, wbase + (size_t)(r0 + r) * p.row_bytes + coff, cbytes, bar);
+        } else {
             // Each row's chunk is copied as the enclosing 16-byte-aligned range.  Only the last
             // row of the tensor can have a range that would end past the buffer: its final <16
             // bytes are moved with plain loads instead.
+            const uint8_t* wend = wbase + p.w_bytes;
+            uint32_t tx = 0;
             for (uint32_t r = lane; r < nrows; r += 32) {
                 const uint8_t* gsrc = wbase + (size_t)(r0 + r) * p.row_bytes + coff;
                 const uint8_t* gs = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(gsrc) & ~(uintptr_t)15);
@@ -556,7 +658,7 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
             }
             tx = __reduce_add_sync(0xFFFFFFFFu, tx);
             __syncwarp();
-            if (lane == 0) mbar_expect_tx(bar_full + 8 * stage, tx);
+            if (lane == 0) mbar_expect_tx(bar, tx);
             __syncwarp();
             for (uint32_t r = lane; r < nrows; r += 32) {
                 const uint8_t* gsrc = wbase + (size_t)(r0 + r) * p.row_bytes + coff;
@@ -565,10 +667,16 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
                 const uint8_t* e16 = reinterpret_cast<const uint8_t*>((reinterpret_cast<uintptr_t>(ge) + 15) & ~(uintptr_t)15);
                 if (e16 > wend) e16 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(ge) & ~(uintptr_t)15);
                 const uint32_t n = (uint32_t)(e16 - gs);
-                if (n) bulk_g2s(sdst + r * p.srow, gs, n, bar_full + 8 * stage);
+                if (n) bulk_g2s(sdst + r * p.srow, gs, n, bar);
             }
         }
+    };
+    auto advance = [&](FillCursor& cur) {
         ++cur.it;
+        if (++cur.stage == p.nstages) {
+            cur.stage = 0;
+            cur.par ^= 1;
+        }
         if (++cur.c >= nch) {
             cur.c = 0;
             if (++cur.mat >= NMAT) {
@@ -578,15 +686,21 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
         }
     };
 
-    // Warp 0 runs nstages-1 fills ahead of the computation.
-    FillCursor pc{blockIdx.x, 0, 0, 0};
-    if (warp == 0)
-        for (uint32_t i = 0; i + 1 < p.nstages; ++i) produce(pc);
+    // Fill f is requested by warp f % nwc: the first nstages fills right away, fill f >= nstages
+    // when that warp has finished fill f - nstages (it then waits for the others to release the
+    // stage).  Every warp walks the same cursor, so the role rotates without communication.
+    FillCursor pc{blockIdx.x, 0, 0, 0, 0, 0};
+    int pw = 0;  // warp that requests fill pc.it
+    TRACE(0);
+    for (uint32_t i = 0; i < p.nstages; ++i) {
+        if (pc.unit < p.total_units && pw == warp) issue_fill(pc);
+        advance(pc);
+        if (++pw == nwc) pw = 0;
+    }
 
     const int g = lane >> 2, t = lane & 3;
     const uint32_t s = warp % p.spc;   // slice within a chunk
     const uint32_t rg = warp / p.spc;  // row group within a slab
-    const int nthr = nwc * 32;
 
     SliceB<FMT, MT, HILO> B[SL];
 #pragma unroll
@@ -596,83 +710,157 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
         B[c].build(p, slice, c < nch && slice < p.nslices, g, t);
     }
 
-    uint32_t it = 0, buf = 0;
-    for (uint32_t unit = blockIdx.x; unit < p.total_units; unit += gridDim.x, buf ^= 1) {
+    // Adds up the partial sums of slab `unit_j` (ring slot `js`) and stores the results: one
+    // output per lane and pass, the slices' terms added in K order.
+    const uint32_t mcp = p.mcount <= 1 ? 1u : p.mcount <= 2 ? 2u : p.mcount <= 4 ? 4u : p.mcount <= 8 ? 8u : 16u;
+    const uint32_t mcp_log = 31 - __clz(mcp);
+    auto reduce_slab = [&](uint32_t unit_j, uint32_t js, uint32_t jpar) {
+        if (!dead && !mbar_wait(bar_rfull + 8 * js, jpar)) give_up(STATUS_TIMEOUT_FULL);
+        if (!dead) {
+            const float* slot = reinterpret_cast<const float*>(smem + p.red_off + js * p.red_slot_bytes);
+            const uint32_t r0 = unit_j * rps;
+            for (uint32_t o = lane; o < rps * mcp; o += 32) {
+                const uint32_t rr = o >> mcp_log, col = o & (mcp - 1);
+                const uint32_t row = r0 + rr;
+                if (row < p.N && col < p.mcount) {
+                    const uint32_t rgi = rr >> 4, r16 = rr & 15;
+                    const uint32_t i = (col >> 3) * 4 + (r16 >= 8 ? 2 : 0) + (col & 1);
+                    const uint32_t ln = (r16 & 7) * 4 + ((col & 7) >> 1);
+                    float v[NMAT];
+#pragma unroll
+                    for (int mat = 0; mat < NMAT; ++mat) {
+                        const float* src = slot + ((size_t)mat * nwc + rgi * p.spc) * PER_RG + i * 32 + ln;
+                        float sum = 0.f;
+                        if (p.spc == 16) {  // all loads first, then the ordered adds
+                            float x[16];
+#pragma unroll
+                            for (int ss = 0; ss < 16; ++ss) x[ss] = src[ss * PER_RG];
+#pragma unroll
+                            for (int ss = 0; ss < 16; ++ss) sum = __fadd_rn(sum, x[ss]);
+                        } else {
+                            for (uint32_t ss = 0; ss < p.spc; ++ss) sum = __fadd_rn(sum, src[(size_t)ss * PER_RG]);
+                        }
+                        v[mat] = sum;
+                    }
+                    if (p.ksplit == 1) {
+                        float r = v[0];
+                        if constexpr (SWIGLU) r = silu_f(v[0]) * v[1];
+                        store_out(p.out, p.out_dtype, (size_t)(p.m0 + col) * p.N + row, r);
+                    } else {
+#pragma unroll
+                        for (int mat = 0; mat < NMAT; ++mat)
+                            p.partial[((size_t)(mat * p.ksplit + ks) * p.M + p.m0 + col) * p.N + row] = v[mat];
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rempty + 8 * js);
+    };
+
+    TRACE(1);
+    uint32_t tu = 0;
+    (void)tu;
+    uint32_t it = 0, stage = 0, par = 0;          // consumer position in the stage ring
+    uint32_t rslot = 0, rpar = 0;                 // reduction ring: slot being written
+    uint32_t jslot = 0, jpar = 0, junit = blockIdx.x;  // reduction ring: slab to be reduced next
+    int jw = 0;                                   // warp that reduces slab junit
+    const uint32_t lag = p.red_slots - 2;         // slabs between publishing partials and reducing them
+    uint32_t published = 0;
+    auto next_reduce = [&]() {
+        if (jw == warp) reduce_slab(junit, jslot, jpar);
+        junit += gridDim.x;
+        if (++jslot == p.red_slots) {
+            jslot = 0;
+            jpar ^= 1;
+        }
+        if (++jw == nwc) jw = 0;
+    };
+    for (uint32_t unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
+        if (*abort_flag) dead = true;
         const uint32_t r0 = unit * rps;
         const uint32_t rowA = rg * 16 + g, rowB = rowA + 8;  // rows of the slab
+        float accs[NMAT][MT][4];
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
-            float acc[MT][4];
+            float(&acc)[MT][4] = accs[mat];
 #pragma unroll
             for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[tl][i] = 0.f;
             // phase of a row inside its 16-byte-aligned copy (0 whenever row_bytes % 16 == 0)
-            const uint32_t phA = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowA) * p.row_bytes) & 15);
-            const uint32_t phB = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowB) * p.row_bytes) & 15);
+            uint32_t phA = 0, phB = 0;
+            if (!p.rows_aligned) {
+                phA = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowA) * p.row_bytes) & 15);
+                phB = (uint32_t)((reinterpret_cast<uintptr_t>(p.w[mat]) + (size_t)(r0 + rowB) * p.row_bytes) & 15);
+            }
 #pragma unroll
             for (int c = 0; c < SL; ++c) {
                 if (c < nch) {
-                    if (warp == 0) produce(pc);  // refills the stage every warp released one fill ago
                     const uint32_t gc = ks * SL + c;
-                    const uint32_t stage = it % p.nstages, par = (it / p.nstages) & 1;
-                    ++it;
-                    if (!*abort_flag && !mbar_wait(bar_full + 8 * stage, par)) {
-                        *abort_flag = 1;
-                        atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                    }
+                    TRACE(2 + 5 * tu);
+                    if (!dead && !mbar_wait(bar_full + 8 * stage, par)) give_up(STATUS_TIMEOUT_FULL);
+                    TRACE(3 + 5 * tu);
                     const uint32_t slice = gc * p.spc + s;
-                    if (!*abort_flag && slice < p.nslices) {
+                    if (!dead && slice < p.nslices) {
                         const uint32_t coff = gc * p.spc * SLICE_B;
-                        const uint32_t sb = stage0 + stage * p.stage_bytes + s * SLICE_B;
-                        const uint32_t ra = sb + rowA * p.srow + ((phA + coff) & 15);
-                        const uint32_t rb = sb + rowB * p.srow + ((phB + coff) & 15);
-                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, HILO>(B[c], ra, rb, t, acc);
-                        else if constexpr (FMT == FMT_Q6_K) slice_q6k<MT, HILO>(B[c], ra, rb, t, acc);
-                        else {
+                        const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + s * SLICE_B;
+                        const uint8_t* ra = sb + rowA * p.srow + ((phA + coff) & 15);
+                        const uint8_t* rb = sb + rowB * p.srow + ((phB + coff) & 15);
+                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, HILO, M1>(B[c], ra, rb, t, acc);
+                        else if constexpr (FMT == FMT_Q6_K) {
+                            const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(ra) | reinterpret_cast<uintptr_t>(rb)) & 3u;
+                            if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, HILO, M1, true>(B[c], ra, rb, t, acc);
+                            else slice_q6k<MT, HILO, M1, false>(B[c], ra, rb, t, acc);
+                        } else {
                             const uint32_t kl = p.K - slice * 256;
-                            slice_f16<FMT, MT, HILO>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
+                            slice_f16<FMT, MT, HILO, M1>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
                         }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty + 8 * stage);
+                    // whoever's turn it is refills the stage just released (fill it + nstages)
+                    if (pc.unit < p.total_units && pw == warp) {
+                        if (!dead && !mbar_wait(bar_empty + 8 * stage, par)) give_up(STATUS_TIMEOUT_EMPTY);
+                        if (!dead) issue_fill(pc);
+                    }
+                    advance(pc);
+                    if (++pw == nwc) pw = 0;
+                    ++it;
+                    if (++stage == p.nstages) {
+                        stage = 0;
+                        par ^= 1;
+                    }
                 }
             }
-            float* rdst = red + ((size_t)(buf * NMAT + mat) * nwc + warp) * (MT * 4 * 32);
+        }
+        TRACE(4 + 5 * tu);
+        // publish the partial sums in the reduction ring ...
+        float* slot = reinterpret_cast<float*>(smem + p.red_off + rslot * p.red_slot_bytes);
+        if (!dead && !mbar_wait(bar_rempty + 8 * rslot, rpar ^ 1)) give_up(STATUS_TIMEOUT_EMPTY);
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+            float* rdst = slot + ((size_t)mat * nwc + warp) * PER_RG;
 #pragma unroll
             for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) rdst[(tl * 4 + i) * 32 + lane] = acc[tl][i];
+                for (int i = 0; i < 4; ++i)
+                    if (!(M1 && (i & 1))) rdst[(tl * 4 + i) * 32 + lane] = accs[mat][tl][i];
         }
-        __syncthreads();
-        // cross-warp sum in slice order, then store
-        const int per_rg = MT * 4 * 32;
-        for (int e = threadIdx.x; e < (int)p.rgs * per_rg; e += nthr) {
-            const int rgi = e / per_rg, rem = e % per_rg, i = rem >> 5, ln = rem & 31;
-            float v[NMAT];
-#pragma unroll
-            for (int mat = 0; mat < NMAT; ++mat) {
-                const float* src = red + ((size_t)(buf * NMAT + mat) * nwc + rgi * p.spc) * per_rg + i * 32 + ln;
-                float sum = 0.f;
-                for (uint32_t ss = 0; ss < p.spc; ++ss) sum = __fadd_rn(sum, src[(size_t)ss * per_rg]);
-                v[mat] = sum;
-            }
-            const int ci = i & 3;
-            const uint32_t row = r0 + rgi * 16 + (ln >> 2) + (ci >= 2 ? 8 : 0);
-            const uint32_t col = (i >> 2) * 8 + 2 * (ln & 3) + (ci & 1);
-            if (row < p.N && col < p.mcount) {
-                if (p.ksplit == 1) {
-                    float r = v[0];
-                    if constexpr (SWIGLU) r = silu_f(v[0]) * v[1];
-                    store_out(p.out, p.out_dtype, (size_t)(p.m0 + col) * p.N + row, r);
-                } else {
-#pragma unroll
-                    for (int mat = 0; mat < NMAT; ++mat)
-                        p.partial[((size_t)(mat * p.ksplit + ks) * p.M + p.m0 + col) * p.N + row] = v[mat];
-                }
-            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rfull + 8 * rslot);
+        if (++rslot == p.red_slots) {
+            rslot = 0;
+            rpar ^= 1;
         }
+        ++published;
+        TRACE(5 + 5 * tu);
+        // ... and one warp (taking turns) adds up an older slab, whose partials arrived long ago
+        if (published > lag) next_reduce();
+        TRACE(6 + 5 * tu);
+        ++tu;
     }
+    while (junit < p.total_units) next_reduce();  // drain the slabs still in the ring
 }
 
 // Adds split-K partials [nmat][ksplit][M][N] in K order and applies the SwiGLU gate.
@@ -689,9 +877,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
-template <int FMT, int MT, int SL, bool HILO, bool SWIGLU>
+template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
 cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    auto k = gemv_kernel<FMT, MT, SL, HILO, SWIGLU>;
+    auto k = gemv_kernel<FMT, MT, SL, M1, SWIGLU>;
     static bool attr_set[64] = {};  // per device; setting the attribute is idempotent, races are harmless
     int dev = 0;
     cudaGetDevice(&dev);
@@ -708,14 +896,19 @@ cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem,
 template <int FMT, bool SWIGLU>
 cudaError_t launch_gemv_fmt(const GemvParams& p, int mt, int sl, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
+    const bool m1 = p.mcount == 1 && p.M == 1;
     if constexpr (KQ) {
-        if (mt == 1 && sl == 1) return launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 1 && sl == 2) return launch_one<FMT, 1, 2, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 1 && sl == 4) return launch_one<FMT, 1, 4, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 2) return m1 ? launch_one<FMT, 1, 2, true, SWIGLU>(p, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 2, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 4) return m1 ? launch_one<FMT, 1, 4, true, SWIGLU>(p, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 4, false, SWIGLU>(p, grid, threads, smem, st);
         if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
         if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, grid, threads, smem, st);
     } else {
-        if (mt == 1 && sl == 1) return launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
         if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
     }
     return cudaErrorInvalidValue;
@@ -732,6 +925,7 @@ int gemv_max_sl(int fmt, int mt) {
 
 struct GemvPlan {
     uint32_t spc, nslices, nchunks, sl, ksplit, rgs, srow, stage_bytes, nstages, total_units, red_off, stage_off;
+    uint32_t red_slot_bytes, red_slots, rows_aligned, contig;
     size_t smem;
     int threads;
     dim3 grid;
@@ -755,16 +949,31 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     const uint32_t need_rg = (N + 15) / 16;
     if (pl.rgs > need_rg) pl.rgs = need_rg;
     uint32_t cmax = pl.spc * slice_b < row_bytes ? pl.spc * slice_b : row_bytes;
+    // Row stride in shared memory: room for the 16-byte phase of unaligned rows and for the
+    // second word of a straddling load, then bumped so that the eight rows a warp touches at
+    // once fall in distinct banks: Q4_K reads 8 bytes per lane (rows 32 bytes apart mod 128),
+    // the other formats 4 bytes per lane (rows 16 bytes apart mod 32).
     uint32_t srow = (cmax + 19 + 15) & ~15u;
-    if ((srow & 31) == 0) srow += 16;  // odd multiple of 16: 8 rows x 4 lanes hit 32 distinct banks
+    if (fmt == FMT_Q4_K) {
+        while ((srow & 63) != 32) srow += 16;
+    } else {
+        if ((srow & 31) == 0) srow += 16;
+    }
+    pl.contig = 0;
+    pl.rows_aligned = (row_bytes % 16 == 0 && (pl.spc * slice_b) % 16 == 0) ? 1u : 0u;
     pl.srow = srow;
-    pl.stage_bytes = 16 * pl.rgs * srow;
+    pl.stage_bytes = ((16 * pl.rgs * srow + 127) & ~127u) + 128;
     const int nwc = pl.spc * pl.rgs;
-    const uint32_t red_bytes = 2u * (swiglu ? 2 : 1) * nwc * mt * 4 * 32 * 4;
-    pl.red_off = 256;
-    pl.stage_off = (pl.red_off + red_bytes + 127) & ~127u;
+    pl.red_slot_bytes = (swiglu ? 2u : 1u) * nwc * mt * 4 * 32 * 4;
     const uint32_t budget = 232448 - 1024;
-    if (pl.stage_off + 2 * pl.stage_bytes > budget) return false;
+    pl.red_off = 256;
+    // reduction ring: 4 slots when they are small, fewer when shared memory is short (with 2
+    // slots a slab is reduced right after it is published, i.e. the warps meet once per slab)
+    for (pl.red_slots = pl.red_slot_bytes * 4 <= 48 * 1024 ? 4u : 3u;; --pl.red_slots) {
+        pl.stage_off = (pl.red_off + pl.red_slots * pl.red_slot_bytes + 127) & ~127u;
+        if (pl.stage_off + 2 * pl.stage_bytes <= budget) break;
+        if (pl.red_slots == 2) return false;
+    }
     uint32_t ns = (budget - pl.stage_off) / pl.stage_bytes;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
     pl.nstages = ns;
@@ -816,6 +1025,7 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         p.nslices = pl.nslices; p.spc = pl.spc; p.nchunks = pl.nchunks; p.ksplit = pl.ksplit; p.rgs = pl.rgs;
         p.srow = pl.srow; p.stage_bytes = pl.stage_bytes; p.nstages = pl.nstages; p.total_units = pl.total_units;
         p.red_off = pl.red_off; p.stage_off = pl.stage_off;
+        p.red_slot_bytes = pl.red_slot_bytes; p.red_slots = pl.red_slots; p.rows_aligned = pl.rows_aligned; p.contig = pl.contig;
         p.act_dtype = act_dtype; p.out_dtype = out_dtype;
         p.w_bytes = (unsigned long long)N * p.row_bytes;
         p.status = status;
@@ -849,5 +1059,11 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     }
     return cudaSuccess;
 }
+
+#ifdef B200Q_TRACE
+extern "C" __attribute__((visibility("default"))) int b200q_debug_trace(void* host, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(host, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace));
+}
+#endif
 
 }  // namespace b200q
