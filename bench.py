@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+Default workload (``--workload c5``): one decode step over the quantized linears of a
+Llama-3-8B-shaped stack in a Q4_K_M-style mix (32 layers of q/k/v/o/gate/up/down + lm_head;
+Q6_K for v, down and lm_head, Q4_K elsewhere), M tokens per step (``--m``, default 1), synthetic
+weights with the block-value distributions of the reference configurations, tensor-parallel over
+``--gpus`` ranks (column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with all-reduce,
+logits all-gathered).  Metric: decode tokens/s = M * steps/s, whole job.
+
+One JSON line is printed by rank 0.  ``--impl reference`` times the CPU restatement of boostr's
+CPU SIMD path (the reference itself is Rust and cannot be built in this environment) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def fmt_bytes(fmt: str, n: int, k: int) -> int:
+    bs, bb = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q4_K": (256, 144), "Q6_K": (256, 210)}[fmt]
+    return n * (k // bs) * bb
+
+
+# the linears of one layer: (name, format, N, K, parallel split)
+LAYER_SPEC = [
+    ("q", "Q4_K", HIDDEN, HIDDEN, "col"), ("k", "Q4_K", KV, HIDDEN, "col"), ("v", "Q6_K", KV, HIDDEN, "col"),
+    ("o", "Q4_K", HIDDEN, HIDDEN, "row"), ("gate", "Q4_K", FFN, HIDDEN, "col"), ("up", "Q4_K", FFN, HIDDEN, "col"),
+    ("down", "Q6_K", HIDDEN, FFN, "row"),
+]
+STEP_BYTES = LAYERS * sum(fmt_bytes(f, n, k) for _, f, n, k, _ in LAYER_SPEC) + fmt_bytes("Q6_K", VOCAB, HIDDEN)
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            p = [x.strip() for x in l.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+
+def device_weight(fmt, n, k, gen):
+    """Synthetic packed weight generated on the device: uniform random codes and scale bytes, then
+    every block's fp16 super-scale(s) overwritten with |N(0,1)| * c so all values are finite."""
+    import torch
+
+    from boostr_b200.format import QuantFormat as F
+    from boostr_b200.tensor import QuantTensor
+
+    f = F.parse(fmt)
+    nb = n * (k // f.block_size)
+    w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device="cuda", generator=gen)
+    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q6_K": 0.0005}[f.name]
+    d = (torch.randn(nb, device="cuda", generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
+    if f is F.Q6_K:
+        w[:, 208:210] = d
+    else:
+        w[:, 0:2] = d
+        if f is F.Q4_K:
+            w[:, 2:4] = d
+    return QuantTensor(w.reshape(-1), f, (n, k))
+
+
+class DecodeStack:
+    """The quantized linears of the Llama-3-8B-shaped stack, sharded for this rank."""
+
+    def __init__(self, m, rank, world, layers=LAYERS):
+        import torch
+
+        from boostr_b200.linear import QuantLinear
+        from boostr_b200.tensor_parallel import ColumnParallelQuantLinear, RowParallelQuantLinear
+
+        self.m, self.rank, self.world = m, rank, world
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(0xB200 + rank)
+        p = world
+        self.layers = []
+        for _ in range(layers):
+            L = {}
+            for name, fmt, n, k, split in LAYER_SPEC:
+                if split == "col":
+                    L[name] = ColumnParallelQuantLinear(device_weight(fmt, n // p, k, gen))
+                else:
+                    L[name] = RowParallelQuantLinear(device_weight(fmt, n, k // p, gen))
+            L["qk"] = [QuantLinear(L["q"].weight), QuantLinear(L["k"].weight)]
+            self.layers.append(L)
+        self.lm_head = ColumnParallelQuantLinear(device_weight("Q6_K", VOCAB // p, HIDDEN, gen))
+        f32 = dict(dtype=torch.float32, device="cuda")
+        self.x = torch.randn(m, HIDDEN, generator=gen, **f32)           # step input (hidden state)
+        self.q = torch.empty(m, HIDDEN // p, **f32)
+        self.k = torch.empty(m, KV // p, **f32)
+        self.v = torch.empty(m, KV // p, **f32)
+        self.o = torch.empty(m, HIDDEN, **f32)
+        self.h = torch.empty(m, FFN // p, **f32)
+        self.d = torch.empty(m, HIDDEN, **f32)
+        self.logits_local = torch.empty(m, VOCAB // p, **f32)
+        self.logits = torch.empty(m, VOCAB, **f32) if p > 1 else self.logits_local
+        self.bytes_local = sum(w.storage_bytes() for L in self.layers for w in
+                               [L[n].weight for n, *_ in LAYER_SPEC]) + self.lm_head.weight.storage_bytes()
+
+    def step(self):
+        """One decode step.  Within a layer the data flows q -> o -> gate/up -> down as in the
+        model (attention itself is not part of this path: o_proj consumes the q projection);
+        every layer starts again from the step input so magnitudes stay finite without the
+        model's normalisation layers."""
+        from boostr_b200 import ops
+        from boostr_b200.linear import QuantLinear
+        from boostr_b200.tensor_parallel import all_reduce_tensor, gather_from_ranks
+
+        for L in self.layers:
+            QuantLinear.forward_batch(L["qk"], self.x, outs=[self.q, self.k])
+            L["v"].forward(self.x, out=self.v)
+            L["o"].forward(self.q, out=self.o)                      # row-parallel: all-reduce inside
+            ops.quant_swiglu(self.o, L["gate"].weight, L["up"].weight, out=self.h)
+            L["down"].forward(self.h, out=self.d)                   # row-parallel: all-reduce inside
+        self.lm_head.forward(self.x, out=self.logits_local)
+        if self.world > 1:
+            gather_from_ranks(self.logits_local, out=self.logits)
+        return self.logits
+
+
+def time_kernel_family(stack, torch, ops):
+    """Average device time of the dominant kernel: the Q4_K decode GEMV on the gate-projection shards
+    of all layers (distinct weights, 1 GB in total at one GPU, so every launch streams from HBM)."""
+    outs = torch.empty(stack.m, stack.layers[0]["gate"].weight.shape[0], device="cuda")
+    ws = [L["gate"].weight for L in stack.layers]
+    for w in ws[:3]:
+        ops.quant_matmul(stack.x, w, out=outs)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for w in ws:
+            ops.quant_matmul(stack.x, w, out=outs)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / (reps * len(ws))
+    return us, ws[0].storage_bytes()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from boostr_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    m = args.m
+    stack = DecodeStack(m, rank, world)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up (also initialises NCCL communicators outside any capture), then capture one step
+    launches0 = ops.launch_count()
+    stack.step()
+    torch.cuda.synchronize()
+    launches_per_step = ops.launch_count() - launches0
+    use_graph = not args.no_graph
+    graph = None
+    if use_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                stack.step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                stack.step()
+        except Exception as e:  # capture of a collective can be refused; fall back to eager launches
+            graph = None
+            sys.stderr.write(f"[bench] CUDA graph capture failed, running eagerly: {e}\n")
+            torch.cuda.synchronize()
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            stack.step()
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    barrier()
+
+    # ---- device-resident timing: K steps, CUDA events, max over ranks
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        ev[0].record()
+        for _ in range(args.steps):
+            one_step()
+        ev[1].record()
+        barrier()
+    ms_total = ev[0].elapsed_time(ev[1])
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    ops.check_device_status()
+
+    # ---- end to end: host activations in, host logits out, every step
+    x_host = torch.randn(m, HIDDEN).pin_memory()
+    logits_host = torch.empty(m, VOCAB).pin_memory()
+    for _ in range(2):
+        stack.x.copy_(x_host, non_blocking=True)
+        one_step()
+        logits_host.copy_(stack.logits, non_blocking=True)
+    barrier()
+    ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev2[0].record()
+    for _ in range(args.steps):
+        stack.x.copy_(x_host, non_blocking=True)
+        one_step()
+        logits_host.copy_(stack.logits, non_blocking=True)
+    ev2[1].record()
+    barrier()
+    e2e_ms = ev2[0].elapsed_time(ev2[1])
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_ms /= args.steps
+
+    result = None
+    if rank == 0:
+        pk = peaks()
+        k_us, k_bytes = time_kernel_family(stack, torch, ops)
+        achieved = k_bytes / k_us / 1e3  # GB/s
+        step_gbs = STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+        result = {
+            "metric": "decode tokens/s over the quantized linears of a Llama-3-8B-shaped stack (Q4_K_M mix)",
+            "value": m * 1000.0 / ms_per_step, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8 blocks x int8 (Q8_K) activations, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"C5 Llama-3-8B-shaped decode step, 32 layers + lm_head, M={m}",
+                       "parallelism": f"tp{world}", "packed_weight_bytes_per_step": STEP_BYTES,
+                       "l2": "weights per step per rank exceed L2 (%d MB > 126 MB)" % (stack.bytes_local // 2**20),
+                       "cuda_graph": graph is not None},
+            "step_weight_gbs": step_gbs, "step_frac_of_8tbs": step_gbs / 8000.0,
+            "e2e": {"value": m * 1000.0 / e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": m * HIDDEN * 4,
+                    "d2h_bytes_per_step": m * VOCAB * 4},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "clocks": clk.summary(),
+            "roofline": {"bound": "hbm", "kernel": "Q4_K decode GEMV, gate-projection shard [%d x %d], M=%d" % (
+                             stack.layers[0]["gate"].weight.shape[0], HIDDEN, m),
+                         "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                         "frac_of_8tbs": achieved / 8000.0, "peak_source": pk["source"], "avg_launch_us": k_us,
+                         "algorithmic_bytes_per_launch": k_bytes, "traffic": None},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_reference(m, budget_s=args.cpu_seconds)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+# --------------------------------------------------------------------------- CPU arm
+
+
+def cpu_reference(m, budget_s=12.0, steps=None, warmup=1):
+    """Times the CPU oracle (C restatement of boostr's CPU SIMD path) on a bounded sample of the
+    decode step: whole layers (all seven linears) plus one eighth of the lm_head, all host threads."""
+    import numpy as np
+
+    from boostr_b200 import synth
+    from oracle import oracle
+
+    oracle.build()
+    threads = os.cpu_count() or 1
+    rng = synth.rng_for(5, 0)
+    nsets = 2  # distinct weight sets so the layer does not sit in the last-level cache
+    sets = []
+    for _ in range(nsets):
+        sets.append([(f, n, k, synth.weight_bytes(f, rng, n, k)) for _, f, n, k, _ in LAYER_SPEC])
+    lm_rows = VOCAB // 8
+    lm = synth.weight_bytes("Q6_K", rng, lm_rows, HIDDEN)
+    acts = {HIDDEN: synth.activations(rng, m, HIDDEN), FFN: synth.activations(rng, m, FFN)}
+
+    def sample(i):
+        t0 = time.perf_counter()
+        for f, n, k, w in sets[i % nsets]:
+            oracle.quant_matmul(f, acts[k], w, n, threads=threads, simd=True)
+        t1 = time.perf_counter()
+        oracle.quant_matmul("Q6_K", acts[HIDDEN], lm, lm_rows, threads=threads, simd=True)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+    for i in range(warmup):
+        sample(i)
+    lay, head = [], []
+    t_start = time.perf_counter()
+    i = 0
+    while (steps is None and time.perf_counter() - t_start < budget_s) or (steps is not None and i < steps):
+        a, b = sample(i)
+        lay.append(a)
+        head.append(b)
+        i += 1
+        if steps is not None and time.perf_counter() - t_start > 150:
+            break
+    t_layer, t_head = statistics.median(lay), statistics.median(head) * 8
+    step_s = LAYERS * t_layer + t_head
+    return {"value": m / step_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{len(lay)} x (one layer's 7 linears + 1/8 of lm_head), median, scaled to 32 layers + lm_head",
+            "ms_per_step": step_s * 1e3,
+            "note": "C restatement of boostr's CPU path (AVX2 integer dots, rayon-style column chunks); boostr itself "
+                    "is Rust and cannot be built here"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    cb = cpu_reference(args.m, steps=max(args.steps, 1), warmup=max(args.warmup, 1))
+    return {
+        "impl": "reference",
+        "metric": "decode tokens/s over the quantized linears of a Llama-3-8B-shaped stack (Q4_K_M mix)",
+        "value": cb["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "u8 blocks x int8 (Q8_K) activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"C5 Llama-3-8B-shaped decode step, 32 layers + lm_head, M={args.m}",
+                   "parallelism": "host threads"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="tokens per decode step")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if res is not None:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

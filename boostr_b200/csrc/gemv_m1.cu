@@ -1,0 +1,271 @@
+// Decode GEMV (M = 1) for Q4_K: y[n] = sum_k x[k] * W[n,k], one activation row.
+//
+// Stands in for boostr's quant_gemv_q4_k_q8_1_mwr launch plus its activation-quantise launch
+// (src/quant/cuda/kernels/quant_gemv.cu:285-379, quant_act.cu:17-69) when there is a single
+// activation row, the shape every decode step of a quantised LLaMA produces.
+//
+// The kernel is bound by HBM: 144 bytes of packed weights per 256 multiply-adds.  Layout of work:
+//   * persistent CTAs, one per SM, each owning a contiguous, evenly sized range of weight rows;
+//   * the rows stream through a 3-stage shared-memory ring, 32 rows (72 KB at K = 4096) per
+//     stage, each stage one 1-D bulk copy (cp.async.bulk) signalled on an mbarrier, so about
+//     150 KB of reads are in flight per SM and no thread spends instructions on loads;
+//   * the activation row is quantised to Q8_K once per CTA (exactly as boostr's CPU path does,
+//     src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98) and every lane keeps the int8 codes
+//     of ONE 256-wide block in registers for the whole kernel;
+//   * a warp takes two rows of a stage; lane (h, b) multiplies block b of row h against its
+//     register-resident activation block with dp4a: 128-bit shared loads, nibbles unpacked with
+//     one AND each (high nibbles stay in place and are divided out of the integer sum), 6-bit
+//     scales and mins unpacked with a handful of byte-parallel logic ops, the min term through
+//     byte-split block sums; then 16 lanes add their block terms with shuffles.
+// Integer sums are exact and each block contributes (d*d8)*sumi - (dmin*d8)*summ as in
+// fused_dot_q4k_q8k (src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172); only the order in
+// which the K/256 block terms are added differs from the CPU loop (pairwise instead of serial).
+#include "common.cuh"
+
+namespace b200q {
+
+struct GemvM1Params {
+    const uint8_t* w;
+    const void* act;
+    void* out;
+    uint32_t K, N;
+    uint32_t nblk;       // K / 256 (<= 16)
+    uint32_t row_bytes;  // nblk * 144
+    uint32_t stage_rows; // 32
+    uint32_t stage_bytes;
+    uint32_t nstages;
+    uint32_t act_off, stage_off;
+    int act_dtype, out_dtype;
+    unsigned int* status;
+};
+
+namespace {
+
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t dp4a_u8u8(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+template <int I>
+__device__ __forceinline__ int ubyte(uint32_t x) { return (int)__byte_perm(x, 0u, 0x4440 | I); }
+
+// shared-memory image of the quantised activation row, per 256-block b (stride 288 B):
+//   [0,256)   int8 codes   [256,264) (bsum_j + 4096) & 127, j = 0..7   [264,272) (bsum_j + 4096) >> 7
+//   [272,276) f32 d8
+constexpr int ACT_STRIDE = 288;
+
+__global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
+    uint8_t* act_s = smem + p.act_off;
+    const uint32_t stage0 = smem_u32(smem + p.stage_off);
+
+    // rows of this CTA: an even split of N over the grid
+    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
+    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
+    const uint32_t nfill = (row_end - row_begin + p.stage_rows - 1) / p.stage_rows;
+
+    auto issue_fill = [&](uint32_t f) {  // one lane
+        const uint32_t r0 = row_begin + f * p.stage_rows;
+        const uint32_t nrows = min(p.stage_rows, row_end - r0);
+        const uint32_t st = f % p.nstages;
+        mbar_expect_tx(bar_full + 8 * st, nrows * p.row_bytes);
+        bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, nrows * p.row_bytes, bar_full + 8 * st);
+    };
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.nstages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 16);
+        }
+        mbar_fence_init();
+        // start the weight stream at once: the first fills need no hand-shake, and the copies
+        // overlap the activation quantisation below
+        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
+    }
+
+    // 1. quantise the activation row: warp w owns block w (8 values per lane); warp 0, whose
+    // first lane is busy issuing copies, takes its block last
+    if ((uint32_t)warp < p.nblk) {
+        float v[8];
+        const size_t base = (size_t)warp * 256 + 8 * lane;
+        if (p.act_dtype == DT_F32) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.act) + base);
+            float4 a = __ldg(src), b = __ldg(src + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+            uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.act) + base));
+            v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+            v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+            v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
+            v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float d8 = __fdiv_rn(amax, 127.0f);
+        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+        int c[8], s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id))));
+            s += c[i];
+        }
+        uint8_t* blk = act_s + warp * ACT_STRIDE;
+        uint2 packed;
+        packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
+        packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
+        *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+        // sum over the 4 lanes of a 32-element sub-block
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        if ((lane & 3) == 0) {
+            const int bs = s + 4096;
+            blk[256 + (lane >> 2)] = (uint8_t)(bs & 127);
+            blk[264 + (lane >> 2)] = (uint8_t)(bs >> 7);
+        }
+        if (lane == 0) *reinterpret_cast<float*>(blk + 272) = d8;
+    }
+    __syncthreads();  // barriers initialised, activation image complete
+
+    // 2. this lane's activation block goes to registers
+    const int b = lane & 15, h = lane >> 4;
+    const bool blk_on = (uint32_t)b < p.nblk;
+    uint32_t a[64];
+    uint32_t bs_lo[2], bs_hi[2];
+    float d8 = 0.f;
+    {
+        const uint8_t* blk = act_s + (blk_on ? b : 0) * ACT_STRIDE;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            uint4 q = *reinterpret_cast<const uint4*>(blk + 16 * i);
+            a[4 * i] = q.x; a[4 * i + 1] = q.y; a[4 * i + 2] = q.z; a[4 * i + 3] = q.w;
+        }
+        uint4 q = *reinterpret_cast<const uint4*>(blk + 256);
+        bs_lo[0] = q.x; bs_lo[1] = q.y; bs_hi[0] = q.z; bs_hi[1] = q.w;
+        d8 = blk_on ? *reinterpret_cast<const float*>(blk + 272) : 0.f;
+    }
+
+    bool dead = false;
+    uint32_t st = 0, par = 0;
+    for (uint32_t f = 0; f < nfill; ++f) {
+        if (!dead && !mbar_wait(bar_full + 8 * st, par)) {
+            dead = true;
+            atomicOr(p.status, STATUS_TIMEOUT_FULL);
+        }
+        const uint32_t r0 = row_begin + f * p.stage_rows;
+        const uint32_t nrows = min(p.stage_rows, row_end - r0);
+        const uint32_t rr = 2 * warp + h;  // row of the stage handled by this half-warp
+        float term = 0.f;
+        if (!dead && rr < nrows && blk_on) {
+            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + rr * p.row_bytes + b * 144;
+            const uint4 hd = *reinterpret_cast<const uint4*>(blk);
+            // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
+            uint32_t sc[2], mn[2];
+            sc[0] = hd.y & 0x3F3F3F3Fu;
+            mn[0] = hd.z & 0x3F3F3F3Fu;
+            sc[1] = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mn[1] = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+            int sum_lo = 0, sum_hi = 0;  // sum_hi is 16x too large: high nibbles are used in place
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
+                const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * jj);
+                const uint4 q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * jj);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                int dl = 0, dh = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dl = dp4a_u8s8(w[i] & 0x0F0F0F0Fu, a[16 * jj + i], dl);
+                    dh = dp4a_u8s8(w[i] & 0xF0F0F0F0u, a[16 * jj + 8 + i], dh);
+                }
+                const uint32_t sw = sc[jj >> 1];
+                const int s0 = (jj & 1) ? ubyte<2>(sw) : ubyte<0>(sw);
+                const int s1 = (jj & 1) ? ubyte<3>(sw) : ubyte<1>(sw);
+                sum_lo += s0 * dl;
+                sum_hi += s1 * dh;
+            }
+            const int sumi = sum_lo + (sum_hi >> 4);
+            // sum_j mins_j * bsum_j with bsum_j + 4096 = hi * 128 + lo, all bytes
+            const uint32_t mlo = dp4a_u8u8(mn[0], bs_lo[0], dp4a_u8u8(mn[1], bs_lo[1], 0u));
+            const uint32_t mhi = dp4a_u8u8(mn[0], bs_hi[0], dp4a_u8u8(mn[1], bs_hi[1], 0u));
+            const uint32_t msum = dp4a_u8u8(mn[0], 0x01010101u, dp4a_u8u8(mn[1], 0x01010101u, 0u));
+            const int summ = (int)mlo + 128 * (int)mhi - 4096 * (int)msum;
+            const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
+            term = __fsub_rn(__fmul_rn(__fmul_rn(d, d8), (float)sumi), __fmul_rn(__fmul_rn(dmin, d8), (float)summ));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+        // add the block terms of a row (16 lanes)
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
+        if (b == 0 && rr < nrows && !dead) {
+            const size_t idx = r0 + rr;
+            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = term;
+            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(term);
+            else static_cast<__half*>(p.out)[idx] = __float2half_rn(term);
+        }
+        // refill the stage just released: the warps take turns, so nobody is "the producer"
+        if (f + p.nstages < nfill && (f & 15) == (uint32_t)warp) {
+            if (!dead && !mbar_wait(bar_empty + 8 * st, par)) {
+                dead = true;
+                atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+            }
+            if (!dead && lane == 0) issue_fill(f + p.nstages);
+        }
+        if (++st == p.nstages) {
+            st = 0;
+            par ^= 1;
+        }
+    }
+}
+
+}  // namespace
+
+bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N) {
+    return fmt == FMT_Q4_K && M == 1 && K % 256 == 0 && K <= 4096 && N >= 1;
+}
+
+cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
+                           size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    (void)fmt;
+    GemvM1Params p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.act = act;
+    p.out = out;
+    p.K = (uint32_t)K;
+    p.N = (uint32_t)N;
+    p.nblk = (uint32_t)(K / 256);
+    p.row_bytes = p.nblk * 144;
+    p.stage_rows = 32;
+    p.stage_bytes = p.stage_rows * p.row_bytes;  // multiple of 128
+    p.act_off = 128;
+    p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
+    p.nstages = 3;
+    p.act_dtype = act_dtype;
+    p.out_dtype = out_dtype;
+    p.status = status;
+    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    // one CTA per SM, but never fewer than ~16 rows per CTA
+    size_t grid = (N + 15) / 16;
+    if (grid > (size_t)sm_count) grid = sm_count;
+    gemv_m1_q4k_kernel<<<(unsigned)grid, 512, smem, st>>>(p);
+    note_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace b200q
