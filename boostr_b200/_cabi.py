@@ -17,6 +17,7 @@ OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_FORMAT, ERR_BAD_SHAPE, ERR_WORKSPACE_TOO_SM
     ERR_UNSUPPORTED_DTYPE = range(8)
 DT_F32, DT_BF16, DT_F16, DT_F64 = range(4)
 OP_QUANT_MATMUL, OP_QUANT_SWIGLU = 0, 1
+STATIC_SCRATCH_BYTES = 8 << 20
 
 # every symbol include/b200q.h declares: name -> (restype, argtypes)
 SIGNATURES = {
@@ -34,6 +35,8 @@ SIGNATURES = {
                                          c_size_t, c_void_p]),
     "b200q_quant_swiglu": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                    c_size_t, c_void_p, c_size_t, c_void_p]),
+    "b200q_quant_matmul_static_scratch": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
+                                                  c_size_t, c_void_p]),
     "b200q_shard_pack": (c_int, [c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_int, c_void_p, c_size_t]),
     "b200q_check_device_status": (c_int, [c_void_p]),
     "b200q_launch_count": (ctypes.c_ulonglong, []),

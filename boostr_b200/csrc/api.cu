@@ -270,6 +270,55 @@ int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, i
     return fail(B200Q_ERR_INVALID_ARG, "shard_pack: dim must be 0 or 1, got %d", dim);
 }
 
+}  // extern "C" (reopened below)
+
+// Scratch of b200q_quant_matmul_static_scratch.  In host code this name is only a handle of the
+// symbol; the address kernels can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[B200Q_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_static_scratch on the current device; resolved on the first call made with
+// that device current.  Returns nullptr (and sets *err) when the lookup fails.
+void* static_scratch_current(cudaError_t* err) {
+    static void* cached[64];
+    static cudaError_t status[64];
+    static std::once_flag once[64];
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev < 0 || dev >= 64) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    std::call_once(once[dev], [dev] {
+        void* p = nullptr;
+        status[dev] = cudaGetSymbolAddress(&p, g_static_scratch);
+        cached[dev] = status[dev] == cudaSuccess ? p : nullptr;
+    });
+    *err = status[dev];
+    return cached[dev];
+}
+}  // namespace
+
+extern "C" {
+
+int b200q_quant_matmul_static_scratch(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype,
+                                      size_t M, size_t K, size_t N, void* stream) {
+    int rc = check_matmul_args("quant_matmul_static_scratch", format, act, act_dtype, w, out, out_dtype, M, K, N);
+    if (rc) return rc;
+    const size_t need = b200q_workspace_bytes(B200Q_OP_QUANT_MATMUL, format, M, K, N);
+    if (need > B200Q_STATIC_SCRATCH_BYTES)
+        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL,
+                    "quant_matmul_static_scratch: this shape (M=%zu K=%zu N=%zu) needs %zu bytes of scratch, the built-in "
+                    "array holds %u; use b200q_quant_matmul with caller-provided scratch",
+                    M, K, N, need, (unsigned)B200Q_STATIC_SCRATCH_BYTES);
+    cudaError_t e = cudaSuccess;
+    void* scratch = static_scratch_current(&e);
+    if (!scratch)
+        return fail(B200Q_ERR_CUDA, "quant_matmul_static_scratch: cannot resolve the scratch array: %s", cudaGetErrorString(e));
+    return b200q_quant_matmul(format, act, act_dtype, w, out, out_dtype, M, K, N, scratch, B200Q_STATIC_SCRATCH_BYTES, stream);
+}
+
 unsigned long long b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int b200q_check_device_status(void* stream) {

@@ -134,6 +134,32 @@ B200Q_API int b200q_quant_swiglu(int format, const void* act, int act_dtype, con
                                  void* stream);
 
 /*
+ * quant_matmul for callers that cannot hand over scratch memory.  (No counterpart in boostr:
+ * its CUDA backend always has numr's allocator at hand.)
+ *
+ * Some hosts reach this library with nothing but the pointers of their inputs and outputs:
+ * an FFI caller whose tensor runtime has reserved all device memory for its own pool, or a
+ * code path where a cudaMalloc — which can synchronise the whole device — is not acceptable.
+ * For them the split-K partial sums that b200q_quant_matmul keeps in `ws` live in a fixed
+ * B200Q_STATIC_SCRATCH_BYTES array inside the library's device image instead (every GPU that
+ * loads the library holds that array until the process exits).  The call allocates nothing:
+ * no cudaMalloc, no cudaFree, no allocating library routine.
+ *
+ *   - Same arguments, results and errors as b200q_quant_matmul, minus ws / ws_bytes.  A shape
+ *     whose scratch need (b200q_workspace_bytes) exceeds B200Q_STATIC_SCRATCH_BYTES is refused
+ *     with B200Q_ERR_WORKSPACE_TOO_SMALL and a message naming both sizes.
+ *   - The first call on a device resolves the array's device address (once per device, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to start at zero: every partial sum is written before it is read.
+ *     Two calls that may run on the GPU at the same time (different streams) race on it;
+ *     keep such calls on one stream or order them yourself.
+ */
+#define B200Q_STATIC_SCRATCH_BYTES (8u << 20)
+B200Q_API int b200q_quant_matmul_static_scratch(int format, const void* act, int act_dtype, const void* w, void* out,
+                                                int out_dtype, size_t M, size_t K, size_t N, void* stream);
+
+/*
  * Tensor-parallel shard extraction, HOST memory to HOST memory.  boostr shards dense
  * weights with scatter_to_rank (src/distributed/tensor_parallel.rs:258-300) and has no
  * quantised counterpart; this cuts rank `rank` of `world` out of a packed [N,K] weight:
