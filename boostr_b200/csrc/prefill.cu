@@ -1,17 +1,337 @@
-// Tensor-core prefill GEMM (M >= 64): placeholder translation unit until the tcgen05 kernel lands.
+// Prefill GEMM (M >= 64) on the 5th-generation tensor cores:  out[M,N] = act[M,K] x dequant(W[N,K])^T.
+//
+// Stands in for boostr's quant_matmul_*_f32 "GEMM" kernels (src/quant/cuda/kernels/quant_matmul.cu:20-330:
+// scalar decode + FFMA, no tensor cores).  Here the contraction runs on tcgen05.mma with the accumulator
+// in tensor memory:
+//   * orientation: the WEIGHT tile is the MMA's A operand (128 weight rows = the 128 TMEM lanes), the
+//     ACTIVATION tile is the B operand (MT = 64/128/256 activation rows = TMEM columns).  The packed
+//     weights are decoded once per (128 x MT) output tile, so a larger MT amortises the decode.
+//   * activations are bf16 [M,K] (converted once from f32 when needed) and arrive by TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring;
+//   * four dequant warps (one thread per weight row) read the packed blocks of their row for a 64-wide
+//     K step, decode them exactly in f32 (the same expressions as the dequant kernel), round once to
+//     bf16 and store the row into the K-major, 128B-swizzled A tile of the stage;
+//   * one thread issues four 128 x MT x 16 tcgen05.mma per K step and commits the stage back to the
+//     producers through an mbarrier; after the last step it commits the accumulator to the epilogue;
+//   * the dequant warps then read the accumulator with tcgen05.ld (lane = weight row, columns =
+//     activation rows) and store out[m, n] with n contiguous across lanes.
+// Every mbarrier wait is bounded; on a timeout the CTA records a status code, skips the work that
+// depended on the wait and still frees its tensor memory.
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200q {
 
-bool prefill_supported(int, size_t, size_t, size_t) { return false; }
-size_t prefill_workspace_bytes(int, int, size_t, size_t, size_t) { return 0; }
-cudaError_t launch_prefill(int, const void*, int, const void*, void*, int, size_t, size_t, size_t, void*, size_t, int,
-                           cudaStream_t, unsigned int*, bool* ws_too_small, char*, size_t) {
-    *ws_too_small = false;
-    return cudaErrorNotSupported;
-}
+struct PrefillParams {
+    const uint8_t* w;
+    void* out;
+    uint32_t M, N, K;
+    uint32_t row_bytes;
+    uint32_t mt;      // activation rows per tile (MMA N): 64, 128 or 256
+    uint32_t idesc;   // tcgen05 instruction descriptor
+    uint32_t nkt;     // K / 64
+    uint32_t nstages;
+    int out_dtype;
+    unsigned int* status;
+};
 
 namespace {
+
+constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
+constexpr int A_TILE_BYTES = 128 * BK * 2;
+constexpr int PF_MAX_STAGES = 6;
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;             // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;             // layout type: 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t g16(const uint8_t* p) { return __ldg(reinterpret_cast<const unsigned short*>(p)); }
+__device__ __forceinline__ uint32_t g32(const uint8_t* p) {  // 4 bytes at a 2-byte-aligned address
+    if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
+    return g16(p) | (g16(p + 2) << 16);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// float value of byte `I` of x (0..255) without an integer-to-float conversion instruction
+template <int I>
+__device__ __forceinline__ float byte_to_float(uint32_t x) {
+    return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 | I)) - 8388608.0f;
+}
+
+// Decodes the 64 elements [64*kt, 64*kt + 64) of one weight row into 64 bf16 (32 packed words).
+// The expressions are those of the dequant kernel, so each value is the RNE bf16 of the exact weight.
+template <int FMT>
+__device__ __forceinline__ void decode64(const uint8_t* row, uint32_t kt, uint32_t (&o)[32]) {
+    if constexpr (FMT == FMT_Q4_K) {
+        const uint8_t* blk = row + (kt >> 2) * 144;
+        const uint32_t jj = kt & 3;  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
+        const uint4 hd = __ldg(reinterpret_cast<const uint4*>(blk));
+        const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
+        uint32_t sc, mn;
+        if (jj < 2) {
+            sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
+            mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
+        } else {
+            const uint32_t sh = 16 * (jj - 2);
+            sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
+            mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
+        }
+        const float dl0 = d * (float)(sc & 0xFF), dl1 = d * (float)(sc >> 8);
+        const float ml0 = dmin * (float)(mn & 0xFF), ml1 = dmin * (float)(mn >> 8);
+        const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * jj));
+        const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * jj));
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+            // dl * q is exact (17 x 4 bits), so the fused form rounds once exactly like multiply-then-subtract
+            o[2 * i] = pack_bf16(fmaf(dl0, byte_to_float<0>(lo), -ml0), fmaf(dl0, byte_to_float<1>(lo), -ml0));
+            o[2 * i + 1] = pack_bf16(fmaf(dl0, byte_to_float<2>(lo), -ml0), fmaf(dl0, byte_to_float<3>(lo), -ml0));
+            o[16 + 2 * i] = pack_bf16(fmaf(dl1, byte_to_float<0>(hi), -ml1), fmaf(dl1, byte_to_float<1>(hi), -ml1));
+            o[16 + 2 * i + 1] = pack_bf16(fmaf(dl1, byte_to_float<2>(hi), -ml1), fmaf(dl1, byte_to_float<3>(hi), -ml1));
+        }
+    } else if constexpr (FMT == FMT_Q6_K) {
+        const uint8_t* blk = row + (kt >> 2) * 210;
+        const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + {0,1}) + l
+        const float d = f16bits_to_f32(g16(blk + 208));
+#pragma unroll
+        for (int gg = 0; gg < 2; ++gg) {
+            const uint32_t gq = g0 + gg;
+            const uint8_t* ql = blk + 64 * n + 32 * gg;  // gq & 1 == gg
+            const uint8_t* qh = blk + 128 + 32 * n;
+            const float s0 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq);
+            const float s1 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq + 1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t lw = g32(ql + 4 * i), hw = g32(qh + 4 * i);
+                const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
+                const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
+                const float s = i < 4 ? s0 : s1;
+                o[16 * gg + 2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
+                o[16 * gg + 2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
+            }
+        }
+    } else if constexpr (FMT == FMT_Q8_0) {
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const uint8_t* blk = row + (2 * kt + b) * 34;
+            const float d = f16bits_to_f32(g16(blk));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t x = g32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
+                o[16 * b + 2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
+                o[16 * b + 2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
+            }
+        }
+    } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const uint8_t* blk = row + (2 * kt + b) * 18;
+            const float d = f16bits_to_f32(g16(blk));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t x = g32(blk + 2 + 4 * i);
+                const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+                o[16 * b + 4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
+                o[16 * b + 4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
+                o[16 * b + 4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
+                o[16 * b + 4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
+            }
+        }
+    }
+}
+
+// dynamic shared memory: [0,1024) barriers + TMEM base; then nstages x (A tile 16 KB | B tile mt*128 B), 1 KB aligned
+constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY = 128, PF_OFF_ACC = 192, PF_OFF_TMEM = 200, PF_OFF_DEAD = 204;
+
+template <int FMT>
+__global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act, const PrefillParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B, bar_empty = sbase + PF_OFF_EMPTY;
+    const uint32_t bar_acc = sbase + PF_OFF_ACC;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_TMEM);
+    volatile uint32_t* dead_flag = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_DEAD);
+    const uint32_t stage_bytes = A_TILE_BYTES + p.mt * 128;
+    const uint32_t tiles0 = sbase + 1024;
+    const uint32_t n0 = blockIdx.x * 128, m0 = blockIdx.y * p.mt;
+    const uint32_t tmem_cols = p.mt < 32 ? 32 : p.mt;  // power of two by construction (64/128/256)
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.nstages; ++s) {
+            mbar_init(bar_full_a + 8 * s, 128);
+            mbar_init(bar_full_b + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *dead_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {  // tensor-memory columns for the accumulator, allocated by one whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + PF_OFF_TMEM), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_holder;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ activation tiles by TMA
+        if (lane == 0) {
+            uint32_t s = 0, par = 0;
+            for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                if (*dead_flag) break;
+                if (!mbar_wait(bar_empty + 8 * s, par ^ 1)) {
+                    *dead_flag = 1;
+                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(bar_full_b + 8 * s, p.mt * 128);
+                tma_load_2d(tiles0 + s * stage_bytes + A_TILE_BYTES, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
+                if (++s == p.nstages) { s = 0; par ^= 1; }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issue (one thread)
+        if (lane == 0) {
+            uint32_t s = 0, par = 0;
+            bool ok = true;
+            for (uint32_t kt = 0; kt < p.nkt && ok; ++kt) {
+                if (*dead_flag || !mbar_wait(bar_full_a + 8 * s, par) || !mbar_wait(bar_full_b + 8 * s, par)) {
+                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                    *dead_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = tiles0 + s * stage_bytes, b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    tc_mma_bf16(tmem_acc, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
+                tc_commit(bar_empty + 8 * s);  // the stage may be overwritten once these MMAs have read it
+                if (++s == p.nstages) { s = 0; par ^= 1; }
+            }
+            tc_commit(bar_acc);  // arrives when every MMA issued above has completed (at once if none were)
+        }
+    } else {
+        // ------------------------------------------------------------ dequant warps, then epilogue
+        const uint32_t r = threadIdx.x;  // weight row of the tile == TMEM lane
+        const bool row_ok = n0 + r < p.N;
+        const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
+        uint32_t s = 0, par = 0;
+        bool ok = true;
+        for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+            uint32_t o[32];
+            if (row_ok) decode64<FMT>(wrow, kt, o);
+            else
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = 0;
+            if (ok && (*dead_flag || !mbar_wait(bar_empty + 8 * s, par ^ 1))) {
+                if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                *dead_flag = 1;
+                ok = false;
+            }
+            if (ok) {
+                uint8_t* arow = smem + 1024 + s * stage_bytes + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)  // 16-byte chunk c of row r lives at chunk c ^ (r & 7)
+                    *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+            }
+            mbar_arrive(bar_full_a + 8 * s);
+            if (++s == p.nstages) { s = 0; par ^= 1; }
+        }
+        // epilogue: accumulator lane r = weight row n0 + r, column c = activation row m0 + c
+        if (ok && !mbar_wait(bar_acc, 0)) {
+            atomicOr(p.status, STATUS_TIMEOUT_MMA);
+            *dead_flag = 1;
+            ok = false;
+        }
+        tc_fence_after();
+        if (ok && !*dead_flag) {
+            for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
+                if (m0 + c0 >= p.M) break;  // warp-uniform
+                uint32_t v[16];
+                tmem_ld16(tmem_acc + ((uint32_t)(warp * 32) << 16) + c0, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t m = m0 + c0 + i;
+                        if (m < p.M) {
+                            const size_t idx = (size_t)m * p.N + n0 + r;
+                            const float f = __uint_as_float(v[i]);
+                            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = f;
+                            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(f);
+                            else static_cast<__half*>(p.out)[idx] = __float2half_rn(f);
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
+    const size_t n4 = n / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
+        uint2 r;
+        r.x = pack_bf16(v.x, v.y);
+        r.y = pack_bf16(v.z, v.w);
+        reinterpret_cast<uint2*>(out)[i] = r;
+    }
+}
+
 __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restrict__ g, const float* __restrict__ u, void* out,
                                                           int out_dtype, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -22,7 +342,113 @@ __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restric
         else static_cast<__half*>(out)[i] = __float2half_rn(v);
     }
 }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
+
+template <int FMT>
+cudaError_t launch_fmt(const CUtensorMap& map, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    prefill_kernel<FMT><<<grid, 192, smem, st>>>(map, p);
+    note_launch();
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
+    (void)fmt;
+    return M >= 64 && K % 64 == 0 && K % 8 == 0 && N >= 1;
+}
+
+size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
+    (void)fmt; (void)N;
+    return act_dtype == DT_BF16 ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
+}
+
+cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
+                           size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
+                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len) {
+    *ws_too_small = false;
+    const void* act_bf16 = act;
+    if (act_dtype != DT_BF16) {
+        const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N);
+        if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
+        size_t n = M * K;
+        int grid = (int)((n / 4 + 255) / 256);
+        if (grid > sm_count * 16) grid = sm_count * 16;
+        if (grid < 1) grid = 1;
+        f32_to_bf16_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(act), static_cast<__nv_bfloat16*>(ws), n);
+        note_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        act_bf16 = ws;
+    }
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled is not available from this driver");
+        return cudaErrorNotSupported;
+    }
+    PrefillParams p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.out = out;
+    p.M = (uint32_t)M; p.N = (uint32_t)N; p.K = (uint32_t)K;
+    p.row_bytes = (uint32_t)(K / fmt_block_size(fmt) * fmt_block_bytes(fmt));
+    p.mt = pick_mt(M);
+    p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.mt >> 3) << 17) | ((128u >> 4) << 24);  // f32 acc, bf16 x bf16, K-major, N = mt, M = 128
+    p.nkt = (uint32_t)(K / BK);
+    const uint32_t stage_bytes = A_TILE_BYTES + p.mt * 128;
+    uint32_t ns = (232448 - 1024 - 2048) / stage_bytes;
+    if (ns > (uint32_t)PF_MAX_STAGES) ns = PF_MAX_STAGES;
+    if (ns > p.nkt) ns = p.nkt;
+    p.nstages = ns;
+    p.out_dtype = out_dtype;
+    p.status = status;
+    const size_t smem = 2048 + (size_t)ns * stage_bytes;
+
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t gstride[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, p.mt};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(act_bf16), gdim, gstride, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (activation pointer %p, K=%zu, M=%zu)", (int)cr, act_bf16, K, M);
+        return cudaErrorInvalidValue;
+    }
+    dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + p.mt - 1) / p.mt), 1);
+    switch (fmt) {
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(map, p, grid, smem, st);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(map, p, grid, smem, st);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(map, p, grid, smem, st);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(map, p, grid, smem, st);
+    default: return cudaErrorInvalidValue;
+    }
+}
 
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
                                cudaStream_t st) {

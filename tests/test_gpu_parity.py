@@ -291,3 +291,84 @@ def test_baseline_shapes(ops, oracle, fmt, m, n, k):
     e_max, e_rms = rel_err(got, want)
     print(f"{fmt} M={m} N={n} K={k}: max-norm {e_max:.2e} rms {e_rms:.2e}")
     assert e_max <= _bound(fmt, m), describe_mismatch(got, want)
+
+
+# ------------------------------------------------------------------ prefill (M >= 64): tcgen05 tensor-core path
+
+PREFILL_SHAPES = [(64, 128, 256), (64, 130, 512), (100, 257, 1024), (128, 384, 4096), (300, 200, 2048), (512, 1024, 4096)]
+
+
+def _bf16_reference(ops, act_bf, qt):
+    """What the tensor-core path computes by construction: bf16 activations x bf16(dequantised weights),
+    f32 accumulate — independent of the CPU path's activation quantisation."""
+    w = ops.dequantize(qt, torch.bfloat16).float()
+    return (act_bf.float() @ w.t()).cpu().numpy()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,n,k", PREFILL_SHAPES)
+def test_prefill_tensor_core_path(ops, oracle, fmt, m, n, k):
+    rng = synth.rng_for(32, seed_of(fmt, m, n, k))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    qt = _qt(fmt, w, n, k)
+    act_t = torch.from_numpy(act).cuda()
+    canary = torch.full((256,), 777.0, device="cuda")
+    got = ops.quant_matmul(act_t, qt).cpu().numpy()
+    ops.check_device_status()
+    assert torch.all(canary == 777.0)
+    assert got.shape == (m, n) and np.isfinite(got).all()
+    # (1) the kernel against its own definition (tight): same bf16 operands, f32 accumulation
+    ref_tc = _bf16_reference(ops, act_t.to(torch.bfloat16), qt)
+    e_tc, _ = rel_err(got, ref_tc)
+    assert e_tc <= 2e-5, f"{fmt} M={m} N={n} K={k}: vs bf16 reference {e_tc:.3e}\n" + describe_mismatch(got, ref_tc)
+    # (2) against boostr's CPU path: the stated bound of the bf16 tensor-core path
+    want = oracle.quant_matmul(fmt, act, w, n, threads=os.cpu_count() or 8)
+    e_max, e_rms = rel_err(got, want)
+    print(f"prefill {fmt} M={m} N={n} K={k}: vs CPU path max-norm {e_max:.2e} rms {e_rms:.2e}")
+    assert e_max <= 1e-2, describe_mismatch(got, want)
+
+
+def test_prefill_bf16_activations_and_outputs(ops):
+    rng = synth.rng_for(33)
+    m, n, k = 96, 256, 1024
+    act = torch.from_numpy(synth.activations(rng, m, k)).cuda().to(torch.bfloat16)
+    qt = _qt("Q4_K", synth.weight_bytes("Q4_K", rng, n, k), n, k)
+    ref = _bf16_reference(ops, act, qt)
+    got = ops.quant_matmul(act, qt).cpu().numpy()
+    assert rel_err(got, ref)[0] <= 2e-5
+    got16 = ops.quant_matmul(act, qt, out_dtype=torch.bfloat16).float().cpu().numpy()
+    assert rel_err(got16, ref)[0] <= 1e-2
+
+
+def test_prefill_baseline_c3(ops, oracle):
+    # config 3: Q4_K, K=4096, N=14336, bf16 activations; M=512 fully against the CPU path,
+    # M=2048 against the bf16 definition plus 64 sampled columns against the CPU path
+    rng = synth.rng_for(3, 2)
+    n, k = 14336, 4096
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    qt = _qt("Q4_K", w, n, k)
+    for m in (512, 2048):
+        act = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(synth.activations(rng, m, k))).reshape(m, k)
+        act_t = torch.from_numpy(act).cuda().to(torch.bfloat16)
+        got = ops.quant_matmul(act_t, qt).cpu().numpy()
+        ops.check_device_status()
+        assert rel_err(got, _bf16_reference(ops, act_t, qt))[0] <= 2e-5
+        cols = np.arange(0, n, n // 64)[:64] if m == 2048 else np.arange(0, n, 7)
+        wsub = np.ascontiguousarray(w.reshape(n, -1)[cols]).reshape(-1)
+        want = oracle.quant_matmul("Q4_K", act, wsub, len(cols), threads=os.cpu_count() or 8)
+        e_max, e_rms = rel_err(got[:, cols], want)
+        print(f"C3 M={m}: vs CPU path max-norm {e_max:.2e} rms {e_rms:.2e}")
+        assert e_max <= 1e-2
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0"])
+def test_prefill_swiglu(ops, oracle, fmt):
+    rng = synth.rng_for(34, F.parse(fmt).value)
+    m, n, k = 80, 192, 1024
+    act = synth.activations(rng, m, k)
+    wg = synth.weight_bytes(fmt, rng, n, k)
+    wu = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt(fmt, wg, n, k), _qt(fmt, wu, n, k)).cpu().numpy()
+    want = oracle.quant_swiglu(fmt, act, wg, wu, n, threads=4)
+    assert rel_err(got, want)[0] <= 2e-2  # product of two 1e-2-class results
