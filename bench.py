@@ -211,6 +211,12 @@ def time_kernel_family(stack, torch, ops):
     return us, ws[0].storage_bytes()
 
 
+def log(msg):
+    if os.environ.get("BENCH_VERBOSE"):
+        sys.stderr.write(f"[bench r{os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}\n")
+        sys.stderr.flush()
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -228,8 +234,10 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     m = args.m
+    log("process group up; building the stack")
     stack = DecodeStack(m, rank, world)
     torch.cuda.synchronize()
+    log("stack built")
 
     def barrier():
         if world > 1:
@@ -241,6 +249,7 @@ def run_ours(args):
     stack.step()
     torch.cuda.synchronize()
     launches_per_step = ops.launch_count() - launches0
+    log(f"eager step done, {launches_per_step} launches")
     use_graph = not args.no_graph
     graph = None
     if use_graph:
@@ -251,8 +260,10 @@ def run_ours(args):
                 stack.step()
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
+            log("side-stream step done; capturing")
             with torch.cuda.graph(graph):
                 stack.step()
+            log("captured")
         except Exception as e:  # capture of a collective can be refused; fall back to eager launches
             graph = None
             sys.stderr.write(f"[bench] CUDA graph capture failed, running eagerly: {e}\n")
@@ -267,6 +278,7 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         one_step()
     barrier()
+    log("warm-up done")
 
     # ---- device-resident timing: K steps, CUDA events, max over ranks
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -284,6 +296,7 @@ def run_ours(args):
         ms_total = float(t.item())
     ms_per_step = ms_total / args.steps
     ops.check_device_status()
+    log(f"timed region done: {ms_per_step:.3f} ms/step")
 
     # ---- end to end: host activations in, host logits out, every step
     x_host = torch.randn(m, HIDDEN).pin_memory()
@@ -307,6 +320,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_ms /= args.steps
+    log("e2e done")
 
     result = None
     if rank == 0:

@@ -332,6 +332,43 @@ __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restric
     }
 }
 
+// K-quants: boostr's CPU path multiplies Q8_K-quantised activations (one f32 scale per 256, int8
+// codes; src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98).  The tensor-core path follows it:
+// each 256-run is quantised exactly that way and d8 * code is then rounded to bf16, so what
+// separates the two results is bf16 rounding only, not a second, different activation quantiser.
+// One warp per 256-run, 8 values per lane.
+template <typename InT>
+__global__ void __launch_bounds__(256) act_q8k_to_bf16_kernel(const InT* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t nruns) {
+    const int lane = threadIdx.x & 31;
+    for (size_t run = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5); run < nruns; run += (size_t)gridDim.x * 8) {
+        float v[8];
+        const size_t base = run * 256 + 8 * lane;
+        if constexpr (sizeof(InT) == 4) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(in + base)), b = __ldg(reinterpret_cast<const float4*>(in + base) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+            const uint4 r = __ldg(reinterpret_cast<const uint4*>(in + base));
+            v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+            v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+            v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
+            v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float d8 = __fdiv_rn(amax, 127.0f);
+        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+        float q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(d8, (float)max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id)))));
+        uint4 r;
+        r.x = pack_bf16(q[0], q[1]); r.y = pack_bf16(q[2], q[3]); r.z = pack_bf16(q[4], q[5]); r.w = pack_bf16(q[6], q[7]);
+        *reinterpret_cast<uint4*>(out + base) = r;
+    }
+}
+
 __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restrict__ g, const float* __restrict__ u, void* out,
                                                           int out_dtype, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -384,8 +421,9 @@ bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
 }
 
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
-    (void)fmt; (void)N;
-    return act_dtype == DT_BF16 ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
+    (void)N;
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
+    return (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
 }
 
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -393,14 +431,25 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
                            unsigned int* status, bool* ws_too_small, char* err, size_t err_len) {
     *ws_too_small = false;
     const void* act_bf16 = act;
-    if (act_dtype != DT_BF16) {
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    if (act_dtype != DT_BF16 || kq) {
         const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N);
         if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
-        size_t n = M * K;
-        int grid = (int)((n / 4 + 255) / 256);
-        if (grid > sm_count * 16) grid = sm_count * 16;
-        if (grid < 1) grid = 1;
-        f32_to_bf16_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(act), static_cast<__nv_bfloat16*>(ws), n);
+        const size_t n = M * K;
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(ws);
+        if (kq) {
+            const size_t nruns = n / 256;
+            int grid = (int)((nruns + 7) / 8);
+            if (grid > sm_count * 16) grid = sm_count * 16;
+            if (grid < 1) grid = 1;
+            if (act_dtype == DT_F32) act_q8k_to_bf16_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(act), dst, nruns);
+            else act_q8k_to_bf16_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(act), dst, nruns);
+        } else {
+            int grid = (int)((n / 4 + 255) / 256);
+            if (grid > sm_count * 16) grid = sm_count * 16;
+            if (grid < 1) grid = 1;
+            f32_to_bf16_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(act), dst, n);
+        }
         note_launch();
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;

@@ -298,11 +298,23 @@ def test_baseline_shapes(ops, oracle, fmt, m, n, k):
 PREFILL_SHAPES = [(64, 128, 256), (64, 130, 512), (100, 257, 1024), (128, 384, 4096), (300, 200, 2048), (512, 1024, 4096)]
 
 
-def _bf16_reference(ops, act_bf, qt):
-    """What the tensor-core path computes by construction: bf16 activations x bf16(dequantised weights),
-    f32 accumulate — independent of the CPU path's activation quantisation."""
+def _prepared_act(oracle, fmt, act):
+    """bf16 activations as the tensor-core path builds them: K-quants quantise each 256-run to Q8_K
+    (CPU oracle), multiply codes by the scale, then round to bf16; Q4_0/Q8_0 round the f32 values."""
+    act = np.ascontiguousarray(act, dtype=np.float32)
+    if fmt in ("Q4_K", "Q6_K"):
+        q = oracle.quantize_q8k(act.reshape(-1)).reshape(-1, 292)
+        d8 = q[:, 0:4].copy().view(np.float32)
+        codes = q[:, 4:260].view(np.int8).astype(np.float32)
+        act = (codes * d8).astype(np.float32).reshape(act.shape)
+    return torch.from_numpy(oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(act)).reshape(act.shape)).cuda()
+
+
+def _bf16_reference(ops, act_prepared, qt):
+    """What the tensor-core path computes by construction: prepared bf16 activations x
+    bf16(dequantised weights), f32 accumulate."""
     w = ops.dequantize(qt, torch.bfloat16).float()
-    return (act_bf.float() @ w.t()).cpu().numpy()
+    return (act_prepared.float() @ w.t()).cpu().numpy()
 
 
 @pytest.mark.parametrize("fmt", FMTS)
@@ -319,7 +331,7 @@ def test_prefill_tensor_core_path(ops, oracle, fmt, m, n, k):
     assert torch.all(canary == 777.0)
     assert got.shape == (m, n) and np.isfinite(got).all()
     # (1) the kernel against its own definition (tight): same bf16 operands, f32 accumulation
-    ref_tc = _bf16_reference(ops, act_t.to(torch.bfloat16), qt)
+    ref_tc = _bf16_reference(ops, _prepared_act(oracle, fmt, act), qt)
     e_tc, _ = rel_err(got, ref_tc)
     assert e_tc <= 2e-5, f"{fmt} M={m} N={n} K={k}: vs bf16 reference {e_tc:.3e}\n" + describe_mismatch(got, ref_tc)
     # (2) against boostr's CPU path: the stated bound of the bf16 tensor-core path
@@ -329,12 +341,12 @@ def test_prefill_tensor_core_path(ops, oracle, fmt, m, n, k):
     assert e_max <= 1e-2, describe_mismatch(got, want)
 
 
-def test_prefill_bf16_activations_and_outputs(ops):
+def test_prefill_bf16_activations_and_outputs(ops, oracle):
     rng = synth.rng_for(33)
     m, n, k = 96, 256, 1024
     act = torch.from_numpy(synth.activations(rng, m, k)).cuda().to(torch.bfloat16)
     qt = _qt("Q4_K", synth.weight_bytes("Q4_K", rng, n, k), n, k)
-    ref = _bf16_reference(ops, act, qt)
+    ref = _bf16_reference(ops, _prepared_act(oracle, "Q4_K", act.float().cpu().numpy()), qt)
     got = ops.quant_matmul(act, qt).cpu().numpy()
     assert rel_err(got, ref)[0] <= 2e-5
     got16 = ops.quant_matmul(act, qt, out_dtype=torch.bfloat16).float().cpu().numpy()
@@ -353,7 +365,7 @@ def test_prefill_baseline_c3(ops, oracle):
         act_t = torch.from_numpy(act).cuda().to(torch.bfloat16)
         got = ops.quant_matmul(act_t, qt).cpu().numpy()
         ops.check_device_status()
-        assert rel_err(got, _bf16_reference(ops, act_t, qt))[0] <= 2e-5
+        assert rel_err(got, _bf16_reference(ops, _prepared_act(oracle, "Q4_K", act), qt))[0] <= 2e-5
         cols = np.arange(0, n, n // 64)[:64] if m == 2048 else np.arange(0, n, 7)
         wsub = np.ascontiguousarray(w.reshape(n, -1)[cols]).reshape(-1)
         want = oracle.quant_matmul("Q4_K", act, wsub, len(cols), threads=os.cpu_count() or 8)
@@ -372,3 +384,30 @@ def test_prefill_swiglu(ops, oracle, fmt):
     got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt(fmt, wg, n, k), _qt(fmt, wu, n, k)).cpu().numpy()
     want = oracle.quant_swiglu(fmt, act, wg, wu, n, threads=4)
     assert rel_err(got, want)[0] <= 2e-2  # product of two 1e-2-class results
+
+
+# ------------------------------------------------------------------ tensor-parallel shard shapes (one GPU)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("m", [1, 16])
+def test_tp_shard_shapes_of_the_decode_stack(ops, oracle, world, m):
+    """Every per-rank linear of the Llama-3-8B-shaped stack at 2/4/8-way tensor parallelism (rows cut
+    to 96 to keep the CPU side quick): K-split shards give 2-byte-aligned rows and odd slice counts."""
+    rng = synth.rng_for(35, world * 100 + m)
+    rows = 96
+    for fmt, k in [("Q4_K", 4096), ("Q6_K", 4096), ("Q4_K", 4096 // world), ("Q6_K", 14336 // world)]:
+        act = synth.activations(rng, m, k)
+        w = synth.weight_bytes(fmt, rng, rows, k)
+        got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, rows, k)).cpu().numpy()
+        ops.check_device_status()
+        want = oracle.quant_matmul(fmt, act, w, rows, threads=4)
+        e_max, _ = rel_err(got, want)
+        assert e_max <= 2e-6, f"{fmt} K={k} M={m}: {e_max:.3e}\n" + describe_mismatch(got, want)
+    k = 4096
+    act = synth.activations(rng, m, k)
+    wg = synth.weight_bytes("Q4_K", rng, rows, k)
+    wu = synth.weight_bytes("Q4_K", rng, rows, k)
+    got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt("Q4_K", wg, rows, k), _qt("Q4_K", wu, rows, k)).cpu().numpy()
+    want = oracle.quant_swiglu("Q4_K", act, wg, wu, rows, threads=4)
+    assert rel_err(got, want)[0] <= 1e-5
