@@ -322,10 +322,18 @@ def run_ours(args):
     e2e_ms /= args.steps
     log("e2e done")
 
+    clocks = clk.summary()
+    if world > 1:
+        # leave the process group before anything else is captured: a graph capture on one rank while
+        # the others wait in a collective (with NCCL's watchdog thread alive) can stall
+        dist.barrier()
+        dist.destroy_process_group()
+        log("process group destroyed")
     result = None
     if rank == 0:
         pk = peaks()
         k_us, k_bytes = time_kernel_family(stack, torch, ops)
+        log("kernel family timed")
         achieved = k_bytes / k_us / 1e3  # GB/s
         step_gbs = STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         result = {
@@ -342,7 +350,7 @@ def run_ours(args):
             "e2e": {"value": m * 1000.0 / e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": m * HIDDEN * 4,
                     "d2h_bytes_per_step": m * VOCAB * 4},
             "gpu_launches": int(launches_per_step * args.steps),
-            "clocks": clk.summary(),
+            "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "Q4_K decode GEMV, gate-projection shard [%d x %d], M=%d" % (
                              stack.layers[0]["gate"].weight.shape[0], HIDDEN, m),
                          "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
@@ -351,9 +359,6 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_reference(m, budget_s=args.cpu_seconds)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
     return result
 
 

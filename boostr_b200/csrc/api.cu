@@ -16,9 +16,9 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
                         size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
                         unsigned int* status, bool* ws_too_small);
 size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count);
-bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N);
-cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
-                           size_t N, int sm_count, cudaStream_t st, unsigned int* status);
+bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu);
+cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
+                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status);
 bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N);
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -177,8 +177,8 @@ int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w
         e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
                            status, &small, msg, sizeof(msg));
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
-    } else if (gemv_m1_supported(format, M, K, N)) {
-        e = launch_gemv_m1(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else if (gemv_m1_supported(format, M, K, N, false)) {
+        e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
     } else {
         e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
                         st, status, &small);
@@ -232,6 +232,8 @@ int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w
                                status, &small, msg, sizeof(msg));
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_swiglu: %s", msg);
         if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
+    } else if (gemv_m1_supported(format, M, K, N, true)) {
+        e = launch_gemv_m1(format, act, act_dtype, w_gate, w_up, out, out_dtype, K, N, sm_count_current(), st, status);
     } else {
         e = launch_gemv(format, act, act_dtype, w_gate, w_up, out, out_dtype, M, K, N, ws, ws_bytes, true, sm_count_current(),
                         st, status, &small);

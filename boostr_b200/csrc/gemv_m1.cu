@@ -26,12 +26,13 @@ namespace b200q {
 
 struct GemvM1Params {
     const uint8_t* w;
+    const uint8_t* w2;   // up-projection weight (SwiGLU variant)
     const void* act;
     void* out;
     uint32_t K, N;
     uint32_t nblk;       // K / 256 (<= 16)
     uint32_t row_bytes;  // nblk * 144
-    uint32_t stage_rows; // 32
+    uint32_t stage_rows; // output rows per stage: 32, or 16 in the SwiGLU variant (16 gate + 16 up rows)
     uint32_t stage_bytes;
     uint32_t nstages;
     uint32_t act_off, stage_off;
@@ -59,6 +60,9 @@ __device__ __forceinline__ int ubyte(uint32_t x) { return (int)__byte_perm(x, 0u
 //   [272,276) f32 d8
 constexpr int ACT_STRIDE = 288;
 
+// SWIGLU: two weights; a warp takes gate row r (lanes 0-15) and up row r (lanes 16-31) and stores
+// silu(gate . x) * (up . x)  (quant_swiglu, src/quant/traits/quant_matmul.rs:122-127).
+template <bool SWIGLU>
 __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,8 +79,15 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         const uint32_t r0 = row_begin + f * p.stage_rows;
         const uint32_t nrows = min(p.stage_rows, row_end - r0);
         const uint32_t st = f % p.nstages;
-        mbar_expect_tx(bar_full + 8 * st, nrows * p.row_bytes);
-        bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, nrows * p.row_bytes, bar_full + 8 * st);
+        const uint32_t bytes = nrows * p.row_bytes;
+        if (SWIGLU) {
+            mbar_expect_tx(bar_full + 8 * st, 2 * bytes);
+            bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+            bulk_g2s(stage0 + st * p.stage_bytes + 16 * p.row_bytes, p.w2 + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+        } else {
+            mbar_expect_tx(bar_full + 8 * st, bytes);
+            bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+        }
     };
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nstages; ++s) {
@@ -162,10 +173,10 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         }
         const uint32_t r0 = row_begin + f * p.stage_rows;
         const uint32_t nrows = min(p.stage_rows, row_end - r0);
-        const uint32_t rr = 2 * warp + h;  // row of the stage handled by this half-warp
+        const uint32_t rr = SWIGLU ? warp : 2 * warp + h;  // output row of the stage handled by this half-warp
         float term = 0.f;
         if (!dead && rr < nrows && blk_on) {
-            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + rr * p.row_bytes + b * 144;
+            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + (SWIGLU ? 16 * h + warp : rr) * p.row_bytes + b * 144;
             const uint4 hd = *reinterpret_cast<const uint4*>(blk);
             // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
             uint32_t sc[2], mn[2];
@@ -205,7 +216,11 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         // add the block terms of a row (16 lanes)
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
-        if (b == 0 && rr < nrows && !dead) {
+        if (SWIGLU) {
+            const float up = __shfl_xor_sync(0xFFFFFFFFu, term, 16);
+            term = term / (1.0f + expf(-term)) * up;  // meaningful in lane 0 (gate half)
+        }
+        if (b == 0 && (!SWIGLU || h == 0) && rr < nrows && !dead) {
             const size_t idx = r0 + rr;
             if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = term;
             else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(term);
@@ -226,25 +241,294 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
     }
 }
 
-}  // namespace
 
-bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N) {
-    return fmt == FMT_Q4_K && M == 1 && K % 256 == 0 && K <= 4096 && N >= 1;
+// ------------------------------------------------------------------------------------ Q6_K, M = 1
+//
+// Same streaming structure; the differences follow from the format:
+//   * a 210-byte block is only 2-byte aligned inside its row, so a lane reads aligned 32-bit words and
+//     re-assembles each needed word with one prmt whose selector depends on the block's parity;
+//   * a block splits into two independent 128-element halves (64 B of low nibbles, 32 B of high bit
+//     pairs, 8 signed scales each): one warp takes ONE row, lane (b, n) half n of block b;
+//   * 16 rows x 16 blocks (52.5 KB) per stage, 4 stages; K longer than 16 blocks is walked in chunks of
+//     16 blocks through the same ring, the row total carried in a register;
+//   * the 6-bit value is never assembled: nibbles and bit pairs are multiplied separately (dp4a) in
+//     place and the place values (x16, x4, x16, x64) are shifted out of the integer sums;
+//     sum (q-32)*a uses the activation's 16-wide block sums.  All integer arithmetic is exact, the block
+//     term is (d*d8)*sumi as in fused_dot_q6k_q8k (src/quant/cpu/kernels/simd/fused_q6k_q8k_dot.rs:170-224).
+struct GemvM1Q6Params {
+    const uint8_t* w;
+    const void* act;
+    void* out;
+    uint32_t K, N;
+    uint32_t nblk;        // K / 256, a multiple of 8 (rows start on 16-byte boundaries)
+    uint32_t nchunk;      // ceil(nblk / 16)
+    uint32_t row_bytes;   // nblk * 210
+    uint32_t stage_bytes; // 16 rows x 16 blocks x 210 B, rounded up to 128
+    uint32_t nstages;
+    uint32_t act_off, stage_off;
+    int act_dtype, out_dtype;
+    unsigned int* status;
+};
+
+// activation image per 256-block (stride 304 B): [0,256) int8 codes | [256,288) 16 x int16 sums of 16 | [288,292) f32 d8
+constexpr int ACT6_STRIDE = 304;
+
+template <int I>
+__device__ __forceinline__ int sbyte(uint32_t x) {
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0u), "n"(((I | 8) << 12) | ((I | 8) << 8) | ((I | 8) << 4) | I));
+    return r;
 }
 
-cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
-                           size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    (void)fmt;
-    GemvM1Params p{};
+template <bool ACT_REGS>
+__global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
+    uint8_t* act_s = smem + p.act_off;
+    const uint32_t stage0 = smem_u32(smem + p.stage_off);
+
+    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
+    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
+    const uint32_t nslab = (row_end - row_begin + 15) / 16;
+    const uint32_t nfill = nslab * p.nchunk;
+
+    // fill f = (slab f / nchunk, chunk f % nchunk); the whole warp calls this
+    auto issue_fill = [&](uint32_t f) {
+        const uint32_t slab = f / p.nchunk, c = f - slab * p.nchunk;
+        const uint32_t r0 = row_begin + slab * 16;
+        const uint32_t nrows = min(16u, row_end - r0);
+        const uint32_t st = f % p.nstages;
+        const uint32_t cblk = min(16u, p.nblk - c * 16);
+        const uint32_t cbytes = cblk * 210;  // a multiple of 16: nblk % 8 == 0
+        const uint32_t dst = stage0 + st * p.stage_bytes, bar = bar_full + 8 * st;
+        if (p.nchunk == 1) {
+            if (lane == 0) {
+                mbar_expect_tx(bar, nrows * cbytes);
+                bulk_g2s(dst, p.w + (size_t)r0 * p.row_bytes, nrows * cbytes, bar);
+            }
+        } else {
+            if (lane == 0) mbar_expect_tx(bar, nrows * cbytes);
+            __syncwarp();
+            if ((uint32_t)lane < nrows)
+                bulk_g2s(dst + lane * (16 * 210), p.w + (size_t)(r0 + lane) * p.row_bytes + (size_t)c * (16 * 210), cbytes, bar);
+        }
+    };
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.nstages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 16);
+        }
+        mbar_fence_init();
+    }
+    __syncwarp();
+    if (warp == 0)
+        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
+
+    // quantise the activation row to Q8_K: warp w takes blocks w, w+16, ... (8 values per lane)
+    for (uint32_t blk_i = warp; blk_i < p.nblk; blk_i += 16) {
+        float v[8];
+        const size_t base = (size_t)blk_i * 256 + 8 * lane;
+        if (p.act_dtype == DT_F32) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.act) + base);
+            float4 a = __ldg(src), b = __ldg(src + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+            uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.act) + base));
+            v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+            v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+            v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
+            v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float d8 = __fdiv_rn(amax, 127.0f);
+        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+        int c[8], s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id))));
+            s += c[i];
+        }
+        uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
+        uint2 packed;
+        packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
+        packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
+        *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
+        if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
+        if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
+    }
+    __syncthreads();
+
+    const int b = lane >> 1, n = lane & 1;  // block within the chunk, half of the block
+    const uint32_t sel = (b & 1) ? 0x5432u : 0x3210u;  // odd blocks start 2 bytes past a word boundary
+
+    uint32_t a[32];   // int8 codes of this lane's half block (ACT_REGS: loaded once)
+    uint32_t bs[4];   // its eight 16-wide sums as int16 pairs
+    float d8 = 0.f;
+    auto load_act = [&](uint32_t gblk) {
+        const uint8_t* blk = act_s + gblk * ACT6_STRIDE;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint4 q = *reinterpret_cast<const uint4*>(blk + 128 * n + 16 * i);
+            a[4 * i] = q.x; a[4 * i + 1] = q.y; a[4 * i + 2] = q.z; a[4 * i + 3] = q.w;
+        }
+        uint4 q = *reinterpret_cast<const uint4*>(blk + 256 + 16 * n);
+        bs[0] = q.x; bs[1] = q.y; bs[2] = q.z; bs[3] = q.w;
+        d8 = *reinterpret_cast<const float*>(blk + 288);
+    };
+    if (ACT_REGS && (uint32_t)b < p.nblk) load_act(b);
+
+    bool dead = false;
+    uint32_t st = 0, par = 0, c = 0, slab = 0;
+    float row_total = 0.f;
+    for (uint32_t f = 0; f < nfill; ++f) {
+        if (!dead && !mbar_wait(bar_full + 8 * st, par)) {
+            dead = true;
+            atomicOr(p.status, STATUS_TIMEOUT_FULL);
+        }
+        const uint32_t r0 = row_begin + slab * 16;
+        const uint32_t nrows = min(16u, row_end - r0);
+        const uint32_t cblk = min(16u, p.nblk - c * 16);
+        int half_sum = 0;
+        float d6 = 0.f;
+        const bool on = !dead && (uint32_t)warp < nrows && (uint32_t)b < cblk;
+        if (on) {
+            if (!ACT_REGS) load_act(c * 16 + b);
+            const uint32_t rstride = p.nchunk == 1 ? cblk * 210 : 16 * 210;
+            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + warp * rstride + b * 210;
+            const uint32_t* W = reinterpret_cast<const uint32_t*>(blk - 2 * (b & 1));  // aligned words covering the block
+            auto word = [&](int i) { return __byte_perm(W[i], W[i + 1], sel); };   // bytes [4i, 4i+4) of the block
+            const uint32_t sc0 = word(48 + 2 * n), sc1 = word(49 + 2 * n);          // 8 signed scales of this half
+            d6 = f16bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
+#pragma unroll
+            for (int is = 0; is < 2; ++is) {
+                int dn[4] = {0, 0, 0, 0}, dh[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int idx = 4 * is + i;
+                    const uint32_t l0 = word(16 * n + idx), l1 = word(16 * n + 8 + idx), hw = word(32 + 8 * n + idx);
+                    dn[0] = dp4a_u8s8(l0 & 0x0F0F0F0Fu, a[4 * (0 + is) + i], dn[0]);
+                    dn[1] = dp4a_u8s8(l1 & 0x0F0F0F0Fu, a[4 * (2 + is) + i], dn[1]);
+                    dn[2] = dp4a_u8s8(l0 & 0xF0F0F0F0u, a[4 * (4 + is) + i], dn[2]);
+                    dn[3] = dp4a_u8s8(l1 & 0xF0F0F0F0u, a[4 * (6 + is) + i], dn[3]);
+                    dh[0] = dp4a_u8s8(hw & 0x03030303u, a[4 * (0 + is) + i], dh[0]);
+                    dh[1] = dp4a_u8s8(hw & 0x0C0C0C0Cu, a[4 * (2 + is) + i], dh[1]);
+                    dh[2] = dp4a_u8s8(hw & 0x30303030u, a[4 * (4 + is) + i], dh[2]);
+                    dh[3] = dp4a_u8s8(hw & 0xC0C0C0C0u, a[4 * (6 + is) + i], dh[3]);
+                }
+                // sub-block (gq, is): local index sb = 2 gq + is; q.a = nibble part + 16 * bit-pair part
+                const int qa0 = dn[0] + (dh[0] << 4);
+                const int qa1 = dn[1] + (dh[1] << 2);
+                const int qa2 = (dn[2] >> 4) + dh[2];
+                const int qa3 = (dn[3] >> 4) + (dh[3] >> 2);
+                const int b0 = is ? (int)bs[0] >> 16 : (int)(short)(bs[0] & 0xFFFF);
+                const int b1 = is ? (int)bs[1] >> 16 : (int)(short)(bs[1] & 0xFFFF);
+                const int b2 = is ? (int)bs[2] >> 16 : (int)(short)(bs[2] & 0xFFFF);
+                const int b3 = is ? (int)bs[3] >> 16 : (int)(short)(bs[3] & 0xFFFF);
+                const int s0 = is ? sbyte<1>(sc0) : sbyte<0>(sc0);
+                const int s1 = is ? sbyte<3>(sc0) : sbyte<2>(sc0);
+                const int s2 = is ? sbyte<1>(sc1) : sbyte<0>(sc1);
+                const int s3 = is ? sbyte<3>(sc1) : sbyte<2>(sc1);
+                half_sum += s0 * (qa0 - 32 * b0) + s1 * (qa1 - 32 * b1) + s2 * (qa2 - 32 * b2) + s3 * (qa3 - 32 * b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+        const int sumi = half_sum + __shfl_xor_sync(0xFFFFFFFFu, half_sum, 1);  // the block's integer sum
+        float term = on ? __fmul_rn(__fmul_rn(d6, d8), (float)sumi) : 0.f;
+#pragma unroll
+        for (int o = 16; o > 1; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);  // over the 16 blocks
+        row_total += term;
+        if (c + 1 == p.nchunk) {
+            if (lane == 0 && (uint32_t)warp < nrows && !dead) {
+                const size_t idx = r0 + warp;
+                if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = row_total;
+                else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(row_total);
+                else static_cast<__half*>(p.out)[idx] = __float2half_rn(row_total);
+            }
+            row_total = 0.f;
+        }
+        // refill the stage just released: the warps take turns
+        if (f + p.nstages < nfill && (f & 15) == (uint32_t)warp) {
+            if (!dead && !mbar_wait(bar_empty + 8 * st, par)) {
+                dead = true;
+                atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+            }
+            if (!dead) issue_fill(f + p.nstages);
+        }
+        if (++st == p.nstages) { st = 0; par ^= 1; }
+        if (++c == p.nchunk) { c = 0; ++slab; }
+    }
+}
+
+}  // namespace
+
+bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu) {
+    if (M != 1 || N < 1 || K % 256) return false;
+    if (fmt == FMT_Q4_K) return K <= 4096;
+    // Q6_K: rows must start on 16-byte boundaries (K a multiple of 2048); the activation image must fit
+    if (fmt == FMT_Q6_K) return !swiglu && K % 2048 == 0 && K <= 16384;
+    return false;
+}
+
+static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
+                                      size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    GemvM1Q6Params p{};
     p.w = static_cast<const uint8_t*>(w);
     p.act = act;
     p.out = out;
     p.K = (uint32_t)K;
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
+    p.nchunk = (p.nblk + 15) / 16;
+    p.row_bytes = p.nblk * 210;
+    p.stage_bytes = (16 * 16 * 210 + 127) & ~127u;
+    p.act_off = 128;
+    p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 8 + 127) & ~127u;  // +8: the word pair past the last block half
+    p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;
+    if (p.nstages > 4) p.nstages = 4;
+    p.act_dtype = act_dtype;
+    p.out_dtype = out_dtype;
+    p.status = status;
+    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;  // +64: the aligned word read past the last block
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    size_t grid = (N + 15) / 16;
+    if (grid > (size_t)sm_count) grid = sm_count;
+    if (p.nchunk == 1) gemv_m1_q6k_kernel<true><<<(unsigned)grid, 512, smem, st>>>(p);
+    else gemv_m1_q6k_kernel<false><<<(unsigned)grid, 512, smem, st>>>(p);
+    note_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
+                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
+    const bool swiglu = w_up != nullptr;
+    GemvM1Params p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.w2 = static_cast<const uint8_t*>(w_up);
+    p.act = act;
+    p.out = out;
+    p.K = (uint32_t)K;
+    p.N = (uint32_t)N;
+    p.nblk = (uint32_t)(K / 256);
     p.row_bytes = p.nblk * 144;
-    p.stage_rows = 32;
-    p.stage_bytes = p.stage_rows * p.row_bytes;  // multiple of 128
+    p.stage_rows = swiglu ? 16 : 32;
+    p.stage_bytes = 32 * p.row_bytes;  // multiple of 128
     p.act_off = 128;
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
     p.nstages = 3;
@@ -256,14 +540,17 @@ cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* 
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     // one CTA per SM, but never fewer than ~16 rows per CTA
     size_t grid = (N + 15) / 16;
     if (grid > (size_t)sm_count) grid = sm_count;
-    gemv_m1_q4k_kernel<<<(unsigned)grid, 512, smem, st>>>(p);
+    if (swiglu) gemv_m1_q4k_kernel<true><<<(unsigned)grid, 512, smem, st>>>(p);
+    else gemv_m1_q4k_kernel<false><<<(unsigned)grid, 512, smem, st>>>(p);
     note_launch();
     return cudaGetLastError();
 }
