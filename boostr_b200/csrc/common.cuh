@@ -100,6 +100,30 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ------------------------------------------------------------- programmatic dependent launch
+// Kernels of this library are launched so that a grid may begin while its predecessor in the
+// stream is still draining (launch_pdl below).  grid_dep_launch() lets the NEXT grid start early;
+// grid_dep_wait() blocks until the PREVIOUS grid has completed and its writes are visible — it
+// must precede the first read of activations and the first write of any output or scratch.
+// Weights never change, so their prefetch may be issued before the wait.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ------------------------------------------------------------------- shared-memory loads
 // Plain C++ loads (not asm) so the compiler can schedule them freely between the barrier
 // operations, whose asm statements carry memory clobbers.

@@ -702,6 +702,9 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     const uint32_t s = warp % p.spc;   // slice within a chunk
     const uint32_t rg = warp / p.spc;  // row group within a slab
 
+    grid_dep_launch();  // the next kernel may begin (its weight prefetch does not depend on us)
+    grid_dep_wait();    // activations written by the previous kernel are complete from here on
+
     SliceB<FMT, MT, HILO> B[SL];
 #pragma unroll
     for (int c = 0; c < SL; ++c) {
@@ -888,9 +891,9 @@ cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem,
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    k<<<grid, threads, smem, st>>>(p);
+    cudaError_t le = launch_pdl(k, grid, dim3(threads), smem, st, p);
     note_launch();
-    return cudaGetLastError();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 template <int FMT, bool SWIGLU>

@@ -25,10 +25,14 @@
 namespace b200q {
 
 struct GemvM1Params {
-    const uint8_t* w;
-    const uint8_t* w2;   // up-projection weight (SwiGLU variant)
+    // Up to three weights that share the activation row (q/k/v-style batches) form one virtual row
+    // space [0, N): segment s covers rows [seg_end[s-1], seg_end[s]) and writes its own output.
+    const uint8_t* w[3];
+    void* out[3];
+    uint32_t seg_end[3];
+    uint32_t nseg;
+    const uint8_t* w2;   // up-projection weight (SwiGLU variant, single segment)
     const void* act;
-    void* out;
     uint32_t K, N;
     uint32_t nblk;       // K / 256 (<= 16)
     uint32_t row_bytes;  // nblk * 144
@@ -82,11 +86,18 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         const uint32_t bytes = nrows * p.row_bytes;
         if (SWIGLU) {
             mbar_expect_tx(bar_full + 8 * st, 2 * bytes);
-            bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+            bulk_g2s(stage0 + st * p.stage_bytes, p.w[0] + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
             bulk_g2s(stage0 + st * p.stage_bytes + 16 * p.row_bytes, p.w2 + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
         } else {
             mbar_expect_tx(bar_full + 8 * st, bytes);
-            bulk_g2s(stage0 + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+            uint32_t seg_begin = 0;
+            for (uint32_t sg = 0; sg < p.nseg; ++sg) {  // the part of [r0, r0 + nrows) inside each segment
+                const uint32_t lo = max(r0, seg_begin), hi = min(r0 + nrows, p.seg_end[sg]);
+                if (lo < hi)
+                    bulk_g2s(stage0 + st * p.stage_bytes + (lo - r0) * p.row_bytes,
+                             p.w[sg] + (size_t)(lo - seg_begin) * p.row_bytes, (hi - lo) * p.row_bytes, bar_full + 8 * st);
+                seg_begin = p.seg_end[sg];
+            }
         }
     };
     if (threadIdx.x == 0) {
@@ -99,6 +110,8 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         // overlap the activation quantisation below
         for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
     }
+    grid_dep_launch();  // the next kernel may start its own weight prefetch as SMs free up
+    grid_dep_wait();    // the previous kernel's output (our activations) is complete from here on
 
     // 1. quantise the activation row: warp w owns block w (8 values per lane); warp 0, whose
     // first lane is busy issuing copies, takes its block last
@@ -221,10 +234,13 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
             term = term / (1.0f + expf(-term)) * up;  // meaningful in lane 0 (gate half)
         }
         if (b == 0 && (!SWIGLU || h == 0) && rr < nrows && !dead) {
-            const size_t idx = r0 + rr;
-            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = term;
-            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(term);
-            else static_cast<__half*>(p.out)[idx] = __float2half_rn(term);
+            uint32_t v = r0 + rr, sg = 0, seg_begin = 0;
+            while (sg + 1 < p.nseg && v >= p.seg_end[sg]) seg_begin = p.seg_end[sg++];
+            const size_t idx = v - seg_begin;
+            void* o = p.out[sg];
+            if (p.out_dtype == DT_F32) static_cast<float*>(o)[idx] = term;
+            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(o)[idx] = __float2bfloat16_rn(term);
+            else static_cast<__half*>(o)[idx] = __float2half_rn(term);
         }
         // refill the stage just released: the warps take turns, so nobody is "the producer"
         if (f + p.nstages < nfill && (f & 15) == (uint32_t)warp) {
@@ -324,6 +340,8 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
     __syncwarp();
     if (warp == 0)
         for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
+    grid_dep_launch();
+    grid_dep_wait();
 
     // quantise the activation row to Q8_K: warp w takes blocks w, w+16, ... (8 values per lane)
     for (uint32_t blk_i = warp; blk_i < p.nblk; blk_i += 16) {
@@ -508,21 +526,38 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
     }
     size_t grid = (N + 15) / 16;
     if (grid > (size_t)sm_count) grid = sm_count;
-    if (p.nchunk == 1) gemv_m1_q6k_kernel<true><<<(unsigned)grid, 512, smem, st>>>(p);
-    else gemv_m1_q6k_kernel<false><<<(unsigned)grid, 512, smem, st>>>(p);
+    cudaError_t le = p.nchunk == 1 ? launch_pdl(gemv_m1_q6k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                                   : launch_pdl(gemv_m1_q6k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();
-    return cudaGetLastError();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
+
+// Q4_K, M = 1: `nseg` weights (1..3) sharing one activation row, each [n[i], K] with its own output.
+cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
+                                 void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
+                                 unsigned int* status);
 
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
                            int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
     if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
+    return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status);
+}
+
+cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
+                                 void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
+                                 unsigned int* status) {
     const bool swiglu = w_up != nullptr;
     GemvM1Params p{};
-    p.w = static_cast<const uint8_t*>(w);
+    size_t N = 0;
+    for (int i = 0; i < nseg && i < 3; ++i) {
+        p.w[i] = static_cast<const uint8_t*>(w[i]);
+        p.out[i] = out[i];
+        N += n[i];
+        p.seg_end[i] = (uint32_t)N;
+    }
+    p.nseg = (uint32_t)nseg;
     p.w2 = static_cast<const uint8_t*>(w_up);
     p.act = act;
-    p.out = out;
     p.K = (uint32_t)K;
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
@@ -549,10 +584,10 @@ cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* 
     // one CTA per SM, but never fewer than ~16 rows per CTA
     size_t grid = (N + 15) / 16;
     if (grid > (size_t)sm_count) grid = sm_count;
-    if (swiglu) gemv_m1_q4k_kernel<true><<<(unsigned)grid, 512, smem, st>>>(p);
-    else gemv_m1_q4k_kernel<false><<<(unsigned)grid, 512, smem, st>>>(p);
+    cudaError_t le = swiglu ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                            : launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();
-    return cudaGetLastError();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 }  // namespace b200q

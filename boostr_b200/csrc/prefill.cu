@@ -8,9 +8,10 @@
 //     weights are decoded once per (128 x MT) output tile, so a larger MT amortises the decode.
 //   * activations are bf16 [M,K] (converted once from f32 when needed) and arrive by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring;
-//   * four dequant warps (one thread per weight row) read the packed blocks of their row for a 64-wide
-//     K step, decode them exactly in f32 (the same expressions as the dequant kernel), round once to
-//     bf16 and store the row into the K-major, 128B-swizzled A tile of the stage;
+//   * eight dequant warps (two threads per weight row, 32 elements each) read the packed blocks of
+//     their row for a 64-wide K step (one step ahead for Q4_K), decode them exactly in f32 (the same
+//     expressions as the dequant kernel), round once to bf16 and store into the K-major,
+//     128B-swizzled A tile of the stage;
 //   * one thread issues four 128 x MT x 16 tcgen05.mma per K step and commits the stage back to the
 //     producers through an mbarrier; after the last step it commits the accumulator to the epilogue;
 //   * the dequant warps then read the accumulator with tcgen05.ld (lane = weight row, columns =
@@ -98,85 +99,86 @@ __device__ __forceinline__ float byte_to_float(uint32_t x) {
     return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 | I)) - 8388608.0f;
 }
 
-// Decodes the 64 elements [64*kt, 64*kt + 64) of one weight row into 64 bf16 (32 packed words).
-// The expressions are those of the dequant kernel, so each value is the RNE bf16 of the exact weight.
+// Raw bytes a thread needs for 32 elements of a Q4_K row (prefetched one K step ahead).
+struct RawQ4K {
+    uint4 hd, q0, q1;
+};
+__device__ __forceinline__ RawQ4K load_raw_q4k(const uint8_t* row, uint32_t kt) {
+    const uint8_t* blk = row + (kt >> 2) * 144;
+    RawQ4K r;
+    r.hd = __ldg(reinterpret_cast<const uint4*>(blk));
+    r.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kt & 3)));
+    r.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (kt & 3)));
+    return r;
+}
+// Elements [64*kt + 32*half, +32) of a Q4_K row: sub-block 2*(kt&3) + half (low / high nibbles of the
+// same 32 bytes).  The expressions are those of the dequant kernel: RNE bf16 of the exact weight.
+__device__ __forceinline__ void decode32_q4k(const RawQ4K& r, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
+    const uint32_t jj = kt & 3;
+    const uint4 hd = r.hd;
+    const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
+    uint32_t sc, mn;
+    if (jj < 2) {
+        sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
+        mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
+    } else {
+        const uint32_t sh = 16 * (jj - 2);
+        sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
+        mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
+    }
+    const float dl = d * (float)((sc >> (8 * half)) & 0xFF);
+    const float nml = -(dmin * (float)((mn >> (8 * half)) & 0xFF));
+    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t q = (w[i] >> (4 * half)) & 0x0F0F0F0Fu;
+        // dl * q is exact (17 x 4 bits), so the fused form rounds once exactly like multiply-then-subtract
+        o[2 * i] = pack_bf16(fmaf(dl, byte_to_float<0>(q), nml), fmaf(dl, byte_to_float<1>(q), nml));
+        o[2 * i + 1] = pack_bf16(fmaf(dl, byte_to_float<2>(q), nml), fmaf(dl, byte_to_float<3>(q), nml));
+    }
+}
+
+// Elements [64*kt + 32*half, +32) of one weight row as 32 bf16 (16 packed words), other formats.
 template <int FMT>
-__device__ __forceinline__ void decode64(const uint8_t* row, uint32_t kt, uint32_t (&o)[32]) {
-    if constexpr (FMT == FMT_Q4_K) {
-        const uint8_t* blk = row + (kt >> 2) * 144;
-        const uint32_t jj = kt & 3;  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
-        const uint4 hd = __ldg(reinterpret_cast<const uint4*>(blk));
-        const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
-        uint32_t sc, mn;
-        if (jj < 2) {
-            sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
-            mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
-        } else {
-            const uint32_t sh = 16 * (jj - 2);
-            sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
-            mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
-        }
-        const float dl0 = d * (float)(sc & 0xFF), dl1 = d * (float)(sc >> 8);
-        const float ml0 = dmin * (float)(mn & 0xFF), ml1 = dmin * (float)(mn >> 8);
-        const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * jj));
-        const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * jj));
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+__device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
+    if constexpr (FMT == FMT_Q6_K) {
+        const uint8_t* blk = row + (kt >> 2) * 210;
+        const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + half) + l
+        const float d = f16bits_to_f32(g16(blk + 208));
+        const uint32_t gq = g0 + half;
+        const uint8_t* ql = blk + 64 * n + 32 * half;  // gq & 1 == half
+        const uint8_t* qh = blk + 128 + 32 * n;
+        const float s0 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq);
+        const float s1 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq + 1);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
-            // dl * q is exact (17 x 4 bits), so the fused form rounds once exactly like multiply-then-subtract
-            o[2 * i] = pack_bf16(fmaf(dl0, byte_to_float<0>(lo), -ml0), fmaf(dl0, byte_to_float<1>(lo), -ml0));
-            o[2 * i + 1] = pack_bf16(fmaf(dl0, byte_to_float<2>(lo), -ml0), fmaf(dl0, byte_to_float<3>(lo), -ml0));
-            o[16 + 2 * i] = pack_bf16(fmaf(dl1, byte_to_float<0>(hi), -ml1), fmaf(dl1, byte_to_float<1>(hi), -ml1));
-            o[16 + 2 * i + 1] = pack_bf16(fmaf(dl1, byte_to_float<2>(hi), -ml1), fmaf(dl1, byte_to_float<3>(hi), -ml1));
-        }
-    } else if constexpr (FMT == FMT_Q6_K) {
-        const uint8_t* blk = row + (kt >> 2) * 210;
-        const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + {0,1}) + l
-        const float d = f16bits_to_f32(g16(blk + 208));
-#pragma unroll
-        for (int gg = 0; gg < 2; ++gg) {
-            const uint32_t gq = g0 + gg;
-            const uint8_t* ql = blk + 64 * n + 32 * gg;  // gq & 1 == gg
-            const uint8_t* qh = blk + 128 + 32 * n;
-            const float s0 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq);
-            const float s1 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq + 1);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t lw = g32(ql + 4 * i), hw = g32(qh + 4 * i);
-                const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
-                const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
-                const float s = i < 4 ? s0 : s1;
-                o[16 * gg + 2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
-                o[16 * gg + 2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
-            }
+            const uint32_t lw = g32(ql + 4 * i), hw = g32(qh + 4 * i);
+            const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
+            const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
+            const float s = i < 4 ? s0 : s1;
+            o[2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
+            o[2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
         }
     } else if constexpr (FMT == FMT_Q8_0) {
+        const uint8_t* blk = row + (2 * kt + half) * 34;
+        const float d = f16bits_to_f32(g16(blk));
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            const uint8_t* blk = row + (2 * kt + b) * 34;
-            const float d = f16bits_to_f32(g16(blk));
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t x = g32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
-                o[16 * b + 2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
-                o[16 * b + 2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
-            }
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = g32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
+            o[2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
+            o[2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
         }
     } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
+        const uint8_t* blk = row + (2 * kt + half) * 18;
+        const float d = f16bits_to_f32(g16(blk));
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            const uint8_t* blk = row + (2 * kt + b) * 18;
-            const float d = f16bits_to_f32(g16(blk));
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t x = g32(blk + 2 + 4 * i);
-                const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-                o[16 * b + 4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
-                o[16 * b + 4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
-                o[16 * b + 4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
-                o[16 * b + 4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t x = g32(blk + 2 + 4 * i);
+            const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+            o[4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
+            o[4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
+            o[4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
+            o[4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
         }
     }
 }
@@ -185,7 +187,7 @@ __device__ __forceinline__ void decode64(const uint8_t* row, uint32_t kt, uint32
 constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY = 128, PF_OFF_ACC = 192, PF_OFF_TMEM = 200, PF_OFF_DEAD = 204;
 
 template <int FMT>
-__global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act, const PrefillParams p) {
+__global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act, const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full_a + 8 * s, 128);
+            mbar_init(bar_full_a + 8 * s, 256);
             mbar_init(bar_full_b + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
@@ -210,7 +212,7 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
         *dead_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) {  // tensor-memory columns for the accumulator, allocated by one whole warp
+    if (warp == 9) {  // tensor-memory columns for the accumulator, allocated by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + PF_OFF_TMEM), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -219,7 +221,7 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_holder;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             uint32_t s = 0, par = 0;
@@ -235,7 +237,7 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
                 if (++s == p.nstages) { s = 0; par ^= 1; }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             uint32_t s = 0, par = 0;
@@ -259,17 +261,26 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------ dequant warps, then epilogue
-        const uint32_t r = threadIdx.x;  // weight row of the tile == TMEM lane
+        // thread (r, half): weight row r of the tile (= TMEM lane), elements [32*half, 32*half+32) of the K step
+        const uint32_t r = threadIdx.x & 127, half = threadIdx.x >> 7;
         const bool row_ok = n0 + r < p.N;
         const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
         uint32_t s = 0, par = 0;
         bool ok = true;
+        RawQ4K raw;
+        if constexpr (FMT == FMT_Q4_K) raw = load_raw_q4k(wrow, 0);
         for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-            uint32_t o[32];
-            if (row_ok) decode64<FMT>(wrow, kt, o);
-            else
+            uint32_t o[16];
+            if constexpr (FMT == FMT_Q4_K) {
+                const RawQ4K cur = raw;
+                if (kt + 1 < p.nkt) raw = load_raw_q4k(wrow, kt + 1);  // next step's bytes are in flight while this one is decoded
+                decode32_q4k(cur, kt, half, o);
+            } else {
+                decode32<FMT>(wrow, kt, half, o);
+            }
+            if (!row_ok)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = 0;
+                for (int i = 0; i < 16; ++i) o[i] = 0;
             if (ok && (*dead_flag || !mbar_wait(bar_empty + 8 * s, par ^ 1))) {
                 if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                 *dead_flag = 1;
@@ -278,14 +289,17 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
             if (ok) {
                 uint8_t* arow = smem + 1024 + s * stage_bytes + r * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c)  // 16-byte chunk c of row r lives at chunk c ^ (r & 7)
-                    *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
+                    const uint32_t cc = 4 * half + c;
+                    *reinterpret_cast<uint4*>(arow + ((cc ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                }
                 fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
             }
             mbar_arrive(bar_full_a + 8 * s);
             if (++s == p.nstages) { s = 0; par ^= 1; }
         }
-        // epilogue: accumulator lane r = weight row n0 + r, column c = activation row m0 + c
+        // epilogue: accumulator lane r = weight row n0 + r, column c = activation row m0 + c;
+        // warps 0-3 take the first half of the columns, warps 4-7 the second half
         if (ok && !mbar_wait(bar_acc, 0)) {
             atomicOr(p.status, STATUS_TIMEOUT_MMA);
             *dead_flag = 1;
@@ -293,10 +307,11 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
         }
         tc_fence_after();
         if (ok && !*dead_flag) {
-            for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
+            const uint32_t cbeg = half * (p.mt / 2), cend = cbeg + p.mt / 2;
+            for (uint32_t c0 = cbeg; c0 < cend; c0 += 16) {
                 if (m0 + c0 >= p.M) break;  // warp-uniform
                 uint32_t v[16];
-                tmem_ld16(tmem_acc + ((uint32_t)(warp * 32) << 16) + c0, v);
+                tmem_ld16(tmem_acc + ((uint32_t)((warp & 3) * 32) << 16) + c0, v);
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -315,7 +330,7 @@ __global__ void __launch_bounds__(192, 1) prefill_kernel(const __grid_constant__
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
     }
@@ -408,7 +423,7 @@ cudaError_t launch_fmt(const CUtensorMap& map, const PrefillParams& p, dim3 grid
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    prefill_kernel<FMT><<<grid, 192, smem, st>>>(map, p);
+    prefill_kernel<FMT><<<grid, 320, smem, st>>>(map, p);
     note_launch();
     return cudaGetLastError();
 }

@@ -411,3 +411,21 @@ def test_tp_shard_shapes_of_the_decode_stack(ops, oracle, world, m):
     got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt("Q4_K", wg, rows, k), _qt("Q4_K", wu, rows, k)).cpu().numpy()
     want = oracle.quant_swiglu("Q4_K", act, wg, wu, rows, threads=4)
     assert rel_err(got, want)[0] <= 1e-5
+
+
+def test_quant_matmul_batch_decode_fused_launch(ops, oracle):
+    # M = 1: consecutive Q4_K weights share one launch (q/k/v-style); odd row counts exercise segment
+    # boundaries inside a stage
+    rng = synth.rng_for(36)
+    k = 4096
+    act = synth.activations(rng, 1, k)
+    specs = [("Q4_K", 333), ("Q4_K", 50), ("Q4_K", 1024), ("Q6_K", 64), ("Q4_K", 70)]
+    ws = [synth.weight_bytes(f, rng, n, k) for f, n in specs]
+    before = ops.launch_count()
+    outs = ops.quant_matmul_batch(torch.from_numpy(act).cuda(), [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)])
+    ops.check_device_status()
+    assert ops.launch_count() - before == 3  # [Q4_K x3] + [Q6_K] + [Q4_K]
+    for (f, n), w, o in zip(specs, ws, outs):
+        want = oracle.quant_matmul(f, act, w, n)
+        assert o.shape == (1, n)
+        assert rel_err(o.cpu().numpy(), want)[0] < 2e-6, (f, n)
