@@ -276,7 +276,7 @@ struct GemvM1Q6Params {
     const void* act;
     void* out;
     uint32_t K, N;
-    uint32_t nblk;        // K / 256, a multiple of 8 (rows start on 16-byte boundaries)
+    uint32_t nblk;        // K / 256 (<= 16 for this kernel)
     uint32_t nchunk;      // ceil(nblk / 16)
     uint32_t row_bytes;   // nblk * 210
     uint32_t stage_bytes; // 16 rows x 16 blocks x 210 B, rounded up to 128
@@ -294,6 +294,122 @@ __device__ __forceinline__ int sbyte(uint32_t x) {
     int r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0u), "n"(((I | 8) << 12) | ((I | 8) << 8) | ((I | 8) << 4) | I));
     return r;
+}
+
+
+// Copies the 2-byte-aligned global range [src, src + bytes) into shared memory as the enclosing 16-byte
+// aligned range (bulk copies need 16-byte alignment): the data lands at dst + (src & 15).  If that range
+// would end past the tensor (`wend`), the last <16 bytes are moved with plain loads.  One lane calls this.
+__device__ __forceinline__ void fill_contiguous(uint32_t dst_s, uint8_t* dst_g, const uint8_t* src, uint32_t bytes,
+                                                const uint8_t* wend, uint32_t bar) {
+    const uint8_t* gs = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15);
+    const uint8_t* ge = src + bytes;
+    const uint8_t* e16 = reinterpret_cast<const uint8_t*>((reinterpret_cast<uintptr_t>(ge) + 15) & ~(uintptr_t)15);
+    if (e16 > wend) {
+        e16 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(ge) & ~(uintptr_t)15);
+        for (const uint8_t* q = e16; q < ge; ++q) dst_g[q - gs] = __ldg(q);
+    }
+    const uint32_t n = (uint32_t)(e16 - gs);
+    mbar_expect_tx(bar, n);  // release: the plain stores above are visible to whoever sees the phase complete
+    if (n) bulk_g2s(dst_s, gs, n, bar);
+}
+
+// Quantises the activation row to Q8_K into the shared-memory image used by the Q6_K kernels:
+// warp w takes blocks w, w+16, ... (8 values per lane).
+__device__ __forceinline__ void quantize_act_q6_image(const void* act, int act_dtype, uint32_t nblk, uint8_t* act_s, int warp, int lane) {
+    // warp w takes blocks w, w+16, w+32, w+48 (8 values per lane); all loads are issued before any
+    // arithmetic so the kernel pays one round trip to L2, not one per block
+    float v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t blk_i = warp + 16 * j;
+        if (blk_i < nblk) {
+            const size_t base = (size_t)blk_i * 256 + 8 * lane;
+            if (act_dtype == DT_F32) {
+                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(act) + base);
+                float4 a = __ldg(src), b = __ldg(src + 1);
+                v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w; v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+            } else {
+                uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(act) + base));
+                v[j][0] = __uint_as_float(r.x << 16); v[j][1] = __uint_as_float(r.x & 0xFFFF0000u);
+                v[j][2] = __uint_as_float(r.y << 16); v[j][3] = __uint_as_float(r.y & 0xFFFF0000u);
+                v[j][4] = __uint_as_float(r.z << 16); v[j][5] = __uint_as_float(r.z & 0xFFFF0000u);
+                v[j][6] = __uint_as_float(r.w << 16); v[j][7] = __uint_as_float(r.w & 0xFFFF0000u);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t blk_i = warp + 16 * j;
+        if (blk_i < nblk) {  // warp-uniform
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            const float d8 = __fdiv_rn(amax, 127.0f);
+            const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+            int c[8], s = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[j][i], id))));
+                s += c[i];
+            }
+            uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
+            uint2 packed;
+            packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
+            packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
+            *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
+            if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
+            if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
+        }
+    }
+}
+
+// Integer sum over half `n` (128 elements) of the Q6_K block at `blk` (2-byte aligned in shared memory)
+// against the int8 codes `a` / 16-wide sums `bs` of the matching activation half; also returns d.
+__device__ __forceinline__ int q6k_half_sum(const uint8_t* blk, int n, const uint32_t (&a)[32],
+                                    const uint32_t (&bs)[4], float& d6) {
+    int half_sum = 0;
+    const uint32_t odd = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 2);     // the block starts 2 bytes past a word boundary
+    const uint32_t sel = odd ? 0x5432u : 0x3210u;
+    const uint32_t* W = reinterpret_cast<const uint32_t*>(blk - odd);          // aligned words covering the block
+    auto word = [&](int i) { return __byte_perm(W[i], W[i + 1], sel); };   // bytes [4i, 4i+4) of the block
+    const uint32_t sc0 = word(48 + 2 * n), sc1 = word(49 + 2 * n);          // 8 signed scales of this half
+    d6 = f16bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
+#pragma unroll
+    for (int is = 0; is < 2; ++is) {
+        int dn[4] = {0, 0, 0, 0}, dh[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = 4 * is + i;
+            const uint32_t l0 = word(16 * n + idx), l1 = word(16 * n + 8 + idx), hw = word(32 + 8 * n + idx);
+            dn[0] = dp4a_u8s8(l0 & 0x0F0F0F0Fu, a[4 * (0 + is) + i], dn[0]);
+            dn[1] = dp4a_u8s8(l1 & 0x0F0F0F0Fu, a[4 * (2 + is) + i], dn[1]);
+            dn[2] = dp4a_u8s8(l0 & 0xF0F0F0F0u, a[4 * (4 + is) + i], dn[2]);
+            dn[3] = dp4a_u8s8(l1 & 0xF0F0F0F0u, a[4 * (6 + is) + i], dn[3]);
+            dh[0] = dp4a_u8s8(hw & 0x03030303u, a[4 * (0 + is) + i], dh[0]);
+            dh[1] = dp4a_u8s8(hw & 0x0C0C0C0Cu, a[4 * (2 + is) + i], dh[1]);
+            dh[2] = dp4a_u8s8(hw & 0x30303030u, a[4 * (4 + is) + i], dh[2]);
+            dh[3] = dp4a_u8s8(hw & 0xC0C0C0C0u, a[4 * (6 + is) + i], dh[3]);
+        }
+        // sub-block (gq, is): local index sb = 2 gq + is; q.a = nibble part + 16 * bit-pair part
+        const int qa0 = dn[0] + (dh[0] << 4);
+        const int qa1 = dn[1] + (dh[1] << 2);
+        const int qa2 = (dn[2] >> 4) + dh[2];
+        const int qa3 = (dn[3] >> 4) + (dh[3] >> 2);
+        const int b0 = is ? (int)bs[0] >> 16 : (int)(short)(bs[0] & 0xFFFF);
+        const int b1 = is ? (int)bs[1] >> 16 : (int)(short)(bs[1] & 0xFFFF);
+        const int b2 = is ? (int)bs[2] >> 16 : (int)(short)(bs[2] & 0xFFFF);
+        const int b3 = is ? (int)bs[3] >> 16 : (int)(short)(bs[3] & 0xFFFF);
+        const int s0 = is ? sbyte<1>(sc0) : sbyte<0>(sc0);
+        const int s1 = is ? sbyte<3>(sc0) : sbyte<2>(sc0);
+        const int s2 = is ? sbyte<1>(sc1) : sbyte<0>(sc1);
+        const int s3 = is ? sbyte<3>(sc1) : sbyte<2>(sc1);
+        half_sum += s0 * (qa0 - 32 * b0) + s1 * (qa1 - 32 * b1) + s2 * (qa2 - 32 * b2) + s3 * (qa3 - 32 * b3);
+    }
+    return half_sum;
 }
 
 template <bool ACT_REGS>
@@ -316,13 +432,14 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
         const uint32_t nrows = min(16u, row_end - r0);
         const uint32_t st = f % p.nstages;
         const uint32_t cblk = min(16u, p.nblk - c * 16);
-        const uint32_t cbytes = cblk * 210;  // a multiple of 16: nblk % 8 == 0
+        const uint32_t cbytes = cblk * 210;
         const uint32_t dst = stage0 + st * p.stage_bytes, bar = bar_full + 8 * st;
         if (p.nchunk == 1) {
-            if (lane == 0) {
-                mbar_expect_tx(bar, nrows * cbytes);
-                bulk_g2s(dst, p.w + (size_t)r0 * p.row_bytes, nrows * cbytes, bar);
-            }
+            // rows are contiguous: one copy of the enclosing 16-byte-aligned range (rows of a K-split
+            // shard need not start on 16-byte boundaries)
+            if (lane == 0)
+                fill_contiguous(dst, smem + p.stage_off + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, nrows * cbytes,
+                                p.w + (size_t)p.N * p.row_bytes, bar);
         } else {
             if (lane == 0) mbar_expect_tx(bar, nrows * cbytes);
             __syncwarp();
@@ -343,47 +460,10 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
     grid_dep_launch();
     grid_dep_wait();
 
-    // quantise the activation row to Q8_K: warp w takes blocks w, w+16, ... (8 values per lane)
-    for (uint32_t blk_i = warp; blk_i < p.nblk; blk_i += 16) {
-        float v[8];
-        const size_t base = (size_t)blk_i * 256 + 8 * lane;
-        if (p.act_dtype == DT_F32) {
-            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.act) + base);
-            float4 a = __ldg(src), b = __ldg(src + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        } else {
-            uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.act) + base));
-            v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
-            v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
-            v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
-            v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        const float d8 = __fdiv_rn(amax, 127.0f);
-        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
-        int c[8], s = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id))));
-            s += c[i];
-        }
-        uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
-        uint2 packed;
-        packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
-        packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
-        *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
-        if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
-        if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
-    }
+    quantize_act_q6_image(p.act, p.act_dtype, p.nblk, act_s, warp, lane);
     __syncthreads();
 
     const int b = lane >> 1, n = lane & 1;  // block within the chunk, half of the block
-    const uint32_t sel = (b & 1) ? 0x5432u : 0x3210u;  // odd blocks start 2 bytes past a word boundary
 
     uint32_t a[32];   // int8 codes of this lane's half block (ACT_REGS: loaded once)
     uint32_t bs[4];   // its eight 16-wide sums as int16 pairs
@@ -418,42 +498,9 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
         if (on) {
             if (!ACT_REGS) load_act(c * 16 + b);
             const uint32_t rstride = p.nchunk == 1 ? cblk * 210 : 16 * 210;
-            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + warp * rstride + b * 210;
-            const uint32_t* W = reinterpret_cast<const uint32_t*>(blk - 2 * (b & 1));  // aligned words covering the block
-            auto word = [&](int i) { return __byte_perm(W[i], W[i + 1], sel); };   // bytes [4i, 4i+4) of the block
-            const uint32_t sc0 = word(48 + 2 * n), sc1 = word(49 + 2 * n);          // 8 signed scales of this half
-            d6 = f16bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
-#pragma unroll
-            for (int is = 0; is < 2; ++is) {
-                int dn[4] = {0, 0, 0, 0}, dh[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int idx = 4 * is + i;
-                    const uint32_t l0 = word(16 * n + idx), l1 = word(16 * n + 8 + idx), hw = word(32 + 8 * n + idx);
-                    dn[0] = dp4a_u8s8(l0 & 0x0F0F0F0Fu, a[4 * (0 + is) + i], dn[0]);
-                    dn[1] = dp4a_u8s8(l1 & 0x0F0F0F0Fu, a[4 * (2 + is) + i], dn[1]);
-                    dn[2] = dp4a_u8s8(l0 & 0xF0F0F0F0u, a[4 * (4 + is) + i], dn[2]);
-                    dn[3] = dp4a_u8s8(l1 & 0xF0F0F0F0u, a[4 * (6 + is) + i], dn[3]);
-                    dh[0] = dp4a_u8s8(hw & 0x03030303u, a[4 * (0 + is) + i], dh[0]);
-                    dh[1] = dp4a_u8s8(hw & 0x0C0C0C0Cu, a[4 * (2 + is) + i], dh[1]);
-                    dh[2] = dp4a_u8s8(hw & 0x30303030u, a[4 * (4 + is) + i], dh[2]);
-                    dh[3] = dp4a_u8s8(hw & 0xC0C0C0C0u, a[4 * (6 + is) + i], dh[3]);
-                }
-                // sub-block (gq, is): local index sb = 2 gq + is; q.a = nibble part + 16 * bit-pair part
-                const int qa0 = dn[0] + (dh[0] << 4);
-                const int qa1 = dn[1] + (dh[1] << 2);
-                const int qa2 = (dn[2] >> 4) + dh[2];
-                const int qa3 = (dn[3] >> 4) + (dh[3] >> 2);
-                const int b0 = is ? (int)bs[0] >> 16 : (int)(short)(bs[0] & 0xFFFF);
-                const int b1 = is ? (int)bs[1] >> 16 : (int)(short)(bs[1] & 0xFFFF);
-                const int b2 = is ? (int)bs[2] >> 16 : (int)(short)(bs[2] & 0xFFFF);
-                const int b3 = is ? (int)bs[3] >> 16 : (int)(short)(bs[3] & 0xFFFF);
-                const int s0 = is ? sbyte<1>(sc0) : sbyte<0>(sc0);
-                const int s1 = is ? sbyte<3>(sc0) : sbyte<2>(sc0);
-                const int s2 = is ? sbyte<1>(sc1) : sbyte<0>(sc1);
-                const int s3 = is ? sbyte<3>(sc1) : sbyte<2>(sc1);
-                half_sum += s0 * (qa0 - 32 * b0) + s1 * (qa1 - 32 * b1) + s2 * (qa2 - 32 * b2) + s3 * (qa3 - 32 * b3);
-            }
+            const uint32_t phase = p.nchunk == 1 ? (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15) : 0u;
+            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + phase + warp * rstride + b * 210;
+            half_sum = q6k_half_sum(blk, n, a, bs, d6);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * st);
@@ -484,18 +531,233 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
     }
 }
 
+
+// Q6_K, M = 1, K longer than 16 blocks.  A stage holds `rpf` WHOLE rows (contiguous in memory, so one
+// bulk copy per fill); warp (r, c) takes chunk c (16 blocks) of row r with its activation half-blocks in
+// registers, and leaves its chunk sum in a small parity-double-buffered table.  The row totals of a fill
+// are added up (chunks in K order) and stored one fill later, when every warp has long delivered, so
+// nobody waits for the slowest warp.
+struct GemvM1Q6RowsParams {
+    const uint8_t* w;
+    const void* act;
+    void* out;
+    uint32_t K, N;
+    uint32_t nblk, nchunk;  // blocks per row, ceil(nblk / 16) in 2..4
+    uint32_t rpf;           // rows per fill = 16 / nchunk
+    uint32_t row_bytes, stage_bytes, nstages;
+    uint32_t act_off, part_off, stage_off;
+    int act_dtype, out_dtype;
+    unsigned int* status;
+};
+
+__global__ void __launch_bounds__(512, 1) gemv_m1_q6k_rows_kernel(const GemvM1Q6RowsParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
+    uint8_t* act_s = smem + p.act_off;
+    float* part = reinterpret_cast<float*>(smem + p.part_off);  // [2 parities][8 stages][16 warps]
+    const uint32_t stage0 = smem_u32(smem + p.stage_off);
+    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
+    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
+    const uint32_t nfill = (row_end - row_begin + p.rpf - 1) / p.rpf;
+    const uint32_t nwork = p.rpf * p.nchunk;  // warps with a (row, chunk) role
+
+    auto issue_fill = [&](uint32_t f) {  // one lane
+        const uint32_t r0 = row_begin + f * p.rpf;
+        const uint32_t nrows = min(p.rpf, row_end - r0);
+        const uint32_t st = f % p.nstages;
+        fill_contiguous(stage0 + st * p.stage_bytes, smem + p.stage_off + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes,
+                        nrows * p.row_bytes, p.w + (size_t)p.N * p.row_bytes, bar_full + 8 * st);
+    };
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.nstages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 16);
+        }
+        mbar_fence_init();
+        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
+    }
+    grid_dep_launch();
+    grid_dep_wait();
+    quantize_act_q6_image(p.act, p.act_dtype, p.nblk, act_s, warp, lane);
+    __syncthreads();
+
+    const uint32_t r = (uint32_t)warp / p.nchunk, c = (uint32_t)warp % p.nchunk;  // row of the fill, K-chunk
+    const int b = lane >> 1, n = lane & 1;
+    const uint32_t gblk = c * 16 + b;
+    const bool role = (uint32_t)warp < nwork && gblk < p.nblk;
+    uint32_t a[32], bs[4];
+    float d8 = 0.f;
+    if (role) {
+        const uint8_t* blk = act_s + gblk * ACT6_STRIDE;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint4 q = *reinterpret_cast<const uint4*>(blk + 128 * n + 16 * i);
+            a[4 * i] = q.x; a[4 * i + 1] = q.y; a[4 * i + 2] = q.z; a[4 * i + 3] = q.w;
+        }
+        uint4 q = *reinterpret_cast<const uint4*>(blk + 256 + 16 * n);
+        bs[0] = q.x; bs[1] = q.y; bs[2] = q.z; bs[3] = q.w;
+        d8 = *reinterpret_cast<const float*>(blk + 288);
+    }
+
+    // stores the row totals of fill f (its chunk sums sit in the table slot (parity, stage))
+    auto flush = [&](uint32_t f, uint32_t fst, uint32_t fpar) {
+        if (warp == 0 && (uint32_t)lane < p.rpf) {
+            const uint32_t r0 = row_begin + f * p.rpf;
+            if (r0 + lane < row_end) {
+                const float* src = part + (fpar * 8 + fst) * 16 + lane * p.nchunk;
+                float tot = 0.f;
+                for (uint32_t k = 0; k < p.nchunk; ++k) tot = __fadd_rn(tot, src[k]);
+                const size_t idx = r0 + lane;
+                if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = tot;
+                else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(tot);
+                else static_cast<__half*>(p.out)[idx] = __float2half_rn(tot);
+            }
+        }
+    };
+
+    // Two fills per trip: their integer sums are independent, which gives every lane two dependency
+    // chains to interleave and halves the hand-shakes per byte.
+    bool dead = false;
+    uint32_t st = 0, par = 0;               // ring position of the first fill of the trip
+    uint32_t pf = 0, pst[2] = {0, 0}, ppar[2] = {0, 0}, pcount = 0;  // fills of the previous trip, to be flushed
+    for (uint32_t f = 0; f < nfill; f += 2) {
+        const uint32_t nf = min(2u, nfill - f);
+        uint32_t sst[2], spar[2];
+        sst[0] = st; spar[0] = par;
+        sst[1] = st + 1 == p.nstages ? 0 : st + 1;
+        spar[1] = st + 1 == p.nstages ? par ^ 1 : par;
+        int half_sum[2] = {0, 0};
+        float d6[2] = {0.f, 0.f};
+        bool on[2] = {false, false};
+#pragma unroll
+        for (uint32_t u = 0; u < 2; ++u) {
+            if (u < nf) {
+                if (!dead && !mbar_wait(bar_full + 8 * sst[u], spar[u])) {
+                    dead = true;
+                    atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                }
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 2; ++u) {
+            if (u < nf) {
+                const uint32_t r0 = row_begin + (f + u) * p.rpf;
+                const uint32_t nrows = min(p.rpf, row_end - r0);
+                const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15);
+                on[u] = !dead && role && r < nrows;
+                if (on[u])
+                    half_sum[u] = q6k_half_sum(smem + p.stage_off + sst[u] * p.stage_bytes + phase + r * p.row_bytes + gblk * 210, n, a, bs, d6[u]);
+            }
+        }
+        float term[2];
+#pragma unroll
+        for (uint32_t u = 0; u < 2; ++u) {
+            const int sumi = half_sum[u] + __shfl_xor_sync(0xFFFFFFFFu, half_sum[u], 1);
+            term[u] = on[u] ? __fmul_rn(__fmul_rn(d6[u], d8), (float)sumi) : 0.f;
+        }
+#pragma unroll
+        for (int o = 16; o > 1; o >>= 1) {
+            term[0] += __shfl_xor_sync(0xFFFFFFFFu, term[0], o);
+            term[1] += __shfl_xor_sync(0xFFFFFFFFu, term[1], o);
+        }
+        if (lane == 0) {
+            part[(spar[0] * 8 + sst[0]) * 16 + warp] = term[0];  // warp index == r * nchunk + c
+            if (nf > 1) part[(spar[1] * 8 + sst[1]) * 16 + warp] = term[1];
+        }
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(bar_empty + 8 * sst[0]);
+            if (nf > 1) mbar_arrive(bar_empty + 8 * sst[1]);
+        }
+        // the previous trip's chunk sums are complete once its stages have been released by all warps
+        if (pcount && warp == 0) {
+            for (uint32_t u = 0; u < pcount; ++u) {
+                if (!dead && !mbar_wait(bar_empty + 8 * pst[u], ppar[u])) {
+                    dead = true;
+                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                }
+                if (!dead) flush(pf + u, pst[u], ppar[u]);
+            }
+        }
+        // refill the stages just released: the warps take turns
+        if (((f >> 1) & 15) == (uint32_t)warp) {
+            for (uint32_t u = 0; u < nf; ++u) {
+                if (f + u + p.nstages < nfill) {
+                    if (!dead && !mbar_wait(bar_empty + 8 * sst[u], spar[u])) {
+                        dead = true;
+                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    }
+                    if (!dead && lane == 0) issue_fill(f + u + p.nstages);
+                }
+            }
+        }
+        pf = f; pcount = nf;
+        pst[0] = sst[0]; pst[1] = sst[1]; ppar[0] = spar[0]; ppar[1] = spar[1];
+        for (uint32_t u = 0; u < nf; ++u)
+            if (++st == p.nstages) { st = 0; par ^= 1; }
+    }
+    if (pcount && warp == 0) {
+        for (uint32_t u = 0; u < pcount; ++u) {
+            if (!dead && !mbar_wait(bar_empty + 8 * pst[u], ppar[u])) {
+                dead = true;
+                atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+            }
+            if (!dead) flush(pf + u, pst[u], ppar[u]);
+        }
+    }
+}
+
 }  // namespace
 
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu) {
     if (M != 1 || N < 1 || K % 256) return false;
     if (fmt == FMT_Q4_K) return K <= 4096;
-    // Q6_K: rows must start on 16-byte boundaries (K a multiple of 2048); the activation image must fit
-    if (fmt == FMT_Q6_K) return !swiglu && K % 2048 == 0 && K <= 16384;
+    // Q6_K: the activation image must fit beside the stages
+    if (fmt == FMT_Q6_K) return !swiglu && K <= 16384;
     return false;
+}
+
+static cudaError_t launch_gemv_m1_q6k_rows(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
+                                           size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    GemvM1Q6RowsParams p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.act = act;
+    p.out = out;
+    p.K = (uint32_t)K;
+    p.N = (uint32_t)N;
+    p.nblk = (uint32_t)(K / 256);
+    p.nchunk = (p.nblk + 15) / 16;
+    p.rpf = 16 / p.nchunk;
+    p.row_bytes = p.nblk * 210;
+    p.stage_bytes = (p.rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
+    p.act_off = 128;
+    p.part_off = (p.act_off + p.nblk * ACT6_STRIDE + 15) & ~15u;
+    p.stage_off = (p.part_off + 2 * 8 * 16 * 4 + 127) & ~127u;
+    p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;
+    if (p.nstages > 8) p.nstages = 8;
+    p.act_dtype = act_dtype;
+    p.out_dtype = out_dtype;
+    p.status = status;
+    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    size_t grid = (N + p.rpf - 1) / p.rpf;
+    if (grid > (size_t)sm_count) grid = sm_count;
+    cudaError_t le = launch_pdl(gemv_m1_q6k_rows_kernel, dim3((unsigned)grid), dim3(512), smem, st, p);
+    note_launch();
+    return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
                                       size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    if (K > 4096) return launch_gemv_m1_q6k_rows(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
     GemvM1Q6Params p{};
     p.w = static_cast<const uint8_t*>(w);
     p.act = act;
@@ -505,7 +767,7 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
     p.nblk = (uint32_t)(K / 256);
     p.nchunk = (p.nblk + 15) / 16;
     p.row_bytes = p.nblk * 210;
-    p.stage_bytes = (16 * 16 * 210 + 127) & ~127u;
+    p.stage_bytes = (16 * 16 * 210 + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
     p.act_off = 128;
     p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 8 + 127) & ~127u;  // +8: the word pair past the last block half
     p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;

@@ -429,3 +429,18 @@ def test_quant_matmul_batch_decode_fused_launch(ops, oracle):
         want = oracle.quant_matmul(f, act, w, n)
         assert o.shape == (1, n)
         assert rel_err(o.cpu().numpy(), want)[0] < 2e-6, (f, n)
+
+
+@pytest.mark.parametrize("k", [256, 1792, 3584, 4096, 4352, 7168, 14336])
+@pytest.mark.parametrize("n", [1, 37, 500])
+def test_q6k_decode_rows_of_any_alignment(ops, oracle, k, n):
+    # Q6_K rows are 210 bytes per block: K-split shards (1792, 3584, 7168) and odd block counts give rows
+    # that start on 2-, 4- or 8-byte boundaries only
+    rng = synth.rng_for(37, k + n)
+    act = synth.activations(rng, 1, k)
+    w = synth.weight_bytes("Q6_K", rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt("Q6_K", w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul("Q6_K", act, w, n)
+    e_max, _ = rel_err(got, want)
+    assert e_max <= 2e-6, f"K={k} N={n}: {e_max:.3e}\n" + describe_mismatch(got, want)
