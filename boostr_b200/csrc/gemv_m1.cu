@@ -24,6 +24,23 @@
 
 namespace b200q {
 
+#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
+// Debug build only: nanosecond stamps of thread 0 of every CTA of the last 64 launches.
+__device__ unsigned long long g_trace_m1[64 * 148 * 16];
+static unsigned g_trace_m1_next = 0;
+#define TRACE1(idx, slot)                                                                                    \
+    do {                                                                                                     \
+        if (threadIdx.x == 0 && blockIdx.x < 148) g_trace_m1[(((idx) & 63) * 148 + blockIdx.x) * 16 + (slot)] = global_timer_ns(); \
+    } while (0)
+#define TRACE1MAX(idx, slot)                                                                                 \
+    do {                                                                                                     \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) atomicMax(&g_trace_m1[(((idx) & 63) * 148 + blockIdx.x) * 16 + (slot)], global_timer_ns()); \
+    } while (0)
+#else
+#define TRACE1(idx, slot) do {} while (0)
+#define TRACE1MAX(idx, slot) do {} while (0)
+#endif
+
 struct GemvM1Params {
     // Up to three weights that share the activation row (q/k/v-style batches) form one virtual row
     // space [0, N): segment s covers rows [seg_end[s-1], seg_end[s]) and writes its own output.
@@ -36,12 +53,13 @@ struct GemvM1Params {
     uint32_t K, N;
     uint32_t nblk;       // K / 256 (<= 16)
     uint32_t row_bytes;  // nblk * 144
-    uint32_t stage_rows; // output rows per stage: 32, or 16 in the SwiGLU variant (16 gate + 16 up rows)
-    uint32_t stage_bytes;
+    uint32_t rows_per_cta;  // CTA c owns rows [c * rows_per_cta, min(N, (c + 1) * rows_per_cta)) of the virtual row space
+    uint32_t stage_bytes;   // one fill: 8 rows, or 4 gate + 4 up rows in the SwiGLU variant
     uint32_t nstages;
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
     unsigned int* status;
+    uint32_t trace_idx, dbg;
 };
 
 namespace {
@@ -64,100 +82,150 @@ __device__ __forceinline__ int ubyte(uint32_t x) { return (int)__byte_perm(x, 0u
 //   [272,276) f32 d8
 constexpr int ACT_STRIDE = 288;
 
+// Loads 8 consecutive activation values of this lane (f32 or bf16 source).
+__device__ __forceinline__ void load_act8(const void* act, int act_dtype, size_t base, float (&v)[8]) {
+    if (act_dtype == DT_F32) {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(act) + base);
+        float4 a = __ldg(src), b = __ldg(src + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(act) + base));
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+    }
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ int dp4a_s8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t f32_to_s8_rni_sat(float x) {
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(x));  // clamps to [-128, 127]; the code in the low byte
+    return (uint32_t)r;
+}
+
+// Q8_K-quantises one 256-block held 8 values per lane: returns d8, the lane's 8 codes packed in `packed`
+// and their sum in `s` (quantize_act_q8k.rs:26-98: d = amax / 127, id = 127 / amax, round half to even).
+// This sits on every decode kernel's critical path, so the chain is kept short: one warp-wide integer
+// max on the bit patterns (non-negative floats order like unsigned integers), saturating converts,
+// byte permutes for the packing and dp4a for the sum.
+__device__ __forceinline__ float quantize_block8(const float (&v)[8], uint2& packed, int& s) {
+    const float m = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                          fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+    const float amax = __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(m)));
+    const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+    uint32_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = f32_to_s8_rni_sat(__fmul_rn(v[i], id));
+    packed.x = prmt(prmt(c[0], c[1], 0x0040u), prmt(c[2], c[3], 0x0040u), 0x5410u);
+    packed.y = prmt(prmt(c[4], c[5], 0x0040u), prmt(c[6], c[7], 0x0040u), 0x5410u);
+    s = dp4a_s8s8(packed.x, 0x01010101u, dp4a_s8s8(packed.y, 0x01010101u, 0));
+    return __fdiv_rn(amax, 127.0f);
+}
+
 // SWIGLU: two weights; a warp takes gate row r (lanes 0-15) and up row r (lanes 16-31) and stores
 // silu(gate . x) * (up . x)  (quant_swiglu, src/quant/traits/quant_matmul.rs:122-127).
+//
+// The 16 warps form 4 groups; a fill is the 8 rows (SwiGLU: 4 gate + 4 up rows) that ONE group consumes,
+// and group g takes fills g, g+4, g+8, ... of the CTA's row range.  Small fills let the arithmetic start
+// as soon as the first 18 KB have landed, while the ring still keeps ~220 KB per SM in flight.
 template <bool SWIGLU>
 __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params p) {
+    constexpr uint32_t FR = SWIGLU ? 4 : 8;  // output rows per fill
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     uint8_t* act_s = smem + p.act_off;
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
+    TRACE1(p.trace_idx, 0);
 
-    // rows of this CTA: an even split of N over the grid
-    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
-    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t nfill = (row_end - row_begin + p.stage_rows - 1) / p.stage_rows;
+    const uint32_t row_begin = blockIdx.x * p.rows_per_cta;
+    const uint32_t row_end = min(p.N, row_begin + p.rows_per_cta);
+    const uint32_t nfill = row_end > row_begin ? (row_end - row_begin + FR - 1) / FR : 0;
 
-    auto issue_fill = [&](uint32_t f) {  // one lane
-        const uint32_t r0 = row_begin + f * p.stage_rows;
-        const uint32_t nrows = min(p.stage_rows, row_end - r0);
-        const uint32_t st = f % p.nstages;
+    auto issue_fill = [&](uint32_t f, uint32_t slot) {  // one lane
+        const uint32_t r0 = row_begin + f * FR;
+        const uint32_t nrows = min(FR, row_end - r0);
         const uint32_t bytes = nrows * p.row_bytes;
+        const uint32_t dst = stage0 + slot * p.stage_bytes, bar = bar_full + 8 * slot;
         if (SWIGLU) {
-            mbar_expect_tx(bar_full + 8 * st, 2 * bytes);
-            bulk_g2s(stage0 + st * p.stage_bytes, p.w[0] + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
-            bulk_g2s(stage0 + st * p.stage_bytes + 16 * p.row_bytes, p.w2 + (size_t)r0 * p.row_bytes, bytes, bar_full + 8 * st);
+            mbar_expect_tx(bar, 2 * bytes);
+            bulk_g2s(dst, p.w[0] + (size_t)r0 * p.row_bytes, bytes, bar);
+            bulk_g2s(dst + FR * p.row_bytes, p.w2 + (size_t)r0 * p.row_bytes, bytes, bar);
+        } else if (p.nseg == 1) {
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(dst, p.w[0] + (size_t)r0 * p.row_bytes, bytes, bar);
         } else {
-            mbar_expect_tx(bar_full + 8 * st, bytes);
+            mbar_expect_tx(bar, bytes);
             uint32_t seg_begin = 0;
             for (uint32_t sg = 0; sg < p.nseg; ++sg) {  // the part of [r0, r0 + nrows) inside each segment
                 const uint32_t lo = max(r0, seg_begin), hi = min(r0 + nrows, p.seg_end[sg]);
                 if (lo < hi)
-                    bulk_g2s(stage0 + st * p.stage_bytes + (lo - r0) * p.row_bytes,
-                             p.w[sg] + (size_t)(lo - seg_begin) * p.row_bytes, (hi - lo) * p.row_bytes, bar_full + 8 * st);
+                    bulk_g2s(dst + (lo - r0) * p.row_bytes, p.w[sg] + (size_t)(lo - seg_begin) * p.row_bytes,
+                             (hi - lo) * p.row_bytes, bar);
                 seg_begin = p.seg_end[sg];
             }
         }
     };
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 16);
-        }
+
+    // Responses come back to an SM in request order, so an activation load issued behind a full ring
+    // of weight fills would wait for all of them (several microseconds).  Hence: one fill per warp group
+    // leaves before the grid dependency is resolved (the weights do not depend on the previous kernel),
+    // then the activation loads, and only then the rest of the ring.
+    if (warp == 15 && (uint32_t)lane < p.nstages) {
+        mbar_init(bar_full + 8 * lane, 1);
+        mbar_init(bar_empty + 8 * lane, 4);
         mbar_fence_init();
-        // start the weight stream at once: the first fills need no hand-shake, and the copies
-        // overlap the activation quantisation below
-        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
     }
+    __syncthreads();
+    if (warp == 15 && lane < 2 && (uint32_t)lane < nfill) issue_fill(lane, lane);
+    TRACE1MAX(p.trace_idx, 1);
     grid_dep_launch();  // the next kernel may start its own weight prefetch as SMs free up
     grid_dep_wait();    // the previous kernel's output (our activations) is complete from here on
+    TRACE1(p.trace_idx, 2);
 
-    // 1. quantise the activation row: warp w owns block w (8 values per lane); warp 0, whose
-    // first lane is busy issuing copies, takes its block last
-    if ((uint32_t)warp < p.nblk) {
+    // 1. quantise the activation row: warp w owns block w; each warp issues its load first and then
+    // its share of the remaining first fills
+    {
         float v[8];
-        const size_t base = (size_t)warp * 256 + 8 * lane;
-        if (p.act_dtype == DT_F32) {
-            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.act) + base);
-            float4 a = __ldg(src), b = __ldg(src + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        } else {
-            uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.act) + base));
-            v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xFFFF0000u);
-            v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xFFFF0000u);
-            v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xFFFF0000u);
-            v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xFFFF0000u);
+#ifdef B200Q_TRACE
+        const bool on = (uint32_t)warp < p.nblk && !(p.dbg & 2);
+#else
+        const bool on = (uint32_t)warp < p.nblk;
+#endif
+        if (on) load_act8(p.act, p.act_dtype, (size_t)warp * 256 + 8 * lane, v);
+        const uint32_t f1 = 2 + (uint32_t)warp;  // the rest of the ring: one fill per warp
+        if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+        TRACE1(p.trace_idx, 7);
+        if (on) {  // warp-uniform
+            uint2 packed;
+            int s;
+            const float d8 = quantize_block8(v, packed, s);
+            uint8_t* blk = act_s + warp * ACT_STRIDE;
+            *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+            // sum over the 4 lanes of a 32-element sub-block
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+            if ((lane & 3) == 0) {
+                const int bs = s + 4096;
+                blk[256 + (lane >> 2)] = (uint8_t)(bs & 127);
+                blk[264 + (lane >> 2)] = (uint8_t)(bs >> 7);
+            }
+            if (lane == 0) *reinterpret_cast<float*>(blk + 272) = d8;
         }
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        const float d8 = __fdiv_rn(amax, 127.0f);
-        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
-        int c[8], s = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id))));
-            s += c[i];
-        }
-        uint8_t* blk = act_s + warp * ACT_STRIDE;
-        uint2 packed;
-        packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
-        packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
-        *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
-        // sum over the 4 lanes of a 32-element sub-block
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-        if ((lane & 3) == 0) {
-            const int bs = s + 4096;
-            blk[256 + (lane >> 2)] = (uint8_t)(bs & 127);
-            blk[264 + (lane >> 2)] = (uint8_t)(bs >> 7);
-        }
-        if (lane == 0) *reinterpret_cast<float*>(blk + 272) = d8;
+        TRACE1(p.trace_idx, 8);
     }
     __syncthreads();  // barriers initialised, activation image complete
+    TRACE1(p.trace_idx, 3);
 
     // 2. this lane's activation block goes to registers
     const int b = lane & 15, h = lane >> 4;
@@ -177,19 +245,27 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
         d8 = blk_on ? *reinterpret_cast<const float*>(blk + 272) : 0.f;
     }
 
+    TRACE1(p.trace_idx, 10);
+    const uint32_t grp = (uint32_t)warp >> 2, wi = (uint32_t)warp & 3;
+    const uint32_t rr = SWIGLU ? wi : 2 * wi + h;  // output row of the fill handled by this half-warp
     bool dead = false;
-    uint32_t st = 0, par = 0;
-    for (uint32_t f = 0; f < nfill; ++f) {
-        if (!dead && !mbar_wait(bar_full + 8 * st, par)) {
+    uint32_t slot = grp, par = 0;  // fill f lives in ring slot f % nstages (nstages >= 4)
+    for (uint32_t f = grp; f < nfill; f += 4) {
+        if (!dead && !mbar_wait(bar_full + 8 * slot, par)) {
             dead = true;
             atomicOr(p.status, STATUS_TIMEOUT_FULL);
         }
-        const uint32_t r0 = row_begin + f * p.stage_rows;
-        const uint32_t nrows = min(p.stage_rows, row_end - r0);
-        const uint32_t rr = SWIGLU ? warp : 2 * warp + h;  // output row of the stage handled by this half-warp
+        if (f == 0) TRACE1(p.trace_idx, 4);
+        if (f + 1 == nfill) TRACE1MAX(p.trace_idx, 5);
+        const uint32_t r0 = row_begin + f * FR;
+        const uint32_t nrows = min(FR, row_end - r0);
         float term = 0.f;
+#ifdef B200Q_TRACE
+        if (!dead && rr < nrows && blk_on && !(p.dbg & 4)) {
+#else
         if (!dead && rr < nrows && blk_on) {
-            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + (SWIGLU ? 16 * h + warp : rr) * p.row_bytes + b * 144;
+#endif
+            const uint8_t* blk = smem + p.stage_off + slot * p.stage_bytes + (SWIGLU ? FR * h + wi : rr) * p.row_bytes + b * 144;
             const uint4 hd = *reinterpret_cast<const uint4*>(blk);
             // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
             uint32_t sc[2], mn[2];
@@ -225,7 +301,8 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
             term = __fsub_rn(__fmul_rn(__fmul_rn(d, d8), (float)sumi), __fmul_rn(__fmul_rn(dmin, d8), (float)summ));
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
+        if (f == 0) TRACE1(p.trace_idx, 11);
+        if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
         // add the block terms of a row (16 lanes)
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
@@ -242,19 +319,21 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
             else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(o)[idx] = __float2bfloat16_rn(term);
             else static_cast<__half*>(o)[idx] = __float2half_rn(term);
         }
-        // refill the stage just released: the warps take turns, so nobody is "the producer"
-        if (f + p.nstages < nfill && (f & 15) == (uint32_t)warp) {
-            if (!dead && !mbar_wait(bar_empty + 8 * st, par)) {
+        // refill the slot just released: the four warps of the group take turns
+        if (f + p.nstages < nfill && ((f >> 2) & 3) == wi) {
+            if (!dead && !mbar_wait(bar_empty + 8 * slot, par)) {
                 dead = true;
                 atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
             }
-            if (!dead && lane == 0) issue_fill(f + p.nstages);
+            if (!dead && lane == 0) issue_fill(f + p.nstages, slot);
         }
-        if (++st == p.nstages) {
-            st = 0;
+        slot += 4;
+        if (slot >= p.nstages) {
+            slot -= p.nstages;
             par ^= 1;
         }
     }
+    TRACE1MAX(p.trace_idx, 6);
 }
 
 
@@ -323,42 +402,16 @@ __device__ __forceinline__ void quantize_act_q6_image(const void* act, int act_d
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint32_t blk_i = warp + 16 * j;
-        if (blk_i < nblk) {
-            const size_t base = (size_t)blk_i * 256 + 8 * lane;
-            if (act_dtype == DT_F32) {
-                const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(act) + base);
-                float4 a = __ldg(src), b = __ldg(src + 1);
-                v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w; v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
-            } else {
-                uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(act) + base));
-                v[j][0] = __uint_as_float(r.x << 16); v[j][1] = __uint_as_float(r.x & 0xFFFF0000u);
-                v[j][2] = __uint_as_float(r.y << 16); v[j][3] = __uint_as_float(r.y & 0xFFFF0000u);
-                v[j][4] = __uint_as_float(r.z << 16); v[j][5] = __uint_as_float(r.z & 0xFFFF0000u);
-                v[j][6] = __uint_as_float(r.w << 16); v[j][7] = __uint_as_float(r.w & 0xFFFF0000u);
-            }
-        }
+        if (blk_i < nblk) load_act8(act, act_dtype, (size_t)blk_i * 256 + 8 * lane, v[j]);
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const uint32_t blk_i = warp + 16 * j;
         if (blk_i < nblk) {  // warp-uniform
-            float amax = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-            const float d8 = __fdiv_rn(amax, 127.0f);
-            const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
-            int c[8], s = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[j][i], id))));
-                s += c[i];
-            }
-            uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
             uint2 packed;
-            packed.x = (uint32_t)(c[0] & 0xFF) | ((uint32_t)(c[1] & 0xFF) << 8) | ((uint32_t)(c[2] & 0xFF) << 16) | ((uint32_t)(c[3] & 0xFF) << 24);
-            packed.y = (uint32_t)(c[4] & 0xFF) | ((uint32_t)(c[5] & 0xFF) << 8) | ((uint32_t)(c[6] & 0xFF) << 16) | ((uint32_t)(c[7] & 0xFF) << 24);
+            int s;
+            const float d8 = quantize_block8(v[j], packed, s);
+            uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
             *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
             s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
             if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
@@ -824,11 +877,22 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
     p.row_bytes = p.nblk * 144;
-    p.stage_rows = swiglu ? 16 : 32;
-    p.stage_bytes = 32 * p.row_bytes;  // multiple of 128
-    p.act_off = 128;
+#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
+    p.trace_idx = g_trace_m1_next++;
+#endif
+#ifdef B200Q_TRACE
+    { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
+#endif
+    p.stage_bytes = 8 * p.row_bytes;  // multiple of 128
+    p.act_off = 256;
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
-    p.nstages = 3;
+    p.nstages = (232448 - 1024 - p.stage_off) / p.stage_bytes;
+    if (p.nstages > 16) p.nstages = 16;
+    // one CTA per SM, but never fewer than ~16 rows per CTA
+    size_t grid = (N + 15) / 16;
+    if (grid > (size_t)sm_count) grid = sm_count;
+    p.rows_per_cta = (uint32_t)((N + grid - 1) / grid);
+    grid = (N + p.rows_per_cta - 1) / p.rows_per_cta;
     p.act_dtype = act_dtype;
     p.out_dtype = out_dtype;
     p.status = status;
@@ -838,18 +902,20 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    // one CTA per SM, but never fewer than ~16 rows per CTA
-    size_t grid = (N + 15) / 16;
-    if (grid > (size_t)sm_count) grid = sm_count;
     cudaError_t le = swiglu ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
                             : launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
 }
+
+#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
+extern "C" __attribute__((visibility("default"))) int b200q_debug_trace_m1(void* host, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(host, g_trace_m1, bytes < sizeof(g_trace_m1) ? bytes : sizeof(g_trace_m1));
+}
+#endif
 
 }  // namespace b200q
