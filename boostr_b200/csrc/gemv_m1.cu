@@ -339,13 +339,15 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
 
 // ------------------------------------------------------------------------------------ Q6_K, M = 1
 //
-// Same streaming structure; the differences follow from the format:
+// Same streaming structure as the Q4_K kernel (ring of small fills, one warp group per fill, activation
+// loads ahead of the ring); the differences follow from the format:
 //   * a 210-byte block is only 2-byte aligned inside its row, so a lane reads aligned 32-bit words and
 //     re-assembles each needed word with one prmt whose selector depends on the block's parity;
 //   * a block splits into two independent 128-element halves (64 B of low nibbles, 32 B of high bit
-//     pairs, 8 signed scales each): one warp takes ONE row, lane (b, n) half n of block b;
-//   * 16 rows x 16 blocks (52.5 KB) per stage, 4 stages; K longer than 16 blocks is walked in chunks of
-//     16 blocks through the same ring, the row total carried in a register;
+//     pairs, 8 signed scales each): lane (b, n) takes half n of block b of a 16-block chunk of K;
+//   * NCHUNK = 1, 2 or 4 warps share a row (K up to 4096 * NCHUNK), so a fill of a 4-warp group is
+//     4 / NCHUNK whole rows, which are contiguous in memory: one bulk copy per fill, rows of any
+//     alignment; chunk sums of a row meet in a small table and the warp that refills the slot adds them;
 //   * the 6-bit value is never assembled: nibbles and bit pairs are multiplied separately (dp4a) in
 //     place and the place values (x16, x4, x16, x64) are shifted out of the integer sums;
 //     sum (q-32)*a uses the activation's 16-wide block sums.  All integer arithmetic is exact, the block
@@ -355,10 +357,10 @@ struct GemvM1Q6Params {
     const void* act;
     void* out;
     uint32_t K, N;
-    uint32_t nblk;        // K / 256 (<= 16 for this kernel)
-    uint32_t nchunk;      // ceil(nblk / 16)
-    uint32_t row_bytes;   // nblk * 210
-    uint32_t stage_bytes; // 16 rows x 16 blocks x 210 B, rounded up to 128
+    uint32_t nblk;          // K / 256 (<= 64)
+    uint32_t row_bytes;     // nblk * 210
+    uint32_t rows_per_cta;  // CTA c owns rows [c * rows_per_cta, min(N, (c + 1) * rows_per_cta))
+    uint32_t stage_bytes;   // 4 / NCHUNK rows + room for the phase of an unaligned first row
     uint32_t nstages;
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
@@ -391,33 +393,6 @@ __device__ __forceinline__ void fill_contiguous(uint32_t dst_s, uint8_t* dst_g, 
     const uint32_t n = (uint32_t)(e16 - gs);
     mbar_expect_tx(bar, n);  // release: the plain stores above are visible to whoever sees the phase complete
     if (n) bulk_g2s(dst_s, gs, n, bar);
-}
-
-// Quantises the activation row to Q8_K into the shared-memory image used by the Q6_K kernels:
-// warp w takes blocks w, w+16, ... (8 values per lane).
-__device__ __forceinline__ void quantize_act_q6_image(const void* act, int act_dtype, uint32_t nblk, uint8_t* act_s, int warp, int lane) {
-    // warp w takes blocks w, w+16, w+32, w+48 (8 values per lane); all loads are issued before any
-    // arithmetic so the kernel pays one round trip to L2, not one per block
-    float v[4][8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t blk_i = warp + 16 * j;
-        if (blk_i < nblk) load_act8(act, act_dtype, (size_t)blk_i * 256 + 8 * lane, v[j]);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t blk_i = warp + 16 * j;
-        if (blk_i < nblk) {  // warp-uniform
-            uint2 packed;
-            int s;
-            const float d8 = quantize_block8(v[j], packed, s);
-            uint8_t* blk = act_s + blk_i * ACT6_STRIDE;
-            *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
-            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
-            if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
-            if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
-        }
-    }
 }
 
 // Integer sum over half `n` (128 elements) of the Q6_K block at `blk` (2-byte aligned in shared memory)
@@ -465,180 +440,72 @@ __device__ __forceinline__ int q6k_half_sum(const uint8_t* blk, int n, const uin
     return half_sum;
 }
 
-template <bool ACT_REGS>
+template <int NCHUNK>
 __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Params p) {
+    constexpr uint32_t RPF = 4 / NCHUNK;  // rows per fill
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
+    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
+    float* part = reinterpret_cast<float*>(smem + 256);  // [16 slots][4 warps of the group]
     uint8_t* act_s = smem + p.act_off;
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
 
-    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
-    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t nslab = (row_end - row_begin + 15) / 16;
-    const uint32_t nfill = nslab * p.nchunk;
+    const uint32_t row_begin = blockIdx.x * p.rows_per_cta;
+    const uint32_t row_end = min(p.N, row_begin + p.rows_per_cta);
+    const uint32_t nfill = row_end > row_begin ? (row_end - row_begin + RPF - 1) / RPF : 0;
 
-    // fill f = (slab f / nchunk, chunk f % nchunk); the whole warp calls this
-    auto issue_fill = [&](uint32_t f) {
-        const uint32_t slab = f / p.nchunk, c = f - slab * p.nchunk;
-        const uint32_t r0 = row_begin + slab * 16;
-        const uint32_t nrows = min(16u, row_end - r0);
-        const uint32_t st = f % p.nstages;
-        const uint32_t cblk = min(16u, p.nblk - c * 16);
-        const uint32_t cbytes = cblk * 210;
-        const uint32_t dst = stage0 + st * p.stage_bytes, bar = bar_full + 8 * st;
-        if (p.nchunk == 1) {
-            // rows are contiguous: one copy of the enclosing 16-byte-aligned range (rows of a K-split
-            // shard need not start on 16-byte boundaries)
-            if (lane == 0)
-                fill_contiguous(dst, smem + p.stage_off + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes, nrows * cbytes,
-                                p.w + (size_t)p.N * p.row_bytes, bar);
-        } else {
-            if (lane == 0) mbar_expect_tx(bar, nrows * cbytes);
-            __syncwarp();
-            if ((uint32_t)lane < nrows)
-                bulk_g2s(dst + lane * (16 * 210), p.w + (size_t)(r0 + lane) * p.row_bytes + (size_t)c * (16 * 210), cbytes, bar);
-        }
+    auto issue_fill = [&](uint32_t f, uint32_t slot) {  // one lane
+        const uint32_t r0 = row_begin + f * RPF;
+        const uint32_t nrows = min(RPF, row_end - r0);
+        fill_contiguous(stage0 + slot * p.stage_bytes, smem + p.stage_off + slot * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes,
+                        nrows * p.row_bytes, p.w + (size_t)p.N * p.row_bytes, bar_full + 8 * slot);
     };
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 16);
-        }
+
+    // two fills leave before the grid dependency is resolved, the rest of the ring after the
+    // activation loads (responses return in request order)
+    if (warp == 15 && (uint32_t)lane < p.nstages) {
+        mbar_init(bar_full + 8 * lane, 1);
+        mbar_init(bar_empty + 8 * lane, 4);
         mbar_fence_init();
     }
-    __syncwarp();
-    if (warp == 0)
-        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
+    __syncthreads();
+    if (warp == 15 && lane < 2 && (uint32_t)lane < nfill) issue_fill(lane, lane);
     grid_dep_launch();
     grid_dep_wait();
 
-    quantize_act_q6_image(p.act, p.act_dtype, p.nblk, act_s, warp, lane);
+    // 1. quantise the activation row: warp w takes blocks w, w + 16, ... (8 values per lane)
+    {
+        float v[NCHUNK][8];
+#pragma unroll
+        for (int j = 0; j < NCHUNK; ++j) {
+            const uint32_t qb = warp + 16 * j;
+            if (qb < p.nblk) load_act8(p.act, p.act_dtype, (size_t)qb * 256 + 8 * lane, v[j]);
+        }
+        const uint32_t f1 = 2 + (uint32_t)warp;
+        if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+#pragma unroll
+        for (int j = 0; j < NCHUNK; ++j) {
+            const uint32_t qb = warp + 16 * j;
+            if (qb < p.nblk) {  // warp-uniform
+                uint2 packed;
+                int s;
+                const float d8 = quantize_block8(v[j], packed, s);
+                uint8_t* blk = act_s + qb * ACT6_STRIDE;
+                *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
+                if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
+                if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
+            }
+        }
+    }
     __syncthreads();
 
-    const int b = lane >> 1, n = lane & 1;  // block within the chunk, half of the block
-
-    uint32_t a[32];   // int8 codes of this lane's half block (ACT_REGS: loaded once)
-    uint32_t bs[4];   // its eight 16-wide sums as int16 pairs
-    float d8 = 0.f;
-    auto load_act = [&](uint32_t gblk) {
-        const uint8_t* blk = act_s + gblk * ACT6_STRIDE;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            uint4 q = *reinterpret_cast<const uint4*>(blk + 128 * n + 16 * i);
-            a[4 * i] = q.x; a[4 * i + 1] = q.y; a[4 * i + 2] = q.z; a[4 * i + 3] = q.w;
-        }
-        uint4 q = *reinterpret_cast<const uint4*>(blk + 256 + 16 * n);
-        bs[0] = q.x; bs[1] = q.y; bs[2] = q.z; bs[3] = q.w;
-        d8 = *reinterpret_cast<const float*>(blk + 288);
-    };
-    if (ACT_REGS && (uint32_t)b < p.nblk) load_act(b);
-
-    bool dead = false;
-    uint32_t st = 0, par = 0, c = 0, slab = 0;
-    float row_total = 0.f;
-    for (uint32_t f = 0; f < nfill; ++f) {
-        if (!dead && !mbar_wait(bar_full + 8 * st, par)) {
-            dead = true;
-            atomicOr(p.status, STATUS_TIMEOUT_FULL);
-        }
-        const uint32_t r0 = row_begin + slab * 16;
-        const uint32_t nrows = min(16u, row_end - r0);
-        const uint32_t cblk = min(16u, p.nblk - c * 16);
-        int half_sum = 0;
-        float d6 = 0.f;
-        const bool on = !dead && (uint32_t)warp < nrows && (uint32_t)b < cblk;
-        if (on) {
-            if (!ACT_REGS) load_act(c * 16 + b);
-            const uint32_t rstride = p.nchunk == 1 ? cblk * 210 : 16 * 210;
-            const uint32_t phase = p.nchunk == 1 ? (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15) : 0u;
-            const uint8_t* blk = smem + p.stage_off + st * p.stage_bytes + phase + warp * rstride + b * 210;
-            half_sum = q6k_half_sum(blk, n, a, bs, d6);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * st);
-        const int sumi = half_sum + __shfl_xor_sync(0xFFFFFFFFu, half_sum, 1);  // the block's integer sum
-        float term = on ? __fmul_rn(__fmul_rn(d6, d8), (float)sumi) : 0.f;
-#pragma unroll
-        for (int o = 16; o > 1; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);  // over the 16 blocks
-        row_total += term;
-        if (c + 1 == p.nchunk) {
-            if (lane == 0 && (uint32_t)warp < nrows && !dead) {
-                const size_t idx = r0 + warp;
-                if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = row_total;
-                else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(row_total);
-                else static_cast<__half*>(p.out)[idx] = __float2half_rn(row_total);
-            }
-            row_total = 0.f;
-        }
-        // refill the stage just released: the warps take turns
-        if (f + p.nstages < nfill && (f & 15) == (uint32_t)warp) {
-            if (!dead && !mbar_wait(bar_empty + 8 * st, par)) {
-                dead = true;
-                atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-            }
-            if (!dead) issue_fill(f + p.nstages);
-        }
-        if (++st == p.nstages) { st = 0; par ^= 1; }
-        if (++c == p.nchunk) { c = 0; ++slab; }
-    }
-}
-
-
-// Q6_K, M = 1, K longer than 16 blocks.  A stage holds `rpf` WHOLE rows (contiguous in memory, so one
-// bulk copy per fill); warp (r, c) takes chunk c (16 blocks) of row r with its activation half-blocks in
-// registers, and leaves its chunk sum in a small parity-double-buffered table.  The row totals of a fill
-// are added up (chunks in K order) and stored one fill later, when every warp has long delivered, so
-// nobody waits for the slowest warp.
-struct GemvM1Q6RowsParams {
-    const uint8_t* w;
-    const void* act;
-    void* out;
-    uint32_t K, N;
-    uint32_t nblk, nchunk;  // blocks per row, ceil(nblk / 16) in 2..4
-    uint32_t rpf;           // rows per fill = 16 / nchunk
-    uint32_t row_bytes, stage_bytes, nstages;
-    uint32_t act_off, part_off, stage_off;
-    int act_dtype, out_dtype;
-    unsigned int* status;
-};
-
-__global__ void __launch_bounds__(512, 1) gemv_m1_q6k_rows_kernel(const GemvM1Q6RowsParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 64;
-    uint8_t* act_s = smem + p.act_off;
-    float* part = reinterpret_cast<float*>(smem + p.part_off);  // [2 parities][8 stages][16 warps]
-    const uint32_t stage0 = smem_u32(smem + p.stage_off);
-    const uint32_t row_begin = (uint32_t)(((uint64_t)p.N * blockIdx.x) / gridDim.x);
-    const uint32_t row_end = (uint32_t)(((uint64_t)p.N * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t nfill = (row_end - row_begin + p.rpf - 1) / p.rpf;
-    const uint32_t nwork = p.rpf * p.nchunk;  // warps with a (row, chunk) role
-
-    auto issue_fill = [&](uint32_t f) {  // one lane
-        const uint32_t r0 = row_begin + f * p.rpf;
-        const uint32_t nrows = min(p.rpf, row_end - r0);
-        const uint32_t st = f % p.nstages;
-        fill_contiguous(stage0 + st * p.stage_bytes, smem + p.stage_off + st * p.stage_bytes, p.w + (size_t)r0 * p.row_bytes,
-                        nrows * p.row_bytes, p.w + (size_t)p.N * p.row_bytes, bar_full + 8 * st);
-    };
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 16);
-        }
-        mbar_fence_init();
-        for (uint32_t f = 0; f < p.nstages && f < nfill; ++f) issue_fill(f);
-    }
-    grid_dep_launch();
-    grid_dep_wait();
-    quantize_act_q6_image(p.act, p.act_dtype, p.nblk, act_s, warp, lane);
-    __syncthreads();
-
-    const uint32_t r = (uint32_t)warp / p.nchunk, c = (uint32_t)warp % p.nchunk;  // row of the fill, K-chunk
+    // 2. this lane's activation half-block goes to registers
+    const uint32_t grp = (uint32_t)warp >> 2, wi = (uint32_t)warp & 3;
+    const uint32_t r = wi / NCHUNK, c = wi % NCHUNK;  // row of the fill, K-chunk
     const int b = lane >> 1, n = lane & 1;
     const uint32_t gblk = c * 16 + b;
-    const bool role = (uint32_t)warp < nwork && gblk < p.nblk;
+    const bool role = gblk < p.nblk;
     uint32_t a[32], bs[4];
     float d8 = 0.f;
     if (role) {
@@ -653,110 +520,58 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_rows_kernel(const GemvM1Q6
         d8 = *reinterpret_cast<const float*>(blk + 288);
     }
 
-    // stores the row totals of fill f (its chunk sums sit in the table slot (parity, stage))
-    auto flush = [&](uint32_t f, uint32_t fst, uint32_t fpar) {
-        if (warp == 0 && (uint32_t)lane < p.rpf) {
-            const uint32_t r0 = row_begin + f * p.rpf;
-            if (r0 + lane < row_end) {
-                const float* src = part + (fpar * 8 + fst) * 16 + lane * p.nchunk;
-                float tot = 0.f;
-                for (uint32_t k = 0; k < p.nchunk; ++k) tot = __fadd_rn(tot, src[k]);
-                const size_t idx = r0 + lane;
-                if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = tot;
-                else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(tot);
-                else static_cast<__half*>(p.out)[idx] = __float2half_rn(tot);
-            }
-        }
+    auto store_row = [&](uint32_t row, float val) {
+        if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[row] = val;
+        else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[row] = __float2bfloat16_rn(val);
+        else static_cast<__half*>(p.out)[row] = __float2half_rn(val);
     };
 
-    // Two fills per trip: their integer sums are independent, which gives every lane two dependency
-    // chains to interleave and halves the hand-shakes per byte.
     bool dead = false;
-    uint32_t st = 0, par = 0;               // ring position of the first fill of the trip
-    uint32_t pf = 0, pst[2] = {0, 0}, ppar[2] = {0, 0}, pcount = 0;  // fills of the previous trip, to be flushed
-    for (uint32_t f = 0; f < nfill; f += 2) {
-        const uint32_t nf = min(2u, nfill - f);
-        uint32_t sst[2], spar[2];
-        sst[0] = st; spar[0] = par;
-        sst[1] = st + 1 == p.nstages ? 0 : st + 1;
-        spar[1] = st + 1 == p.nstages ? par ^ 1 : par;
-        int half_sum[2] = {0, 0};
-        float d6[2] = {0.f, 0.f};
-        bool on[2] = {false, false};
-#pragma unroll
-        for (uint32_t u = 0; u < 2; ++u) {
-            if (u < nf) {
-                if (!dead && !mbar_wait(bar_full + 8 * sst[u], spar[u])) {
-                    dead = true;
-                    atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                }
-            }
+    uint32_t slot = grp, par = 0;  // fill f lives in ring slot f % nstages (nstages >= 4)
+    for (uint32_t f = grp; f < nfill; f += 4) {
+        if (!dead && !mbar_wait(bar_full + 8 * slot, par)) {
+            dead = true;
+            atomicOr(p.status, STATUS_TIMEOUT_FULL);
         }
+        const uint32_t r0 = row_begin + f * RPF;
+        const uint32_t nrows = min(RPF, row_end - r0);
+        const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15);
+        const bool on = !dead && role && r < nrows;
+        int half_sum = 0;
+        float d6 = 0.f;
+        if (on) half_sum = q6k_half_sum(smem + p.stage_off + slot * p.stage_bytes + phase + r * p.row_bytes + gblk * 210, n, a, bs, d6);
+        const int sumi = half_sum + __shfl_xor_sync(0xFFFFFFFFu, half_sum, 1);
+        float term = on ? __fmul_rn(__fmul_rn(d6, d8), (float)sumi) : 0.f;
 #pragma unroll
-        for (uint32_t u = 0; u < 2; ++u) {
-            if (u < nf) {
-                const uint32_t r0 = row_begin + (f + u) * p.rpf;
-                const uint32_t nrows = min(p.rpf, row_end - r0);
-                const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15);
-                on[u] = !dead && role && r < nrows;
-                if (on[u])
-                    half_sum[u] = q6k_half_sum(smem + p.stage_off + sst[u] * p.stage_bytes + phase + r * p.row_bytes + gblk * 210, n, a, bs, d6[u]);
-            }
-        }
-        float term[2];
-#pragma unroll
-        for (uint32_t u = 0; u < 2; ++u) {
-            const int sumi = half_sum[u] + __shfl_xor_sync(0xFFFFFFFFu, half_sum[u], 1);
-            term[u] = on[u] ? __fmul_rn(__fmul_rn(d6[u], d8), (float)sumi) : 0.f;
-        }
-#pragma unroll
-        for (int o = 16; o > 1; o >>= 1) {
-            term[0] += __shfl_xor_sync(0xFFFFFFFFu, term[0], o);
-            term[1] += __shfl_xor_sync(0xFFFFFFFFu, term[1], o);
-        }
-        if (lane == 0) {
-            part[(spar[0] * 8 + sst[0]) * 16 + warp] = term[0];  // warp index == r * nchunk + c
-            if (nf > 1) part[(spar[1] * 8 + sst[1]) * 16 + warp] = term[1];
+        for (int o = 16; o > 1; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
+        if (NCHUNK == 1) {
+            if (lane == 0 && on) store_row(r0 + r, term);
+        } else {
+            if (lane == 0) part[slot * 4 + wi] = term;
         }
         __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(bar_empty + 8 * sst[0]);
-            if (nf > 1) mbar_arrive(bar_empty + 8 * sst[1]);
-        }
-        // the previous trip's chunk sums are complete once its stages have been released by all warps
-        if (pcount && warp == 0) {
-            for (uint32_t u = 0; u < pcount; ++u) {
-                if (!dead && !mbar_wait(bar_empty + 8 * pst[u], ppar[u])) {
-                    dead = true;
-                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                }
-                if (!dead) flush(pf + u, pst[u], ppar[u]);
-            }
-        }
-        // refill the stages just released: the warps take turns
-        if (((f >> 1) & 15) == (uint32_t)warp) {
-            for (uint32_t u = 0; u < nf; ++u) {
-                if (f + u + p.nstages < nfill) {
-                    if (!dead && !mbar_wait(bar_empty + 8 * sst[u], spar[u])) {
-                        dead = true;
-                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    }
-                    if (!dead && lane == 0) issue_fill(f + u + p.nstages);
-                }
-            }
-        }
-        pf = f; pcount = nf;
-        pst[0] = sst[0]; pst[1] = sst[1]; ppar[0] = spar[0]; ppar[1] = spar[1];
-        for (uint32_t u = 0; u < nf; ++u)
-            if (++st == p.nstages) { st = 0; par ^= 1; }
-    }
-    if (pcount && warp == 0) {
-        for (uint32_t u = 0; u < pcount; ++u) {
-            if (!dead && !mbar_wait(bar_empty + 8 * pst[u], ppar[u])) {
+        if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
+        // one warp of the group (they take turns) waits for its siblings, adds the chunk sums of the
+        // fill's rows and refills the slot
+        const bool refill = f + p.nstages < nfill;
+        if (((f >> 2) & 3) == wi && (NCHUNK > 1 || refill)) {
+            if (!dead && !mbar_wait(bar_empty + 8 * slot, par)) {
                 dead = true;
                 atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
             }
-            if (!dead) flush(pf + u, pst[u], ppar[u]);
+            if (NCHUNK > 1 && !dead && (uint32_t)lane < nrows) {
+                float tot = 0.f;
+#pragma unroll
+                for (int k = 0; k < NCHUNK; ++k) tot = __fadd_rn(tot, part[slot * 4 + lane * NCHUNK + k]);
+                store_row(r0 + lane, tot);
+            }
+            __syncwarp();
+            if (!dead && refill && lane == 0) issue_fill(f + p.nstages, slot);
+        }
+        slot += 4;
+        if (slot >= p.nstages) {
+            slot -= p.nstages;
+            par ^= 1;
         }
     }
 }
@@ -771,46 +586,8 @@ bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu) {
     return false;
 }
 
-static cudaError_t launch_gemv_m1_q6k_rows(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
-                                           size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    GemvM1Q6RowsParams p{};
-    p.w = static_cast<const uint8_t*>(w);
-    p.act = act;
-    p.out = out;
-    p.K = (uint32_t)K;
-    p.N = (uint32_t)N;
-    p.nblk = (uint32_t)(K / 256);
-    p.nchunk = (p.nblk + 15) / 16;
-    p.rpf = 16 / p.nchunk;
-    p.row_bytes = p.nblk * 210;
-    p.stage_bytes = (p.rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
-    p.act_off = 128;
-    p.part_off = (p.act_off + p.nblk * ACT6_STRIDE + 15) & ~15u;
-    p.stage_off = (p.part_off + 2 * 8 * 16 * 4 + 127) & ~127u;
-    p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;
-    if (p.nstages > 8) p.nstages = 8;
-    p.act_dtype = act_dtype;
-    p.out_dtype = out_dtype;
-    p.status = status;
-    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
-    size_t grid = (N + p.rpf - 1) / p.rpf;
-    if (grid > (size_t)sm_count) grid = sm_count;
-    cudaError_t le = launch_pdl(gemv_m1_q6k_rows_kernel, dim3((unsigned)grid), dim3(512), smem, st, p);
-    note_launch();
-    return le != cudaSuccess ? le : cudaGetLastError();
-}
-
 static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
                                       size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    if (K > 4096) return launch_gemv_m1_q6k_rows(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
     GemvM1Q6Params p{};
     p.w = static_cast<const uint8_t*>(w);
     p.act = act;
@@ -818,13 +595,19 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
     p.K = (uint32_t)K;
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
-    p.nchunk = (p.nblk + 15) / 16;
+    const uint32_t nchunk = p.nblk <= 16 ? 1 : p.nblk <= 32 ? 2 : 4;
+    const uint32_t rpf = 4 / nchunk;
     p.row_bytes = p.nblk * 210;
-    p.stage_bytes = (16 * 16 * 210 + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
-    p.act_off = 128;
-    p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 8 + 127) & ~127u;  // +8: the word pair past the last block half
+    p.stage_bytes = (rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
+    p.act_off = 512;
+    p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 127) & ~127u;
     p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;
-    if (p.nstages > 4) p.nstages = 4;
+    if (p.nstages > 16) p.nstages = 16;
+    // one CTA per SM, but never fewer than ~16 rows per CTA
+    size_t grid = (N + 15) / 16;
+    if (grid > (size_t)sm_count) grid = sm_count;
+    p.rows_per_cta = (uint32_t)((N + grid - 1) / grid);
+    grid = (N + p.rows_per_cta - 1) / p.rows_per_cta;
     p.act_dtype = act_dtype;
     p.out_dtype = out_dtype;
     p.status = status;
@@ -833,16 +616,15 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    size_t grid = (N + 15) / 16;
-    if (grid > (size_t)sm_count) grid = sm_count;
-    cudaError_t le = p.nchunk == 1 ? launch_pdl(gemv_m1_q6k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
-                                   : launch_pdl(gemv_m1_q6k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
+    cudaError_t le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                     : nchunk == 2 ? launch_pdl(gemv_m1_q6k_kernel<2>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                                   : launch_pdl(gemv_m1_q6k_kernel<4>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
 }
