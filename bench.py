@@ -149,7 +149,7 @@ class DecodeStack:
                     L[name] = ColumnParallelQuantLinear(device_weight(fmt, n // p, k, gen))
                 else:
                     L[name] = RowParallelQuantLinear(device_weight(fmt, n, k // p, gen))
-            L["qk"] = [QuantLinear(L["q"].weight), QuantLinear(L["k"].weight)]
+            L["qkv"] = [QuantLinear(L["q"].weight), QuantLinear(L["k"].weight), QuantLinear(L["v"].weight)]
             self.layers.append(L)
         self.lm_head = ColumnParallelQuantLinear(device_weight("Q6_K", VOCAB // p, HIDDEN, gen))
         f32 = dict(dtype=torch.float32, device="cuda")
@@ -175,8 +175,7 @@ class DecodeStack:
         from boostr_b200.tensor_parallel import all_reduce_tensor, gather_from_ranks
 
         for L in self.layers:
-            QuantLinear.forward_batch(L["qk"], self.x, outs=[self.q, self.k])
-            L["v"].forward(self.x, out=self.v)
+            QuantLinear.forward_batch(L["qkv"], self.x, outs=[self.q, self.k, self.v])   # column-parallel
             L["o"].forward(self.q, out=self.o)                      # row-parallel: all-reduce inside
             ops.quant_swiglu(self.o, L["gate"].weight, L["up"].weight, out=self.h)
             L["down"].forward(self.h, out=self.d)                   # row-parallel: all-reduce inside

@@ -19,6 +19,9 @@ size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, 
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu);
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
                            int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status);
+cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
+                                 void* const* out, const void* w6, size_t n6, void* out6, int out_dtype, size_t K, int sm_count,
+                                 cudaStream_t st, unsigned int* status);
 cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
                                  unsigned int* status);
@@ -200,26 +203,32 @@ int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* cons
     if (n_weights == 0) return B200Q_OK;
     if (!formats || !w || !N || !out) return fail(B200Q_ERR_INVALID_ARG, "quant_matmul_batch: null array");
     for (int i = 0; i < n_weights;) {
-        // decode (M = 1): runs of up to three Q4_K weights go out as ONE launch that quantises the
-        // activation row once and streams the weights back to back
+        // decode (M = 1): runs of up to three Q4_K weights, optionally followed by one Q6_K weight (the
+        // q/k/v projections of a Q4_K_M model), go out as ONE launch that streams them side by side
         int run = 1;
-        if (formats[i] == FMT_Q4_K && gemv_m1_supported(FMT_Q4_K, M, K, N[i], false))
+        bool mixed = false;
+        if (formats[i] == FMT_Q4_K && gemv_m1_supported(FMT_Q4_K, M, K, N[i], false)) {
             while (run < 3 && i + run < n_weights && formats[i + run] == FMT_Q4_K) ++run;
-        if (run > 1) {
-            for (int j = 0; j < run; ++j) {
+            mixed = i + run < n_weights && formats[i + run] == FMT_Q6_K && gemv_m1_supported(FMT_Q6_K, M, K, N[i + run], false);
+        }
+        const int total = run + (mixed ? 1 : 0);
+        if (total > 1) {
+            for (int j = 0; j < total; ++j) {
                 int rc = check_matmul_args("quant_matmul_batch", formats[i + j], act, act_dtype, w[i + j], out[i + j], out_dtype, M, K, N[i + j]);
                 if (rc) return rc;
             }
             unsigned int* status = status_ptr_current();
             if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul_batch: cannot resolve the device status word");
-            cudaError_t e = launch_gemv_m1_batch(act, act_dtype, run, w + i, N + i, out + i, nullptr, out_dtype, K,
-                                                 sm_count_current(), static_cast<cudaStream_t>(stream), status);
+            cudaError_t e = mixed ? launch_gemv_m1_mixed(act, act_dtype, run, w + i, N + i, out + i, w[i + run], N[i + run], out[i + run],
+                                                         out_dtype, K, sm_count_current(), static_cast<cudaStream_t>(stream), status)
+                                  : launch_gemv_m1_batch(act, act_dtype, run, w + i, N + i, out + i, nullptr, out_dtype, K,
+                                                         sm_count_current(), static_cast<cudaStream_t>(stream), status);
             if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_matmul_batch kernel launch failed: %s", cudaGetErrorString(e));
         } else {
             int rc = b200q_quant_matmul(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream);
             if (rc) return rc;
         }
-        i += run;
+        i += total;
     }
     return B200Q_OK;
 }

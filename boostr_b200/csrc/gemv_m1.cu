@@ -139,16 +139,15 @@ __device__ __forceinline__ float quantize_block8(const float (&v)[8], uint2& pac
 // and group g takes fills g, g+4, g+8, ... of the CTA's row range.  Small fills let the arithmetic start
 // as soon as the first 18 KB have landed, while the ring still keeps ~220 KB per SM in flight.
 template <bool SWIGLU>
-__global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params p) {
+__device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t cta, uint8_t* smem) {
     constexpr uint32_t FR = SWIGLU ? 4 : 8;  // output rows per fill
-    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     uint8_t* act_s = smem + p.act_off;
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
     TRACE1(p.trace_idx, 0);
 
-    const uint32_t row_begin = blockIdx.x * p.rows_per_cta;
+    const uint32_t row_begin = cta * p.rows_per_cta;
     const uint32_t row_end = min(p.N, row_begin + p.rows_per_cta);
     const uint32_t nfill = row_end > row_begin ? (row_end - row_begin + FR - 1) / FR : 0;
 
@@ -336,6 +335,12 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const GemvM1Params 
     TRACE1MAX(p.trace_idx, 6);
 }
 
+template <bool SWIGLU>
+__global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const __grid_constant__ GemvM1Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    q4k_body<SWIGLU>(p, blockIdx.x, smem);
+}
+
 
 // ------------------------------------------------------------------------------------ Q6_K, M = 1
 //
@@ -441,16 +446,15 @@ __device__ __forceinline__ int q6k_half_sum(const uint8_t* blk, int n, const uin
 }
 
 template <int NCHUNK>
-__global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Params p) {
+__device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t cta, uint8_t* smem) {
     constexpr uint32_t RPF = 4 / NCHUNK;  // rows per fill
-    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     float* part = reinterpret_cast<float*>(smem + 256);  // [16 slots][4 warps of the group]
     uint8_t* act_s = smem + p.act_off;
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
 
-    const uint32_t row_begin = blockIdx.x * p.rows_per_cta;
+    const uint32_t row_begin = cta * p.rows_per_cta;
     const uint32_t row_end = min(p.N, row_begin + p.rows_per_cta);
     const uint32_t nfill = row_end > row_begin ? (row_end - row_begin + RPF - 1) / RPF : 0;
 
@@ -576,6 +580,21 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const GemvM1Q6Param
     }
 }
 
+template <int NCHUNK>
+__global__ void __launch_bounds__(512, 1) gemv_m1_q6k_kernel(const __grid_constant__ GemvM1Q6Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    q6k_body<NCHUNK>(p, blockIdx.x, smem);
+}
+
+// Q4_K weights and one Q6_K weight that share the activation row (the q/k/v projections of a Q4_K_M
+// model) in ONE launch: the first `split` CTAs stream the Q4_K rows, the others the Q6_K rows.
+__global__ void __launch_bounds__(512, 1) gemv_m1_mixed_kernel(const __grid_constant__ GemvM1Params p4,
+                                                               const __grid_constant__ GemvM1Q6Params p6, const uint32_t split) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    if (blockIdx.x < split) q4k_body<false>(p4, blockIdx.x, smem);
+    else q6k_body<1>(p6, blockIdx.x - split, smem);
+}
+
 }  // namespace
 
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu) {
@@ -586,65 +605,43 @@ bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu) {
     return false;
 }
 
-static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
-                                      size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    GemvM1Q6Params p{};
+constexpr size_t M1_SMEM_MAX = 232448 - 1024;
+
+// Fills in the Q6_K parameters for a launch on at most `max_grid` CTAs; returns the grid, 0 if none.
+static size_t setup_q6k(GemvM1Q6Params& p, uint32_t& nchunk, size_t& smem, const void* act, int act_dtype, const void* w, void* out,
+                        int out_dtype, size_t K, size_t N, size_t max_grid, unsigned int* status) {
+    p = GemvM1Q6Params{};
     p.w = static_cast<const uint8_t*>(w);
     p.act = act;
     p.out = out;
     p.K = (uint32_t)K;
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
-    const uint32_t nchunk = p.nblk <= 16 ? 1 : p.nblk <= 32 ? 2 : 4;
+    nchunk = p.nblk <= 16 ? 1 : p.nblk <= 32 ? 2 : 4;
     const uint32_t rpf = 4 / nchunk;
     p.row_bytes = p.nblk * 210;
     p.stage_bytes = (rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
     p.act_off = 512;
     p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 127) & ~127u;
-    p.nstages = (232448 - 1024 - p.stage_off - 64) / p.stage_bytes;
+    p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off - 64) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
-    // one CTA per SM, but never fewer than ~16 rows per CTA
+    // never fewer than ~16 rows per CTA
     size_t grid = (N + 15) / 16;
-    if (grid > (size_t)sm_count) grid = sm_count;
+    if (grid > max_grid) grid = max_grid;
     p.rows_per_cta = (uint32_t)((N + grid - 1) / grid);
     grid = (N + p.rows_per_cta - 1) / p.rows_per_cta;
     p.act_dtype = act_dtype;
     p.out_dtype = out_dtype;
     p.status = status;
-    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;  // +64: the aligned word read past the last block
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
-    cudaError_t le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
-                     : nchunk == 2 ? launch_pdl(gemv_m1_q6k_kernel<2>, dim3((unsigned)grid), dim3(512), smem, st, p)
-                                   : launch_pdl(gemv_m1_q6k_kernel<4>, dim3((unsigned)grid), dim3(512), smem, st, p);
-    note_launch();
-    return le != cudaSuccess ? le : cudaGetLastError();
+    smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;  // +64: the aligned word read past the last block
+    return grid;
 }
 
-// Q4_K, M = 1: `nseg` weights (1..3) sharing one activation row, each [n[i], K] with its own output.
-cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
-                                 void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
-                                 unsigned int* status);
-
-cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
-                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
-    return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status);
-}
-
-cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
-                                 void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
-                                 unsigned int* status) {
-    const bool swiglu = w_up != nullptr;
-    GemvM1Params p{};
+// Same for Q4_K: `nseg` weights (1..3) sharing one activation row, or gate/up for SwiGLU.
+static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_dtype, int nseg, const void* const* w,
+                        const size_t* n, void* const* out, const void* w_up, int out_dtype, size_t K, size_t max_grid,
+                        unsigned int* status) {
+    p = GemvM1Params{};
     size_t N = 0;
     for (int i = 0; i < nseg && i < 3; ++i) {
         p.w[i] = static_cast<const uint8_t*>(w[i]);
@@ -668,30 +665,94 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
     p.stage_bytes = 8 * p.row_bytes;  // multiple of 128
     p.act_off = 256;
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
-    p.nstages = (232448 - 1024 - p.stage_off) / p.stage_bytes;
+    p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
-    // one CTA per SM, but never fewer than ~16 rows per CTA
     size_t grid = (N + 15) / 16;
-    if (grid > (size_t)sm_count) grid = sm_count;
+    if (grid > max_grid) grid = max_grid;
     p.rows_per_cta = (uint32_t)((N + grid - 1) / grid);
     grid = (N + p.rows_per_cta - 1) / p.rows_per_cta;
     p.act_dtype = act_dtype;
     p.out_dtype = out_dtype;
     p.status = status;
-    const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes;
+    smem = p.stage_off + (size_t)p.nstages * p.stage_bytes;
+    return grid;
+}
+
+static cudaError_t m1_attrs() {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
-    cudaError_t le = swiglu ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
-                            : launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
+    if (dev < 0 || dev >= 64 || attr_set[dev]) return cudaSuccess;
+    const int v = (int)M1_SMEM_MAX;
+    cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_mixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
+    if (e == cudaSuccess) attr_set[dev] = true;
+    return e;
+}
+
+static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
+                                      size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    GemvM1Q6Params p;
+    uint32_t nchunk;
+    size_t smem;
+    const size_t grid = setup_q6k(p, nchunk, smem, act, act_dtype, w, out, out_dtype, K, N, (size_t)sm_count, status);
+    cudaError_t e = m1_attrs();
+    if (e != cudaSuccess) return e;
+    cudaError_t le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                     : nchunk == 2 ? launch_pdl(gemv_m1_q6k_kernel<2>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                                   : launch_pdl(gemv_m1_q6k_kernel<4>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+// Q4_K, M = 1: `nseg` weights (1..3) sharing one activation row, each [n[i], K] with its own output.
+cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
+                                 void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
+                                 unsigned int* status) {
+    GemvM1Params p;
+    size_t smem;
+    const size_t grid = setup_q4k(p, smem, act, act_dtype, nseg, w, n, out, w_up, out_dtype, K, (size_t)sm_count, status);
+    cudaError_t e = m1_attrs();
+    if (e != cudaSuccess) return e;
+    cudaError_t le = w_up ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                          : launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
+    note_launch();
+    return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+// `nseg` Q4_K weights plus one Q6_K weight [n6, K] on the same activation row, one launch.  The SMs are
+// divided in proportion to the packed bytes, Q6_K bytes counting 1.3x (more arithmetic per byte).
+cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
+                                 void* const* out, const void* w6, size_t n6, void* out6, int out_dtype, size_t K, int sm_count,
+                                 cudaStream_t st, unsigned int* status) {
+    size_t n4 = 0;
+    for (int i = 0; i < nseg; ++i) n4 += n[i];
+    const double b4 = (double)n4 * 144.0, b6 = (double)n6 * 210.0 * 1.3;
+    size_t g6 = (size_t)((double)sm_count * b6 / (b4 + b6) + 0.5);
+    if (g6 < 1) g6 = 1;
+    if (g6 > (size_t)sm_count - 1) g6 = (size_t)sm_count - 1;
+    GemvM1Params p4;
+    GemvM1Q6Params p6;
+    uint32_t nchunk;
+    size_t smem4, smem6;
+    const size_t grid4 = setup_q4k(p4, smem4, act, act_dtype, nseg, w, n, out, nullptr, out_dtype, K, (size_t)sm_count - g6, status);
+    const size_t grid6 = setup_q6k(p6, nchunk, smem6, act, act_dtype, w6, out6, out_dtype, K, n6, g6, status);
+    cudaError_t e = m1_attrs();
+    if (e != cudaSuccess) return e;
+    cudaError_t le = launch_pdl(gemv_m1_mixed_kernel, dim3((unsigned)(grid4 + grid6)), dim3(512), smem4 > smem6 ? smem4 : smem6, st,
+                                p4, p6, (uint32_t)grid4);
+    note_launch();
+    return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
+                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+    if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
+    return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status);
 }
 
 #if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)

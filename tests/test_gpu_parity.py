@@ -414,8 +414,8 @@ def test_tp_shard_shapes_of_the_decode_stack(ops, oracle, world, m):
 
 
 def test_quant_matmul_batch_decode_fused_launch(ops, oracle):
-    # M = 1: consecutive Q4_K weights share one launch (q/k/v-style); odd row counts exercise segment
-    # boundaries inside a stage
+    # M = 1: consecutive Q4_K weights, and a Q6_K weight right after them, share one launch (q/k/v-style);
+    # odd row counts exercise segment boundaries inside a fill
     rng = synth.rng_for(36)
     k = 4096
     act = synth.activations(rng, 1, k)
@@ -424,7 +424,29 @@ def test_quant_matmul_batch_decode_fused_launch(ops, oracle):
     before = ops.launch_count()
     outs = ops.quant_matmul_batch(torch.from_numpy(act).cuda(), [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)])
     ops.check_device_status()
-    assert ops.launch_count() - before == 3  # [Q4_K x3] + [Q6_K] + [Q4_K]
+    assert ops.launch_count() - before == 2  # [Q4_K x3 + Q6_K] + [Q4_K]
+    for (f, n), w, o in zip(specs, ws, outs):
+        want = oracle.quant_matmul(f, act, w, n)
+        assert o.shape == (1, n)
+        assert rel_err(o.cpu().numpy(), want)[0] < 2e-6, (f, n)
+
+
+@pytest.mark.parametrize("specs", [
+    [("Q4_K", 4096), ("Q4_K", 1024), ("Q6_K", 1024)],   # q, k, v of the decode stack
+    [("Q4_K", 2048), ("Q4_K", 512), ("Q6_K", 512)],     # the same on 2 ranks
+    [("Q4_K", 7), ("Q6_K", 3)],
+    [("Q4_K", 5000), ("Q6_K", 1)],
+    [("Q4_K", 16), ("Q4_K", 16), ("Q4_K", 16), ("Q6_K", 6000)],
+])
+@pytest.mark.parametrize("k", [4096, 1024])
+def test_quant_matmul_batch_decode_mixed_formats_one_launch(ops, oracle, specs, k):
+    rng = synth.rng_for(38, k + len(specs) + specs[-1][1])
+    act = synth.activations(rng, 1, k)
+    ws = [synth.weight_bytes(f, rng, n, k) for f, n in specs]
+    before = ops.launch_count()
+    outs = ops.quant_matmul_batch(torch.from_numpy(act).cuda(), [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)])
+    ops.check_device_status()
+    assert ops.launch_count() - before == 1
     for (f, n), w, o in zip(specs, ws, outs):
         want = oracle.quant_matmul(f, act, w, n)
         assert o.shape == (1, n)
