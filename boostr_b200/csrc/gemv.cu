@@ -692,7 +692,10 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     FillCursor pc{blockIdx.x, 0, 0, 0, 0, 0};
     int pw = 0;  // warp that requests fill pc.it
     TRACE(0);
-    for (uint32_t i = 0; i < p.nstages; ++i) {
+    // Only two fills leave before the activations are fetched: responses return to an SM in request
+    // order, so activation loads issued behind a full ring would wait for every stage to land.
+    const uint32_t early = min(2u, p.nstages);
+    for (uint32_t i = 0; i < early; ++i) {
         if (pc.unit < p.total_units && pw == warp) issue_fill(pc);
         advance(pc);
         if (++pw == nwc) pw = 0;
@@ -711,6 +714,11 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
         const uint32_t gc = ks * SL + c;
         const uint32_t slice = gc * p.spc + s;
         B[c].build(p, slice, c < nch && slice < p.nslices, g, t);
+    }
+    for (uint32_t i = early; i < p.nstages; ++i) {  // the rest of the ring
+        if (pc.unit < p.total_units && pw == warp) issue_fill(pc);
+        advance(pc);
+        if (++pw == nwc) pw = 0;
     }
 
     // Adds up the partial sums of slab `unit_j` (ring slot `js`) and stores the results: one
