@@ -185,18 +185,27 @@ class DecodeStack:
         return self.logits
 
 
+# DRAM bytes (read + written) of one launch of the dominant kernel at one GPU, from the ncu capture
+# summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.256 MB, dram__bytes_write.sum 0.
+# A K-split shard streams proportionally fewer bytes, so the figure is scaled by the shard's packed bytes.
+NCU_TRAFFIC_DOWN_1GPU = 48_256_000
+NCU_ALGORITHMIC_DOWN_1GPU = 4096 * 56 * 210
+
+
 def time_kernel_family(stack, torch, ops):
-    """Average device time of the dominant kernel: the Q4_K decode GEMV on the gate-projection shards
-    of all layers (distinct weights, 1 GB in total at one GPU, so every launch streams from HBM)."""
-    outs = torch.empty(stack.m, stack.layers[0]["gate"].weight.shape[0], device="cuda")
-    ws = [L["gate"].weight for L in stack.layers]
+    """Average device time of the dominant kernel (largest share of the step in the ncu launch list):
+    the Q6_K decode GEMV on the down-projection shards of all layers (distinct weights, 1.5 GB in total
+    at one GPU, so every launch streams from HBM)."""
+    ws = [L["down"].weight for L in stack.layers]
+    x = torch.randn(stack.m, ws[0].shape[1], device="cuda")
+    outs = torch.empty(stack.m, ws[0].shape[0], device="cuda")
     for w in ws[:3]:
-        ops.quant_matmul(stack.x, w, out=outs)
+        ops.quant_matmul(x, w, out=outs)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         for w in ws:
-            ops.quant_matmul(stack.x, w, out=outs)
+            ops.quant_matmul(x, w, out=outs)
     g.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -346,11 +355,14 @@ def run_ours(args):
                     "d2h_bytes_per_step": m * VOCAB * 4},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "Q4_K decode GEMV, gate-projection shard [%d x %d], M=%d" % (
-                             stack.layers[0]["gate"].weight.shape[0], HIDDEN, m),
+            "roofline": {"bound": "hbm", "kernel": "Q6_K decode GEMV, down-projection shard [%d x %d], M=%d" % (
+                             HIDDEN, stack.layers[0]["down"].weight.shape[1], m),
                          "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                          "frac_of_8tbs": achieved / 8000.0, "peak_source": pk["source"], "avg_launch_us": k_us,
-                         "algorithmic_bytes_per_launch": k_bytes, "traffic": None},
+                         "algorithmic_bytes_per_launch": k_bytes,
+                         "traffic": int(NCU_TRAFFIC_DOWN_1GPU * k_bytes / NCU_ALGORITHMIC_DOWN_1GPU),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 1 GPU "
+                                           "(profiles/gemv_m1_q6k_down.md), scaled by the shard's packed bytes"},
         }
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_reference(m, budget_s=args.cpu_seconds)
