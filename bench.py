@@ -250,6 +250,14 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         log("process group up")
+        if args.collective == "fused":
+            from boostr_b200.tensor_parallel import PeerExchange
+
+            stack.exchange = PeerExchange()
+            for L in stack.layers:
+                L["o"].exchange = stack.exchange
+                L["down"].exchange = stack.exchange
+            log("peer exchange mapped")
 
     def barrier():
         if world > 1:
@@ -347,7 +355,8 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "u8 blocks x int8 (Q8_K) activations, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": f"C5 Llama-3-8B-shaped decode step, 32 layers + lm_head, M={m}",
-                       "parallelism": f"tp{world}", "packed_weight_bytes_per_step": STEP_BYTES,
+                       "parallelism": f"tp{world}", "row_parallel_reduce": (args.collective if world > 1 else "none"),
+                       "packed_weight_bytes_per_step": STEP_BYTES,
                        "l2": "weights per step per rank exceed L2 (%d MB > 126 MB)" % (stack.bytes_local // 2**20),
                        "cuda_graph": graph is not None},
             "step_weight_gbs": step_gbs, "step_frac_of_8tbs": step_gbs / 8000.0,
@@ -447,6 +456,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="tokens per decode step")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="row-parallel all-reduce at N > 1: fused into the GEMV kernel over peer memory, or NCCL")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()

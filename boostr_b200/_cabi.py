@@ -14,10 +14,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200q.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED_FORMAT, ERR_BAD_SHAPE, ERR_WORKSPACE_TOO_SMALL, ERR_CUDA, ERR_TIMEOUT, \
-    ERR_UNSUPPORTED_DTYPE = range(8)
+    ERR_UNSUPPORTED_DTYPE, ERR_NOT_FUSED = range(9)
 DT_F32, DT_BF16, DT_F16, DT_F64 = range(4)
 OP_QUANT_MATMUL, OP_QUANT_SWIGLU = 0, 1
 STATIC_SCRATCH_BYTES = 8 << 20
+TP_HANDLE_BYTES = 64
 
 # every symbol include/b200q.h declares: name -> (restype, argtypes)
 SIGNATURES = {
@@ -39,6 +40,13 @@ SIGNATURES = {
                                                   c_size_t, c_void_p]),
     "b200q_shard_pack": (c_int, [c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_int, c_void_p, c_size_t]),
     "b200q_check_device_status": (c_int, [c_void_p]),
+    "b200q_tp_buffer_bytes": (c_size_t, []),
+    "b200q_tp_alloc": (c_int, [POINTER(c_void_p), ctypes.c_char_p]),
+    "b200q_tp_open": (c_int, [ctypes.c_char_p, POINTER(c_void_p)]),
+    "b200q_tp_close": (c_int, [c_void_p]),
+    "b200q_tp_free": (c_int, [c_void_p]),
+    "b200q_row_parallel_matmul": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_size_t,
+                                          c_int, c_int, POINTER(c_void_p), c_void_p]),
     "b200q_launch_count": (ctypes.c_ulonglong, []),
 }
 

@@ -25,6 +25,8 @@ cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const
 cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
                                  unsigned int* status);
+cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
+                                  int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm);
 bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N);
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -352,6 +354,72 @@ int b200q_quant_matmul_static_scratch(int format, const void* act, int act_dtype
 }
 
 unsigned long long b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+size_t b200q_tp_buffer_bytes(void) { return TP_BUF_BYTES; }
+
+int b200q_tp_alloc(void** buf, unsigned char* handle) {
+    if (!buf || !handle) return fail(B200Q_ERR_INVALID_ARG, "tp_alloc: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200Q_TP_HANDLE_BYTES, "IPC handle size");
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, TP_BUF_BYTES);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, TP_BUF_BYTES);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        return fail(B200Q_ERR_CUDA, "tp_alloc: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, sizeof(h));
+    *buf = p;
+    return B200Q_OK;
+}
+
+int b200q_tp_open(const unsigned char* handle, void** peer_buf) {
+    if (!handle || !peer_buf) return fail(B200Q_ERR_INVALID_ARG, "tp_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "tp_open: %s", cudaGetErrorString(e));
+    *peer_buf = p;
+    return B200Q_OK;
+}
+
+int b200q_tp_close(void* peer_buf) {
+    cudaError_t e = cudaIpcCloseMemHandle(peer_buf);
+    return e == cudaSuccess ? B200Q_OK : fail(B200Q_ERR_CUDA, "tp_close: %s", cudaGetErrorString(e));
+}
+
+int b200q_tp_free(void* buf) {
+    cudaError_t e = cudaFree(buf);
+    return e == cudaSuccess ? B200Q_OK : fail(B200Q_ERR_CUDA, "tp_free: %s", cudaGetErrorString(e));
+}
+
+int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
+                              size_t K, size_t N, int rank, int world, void* const* bufs, void* stream) {
+    int rc = check_matmul_args("row_parallel_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
+    if (rc) return rc;
+    if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(B200Q_ERR_INVALID_ARG, "row_parallel_matmul: rank %d of world %d (at most %u ranks)", rank, world, TP_MAX_WORLD);
+    if (!bufs) return fail(B200Q_ERR_INVALID_ARG, "row_parallel_matmul: null buffer table");
+    if (M != 1 || out_dtype != DT_F32 || N > TP_MAX_N || !gemv_m1_supported(format, M, K, N, false))
+        return fail(B200Q_ERR_NOT_FUSED, "row_parallel_matmul: no fused exchange for %s M=%zu K=%zu N=%zu; use quant_matmul + all-reduce",
+                    format_name(format), M, K, N);
+    PeerComm comm{};
+    comm.world = (uint32_t)world;
+    comm.rank = (uint32_t)rank;
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r]) return fail(B200Q_ERR_INVALID_ARG, "row_parallel_matmul: null exchange buffer of rank %d", r);
+        comm.buf[r] = static_cast<uint8_t*>(bufs[r]);
+    }
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "row_parallel_matmul: cannot resolve the device status word");
+    cudaError_t e = launch_gemv_m1_rowpar(format, act, act_dtype, w, out, K, N, sm_count_current(), static_cast<cudaStream_t>(stream),
+                                          status, comm);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA row_parallel_matmul kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
 
 int b200q_check_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

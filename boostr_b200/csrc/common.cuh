@@ -17,7 +17,7 @@ enum : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_F64 = 3 };
 // Device status word (one per device, owned by the C-ABI translation unit and handed to
 // kernels as a pointer): a kernel that gives up on a bounded wait ORs a code in here and
 // finishes without touching the data it waited for.
-enum : unsigned { STATUS_TIMEOUT_FULL = 1u, STATUS_TIMEOUT_EMPTY = 2u, STATUS_TIMEOUT_MMA = 4u, STATUS_TIMEOUT_TMEM = 8u };
+enum : unsigned { STATUS_TIMEOUT_FULL = 1u, STATUS_TIMEOUT_EMPTY = 2u, STATUS_TIMEOUT_MMA = 4u, STATUS_TIMEOUT_TMEM = 8u, STATUS_TIMEOUT_PEER = 16u };
 
 __host__ __device__ constexpr int fmt_block_size(int f) { return (f == FMT_Q4_0 || f == FMT_Q8_0) ? 32 : 256; }
 __host__ __device__ constexpr int fmt_block_bytes(int f) {
@@ -122,6 +122,85 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ------------------------------------------------------------------- peer exchange (tensor parallel)
+// Row-parallel decode products end in an all-reduce of one f32 row.  Instead of a separate collective
+// the GEMV kernel pushes its partial row into EVERY rank's exchange buffer over NVLink (plain stores
+// to peer-mapped memory); the last CTA of each rank then raises that rank's flag on every peer, waits
+// (bounded) for all flags and adds the partial rows in rank order, so every rank stores the same bits.
+//
+// Exchange buffer of a rank (TP_BUF_BYTES, zeroed at allocation):
+//   [0]   u32 epoch: number of exchanges completed by this rank (written by the last CTA)
+//   [4]   u32 count of local CTAs that finished pushing (reset by the last CTA)
+//   [64 + 64 r] u32 flag of rank r: the epoch whose partial row from r has fully arrived here
+//   [1024 + ((e & 1) * 8 + r) * 65536]  partial row of rank r for epoch e (up to 16384 f32)
+// Two parities suffice: a rank can start epoch e + 2 only after every peer signalled e + 1, which a
+// peer does after it finished reading epoch e.
+constexpr uint32_t TP_MAX_WORLD = 8, TP_MAX_N = 16384;
+constexpr size_t TP_BUF_BYTES = 1024 + 2 * (size_t)TP_MAX_WORLD * TP_MAX_N * 4;
+struct PeerComm {
+    uint32_t world, rank;  // world <= 1: no exchange
+    uint8_t* buf[TP_MAX_WORLD];
+};
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// epoch this launch takes part in (call after grid_dep_wait)
+__device__ __forceinline__ uint32_t tp_epoch(const PeerComm& c) {
+    return *reinterpret_cast<volatile const uint32_t*>(c.buf[c.rank]) + 1u;
+}
+__device__ __forceinline__ void tp_push(const PeerComm& c, uint32_t e, uint32_t row, float v) {
+    const size_t off = 1024 + ((size_t)(e & 1u) * TP_MAX_WORLD + c.rank) * (TP_MAX_N * 4) + (size_t)row * 4;
+    for (uint32_t r = 0; r < c.world; ++r) *reinterpret_cast<float*>(c.buf[r] + off) = v;
+}
+// Called by ALL threads of every CTA after its last tp_push.  `s_flag`: one u32 of shared memory.
+__device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_t n, float* out, unsigned int* status, uint32_t* s_flag) {
+    __syncthreads();  // every push of this CTA has been issued
+    uint32_t* ctl = reinterpret_cast<uint32_t*>(c.buf[c.rank]);
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        *s_flag = atomicAdd(ctl + 1, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!*s_flag) return;
+    // last CTA of this rank: all local pushes are ordered before the flags raised here
+    bool ok = true;
+    if (threadIdx.x < c.world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(c.buf[threadIdx.x] + 64 + 64 * c.rank), e);
+        const uint32_t* f = reinterpret_cast<const uint32_t*>(c.buf[c.rank] + 64 + 64 * threadIdx.x);
+        const bool broken = (*reinterpret_cast<volatile unsigned int*>(status) & STATUS_TIMEOUT_PEER) != 0;  // a peer was lost before
+        const uint64_t t0 = global_timer_ns();
+        while (!broken && (int32_t)(ld_acquire_sys(f) - e) < 0) {
+            if (global_timer_ns() - t0 > 1000000000ull) {
+                atomicOr(status, STATUS_TIMEOUT_PEER);
+                ok = false;
+                break;
+            }
+        }
+        if (broken) ok = false;
+    }
+    ok = __syncthreads_and(ok);
+    if (ok) {
+        const uint8_t* base = c.buf[c.rank] + 1024 + (size_t)(e & 1u) * TP_MAX_WORLD * (TP_MAX_N * 4);
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            float sum = 0.f;
+            for (uint32_t r = 0; r < c.world; ++r)
+                sum = __fadd_rn(sum, __ldcg(reinterpret_cast<const float*>(base + (size_t)r * (TP_MAX_N * 4)) + i));
+            out[i] = sum;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ctl[1] = 0;
+        ctl[0] = e;
+    }
 }
 
 // ------------------------------------------------------------------- shared-memory loads

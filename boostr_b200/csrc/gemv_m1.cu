@@ -60,6 +60,7 @@ struct GemvM1Params {
     int act_dtype, out_dtype;
     unsigned int* status;
     uint32_t trace_idx, dbg;
+    PeerComm comm;  // row-parallel shard: push the partial row to every rank and add them up (single weight, f32 out)
 };
 
 namespace {
@@ -191,6 +192,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
     grid_dep_launch();  // the next kernel may start its own weight prefetch as SMs free up
     grid_dep_wait();    // the previous kernel's output (our activations) is complete from here on
     TRACE1(p.trace_idx, 2);
+    const bool tp = !SWIGLU && p.comm.world > 1;
+    const uint32_t tp_e = tp ? tp_epoch(p.comm) : 0u;
 
     // 1. quantise the activation row: warp w owns block w; each warp issues its load first and then
     // its share of the remaining first fills
@@ -314,7 +317,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             while (sg + 1 < p.nseg && v >= p.seg_end[sg]) seg_begin = p.seg_end[sg++];
             const size_t idx = v - seg_begin;
             void* o = p.out[sg];
-            if (p.out_dtype == DT_F32) static_cast<float*>(o)[idx] = term;
+            if (tp) tp_push(p.comm, tp_e, v, term);
+            else if (p.out_dtype == DT_F32) static_cast<float*>(o)[idx] = term;
             else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(o)[idx] = __float2bfloat16_rn(term);
             else static_cast<__half*>(o)[idx] = __float2half_rn(term);
         }
@@ -333,6 +337,7 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         }
     }
     TRACE1MAX(p.trace_idx, 6);
+    if (tp) tp_finish(p.comm, tp_e, p.N, static_cast<float*>(p.out[0]), p.status, reinterpret_cast<uint32_t*>(smem + 256));
 }
 
 template <bool SWIGLU>
@@ -370,6 +375,7 @@ struct GemvM1Q6Params {
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
     unsigned int* status;
+    PeerComm comm;  // row-parallel shard: push the partial row to every rank and add them up (f32 out)
 };
 
 // activation image per 256-block (stride 304 B): [0,256) int8 codes | [256,288) 16 x int16 sums of 16 | [288,292) f32 d8
@@ -476,6 +482,8 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
     if (warp == 15 && lane < 2 && (uint32_t)lane < nfill) issue_fill(lane, lane);
     grid_dep_launch();
     grid_dep_wait();
+    const bool tp = p.comm.world > 1;
+    const uint32_t tp_e = tp ? tp_epoch(p.comm) : 0u;
 
     // 1. quantise the activation row: warp w takes blocks w, w + 16, ... (8 values per lane)
     {
@@ -525,7 +533,8 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
     }
 
     auto store_row = [&](uint32_t row, float val) {
-        if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[row] = val;
+        if (tp) tp_push(p.comm, tp_e, row, val);
+        else if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[row] = val;
         else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[row] = __float2bfloat16_rn(val);
         else static_cast<__half*>(p.out)[row] = __float2half_rn(val);
     };
@@ -578,6 +587,7 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
             par ^= 1;
         }
     }
+    if (tp) tp_finish(p.comm, tp_e, p.N, static_cast<float*>(p.out), p.status, reinterpret_cast<uint32_t*>(smem + 512));
 }
 
 template <int NCHUNK>
@@ -621,7 +631,7 @@ static size_t setup_q6k(GemvM1Q6Params& p, uint32_t& nchunk, size_t& smem, const
     const uint32_t rpf = 4 / nchunk;
     p.row_bytes = p.nblk * 210;
     p.stage_bytes = (rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
-    p.act_off = 512;
+    p.act_off = 576;  // [0,256) barriers, [256,512) chunk-sum table, [512,576) exchange flag
     p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off - 64) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
@@ -663,7 +673,7 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
     { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
 #endif
     p.stage_bytes = 8 * p.row_bytes;  // multiple of 128
-    p.act_off = 256;
+    p.act_off = 320;  // [0,256) barriers, [256,320) exchange flag
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
@@ -745,6 +755,32 @@ cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const
     if (e != cudaSuccess) return e;
     cudaError_t le = launch_pdl(gemv_m1_mixed_kernel, dim3((unsigned)(grid4 + grid6)), dim3(512), smem4 > smem6 ? smem4 : smem6, st,
                                 p4, p6, (uint32_t)grid4);
+    note_launch();
+    return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+// Row-parallel shard, M = 1: the local product's row is pushed to every rank and the rank-ordered sum
+// lands in `out` (f32), all in this one launch.
+cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
+                                  int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm) {
+    cudaError_t e = m1_attrs();
+    if (e != cudaSuccess) return e;
+    cudaError_t le;
+    size_t smem;
+    if (fmt == FMT_Q6_K) {
+        GemvM1Q6Params p;
+        uint32_t nchunk;
+        const size_t grid = setup_q6k(p, nchunk, smem, act, act_dtype, w, out, DT_F32, K, N, (size_t)sm_count, status);
+        p.comm = comm;
+        le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
+             : nchunk == 2 ? launch_pdl(gemv_m1_q6k_kernel<2>, dim3((unsigned)grid), dim3(512), smem, st, p)
+                           : launch_pdl(gemv_m1_q6k_kernel<4>, dim3((unsigned)grid), dim3(512), smem, st, p);
+    } else {
+        GemvM1Params p;
+        const size_t grid = setup_q4k(p, smem, act, act_dtype, 1, &w, &N, &out, nullptr, DT_F32, K, (size_t)sm_count, status);
+        p.comm = comm;
+        le = launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
+    }
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
 }

@@ -104,6 +104,25 @@ def quant_matmul(activation: torch.Tensor, weight: QuantTensor, out_dtype: torch
     return out
 
 
+def row_parallel_matmul(activation: torch.Tensor, weight: QuantTensor, rank: int, world: int, table,
+                        out: torch.Tensor = None):
+    """Local product of a row-parallel shard fused with the all-reduce over peer memory
+    (``b200q_row_parallel_matmul``).  Returns None, having launched nothing, when the shape has no fused
+    path; the caller then runs ``quant_matmul`` and a collective."""
+    act, m, k, n = _check_act("row_parallel_matmul", activation, weight, True)
+    if m != 1:
+        return None
+    out = _out_buffer(out, (*activation.shape[:-1], n), torch.float32, act.device)
+    L = _cabi.lib()
+    with torch.cuda.device(act.device):
+        rc = L.b200q_row_parallel_matmul(weight.format.format_id, act.data_ptr(), _DT[act.dtype], weight.storage.data_ptr(),
+                                         out.data_ptr(), _cabi.DT_F32, m, k, n, rank, world, table, _stream())
+    if rc == _cabi.ERR_NOT_FUSED:
+        return None
+    _cabi.check(rc)
+    return out
+
+
 def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
                        out_dtype: torch.dtype = torch.float32, outs: Sequence[torch.Tensor] = None) -> List[torch.Tensor]:
     """One activation against several weights sharing K (q/k/v, gate/up)."""

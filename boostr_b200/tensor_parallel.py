@@ -99,6 +99,60 @@ def gather_from_ranks(local_shard: torch.Tensor, group=None, out: Optional[torch
     return full
 
 
+class PeerExchange:
+    """Exchange buffers for the fused row-parallel decode product (``b200q_row_parallel_matmul``).
+
+    Every rank allocates one buffer in the library, the CUDA IPC handles travel through the process
+    group, and each rank maps its peers' buffers.  One PeerExchange serves one stream of calls, issued
+    in the same order on all ranks.  With one rank (or no process group) it is inert.
+    """
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = _world(group)
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self._own = None
+        self._peers = {}
+        self.table = None
+        if self.world <= 1:
+            return
+        L = _cabi.lib()
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_cabi.TP_HANDLE_BYTES)
+        _cabi.check(L.b200q_tp_alloc(ctypes.byref(own), handle))
+        self._own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        table = (ctypes.c_void_p * self.world)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                table[r] = self._own
+            else:
+                peer = ctypes.c_void_p()
+                _cabi.check(L.b200q_tp_open(ctypes.c_char_p(h), ctypes.byref(peer)))
+                self._peers[r] = peer.value
+                table[r] = peer.value
+        self.table = table
+        dist.barrier(group=group)  # nobody pushes before every mapping exists
+
+    def close(self):
+        """Unmap the peers and free the own buffer (all ranks, after the last fused call has finished)."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        L = _cabi.lib()
+        for ptr in self._peers.values():
+            L.b200q_tp_close(ptr)
+        self._peers = {}
+        if dist.is_initialized():
+            dist.barrier(group=self.group)  # a buffer is freed only when nobody maps it any more
+        L.b200q_tp_free(self._own)
+        self._own = None
+        self.table = None
+
+
 class ColumnParallelQuantLinear:
     """Output features split across ranks; no communication in forward."""
 
@@ -121,20 +175,32 @@ class ColumnParallelQuantLinear:
 
 
 class RowParallelQuantLinear:
-    """Input features split across ranks; forward = local product, all-reduce SUM, then bias."""
+    """Input features split across ranks; forward = local product, all-reduce SUM, then bias.
 
-    def __init__(self, local_weight: QuantTensor, bias: Optional[torch.Tensor] = None, group=None):
+    With a ``PeerExchange`` the decode case (one activation row, Q4_K/Q6_K, N <= 16384) runs as ONE
+    kernel that pushes the partial row to all ranks over NVLink and adds the rows in rank order; every
+    other shape falls back to ``quant_matmul`` + the process group's all-reduce."""
+
+    def __init__(self, local_weight: QuantTensor, bias: Optional[torch.Tensor] = None, group=None,
+                 exchange: Optional[PeerExchange] = None):
         self.weight = local_weight
         self.bias = bias
         self.group = group
+        self.exchange = exchange
 
     @classmethod
-    def from_full(cls, fmt, packed: np.ndarray, n: int, k: int, rank: int, world_size: int, device="cuda", group=None):
-        return cls(scatter_to_rank(fmt, packed, n, k, 1, rank, world_size, device), None, group)
+    def from_full(cls, fmt, packed: np.ndarray, n: int, k: int, rank: int, world_size: int, device="cuda", group=None,
+                  exchange: Optional[PeerExchange] = None):
+        return cls(scatter_to_rank(fmt, packed, n, k, 1, rank, world_size, device), None, group, exchange)
 
     def forward(self, input_shard: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        y = ops.quant_matmul(input_shard, self.weight, out=out)
-        all_reduce_tensor(y, self.group)
+        ex = self.exchange
+        y = None
+        if ex is not None and ex.table is not None and input_shard.is_cuda:
+            y = ops.row_parallel_matmul(input_shard, self.weight, ex.rank, ex.world, ex.table, out=out)
+        if y is None:
+            y = ops.quant_matmul(input_shard, self.weight, out=out)
+            all_reduce_tensor(y, self.group)
         if self.bias is not None:
             y.add_(self.bias)
         return y

@@ -42,7 +42,8 @@ typedef enum b200q_status {
     B200Q_ERR_WORKSPACE_TOO_SMALL = 4,
     B200Q_ERR_CUDA = 5,
     B200Q_ERR_TIMEOUT = 6,
-    B200Q_ERR_UNSUPPORTED_DTYPE = 7
+    B200Q_ERR_UNSUPPORTED_DTYPE = 7,
+    B200Q_ERR_NOT_FUSED = 8 /* b200q_row_parallel_matmul has no fused exchange for this shape */
 } b200q_status;
 
 /* Block formats; values are QuantFormat::format_id (src/quant/format.rs:204-230). */
@@ -184,6 +185,36 @@ B200Q_API int b200q_check_device_status(void* stream);
  * Diagnostic: lets a harness state how many of this library's kernels ran in a timed region.
  */
 B200Q_API unsigned long long b200q_launch_count(void);
+
+/*
+ * Tensor-parallel exchange over peer memory (one process per GPU, GPUs of one NVLink domain).
+ *
+ * Replaces, for decode (M = 1), the pair "local quant_matmul, then Communicator::all_reduce(Sum) and
+ * sync" of RowParallelLinear::forward (src/distributed/tensor_parallel.rs:230-238, all_reduce_tensor in
+ * src/distributed/comm_utils.rs:15-39) by ONE kernel: it pushes the local partial row into every
+ * rank's exchange buffer with plain stores over NVLink, the last CTA raises this rank's flag on every
+ * peer, waits (at most 1 s, then B200Q_ERR_TIMEOUT is reported by b200q_check_device_status) for all
+ * flags and adds the partial rows in rank order, so all ranks store bit-identical sums.
+ *
+ * Set-up, once per process: b200q_tp_alloc creates this rank's exchange buffer (cudaMalloc, zeroed) and
+ * its 64-byte CUDA IPC handle; the handles are exchanged by whatever the host uses (boostr: its
+ * Communicator's broadcast/all_gather of bytes); b200q_tp_open maps a peer's buffer.  `bufs[r]` is rank
+ * r's buffer as seen from this process (own buffer at bufs[rank]).  All ranks must issue the same
+ * sequence of b200q_row_parallel_matmul calls.  The buffers carry the exchange state (epoch, flags), so
+ * one set of buffers serves one stream of calls.
+ *
+ * Shapes without a fused path (M > 1, formats other than Q4_K/Q6_K, N > 16384, non-f32 output) return
+ * B200Q_ERR_NOT_FUSED without launching anything: run b200q_quant_matmul and the communicator's
+ * all_reduce instead.
+ */
+#define B200Q_TP_HANDLE_BYTES 64
+B200Q_API size_t b200q_tp_buffer_bytes(void);
+B200Q_API int b200q_tp_alloc(void** buf, unsigned char* handle /* B200Q_TP_HANDLE_BYTES */);
+B200Q_API int b200q_tp_open(const unsigned char* handle, void** peer_buf);
+B200Q_API int b200q_tp_close(void* peer_buf);
+B200Q_API int b200q_tp_free(void* buf);
+B200Q_API int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype,
+                                        size_t M, size_t K, size_t N, int rank, int world, void* const* bufs, void* stream);
 
 #ifdef __cplusplus
 }

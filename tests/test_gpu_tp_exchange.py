@@ -1,0 +1,109 @@
+"""Fused row-parallel decode product (b200q_row_parallel_matmul) on ONE GPU.
+
+Two exchange buffers are allocated on the same device and the peer's contribution (its partial row
+and its flag) is staged by the host before the launch, so the kernel's wait is satisfied at once and
+no kernel ever waits for another launch.  What is checked: the pushed partial row lands in the peer's
+buffer under the right parity, flags and epochs advance, the rank-ordered sum is bit-identical to the
+plain sum of the two partial products, over several consecutive calls (both parities).
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from boostr_b200 import _cabi, synth
+from boostr_b200.format import QuantFormat
+from boostr_b200.tensor import QuantTensor
+from boostr_b200.tensor_parallel import shard_bytes
+
+pytestmark = pytest.mark.gpu
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from boostr_b200 import ops as o
+
+    return o
+
+
+INBOX0 = 1024
+ROW_BYTES = 16384 * 4
+
+
+def _cudart():
+    for name in ("libcudart.so.12", "libcudart.so"):
+        try:
+            return ctypes.CDLL(name)
+        except OSError:
+            continue
+    pytest.skip("libcudart not loadable for raw device copies")
+
+
+def _h2d(rt, dst, arr):
+    assert rt.cudaMemcpy(ctypes.c_void_p(dst), ctypes.c_void_p(arr.ctypes.data), ctypes.c_size_t(arr.nbytes), 1) == 0
+
+
+def _d2h(rt, src, nbytes):
+    out = np.empty(nbytes, dtype=np.uint8)
+    assert rt.cudaMemcpy(ctypes.c_void_p(out.ctypes.data), ctypes.c_void_p(src), ctypes.c_size_t(nbytes), 2) == 0
+    return out
+
+
+@pytest.mark.parametrize("fmt,n,k", [("Q4_K", 4096, 4096), ("Q6_K", 4096, 14336), ("Q6_K", 300, 2048), ("Q4_K", 37, 1024)])
+def test_row_parallel_exchange_against_staged_peer(ops, fmt, n, k):
+    rt = _cudart()
+    L = _cabi.lib()
+    torch.cuda.synchronize()
+    bufs, table = [], (ctypes.c_void_p * 2)()
+    for r in range(2):
+        b, h = ctypes.c_void_p(), ctypes.create_string_buffer(_cabi.TP_HANDLE_BYTES)
+        _cabi.check(L.b200q_tp_alloc(ctypes.byref(b), h))
+        bufs.append(b.value)
+        table[r] = b.value
+    try:
+        rng = synth.rng_for(41, n + k)
+        full = synth.weight_bytes(fmt, rng, n, k)
+        f = QuantFormat.parse(fmt)
+        shards = [QuantTensor.from_bytes(shard_bytes(fmt, full, n, k, 1, r, 2), f, (n, k // 2), device="cuda") for r in range(2)]
+        for call in range(1, 5):  # epochs 1..4: both parities twice
+            act = synth.activations(rng, 1, k)
+            a = [torch.from_numpy(np.ascontiguousarray(act[:, r * (k // 2):(r + 1) * (k // 2)])).cuda() for r in range(2)]
+            y = [ops.quant_matmul(a[r], shards[r]) for r in range(2)]
+            torch.cuda.synchronize()
+            # stage rank 1's push into rank 0's buffer: its partial row, then its flag
+            par = call & 1
+            _h2d(rt, bufs[0] + INBOX0 + (par * 8 + 1) * ROW_BYTES, y[1].cpu().numpy().reshape(-1))
+            _h2d(rt, bufs[0] + 64 + 64 * 1, np.array([call], dtype=np.uint32))
+            out = ops.row_parallel_matmul(a[0], shards[0], 0, 2, table)
+            assert out is not None
+            ops.check_device_status()
+            want = (y[0] + y[1]).cpu().numpy()
+            assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32)), f"call {call}"
+            # what rank 0 left behind: its row in the peer's inbox, its flag on both sides, its epoch
+            pushed = _d2h(rt, bufs[1] + INBOX0 + (par * 8 + 0) * ROW_BYTES, n * 4).view(np.float32)
+            assert np.array_equal(pushed.view(np.uint32), y[0].cpu().numpy().reshape(-1).view(np.uint32))
+            assert _d2h(rt, bufs[1] + 64, 4).view(np.uint32)[0] == call
+            ctl = _d2h(rt, bufs[0], 8).view(np.uint32)
+            assert ctl[0] == call and ctl[1] == 0
+    finally:
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.b200q_tp_free(b)
+
+
+def test_row_parallel_shapes_without_fused_path_launch_nothing(ops):
+    L = _cabi.lib()
+    b, h = ctypes.c_void_p(), ctypes.create_string_buffer(_cabi.TP_HANDLE_BYTES)
+    _cabi.check(L.b200q_tp_alloc(ctypes.byref(b), h))
+    try:
+        table = (ctypes.c_void_p * 2)(b.value, b.value)
+        rng = synth.rng_for(42)
+        before = ops.launch_count()
+        for fmt, m, n, k in [("Q8_0", 1, 64, 256), ("Q4_K", 2, 64, 256), ("Q4_K", 1, 20000, 256), ("Q4_K", 1, 64, 8192)]:
+            w = QuantTensor.from_bytes(synth.weight_bytes(fmt, rng, n, k), QuantFormat.parse(fmt), (n, k), device="cuda")
+            act = torch.from_numpy(synth.activations(rng, m, k)).cuda()
+            assert ops.row_parallel_matmul(act, w, 0, 2, table) is None
+        assert ops.launch_count() == before
+    finally:
+        L.b200q_tp_free(b.value)

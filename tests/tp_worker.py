@@ -1,0 +1,58 @@
+"""One rank of the multi-GPU tensor-parallel check (started by test_gpu_tp_multi.py through
+torch.distributed.run).  Row-parallel decode products through the fused peer exchange are compared
+with the same products through NCCL's all-reduce, and with the unsharded product."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from boostr_b200 import ops, synth  # noqa: E402
+from boostr_b200.tensor import QuantTensor  # noqa: E402
+from boostr_b200.format import QuantFormat  # noqa: E402
+from boostr_b200.tensor_parallel import PeerExchange, RowParallelQuantLinear  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    ex = PeerExchange()
+    worst = 0.0
+    for case, (fmt, n, k) in enumerate([("Q4_K", 4096, 4096), ("Q6_K", 4096, 14336 // 8 * 8), ("Q6_K", 512, 2048 * world), ("Q4_K", 100, 1024 * world)]):
+        if (k // world) % 256:
+            continue
+        rng = synth.rng_for(77, case)  # same stream on every rank
+        full = synth.weight_bytes(fmt, rng, n, k)
+        fused = RowParallelQuantLinear.from_full(fmt, full, n, k, rank, world, exchange=ex)
+        plain = RowParallelQuantLinear(fused.weight)
+        whole = QuantTensor.from_bytes(full, QuantFormat.parse(fmt), (n, k), device="cuda")
+        for it in range(6):
+            act = synth.activations(rng, 1, k)
+            shard = torch.from_numpy(np.ascontiguousarray(act[:, rank * (k // world):(rank + 1) * (k // world)])).cuda()
+            y_fused = fused(shard).clone()
+            y_nccl = plain(shard)
+            y_one = ops.quant_matmul(torch.from_numpy(act).cuda(), whole)
+            ops.check_device_status()
+            scale = float(y_one.abs().max())
+            e1 = float((y_fused - y_nccl).abs().max()) / scale
+            e2 = float((y_fused - y_one).abs().max()) / scale
+            worst = max(worst, e1, e2)
+            # every rank must hold the same bits
+            gathered = [torch.empty_like(y_fused) for _ in range(world)]
+            dist.all_gather(gathered, y_fused)
+            for g in gathered:
+                assert torch.equal(g.view(torch.int32), y_fused.view(torch.int32)), "ranks disagree on the fused sum"
+            assert e1 <= 2e-6 and e2 <= 2e-6, (fmt, n, k, it, e1, e2)
+    ex.close()
+    if rank == 0:
+        print(f"TP_WORKER_OK world={world} worst_rel_err={worst:.3e}", flush=True)
+    dist.barrier()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
