@@ -126,80 +126,70 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 // ------------------------------------------------------------------- peer exchange (tensor parallel)
 // Row-parallel decode products end in an all-reduce of one f32 row.  Instead of a separate collective
-// the GEMV kernel pushes its partial row into EVERY rank's exchange buffer over NVLink (plain stores
-// to peer-mapped memory); the last CTA of each rank then raises that rank's flag on every peer, waits
-// (bounded) for all flags and adds the partial rows in rank order, so every rank stores the same bits.
+// the GEMV kernel pushes every element of its partial row into EVERY rank's exchange buffer over NVLink
+// as one 8-byte store {value bits, epoch}: the epoch travels with the value, so a reader that sees the
+// expected epoch has the value (8-byte stores arrive whole) and no fence, flag or barrier is needed.
+// Each CTA then collects, for ITS OWN rows, the P partial values (all ranks split the rows alike) and
+// adds them in rank order, so every rank stores the same bits.  Waits are bounded.
 //
 // Exchange buffer of a rank (TP_BUF_BYTES, zeroed at allocation):
-//   [0]   u32 epoch: number of exchanges completed by this rank (written by the last CTA)
-//   [4]   u32 count of local CTAs that finished pushing (reset by the last CTA)
-//   [64 + 64 r] u32 flag of rank r: the epoch whose partial row from r has fully arrived here
-//   [1024 + ((e & 1) * 8 + r) * 65536]  partial row of rank r for epoch e (up to 16384 f32)
-// Two parities suffice: a rank can start epoch e + 2 only after every peer signalled e + 1, which a
-// peer does after it finished reading epoch e.
+//   [0]   u32 epoch: number of exchanges completed by this rank (advanced by the CTA that finishes last)
+//   [4]   u32 count of local CTAs that finished (reset by the same CTA)
+//   [1024 + (((e & 1) * 8 + r) * 16384 + row) * 8]  {bits, e}: element `row` of rank r's partial row, epoch e
+// Two parities suffice: a rank can push epoch e + 2 only after it has collected e + 1 from every peer,
+// which a peer pushes after it finished collecting epoch e.
 constexpr uint32_t TP_MAX_WORLD = 8, TP_MAX_N = 16384;
-constexpr size_t TP_BUF_BYTES = 1024 + 2 * (size_t)TP_MAX_WORLD * TP_MAX_N * 4;
+constexpr size_t TP_BUF_BYTES = 1024 + 2 * (size_t)TP_MAX_WORLD * TP_MAX_N * 8;
 struct PeerComm {
     uint32_t world, rank;  // world <= 1: no exchange
     uint8_t* buf[TP_MAX_WORLD];
 };
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ size_t tp_slot(uint32_t e, uint32_t src, uint32_t row) {
+    return 1024 + (((size_t)(e & 1u) * TP_MAX_WORLD + src) * TP_MAX_N + row) * 8;
 }
 // epoch this launch takes part in (call after grid_dep_wait)
 __device__ __forceinline__ uint32_t tp_epoch(const PeerComm& c) {
     return *reinterpret_cast<volatile const uint32_t*>(c.buf[c.rank]) + 1u;
 }
 __device__ __forceinline__ void tp_push(const PeerComm& c, uint32_t e, uint32_t row, float v) {
-    const size_t off = 1024 + ((size_t)(e & 1u) * TP_MAX_WORLD + c.rank) * (TP_MAX_N * 4) + (size_t)row * 4;
-    for (uint32_t r = 0; r < c.world; ++r) *reinterpret_cast<float*>(c.buf[r] + off) = v;
+    const size_t off = tp_slot(e, c.rank, row);
+    const uint32_t bits = __float_as_uint(v);
+    for (uint32_t r = 0; r < c.world; ++r)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(c.buf[r] + off), "r"(bits), "r"(e) : "memory");
 }
-// Called by ALL threads of every CTA after its last tp_push.  `s_flag`: one u32 of shared memory.
-__device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_t n, float* out, unsigned int* status, uint32_t* s_flag) {
-    __syncthreads();  // every push of this CTA has been issued
-    uint32_t* ctl = reinterpret_cast<uint32_t*>(c.buf[c.rank]);
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        *s_flag = atomicAdd(ctl + 1, 1u) == gridDim.x - 1 ? 1u : 0u;
-    }
-    __syncthreads();
-    if (!*s_flag) return;
-    // last CTA of this rank: all local pushes are ordered before the flags raised here
-    bool ok = true;
-    if (threadIdx.x < c.world) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(c.buf[threadIdx.x] + 64 + 64 * c.rank), e);
-        const uint32_t* f = reinterpret_cast<const uint32_t*>(c.buf[c.rank] + 64 + 64 * threadIdx.x);
-        const bool broken = (*reinterpret_cast<volatile unsigned int*>(status) & STATUS_TIMEOUT_PEER) != 0;  // a peer was lost before
-        const uint64_t t0 = global_timer_ns();
-        while (!broken && (int32_t)(ld_acquire_sys(f) - e) < 0) {
-            if (global_timer_ns() - t0 > 1000000000ull) {
-                atomicOr(status, STATUS_TIMEOUT_PEER);
-                ok = false;
-                break;
+// Called by ALL threads of every CTA after its last tp_push: adds up rows [row_begin, row_end).
+__device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_t row_begin, uint32_t row_end, float* out,
+                                          unsigned int* status) {
+    bool lost = (*reinterpret_cast<volatile unsigned int*>(status) & STATUS_TIMEOUT_PEER) != 0;  // a peer was lost before
+    for (uint32_t row = row_begin + threadIdx.x; row < row_end; row += blockDim.x) {
+        float sum = 0.f;
+        for (uint32_t r = 0; r < c.world; ++r) {
+            const uint8_t* slot = c.buf[c.rank] + tp_slot(e, r, row);
+            uint32_t bits, tag;
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0;; ++spin) {
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(tag) : "l"(slot) : "memory");
+                if (tag == e || lost) break;
+                if ((spin & 63u) == 63u) {
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > 1000000000ull) {
+                        atomicOr(status, STATUS_TIMEOUT_PEER);
+                        lost = true;
+                    }
+                }
             }
+            sum = __fadd_rn(sum, __uint_as_float(bits));
         }
-        if (broken) ok = false;
-    }
-    ok = __syncthreads_and(ok);
-    if (ok) {
-        const uint8_t* base = c.buf[c.rank] + 1024 + (size_t)(e & 1u) * TP_MAX_WORLD * (TP_MAX_N * 4);
-        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-            float sum = 0.f;
-            for (uint32_t r = 0; r < c.world; ++r)
-                sum = __fadd_rn(sum, __ldcg(reinterpret_cast<const float*>(base + (size_t)r * (TP_MAX_N * 4)) + i));
-            out[i] = sum;
-        }
+        out[row] = sum;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        ctl[1] = 0;
-        ctl[0] = e;
+        uint32_t* ctl = reinterpret_cast<uint32_t*>(c.buf[c.rank]);
+        if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {  // the CTA that finishes last closes the epoch
+            ctl[1] = 0;
+            ctl[0] = e;
+        }
     }
 }
 

@@ -337,7 +337,7 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         }
     }
     TRACE1MAX(p.trace_idx, 6);
-    if (tp) tp_finish(p.comm, tp_e, p.N, static_cast<float*>(p.out[0]), p.status, reinterpret_cast<uint32_t*>(smem + 256));
+    if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out[0]), p.status);
 }
 
 template <bool SWIGLU>
@@ -587,7 +587,7 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
             par ^= 1;
         }
     }
-    if (tp) tp_finish(p.comm, tp_e, p.N, static_cast<float*>(p.out), p.status, reinterpret_cast<uint32_t*>(smem + 512));
+    if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out), p.status);
 }
 
 template <int NCHUNK>
@@ -631,7 +631,7 @@ static size_t setup_q6k(GemvM1Q6Params& p, uint32_t& nchunk, size_t& smem, const
     const uint32_t rpf = 4 / nchunk;
     p.row_bytes = p.nblk * 210;
     p.stage_bytes = (rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
-    p.act_off = 576;  // [0,256) barriers, [256,512) chunk-sum table, [512,576) exchange flag
+    p.act_off = 512;  // [0,256) barriers, [256,512) chunk-sum table
     p.stage_off = (p.act_off + p.nblk * ACT6_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off - 64) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
@@ -673,7 +673,7 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
     { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
 #endif
     p.stage_bytes = 8 * p.row_bytes;  // multiple of 128
-    p.act_off = 320;  // [0,256) barriers, [256,320) exchange flag
+    p.act_off = 256;  // [0,256) barriers
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;

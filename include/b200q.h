@@ -191,16 +191,17 @@ B200Q_API unsigned long long b200q_launch_count(void);
  *
  * Replaces, for decode (M = 1), the pair "local quant_matmul, then Communicator::all_reduce(Sum) and
  * sync" of RowParallelLinear::forward (src/distributed/tensor_parallel.rs:230-238, all_reduce_tensor in
- * src/distributed/comm_utils.rs:15-39) by ONE kernel: it pushes the local partial row into every
- * rank's exchange buffer with plain stores over NVLink, the last CTA raises this rank's flag on every
- * peer, waits (at most 1 s, then B200Q_ERR_TIMEOUT is reported by b200q_check_device_status) for all
- * flags and adds the partial rows in rank order, so all ranks store bit-identical sums.
+ * src/distributed/comm_utils.rs:15-39) by ONE kernel: it pushes every element of the local partial row
+ * into every rank's exchange buffer as one 8-byte store {value, epoch} over NVLink, and each CTA then
+ * collects the partial values of its own rows from all ranks (waiting at most 1 s for an element whose
+ * epoch has not arrived, then B200Q_ERR_TIMEOUT is reported by b200q_check_device_status) and adds them
+ * in rank order, so all ranks store bit-identical sums.
  *
  * Set-up, once per process: b200q_tp_alloc creates this rank's exchange buffer (cudaMalloc, zeroed) and
  * its 64-byte CUDA IPC handle; the handles are exchanged by whatever the host uses (boostr: its
  * Communicator's broadcast/all_gather of bytes); b200q_tp_open maps a peer's buffer.  `bufs[r]` is rank
  * r's buffer as seen from this process (own buffer at bufs[rank]).  All ranks must issue the same
- * sequence of b200q_row_parallel_matmul calls.  The buffers carry the exchange state (epoch, flags), so
+ * sequence of b200q_row_parallel_matmul calls.  The buffers carry the exchange state (the epoch), so
  * one set of buffers serves one stream of calls.
  *
  * Shapes without a fused path (M > 1, formats other than Q4_K/Q6_K, N > 16384, non-f32 output) return

@@ -1,10 +1,11 @@
 """Fused row-parallel decode product (b200q_row_parallel_matmul) on ONE GPU.
 
-Two exchange buffers are allocated on the same device and the peer's contribution (its partial row
-and its flag) is staged by the host before the launch, so the kernel's wait is satisfied at once and
-no kernel ever waits for another launch.  What is checked: the pushed partial row lands in the peer's
-buffer under the right parity, flags and epochs advance, the rank-ordered sum is bit-identical to the
-plain sum of the two partial products, over several consecutive calls (both parities).
+Two exchange buffers are allocated on the same device and the peer's contribution (its partial row,
+every element tagged with the epoch) is staged by the host before the launch, so the kernel's wait is
+satisfied at once and no kernel ever waits for another launch.  What is checked: the pushed partial
+row lands in the peer's buffer under the right parity and tag, the epoch advances, the rank-ordered sum
+is bit-identical to the plain sum of the two partial products, over several consecutive calls (both
+parities).
 """
 import ctypes
 
@@ -28,7 +29,7 @@ def ops():
 
 
 INBOX0 = 1024
-ROW_BYTES = 16384 * 4
+ROW_BYTES = 16384 * 8  # one partial row: 16384 slots of {f32 bits, epoch}
 
 
 def _cudart():
@@ -71,19 +72,21 @@ def test_row_parallel_exchange_against_staged_peer(ops, fmt, n, k):
             a = [torch.from_numpy(np.ascontiguousarray(act[:, r * (k // 2):(r + 1) * (k // 2)])).cuda() for r in range(2)]
             y = [ops.quant_matmul(a[r], shards[r]) for r in range(2)]
             torch.cuda.synchronize()
-            # stage rank 1's push into rank 0's buffer: its partial row, then its flag
+            # stage rank 1's push into rank 0's buffer: {value bits, epoch} per element
             par = call & 1
-            _h2d(rt, bufs[0] + INBOX0 + (par * 8 + 1) * ROW_BYTES, y[1].cpu().numpy().reshape(-1))
-            _h2d(rt, bufs[0] + 64 + 64 * 1, np.array([call], dtype=np.uint32))
+            staged = np.empty((n, 2), dtype=np.uint32)
+            staged[:, 0] = y[1].cpu().numpy().reshape(-1).view(np.uint32)
+            staged[:, 1] = call
+            _h2d(rt, bufs[0] + INBOX0 + (par * 8 + 1) * ROW_BYTES, staged)
             out = ops.row_parallel_matmul(a[0], shards[0], 0, 2, table)
             assert out is not None
             ops.check_device_status()
             want = (y[0] + y[1]).cpu().numpy()
             assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32)), f"call {call}"
-            # what rank 0 left behind: its row in the peer's inbox, its flag on both sides, its epoch
-            pushed = _d2h(rt, bufs[1] + INBOX0 + (par * 8 + 0) * ROW_BYTES, n * 4).view(np.float32)
-            assert np.array_equal(pushed.view(np.uint32), y[0].cpu().numpy().reshape(-1).view(np.uint32))
-            assert _d2h(rt, bufs[1] + 64, 4).view(np.uint32)[0] == call
+            # what rank 0 left behind: its tagged row in the peer's inbox, its epoch
+            pushed = _d2h(rt, bufs[1] + INBOX0 + (par * 8 + 0) * ROW_BYTES, n * 8).view(np.uint32).reshape(n, 2)
+            assert np.array_equal(pushed[:, 0], y[0].cpu().numpy().reshape(-1).view(np.uint32))
+            assert (pushed[:, 1] == call).all()
             ctl = _d2h(rt, bufs[0], 8).view(np.uint32)
             assert ctl[0] == call and ctl[1] == 0
     finally:
