@@ -8,10 +8,14 @@
 //     weights are decoded once per (128 x MT) output tile, so a larger MT amortises the decode.
 //   * activations are bf16 [M,K] (converted once from f32 when needed) and arrive by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring;
-//   * eight dequant warps (two threads per weight row, 32 elements each) read the packed blocks of
-//     their row for a 64-wide K step (one step ahead for Q4_K), decode them exactly in f32 (the same
-//     expressions as the dequant kernel), round once to bf16 and store into the K-major,
-//     128B-swizzled A tile of the stage;
+//   * two sets of eight dequant warps take the even and the odd K steps (64 wide); within a set two
+//     threads share a weight row, 32 elements each: they read the packed blocks of their row (one of
+//     their steps ahead for Q4_K), decode them exactly in f32 (the same expressions as the dequant
+//     kernel), round once to bf16 and store into the K-major, 128B-swizzled A tile of the stage;
+//   * Q4_K: the packed blocks themselves arrive by TMA as tiles of 128 rows x one 144-byte block (four
+//     K steps), double buffered.  When every thread fetched its own row's bytes with 16-byte global
+//     loads, a warp touched 32 different lines per instruction and the L1 data pipe (one wavefront per
+//     line) was 73 % busy with them: that, not the arithmetic, held the tensor pipe at 36 %;
 //   * one thread issues four 128 x MT x 16 tcgen05.mma per K step and commits the stage back to the
 //     producers through an mbarrier; after the last step it commits the accumulator to the epilogue;
 //   * the dequant warps then read the accumulator with tcgen05.ld (lane = weight row, columns =
@@ -35,7 +39,7 @@ struct PrefillParams {
     uint32_t mt;      // activation rows per tile (MMA N): 64, 128 or 256
     uint32_t idesc;   // tcgen05 instruction descriptor
     uint32_t nkt;     // K / 64
-    uint32_t nstages;
+    uint32_t nsa, nsb;  // ring depth of the weight (A) tiles and of the activation (B) tiles
     int out_dtype;
     unsigned int* status;
 };
@@ -44,7 +48,9 @@ namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int A_TILE_BYTES = 128 * BK * 2;
-constexpr int PF_MAX_STAGES = 6;
+constexpr int PF_MAX_STAGES = 8;
+constexpr int RAW_TILE_BYTES = 128 * 144;  // Q4_K: 128 rows x one block, row pitch 144 B (conflict-free 16-byte reads)
+constexpr int PF_THREADS = 19 * 32;        // 16 dequant warps, activation TMA, MMA issue, packed-weight TMA
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -99,16 +105,15 @@ __device__ __forceinline__ float byte_to_float(uint32_t x) {
     return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 | I)) - 8388608.0f;
 }
 
-// Raw bytes a thread needs for 32 elements of a Q4_K row (prefetched one K step ahead).
+// Raw bytes a thread needs for 32 elements of a Q4_K row.
 struct RawQ4K {
     uint4 hd, q0, q1;
 };
-__device__ __forceinline__ RawQ4K load_raw_q4k(const uint8_t* row, uint32_t kt) {
-    const uint8_t* blk = row + (kt >> 2) * 144;
+__device__ __forceinline__ RawQ4K load_raw_q4k_smem(const uint8_t* blk, uint32_t kt) {
     RawQ4K r;
-    r.hd = __ldg(reinterpret_cast<const uint4*>(blk));
-    r.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kt & 3)));
-    r.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (kt & 3)));
+    r.hd = *reinterpret_cast<const uint4*>(blk);
+    r.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (kt & 3));
+    r.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (kt & 3));
     return r;
 }
 // Elements [64*kt + 32*half, +32) of a Q4_K row: sub-block 2*(kt&3) + half (low / high nibbles of the
@@ -183,36 +188,52 @@ __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32
     }
 }
 
-// dynamic shared memory: [0,1024) barriers + TMEM base; then nstages x (A tile 16 KB | B tile mt*128 B), 1 KB aligned
-constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY = 128, PF_OFF_ACC = 192, PF_OFF_TMEM = 200, PF_OFF_DEAD = 204;
+// dynamic shared memory: [0,1024) barriers + TMEM base; then nsa A tiles of 16 KB, then nsb B tiles of mt*128 B, 1 KB aligned.
+// The two rings are separate because they hide different latencies: an activation tile is requested
+// from L2 when its slot is released (the ring must cover that round trip at the full MMA rate: 5 slots
+// at mt = 256), a weight tile is written by the dequant warps just in time.
+constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OFF_EMPTY_B = 192, PF_OFF_ACC = 256, PF_OFF_TMEM = 264,
+              PF_OFF_DEAD = 268, PF_OFF_FULL_RAW = 272, PF_OFF_EMPTY_RAW = 288;
 
 template <int FMT>
-__global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act, const PrefillParams p) {
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
+                                                                const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
+    constexpr bool RAW_TMA = FMT == FMT_Q4_K;  // packed weights staged in shared memory by TMA
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B, bar_empty = sbase + PF_OFF_EMPTY;
+    const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B;
+    const uint32_t bar_empty_a = sbase + PF_OFF_EMPTY_A, bar_empty_b = sbase + PF_OFF_EMPTY_B;
     const uint32_t bar_acc = sbase + PF_OFF_ACC;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_TMEM);
     volatile uint32_t* dead_flag = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_DEAD);
-    const uint32_t stage_bytes = A_TILE_BYTES + p.mt * 128;
-    const uint32_t tiles0 = sbase + 1024;
+    const uint32_t bar_full_raw = sbase + PF_OFF_FULL_RAW, bar_empty_raw = sbase + PF_OFF_EMPTY_RAW;
+    const uint32_t b_tile_bytes = p.mt * 128;
+    const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;  // two packed-weight tiles ahead of the A ring
+    const uint32_t raw_tiles = sbase + 1024, a_tiles = raw_tiles + raw_bytes, b_tiles = a_tiles + p.nsa * A_TILE_BYTES;
     const uint32_t n0 = blockIdx.x * 128, m0 = blockIdx.y * p.mt;
     const uint32_t tmem_cols = p.mt < 32 ? 32 : p.mt;  // power of two by construction (64/128/256)
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full_a + 8 * s, 256);
+        for (uint32_t s = 0; s < p.nsa; ++s) {
+            mbar_init(bar_full_a + 8 * s, 8);  // one arrival per warp of the set that wrote the tile
+            mbar_init(bar_empty_a + 8 * s, 1);
+        }
+        for (uint32_t s = 0; s < p.nsb; ++s) {
             mbar_init(bar_full_b + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_empty_b + 8 * s, 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar_full_raw + 8 * s, 1);
+            mbar_init(bar_empty_raw + 8 * s, 16);  // every dequant warp reads every packed tile
         }
         mbar_init(bar_acc, 1);
         *dead_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 9) {  // tensor-memory columns for the accumulator, allocated by one whole warp
+    if (warp == 17) {  // tensor-memory columns for the accumulator, allocated by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + PF_OFF_TMEM), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -221,59 +242,88 @@ __global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_holder;
 
-    if (warp == 8) {
+    if (warp == 18) {
+        // ------------------------------------------------------------ packed weight tiles by TMA (Q4_K)
+        if (RAW_TMA && lane == 0) {
+            const uint32_t nblk = (p.nkt + 3) / 4;
+            uint32_t s = 0, par = 0;
+            for (uint32_t j = 0; j < nblk; ++j) {
+                if (*dead_flag) break;
+                if (!mbar_wait(bar_empty_raw + 8 * s, par ^ 1)) {
+                    *dead_flag = 1;
+                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
+                tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * 144), (int)n0, bar_full_raw + 8 * s);
+                if (++s == 2) { s = 0; par ^= 1; }
+            }
+        }
+    } else if (warp == 16) {
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             uint32_t s = 0, par = 0;
             for (uint32_t kt = 0; kt < p.nkt; ++kt) {
                 if (*dead_flag) break;
-                if (!mbar_wait(bar_empty + 8 * s, par ^ 1)) {
+                if (!mbar_wait(bar_empty_b + 8 * s, par ^ 1)) {
                     *dead_flag = 1;
                     atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                     break;
                 }
-                mbar_expect_tx(bar_full_b + 8 * s, p.mt * 128);
-                tma_load_2d(tiles0 + s * stage_bytes + A_TILE_BYTES, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
-                if (++s == p.nstages) { s = 0; par ^= 1; }
+                mbar_expect_tx(bar_full_b + 8 * s, b_tile_bytes);
+                tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
+                if (++s == p.nsb) { s = 0; par ^= 1; }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
-            uint32_t s = 0, par = 0;
+            uint32_t sa = 0, para = 0, sb = 0, parb = 0;
             bool ok = true;
             for (uint32_t kt = 0; kt < p.nkt && ok; ++kt) {
-                if (*dead_flag || !mbar_wait(bar_full_a + 8 * s, par) || !mbar_wait(bar_full_b + 8 * s, par)) {
+                if (*dead_flag || !mbar_wait(bar_full_a + 8 * sa, para) || !mbar_wait(bar_full_b + 8 * sb, parb)) {
                     if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
                     *dead_flag = 1;
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = tiles0 + s * stage_bytes, b_addr = a_addr + A_TILE_BYTES;
+                const uint32_t a_addr = a_tiles + sa * A_TILE_BYTES, b_addr = b_tiles + sb * b_tile_bytes;
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
                     tc_mma_bf16(tmem_acc, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
-                tc_commit(bar_empty + 8 * s);  // the stage may be overwritten once these MMAs have read it
-                if (++s == p.nstages) { s = 0; par ^= 1; }
+                // both tiles may be overwritten once these MMAs have read them
+                tc_commit(bar_empty_a + 8 * sa);
+                tc_commit(bar_empty_b + 8 * sb);
+                if (++sa == p.nsa) { sa = 0; para ^= 1; }
+                if (++sb == p.nsb) { sb = 0; parb ^= 1; }
             }
             tc_commit(bar_acc);  // arrives when every MMA issued above has completed (at once if none were)
         }
     } else {
         // ------------------------------------------------------------ dequant warps, then epilogue
-        // thread (r, half): weight row r of the tile (= TMEM lane), elements [32*half, 32*half+32) of the K step
-        const uint32_t r = threadIdx.x & 127, half = threadIdx.x >> 7;
+        // thread (set, half, r): weight row r of the tile (= TMEM lane), elements [32*half, 32*half+32) of
+        // the K steps kt = set, set + 2, ...
+        const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
         const bool row_ok = n0 + r < p.N;
         const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
-        uint32_t s = 0, par = 0;
+        uint32_t s = set % p.nsa, par = 0;  // nsa >= 2 whenever there are two K steps
         bool ok = true;
-        RawQ4K raw;
-        if constexpr (FMT == FMT_Q4_K) raw = load_raw_q4k(wrow, 0);
-        for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+        for (uint32_t kt = set; kt < p.nkt; kt += 2) {
             uint32_t o[16];
-            if constexpr (FMT == FMT_Q4_K) {
-                const RawQ4K cur = raw;
-                if (kt + 1 < p.nkt) raw = load_raw_q4k(wrow, kt + 1);  // next step's bytes are in flight while this one is decoded
+            if constexpr (RAW_TMA) {
+                const uint32_t j = kt >> 2, rs = j & 1;  // packed tile j covers K steps 4j .. 4j+3
+                if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (j >> 1) & 1))) {
+                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                    *dead_flag = 1;
+                    ok = false;
+                }
+                RawQ4K cur{};
+                if (ok) cur = load_raw_q4k_smem(smem + 1024 + rs * RAW_TILE_BYTES + r * 144, kt);
+                if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != j) {  // this set's last step in the tile: release it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                }
                 decode32_q4k(cur, kt, half, o);
             } else {
                 decode32<FMT>(wrow, kt, half, o);
@@ -281,13 +331,13 @@ __global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__
             if (!row_ok)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) o[i] = 0;
-            if (ok && (*dead_flag || !mbar_wait(bar_empty + 8 * s, par ^ 1))) {
+            if (ok && (*dead_flag || !mbar_wait(bar_empty_a + 8 * s, par ^ 1))) {
                 if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                 *dead_flag = 1;
                 ok = false;
             }
             if (ok) {
-                uint8_t* arow = smem + 1024 + s * stage_bytes + r * 128;
+                uint8_t* arow = smem + 1024 + raw_bytes + s * A_TILE_BYTES + r * 128;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
                     const uint32_t cc = 4 * half + c;
@@ -295,11 +345,16 @@ __global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__
                 }
                 fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
             }
-            mbar_arrive(bar_full_a + 8 * s);
-            if (++s == p.nstages) { s = 0; par ^= 1; }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+            s += 2;
+            if (s >= p.nsa) {
+                s -= p.nsa;
+                par ^= 1;
+            }
         }
         // epilogue: accumulator lane r = weight row n0 + r, column c = activation row m0 + c;
-        // warps 0-3 take the first half of the columns, warps 4-7 the second half
+        // a warp reaches the 32 lanes of its quarter (warp & 3); the four warps of a quarter split the columns
         if (ok && !mbar_wait(bar_acc, 0)) {
             atomicOr(p.status, STATUS_TIMEOUT_MMA);
             *dead_flag = 1;
@@ -307,7 +362,7 @@ __global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__
         }
         tc_fence_after();
         if (ok && !*dead_flag) {
-            const uint32_t cbeg = half * (p.mt / 2), cend = cbeg + p.mt / 2;
+            const uint32_t cbeg = ((uint32_t)warp >> 2) * (p.mt / 4), cend = cbeg + p.mt / 4;
             for (uint32_t c0 = cbeg; c0 < cend; c0 += 16) {
                 if (m0 + c0 >= p.M) break;  // warp-uniform
                 uint32_t v[16];
@@ -330,7 +385,7 @@ __global__ void __launch_bounds__(320, 1) prefill_kernel(const __grid_constant__
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 17) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
     }
@@ -414,7 +469,7 @@ EncodeTiledFn encode_tiled() {
 uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
 
 template <int FMT>
-cudaError_t launch_fmt(const CUtensorMap& map, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -423,7 +478,7 @@ cudaError_t launch_fmt(const CUtensorMap& map, const PrefillParams& p, dim3 grid
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    prefill_kernel<FMT><<<grid, 320, smem, st>>>(map, p);
+    prefill_kernel<FMT><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
     note_launch();
     return cudaGetLastError();
 }
@@ -483,14 +538,19 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.mt = pick_mt(M);
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.mt >> 3) << 17) | ((128u >> 4) << 24);  // f32 acc, bf16 x bf16, K-major, N = mt, M = 128
     p.nkt = (uint32_t)(K / BK);
-    const uint32_t stage_bytes = A_TILE_BYTES + p.mt * 128;
-    uint32_t ns = (232448 - 1024 - 2048) / stage_bytes;
-    if (ns > (uint32_t)PF_MAX_STAGES) ns = PF_MAX_STAGES;
-    if (ns > p.nkt) ns = p.nkt;
-    p.nstages = ns;
+    const uint32_t raw_bytes = fmt == FMT_Q4_K ? 2 * RAW_TILE_BYTES : 0;
+    // the formats that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
+    const uint32_t budget = (fmt == FMT_Q4_K ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
+    uint32_t nsa = 4, nsb = (budget - nsa * A_TILE_BYTES) / b_tile;
+    if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
+    { const char* e = getenv("B200Q_PF_NSB"); if (e && atoi(e) >= 2 && (uint32_t)atoi(e) < nsb) nsb = atoi(e); }
+    if (nsa > p.nkt) nsa = p.nkt;
+    if (nsb > p.nkt) nsb = p.nkt;
+    p.nsa = nsa;
+    p.nsb = nsb;
     p.out_dtype = out_dtype;
     p.status = status;
-    const size_t smem = 2048 + (size_t)ns * stage_bytes;
+    const size_t smem = 2048 + raw_bytes + (size_t)nsa * A_TILE_BYTES + (size_t)nsb * b_tile;
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -504,12 +564,25 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
         snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (activation pointer %p, K=%zu, M=%zu)", (int)cr, act_bf16, K, M);
         return cudaErrorInvalidValue;
     }
+    // packed weights as a byte matrix [N, row_bytes]: tiles of 128 rows x one 144-byte Q4_K block
+    CUtensorMap wmap = map;
+    if (fmt == FMT_Q4_K) {
+        const cuuint64_t wdim[2] = {(cuuint64_t)p.row_bytes, (cuuint64_t)N};
+        const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
+        const cuuint32_t wbox[2] = {144, 128};
+        cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (weight pointer %p, row bytes %u, N=%zu)", (int)cr, w, p.row_bytes, N);
+            return cudaErrorInvalidValue;
+        }
+    }
     dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + p.mt - 1) / p.mt), 1);
     switch (fmt) {
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(map, p, grid, smem, st);
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(map, p, grid, smem, st);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(map, p, grid, smem, st);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(map, p, grid, smem, st);
+    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(map, wmap, p, grid, smem, st);
+    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(map, wmap, p, grid, smem, st);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(map, wmap, p, grid, smem, st);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(map, wmap, p, grid, smem, st);
     default: return cudaErrorInvalidValue;
     }
 }
