@@ -6,20 +6,24 @@
 //   * orientation: the WEIGHT tile is the MMA's A operand (128 weight rows = the 128 TMEM lanes), the
 //     ACTIVATION tile is the B operand (MT = 64/128/256 activation rows = TMEM columns).  The packed
 //     weights are decoded once per (128 x MT) output tile, so a larger MT amortises the decode.
-//   * activations are bf16 [M,K] (converted once from f32 when needed) and arrive by TMA
-//     (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) into a 4-stage ring;
+//   * persistent: one CTA per SM walks the output tiles; tensor memory holds TWO accumulators, so four
+//     epilogue warps drain tile i (tcgen05.ld: lane = weight row, columns = activation rows; out[m, n]
+//     stored with n contiguous across lanes) while the MMA warp already accumulates tile i + 1;
+//   * activations are bf16 [M,K] (prepared once per call) and arrive by TMA (cp.async.bulk.tensor.2d,
+//     128-byte swizzle, no multicast) into their own ring;
 //   * two sets of eight dequant warps take the even and the odd K steps (64 wide); within a set two
-//     threads share a weight row, 32 elements each: they read the packed blocks of their row (one of
-//     their steps ahead for Q4_K), decode them exactly in f32 (the same expressions as the dequant
-//     kernel), round once to bf16 and store into the K-major, 128B-swizzled A tile of the stage;
+//     threads share a weight row, 32 elements each: they decode the packed blocks exactly in f32 (the
+//     same expressions as the dequant kernel), round once to bf16 and store into the K-major,
+//     128B-swizzled A tile of the step;
 //   * Q4_K: the packed blocks themselves arrive by TMA as tiles of 128 rows x one 144-byte block (four
-//     K steps), double buffered.  When every thread fetched its own row's bytes with 16-byte global
-//     loads, a warp touched 32 different lines per instruction and the L1 data pipe (one wavefront per
-//     line) was 73 % busy with them: that, not the arithmetic, held the tensor pipe at 36 %;
-//   * one thread issues four 128 x MT x 16 tcgen05.mma per K step and commits the stage back to the
-//     producers through an mbarrier; after the last step it commits the accumulator to the epilogue;
-//   * the dequant warps then read the accumulator with tcgen05.ld (lane = weight row, columns =
-//     activation rows) and store out[m, n] with n contiguous across lanes.
+//     K steps), double buffered, and are read from shared memory with conflict-free 16-byte loads
+//     (per-thread 16-byte global loads touch 32 lines per warp instruction; they kept the L1 data pipe
+//     73 % busy);
+//   * one thread issues four 128 x MT x 16 tcgen05.mma per K step and commits the A and B slots back to
+//     their producers through mbarriers; after the last step it commits the accumulator to the epilogue.
+// Measured (M = 8192, N = 14336, K = 4096): 814 TFLOP/s; with the decode arithmetic and the tile stores
+// switched off the same pipeline reaches 980 TFLOP/s, cuBLAS bf16 on the same shape 1455 TFLOP/s, so
+// the single-CTA (cta_group::1) pipeline itself, not the decode, is the larger part of the gap.
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code, skips the work that
 // depended on the wait and still frees its tensor memory.
 #include <cuda.h>
@@ -40,8 +44,10 @@ struct PrefillParams {
     uint32_t idesc;   // tcgen05 instruction descriptor
     uint32_t nkt;     // K / 64
     uint32_t nsa, nsb;  // ring depth of the weight (A) tiles and of the activation (B) tiles
+    uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
     int out_dtype;
     unsigned int* status;
+    uint32_t dbg;  // debug builds only: phases switched off for timing experiments
 };
 
 namespace {
@@ -50,7 +56,7 @@ constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle r
 constexpr int A_TILE_BYTES = 128 * BK * 2;
 constexpr int PF_MAX_STAGES = 8;
 constexpr int RAW_TILE_BYTES = 128 * 144;  // Q4_K: 128 rows x one block, row pitch 144 B (conflict-free 16-byte reads)
-constexpr int PF_THREADS = 19 * 32;        // 16 dequant warps, activation TMA, MMA issue, packed-weight TMA
+constexpr int PF_THREADS = 23 * 32;  // warps 0-15 dequant | 16 activation TMA | 17 MMA issue, TMEM | 18 packed-weight TMA | 19-22 epilogue
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -188,13 +194,16 @@ __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32
     }
 }
 
-// dynamic shared memory: [0,1024) barriers + TMEM base; then nsa A tiles of 16 KB, then nsb B tiles of mt*128 B, 1 KB aligned.
-// The two rings are separate because they hide different latencies: an activation tile is requested
-// from L2 when its slot is released (the ring must cover that round trip at the full MMA rate: 5 slots
-// at mt = 256), a weight tile is written by the dequant warps just in time.
-constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OFF_EMPTY_B = 192, PF_OFF_ACC = 256, PF_OFF_TMEM = 264,
-              PF_OFF_DEAD = 268, PF_OFF_FULL_RAW = 272, PF_OFF_EMPTY_RAW = 288;
+// dynamic shared memory: [0,1024) barriers + TMEM base; then two packed-weight tiles (Q4_K), nsa A tiles of 16 KB,
+// nsb B tiles of mt*128 B, all 1 KB aligned.  The A and B rings are separate because they hide different latencies:
+// an activation tile is requested from L2 when its slot is released, a weight tile is written by the dequant warps
+// just in time.
+constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OFF_EMPTY_B = 192, PF_OFF_ACC_FULL = 256,
+              PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 296, PF_OFF_EMPTY_RAW = 312;
 
+// Persistent: one CTA per SM walks the output tiles t = blockIdx.x, + gridDim.x, ... (consecutive CTAs share an
+// activation tile, which therefore stays in L2).  Tensor memory holds TWO accumulators, so the four epilogue warps
+// drain tile i while the MMA warp is already accumulating tile i + 1 and the rings never run dry between tiles.
 template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
@@ -206,15 +215,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B;
     const uint32_t bar_empty_a = sbase + PF_OFF_EMPTY_A, bar_empty_b = sbase + PF_OFF_EMPTY_B;
-    const uint32_t bar_acc = sbase + PF_OFF_ACC;
+    const uint32_t bar_acc_full = sbase + PF_OFF_ACC_FULL, bar_acc_empty = sbase + PF_OFF_ACC_EMPTY;
+    const uint32_t bar_full_raw = sbase + PF_OFF_FULL_RAW, bar_empty_raw = sbase + PF_OFF_EMPTY_RAW;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_TMEM);
     volatile uint32_t* dead_flag = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_DEAD);
-    const uint32_t bar_full_raw = sbase + PF_OFF_FULL_RAW, bar_empty_raw = sbase + PF_OFF_EMPTY_RAW;
     const uint32_t b_tile_bytes = p.mt * 128;
-    const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;  // two packed-weight tiles ahead of the A ring
+    const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;
     const uint32_t raw_tiles = sbase + 1024, a_tiles = raw_tiles + raw_bytes, b_tiles = a_tiles + p.nsa * A_TILE_BYTES;
-    const uint32_t n0 = blockIdx.x * 128, m0 = blockIdx.y * p.mt;
-    const uint32_t tmem_cols = p.mt < 32 ? 32 : p.mt;  // power of two by construction (64/128/256)
+    const uint32_t tmem_cols = 2 * p.mt;  // two accumulators of mt columns: 128, 256 or 512 (a power of two)
+    const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nsa; ++s) {
@@ -228,12 +237,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(bar_full_raw + 8 * s, 1);
             mbar_init(bar_empty_raw + 8 * s, 16);  // every dequant warp reads every packed tile
+            mbar_init(bar_acc_full + 8 * s, 1);
+            mbar_init(bar_acc_empty + 8 * s, 4);   // the four epilogue warps
         }
-        mbar_init(bar_acc, 1);
         *dead_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 17) {  // tensor-memory columns for the accumulator, allocated by one whole warp
+    if (warp == 17) {  // tensor-memory columns for the accumulators, allocated by one whole warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + PF_OFF_TMEM), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -245,128 +255,102 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     if (warp == 18) {
         // ------------------------------------------------------------ packed weight tiles by TMA (Q4_K)
         if (RAW_TMA && lane == 0) {
-            const uint32_t nblk = (p.nkt + 3) / 4;
             uint32_t s = 0, par = 0;
-            for (uint32_t j = 0; j < nblk; ++j) {
-                if (*dead_flag) break;
-                if (!mbar_wait(bar_empty_raw + 8 * s, par ^ 1)) {
-                    *dead_flag = 1;
-                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    break;
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+                const uint32_t n0 = (tile % p.ntn) * 128;
+                for (uint32_t j = 0; j < nraw; ++j) {
+                    if (*dead_flag) break;
+                    if (!mbar_wait(bar_empty_raw + 8 * s, par ^ 1)) {
+                        *dead_flag = 1;
+                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                        break;
+                    }
+                    mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * 144), (int)n0, bar_full_raw + 8 * s);
+                    if (++s == 2) { s = 0; par ^= 1; }
                 }
-                mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
-                tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * 144), (int)n0, bar_full_raw + 8 * s);
-                if (++s == 2) { s = 0; par ^= 1; }
+                if (*dead_flag) break;
             }
         }
     } else if (warp == 16) {
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             uint32_t s = 0, par = 0;
-            for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                if (*dead_flag) break;
-                if (!mbar_wait(bar_empty_b + 8 * s, par ^ 1)) {
-                    *dead_flag = 1;
-                    atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    break;
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+                const uint32_t m0 = (tile / p.ntn) * p.mt;
+                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                    if (*dead_flag) break;
+                    if (!mbar_wait(bar_empty_b + 8 * s, par ^ 1)) {
+                        *dead_flag = 1;
+                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                        break;
+                    }
+                    mbar_expect_tx(bar_full_b + 8 * s, b_tile_bytes);
+                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
+                    if (++s == p.nsb) { s = 0; par ^= 1; }
                 }
-                mbar_expect_tx(bar_full_b + 8 * s, b_tile_bytes);
-                tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
-                if (++s == p.nsb) { s = 0; par ^= 1; }
+                if (*dead_flag) break;
             }
         }
     } else if (warp == 17) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
-            uint32_t sa = 0, para = 0, sb = 0, parb = 0;
+            uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
             bool ok = true;
-            for (uint32_t kt = 0; kt < p.nkt && ok; ++kt) {
-                if (*dead_flag || !mbar_wait(bar_full_a + 8 * sa, para) || !mbar_wait(bar_full_b + 8 * sb, parb)) {
-                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, u = it >> 1;
+                // the accumulator must have been drained by the epilogue of two tiles ago
+                if (u > 0 && (*dead_flag || !mbar_wait(bar_acc_empty + 8 * acc, (u - 1) & 1))) {
+                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                     *dead_flag = 1;
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = a_tiles + sa * A_TILE_BYTES, b_addr = b_tiles + sb * b_tile_bytes;
+                const uint32_t d_tmem = tmem_acc + acc * p.mt;
+                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                    if (*dead_flag || !mbar_wait(bar_full_a + 8 * sa, para) || !mbar_wait(bar_full_b + 8 * sb, parb)) {
+                        if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                        *dead_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = a_tiles + sa * A_TILE_BYTES, b_addr = b_tiles + sb * b_tile_bytes;
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)
-                    tc_mma_bf16(tmem_acc, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
-                // both tiles may be overwritten once these MMAs have read them
-                tc_commit(bar_empty_a + 8 * sa);
-                tc_commit(bar_empty_b + 8 * sb);
-                if (++sa == p.nsa) { sa = 0; para ^= 1; }
-                if (++sb == p.nsb) { sb = 0; parb ^= 1; }
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_bf16(d_tmem, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
+                    // both tiles may be overwritten once these MMAs have read them
+                    tc_commit(bar_empty_a + 8 * sa);
+                    tc_commit(bar_empty_b + 8 * sb);
+                    if (++sa == p.nsa) { sa = 0; para ^= 1; }
+                    if (++sb == p.nsb) { sb = 0; parb ^= 1; }
+                }
+                if (ok) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
             }
-            tc_commit(bar_acc);  // arrives when every MMA issued above has completed (at once if none were)
         }
-    } else {
-        // ------------------------------------------------------------ dequant warps, then epilogue
-        // thread (set, half, r): weight row r of the tile (= TMEM lane), elements [32*half, 32*half+32) of
-        // the K steps kt = set, set + 2, ...
-        const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
-        const bool row_ok = n0 + r < p.N;
-        const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
-        uint32_t s = set % p.nsa, par = 0;  // nsa >= 2 whenever there are two K steps
+    } else if (warp >= 19) {
+        // ------------------------------------------------------------ epilogue: accumulator -> out[m, n]
+        // lane r of the accumulator = weight row n0 + r, column c = activation row m0 + c; a warp reaches the
+        // 32 lanes of its quarter (warp & 3)
+        const uint32_t quarter = (uint32_t)warp & 3, r = quarter * 32 + lane;
+        uint32_t it = 0;
         bool ok = true;
-        for (uint32_t kt = set; kt < p.nkt; kt += 2) {
-            uint32_t o[16];
-            if constexpr (RAW_TMA) {
-                const uint32_t j = kt >> 2, rs = j & 1;  // packed tile j covers K steps 4j .. 4j+3
-                if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (j >> 1) & 1))) {
-                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                    *dead_flag = 1;
-                    ok = false;
-                }
-                RawQ4K cur{};
-                if (ok) cur = load_raw_q4k_smem(smem + 1024 + rs * RAW_TILE_BYTES + r * 144, kt);
-                if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != j) {  // this set's last step in the tile: release it
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
-                }
-                decode32_q4k(cur, kt, half, o);
-            } else {
-                decode32<FMT>(wrow, kt, half, o);
-            }
-            if (!row_ok)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) o[i] = 0;
-            if (ok && (*dead_flag || !mbar_wait(bar_empty_a + 8 * s, par ^ 1))) {
-                if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+        for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, u = it >> 1;
+            const uint32_t n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt;
+            if (*dead_flag || !mbar_wait(bar_acc_full + 8 * acc, u & 1)) {
+                if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_MMA);
                 *dead_flag = 1;
                 ok = false;
+                break;
             }
-            if (ok) {
-                uint8_t* arow = smem + 1024 + raw_bytes + s * A_TILE_BYTES + r * 128;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
-                    const uint32_t cc = 4 * half + c;
-                    *reinterpret_cast<uint4*>(arow + ((cc ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-                }
-                fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
-            s += 2;
-            if (s >= p.nsa) {
-                s -= p.nsa;
-                par ^= 1;
-            }
-        }
-        // epilogue: accumulator lane r = weight row n0 + r, column c = activation row m0 + c;
-        // a warp reaches the 32 lanes of its quarter (warp & 3); the four warps of a quarter split the columns
-        if (ok && !mbar_wait(bar_acc, 0)) {
-            atomicOr(p.status, STATUS_TIMEOUT_MMA);
-            *dead_flag = 1;
-            ok = false;
-        }
-        tc_fence_after();
-        if (ok && !*dead_flag) {
-            const uint32_t cbeg = ((uint32_t)warp >> 2) * (p.mt / 4), cend = cbeg + p.mt / 4;
-            for (uint32_t c0 = cbeg; c0 < cend; c0 += 16) {
+            tc_fence_after();
+            const bool row_ok = n0 + r < p.N;
+            for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
                 if (m0 + c0 >= p.M) break;  // warp-uniform
                 uint32_t v[16];
-                tmem_ld16(tmem_acc + ((uint32_t)((warp & 3) * 32) << 16) + c0, v);
+                tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
                 if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -381,9 +365,75 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
         }
-        tc_fence_before();
+    } else {
+        // ------------------------------------------------------------ dequant warps
+        // thread (set, half, r): weight row r of the tile, elements [32*half, 32*half+32) of the K steps
+        // kt = set, set + 2, ... of every tile
+        const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
+        bool ok = true;
+        uint32_t it = 0;
+        for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
+            const uint32_t n0 = (tile % p.ntn) * 128;
+            const bool row_ok = n0 + r < p.N;
+            const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
+            for (uint32_t kt = set; kt < p.nkt; kt += 2) {
+                uint32_t o[16];
+                if constexpr (RAW_TMA) {
+                    const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
+                    if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1))) {
+                        if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
+                        *dead_flag = 1;
+                        ok = false;
+                    }
+                    RawQ4K cur{};
+                    if (ok) cur = load_raw_q4k_smem(smem + 1024 + rs * RAW_TILE_BYTES + r * 144, kt);
+                    if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {  // this set's last step in the tile: release it
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                    }
+#ifdef B200Q_TRACE
+                    if (p.dbg & 1) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = cur.q0.x;
+                    } else
+#endif
+                    decode32_q4k(cur, kt, half, o);
+                } else {
+                    decode32<FMT>(wrow, kt, half, o);
+                }
+                if (!row_ok)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = 0;
+                const uint32_t gk = it * p.nkt + kt;  // position in the stream of K steps the MMA warp consumes
+                const uint32_t s = gk % p.nsa, par = (gk / p.nsa) & 1;
+                if (ok && (*dead_flag || !mbar_wait(bar_empty_a + 8 * s, par ^ 1))) {
+                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    *dead_flag = 1;
+                    ok = false;
+                }
+#ifdef B200Q_TRACE
+                if (ok && !(p.dbg & 2)) {
+#else
+                if (ok) {
+#endif
+                    uint8_t* arow = smem + 1024 + raw_bytes + s * A_TILE_BYTES + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
+                        const uint32_t cc = 4 * half + c;
+                        *reinterpret_cast<uint4*>(arow + ((cc ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                    }
+                    fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+            }
+        }
     }
+    tc_fence_before();
     __syncthreads();
     if (warp == 17) {
         tc_fence_after();
@@ -541,15 +591,26 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     const uint32_t raw_bytes = fmt == FMT_Q4_K ? 2 * RAW_TILE_BYTES : 0;
     // the formats that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (fmt == FMT_Q4_K ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
-    uint32_t nsa = 4, nsb = (budget - nsa * A_TILE_BYTES) / b_tile;
+    uint32_t nsa = 4;
+#ifdef B200Q_TRACE
+    { const char* e = getenv("B200Q_PF_NSA"); if (e && atoi(e) >= 2 && atoi(e) <= 8) nsa = atoi(e); }
+#endif
+    uint32_t nsb = (budget - nsa * A_TILE_BYTES) / b_tile;
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
+#ifdef B200Q_TRACE
     { const char* e = getenv("B200Q_PF_NSB"); if (e && atoi(e) >= 2 && (uint32_t)atoi(e) < nsb) nsb = atoi(e); }
+#endif
     if (nsa > p.nkt) nsa = p.nkt;
     if (nsb > p.nkt) nsb = p.nkt;
     p.nsa = nsa;
     p.nsb = nsb;
+    p.ntn = (uint32_t)((N + 127) / 128);
+    p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
     p.out_dtype = out_dtype;
     p.status = status;
+#ifdef B200Q_TRACE
+    { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
+#endif
     const size_t smem = 2048 + raw_bytes + (size_t)nsa * A_TILE_BYTES + (size_t)nsb * b_tile;
 
     CUtensorMap map;
@@ -577,7 +638,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
             return cudaErrorInvalidValue;
         }
     }
-    dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + p.mt - 1) / p.mt), 1);
+    dim3 grid(p.ntiles < (uint32_t)sm_count ? p.ntiles : (uint32_t)sm_count, 1, 1);
     switch (fmt) {
     case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(map, wmap, p, grid, smem, st);
     case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(map, wmap, p, grid, smem, st);
