@@ -162,25 +162,34 @@ __device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_
                                           unsigned int* status) {
     bool lost = (*reinterpret_cast<volatile unsigned int*>(status) & STATUS_TIMEOUT_PEER) != 0;  // a peer was lost before
     for (uint32_t row = row_begin + threadIdx.x; row < row_end; row += blockDim.x) {
-        float sum = 0.f;
-        for (uint32_t r = 0; r < c.world; ++r) {
-            const uint8_t* slot = c.buf[c.rank] + tp_slot(e, r, row);
-            uint32_t bits, tag;
-            uint64_t t0 = 0;
-            for (uint32_t spin = 0;; ++spin) {
-                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(tag) : "l"(slot) : "memory");
-                if (tag == e || lost) break;
-                if ((spin & 63u) == 63u) {
-                    const uint64_t now = global_timer_ns();
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > 1000000000ull) {
-                        atomicOr(status, STATUS_TIMEOUT_PEER);
-                        lost = true;
-                    }
+        // all ranks' slots are read at once (independent loads: one round trip, not one per rank); only
+        // the slots whose epoch has not arrived yet are read again
+        uint32_t bits[TP_MAX_WORLD], tag[TP_MAX_WORLD];
+        uint32_t pending = (1u << c.world) - 1u;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0; pending; ++spin) {
+#pragma unroll
+            for (uint32_t r = 0; r < TP_MAX_WORLD; ++r)
+                if (pending >> r & 1u) {
+                    const uint8_t* slot = c.buf[c.rank] + tp_slot(e, r, row);
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits[r]), "=r"(tag[r]) : "l"(slot) : "memory");
+                }
+#pragma unroll
+            for (uint32_t r = 0; r < TP_MAX_WORLD; ++r)
+                if ((pending >> r & 1u) && (tag[r] == e || lost)) pending &= ~(1u << r);
+            if (pending && (spin & 63u) == 63u) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > 1000000000ull) {
+                    atomicOr(status, STATUS_TIMEOUT_PEER);
+                    lost = true;
                 }
             }
-            sum = __fadd_rn(sum, __uint_as_float(bits));
         }
+        float sum = 0.f;
+#pragma unroll
+        for (uint32_t r = 0; r < TP_MAX_WORLD; ++r)
+            if (r < c.world) sum = __fadd_rn(sum, __uint_as_float(bits[r]));
         out[row] = sum;
     }
     __syncthreads();

@@ -54,7 +54,8 @@ struct GemvM1Params {
     uint32_t nblk;       // K / 256 (<= 16)
     uint32_t row_bytes;  // nblk * 144
     uint32_t rows_per_cta;  // CTA c owns rows [c * rows_per_cta, min(N, (c + 1) * rows_per_cta)) of the virtual row space
-    uint32_t stage_bytes;   // one fill: 8 rows, or 4 gate + 4 up rows in the SwiGLU variant
+    uint32_t lpr;           // lanes per row: nblk rounded up to a power of two
+    uint32_t stage_bytes;   // one fill: 4 warps x (32 / lpr) rows, or 4 gate + 4 up rows in the SwiGLU variant
     uint32_t nstages;
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
@@ -141,7 +142,10 @@ __device__ __forceinline__ float quantize_block8(const float (&v)[8], uint2& pac
 // as soon as the first 18 KB have landed, while the ring still keeps ~220 KB per SM in flight.
 template <bool SWIGLU>
 __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t cta, uint8_t* smem) {
-    constexpr uint32_t FR = SWIGLU ? 4 : 8;  // output rows per fill
+    // A row takes `lpr` lanes (the block count rounded up to a power of two; 16 for SwiGLU), so a warp
+    // takes 32 / lpr rows: short rows (K-split shards of a tensor-parallel group) keep all lanes busy.
+    const uint32_t lpr = SWIGLU ? 16u : p.lpr, lpr_log = 31 - __clz(lpr), rpw = 32u >> lpr_log;
+    const uint32_t FR = SWIGLU ? 4u : 4u * rpw;  // output rows per fill
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     uint8_t* act_s = smem + p.act_off;
@@ -230,7 +234,7 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
     TRACE1(p.trace_idx, 3);
 
     // 2. this lane's activation block goes to registers
-    const int b = lane & 15, h = lane >> 4;
+    const int b = lane & (lpr - 1), h = lane >> lpr_log;
     const bool blk_on = (uint32_t)b < p.nblk;
     uint32_t a[64];
     uint32_t bs_lo[2], bs_hi[2];
@@ -249,7 +253,7 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
 
     TRACE1(p.trace_idx, 10);
     const uint32_t grp = (uint32_t)warp >> 2, wi = (uint32_t)warp & 3;
-    const uint32_t rr = SWIGLU ? wi : 2 * wi + h;  // output row of the fill handled by this half-warp
+    const uint32_t rr = SWIGLU ? wi : rpw * wi + h;  // output row of the fill handled by this lane group
     bool dead = false;
     uint32_t slot = grp, par = 0;  // fill f lives in ring slot f % nstages (nstages >= 4)
     for (uint32_t f = grp; f < nfill; f += 4) {
@@ -305,9 +309,10 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         __syncwarp();
         if (f == 0) TRACE1(p.trace_idx, 11);
         if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
-        // add the block terms of a row (16 lanes)
+        // add the block terms of a row (lpr lanes)
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
+        for (uint32_t o = 8; o > 0; o >>= 1)
+            if (o < lpr) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
         if (SWIGLU) {
             const float up = __shfl_xor_sync(0xFFFFFFFFu, term, 16);
             term = term / (1.0f + expf(-term)) * up;  // meaningful in lane 0 (gate half)
@@ -370,7 +375,8 @@ struct GemvM1Q6Params {
     uint32_t nblk;          // K / 256 (<= 64)
     uint32_t row_bytes;     // nblk * 210
     uint32_t rows_per_cta;  // CTA c owns rows [c * rows_per_cta, min(N, (c + 1) * rows_per_cta))
-    uint32_t stage_bytes;   // 4 / NCHUNK rows + room for the phase of an unaligned first row
+    uint32_t lpr;           // single chunk: lanes per row = 2 * (nblk rounded up to a power of two)
+    uint32_t stage_bytes;   // rows of a fill + room for the phase of an unaligned first row
     uint32_t nstages;
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
@@ -453,7 +459,10 @@ __device__ __forceinline__ int q6k_half_sum(const uint8_t* blk, int n, const uin
 
 template <int NCHUNK>
 __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t cta, uint8_t* smem) {
-    constexpr uint32_t RPF = 4 / NCHUNK;  // rows per fill
+    // One warp per row and chunk; with a single chunk a row takes only `lpr` lanes (twice the block count
+    // rounded up to a power of two), so short rows (K-split shards) put 32 / lpr rows into a warp.
+    const uint32_t lpr = NCHUNK == 1 ? p.lpr : 32u, lpr_log = 31 - __clz(lpr), rpw = 32u >> lpr_log;
+    const uint32_t RPF = NCHUNK == 1 ? 4u * rpw : 4u / NCHUNK;  // rows per fill
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     float* part = reinterpret_cast<float*>(smem + 256);  // [16 slots][4 warps of the group]
@@ -514,8 +523,9 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
 
     // 2. this lane's activation half-block goes to registers
     const uint32_t grp = (uint32_t)warp >> 2, wi = (uint32_t)warp & 3;
-    const uint32_t r = wi / NCHUNK, c = wi % NCHUNK;  // row of the fill, K-chunk
-    const int b = lane >> 1, n = lane & 1;
+    const uint32_t r = NCHUNK == 1 ? wi * rpw + ((uint32_t)lane >> lpr_log) : wi / NCHUNK;  // row of the fill
+    const uint32_t c = NCHUNK == 1 ? 0u : wi % NCHUNK;                                   // K-chunk
+    const int b = (lane & (lpr - 1)) >> 1, n = lane & 1;
     const uint32_t gblk = c * 16 + b;
     const bool role = gblk < p.nblk;
     uint32_t a[32], bs[4];
@@ -556,9 +566,10 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
         const int sumi = half_sum + __shfl_xor_sync(0xFFFFFFFFu, half_sum, 1);
         float term = on ? __fmul_rn(__fmul_rn(d6, d8), (float)sumi) : 0.f;
 #pragma unroll
-        for (int o = 16; o > 1; o >>= 1) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
+        for (uint32_t o = 16; o > 1; o >>= 1)
+            if (o < lpr) term += __shfl_xor_sync(0xFFFFFFFFu, term, o);
         if (NCHUNK == 1) {
-            if (lane == 0 && on) store_row(r0 + r, term);
+            if ((lane & (lpr - 1)) == 0 && on) store_row(r0 + r, term);
         } else {
             if (lane == 0) part[slot * 4 + wi] = term;
         }
@@ -628,7 +639,9 @@ static size_t setup_q6k(GemvM1Q6Params& p, uint32_t& nchunk, size_t& smem, const
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
     nchunk = p.nblk <= 16 ? 1 : p.nblk <= 32 ? 2 : 4;
-    const uint32_t rpf = 4 / nchunk;
+    p.lpr = 2;
+    while (p.lpr < 2 * p.nblk && p.lpr < 32) p.lpr *= 2;
+    const uint32_t rpf = nchunk == 1 ? 4 * (32 / p.lpr) : 4 / nchunk;
     p.row_bytes = p.nblk * 210;
     p.stage_bytes = (rpf * p.row_bytes + 32 + 127) & ~127u;  // + phase of an unaligned first row + round-up
     p.act_off = 512;  // [0,256) barriers, [256,512) chunk-sum table
@@ -672,7 +685,10 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
 #ifdef B200Q_TRACE
     { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
 #endif
-    p.stage_bytes = 8 * p.row_bytes;  // multiple of 128
+    p.lpr = 1;
+    while (p.lpr < p.nblk) p.lpr *= 2;
+    if (p.lpr < 2) p.lpr = 2;
+    p.stage_bytes = (w_up ? 8 : 4 * (32 / p.lpr)) * p.row_bytes;  // 4 warps x rows per warp (SwiGLU: 4 gate + 4 up); multiple of 128
     p.act_off = 256;  // [0,256) barriers
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off) / p.stage_bytes);

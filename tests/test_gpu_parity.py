@@ -453,6 +453,21 @@ def test_quant_matmul_batch_decode_mixed_formats_one_launch(ops, oracle, specs, 
         assert rel_err(o.cpu().numpy(), want)[0] < 2e-6, (f, n)
 
 
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("k", [256, 512, 768, 1024, 1280, 2048, 2304])
+@pytest.mark.parametrize("n", [1, 63, 64, 65, 1000, 4096])
+def test_decode_short_rows_share_a_warp(ops, oracle, fmt, k, n):
+    # K-split shards of a tensor-parallel group have few blocks per row: several rows then share a warp
+    rng = synth.rng_for(39, k * 7 + n)
+    act = synth.activations(rng, 1, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul(fmt, act, w, n)
+    e_max, _ = rel_err(got, want)
+    assert e_max <= 2e-6, f"{fmt} K={k} N={n}: {e_max:.3e}\n" + describe_mismatch(got, want)
+
+
 @pytest.mark.parametrize("k", [256, 1792, 3584, 4096, 4352, 7168, 14336])
 @pytest.mark.parametrize("n", [1, 37, 500])
 def test_q6k_decode_rows_of_any_alignment(ops, oracle, k, n):
