@@ -60,6 +60,12 @@ __device__ __forceinline__ void store8<__half>(__half* out, const float (&v)[8])
     *reinterpret_cast<uint4*>(out) = r;
 }
 
+// float value of byte `I` of x (0..255) without an integer-to-float conversion instruction
+template <int I>
+__device__ __forceinline__ float byte_to_float(uint32_t x) {
+    return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 | I)) - 8388608.0f;
+}
+
 // Decode the 8 consecutive elements [8*lane, 8*lane+8) of one 256-element run starting at `u`.
 template <int FMT>
 __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8]) {
@@ -68,49 +74,43 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         // (src/quant/cpu/kernels/dequant_simple.rs:11-32)
         const uint8_t* blk = u + (lane >> 2) * 18;
         float d = f16bits_to_f32(ldg_u16(blk));
-        uint32_t w = ldg_w(blk + 2 + 4 * (lane & 3));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            int b = (w >> (8 * i)) & 0xFF;
-            v[2 * i] = (float)((b & 15) - 8) * d;
-            v[2 * i + 1] = (float)((b >> 4) - 8) * d;
-        }
+        const uint32_t w = ldg_w(blk + 2 + 4 * (lane & 3));
+        const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+        v[0] = (byte_to_float<0>(lo) - 8.0f) * d; v[1] = (byte_to_float<0>(hi) - 8.0f) * d;
+        v[2] = (byte_to_float<1>(lo) - 8.0f) * d; v[3] = (byte_to_float<1>(hi) - 8.0f) * d;
+        v[4] = (byte_to_float<2>(lo) - 8.0f) * d; v[5] = (byte_to_float<2>(hi) - 8.0f) * d;
+        v[6] = (byte_to_float<3>(lo) - 8.0f) * d; v[7] = (byte_to_float<3>(hi) - 8.0f) * d;
     } else if constexpr (FMT == FMT_Q8_0) {
         // block = f16 d | 32 x i8 (dequant_simple.rs:137-155)
         const uint8_t* blk = u + (lane >> 2) * 34;
         float d = f16bits_to_f32(ldg_u16(blk));
         const uint8_t* q = blk + 2 + 8 * (lane & 3);
-        uint32_t w0 = ldg_w(q), w1 = ldg_w(q + 4);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[i] = (float)(int)(signed char)((w0 >> (8 * i)) & 0xFF) * d;
-            v[4 + i] = (float)(int)(signed char)((w1 >> (8 * i)) & 0xFF) * d;
-        }
+        const uint32_t w0 = ldg_w(q) ^ 0x80808080u, w1 = ldg_w(q + 4) ^ 0x80808080u;  // q + 128 as unsigned bytes
+        v[0] = (byte_to_float<0>(w0) - 128.0f) * d; v[1] = (byte_to_float<1>(w0) - 128.0f) * d;
+        v[2] = (byte_to_float<2>(w0) - 128.0f) * d; v[3] = (byte_to_float<3>(w0) - 128.0f) * d;
+        v[4] = (byte_to_float<0>(w1) - 128.0f) * d; v[5] = (byte_to_float<1>(w1) - 128.0f) * d;
+        v[6] = (byte_to_float<2>(w1) - 128.0f) * d; v[7] = (byte_to_float<3>(w1) - 128.0f) * d;
     } else if constexpr (FMT == FMT_Q4_K) {
         // block = f16 d | f16 dmin | 12 B packed 6-bit scales/mins | 128 B nibbles
         // (src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:10-47, :108-122)
-        int j = lane >> 2;  // 32-element sub-block
-        uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(u));
-        float d = f16bits_to_f32(dm & 0xFFFF), dmin = f16bits_to_f32(dm >> 16);
-        const uint8_t* sc = u + 4;
-        int s, m;
-        if (j < 4) {
-            s = __ldg(sc + j) & 63;
-            m = __ldg(sc + j + 4) & 63;
-        } else {
-            int hi = __ldg(sc + j + 4);
-            s = (hi & 15) | ((__ldg(sc + j - 4) >> 6) << 4);
-            m = (hi >> 4) | ((__ldg(sc + j) >> 6) << 4);
-        }
-        float dl = d * (float)s, ml = dmin * (float)m;
-        uint2 w = __ldg(reinterpret_cast<const uint2*>(u + 16 + (j >> 1) * 32 + 8 * (lane & 3)));
-        int sh = (j & 1) * 4;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float q0 = (float)((w.x >> (8 * i + sh)) & 15), q1 = (float)((w.y >> (8 * i + sh)) & 15);
-            v[i] = __fsub_rn(__fmul_rn(dl, q0), ml);
-            v[4 + i] = __fsub_rn(__fmul_rn(dl, q1), ml);
-        }
+        const int j = lane >> 2;  // 32-element sub-block
+        const uint32_t* hd = reinterpret_cast<const uint32_t*>(u);
+        const uint32_t dm = __ldg(hd), h1 = __ldg(hd + 1), h2 = __ldg(hd + 2), h3 = __ldg(hd + 3);
+        const float d = f16bits_to_f32(dm & 0xFFFF), dmin = f16bits_to_f32(dm >> 16);
+        // the four 6-bit scales / mins of sub-blocks 0-3 or 4-7 as packed bytes
+        const uint32_t scw = j < 4 ? (h1 & 0x3F3F3F3Fu) : ((h3 & 0x0F0F0F0Fu) | ((h1 >> 2) & 0x30303030u));
+        const uint32_t mnw = j < 4 ? (h2 & 0x3F3F3F3Fu) : (((h3 >> 4) & 0x0F0F0F0Fu) | ((h2 >> 2) & 0x30303030u));
+        const int sh8 = 8 * (j & 3);
+        // d * sc and dmin * m are exact (11 x 6 bits), and so is (d * sc) * q: the fused multiply-add below
+        // rounds once, exactly like the multiply-then-subtract of the reference
+        const float dl = d * (float)((scw >> sh8) & 0xFF), nml = -(dmin * (float)((mnw >> sh8) & 0xFF));
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(u + 16 + (j >> 1) * 32 + 8 * (lane & 3)));
+        const int sh = (j & 1) * 4;
+        const uint32_t q0 = (w.x >> sh) & 0x0F0F0F0Fu, q1 = (w.y >> sh) & 0x0F0F0F0Fu;
+        v[0] = fmaf(dl, byte_to_float<0>(q0), nml); v[1] = fmaf(dl, byte_to_float<1>(q0), nml);
+        v[2] = fmaf(dl, byte_to_float<2>(q0), nml); v[3] = fmaf(dl, byte_to_float<3>(q0), nml);
+        v[4] = fmaf(dl, byte_to_float<0>(q1), nml); v[5] = fmaf(dl, byte_to_float<1>(q1), nml);
+        v[6] = fmaf(dl, byte_to_float<2>(q1), nml); v[7] = fmaf(dl, byte_to_float<3>(q1), nml);
     } else {
         // Q6_K block = 128 B ql | 64 B qh | 16 x i8 scales | f16 d
         // (src/quant/cpu/kernels/dequant_k_quants/q6k_q8k.rs:10-56)
@@ -121,14 +121,14 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         const uint8_t* ql = u + 64 * n + 32 * (gq & 1) + l0;
         const uint8_t* qh = u + 128 + 32 * n + l0;
         uint32_t l_0 = ldg_w(ql), l_1 = ldg_w(ql + 4), h_0 = ldg_w(qh), h_1 = ldg_w(qh + 4);
-        int lsh = (gq >> 1) * 4, hsh = 2 * gq;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            int qa = (int)(((l_0 >> (8 * i + lsh)) & 15) | (((h_0 >> (8 * i + hsh)) & 3) << 4)) - 32;
-            int qb = (int)(((l_1 >> (8 * i + lsh)) & 15) | (((h_1 >> (8 * i + hsh)) & 3) << 4)) - 32;
-            v[i] = ds * (float)qa;
-            v[4 + i] = ds * (float)qb;
-        }
+        const int lsh = (gq >> 1) * 4, hsh = 2 * gq;
+        // four 6-bit values per word; (float)q - 32 and its product with d * sc round exactly as d * sc * (q - 32)
+        const uint32_t qa = ((l_0 >> lsh) & 0x0F0F0F0Fu) | (((h_0 >> hsh) & 0x03030303u) << 4);
+        const uint32_t qb = ((l_1 >> lsh) & 0x0F0F0F0Fu) | (((h_1 >> hsh) & 0x03030303u) << 4);
+        v[0] = ds * (byte_to_float<0>(qa) - 32.0f); v[1] = ds * (byte_to_float<1>(qa) - 32.0f);
+        v[2] = ds * (byte_to_float<2>(qa) - 32.0f); v[3] = ds * (byte_to_float<3>(qa) - 32.0f);
+        v[4] = ds * (byte_to_float<0>(qb) - 32.0f); v[5] = ds * (byte_to_float<1>(qb) - 32.0f);
+        v[6] = ds * (byte_to_float<2>(qb) - 32.0f); v[7] = ds * (byte_to_float<3>(qb) - 32.0f);
     }
 }
 
@@ -140,12 +140,18 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     size_t warp = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const size_t nwarps = (size_t)gridDim.x * (blockDim.x >> 5);
     constexpr int UB = fmt_slice_bytes(FMT);
-    for (size_t unit = warp; unit < nunits; unit += nwarps) {
-        int valid = (unit + 1 == nunits && tail_elems) ? tail_elems : 256;
-        if (8 * lane >= valid) continue;  // elements come in whole 32-blocks, so 8-lane groups are all-or-nothing
-        float v[8];
-        decode8<FMT>(w + unit * UB, lane, v);
-        store8<OutT>(out + unit * 256 + 8 * lane, v);
+    // two runs per trip: the loads of both are in flight before either is decoded
+    for (size_t unit = warp; unit < nunits; unit += 2 * nwarps) {
+        const size_t unit2 = unit + nwarps;
+        const bool has2 = unit2 < nunits;
+        const int valid = (unit + 1 == nunits && tail_elems) ? tail_elems : 256;
+        const int valid2 = !has2 ? 0 : (unit2 + 1 == nunits && tail_elems) ? tail_elems : 256;
+        // elements come in whole 32-blocks, so 8-lane groups are all-or-nothing
+        float v[8], v2[8];
+        if (8 * lane < valid) decode8<FMT>(w + unit * UB, lane, v);
+        if (8 * lane < valid2) decode8<FMT>(w + unit2 * UB, lane, v2);
+        if (8 * lane < valid) store8<OutT>(out + unit * 256 + 8 * lane, v);
+        if (8 * lane < valid2) store8<OutT>(out + unit2 * 256 + 8 * lane, v2);
     }
 }
 
