@@ -55,16 +55,56 @@ STEP_BYTES = LAYERS * sum(fmt_bytes(f, n, k) for _, f, n, k, _ in LAYER_SPEC) + 
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    """SM clock / throttle-reason samples while the timed region runs.
+
+    Reads NVML directly every 2 ms (a decode step lasts about a millisecond, so `nvidia-smi -lms`
+    would miss short regions); falls back to `nvidia-smi -lms 100` when the NVML binding is missing.
+    Only reads: no clock, power or mode setting is touched."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.stop = threading.Event()
+        self.thread = None
+        self.handle = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _poll(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in self.BITS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def __enter__(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
@@ -76,6 +116,9 @@ class ClockSampler:
         return self
 
     def __exit__(self, *a):
+        if self.thread is not None:
+            self.stop.set()
+            self.thread.join(timeout=1)
         if self.proc:
             time.sleep(0.15)
             self.proc.terminate()
@@ -85,6 +128,11 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
+        if self.thread is not None:
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+            return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                    "samples": len(self.samples), "source": "nvml, 2 ms period"}
         sm, mx, reasons = [], [], set()
         for l in self.lines:
             p = [x.strip() for x in l.split(",")]
@@ -100,7 +148,8 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi -lms 100"}
 
 
 # --------------------------------------------------------------------------- GPU arm
