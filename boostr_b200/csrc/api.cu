@@ -27,6 +27,9 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
                                  unsigned int* status);
 cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
                                   int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm);
+bool gemv_m1_f32_supported(int fmt, size_t M, size_t K, size_t N);
+cudaError_t launch_gemv_m1_f32(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
+                               size_t N, int sm_count, cudaStream_t st, unsigned int* status);
 bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N);
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -187,6 +190,8 @@ int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
     } else if (gemv_m1_supported(format, M, K, N, false)) {
         e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else if (gemv_m1_f32_supported(format, M, K, N)) {
+        e = launch_gemv_m1_f32(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
     } else {
         e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
                         st, status, &small);

@@ -100,6 +100,23 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Copies the 2-byte-aligned global range [src, src + bytes) into shared memory as the enclosing 16-byte
+// aligned range (bulk copies need 16-byte alignment): the data lands at dst + (src & 15).  If that range
+// would end past the tensor (`wend`), the last <16 bytes are moved with plain loads.  One lane calls this.
+__device__ __forceinline__ void fill_contiguous(uint32_t dst_s, uint8_t* dst_g, const uint8_t* src, uint32_t bytes,
+                                                const uint8_t* wend, uint32_t bar) {
+    const uint8_t* gs = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15);
+    const uint8_t* ge = src + bytes;
+    const uint8_t* e16 = reinterpret_cast<const uint8_t*>((reinterpret_cast<uintptr_t>(ge) + 15) & ~(uintptr_t)15);
+    if (e16 > wend) {
+        e16 = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(ge) & ~(uintptr_t)15);
+        for (const uint8_t* q = e16; q < ge; ++q) dst_g[q - gs] = __ldg(q);
+    }
+    const uint32_t n = (uint32_t)(e16 - gs);
+    mbar_expect_tx(bar, n);  // release: the plain stores above are visible to whoever sees the phase complete
+    if (n) bulk_g2s(dst_s, gs, n, bar);
+}
+
 // ------------------------------------------------------------- programmatic dependent launch
 // Kernels of this library are launched so that a grid may begin while its predecessor in the
 // stream is still draining (launch_pdl below).  grid_dep_launch() lets the NEXT grid start early;
