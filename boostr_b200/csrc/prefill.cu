@@ -55,7 +55,8 @@ namespace {
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int A_TILE_BYTES = 128 * BK * 2;
 constexpr int PF_MAX_STAGES = 8;
-constexpr int RAW_TILE_BYTES = 128 * 144;  // Q4_K: 128 rows x one block, row pitch 144 B (conflict-free 16-byte reads)
+// packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
+__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : 144; }  // Q4_K block, 8 Q4_0 / Q8_0 blocks
 constexpr int PF_THREADS = 23 * 32;  // warps 0-15 dequant | 16 activation TMA | 17 MMA issue, TMEM | 18 packed-weight TMA | 19-22 epilogue
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -149,6 +150,35 @@ __device__ __forceinline__ void decode32_q4k(const RawQ4K& r, uint32_t kt, uint3
     }
 }
 
+// One 32-element Q8_0 / Q4_0 block (2-byte aligned) as 32 bf16.  SM: the block sits in shared memory.
+template <int FMT, bool SM>
+__device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t (&o)[16]) {
+    auto l16 = [&](const uint8_t* p) -> uint32_t { return SM ? (uint32_t)*reinterpret_cast<const unsigned short*>(p) : g16(p); };
+    auto l32 = [&](const uint8_t* p) -> uint32_t {
+        if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return SM ? *reinterpret_cast<const uint32_t*>(p) : __ldg(reinterpret_cast<const uint32_t*>(p));
+        return l16(p) | (l16(p + 2) << 16);
+    };
+    const float d = f16bits_to_f32(l16(blk));
+    if constexpr (FMT == FMT_Q8_0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = l32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
+            o[2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
+            o[2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
+        }
+    } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t x = l32(blk + 2 + 4 * i);
+            const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+            o[4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
+            o[4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
+            o[4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
+            o[4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
+        }
+    }
+}
+
 // Elements [64*kt + 32*half, +32) of one weight row as 32 bf16 (16 packed words), other formats.
 template <int FMT>
 __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
@@ -171,26 +201,9 @@ __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32
             o[2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
         }
     } else if constexpr (FMT == FMT_Q8_0) {
-        const uint8_t* blk = row + (2 * kt + half) * 34;
-        const float d = f16bits_to_f32(g16(blk));
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t x = g32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
-            o[2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
-            o[2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
-        }
-    } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
-        const uint8_t* blk = row + (2 * kt + half) * 18;
-        const float d = f16bits_to_f32(g16(blk));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t x = g32(blk + 2 + 4 * i);
-            const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-            o[4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
-            o[4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
-            o[4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
-            o[4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
-        }
+        decode32_blk<FMT_Q8_0, false>(row + (2 * kt + half) * 34, o);
+    } else {
+        decode32_blk<FMT_Q4_0, false>(row + (2 * kt + half) * 18, o);
     }
 }
 
@@ -204,10 +217,10 @@ constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OF
 // Persistent: one CTA per SM walks the output tiles t = blockIdx.x, + gridDim.x, ... (consecutive CTAs share an
 // activation tile, which therefore stays in L2).  Tensor memory holds TWO accumulators, so the four epilogue warps
 // drain tile i while the MMA warp is already accumulating tile i + 1 and the rings never run dry between tiles.
-template <int FMT>
+template <int FMT, bool RAW_TMA>  // RAW_TMA: packed weights staged in shared memory by TMA (rows a multiple of 16 bytes)
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
-    constexpr bool RAW_TMA = FMT == FMT_Q4_K;  // packed weights staged in shared memory by TMA
+    constexpr uint32_t RAW_PITCH = raw_pitch(FMT), RAW_TILE_BYTES = 128 * RAW_PITCH;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -266,7 +279,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         break;
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
-                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * 144), (int)n0, bar_full_raw + 8 * s);
+                    // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * (FMT == FMT_Q8_0 ? 136 : 144)), (int)n0, bar_full_raw + 8 * s);
                     if (++s == 2) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -389,19 +403,29 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         *dead_flag = 1;
                         ok = false;
                     }
-                    RawQ4K cur{};
-                    if (ok) cur = load_raw_q4k_smem(smem + 1024 + rs * RAW_TILE_BYTES + r * 144, kt);
-                    if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {  // this set's last step in the tile: release it
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
-                    }
+                    const uint8_t* rrow = smem + 1024 + rs * RAW_TILE_BYTES + r * RAW_PITCH;
+                    if constexpr (FMT == FMT_Q4_K) {
+                        RawQ4K cur{};
+                        if (ok) cur = load_raw_q4k_smem(rrow, kt);
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {  // this set's last step in the tile: release it
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                        }
 #ifdef B200Q_TRACE
-                    if (p.dbg & 1) {
+                        if (p.dbg & 1) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = cur.q0.x;
-                    } else
+                            for (int i = 0; i < 16; ++i) o[i] = cur.q0.x;
+                        } else
 #endif
-                    decode32_q4k(cur, kt, half, o);
+                        decode32_q4k(cur, kt, half, o);
+                    } else {
+                        constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
+                        if (ok) decode32_blk<FMT, true>(rrow + (2 * (kt & 3) + half) * BB, o);
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                        }
+                    }
                 } else {
                     decode32<FMT>(wrow, kt, half, o);
                 }
@@ -518,17 +542,17 @@ EncodeTiledFn encode_tiled() {
 
 uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
 
-template <int FMT>
+template <int FMT, bool RAW>
 cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<FMT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    prefill_kernel<FMT><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
+    prefill_kernel<FMT, RAW><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
     note_launch();
     return cudaGetLastError();
 }
@@ -588,9 +612,11 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.mt = pick_mt(M);
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.mt >> 3) << 17) | ((128u >> 4) << 24);  // f32 acc, bf16 x bf16, K-major, N = mt, M = 128
     p.nkt = (uint32_t)(K / BK);
-    const uint32_t raw_bytes = fmt == FMT_Q4_K ? 2 * RAW_TILE_BYTES : 0;
-    // the formats that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
-    const uint32_t budget = (fmt == FMT_Q4_K ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
+    // packed tiles by TMA need rows that are a multiple of 16 bytes and whole 256-element tiles
+    const bool raw = fmt != FMT_Q6_K && K % 256 == 0 && p.row_bytes % 16 == 0;
+    const uint32_t raw_bytes = raw ? 2u * 128u * (uint32_t)raw_pitch(fmt) : 0u;
+    // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
+    const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
     uint32_t nsa = 4;
 #ifdef B200Q_TRACE
     { const char* e = getenv("B200Q_PF_NSA"); if (e && atoi(e) >= 2 && atoi(e) <= 8) nsa = atoi(e); }
@@ -625,14 +651,17 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
         snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (activation pointer %p, K=%zu, M=%zu)", (int)cr, act_bf16, K, M);
         return cudaErrorInvalidValue;
     }
-    // packed weights as a byte matrix [N, row_bytes]: tiles of 128 rows x one 144-byte Q4_K block
+    // packed weights as a matrix [N, row_bytes]: tiles of 128 rows x the bytes of 256 elements (bytes for the
+    // 144-byte formats, 16-bit units for Q8_0's 272 bytes: a box dimension holds at most 256 elements)
     CUtensorMap wmap = map;
-    if (fmt == FMT_Q4_K) {
-        const cuuint64_t wdim[2] = {(cuuint64_t)p.row_bytes, (cuuint64_t)N};
+    if (raw) {
+        const bool q8 = fmt == FMT_Q8_0;
+        const cuuint64_t wdim[2] = {(cuuint64_t)(q8 ? p.row_bytes / 2 : p.row_bytes), (cuuint64_t)N};
         const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
-        const cuuint32_t wbox[2] = {144, 128};
-        cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint32_t wbox[2] = {q8 ? 136u : 144u, 128u};
+        cr = enc(&wmap, q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox,
+                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) {
             snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (weight pointer %p, row bytes %u, N=%zu)", (int)cr, w, p.row_bytes, N);
             return cudaErrorInvalidValue;
@@ -640,10 +669,10 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     }
     dim3 grid(p.ntiles < (uint32_t)sm_count ? p.ntiles : (uint32_t)sm_count, 1, 1);
     switch (fmt) {
-    case FMT_Q4_0: return launch_fmt<FMT_Q4_0>(map, wmap, p, grid, smem, st);
-    case FMT_Q8_0: return launch_fmt<FMT_Q8_0>(map, wmap, p, grid, smem, st);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K>(map, wmap, p, grid, smem, st);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K>(map, wmap, p, grid, smem, st);
+    case FMT_Q4_0: return raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st);
+    case FMT_Q8_0: return raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st);
+    case FMT_Q4_K: return launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K, false>(map, wmap, p, grid, smem, st);
     default: return cudaErrorInvalidValue;
     }
 }
