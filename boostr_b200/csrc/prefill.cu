@@ -56,7 +56,11 @@ constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle r
 constexpr int A_TILE_BYTES = 128 * BK * 2;
 constexpr int PF_MAX_STAGES = 8;
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
-__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : 144; }  // Q4_K block, 8 Q4_0 / Q8_0 blocks
+__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : 144; }
+// tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
+// multiples of 16 bytes, so TMA cannot fetch them: the dequant warps copy them themselves, coalesced, 2 bytes per lane,
+// into rows of 212 bytes (4-byte aligned blocks, conflict-free row-per-thread reads).
+__host__ __device__ constexpr int raw_tile_bytes(int fmt) { return (128 * raw_pitch(fmt) + 1023) & ~1023; }
 constexpr int PF_THREADS = 23 * 32;  // warps 0-15 dequant | 16 activation TMA | 17 MMA issue, TMEM | 18 packed-weight TMA | 19-22 epilogue
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -179,27 +183,35 @@ __device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t (&o)[1
     }
 }
 
+// 32 elements of the Q6_K block at `blk`: K step kt of the block's four, half `half`.
+// SM: the block sits 4-byte aligned in shared memory; otherwise 2-byte aligned in global memory.
+template <bool SM>
+__device__ __forceinline__ void decode32_q6k(const uint8_t* blk, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
+    auto l8 = [&](const uint8_t* p) -> int { return SM ? (int)(signed char)*p : (int)(signed char)__ldg(p); };
+    auto l32 = [&](const uint8_t* p) -> uint32_t { return SM ? *reinterpret_cast<const uint32_t*>(p) : g32(p); };
+    const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + half) + l
+    const float d = f16bits_to_f32(SM ? (uint32_t)*reinterpret_cast<const unsigned short*>(blk + 208) : g16(blk + 208));
+    const uint32_t gq = g0 + half;
+    const uint8_t* ql = blk + 64 * n + 32 * half;  // gq & 1 == half
+    const uint8_t* qh = blk + 128 + 32 * n;
+    const float s0 = d * (float)l8(blk + 192 + 8 * n + 2 * gq);
+    const float s1 = d * (float)l8(blk + 192 + 8 * n + 2 * gq + 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t lw = l32(ql + 4 * i), hw = l32(qh + 4 * i);
+        const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
+        const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
+        const float s = i < 4 ? s0 : s1;
+        o[2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
+        o[2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
+    }
+}
+
 // Elements [64*kt + 32*half, +32) of one weight row as 32 bf16 (16 packed words), other formats.
 template <int FMT>
 __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
     if constexpr (FMT == FMT_Q6_K) {
-        const uint8_t* blk = row + (kt >> 2) * 210;
-        const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + half) + l
-        const float d = f16bits_to_f32(g16(blk + 208));
-        const uint32_t gq = g0 + half;
-        const uint8_t* ql = blk + 64 * n + 32 * half;  // gq & 1 == half
-        const uint8_t* qh = blk + 128 + 32 * n;
-        const float s0 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq);
-        const float s1 = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * n + 2 * gq + 1);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t lw = g32(ql + 4 * i), hw = g32(qh + 4 * i);
-            const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
-            const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
-            const float s = i < 4 ? s0 : s1;
-            o[2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
-            o[2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
-        }
+        decode32_q6k<false>(row + (kt >> 2) * 210, kt, half, o);
     } else if constexpr (FMT == FMT_Q8_0) {
         decode32_blk<FMT_Q8_0, false>(row + (2 * kt + half) * 34, o);
     } else {
@@ -220,7 +232,8 @@ constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OF
 template <int FMT, bool RAW_TMA>  // RAW_TMA: packed weights staged in shared memory by TMA (rows a multiple of 16 bytes)
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
-    constexpr uint32_t RAW_PITCH = raw_pitch(FMT), RAW_TILE_BYTES = 128 * RAW_PITCH;
+    constexpr uint32_t RAW_PITCH = raw_pitch(FMT), RAW_TILE_BYTES = raw_tile_bytes(FMT);
+    constexpr bool COOP = RAW_TMA && FMT == FMT_Q6_K;  // packed tiles copied by the dequant warps instead of TMA
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -248,8 +261,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             mbar_init(bar_empty_b + 8 * s, 1);
         }
         for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(bar_full_raw + 8 * s, 1);
-            mbar_init(bar_empty_raw + 8 * s, 16);  // every dequant warp reads every packed tile
+            mbar_init(bar_full_raw + 8 * s, COOP ? 16 : 1);  // COOP: every dequant warp copies its 8 rows
+            mbar_init(bar_empty_raw + 8 * s, 16);            // every dequant warp reads every packed tile
             mbar_init(bar_acc_full + 8 * s, 1);
             mbar_init(bar_acc_empty + 8 * s, 4);   // the four epilogue warps
         }
@@ -267,7 +280,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
 
     if (warp == 18) {
         // ------------------------------------------------------------ packed weight tiles by TMA (Q4_K)
-        if (RAW_TMA && lane == 0) {
+        if (RAW_TMA && !COOP && lane == 0) {
             uint32_t s = 0, par = 0;
             for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
                 const uint32_t n0 = (tile % p.ntn) * 128;
@@ -390,6 +403,47 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
         bool ok = true;
         uint32_t it = 0;
+        // COOP: packed tile c (counted over all output tiles of this CTA) is copied by all 16 dequant warps, 8 rows
+        // each, one tile ahead of its use; buffer c & 1 must have been released by every reader of tile c - 2
+        uint32_t next_copy = 0;
+        auto copy_upto = [&](uint32_t upto) {
+            for (; next_copy <= upto; ++next_copy) {
+                const uint32_t c = next_copy, tc = blockIdx.x + (c / nraw) * gridDim.x, jc = c % nraw;
+                if (tc >= p.ntiles) continue;
+                const uint32_t cs = c & 1;
+                if (ok && (*dead_flag || !mbar_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1))) {
+                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    *dead_flag = 1;
+                    ok = false;
+                }
+                if (ok) {
+                    const uint32_t cn0 = (tc % p.ntn) * 128;
+                    uint8_t* dst = smem + 1024 + cs * RAW_TILE_BYTES;
+                    unsigned short v[8][4];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const uint32_t row = 8 * (uint32_t)warp + q;
+                        const unsigned short* src = reinterpret_cast<const unsigned short*>(p.w + (size_t)(cn0 + row) * p.row_bytes + (size_t)jc * 210);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t hw = lane + 32 * i;
+                            v[q][i] = (cn0 + row < p.N && hw < 105) ? __ldg(src + hw) : (unsigned short)0;
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        unsigned short* d16 = reinterpret_cast<unsigned short*>(dst + (8 * (uint32_t)warp + q) * RAW_PITCH);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t hw = lane + 32 * i;
+                            if (hw < 105) d16[hw] = v[q][i];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full_raw + 8 * cs);
+            }
+        };
         for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
             const uint32_t n0 = (tile % p.ntn) * 128;
             const bool row_ok = n0 + r < p.N;
@@ -398,6 +452,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 uint32_t o[16];
                 if constexpr (RAW_TMA) {
                     const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
+                    if constexpr (COOP) copy_upto(jr + 1);
                     if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1))) {
                         if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
                         *dead_flag = 1;
@@ -418,6 +473,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         } else
 #endif
                         decode32_q4k(cur, kt, half, o);
+                    } else if constexpr (FMT == FMT_Q6_K) {
+                        if (ok) decode32_q6k<true>(rrow, kt, half, o);
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                        }
                     } else {
                         constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
                         if (ok) decode32_blk<FMT, true>(rrow + (2 * (kt & 3) + half) * BB, o);
@@ -613,8 +674,9 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.mt >> 3) << 17) | ((128u >> 4) << 24);  // f32 acc, bf16 x bf16, K-major, N = mt, M = 128
     p.nkt = (uint32_t)(K / BK);
     // packed tiles by TMA need rows that are a multiple of 16 bytes and whole 256-element tiles
-    const bool raw = fmt != FMT_Q6_K && K % 256 == 0 && p.row_bytes % 16 == 0;
-    const uint32_t raw_bytes = raw ? 2u * 128u * (uint32_t)raw_pitch(fmt) : 0u;
+    // (Q6_K's tiles are copied by the dequant warps and only need whole blocks, which the format guarantees)
+    const bool raw = K % 256 == 0 && (fmt == FMT_Q6_K || p.row_bytes % 16 == 0);
+    const uint32_t raw_bytes = raw ? 2u * (uint32_t)raw_tile_bytes(fmt) : 0u;
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
     uint32_t nsa = 4;
@@ -654,7 +716,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // packed weights as a matrix [N, row_bytes]: tiles of 128 rows x the bytes of 256 elements (bytes for the
     // 144-byte formats, 16-bit units for Q8_0's 272 bytes: a box dimension holds at most 256 elements)
     CUtensorMap wmap = map;
-    if (raw) {
+    if (raw && fmt != FMT_Q6_K) {
         const bool q8 = fmt == FMT_Q8_0;
         const cuuint64_t wdim[2] = {(cuuint64_t)(q8 ? p.row_bytes / 2 : p.row_bytes), (cuuint64_t)N};
         const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
@@ -672,7 +734,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     case FMT_Q4_0: return raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st);
     case FMT_Q8_0: return raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st);
     case FMT_Q4_K: return launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K, false>(map, wmap, p, grid, smem, st);
+    case FMT_Q6_K: return launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st);
     default: return cudaErrorInvalidValue;
     }
 }
