@@ -235,9 +235,9 @@ class DecodeStack:
 
 
 # DRAM bytes (read + written) of one launch of the dominant kernel at one GPU, from the ncu capture
-# summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.256 MB, dram__bytes_write.sum 0.
+# summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.262 MB, dram__bytes_write.sum 2 KB.
 # A K-split shard streams proportionally fewer bytes, so the figure is scaled by the shard's packed bytes.
-NCU_TRAFFIC_DOWN_1GPU = 48_256_000
+NCU_TRAFFIC_DOWN_1GPU = 48_264_148
 NCU_ALGORITHMIC_DOWN_1GPU = 4096 * 56 * 210
 
 
