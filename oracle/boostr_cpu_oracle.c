@@ -618,7 +618,7 @@ ORACLE_API int oracle_quant_swiglu(int fmt, const float *act, const uint8_t *wg,
     return rc;
 }
 
-/* Diagnostic only (not the judged oracle): exact-weight x f32-activation dot in f64. */
+/* Diagnostic only (not the parity reference): exact-weight x f32-activation dot in f64. */
 ORACLE_API int oracle_matmul_exact_f64(int fmt, const float *act, const uint8_t *w, double *out, size_t m, size_t k,
                                        size_t n) {
     int bs = oracle_block_size(fmt);
