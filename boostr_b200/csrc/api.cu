@@ -53,19 +53,23 @@ __device__ unsigned int g_status_word = 0;
 
 namespace {
 
-// Device address of g_status_word on the current device, looked up once per device.
-// (The symbol's name in host code is only a handle; kernels need the address.)
+// Device address of g_status_word on the current device.  (The symbol's name in host code is only a
+// handle; kernels need the address.)  Only a successful lookup is cached, so a failure (for instance a
+// first call made while a stream is being captured) is retried by the next call.  The address belongs
+// to the device's primary context.
 unsigned int* status_ptr_current() {
-    static unsigned int* cached[64];
-    static std::once_flag once[64];
+    static std::atomic<unsigned int*> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    std::call_once(once[dev], [dev] {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) p = nullptr;
-        cached[dev] = static_cast<unsigned int*>(p);
-    });
-    return cached[dev];
+    unsigned int* p = cached[dev].load(std::memory_order_acquire);
+    if (p) return p;
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_status_word) != cudaSuccess || !q) {
+        cudaGetLastError();  // the failed lookup must not poison the next launch check
+        return nullptr;
+    }
+    cached[dev].store(static_cast<unsigned int*>(q), std::memory_order_release);
+    return static_cast<unsigned int*>(q);
 }
 
 thread_local char t_err[512] = "";
@@ -124,6 +128,19 @@ int check_matmul_args(const char* op, int format, const void* act, int act_dtype
     return B200Q_OK;
 }
 
+// Scratch bytes of one call with activations of `act_dtype` (the public query assumes F32).
+size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, size_t N) {
+    if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
+    const bool swiglu = op == B200Q_OP_QUANT_SWIGLU;
+    if (prefill_supported(format, M, K, N)) {
+        size_t a = prefill_workspace_bytes(format, act_dtype, M, K, N);
+        // large-M SwiGLU = two prefill GEMMs into scratch, then the gate
+        if (swiglu) a += 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255);
+        return a;
+    }
+    return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
+}
+
 }  // namespace
 
 extern "C" {
@@ -159,19 +176,8 @@ int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int o
 }
 
 size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N) {
-    if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
-    const bool swiglu = op == B200Q_OP_QUANT_SWIGLU;
-    size_t need = gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
-    if (!swiglu && prefill_supported(format, M, K, N)) {
-        size_t a = prefill_workspace_bytes(format, DT_F32, M, K, N);
-        if (a > need) need = a;
-    }
-    if (swiglu && prefill_supported(format, M, K, N)) {
-        // large-M SwiGLU = two prefill GEMMs into scratch, then the gate
-        size_t a = prefill_workspace_bytes(format, DT_F32, M, K, N) + 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255);
-        if (a > need) need = a;
-    }
-    return need;
+    // F32 activations need the most scratch (the bf16 / Q8_K activation image of the tensor-core path)
+    return workspace_need(op, format, DT_F32, M, K, N);
 }
 
 int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -317,11 +323,11 @@ static __device__ __align__(256) unsigned char g_static_scratch[B200Q_STATIC_SCR
 
 namespace {
 // Device address of g_static_scratch on the current device; resolved on the first call made with
-// that device current.  Returns nullptr (and sets *err) when the lookup fails.
+// that device current.  Returns nullptr (and sets *err) when the lookup fails; only a successful
+// lookup is remembered, so the next call tries again.  The address belongs to the device's primary
+// context.
 void* static_scratch_current(cudaError_t* err) {
-    static void* cached[64];
-    static cudaError_t status[64];
-    static std::once_flag once[64];
+    static std::atomic<void*> cached[64];
     int dev = 0;
     *err = cudaGetDevice(&dev);
     if (*err != cudaSuccess) return nullptr;
@@ -329,13 +335,16 @@ void* static_scratch_current(cudaError_t* err) {
         *err = cudaErrorInvalidDevice;
         return nullptr;
     }
-    std::call_once(once[dev], [dev] {
-        void* p = nullptr;
-        status[dev] = cudaGetSymbolAddress(&p, g_static_scratch);
-        cached[dev] = status[dev] == cudaSuccess ? p : nullptr;
-    });
-    *err = status[dev];
-    return cached[dev];
+    void* p = cached[dev].load(std::memory_order_acquire);
+    if (p) return p;
+    *err = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (*err != cudaSuccess || !p) {
+        cudaGetLastError();
+        if (*err == cudaSuccess) *err = cudaErrorInvalidSymbol;
+        return nullptr;
+    }
+    cached[dev].store(p, std::memory_order_release);
+    return p;
 }
 }  // namespace
 
@@ -345,7 +354,7 @@ int b200q_quant_matmul_static_scratch(int format, const void* act, int act_dtype
                                       size_t M, size_t K, size_t N, void* stream) {
     int rc = check_matmul_args("quant_matmul_static_scratch", format, act, act_dtype, w, out, out_dtype, M, K, N);
     if (rc) return rc;
-    const size_t need = b200q_workspace_bytes(B200Q_OP_QUANT_MATMUL, format, M, K, N);
+    const size_t need = workspace_need(B200Q_OP_QUANT_MATMUL, format, act_dtype, M, K, N);
     if (need > B200Q_STATIC_SCRATCH_BYTES)
         return fail(B200Q_ERR_WORKSPACE_TOO_SMALL,
                     "quant_matmul_static_scratch: this shape (M=%zu K=%zu N=%zu) needs %zu bytes of scratch, the built-in "

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace b200q {
 
 // Block formats (QuantFormat::format_id of the reference).
@@ -28,6 +30,24 @@ __host__ __device__ constexpr int fmt_slice_bytes(int f) { return fmt_block_byte
 
 // Host-side count of kernel launches issued by the library (see b200q_launch_count).
 void note_launch(unsigned n = 1);
+
+// Per-device "done once" flags for host-side set-up (kernel attributes): the action runs until it has
+// succeeded once on the current device; concurrent first calls may both run it, which is harmless for
+// idempotent CUDA attribute calls, and the flag itself is an atomic.
+struct PerDeviceOnce {
+    std::atomic<bool> done[64];
+    template <typename F>
+    cudaError_t run(F&& action) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return action();
+        if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+        e = action();
+        if (e == cudaSuccess) done[dev].store(true, std::memory_order_release);
+        return e;
+    }
+};
 
 // ---------------------------------------------------------------- shared memory / mbarrier
 
@@ -144,8 +164,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // ------------------------------------------------------------------- peer exchange (tensor parallel)
 // Row-parallel decode products end in an all-reduce of one f32 row.  Instead of a separate collective
 // the GEMV kernel pushes every element of its partial row into EVERY rank's exchange buffer over NVLink
-// as one 8-byte store {value bits, epoch}: the epoch travels with the value, so a reader that sees the
-// expected epoch has the value (8-byte stores arrive whole) and no fence, flag or barrier is needed.
+// as one 64-bit scalar store {epoch : value bits}: the epoch travels with the value, so a reader that sees the
+// expected epoch has the value (an aligned 64-bit scalar access is single-copy atomic) and no fence, flag or
+// barrier is needed.
 // Each CTA then collects, for ITS OWN rows, the P partial values (all ranks split the rows alike) and
 // adds them in rank order, so every rank stores the same bits.  Waits are bounded.
 //
@@ -170,9 +191,10 @@ __device__ __forceinline__ uint32_t tp_epoch(const PeerComm& c) {
 }
 __device__ __forceinline__ void tp_push(const PeerComm& c, uint32_t e, uint32_t row, float v) {
     const size_t off = tp_slot(e, c.rank, row);
-    const uint32_t bits = __float_as_uint(v);
+    // one 64-bit scalar {epoch : value bits}: a single-copy-atomic access, so the tag and the value arrive together
+    const unsigned long long word = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
     for (uint32_t r = 0; r < c.world; ++r)
-        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(c.buf[r] + off), "r"(bits), "r"(e) : "memory");
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(c.buf[r] + off), "l"(word) : "memory");
 }
 // Called by ALL threads of every CTA after its last tp_push: adds up rows [row_begin, row_end).
 __device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_t row_begin, uint32_t row_end, float* out,
@@ -189,7 +211,10 @@ __device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_
             for (uint32_t r = 0; r < TP_MAX_WORLD; ++r)
                 if (pending >> r & 1u) {
                     const uint8_t* slot = c.buf[c.rank] + tp_slot(e, r, row);
-                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits[r]), "=r"(tag[r]) : "l"(slot) : "memory");
+                    unsigned long long word;
+                    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(slot) : "memory");
+                    bits[r] = (uint32_t)word;
+                    tag[r] = (uint32_t)(word >> 32);
                 }
 #pragma unroll
             for (uint32_t r = 0; r < TP_MAX_WORLD; ++r)

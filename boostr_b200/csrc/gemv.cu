@@ -35,8 +35,6 @@
 //   * Partial sums of the warps of a CTA meet in shared memory and are added in slice order.
 //     When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks
 //     are spread over gridDim.y and a second small kernel adds the partials.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace b200q {
@@ -64,23 +62,10 @@ struct GemvParams {
     uint32_t red_slots;   // slots in the reduction ring (3 or 4)
     uint32_t stage_off;   // byte offset of stage 0
     uint32_t rows_aligned;  // 1 when every row chunk starts and ends on a 16-byte boundary
-    uint32_t contig;        // experiment: one linear copy per stage, rows unpadded
     int act_dtype, out_dtype;
     unsigned long long w_bytes;  // bytes of each weight tensor
     unsigned int* status;        // device status word (bounded-wait timeouts)
 };
-
-#ifdef B200Q_TRACE
-// Debug build only: per-CTA timeline of warps 0/7/15 (nanosecond stamps), read back by the host.
-__device__ unsigned long long g_trace[148 * 3 * 64];
-#define TRACE(slot)                                                                                          \
-    do {                                                                                                     \
-        if (lane == 0 && (warp == 0 || warp == 7 || warp == 15) && (slot) < 64 && blockIdx.x < 148)          \
-            g_trace[(blockIdx.x * 3 + (warp == 0 ? 0 : warp == 7 ? 1 : 2)) * 64 + (slot)] = global_timer_ns(); \
-    } while (0)
-#else
-#define TRACE(slot) do {} while (0)
-#endif
 
 namespace {
 
@@ -691,7 +676,6 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     // stage).  Every warp walks the same cursor, so the role rotates without communication.
     FillCursor pc{blockIdx.x, 0, 0, 0, 0, 0};
     int pw = 0;  // warp that requests fill pc.it
-    TRACE(0);
     // Only two fills leave before the activations are fetched: responses return to an SM in request
     // order, so activation loads issued behind a full ring would wait for every stage to land.
     const uint32_t early = min(2u, p.nstages);
@@ -768,10 +752,6 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_rempty + 8 * js);
     };
-
-    TRACE(1);
-    uint32_t tu = 0;
-    (void)tu;
     uint32_t it = 0, stage = 0, par = 0;          // consumer position in the stage ring
     uint32_t rslot = 0, rpar = 0;                 // reduction ring: slot being written
     uint32_t jslot = 0, jpar = 0, junit = blockIdx.x;  // reduction ring: slab to be reduced next
@@ -809,9 +789,7 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
             for (int c = 0; c < SL; ++c) {
                 if (c < nch) {
                     const uint32_t gc = ks * SL + c;
-                    TRACE(2 + 5 * tu);
                     if (!dead && !mbar_wait(bar_full + 8 * stage, par)) give_up(STATUS_TIMEOUT_FULL);
-                    TRACE(3 + 5 * tu);
                     const uint32_t slice = gc * p.spc + s;
                     if (!dead && slice < p.nslices) {
                         const uint32_t coff = gc * p.spc * SLICE_B;
@@ -845,7 +823,6 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
                 }
             }
         }
-        TRACE(4 + 5 * tu);
         // publish the partial sums in the reduction ring ...
         float* slot = reinterpret_cast<float*>(smem + p.red_off + rslot * p.red_slot_bytes);
         if (!dead && !mbar_wait(bar_rempty + 8 * rslot, rpar ^ 1)) give_up(STATUS_TIMEOUT_EMPTY);
@@ -865,11 +842,8 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
             rpar ^= 1;
         }
         ++published;
-        TRACE(5 + 5 * tu);
         // ... and one warp (taking turns) adds up an older slab, whose partials arrived long ago
         if (published > lag) next_reduce();
-        TRACE(6 + 5 * tu);
-        ++tu;
     }
     while (junit < p.total_units) next_reduce();  // drain the slabs still in the ring
 }
@@ -891,14 +865,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
 cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     auto k = gemv_kernel<FMT, MT, SL, M1, SWIGLU>;
-    static bool attr_set[64] = {};  // per device; setting the attribute is idempotent, races are harmless
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    static PerDeviceOnce attrs;
+    cudaError_t ae = attrs.run([&] { return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024); });
+    if (ae != cudaSuccess) return ae;
     cudaError_t le = launch_pdl(k, grid, dim3(threads), smem, st, p);
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
@@ -936,7 +905,7 @@ int gemv_max_sl(int fmt, int mt) {
 
 struct GemvPlan {
     uint32_t spc, nslices, nchunks, sl, ksplit, rgs, srow, stage_bytes, nstages, total_units, red_off, stage_off;
-    uint32_t red_slot_bytes, red_slots, rows_aligned, contig;
+    uint32_t red_slot_bytes, red_slots, rows_aligned;
     size_t smem;
     int threads;
     dim3 grid;
@@ -970,7 +939,6 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     } else {
         if ((srow & 31) == 0) srow += 16;
     }
-    pl.contig = 0;
     pl.rows_aligned = (row_bytes % 16 == 0 && (pl.spc * slice_b) % 16 == 0) ? 1u : 0u;
     pl.srow = srow;
     pl.stage_bytes = ((16 * pl.rgs * srow + 127) & ~127u) + 128;
@@ -1036,7 +1004,7 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         p.nslices = pl.nslices; p.spc = pl.spc; p.nchunks = pl.nchunks; p.ksplit = pl.ksplit; p.rgs = pl.rgs;
         p.srow = pl.srow; p.stage_bytes = pl.stage_bytes; p.nstages = pl.nstages; p.total_units = pl.total_units;
         p.red_off = pl.red_off; p.stage_off = pl.stage_off;
-        p.red_slot_bytes = pl.red_slot_bytes; p.red_slots = pl.red_slots; p.rows_aligned = pl.rows_aligned; p.contig = pl.contig;
+        p.red_slot_bytes = pl.red_slot_bytes; p.red_slots = pl.red_slots; p.rows_aligned = pl.rows_aligned;
         p.act_dtype = act_dtype; p.out_dtype = out_dtype;
         p.w_bytes = (unsigned long long)N * p.row_bytes;
         p.status = status;
@@ -1070,11 +1038,5 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     }
     return cudaSuccess;
 }
-
-#ifdef B200Q_TRACE
-extern "C" __attribute__((visibility("default"))) int b200q_debug_trace(void* host, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(host, g_trace, bytes < sizeof(g_trace) ? bytes : sizeof(g_trace));
-}
-#endif
 
 }  // namespace b200q

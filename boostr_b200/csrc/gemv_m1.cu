@@ -6,13 +6,14 @@
 //
 // The kernel is bound by HBM: 144 bytes of packed weights per 256 multiply-adds.  Layout of work:
 //   * persistent CTAs, one per SM, each owning a contiguous, evenly sized range of weight rows;
-//   * the rows stream through a 3-stage shared-memory ring, 32 rows (72 KB at K = 4096) per
-//     stage, each stage one 1-D bulk copy (cp.async.bulk) signalled on an mbarrier, so about
-//     150 KB of reads are in flight per SM and no thread spends instructions on loads;
+//   * the rows stream through a ring of up to 16 small fills (8 rows = 18 KB at K = 4096), each
+//     fill one 1-D bulk copy (cp.async.bulk) signalled on an mbarrier and consumed by one group of
+//     four warps (group g takes fills g, g + 4, ...), so about 220 KB of reads are in flight per
+//     SM, no thread spends instructions on loads and the arithmetic starts when 18 KB have landed;
 //   * the activation row is quantised to Q8_K once per CTA (exactly as boostr's CPU path does,
 //     src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98) and every lane keeps the int8 codes
 //     of ONE 256-wide block in registers for the whole kernel;
-//   * a warp takes two rows of a stage; lane (h, b) multiplies block b of row h against its
+//   * a warp takes two rows of a fill; lane (h, b) multiplies block b of row h against its
 //     register-resident activation block with dp4a: 128-bit shared loads, nibbles unpacked with
 //     one AND each (high nibbles stay in place and are divided out of the integer sum), 6-bit
 //     scales and mins unpacked with a handful of byte-parallel logic ops, the min term through
@@ -23,23 +24,6 @@
 #include "common.cuh"
 
 namespace b200q {
-
-#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
-// Debug build only: nanosecond stamps of thread 0 of every CTA of the last 64 launches.
-__device__ unsigned long long g_trace_m1[64 * 148 * 16];
-static unsigned g_trace_m1_next = 0;
-#define TRACE1(idx, slot)                                                                                    \
-    do {                                                                                                     \
-        if (threadIdx.x == 0 && blockIdx.x < 148) g_trace_m1[(((idx) & 63) * 148 + blockIdx.x) * 16 + (slot)] = global_timer_ns(); \
-    } while (0)
-#define TRACE1MAX(idx, slot)                                                                                 \
-    do {                                                                                                     \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 148) atomicMax(&g_trace_m1[(((idx) & 63) * 148 + blockIdx.x) * 16 + (slot)], global_timer_ns()); \
-    } while (0)
-#else
-#define TRACE1(idx, slot) do {} while (0)
-#define TRACE1MAX(idx, slot) do {} while (0)
-#endif
 
 struct GemvM1Params {
     // Up to three weights that share the activation row (q/k/v-style batches) form one virtual row
@@ -60,7 +44,6 @@ struct GemvM1Params {
     uint32_t act_off, stage_off;
     int act_dtype, out_dtype;
     unsigned int* status;
-    uint32_t trace_idx, dbg;
     PeerComm comm;  // row-parallel shard: push the partial row to every rank and add them up (single weight, f32 out)
 };
 
@@ -150,7 +133,6 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
     const uint32_t bar_full = smem_u32(smem), bar_empty = bar_full + 128;
     uint8_t* act_s = smem + p.act_off;
     const uint32_t stage0 = smem_u32(smem + p.stage_off);
-    TRACE1(p.trace_idx, 0);
 
     const uint32_t row_begin = cta * p.rows_per_cta;
     const uint32_t row_end = min(p.N, row_begin + p.rows_per_cta);
@@ -192,10 +174,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
     }
     __syncthreads();
     if (warp == 15 && lane < 2 && (uint32_t)lane < nfill) issue_fill(lane, lane);
-    TRACE1MAX(p.trace_idx, 1);
     grid_dep_launch();  // the next kernel may start its own weight prefetch as SMs free up
     grid_dep_wait();    // the previous kernel's output (our activations) is complete from here on
-    TRACE1(p.trace_idx, 2);
     const bool tp = !SWIGLU && p.comm.world > 1;
     const uint32_t tp_e = tp ? tp_epoch(p.comm) : 0u;
 
@@ -203,15 +183,10 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
     // its share of the remaining first fills
     {
         float v[8];
-#ifdef B200Q_TRACE
-        const bool on = (uint32_t)warp < p.nblk && !(p.dbg & 2);
-#else
         const bool on = (uint32_t)warp < p.nblk;
-#endif
         if (on) load_act8(p.act, p.act_dtype, (size_t)warp * 256 + 8 * lane, v);
         const uint32_t f1 = 2 + (uint32_t)warp;  // the rest of the ring: one fill per warp
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
-        TRACE1(p.trace_idx, 7);
         if (on) {  // warp-uniform
             uint2 packed;
             int s;
@@ -228,10 +203,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             }
             if (lane == 0) *reinterpret_cast<float*>(blk + 272) = d8;
         }
-        TRACE1(p.trace_idx, 8);
     }
     __syncthreads();  // barriers initialised, activation image complete
-    TRACE1(p.trace_idx, 3);
 
     // 2. this lane's activation block goes to registers
     const int b = lane & (lpr - 1), h = lane >> lpr_log;
@@ -250,8 +223,6 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         bs_lo[0] = q.x; bs_lo[1] = q.y; bs_hi[0] = q.z; bs_hi[1] = q.w;
         d8 = blk_on ? *reinterpret_cast<const float*>(blk + 272) : 0.f;
     }
-
-    TRACE1(p.trace_idx, 10);
     const uint32_t grp = (uint32_t)warp >> 2, wi = (uint32_t)warp & 3;
     const uint32_t rr = SWIGLU ? wi : rpw * wi + h;  // output row of the fill handled by this lane group
     bool dead = false;
@@ -261,16 +232,10 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             dead = true;
             atomicOr(p.status, STATUS_TIMEOUT_FULL);
         }
-        if (f == 0) TRACE1(p.trace_idx, 4);
-        if (f + 1 == nfill) TRACE1MAX(p.trace_idx, 5);
         const uint32_t r0 = row_begin + f * FR;
         const uint32_t nrows = min(FR, row_end - r0);
         float term = 0.f;
-#ifdef B200Q_TRACE
-        if (!dead && rr < nrows && blk_on && !(p.dbg & 4)) {
-#else
         if (!dead && rr < nrows && blk_on) {
-#endif
             const uint8_t* blk = smem + p.stage_off + slot * p.stage_bytes + (SWIGLU ? FR * h + wi : rr) * p.row_bytes + b * 144;
             const uint4 hd = *reinterpret_cast<const uint4*>(blk);
             // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
@@ -307,7 +272,6 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             term = __fsub_rn(__fmul_rn(__fmul_rn(d, d8), (float)sumi), __fmul_rn(__fmul_rn(dmin, d8), (float)summ));
         }
         __syncwarp();
-        if (f == 0) TRACE1(p.trace_idx, 11);
         if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
         // add the block terms of a row (lpr lanes)
 #pragma unroll
@@ -341,7 +305,6 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             par ^= 1;
         }
     }
-    TRACE1MAX(p.trace_idx, 6);
     if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out[0]), p.status);
 }
 
@@ -662,12 +625,6 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
     p.N = (uint32_t)N;
     p.nblk = (uint32_t)(K / 256);
     p.row_bytes = p.nblk * 144;
-#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
-    p.trace_idx = g_trace_m1_next++;
-#endif
-#ifdef B200Q_TRACE
-    { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
-#endif
     p.lpr = 1;
     while (p.lpr < p.nblk) p.lpr *= 2;
     if (p.lpr < 2) p.lpr = 2;
@@ -688,10 +645,8 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
 }
 
 static cudaError_t m1_attrs() {
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || attr_set[dev]) return cudaSuccess;
+    static PerDeviceOnce attrs;
+    return attrs.run([] {
     const int v = (int)M1_SMEM_MAX;
     cudaError_t e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
@@ -699,8 +654,8 @@ static cudaError_t m1_attrs() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_q6k_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_mixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, v);
-    if (e == cudaSuccess) attr_set[dev] = true;
     return e;
+    });
 }
 
 static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
@@ -789,11 +744,5 @@ cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* 
     if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
     return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status);
 }
-
-#if defined(B200Q_TRACE) && !defined(B200Q_NOSTAMP)
-extern "C" __attribute__((visibility("default"))) int b200q_debug_trace_m1(void* host, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(host, g_trace_m1, bytes < sizeof(g_trace_m1) ? bytes : sizeof(g_trace_m1));
-}
-#endif
 
 }  // namespace b200q

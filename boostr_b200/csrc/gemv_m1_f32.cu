@@ -229,15 +229,13 @@ cudaError_t launch_gemv_m1_f32(int fmt, const void* act, int act_dtype, const vo
     p.out_dtype = out_dtype;
     p.status = status;
     const size_t smem = p.stage_off + (size_t)p.nstages * p.stage_bytes + 64;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    static PerDeviceOnce attrs;
+    cudaError_t ae = attrs.run([] {
         cudaError_t e = cudaFuncSetAttribute(gemv_m1_f32_kernel<FMT_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_m1_f32_kernel<FMT_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+        return e;
+    });
+    if (ae != cudaSuccess) return ae;
     cudaError_t le = fmt == FMT_Q8_0 ? launch_pdl(gemv_m1_f32_kernel<FMT_Q8_0>, dim3((unsigned)grid), dim3(512), smem, st, p)
                                      : launch_pdl(gemv_m1_f32_kernel<FMT_Q4_0>, dim3((unsigned)grid), dim3(512), smem, st, p);
     note_launch();

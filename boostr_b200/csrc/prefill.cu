@@ -47,7 +47,6 @@ struct PrefillParams {
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
     int out_dtype;
     unsigned int* status;
-    uint32_t dbg;  // debug builds only: phases switched off for timing experiments
 };
 
 namespace {
@@ -466,12 +465,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                         }
-#ifdef B200Q_TRACE
-                        if (p.dbg & 1) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) o[i] = cur.q0.x;
-                        } else
-#endif
                         decode32_q4k(cur, kt, half, o);
                     } else if constexpr (FMT == FMT_Q6_K) {
                         if (ok) decode32_q6k<true>(rrow, kt, half, o);
@@ -500,11 +493,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     *dead_flag = 1;
                     ok = false;
                 }
-#ifdef B200Q_TRACE
-                if (ok && !(p.dbg & 2)) {
-#else
                 if (ok) {
-#endif
                     uint8_t* arow = smem + 1024 + raw_bytes + s * A_TILE_BYTES + r * 128;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
@@ -605,14 +594,9 @@ uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
 
 template <int FMT, bool RAW>
 cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<FMT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
+    static PerDeviceOnce attrs;
+    cudaError_t ae = attrs.run([] { return cudaFuncSetAttribute(prefill_kernel<FMT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024); });
+    if (ae != cudaSuccess) return ae;
     prefill_kernel<FMT, RAW><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
     note_launch();
     return cudaGetLastError();
@@ -680,14 +664,8 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
     uint32_t nsa = 4;
-#ifdef B200Q_TRACE
-    { const char* e = getenv("B200Q_PF_NSA"); if (e && atoi(e) >= 2 && atoi(e) <= 8) nsa = atoi(e); }
-#endif
     uint32_t nsb = (budget - nsa * A_TILE_BYTES) / b_tile;
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
-#ifdef B200Q_TRACE
-    { const char* e = getenv("B200Q_PF_NSB"); if (e && atoi(e) >= 2 && (uint32_t)atoi(e) < nsb) nsb = atoi(e); }
-#endif
     if (nsa > p.nkt) nsa = p.nkt;
     if (nsb > p.nkt) nsb = p.nkt;
     p.nsa = nsa;
@@ -696,9 +674,6 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
     p.out_dtype = out_dtype;
     p.status = status;
-#ifdef B200Q_TRACE
-    { const char* e = getenv("B200Q_DBG"); p.dbg = e ? atoi(e) : 0; }
-#endif
     const size_t smem = 2048 + raw_bytes + (size_t)nsa * A_TILE_BYTES + (size_t)nsb * b_tile;
 
     CUtensorMap map;

@@ -527,23 +527,78 @@ static void mm_chunk(const mm_job *J) {
     }
 }
 
+/* Persistent worker pool (rayon keeps one too: src/quant/cpu/kernels/quant_matmul.rs:138 runs on the
+ * global rayon pool).  Workers sleep on a condition variable between calls; a call publishes its job
+ * array under a new generation number, workers and the caller claim chunks with an atomic counter, and
+ * the caller waits until every claimed chunk has finished.  One call at a time (calls serialise on
+ * run_mu); the pool only grows. */
+#define MM_MAX_WORKERS 256
 typedef struct {
+    pthread_mutex_t mu, run_mu;
+    pthread_cond_t wake, done;
+    pthread_t th[MM_MAX_WORKERS];
+    size_t nworkers;
+    unsigned long generation;
     mm_job *jobs;
-    size_t njobs;
-    size_t next; /* guarded by mu: a work queue, as rayon's par_iter over col_ranges */
-    pthread_mutex_t mu;
+    size_t njobs, active_limit; /* workers with index >= active_limit sit a call out */
+    size_t next;                /* atomic: next chunk to claim */
+    size_t finished;            /* guarded by mu: workers that have drained the queue of this generation */
+    size_t participants;
 } mm_pool;
+static mm_pool g_pool = {PTHREAD_MUTEX_INITIALIZER, PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER,
+                         PTHREAD_COND_INITIALIZER, {0}, 0, 0, NULL, 0, 0, 0, 0, 0};
 
-static void *mm_worker(void *p) {
-    mm_pool *P = (mm_pool *)p;
+static void mm_drain(mm_pool *P) {
     for (;;) {
-        pthread_mutex_lock(&P->mu);
-        size_t i = P->next++;
-        pthread_mutex_unlock(&P->mu);
+        size_t i = __atomic_fetch_add(&P->next, 1, __ATOMIC_RELAXED);
         if (i >= P->njobs) break;
         mm_chunk(&P->jobs[i]);
     }
+}
+
+static void *mm_worker(void *arg) {
+    mm_pool *P = &g_pool;
+    size_t me = (size_t)(uintptr_t)arg;
+    unsigned long seen = 0;
+    pthread_mutex_lock(&P->mu);
+    for (;;) {
+        while (P->generation == seen) pthread_cond_wait(&P->wake, &P->mu);
+        seen = P->generation;
+        if (me >= P->active_limit) continue;
+        pthread_mutex_unlock(&P->mu);
+        mm_drain(P);
+        pthread_mutex_lock(&P->mu);
+        if (++P->finished == P->participants) pthread_cond_signal(&P->done);
+    }
     return NULL;
+}
+
+/* Runs jobs[0..njobs) on `threads` threads (the caller is one of them). */
+static void mm_run(mm_job *jobs, size_t njobs, size_t threads) {
+    mm_pool *P = &g_pool;
+    if (threads > MM_MAX_WORKERS + 1) threads = MM_MAX_WORKERS + 1;
+    pthread_mutex_lock(&P->run_mu);
+    pthread_mutex_lock(&P->mu);
+    while (P->nworkers + 1 < threads) {
+        if (pthread_create(&P->th[P->nworkers], NULL, mm_worker, (void *)(uintptr_t)P->nworkers) != 0) break;
+        pthread_detach(P->th[P->nworkers]);
+        P->nworkers++;
+    }
+    size_t helpers = threads - 1 < P->nworkers ? threads - 1 : P->nworkers;
+    P->jobs = jobs;
+    P->njobs = njobs;
+    P->active_limit = helpers;
+    P->participants = helpers;
+    P->finished = 0;
+    __atomic_store_n(&P->next, 0, __ATOMIC_RELAXED);
+    P->generation++;
+    pthread_cond_broadcast(&P->wake);
+    pthread_mutex_unlock(&P->mu);
+    mm_drain(P);
+    pthread_mutex_lock(&P->mu);
+    while (P->finished < P->participants) pthread_cond_wait(&P->done, &P->mu);
+    pthread_mutex_unlock(&P->mu);
+    pthread_mutex_unlock(&P->run_mu);
 }
 
 /* quant_matmul_f32: src/quant/cpu/kernels/quant_matmul.rs:55-212.
@@ -582,17 +637,7 @@ ORACLE_API int oracle_quant_matmul(int fmt, const float *act, const uint8_t *w, 
     if (threads == 1 || njobs <= 1) {
         for (size_t c = 0; c < njobs; c++) mm_chunk(&jobs[c]);
     } else {
-        mm_pool P;
-        P.jobs = jobs;
-        P.njobs = njobs;
-        P.next = 0;
-        pthread_mutex_init(&P.mu, NULL);
-        size_t nt = (size_t)threads < njobs ? (size_t)threads : njobs;
-        pthread_t *th = (pthread_t *)malloc(sizeof(pthread_t) * nt);
-        for (size_t t = 0; t < nt; t++) pthread_create(&th[t], NULL, mm_worker, &P);
-        for (size_t t = 0; t < nt; t++) pthread_join(th[t], NULL);
-        pthread_mutex_destroy(&P.mu);
-        free(th);
+        mm_run(jobs, njobs, (size_t)threads < njobs ? (size_t)threads : njobs);
     }
     free(jobs);
     free(aq);
