@@ -26,7 +26,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32
+HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32  # the shapes boostr_b200.decode_stack builds
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -154,91 +154,34 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- GPU arm
 
-
-def device_weight(fmt, n, k, gen):
-    """Synthetic packed weight generated on the device: uniform random codes and scale bytes, then
-    every block's fp16 super-scale(s) overwritten with |N(0,1)| * c so all values are finite."""
-    import torch
-
-    from boostr_b200.format import QuantFormat as F
-    from boostr_b200.tensor import QuantTensor
-
-    f = F.parse(fmt)
-    nb = n * (k // f.block_size)
-    w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device="cuda", generator=gen)
-    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q6_K": 0.0005}[f.name]
-    d = (torch.randn(nb, device="cuda", generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
-    if f is F.Q6_K:
-        w[:, 208:210] = d
-    else:
-        w[:, 0:2] = d
-        if f is F.Q4_K:
-            w[:, 2:4] = d
-    return QuantTensor(w.reshape(-1), f, (n, k))
-
-
-class DecodeStack:
-    """The quantized linears of the Llama-3-8B-shaped stack, sharded for this rank."""
-
-    def __init__(self, m, rank, world, layers=LAYERS):
-        import torch
-
-        from boostr_b200.linear import QuantLinear
-        from boostr_b200.tensor_parallel import ColumnParallelQuantLinear, RowParallelQuantLinear
-
-        self.m, self.rank, self.world = m, rank, world
-        gen = torch.Generator(device="cuda")
-        gen.manual_seed(0xB200 + rank)
-        p = world
-        self.layers = []
-        for _ in range(layers):
-            L = {}
-            for name, fmt, n, k, split in LAYER_SPEC:
-                if split == "col":
-                    L[name] = ColumnParallelQuantLinear(device_weight(fmt, n // p, k, gen))
-                else:
-                    L[name] = RowParallelQuantLinear(device_weight(fmt, n, k // p, gen))
-            L["qkv"] = [QuantLinear(L["q"].weight), QuantLinear(L["k"].weight), QuantLinear(L["v"].weight)]
-            self.layers.append(L)
-        self.lm_head = ColumnParallelQuantLinear(device_weight("Q6_K", VOCAB // p, HIDDEN, gen))
-        f32 = dict(dtype=torch.float32, device="cuda")
-        self.x = torch.randn(m, HIDDEN, generator=gen, **f32)           # step input (hidden state)
-        self.q = torch.empty(m, HIDDEN // p, **f32)
-        self.k = torch.empty(m, KV // p, **f32)
-        self.v = torch.empty(m, KV // p, **f32)
-        self.o = torch.empty(m, HIDDEN, **f32)
-        self.h = torch.empty(m, FFN // p, **f32)
-        self.d = torch.empty(m, HIDDEN, **f32)
-        self.logits_local = torch.empty(m, VOCAB // p, **f32)
-        self.logits = torch.empty(m, VOCAB, **f32) if p > 1 else self.logits_local
-        self.bytes_local = sum(w.storage_bytes() for L in self.layers for w in
-                               [L[n].weight for n, *_ in LAYER_SPEC]) + self.lm_head.weight.storage_bytes()
-
-    def step(self):
-        """One decode step.  Within a layer the data flows q -> o -> gate/up -> down as in the
-        model (attention itself is not part of this path: o_proj consumes the q projection);
-        every layer starts again from the step input so magnitudes stay finite without the
-        model's normalisation layers."""
-        from boostr_b200 import ops
-        from boostr_b200.linear import QuantLinear
-        from boostr_b200.tensor_parallel import all_reduce_tensor, gather_from_ranks
-
-        for L in self.layers:
-            QuantLinear.forward_batch(L["qkv"], self.x, outs=[self.q, self.k, self.v])   # column-parallel
-            L["o"].forward(self.q, out=self.o)                      # row-parallel: all-reduce inside
-            ops.quant_swiglu(self.o, L["gate"].weight, L["up"].weight, out=self.h)
-            L["down"].forward(self.h, out=self.d)                   # row-parallel: all-reduce inside
-        self.lm_head.forward(self.x, out=self.logits_local)
-        if self.world > 1:
-            gather_from_ranks(self.logits_local, out=self.logits)
-        return self.logits
-
-
 # DRAM bytes (read + written) of one launch of the dominant kernel at one GPU, from the ncu capture
 # summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.262 MB, dram__bytes_write.sum 2 KB.
 # A K-split shard streams proportionally fewer bytes, so the figure is scaled by the shard's packed bytes.
 NCU_TRAFFIC_DOWN_1GPU = 48_264_148
 NCU_ALGORITHMIC_DOWN_1GPU = 4096 * 56 * 210
+REGION_REPEATS = 30
+
+
+def timed_graph(torch, fn, reps, warm=2):
+    """Captures `fn` (a sequence of library calls on distinct weights) in a CUDA graph and returns the
+    median / min / max device time of one replay in microseconds over `reps` replays (CUDA events)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1000.0)
+    return statistics.median(ts), min(ts), max(ts)
 
 
 def time_kernel_family(stack, torch, ops):
@@ -248,24 +191,119 @@ def time_kernel_family(stack, torch, ops):
     ws = [L["down"].weight for L in stack.layers]
     x = torch.randn(stack.m, ws[0].shape[1], device="cuda")
     outs = torch.empty(stack.m, ws[0].shape[0], device="cuda")
-    for w in ws[:3]:
-        ops.quant_matmul(x, w, out=outs)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+
+    def run():
         for w in ws:
             ops.quant_matmul(x, w, out=outs)
-    g.replay()
+
+    med, lo, hi = timed_graph(torch, run, reps=20)
+    return med / len(ws), ws[0].storage_bytes()
+
+
+def per_config(torch, ops, pk, world, rank):
+    """Device time of every reference configuration that is not the headline workload, each on enough
+    distinct weight copies that the rotation exceeds four times the L2 (so every launch streams from HBM),
+    replayed as one CUDA graph; median over 10 replays divided by the number of copies.
+    At N > 1 only the sharded configurations run (C3: N-split, no communication; C4: N-split + gather)."""
+    from boostr_b200 import synth
+    from boostr_b200.format import QuantFormat as F
+    from boostr_b200.tensor_parallel import gather_from_ranks
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0xC0F + rank)
+    out = {}
+    l2x4 = 4 * L2_BYTES
+
+    def gemv_case(key, fmt, m, n, k, dt=torch.float32, gather=False):
+        f = F.parse(fmt)
+        nl = n // world
+        wbytes = f.storage_bytes(nl * k)
+        copies = max(2, -(-l2x4 // wbytes))
+        ws = [synth.device_weight(fmt, nl, k, gen) for _ in range(copies)]
+        x = torch.randn(m, k, device="cuda", generator=gen).to(dt)
+        y = torch.empty(m, nl, device="cuda")
+        full = torch.empty(m, n, device="cuda") if gather and world > 1 else None
+
+        def run():
+            for w in ws:
+                ops.quant_matmul(x, w, out=y)
+                if full is not None:
+                    gather_from_ranks(y, out=full)
+
+        med, lo, hi = timed_graph(torch, run, reps=10)
+        us = med / copies
+        r = {"us": us, "us_min": lo / copies, "us_max": hi / copies, "copies": copies, "rows_per_rank": nl}
+        flops = 2.0 * m * nl * k
+        if m >= 64:
+            r["tflops"] = flops / us / 1e6
+            r["frac_measured"] = r["tflops"] / pk["bf16_tflops"]
+            r["frac_nominal"] = r["tflops"] / 2250.0
+        else:
+            r["gbs"] = wbytes / us / 1e3
+            r["frac_measured"] = r["gbs"] / pk["hbm_gbs"]
+            r["frac_nominal"] = r["gbs"] / 8000.0
+        out[key] = r
+        del ws
+
+    if world == 1:
+        gemv_case("C1 Q4_0 M=1 [4096x4096]", "Q4_0", 1, 4096, 4096)
+        for m in (1, 8, 32):
+            gemv_case(f"C2 Q8_0 M={m} [11008x4096]", "Q8_0", m, 11008, 4096)
+    for m in (512, 2048):
+        gemv_case(f"C3 Q4_K M={m} [14336x4096] bf16 acts", "Q4_K", m, 14336, 4096, dt=torch.bfloat16)
+    for m in (1, 16):
+        gemv_case(f"C4 Q6_K M={m} [128256x4096] lm-head" + (" + gather" if world > 1 else ""), "Q6_K", m, 128256, 4096, gather=True)
+    if world == 1:
+        # dequant Q4_K -> bf16: packed bytes in + 2 bytes per element out
+        n, k = 14336, 4096
+        ws = [synth.device_weight("Q4_K", n, k, gen) for _ in range(4)]
+
+        def run():
+            for w in ws:
+                ops.dequantize(w, torch.bfloat16)
+
+        med, lo, hi = timed_graph(torch, run, reps=10)
+        us = med / len(ws)
+        nbytes = ws[0].storage_bytes() + 2 * n * k
+        out["dequant Q4_K->bf16 [14336x4096]"] = {"us": us, "gbs": nbytes / us / 1e3, "frac_measured": nbytes / us / 1e3 / pk["hbm_gbs"],
+                                                  "frac_nominal": nbytes / us / 1e3 / 8000.0, "bytes_in_plus_out": nbytes}
+    return out
+
+
+def c5_batched(stack, torch, dist, ops, m2, world, steps=5, repeats=5):
+    """The same decode stack (same weights) with m2 tokens per step: median ms/step of `repeats` regions of
+    `steps` graph replays, max over ranks.  Row-parallel layers with more than one token use the library's
+    product followed by the process group's all-reduce."""
+    from boostr_b200.decode_graph import DecodeGraph
+    from boostr_b200.decode_stack import DecodeStack
+
+    st = DecodeStack(m2, stack.rank, world, weights=stack.layers, lm_head=stack.lm_head)
+    st.use_exchange(stack.exchange)
+    st.step()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 5
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1000.0 / (reps * len(ws))
-    return us, ws[0].storage_bytes()
+    runner = DecodeGraph(st.step, {"x": st.x}, {"logits": st.logits}).capture()
+    for _ in range(3):
+        runner.graph.replay()
+    ts = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            runner.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / steps)
+    t = torch.tensor(ts, device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = statistics.median(float(v) for v in t.tolist())
+    gbs = STEP_BYTES / (ms * 1e-3) / 1e9
+    return {"ms_per_step": ms, "tokens_per_s": m2 * 1000.0 / ms, "step_weight_gbs_per_gpu": gbs / world,
+            "frac_measured_per_gpu": gbs / world / peaks()["hbm_gbs"], "frac_of_8tbs_per_gpu": gbs / world / 8000.0,
+            "tflops": 2.0 * m2 * 7_504_658_432 / (ms * 1e-3) / 1e12}
 
 
 def log(msg):
@@ -274,11 +312,42 @@ def log(msg):
         sys.stderr.flush()
 
 
+def tp_parity(stack, torch, dist, ops, exchange):
+    """Cross-GPU correctness of the timed path, outside the timed region: one eager step through the fused
+    row-parallel exchange against one through NCCL's all-reduce (last layer's down-projection output and the
+    gathered logits), and every rank must hold the same bits of the fused result."""
+    world = dist.get_world_size()
+    stack.use_exchange(exchange)
+    stack.step()
+    ops.check_device_status()
+    d_f, lg_f = stack.d.clone(), stack.logits.clone()
+    stack.use_exchange(None)
+    stack.step()
+    torch.cuda.synchronize()
+    d_n, lg_n = stack.d.clone(), stack.logits.clone()
+    stack.use_exchange(exchange)
+    rel = max(float((d_f - d_n).abs().max() / d_n.abs().max().clamp_min(1e-30)),
+              float((lg_f - lg_n).abs().max() / lg_n.abs().max().clamp_min(1e-30)))
+    got = [torch.empty_like(d_f) for _ in range(world)]
+    dist.all_gather(got, d_f)
+    same = all(torch.equal(g.view(torch.int32), d_f.view(torch.int32)) for g in got)
+    got = [torch.empty_like(lg_f) for _ in range(world)]
+    dist.all_gather(got, lg_f)
+    same = same and all(torch.equal(g.view(torch.int32), lg_f.view(torch.int32)) for g in got)
+    finite = bool(torch.isfinite(d_f).all() and torch.isfinite(lg_f).all())
+    flag = torch.tensor([rel, 0.0 if (same and finite) else 1.0], device="cuda", dtype=torch.float64)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return {"max_rel": float(flag[0]), "ranks_bit_identical": bool(flag[1] == 0.0), "compared": "last layer down-projection output "
+            "[M,4096] and gathered logits [M,128256]: fused peer exchange vs NCCL all-reduce, eager step"}, d_f
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     from boostr_b200 import ops
+    from boostr_b200.decode_graph import DecodeGraph
+    from boostr_b200.decode_stack import DecodeStack
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -288,13 +357,21 @@ def run_ours(args):
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
     torch.cuda.set_device(local_rank)
     m = args.m
+    pk = peaks()
     stack = DecodeStack(m, rank, world)
     torch.cuda.synchronize()
     log("stack built")
-    # the dominant kernel is timed on rank 0 before any process group exists: a graph capture on
-    # one rank while NCCL's watchdog threads are alive and the other ranks sit in a collective can stall
+    # kernel-family and per-configuration timings run before any process group exists (one-GPU figures on
+    # rank 0; the sharded configurations on every rank, no collective inside): a graph capture on one rank
+    # while NCCL's watchdog threads are alive and the other ranks sit in a collective can stall
     k_us, k_bytes = time_kernel_family(stack, torch, ops) if rank == 0 else (0.0, 0)
     log("kernel family timed")
+    configs = {}
+    if not args.no_per_config and world == 1:
+        configs = per_config(torch, ops, pk, 1, 0)
+        log("per-config timed")
+    exchange = None
+    parity = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -302,11 +379,16 @@ def run_ours(args):
         if args.collective == "fused":
             from boostr_b200.tensor_parallel import PeerExchange
 
-            stack.exchange = PeerExchange()
-            for L in stack.layers:
-                L["o"].exchange = stack.exchange
-                L["down"].exchange = stack.exchange
+            exchange = PeerExchange()
+            stack.use_exchange(exchange)
             log("peer exchange mapped")
+            parity, d_eager = tp_parity(stack, torch, dist, ops, exchange)
+            log(f"tp parity {parity}")
+            if parity["max_rel"] > 2e-6 or not parity["ranks_bit_identical"]:
+                if rank == 0:
+                    print(json.dumps({"error": "tensor-parallel parity check failed", "tp_parity": parity}), flush=True)
+                sys.stdout.flush()
+                os._exit(3)
 
     def barrier():
         if world > 1:
@@ -319,28 +401,20 @@ def run_ours(args):
     torch.cuda.synchronize()
     launches_per_step = ops.launch_count() - launches0
     log(f"eager step done, {launches_per_step} launches")
-    use_graph = not args.no_graph
-    graph = None
-    if use_graph:
+    runner = DecodeGraph(stack.step, {"x": stack.x}, {"logits": stack.logits, "d": stack.d})
+    graph_ok = False
+    if not args.no_graph:
         try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                stack.step()
-            torch.cuda.current_stream().wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            log("side-stream step done; capturing")
-            with torch.cuda.graph(graph):
-                stack.step()
+            runner.capture()
+            graph_ok = True
             log("captured")
         except Exception as e:  # capture of a collective can be refused; fall back to eager launches
-            graph = None
             sys.stderr.write(f"[bench] CUDA graph capture failed, running eagerly: {e}\n")
             torch.cuda.synchronize()
 
     def one_step():
-        if graph is not None:
-            graph.replay()
+        if graph_ok:
+            runner.graph.replay()
         else:
             stack.step()
 
@@ -348,53 +422,79 @@ def run_ours(args):
         one_step()
     barrier()
     log("warm-up done")
+    if parity is not None:
+        # the replayed graph (fused exchange included, epoch carried in device memory) must give the eager bits
+        parity["graph_replay_bit_identical"] = bool(torch.equal(stack.d.view(torch.int32), d_eager.view(torch.int32)))
 
-    # ---- device-resident timing: K steps, CUDA events, max over ranks
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    # ---- device-resident timing: the K-step region, CUDA events, max over ranks; the region is repeated
+    # REGION_REPEATS times and the median is reported (min / max beside it)
+    regions = []
     with ClockSampler(local_rank) as clk:
-        barrier()
-        ev[0].record()
-        for _ in range(args.steps):
-            one_step()
-        ev[1].record()
-        barrier()
-    ms_total = ev[0].elapsed_time(ev[1])
+        for _ in range(REGION_REPEATS):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            barrier()
+            ev[0].record()
+            for _ in range(args.steps):
+                one_step()
+            ev[1].record()
+            barrier()
+            regions.append(ev[0].elapsed_time(ev[1]))
+    t = torch.tensor(regions, device="cuda", dtype=torch.float64)
     if world > 1:
-        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
+    regions = [float(v) / args.steps for v in t.tolist()]
+    ms_per_step = statistics.median(regions)
     ops.check_device_status()
     log(f"timed region done: {ms_per_step:.3f} ms/step")
 
     # ---- end to end: host activations in, host logits out, every step
-    x_host = torch.randn(m, HIDDEN).pin_memory()
-    logits_host = torch.empty(m, VOCAB).pin_memory()
-    for _ in range(2):
-        stack.x.copy_(x_host, non_blocking=True)
-        one_step()
-        logits_host.copy_(stack.logits, non_blocking=True)
-    barrier()
-    ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev2[0].record()
-    for _ in range(args.steps):
-        stack.x.copy_(x_host, non_blocking=True)
-        one_step()
-        logits_host.copy_(stack.logits, non_blocking=True)
-    ev2[1].record()
-    barrier()
-    e2e_ms = ev2[0].elapsed_time(ev2[1])
-    if world > 1:
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_ms /= args.steps
-    log("e2e done")
+    x_host = torch.randn(m, stack.hidden).pin_memory()
+    logits_host = torch.empty(m, stack.vocab).pin_memory()
 
+    def e2e_step():
+        stack.x.copy_(x_host, non_blocking=True)
+        one_step()
+        logits_host.copy_(stack.logits, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_regions = []
+    for _ in range(REGION_REPEATS):
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        barrier()
+        ev2[0].record()
+        for _ in range(args.steps):
+            e2e_step()
+        ev2[1].record()
+        barrier()
+        e2e_regions.append(ev2[0].elapsed_time(ev2[1]))
+    t = torch.tensor(e2e_regions, device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = statistics.median(float(v) / args.steps for v in t.tolist())
+    log("e2e done")
     clocks = clk.summary()
+
+    if world > 1 and not args.no_per_config:
+        # sharded configurations per rank (C3 N-split; C4 N-split + gather of the logits), after the
+        # headline numbers; rank 0 reports its own figures (all ranks do the same work)
+        try:
+            configs = per_config(torch, ops, pk, world, rank)
+        except Exception as e:
+            configs = {"error": f"{type(e).__name__}: {e}"}
+        barrier()
+        log("per-config timed")
+    if not args.no_per_config and m == 1:
+        for m2 in (16, 64):
+            try:
+                configs[f"C5 decode step M={m2}"] = c5_batched(stack, torch, dist, ops, m2, world)
+            except Exception as e:
+                configs[f"C5 decode step M={m2}"] = {"error": f"{type(e).__name__}: {e}"}
+            barrier()
+        log("batched C5 timed")
+
     result = None
     if rank == 0:
-        pk = peaks()
         achieved = k_bytes / k_us / 1e3  # GB/s
         step_gbs = STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         result = {
@@ -407,14 +507,17 @@ def run_ours(args):
                        "parallelism": f"tp{world}", "row_parallel_reduce": (args.collective if world > 1 else "none"),
                        "packed_weight_bytes_per_step": STEP_BYTES,
                        "l2": "weights per step per rank exceed L2 (%d MB > 126 MB)" % (stack.bytes_local // 2**20),
-                       "cuda_graph": graph is not None},
-            "step_weight_gbs": step_gbs, "step_frac_of_8tbs": step_gbs / 8000.0,
-            "e2e": {"value": m * 1000.0 / e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": m * HIDDEN * 4,
-                    "d2h_bytes_per_step": m * VOCAB * 4},
+                       "cuda_graph": graph_ok},
+            "timed_regions": {"repeats": REGION_REPEATS, "steps_each": args.steps, "ms_per_step_median": ms_per_step,
+                              "ms_per_step_min": min(regions), "ms_per_step_max": max(regions)},
+            "step_weight_gbs": step_gbs, "step_weight_gbs_per_gpu": step_gbs / world,
+            "step_frac_of_8tbs_per_gpu": step_gbs / world / 8000.0,
+            "e2e": {"value": m * 1000.0 / e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": m * stack.hidden * 4,
+                    "d2h_bytes_per_step": m * stack.vocab * 4},
             "gpu_launches": int(launches_per_step * args.steps),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "Q6_K decode GEMV, down-projection shard [%d x %d], M=%d" % (
-                             HIDDEN, stack.layers[0]["down"].weight.shape[1], m),
+                             stack.hidden, stack.layers[0]["down"].weight.shape[1], m),
                          "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                          "frac_of_8tbs": achieved / 8000.0, "peak_source": pk["source"], "avg_launch_us": k_us,
                          "algorithmic_bytes_per_launch": k_bytes,
@@ -422,6 +525,10 @@ def run_ours(args):
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 1 GPU "
                                            "(profiles/gemv_m1_q6k_down.md), scaled by the shard's packed bytes"},
         }
+        if parity is not None:
+            result["tp_parity"] = parity
+        if configs:
+            result["per_config"] = configs
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_reference(m, budget_s=args.cpu_seconds)
     return result
@@ -508,6 +615,7 @@ def main():
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="row-parallel all-reduce at N > 1: fused into the GEMV kernel over peer memory, or NCCL")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the per-configuration kernel timings")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     res = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -16,24 +16,7 @@ import argparse
 import sys
 
 
-def device_weight(fmt: str, n: int, k: int, gen):
-    import torch
-
-    from .format import QuantFormat as F
-    from .tensor import QuantTensor
-
-    f = F.parse(fmt)
-    nb = n * (k // f.block_size)
-    w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device="cuda", generator=gen)
-    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q6_K": 0.0005}[f.name]
-    d = (torch.randn(nb, device="cuda", generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
-    if f is F.Q6_K:
-        w[:, 208:210] = d
-    else:
-        w[:, 0:2] = d
-        if f is F.Q4_K:
-            w[:, 2:4] = d
-    return QuantTensor(w.reshape(-1), f, (n, k))
+from .synth import device_weight  # noqa: E402
 
 
 def main(argv=None) -> int:

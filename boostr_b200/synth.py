@@ -86,3 +86,33 @@ def weight_bytes(fmt: QuantFormat, rng, n: int, k: int) -> np.ndarray:
     fmt = QuantFormat.parse(fmt)
     assert k % fmt.block_size == 0
     return _GEN[fmt](rng, n * (k // fmt.block_size))
+
+
+def device_weight(fmt, n: int, k: int, gen, device="cuda"):
+    """The same distributions drawn ON THE DEVICE with torch's generator (for workloads too large to
+    build on the host): every code byte uniform, Q6_K sub-scales uniform -64..63, Q4_K's twelve scale
+    bytes uniform (which is exactly eight 6-bit scales and eight 6-bit mins uniform 0..63), block
+    scales |N(0,1)| * c as fp16, Q4_K's d and dmin drawn independently.  Returns a ``QuantTensor``."""
+    import torch
+
+    from .tensor import QuantTensor
+
+    f = QuantFormat.parse(fmt)
+    nb = n * (k // f.block_size)
+    w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device=device, generator=gen)
+    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q6_K": 0.0005}[f.name]
+
+    def scale():
+        return (torch.randn(nb, device=device, generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
+
+    if f is QuantFormat.Q6_K:
+        w[:, 192:208] = torch.randint(-64, 64, (nb, 16), dtype=torch.int8, device=device, generator=gen).view(torch.uint8)
+        w[:, 208:210] = scale()
+    elif f is QuantFormat.Q8_0:
+        w[:, 2:34] = torch.randint(-127, 128, (nb, 32), dtype=torch.int8, device=device, generator=gen).view(torch.uint8)
+        w[:, 0:2] = scale()
+    else:
+        w[:, 0:2] = scale()
+        if f is QuantFormat.Q4_K:
+            w[:, 2:4] = scale()
+    return QuantTensor(w.reshape(-1), f, (n, k))

@@ -141,18 +141,20 @@ B200Q_API int b200q_quant_swiglu(int format, const void* act, int act_dtype, con
  * Some hosts reach this library with nothing but the pointers of their inputs and outputs:
  * an FFI caller whose tensor runtime has reserved all device memory for its own pool, or a
  * code path where a cudaMalloc — which can synchronise the whole device — is not acceptable.
- * For them the split-K partial sums that b200q_quant_matmul keeps in `ws` live in a fixed
- * B200Q_STATIC_SCRATCH_BYTES array inside the library's device image instead (every GPU that
- * loads the library holds that array until the process exits).  The call allocates nothing:
+ * For them everything b200q_quant_matmul keeps in `ws` — split-K partial sums, and the prepared
+ * activation image (Q8_K codes / bf16) that the small-M and tensor-core kernels read — lives in a
+ * fixed B200Q_STATIC_SCRATCH_BYTES array inside the library's device image instead (every GPU
+ * that loads the library holds that array until the process exits).  The call allocates nothing:
  * no cudaMalloc, no cudaFree, no allocating library routine.
  *
  *   - Same arguments, results and errors as b200q_quant_matmul, minus ws / ws_bytes.  A shape
- *     whose scratch need (b200q_workspace_bytes) exceeds B200Q_STATIC_SCRATCH_BYTES is refused
+ *     whose scratch need (for its activation type) exceeds B200Q_STATIC_SCRATCH_BYTES is refused
  *     with B200Q_ERR_WORKSPACE_TOO_SMALL and a message naming both sizes.
  *   - The first call on a device resolves the array's device address (once per device, with
- *     that device current).  Make that first call before starting any stream capture.
+ *     that device current; a failed look-up is tried again by the next call).  Make that first
+ *     call before starting any stream capture.  The address belongs to the device's primary context.
  *   - All calls on a device share the one array and it keeps the previous call's contents.
- *     Nothing in it has to start at zero: every partial sum is written before it is read.
+ *     Nothing in it has to start at zero: every byte a kernel reads is written earlier in the same call.
  *     Two calls that may run on the GPU at the same time (different streams) race on it;
  *     keep such calls on one stream or order them yourself.
  */

@@ -124,9 +124,12 @@ def test_quant_matmul_small_m(ops, oracle, fmt, m, n, k):
     rng = synth.rng_for(23, (seed_of(fmt, m, n, k)))
     act = synth.activations(rng, m, k)
     w = synth.weight_bytes(fmt, rng, n, k)
-    canary = torch.full((m * n + 64,), 12345.0, device="cuda")
-    got_t = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k))
+    # the output is the middle of one flat buffer: the guard regions before and after it must stay untouched
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 12345.0, device="cuda")
+    got_t = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k), out=flat[guard:guard + m * n].view(m, n))
     ops.check_device_status()
+    canary = torch.cat([flat[:guard], flat[guard + m * n:]])
     got = got_t.cpu().numpy()
     want = oracle.quant_matmul(fmt, act, w, n, threads=8)
     e_max, e_rms = rel_err(got, want)
@@ -274,12 +277,14 @@ def test_quant_matmul_batch_mixed_formats(ops, oracle):
     ("Q4_0", 1, 4096, 4096),      # config 1
     ("Q8_0", 1, 11008, 4096),     # config 2
     ("Q8_0", 8, 11008, 4096),
+    ("Q8_0", 32, 11008, 4096),
     ("Q6_K", 1, 128256, 4096),    # config 4
     ("Q6_K", 16, 128256, 4096),
     ("Q4_K", 1, 14336, 4096),     # config 5 layer shapes
     ("Q6_K", 1, 4096, 14336),
     ("Q4_K", 16, 4096, 4096),
     ("Q6_K", 16, 4096, 14336),
+    ("Q4_K", 32, 14336, 4096),
 ])
 def test_baseline_shapes(ops, oracle, fmt, m, n, k):
     rng = synth.rng_for(2, seed_of(fmt, m, n))
@@ -325,10 +330,11 @@ def test_prefill_tensor_core_path(ops, oracle, fmt, m, n, k):
     w = synth.weight_bytes(fmt, rng, n, k)
     qt = _qt(fmt, w, n, k)
     act_t = torch.from_numpy(act).cuda()
-    canary = torch.full((256,), 777.0, device="cuda")
-    got = ops.quant_matmul(act_t, qt).cpu().numpy()
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 777.0, device="cuda")
+    got = ops.quant_matmul(act_t, qt, out=flat[guard:guard + m * n].view(m, n)).cpu().numpy()
     ops.check_device_status()
-    assert torch.all(canary == 777.0)
+    assert torch.all(flat[:guard] == 777.0) and torch.all(flat[guard + m * n:] == 777.0)
     assert got.shape == (m, n) and np.isfinite(got).all()
     # (1) the kernel against its own definition (tight): same bf16 operands, f32 accumulation
     ref_tc = _bf16_reference(ops, _prepared_act(oracle, fmt, act), qt)
@@ -372,6 +378,21 @@ def test_prefill_baseline_c3(ops, oracle):
         e_max, e_rms = rel_err(got[:, cols], want)
         print(f"C3 M={m}: vs CPU path max-norm {e_max:.2e} rms {e_rms:.2e}")
         assert e_max <= 1e-2
+
+
+@pytest.mark.parametrize("fmt,n,k", [("Q4_K", 4096, 4096), ("Q6_K", 4096, 14336), ("Q4_K", 14336, 4096)])
+def test_prefill_c5_m64_layer_shapes(ops, oracle, fmt, n, k):
+    # config 5 at 64 tokens per step: every linear of the stack takes the tensor-core path
+    rng = synth.rng_for(5, seed_of(fmt, n, k))
+    m = 64
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(fmt, w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul(fmt, act, w, n, threads=os.cpu_count() or 8)
+    e_max, e_rms = rel_err(got, want)
+    print(f"C5 M=64 {fmt} N={n} K={k}: vs CPU path max-norm {e_max:.2e} rms {e_rms:.2e}")
+    assert e_max <= 1e-2
 
 
 @pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0"])

@@ -1,8 +1,9 @@
 """b200q_quant_matmul_static_scratch: the entry point for hosts that cannot allocate scratch.
 
 Such a caller — an FFI user whose runtime owns all device memory, or a path where cudaMalloc's
-device-wide synchronisation is unacceptable — passes only inputs and outputs; the split-K partial
-sums live in an array inside the library.  The test drives the raw C ABI and requires the same
+device-wide synchronisation is unacceptable — passes only inputs and outputs; what the kernels keep
+between their phases (split-K partial sums, the prepared activation image of the small-M and
+tensor-core paths) lives in an array inside the library.  The test drives the raw C ABI and requires the same
 output as b200q_quant_matmul with caller-provided scratch, on two calls in a row (the array is
 shared and keeps old contents, so the second call runs over the first call's leftovers).
 
@@ -39,8 +40,9 @@ def _run(lib, fmt, act_t, w_t, m, k, n, static):
     return out.cpu().numpy(), (lib.b200q_workspace_bytes(_cabi.OP_QUANT_MATMUL, fid, m, k, n))
 
 
-@pytest.mark.parametrize("fmt,m,n,k", [("Q6_K", 12, 35, 14336), ("Q8_0", 3, 70, 8192), ("Q4_K", 1, 64, 4096)])
-def test_static_scratch_matches_caller_scratch_twice(fmt, m, n, k):
+@pytest.mark.parametrize("fmt,m,n,k", [("Q6_K", 12, 35, 14336), ("Q8_0", 3, 70, 8192), ("Q4_K", 1, 64, 4096),
+                                       ("Q4_K", 128, 256, 4096)])   # the last one keeps a 1 MiB activation image in the array
+def test_static_scratch_matches_caller_scratch_twice(fmt, m, n, k, oracle):
     assert torch.cuda.is_available()
     lib = _cabi.lib()
     rng = synth.rng_for(50, F.parse(fmt).value)
@@ -55,8 +57,11 @@ def test_static_scratch_matches_caller_scratch_twice(fmt, m, n, k):
         assert np.isfinite(got).all()
         e_max, _ = rel_err(got, ref)
         assert e_max <= 1e-6, f"call {call}: {fmt} differs from the caller-scratch entry point by {e_max:.3e}"
+        # and against the CPU path itself, so this test stands alone (tensor-core shapes: the bf16 bar)
+        e_cpu, _ = rel_err(got, oracle.quant_matmul(fmt, act, w, n, threads=4))
+        assert e_cpu <= (1e-2 if m >= 64 else 1e-5), f"call {call}: {fmt} vs the CPU path {e_cpu:.3e}"
         results.append(need)
-    if fmt != "Q4_K":
+    if (fmt, m) != ("Q4_K", 1):
         assert results[0] > 0, "this shape was chosen because it uses scratch"
 
 
