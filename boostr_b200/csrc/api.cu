@@ -138,6 +138,10 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
         if (swiglu) a += 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255);
         return a;
     }
+    // the decode kernels (one activation row) quantise the row inside the kernel and need no scratch
+    if (gemv_m1_supported(format, M, K, N, swiglu)) return 0;
+    if (!swiglu && gemv_m1_f32_supported(format, M, K, N)) return 0;
+    // small-M kernel: the activation image, plus split-K partial sums when K is long
     return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
 }
 

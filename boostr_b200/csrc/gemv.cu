@@ -1,40 +1,36 @@
-// Memory-bound quantized GEMV / small-M kernel (M <= 16 per launch) for Q4_0, Q8_0, Q4_K, Q6_K.
+// Memory-bound quantized small-M kernel (2 <= M <= 32 per pass, and every M = 1 shape the decode kernels do
+// not take) for Q4_0, Q8_0, Q4_K, Q6_K.
 //
 // Stands in for boostr's quant_gemv_*_q8_1_mwr / quant_gemv_*_f32 / fused_swiglu_*_mwr kernels
 // (src/quant/cuda/kernels/quant_gemv.cu:43-1215) and its separate activation-quantise launch
 // (src/quant/cuda/kernels/quant_act.cu:17-69).
 //
-// Shape of the kernel
-//   * Persistent CTAs, one per SM, 16 warps each (four per scheduler, so every warp may use 128
-//     registers).  Slabs of packed weight rows stream into a ring of shared-memory stages
-//     through 1-D bulk copies (cp.async.bulk + mbarrier byte counts); the warps take turns
-//     requesting the next fill of the stage they have just released, so no warp is "the
-//     producer"; 3-5 stages of 37-70 KB keep over 100 KB of HBM reads in flight per SM.
-//   * There is no block-wide barrier in the steady state: stages are handed over through
-//     full/empty mbarriers and the per-slab partial sums through a second ring of mbarrier-
-//     guarded slots; the warps take turns adding up a slab published two slabs earlier, so
-//     nobody waits for the slowest warp and warps drift apart freely.
-//   * Each compute warp owns one 256-wide run of K (a "slice": one Q4_K/Q6_K block or eight
-//     Q4_0/Q8_0 blocks) of a K-chunk of up to 16 slices.  The activations of that run are
-//     prepared ONCE per launch and kept in registers as MMA B-fragments, so the only
-//     shared-memory traffic in the loop is the packed weights themselves.
-//   * Dot products run on the tensor cores through mma.sync (16 weight rows x 8 activation
-//     rows per instruction).  The tensor pipe is nearly idle at these shapes; the point is that
-//     one instruction replaces 128 dp4a/FFMA lanes of work, which keeps the integer ALUs (nibble
-//     and 6-bit unpacking) under the HBM rate.
-//   * Q4_K / Q6_K reproduce boostr's CPU numerics: the activation run is quantised to Q8_K
-//     (amax/127 scale, round-half-even, src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98)
-//     inside the kernel, integer dots are exact, and each block contributes
-//     (d*d8)*sumi - (dmin*d8)*sumi_mins without FMA contraction
-//     (src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172, fused_q6k_q8k_dot.rs:170-224).
-//     Blocks are summed in K order, so for K <= 4096 the result is bit-identical to the CPU path.
-//   * Q4_0 / Q8_0 keep full activation precision as the CPU path does
-//     (src/quant/cpu/kernels/quant_matmul.rs:193-209): each run is scaled by a power of two and
-//     split into fp16 hi + lo parts (M <= 8), or rounded once to fp16 (M 9..16, relative error
-//     2^-12); codes are exact in fp16 and products accumulate in f32.
-//   * Partial sums of the warps of a CTA meet in shared memory and are added in slice order.
-//     When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks
-//     are spread over gridDim.y and a second small kernel adds the partials.
+// Shape of the kernels
+//   * act_prep_kernel: ONE small launch per call turns the activations into the "image" the main kernel
+//     multiplies with: for every 256-wide run of K ("slice") and every tile of 8 activation rows, the
+//     tensor-core B fragments of all 32 lanes, stored so that a warp fetches them with 16-byte loads.
+//     Q4_K / Q6_K: the run quantised to Q8_K exactly as boostr's CPU path does (amax/127 scale,
+//     round-half-even, src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98) plus the 32-wide block
+//     sums the Q4_K min term needs.  Q4_0 / Q8_0 (f32 activations on the CPU path,
+//     src/quant/cpu/kernels/quant_matmul.rs:193-209): each value as a sum of int8 pieces
+//     x = (amax/127) * (a1 + a2/254 + a3/254^2): three pieces for M <= 8 (relative error ~1e-7 of the
+//     run's amax), two for M 9..16 per pass (~3e-5), so the weights' int8 codes go to the tensor cores
+//     unconverted.
+//   * gemv_kernel: persistent CTAs, one per SM, 16 warps.  A warp owns one slice of a K-chunk of up to 16
+//     slices and keeps that slice's fragments for up to four 8-row tiles in registers for the whole
+//     launch, so the only shared-memory traffic in the loop is the packed weights.  Slabs of 16 weight
+//     rows per warp row-group stream through a ring of stages filled by bulk copies (cp.async.bulk +
+//     mbarrier byte counts); the warps take turns requesting the refill of the stage they have just
+//     released.  There is no block-wide barrier in the steady state: stages and per-slab partial sums
+//     are handed over through mbarriers and warps drift apart freely.
+//   * Dot products are mma.sync int8 (16 weight rows x 8 activation rows x 32 K per instruction).
+//     Q4_K / Q6_K integer sums are exact and each block contributes (d*d8)*sumi - (dmin*d8)*sumi_mins
+//     without FMA contraction (fused_q4k_q8k_dot.rs:111-172, fused_q6k_q8k_dot.rs:170-224); blocks are
+//     added in K order, so for K <= 4096 the result is bit-identical to the CPU path.  Q4_0 / Q8_0: the
+//     accumulator starts at the bit pattern of 1.5 * 2^23, so the finished integer sum is read as a float
+//     without a conversion instruction, the pieces are combined in f32 and scaled by the block's d.
+//   * When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks are
+//     spread over gridDim.y and a second small kernel adds the partials in K order.
 #include "common.cuh"
 
 namespace b200q {
@@ -43,10 +39,12 @@ struct GemvParams {
     const uint8_t* w[2];  // [1] = up-projection weight in SwiGLU mode
     const void* act;
     void* out;
+    const uint4* img;     // activation image written by act_prep_kernel: [slice][tile][vector][lane]
     float* partial;       // [nmat][ksplit][M][N] f32 when ksplit > 1
     uint32_t M, K, N;
-    uint32_t m0;          // first activation row of this launch (M tiles of 16)
+    uint32_t m0;          // first activation row of this launch
     uint32_t mcount;      // activation rows handled by this launch (<= 8*MT)
+    uint32_t tiles_total; // 8-row tiles in the image (ceil(M / 8))
     uint32_t row_bytes;
     uint32_t nslices;     // ceil(K / 256)
     uint32_t spc;         // slices per chunk (<= 16) == compute warps per row group
@@ -120,175 +118,258 @@ __device__ __forceinline__ int quad_sum(int v) {
 // Lane naming follows the MMA fragment layout: g = lane / 4 (weight row within the 16-row
 // group, and activation row within an 8-row tile), t = lane % 4 (position along K).
 
-template <int FMT, int MT, bool HILO>
-struct SliceB;
+// Every format has two types:
+//   TileB<FMT, P>      the fragments of ONE (slice, 8-row tile): built from the activations by the prep
+//                      kernel (build), written to / read from the image (store / load);
+//   SliceB<FMT, MT, P> what a warp of the main kernel keeps: MT tiles of its slice.
+// P = number of int8 pieces per activation value (Q4_0 / Q8_0 only; 0 for the K-quants).
+// Image layout of one (slice, tile): NV 16-byte vectors per lane, vector v of lane l at index v * 32 + l.
+
+struct PrepParams {
+    const void* act;
+    uint4* img;
+    uint32_t M, K;
+    uint32_t nslices, tiles_total;
+    int act_dtype;
+};
+
+template <int FMT, int P>
+struct TileB;
 
 // ---- Q4_K: int8 activations; sub-block j (32 wide) uses elements 8t..8t+7 of the lane ----
-template <int MT, bool HILO>
-struct SliceB<FMT_Q4_K, MT, HILO> {
-    uint32_t q[MT][16];   // [2*j + half]: k32 B fragment of sub-block j
-    uint32_t bs_lo[MT];   // bytes: (bsum_j + 4096) & 127 for j = 4t..4t+3 (t < 2), else 0
-    uint32_t bs_hi[MT];   // bytes: (bsum_j + 4096) >> 7
-    float d8[MT][2];      // Q8_K scale of activation rows 2t, 2t+1 of the tile
+template <int P>
+struct TileB<FMT_Q4_K, P> {
+    static constexpr int NV = 5;
+    uint32_t q[16];   // [2*j + half]: k32 B fragment of sub-block j
+    uint32_t bs_lo;   // bytes: (bsum_j + 4096) & 127 for j = 4t..4t+3 (t < 2), else 0
+    uint32_t bs_hi;   // bytes: (bsum_j + 4096) >> 7
+    float d8[2];      // Q8_K scale of activation rows 2t, 2t+1 of the tile
 
-    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
+    // rows = activation rows of this tile that exist (rows beyond it count as zero)
+    __device__ __forceinline__ void build(const PrepParams& p, uint32_t slice, uint32_t m_first, uint32_t rows, int g, int t) {
+        const bool on = (uint32_t)g < rows;
+        const size_t base = (size_t)(m_first + g) * p.K + (size_t)slice * 256 + 8 * t;
+        // one round of loads: the lane's 64 activations stay in registers for both passes
+        float v[8][8];
 #pragma unroll
-        for (int tl = 0; tl < MT; ++tl) {
-            uint32_t m = tl * 8 + g;
-            bool on = valid && m < p.mcount;
-            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 8 * t;
-            // one round of loads: the lane's 64 activations stay in registers for both passes
-            float v[8][8];
+        for (int j = 0; j < 8; ++j) {
+            if (on) load_act8(p.act, p.act_dtype, base + 32 * j, v[j]);
+            else
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (on) load_act8(p.act, p.act_dtype, base + 32 * j, v[j]);
-                else
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-            }
-            float amax = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-            amax = quad_max(amax);
-            float d = __fdiv_rn(amax, 127.0f);
-            float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
-            uint32_t lo[2] = {0, 0}, hi[2] = {0, 0};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int c[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) c[i] = q8k_code(v[j][i], id);
-                q[tl][2 * j] = pack4(c[0], c[1], c[2], c[3]);
-                q[tl][2 * j + 1] = pack4(c[4], c[5], c[6], c[7]);
-                int bsum = quad_sum(c[0] + c[1] + c[2] + c[3] + c[4] + c[5] + c[6] + c[7]) + 4096;
-                lo[j >> 2] |= (uint32_t)(bsum & 127) << (8 * (j & 3));
-                hi[j >> 2] |= (uint32_t)(bsum >> 7) << (8 * (j & 3));
-            }
-            bs_lo[tl] = !on ? 0u : t == 0 ? lo[0] : t == 1 ? lo[1] : 0u;
-            bs_hi[tl] = !on ? 0u : t == 0 ? hi[0] : t == 1 ? hi[1] : 0u;
-            float dd = on ? d : 0.f;
-            d8[tl][0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
-            d8[tl][1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+                for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
         }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+        amax = quad_max(amax);
+        float d = __fdiv_rn(amax, 127.0f);
+        float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+        uint32_t lo[2] = {0, 0}, hi[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int c[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = q8k_code(v[j][i], id);
+            q[2 * j] = pack4(c[0], c[1], c[2], c[3]);
+            q[2 * j + 1] = pack4(c[4], c[5], c[6], c[7]);
+            int bsum = quad_sum(c[0] + c[1] + c[2] + c[3] + c[4] + c[5] + c[6] + c[7]) + 4096;
+            lo[j >> 2] |= (uint32_t)(bsum & 127) << (8 * (j & 3));
+            hi[j >> 2] |= (uint32_t)(bsum >> 7) << (8 * (j & 3));
+        }
+        bs_lo = !on ? 0u : t == 0 ? lo[0] : t == 1 ? lo[1] : 0u;
+        bs_hi = !on ? 0u : t == 0 ? hi[0] : t == 1 ? hi[1] : 0u;
+        float dd = on ? d : 0.f;
+        d8[0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
+        d8[1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+    }
+    __device__ __forceinline__ void store(uint4* dst, int lane) const {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = make_uint4(q[4 * v], q[4 * v + 1], q[4 * v + 2], q[4 * v + 3]);
+        dst[4 * 32 + lane] = make_uint4(bs_lo, bs_hi, __float_as_uint(d8[0]), __float_as_uint(d8[1]));
+    }
+    __device__ __forceinline__ void load(const uint4* src, int lane) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint4 x = __ldg(src + v * 32 + lane);
+            q[4 * v] = x.x; q[4 * v + 1] = x.y; q[4 * v + 2] = x.z; q[4 * v + 3] = x.w;
+        }
+        const uint4 x = __ldg(src + 4 * 32 + lane);
+        bs_lo = x.x; bs_hi = x.y; d8[0] = __uint_as_float(x.z); d8[1] = __uint_as_float(x.w);
     }
 };
 
 // ---- Q6_K: int8 activations; sub-block sb (16 wide) uses elements 4t..4t+3 ----
-template <int MT, bool HILO>
-struct SliceB<FMT_Q6_K, MT, HILO> {
-    uint32_t q[MT][16];  // [sb]: k16 B fragment of 16-wide sub-block sb
-    float d8[MT][2];
+template <int P>
+struct TileB<FMT_Q6_K, P> {
+    static constexpr int NV = 5;
+    uint32_t q[16];  // [sb]: k16 B fragment of 16-wide sub-block sb
+    float d8[2];
 
-    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
+    __device__ __forceinline__ void build(const PrepParams& p, uint32_t slice, uint32_t m_first, uint32_t rows, int g, int t) {
+        const bool on = (uint32_t)g < rows;
+        const size_t base = (size_t)(m_first + g) * p.K + (size_t)slice * 256 + 4 * t;
+        float v[16][4];
 #pragma unroll
-        for (int tl = 0; tl < MT; ++tl) {
-            uint32_t m = tl * 8 + g;
-            bool on = valid && m < p.mcount;
-            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + 4 * t;
-            float v[16][4];
+        for (int sb = 0; sb < 16; ++sb) {
+            if (on) load_act4(p.act, p.act_dtype, base + 16 * sb, v[sb]);
+            else
 #pragma unroll
-            for (int sb = 0; sb < 16; ++sb) {
-                if (on) load_act4(p.act, p.act_dtype, base + 16 * sb, v[sb]);
-                else
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) v[sb][i] = 0.f;
-            }
-            float amax = 0.f;
-#pragma unroll
-            for (int sb = 0; sb < 16; ++sb)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[sb][i]));
-            amax = quad_max(amax);
-            float d = __fdiv_rn(amax, 127.0f);
-            float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
-#pragma unroll
-            for (int sb = 0; sb < 16; ++sb)
-                q[tl][sb] = pack4(q8k_code(v[sb][0], id), q8k_code(v[sb][1], id), q8k_code(v[sb][2], id), q8k_code(v[sb][3], id));
-            float dd = on ? d : 0.f;
-            d8[tl][0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
-            d8[tl][1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+                for (int i = 0; i < 4; ++i) v[sb][i] = 0.f;
         }
+        float amax = 0.f;
+#pragma unroll
+        for (int sb = 0; sb < 16; ++sb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[sb][i]));
+        amax = quad_max(amax);
+        float d = __fdiv_rn(amax, 127.0f);
+        float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+#pragma unroll
+        for (int sb = 0; sb < 16; ++sb)
+            q[sb] = pack4(q8k_code(v[sb][0], id), q8k_code(v[sb][1], id), q8k_code(v[sb][2], id), q8k_code(v[sb][3], id));
+        float dd = on ? d : 0.f;
+        d8[0] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t) * 4);
+        d8[1] = __shfl_sync(0xFFFFFFFFu, dd, (2 * t + 1) * 4);
+    }
+    __device__ __forceinline__ void store(uint4* dst, int lane) const {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = make_uint4(q[4 * v], q[4 * v + 1], q[4 * v + 2], q[4 * v + 3]);
+        dst[4 * 32 + lane] = make_uint4(__float_as_uint(d8[0]), __float_as_uint(d8[1]), 0u, 0u);
+    }
+    __device__ __forceinline__ void load(const uint4* src, int lane) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint4 x = __ldg(src + v * 32 + lane);
+            q[4 * v] = x.x; q[4 * v + 1] = x.y; q[4 * v + 2] = x.z; q[4 * v + 3] = x.w;
+        }
+        const uint4 x = __ldg(src + 4 * 32 + lane);
+        d8[0] = __uint_as_float(x.x); d8[1] = __uint_as_float(x.y);
     }
 };
 
-// ---- Q8_0 / Q4_0: fp16 activations scaled by a power of two per (row, slice) ----
-template <int FMT, int MT, bool HILO>
-struct SliceBF16 {
-    uint32_t h[MT][8][4];                 // [block][step*2 + {b0,b1}] half2 fragments
-    uint32_t l[HILO ? MT : 1][8][4];      // low parts * 2048 (HILO only)
-    float inv[MT][2];                     // 1 / scale of activation rows 2t, 2t+1
+// ---- Q8_0 / Q4_0: every activation as P int8 pieces, x = (amax/127) * (a1 + a2/254 [+ a3/254^2]) ----
+// The lane holds the 8 consecutive elements 8t..8t+7 of each 32-block.  K order inside a block follows
+// what the weight side reads without shuffling bytes:
+//   Q8_0: the lane's two code words -> k-slots 4t..4t+3 = elements 8t..8t+3, k-slots 16+4t.. = elements 8t+4..8t+7
+//   Q4_0: byte i of the lane's word holds elements 8t+2i (low nibble) and 8t+2i+1 (high nibble)
+//         -> k-slots 4t..4t+3 = elements 8t+{0,2,4,6}, k-slots 16+4t.. = elements 8t+{1,3,5,7}
+constexpr float PIECE_STEP = 254.0f;
+template <int FMT, int P>
+struct TileBI8 {
+    static constexpr int NV = 4 * P + 1;
+    uint32_t q[8][P][2];  // [block][piece][{b0, b1}]
+    float scale[2];       // amax / 127 of activation rows 2t, 2t+1 of the tile (this slice)
 
-    __device__ __forceinline__ void build(const GemvParams& p, uint32_t slice, bool valid, int g, int t) {
-        const uint32_t kleft = valid ? p.K - slice * 256 : 0;  // elements of this slice that exist
+    __device__ __forceinline__ void build(const PrepParams& p, uint32_t slice, uint32_t m_first, uint32_t rows, int g, int t) {
+        const bool on = (uint32_t)g < rows;
+        const uint32_t kleft = p.K - slice * 256;  // elements of this slice that exist (ragged last slice)
+        const size_t base = (size_t)(m_first + g) * p.K + (size_t)slice * 256 + 8 * t;
+        float v[8][8];
 #pragma unroll
-        for (int tl = 0; tl < MT; ++tl) {
-            uint32_t m = tl * 8 + g;
-            bool on = valid && m < p.mcount;
-            // elements of a 32-block held by this lane: Q4_0 8t..8t+7; Q8_0 4t..4t+3 and 16+4t..16+4t+3
-            size_t base = (size_t)(p.m0 + m) * p.K + (size_t)slice * 256 + (FMT == FMT_Q8_0 ? 4 : 8) * t;
-            auto load_blk = [&](int b, float (&v)[8]) {
+        for (int b = 0; b < 8; ++b) {
+            if (on && 32u * b < kleft) load_act8(p.act, p.act_dtype, base + 32 * b, v[b]);
+            else
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[b][i] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[b][i]));
+        amax = quad_max(amax);
+        const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+        constexpr int O8[8] = {0, 1, 2, 3, 4, 5, 6, 7};
+        constexpr int O4[8] = {0, 2, 4, 6, 1, 3, 5, 7};
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            int c[P][8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float r = __fmul_rn(v[b][i], id);  // |r| <= 127 (+ one rounding)
+#pragma unroll
+                for (int pc = 0; pc < P; ++pc) {
+                    const float a = rintf(r);
+                    c[pc][i] = max(-127, min(127, (int)a));
+                    r = __fmul_rn(__fsub_rn(r, (float)c[pc][i]), PIECE_STEP);  // remainder in [-0.5, 0.5] -> [-127, 127]
+                }
+            }
+#pragma unroll
+            for (int pc = 0; pc < P; ++pc) {
                 if constexpr (FMT == FMT_Q8_0) {
-                    float lo4[4], hi4[4];
-                    load_act4(p.act, p.act_dtype, base + 32 * b, lo4);
-                    load_act4(p.act, p.act_dtype, base + 32 * b + 16, hi4);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) { v[i] = lo4[i]; v[4 + i] = hi4[i]; }
+                    q[b][pc][0] = pack4(c[pc][O8[0]], c[pc][O8[1]], c[pc][O8[2]], c[pc][O8[3]]);
+                    q[b][pc][1] = pack4(c[pc][O8[4]], c[pc][O8[5]], c[pc][O8[6]], c[pc][O8[7]]);
                 } else {
-                    load_act8(p.act, p.act_dtype, base + 32 * b, v);
-                }
-            };
-            float v[8][8];
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                if (on && 32u * b < kleft) load_blk(b, v[b]);
-                else
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[b][i] = 0.f;
-            }
-            float amax = 0.f;
-#pragma unroll
-            for (int b = 0; b < 8; ++b)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[b][i]));
-            amax = quad_max(amax);
-            uint32_t e = __float_as_uint(amax) >> 23;  // biased exponent (amax >= 0)
-            e = e == 0 ? 127u : (e > 253u ? 253u : e);
-            float sc = __uint_as_float((254u - e) << 23);  // 2^(127-e): amax*sc in [1,2)
-            float isc = __uint_as_float(e << 23);
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                __half hi[8], lo[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float x = v[b][i] * sc;
-                    hi[i] = __float2half_rn(x);
-                    lo[i] = __float2half_rn((x - __half2float(hi[i])) * 2048.0f);
-                }
-                // K order inside a 32-block follows what the weight side can unpack cheaply:
-                //   Q8_0: byte pairs of the lane's two words -> (0,1) (2,3) | (4,5) (6,7)
-                //   Q4_0: byte i holds elements 2i, 2i+1 -> lop3 yields (0,4) (1,5) | (2,6) (3,7)
-                constexpr int P8[8] = {0, 1, 2, 3, 4, 5, 6, 7};
-                constexpr int P4[8] = {0, 4, 1, 5, 2, 6, 3, 7};
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    int i0 = FMT == FMT_Q8_0 ? P8[2 * r] : P4[2 * r];
-                    int i1 = FMT == FMT_Q8_0 ? P8[2 * r + 1] : P4[2 * r + 1];
-                    h[tl][b][r] = h2_as_u32(__halves2half2(hi[i0], hi[i1]));
-                    if (HILO) l[tl][b][r] = h2_as_u32(__halves2half2(lo[i0], lo[i1]));
+                    q[b][pc][0] = pack4(c[pc][O4[0]], c[pc][O4[1]], c[pc][O4[2]], c[pc][O4[3]]);
+                    q[b][pc][1] = pack4(c[pc][O4[4]], c[pc][O4[5]], c[pc][O4[6]], c[pc][O4[7]]);
                 }
             }
-            float ii = on ? isc : 0.f;
-            inv[tl][0] = __shfl_sync(0xFFFFFFFFu, ii, (2 * t) * 4);
-            inv[tl][1] = __shfl_sync(0xFFFFFFFFu, ii, (2 * t + 1) * 4);
+        }
+        const float sc = on ? __fdiv_rn(amax, 127.0f) : 0.f;
+        scale[0] = __shfl_sync(0xFFFFFFFFu, sc, (2 * t) * 4);
+        scale[1] = __shfl_sync(0xFFFFFFFFu, sc, (2 * t + 1) * 4);
+    }
+    __device__ __forceinline__ void store(uint4* dst, int lane) const {
+        const uint32_t* f = &q[0][0][0];
+#pragma unroll
+        for (int v = 0; v < 4 * P; ++v) dst[v * 32 + lane] = make_uint4(f[4 * v], f[4 * v + 1], f[4 * v + 2], f[4 * v + 3]);
+        dst[4 * P * 32 + lane] = make_uint4(__float_as_uint(scale[0]), __float_as_uint(scale[1]), 0u, 0u);
+    }
+    __device__ __forceinline__ void load(const uint4* src, int lane) {
+        uint32_t* f = &q[0][0][0];
+#pragma unroll
+        for (int v = 0; v < 4 * P; ++v) {
+            const uint4 x = __ldg(src + v * 32 + lane);
+            f[4 * v] = x.x; f[4 * v + 1] = x.y; f[4 * v + 2] = x.z; f[4 * v + 3] = x.w;
+        }
+        const uint4 x = __ldg(src + 4 * P * 32 + lane);
+        scale[0] = __uint_as_float(x.x); scale[1] = __uint_as_float(x.y);
+    }
+};
+template <int P>
+struct TileB<FMT_Q8_0, P> : TileBI8<FMT_Q8_0, P> {};
+template <int P>
+struct TileB<FMT_Q4_0, P> : TileBI8<FMT_Q4_0, P> {};
+
+// pieces per activation value: K-quants none; Q4_0 / Q8_0 three while one 8-row tile is held, two beyond
+__host__ __device__ constexpr int fmt_pieces(int fmt, int mt) { return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? (mt == 1 ? 3 : 2) : 0; }
+__host__ __device__ constexpr int fmt_image_vectors(int fmt, int mt) {
+    return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? 4 * fmt_pieces(fmt, mt) + 1 : 5;
+}
+
+template <int FMT, int MT, int P>
+struct SliceB {
+    TileB<FMT, P> tile[MT];
+    // tiles [tile0, tile0 + MT) of `slice`; tiles past the image or an absent slice read as zero
+    __device__ __forceinline__ void load(const GemvParams& p, uint32_t slice, bool valid, uint32_t tile0, int lane) {
+        constexpr int NV = TileB<FMT, P>::NV;
+#pragma unroll
+        for (int tl = 0; tl < MT; ++tl) {
+            if (valid && tile0 + tl < p.tiles_total) {
+                tile[tl].load(p.img + ((size_t)slice * p.tiles_total + tile0 + tl) * (NV * 32), lane);
+            } else {
+                tile[tl] = TileB<FMT, P>{};
+            }
         }
     }
 };
-template <int MT, bool HILO>
-struct SliceB<FMT_Q8_0, MT, HILO> : SliceBF16<FMT_Q8_0, MT, HILO> {};
-template <int MT, bool HILO>
-struct SliceB<FMT_Q4_0, MT, HILO> : SliceBF16<FMT_Q4_0, MT, HILO> {};
+
+// One warp per (slice, tile): builds the fragments and writes them to the image.
+template <int FMT, int P>
+__global__ void __launch_bounds__(128) act_prep_kernel(const PrepParams p) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+    grid_dep_launch();
+    grid_dep_wait();  // the activations may be the previous kernel's output; the image may still be read by it
+    if (unit >= p.nslices * p.tiles_total) return;
+    const uint32_t slice = unit / p.tiles_total, tl = unit % p.tiles_total;
+    const uint32_t m_first = tl * 8, rows = min(8u, p.M - m_first);
+    TileB<FMT, P> b;
+    b.build(p, slice, m_first, rows, g, t);
+    b.store(p.img + (size_t)unit * (TileB<FMT, P>::NV * 32), lane);
+}
 
 // ------------------------------------------------------------------ slice x 16 rows
 
@@ -308,8 +389,8 @@ __device__ __forceinline__ int byte_s(uint32_t x) {
     return r;
 }
 
-template <int MT, bool HILO, bool M1>
-__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t,
+template <int MT, bool M1>
+__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, const uint8_t* ra, const uint8_t* rb, int t,
                                           float (&acc)[MT][4]) {
     const int zero[4] = {0, 0, 0, 0};
     uint4 ha = lds128(ra), hb = lds128(rb);
@@ -324,11 +405,13 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, c
     sB[1] = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
     mB[1] = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
 
-    int isum_lo[MT][4], isum_hi[MT][4];  // hi: 16x too large (high nibbles are used unshifted)
+    // 16 * sumi: low-nibble sub-blocks enter with 16 * scale, high nibbles are used unshifted (16 * q);
+    // |16 * sumi| <= 16 * 8 * 63 * 32 * 15 * 127 < 2^31
+    int isum[MT][4];
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) isum_lo[tl][i] = isum_hi[tl][i] = 0;
+        for (int i = 0; i < 4; ++i) isum[tl][i] = 0;
 
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
@@ -341,24 +424,26 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, c
             scA0 = byte_u<2>(sA[jj >> 1]); scA1 = byte_u<3>(sA[jj >> 1]);
             scB0 = byte_u<2>(sB[jj >> 1]); scB1 = byte_u<3>(sB[jj >> 1]);
         }
+        scA0 <<= 4;
+        scB0 <<= 4;
+        const uint32_t al0 = qa.x & 0x0F0F0F0Fu, al1 = qb.x & 0x0F0F0F0Fu, al2 = qa.y & 0x0F0F0F0Fu, al3 = qb.y & 0x0F0F0F0Fu;
+        const uint32_t ah0 = qa.x & 0xF0F0F0F0u, ah1 = qb.x & 0xF0F0F0F0u, ah2 = qa.y & 0xF0F0F0F0u, ah3 = qb.y & 0xF0F0F0F0u;
 #pragma unroll
         for (int tl = 0; tl < MT; ++tl) {
             int d[4];
-            mma_u8s8_k32(d, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu,
-                         B.q[tl][4 * jj], B.q[tl][4 * jj + 1], zero);
-            isum_lo[tl][0] += scA0 * d[0];
-            isum_lo[tl][2] += scB0 * d[2];
+            mma_u8s8_k32(d, al0, al1, al2, al3, B.tile[tl].q[4 * jj], B.tile[tl].q[4 * jj + 1], zero);
+            isum[tl][0] += scA0 * d[0];
+            isum[tl][2] += scB0 * d[2];
             if (!M1) {
-                isum_lo[tl][1] += scA0 * d[1];
-                isum_lo[tl][3] += scB0 * d[3];
+                isum[tl][1] += scA0 * d[1];
+                isum[tl][3] += scB0 * d[3];
             }
-            mma_u8s8_k32(d, qa.x & 0xF0F0F0F0u, qb.x & 0xF0F0F0F0u, qa.y & 0xF0F0F0F0u, qb.y & 0xF0F0F0F0u,
-                         B.q[tl][4 * jj + 2], B.q[tl][4 * jj + 3], zero);
-            isum_hi[tl][0] += scA1 * d[0];
-            isum_hi[tl][2] += scB1 * d[2];
+            mma_u8s8_k32(d, ah0, ah1, ah2, ah3, B.tile[tl].q[4 * jj + 2], B.tile[tl].q[4 * jj + 3], zero);
+            isum[tl][0] += scA1 * d[0];
+            isum[tl][2] += scB1 * d[2];
             if (!M1) {
-                isum_hi[tl][1] += scA1 * d[1];
-                isum_hi[tl][3] += scB1 * d[3];
+                isum[tl][1] += scA1 * d[1];
+                isum[tl][3] += scB1 * d[3];
             }
         }
     }
@@ -372,14 +457,14 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, HILO>& B, c
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl) {
         int ml[4], mh[4];
-        mma_u8u8_k16(ml, am0, am1, B.bs_lo[tl], zero);
-        mma_u8u8_k16(mh, am0, am1, B.bs_hi[tl], zero);
+        mma_u8u8_k16(ml, am0, am1, B.tile[tl].bs_lo, zero);
+        mma_u8u8_k16(mh, am0, am1, B.tile[tl].bs_hi, zero);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (M1 && (i & 1)) continue;
-            const int sumi = isum_lo[tl][i] + (isum_hi[tl][i] >> 4);
+            const int sumi = isum[tl][i] >> 4;
             const int summ = ml[i] + 128 * mh[i] - 4096 * (i < 2 ? sumA : sumB);
-            const float d8 = B.d8[tl][i & 1];
+            const float d8 = B.tile[tl].d8[i & 1];
             const float dall = __fmul_rn(i < 2 ? dA : dB, d8);
             const float dmall = __fmul_rn(i < 2 ? dminA : dminB, d8);
             const float term = __fsub_rn(__fmul_rn(dall, (float)sumi), __fmul_rn(dmall, (float)summ));
@@ -405,8 +490,8 @@ __device__ __forceinline__ int q6k_scale(const uint32_t (&sc)[4]) { return byte_
 
 // ALIGNED: both slices start on a 4-byte boundary (plain 32-bit loads); otherwise they are only
 // 2-byte aligned and every word is assembled from two.
-template <int MT, bool HILO, bool M1, bool ALIGNED>
-__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t,
+template <int MT, bool M1, bool ALIGNED>
+__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, 0>& B, const uint8_t* ra, const uint8_t* rb, int t,
                                           float (&acc)[MT][4]) {
     auto ld = [](const uint8_t* a) { return ALIGNED ? lds32(a) : lds32_u(a); };
     const int zero[4] = {0, 0, 0, 0};
@@ -441,7 +526,7 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, c
 #pragma unroll
                 for (int tl = 0; tl < MT; ++tl) {
                     int d[4];
-                    mma_s8s8_k16(d, va, vb, B.q[tl][sb], zero);
+                    mma_s8s8_k16(d, va, vb, B.tile[tl].q[sb], zero);
                     isum[tl][0] += sA_ * d[0];
                     isum[tl][2] += sB_ * d[2];
                     if (!M1) {
@@ -458,24 +543,22 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, HILO>& B, c
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (M1 && (i & 1)) continue;
-            const float dall = __fmul_rn(i < 2 ? dA : dB, B.d8[tl][i & 1]);
+            const float dall = __fmul_rn(i < 2 ? dA : dB, B.tile[tl].d8[i & 1]);
             acc[tl][i] = __fadd_rn(acc[tl][i], __fmul_rn(dall, (float)(isum[tl][i] >> 2)));
         }
 }
 
-// int8 x4 (as stored, two's complement) -> two half2 holding the exact integers
-__device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
-    const uint32_t x = w ^ 0x80808080u;  // q + 128 in 0..255
-    const __half2 bias = __floats2half2_rn(1152.f, 1152.f);  // 1024 (magic) + 128
-    lo = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4140)), bias));
-    hi = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(x, 0x64646464u, 0x4342)), bias));
-}
-
-template <int FMT, int MT, bool HILO, bool M1>
-__device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, const uint8_t* ra, const uint8_t* rb, int t, uint32_t nblk,
-                                          float (&acc)[MT][4]) {
+// Q8_0 / Q4_0 slice: per 32-block one int8 MMA per activation piece.  The accumulator starts at the bit
+// pattern of 1.5 * 2^23, so the finished integer sum S (|S| <= 32 * 128 * 127 < 2^22) reads back as the
+// float 1.5 * 2^23 + S, and S itself costs one FADD instead of a conversion.
+template <int FMT, int MT, int P, bool M1>
+__device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint8_t* ra, const uint8_t* rb, int t, uint32_t nblk,
+                                         float (&acc)[MT][4]) {
     constexpr int BB = fmt_block_bytes(FMT);
-    const float zf[4] = {0.f, 0.f, 0.f, 0.f};
+    constexpr int MAGIC_I = 0x4B400000;
+    constexpr float MAGIC_F = 12582912.0f;
+    const int magic[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
+    constexpr float C1 = 1.0f / PIECE_STEP, C2 = 1.0f / (PIECE_STEP * PIECE_STEP);
     float sacc[MT][4];
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
@@ -484,47 +567,44 @@ __device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, const 
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
         if ((uint32_t)b < nblk) {  // warp-uniform: ragged last slice when K % 256 != 0
-            uint32_t a[2][4];  // [row][step*2 + {k 2t.., k 2t+8..}]
+            uint32_t a0, a1, a2, a3;  // row g k-slots 4t.. | row g+8 | row g k-slots 16+4t.. | row g+8
+            float dA = f16bits_to_f32(lds16(ra + BB * b)), dB = f16bits_to_f32(lds16(rb + BB * b));
             if constexpr (FMT == FMT_Q8_0) {
-                // block = f16 d | 32 x i8 ; lane uses bytes 4t..4t+3 and 16+4t..16+4t+3, so the four
-                // lanes of a row read 16 contiguous bytes per load
-                s8x4_to_h2(lds32_u(ra + BB * b + 2 + 4 * t), a[0][0], a[0][1]);
-                s8x4_to_h2(lds32_u(ra + BB * b + 18 + 4 * t), a[0][2], a[0][3]);
-                s8x4_to_h2(lds32_u(rb + BB * b + 2 + 4 * t), a[1][0], a[1][1]);
-                s8x4_to_h2(lds32_u(rb + BB * b + 18 + 4 * t), a[1][2], a[1][3]);
+                // block = f16 d | 32 x i8; the lane's 8 codes are bytes 8t..8t+7 (2-byte aligned): three aligned words
+                const uint8_t* pa = ra + BB * b + 2 + 8 * t;
+                const uint8_t* pb = rb + BB * b + 2 + 8 * t;
+                const uint32_t sha = (uint32_t)(reinterpret_cast<uintptr_t>(pa) & 3u) * 8u, shb = (uint32_t)(reinterpret_cast<uintptr_t>(pb) & 3u) * 8u;
+                const uint32_t* wa = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(pa) & ~(uintptr_t)3);
+                const uint32_t* wb = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(pb) & ~(uintptr_t)3);
+                const uint32_t x0 = wa[0], x1 = wa[1], x2 = wa[2], y0 = wb[0], y1 = wb[1], y2 = wb[2];
+                a0 = __funnelshift_r(x0, x1, sha);
+                a2 = __funnelshift_r(x1, x2, sha);
+                a1 = __funnelshift_r(y0, y1, shb);
+                a3 = __funnelshift_r(y1, y2, shb);
             } else {
-                // Q4_0 block = f16 d | 16 B ; byte i = elements 2i (low nibble), 2i+1 (high); lane uses bytes 4t..4t+3
-                const __half2 b8 = __floats2half2_rn(1032.f, 1032.f);              // 1024 + 8
-                const __half2 s16 = __floats2half2_rn(0.0625f, 0.0625f), b72 = __floats2half2_rn(-72.f, -72.f);
-                uint32_t wv[2] = {lds32_u(ra + BB * b + 2 + 4 * t), lds32_u(rb + BB * b + 2 + 4 * t)};
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    const uint32_t w0 = wv[r], w1 = wv[r] >> 8;
-                    a[r][0] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w0, 0x000F000Fu, 0x64006400u)), b8));        // e0,e4
-                    a[r][1] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w0, 0x00F000F0u, 0x64006400u)), s16, b72));  // e1,e5
-                    a[r][2] = h2_as_u32(__hsub2(u32_as_h2(lop3_and_or(w1, 0x000F000Fu, 0x64006400u)), b8));        // e2,e6
-                    a[r][3] = h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(w1, 0x00F000F0u, 0x64006400u)), s16, b72));  // e3,e7
-                }
+                // Q4_0 block = f16 d | 16 B; byte i = elements 2i (low nibble), 2i+1 (high); the lane's word = bytes 4t..4t+3.
+                // (w ^ 0x88..) keeps each nibble as q - 8 in 4-bit two's complement; placed in the high nibble of a byte
+                // it reads as the int8 value 16 * (q - 8): the factor 16 leaves through the block scale.
+                const uint32_t wa = lds32_u(ra + BB * b + 2 + 4 * t) ^ 0x88888888u, wb = lds32_u(rb + BB * b + 2 + 4 * t) ^ 0x88888888u;
+                a0 = (wa << 4) & 0xF0F0F0F0u;
+                a2 = wa & 0xF0F0F0F0u;
+                a1 = (wb << 4) & 0xF0F0F0F0u;
+                a3 = wb & 0xF0F0F0F0u;
+                dA *= 0.0625f;
+                dB *= 0.0625f;
             }
-            const float dA = f16bits_to_f32(lds16(ra + BB * b)), dB = f16bits_to_f32(lds16(rb + BB * b));
 #pragma unroll
             for (int tl = 0; tl < MT; ++tl) {
-                float d[4];
-                mma_f16_k16(d, a[0][0], a[1][0], a[0][1], a[1][1], B.h[tl][b][0], B.h[tl][b][1], zf);
-                mma_f16_k16(d, a[0][2], a[1][2], a[0][3], a[1][3], B.h[tl][b][2], B.h[tl][b][3], d);
-                if constexpr (HILO) {
-                    float e[4];
-                    mma_f16_k16(e, a[0][0], a[1][0], a[0][1], a[1][1], B.l[tl][b][0], B.l[tl][b][1], zf);
-                    mma_f16_k16(e, a[0][2], a[1][2], a[0][3], a[1][3], B.l[tl][b][2], B.l[tl][b][3], e);
+                int d[P][4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (!(M1 && (i & 1))) d[i] = fmaf(e[i], 1.0f / 2048.0f, d[i]);
-                }
-                sacc[tl][0] = fmaf(dA, d[0], sacc[tl][0]);
-                sacc[tl][2] = fmaf(dB, d[2], sacc[tl][2]);
-                if (!M1) {
-                    sacc[tl][1] = fmaf(dA, d[1], sacc[tl][1]);
-                    sacc[tl][3] = fmaf(dB, d[3], sacc[tl][3]);
+                for (int pc = 0; pc < P; ++pc) mma_s8s8_k32(d[pc], a0, a1, a2, a3, B.tile[tl].q[b][pc][0], B.tile[tl].q[b][pc][1], magic);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (M1 && (i & 1)) continue;
+                    float h = __int_as_float(d[0][i]) - MAGIC_F;
+                    h = fmaf(__int_as_float(d[1][i]) - MAGIC_F, C1, h);
+                    if constexpr (P > 2) h = fmaf(__int_as_float(d[2][i]) - MAGIC_F, C2, h);
+                    sacc[tl][i] = fmaf(i < 2 ? dA : dB, h, sacc[tl][i]);
                 }
             }
         }
@@ -532,7 +612,7 @@ __device__ __forceinline__ void slice_f16(const SliceB<FMT, MT, HILO>& B, const 
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[tl][i] = fmaf(sacc[tl][i], B.inv[tl][i & 1], acc[tl][i]);
+        for (int i = 0; i < 4; ++i) acc[tl][i] = fmaf(sacc[tl][i], B.tile[tl].scale[i & 1], acc[tl][i]);
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
@@ -546,10 +626,9 @@ __device__ __forceinline__ void store_out(void* out, int dt, size_t idx, float v
 // ------------------------------------------------------------------------- the kernel
 //
 // FMT    block format
-// MT     8-row activation tiles per launch (1 or 2)
+// MT     8-row activation tiles per launch (1, 2 or 4)
 // SL     K-chunks (of up to 16 slices) one CTA walks per slab; its activation fragments for all
 //        of them stay in registers
-// HILO   fp16 hi+lo activation split (Q4_0 / Q8_0 only)
 // SWIGLU two weights (gate, up) and out = silu(gate) * up
 // Cursor over the sequence of stage fills of one CTA: slab -> matrix -> K-chunk.
 struct FillCursor {
@@ -568,7 +647,7 @@ constexpr int OFF_EMPTY = 8 * MAX_STAGES, OFF_ABORT = 16 * MAX_STAGES, OFF_RFULL
 template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
 __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr bool HILO = (FMT == FMT_Q4_0 || FMT == FMT_Q8_0) && MT == 1;
+    constexpr int P = fmt_pieces(FMT, MT);
     constexpr int NMAT = SWIGLU ? 2 : 1;
     constexpr int SLICE_B = fmt_slice_bytes(FMT);
     constexpr int PER_RG = MT * 4 * 32;  // floats one warp contributes per row group
@@ -692,12 +771,12 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     grid_dep_launch();  // the next kernel may begin (its weight prefetch does not depend on us)
     grid_dep_wait();    // activations written by the previous kernel are complete from here on
 
-    SliceB<FMT, MT, HILO> B[SL];
+    SliceB<FMT, MT, P> B[SL];  // written by act_prep_kernel, the previous launch in the stream
 #pragma unroll
     for (int c = 0; c < SL; ++c) {
         const uint32_t gc = ks * SL + c;
         const uint32_t slice = gc * p.spc + s;
-        B[c].build(p, slice, c < nch && slice < p.nslices, g, t);
+        B[c].load(p, slice, c < nch && slice < p.nslices, p.m0 >> 3, lane);
     }
     for (uint32_t i = early; i < p.nstages; ++i) {  // the rest of the ring
         if (pc.unit < p.total_units && pw == warp) issue_fill(pc);
@@ -796,14 +875,14 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
                         const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + s * SLICE_B;
                         const uint8_t* ra = sb + rowA * p.srow + ((phA + coff) & 15);
                         const uint8_t* rb = sb + rowB * p.srow + ((phB + coff) & 15);
-                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, HILO, M1>(B[c], ra, rb, t, acc);
+                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, M1>(B[c], ra, rb, t, acc);
                         else if constexpr (FMT == FMT_Q6_K) {
                             const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(ra) | reinterpret_cast<uintptr_t>(rb)) & 3u;
-                            if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, HILO, M1, true>(B[c], ra, rb, t, acc);
-                            else slice_q6k<MT, HILO, M1, false>(B[c], ra, rb, t, acc);
+                            if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, M1, true>(B[c], ra, rb, t, acc);
+                            else slice_q6k<MT, M1, false>(B[c], ra, rb, t, acc);
                         } else {
                             const uint32_t kl = p.K - slice * 256;
-                            slice_f16<FMT, MT, HILO, M1>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
+                            slice_i8<FMT, MT, P, M1>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
                         }
                     }
                     __syncwarp();
@@ -886,6 +965,7 @@ cudaError_t launch_gemv_fmt(const GemvParams& p, int mt, int sl, dim3 grid, int 
                                           : launch_one<FMT, 1, 4, false, SWIGLU>(p, grid, threads, smem, st);
         if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
         if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 4 && sl == 1) return launch_one<FMT, 4, 1, false, SWIGLU>(p, grid, threads, smem, st);
     } else {
         if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st)
                                           : launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
@@ -894,13 +974,38 @@ cudaError_t launch_gemv_fmt(const GemvParams& p, int mt, int sl, dim3 grid, int 
     return cudaErrorInvalidValue;
 }
 
+template <int FMT>
+cudaError_t launch_prep_fmt(const PrepParams& pp, int mt, cudaStream_t st) {
+    const unsigned units = pp.nslices * pp.tiles_total;
+    const dim3 grid((units + 3) / 4), block(128);
+    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
+    cudaError_t e;
+    if constexpr (KQ) {
+        e = launch_pdl(act_prep_kernel<FMT, 0>, grid, block, 0, st, pp);
+    } else {
+        e = mt == 1 ? launch_pdl(act_prep_kernel<FMT, 3>, grid, block, 0, st, pp) : launch_pdl(act_prep_kernel<FMT, 2>, grid, block, 0, st, pp);
+    }
+    note_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 }  // namespace
 
-// Largest number of K-chunks a CTA may keep activation fragments for, per format and tile count.
+// Largest number of K-chunks a CTA may keep activation fragments for, per format and tile count
+// (the fragments of SL chunks x MT tiles live in registers).
 int gemv_max_sl(int fmt, int mt) {
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
-    if (kq) return mt == 1 ? 4 : 2;
+    if (kq) return mt == 1 ? 4 : mt == 2 ? 2 : 1;
     return 1;
+}
+
+// 8-row tiles per pass: K-quants hold up to four (32 activation rows) when K fits one chunk, two
+// otherwise; Q4_0 / Q8_0 hold one tile of three-piece activations or two tiles of two-piece ones.
+int gemv_tiles_per_pass(int fmt, size_t M, size_t K) {
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    if (M <= 8) return 1;
+    if (M <= 16 || !kq) return 2;
+    return K <= 4096 ? 4 : 2;
 }
 
 struct GemvPlan {
@@ -966,38 +1071,63 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     return true;
 }
 
+// bytes of the activation image: [nslices][tiles_total][NV][32] 16-byte vectors, rounded up to 256
+static size_t gemv_image_bytes(int fmt, size_t M, size_t K, int mt) {
+    const size_t nslices = (K + 255) / 256, tiles = (M + 7) / 8;
+    return (nslices * tiles * (size_t)fmt_image_vectors(fmt, mt) * 32 * 16 + 255) & ~(size_t)255;
+}
+
 size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count) {
-    size_t need = 0;
-    for (int mt = 1; mt <= 2; ++mt) {
-        if (mt == 2 && M <= 8) break;
-        GemvPlan pl;
-        if (!gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl)) continue;
-        if (pl.ksplit > 1) {
-            size_t b = (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float);
-            if (b > need) need = b;
-        }
-    }
+    const int mt = gemv_tiles_per_pass(fmt, M, K);
+    size_t need = gemv_image_bytes(fmt, M, K, mt);
+    GemvPlan pl;
+    if (gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl) && pl.ksplit > 1)
+        need += (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float);
     return need;
 }
 
-// out[M,N] = act[M,K] x W^T for any M, in passes of up to 16 activation rows.
+// out[M,N] = act[M,K] x W^T for any M: one activation-image launch, then passes of up to 8 * MT activation rows.
 cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
                         size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
                         unsigned int* status, bool* ws_too_small) {
     *ws_too_small = false;
-    bool need_reduce = false;
-    uint32_t red_ksplit = 1;
-    for (size_t m0 = 0; m0 < M; m0 += 16) {
-        const uint32_t mc = (uint32_t)(M - m0 < 16 ? M - m0 : 16);
-        const int mt = M <= 8 ? 1 : 2;  // one geometry for every pass, so split-K partials line up
-        GemvPlan pl;
-        if (!gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl)) return cudaErrorInvalidConfiguration;
+    const int mt = gemv_tiles_per_pass(fmt, M, K);  // one geometry for every pass, so split-K partials line up
+    GemvPlan pl;
+    if (!gemv_plan(fmt, (uint32_t)K, (uint32_t)N, mt, swiglu, sm_count, pl)) return cudaErrorInvalidConfiguration;
+    const size_t img_bytes = gemv_image_bytes(fmt, M, K, mt);
+    const size_t part_bytes = pl.ksplit > 1 ? (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float) : 0;
+    if (!ws || ws_bytes < img_bytes + part_bytes || (reinterpret_cast<uintptr_t>(ws) & 15)) {
+        *ws_too_small = true;
+        return cudaSuccess;
+    }
+    PrepParams pp{};
+    pp.act = act;
+    pp.img = static_cast<uint4*>(ws);
+    pp.M = (uint32_t)M;
+    pp.K = (uint32_t)K;
+    pp.nslices = pl.nslices;
+    pp.tiles_total = (uint32_t)((M + 7) / 8);
+    pp.act_dtype = act_dtype;
+    cudaError_t e;
+    switch (fmt) {
+    case FMT_Q4_0: e = launch_prep_fmt<FMT_Q4_0>(pp, mt, st); break;
+    case FMT_Q8_0: e = launch_prep_fmt<FMT_Q8_0>(pp, mt, st); break;
+    case FMT_Q4_K: e = launch_prep_fmt<FMT_Q4_K>(pp, mt, st); break;
+    case FMT_Q6_K: e = launch_prep_fmt<FMT_Q6_K>(pp, mt, st); break;
+    default: return cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return e;
+    const uint32_t rows_per_pass = 8u * (uint32_t)mt;
+    for (size_t m0 = 0; m0 < M; m0 += rows_per_pass) {
+        const uint32_t mc = (uint32_t)(M - m0 < rows_per_pass ? M - m0 : rows_per_pass);
         GemvParams p{};
         p.w[0] = static_cast<const uint8_t*>(w0);
         p.w[1] = static_cast<const uint8_t*>(w1 ? w1 : w0);
         p.act = act;
         p.out = out;
-        p.partial = static_cast<float*>(ws);
+        p.img = static_cast<const uint4*>(ws);
+        p.tiles_total = pp.tiles_total;
+        p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + img_bytes);
         p.M = (uint32_t)M; p.K = (uint32_t)K; p.N = (uint32_t)N;
         p.m0 = (uint32_t)m0; p.mcount = mc;
         p.row_bytes = (uint32_t)(K / fmt_block_size(fmt) * fmt_block_bytes(fmt));
@@ -1008,13 +1138,6 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         p.act_dtype = act_dtype; p.out_dtype = out_dtype;
         p.w_bytes = (unsigned long long)N * p.row_bytes;
         p.status = status;
-        if (pl.ksplit > 1) {
-            size_t need = (size_t)(swiglu ? 2 : 1) * pl.ksplit * M * N * sizeof(float);
-            if (!ws || ws_bytes < need) { *ws_too_small = true; return cudaSuccess; }
-            need_reduce = true;
-            red_ksplit = pl.ksplit;
-        }
-        cudaError_t e;
         switch (fmt) {
         case FMT_Q4_0: e = swiglu ? launch_gemv_fmt<FMT_Q4_0, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
                                   : launch_gemv_fmt<FMT_Q4_0, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
@@ -1028,11 +1151,12 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         }
         if (e != cudaSuccess) return e;
     }
-    if (need_reduce) {
+    if (pl.ksplit > 1) {
         size_t mn = M * N;
         int grid = (int)((mn + 255) / 256);
         if (grid > sm_count * 8) grid = sm_count * 8;
-        splitk_reduce_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(ws), out, out_dtype, mn, red_ksplit, swiglu ? 1 : 0);
+        splitk_reduce_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + img_bytes), out, out_dtype, mn,
+                                                  pl.ksplit, swiglu ? 1 : 0);
         note_launch();
         return cudaGetLastError();
     }

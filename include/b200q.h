@@ -93,8 +93,11 @@ B200Q_API int b200q_storage_bytes(int format, size_t numel, size_t* out_bytes);
 B200Q_API int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int out_dtype, void* stream);
 
 /*
- * Scratch bytes b200q_quant_matmul / b200q_quant_swiglu need for this shape (0 for most
- * decode shapes).  Scratch contents need no initialisation and carry nothing between calls.
+ * Scratch bytes b200q_quant_matmul / b200q_quant_swiglu need for this shape with F32 activations:
+ * 0 for the decode shapes (one activation row); the prepared activation image for 2 <= M < 64 (a few
+ * hundred KB) and for the tensor-core path (2 bytes per activation), plus split-K partial sums when K
+ * is long.  `ws` must be 16-byte aligned.  Scratch contents need no initialisation and carry nothing
+ * between calls, but calls that may overlap on the GPU must not share one scratch buffer.
  * Returns 0 as well when the arguments are invalid; the op itself reports the error.
  */
 B200Q_API size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N);

@@ -47,6 +47,31 @@ def main():
             for g in gathered:
                 assert torch.equal(g.view(torch.int32), y_fused.view(torch.int32)), "ranks disagree on the fused sum"
             assert e1 <= 2e-6 and e2 <= 2e-6, (fmt, n, k, it, e1, e2)
+    # a captured decode step that contains the fused exchange (its epoch lives in device memory) replays to
+    # the bits of the eager step, on every rank; M = 1 (fused) and M = 4 (product + NCCL all-reduce)
+    from boostr_b200.decode_graph import DecodeGraph
+    from boostr_b200.decode_stack import DecodeStack
+
+    for m in (1, 4):
+        stack = DecodeStack(m, rank, world, layers=3, hidden=1024, kv=256, ffn=2048, vocab=4096, seed=21)
+        stack.use_exchange(ex)
+        stack.step()  # communicators and lazy set-up outside capture
+        torch.cuda.synchronize()
+        dist.barrier()
+        runner = DecodeGraph(stack.step, {"x": stack.x}, {"logits": stack.logits, "d": stack.d}).capture()
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(5)  # the same hidden state on every rank
+        for it in range(3):
+            x = torch.randn(m, 1024, device="cuda", generator=gen)
+            eager = {k: v.clone() for k, v in runner.run_eager(x=x).items()}
+            stack.d.zero_()
+            out = runner.replay(x=x)
+            ops.check_device_status()
+            for k in eager:
+                assert torch.equal(out[k], eager[k]), ("graph replay differs from eager", m, it, k)
+            gathered = [torch.empty_like(out["d"]) for _ in range(world)]
+            dist.all_gather(gathered, out["d"])
+            assert all(torch.equal(g, out["d"]) for g in gathered), "ranks disagree after a graph replay"
     ex.close()
     if rank == 0:
         print(f"TP_WORKER_OK world={world} worst_rel_err={worst:.3e}", flush=True)
