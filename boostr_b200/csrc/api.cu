@@ -439,6 +439,35 @@ int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const 
     return B200Q_OK;
 }
 
+int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype, const void* w, void* out_full, size_t M, size_t K,
+                                     size_t n_local, int rank, int world, void* const* bufs, void* stream) {
+    int rc = check_matmul_args("col_parallel_matmul_gather", format, act, act_dtype, w, out_full, DT_F32, M, K, n_local);
+    if (rc) return rc;
+    if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(B200Q_ERR_INVALID_ARG, "col_parallel_matmul_gather: rank %d of world %d (at most %u ranks)", rank, world, TP_MAX_WORLD);
+    if (!bufs) return fail(B200Q_ERR_INVALID_ARG, "col_parallel_matmul_gather: null buffer table");
+    const size_t n_total = n_local * (size_t)world;
+    if (M != 1 || n_total > (size_t)TP_MAX_WORLD * TP_MAX_N || !gemv_m1_supported(format, M, K, n_local, false))
+        return fail(B200Q_ERR_NOT_FUSED,
+                    "col_parallel_matmul_gather: no fused gather for %s M=%zu K=%zu N=%zu x %d ranks; use quant_matmul + all-gather",
+                    format_name(format), M, K, n_local, world);
+    PeerComm comm{};
+    comm.world = (uint32_t)world;
+    comm.rank = (uint32_t)rank;
+    comm.gather = 1;
+    comm.n_total = (uint32_t)n_total;
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r]) return fail(B200Q_ERR_INVALID_ARG, "col_parallel_matmul_gather: null exchange buffer of rank %d", r);
+        comm.buf[r] = static_cast<uint8_t*>(bufs[r]);
+    }
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "col_parallel_matmul_gather: cannot resolve the device status word");
+    cudaError_t e = launch_gemv_m1_rowpar(format, act, act_dtype, w, out_full, K, n_local, sm_count_current(),
+                                          static_cast<cudaStream_t>(stream), status, comm);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA col_parallel_matmul_gather kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
 int b200q_check_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "stream synchronize failed: %s", cudaGetErrorString(e));

@@ -180,6 +180,8 @@ constexpr uint32_t TP_MAX_WORLD = 8, TP_MAX_N = 16384;
 constexpr size_t TP_BUF_BYTES = 1024 + 2 * (size_t)TP_MAX_WORLD * TP_MAX_N * 8;
 struct PeerComm {
     uint32_t world, rank;  // world <= 1: no exchange
+    uint32_t gather;       // 0: add the ranks' partial rows (row-parallel); 1: place the ranks' row slices side by side (column-parallel)
+    uint32_t n_total;      // gather: length of the assembled row (world * local rows, <= TP_MAX_WORLD * TP_MAX_N)
     uint8_t* buf[TP_MAX_WORLD];
 };
 __device__ __forceinline__ size_t tp_slot(uint32_t e, uint32_t src, uint32_t row) {
@@ -195,6 +197,51 @@ __device__ __forceinline__ void tp_push(const PeerComm& c, uint32_t e, uint32_t 
     const unsigned long long word = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
     for (uint32_t r = 0; r < c.world; ++r)
         asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(c.buf[r] + off), "l"(word) : "memory");
+}
+// Column-parallel gather: element `col` of the assembled row [0, n_total) lives at slot `col` of the epoch's
+// parity half (the same memory the row-parallel exchange uses as [rank][row]; the two kinds of exchange may
+// alternate freely because consecutive epochs never share a half).
+__device__ __forceinline__ size_t tp_gather_slot(uint32_t e, uint32_t col) {
+    return 1024 + ((size_t)(e & 1u) * TP_MAX_WORLD * TP_MAX_N + col) * 8;
+}
+__device__ __forceinline__ void tp_push_gather(const PeerComm& c, uint32_t e, uint32_t col, float v) {
+    const size_t off = tp_gather_slot(e, col);
+    const unsigned long long word = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
+    for (uint32_t r = 0; r < c.world; ++r)
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(c.buf[r] + off), "l"(word) : "memory");
+}
+// Called by ALL threads of every CTA after its last tp_push_gather: CTA b copies columns
+// [b * chunk, (b + 1) * chunk) of the assembled row from this rank's buffer to `out` once their tags have arrived.
+__device__ __forceinline__ void tp_finish_gather(const PeerComm& c, uint32_t e, float* out, unsigned int* status) {
+    bool lost = (*reinterpret_cast<volatile unsigned int*>(status) & STATUS_TIMEOUT_PEER) != 0;
+    const uint32_t chunk = (c.n_total + gridDim.x - 1) / gridDim.x;
+    const uint32_t begin = min(c.n_total, blockIdx.x * chunk), end = min(c.n_total, begin + chunk);
+    for (uint32_t col = begin + threadIdx.x; col < end; col += blockDim.x) {
+        const uint8_t* slot = c.buf[c.rank] + tp_gather_slot(e, col);
+        unsigned long long word = 0;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0;; ++spin) {
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(slot) : "memory");
+            if ((uint32_t)(word >> 32) == e || lost) break;
+            if ((spin & 63u) == 63u) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > 1000000000ull) {
+                    atomicOr(status, STATUS_TIMEOUT_PEER);
+                    lost = true;
+                }
+            }
+        }
+        out[col] = __uint_as_float((uint32_t)word);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t* ctl = reinterpret_cast<uint32_t*>(c.buf[c.rank]);
+        if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {  // the CTA that finishes last closes the epoch
+            ctl[1] = 0;
+            ctl[0] = e;
+        }
+    }
 }
 // Called by ALL threads of every CTA after its last tp_push: adds up rows [row_begin, row_end).
 __device__ __forceinline__ void tp_finish(const PeerComm& c, uint32_t e, uint32_t row_begin, uint32_t row_end, float* out,

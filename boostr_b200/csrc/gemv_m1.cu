@@ -286,7 +286,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             while (sg + 1 < p.nseg && v >= p.seg_end[sg]) seg_begin = p.seg_end[sg++];
             const size_t idx = v - seg_begin;
             void* o = p.out[sg];
-            if (tp) tp_push(p.comm, tp_e, v, term);
+            if (tp && p.comm.gather) tp_push_gather(p.comm, tp_e, p.comm.rank * p.N + v, term);
+            else if (tp) tp_push(p.comm, tp_e, v, term);
             else if (p.out_dtype == DT_F32) static_cast<float*>(o)[idx] = term;
             else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(o)[idx] = __float2bfloat16_rn(term);
             else static_cast<__half*>(o)[idx] = __float2half_rn(term);
@@ -305,7 +306,8 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
             par ^= 1;
         }
     }
-    if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out[0]), p.status);
+    if (tp && p.comm.gather) tp_finish_gather(p.comm, tp_e, static_cast<float*>(p.out[0]), p.status);
+    else if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out[0]), p.status);
 }
 
 template <bool SWIGLU>
@@ -489,7 +491,8 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
     }
 
     auto store_row = [&](uint32_t row, float val) {
-        if (tp) tp_push(p.comm, tp_e, row, val);
+        if (tp && p.comm.gather) tp_push_gather(p.comm, tp_e, p.comm.rank * p.N + row, val);
+        else if (tp) tp_push(p.comm, tp_e, row, val);
         else if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[row] = val;
         else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[row] = __float2bfloat16_rn(val);
         else static_cast<__half*>(p.out)[row] = __float2half_rn(val);
@@ -544,7 +547,8 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
             par ^= 1;
         }
     }
-    if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out), p.status);
+    if (tp && p.comm.gather) tp_finish_gather(p.comm, tp_e, static_cast<float*>(p.out), p.status);
+    else if (tp) tp_finish(p.comm, tp_e, row_begin, row_end, static_cast<float*>(p.out), p.status);
 }
 
 template <int NCHUNK>

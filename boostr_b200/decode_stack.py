@@ -15,7 +15,7 @@ import torch
 
 from . import ops, synth
 from .linear import QuantLinear
-from .tensor_parallel import ColumnParallelQuantLinear, PeerExchange, RowParallelQuantLinear, gather_from_ranks
+from .tensor_parallel import ColumnParallelQuantLinear, PeerExchange, RowParallelQuantLinear
 
 # (name, format, N, K, parallel split) of one layer of a Llama-3-8B-shaped model in a Q4_K_M-style mix
 HIDDEN, KV, FFN, VOCAB, LAYERS = 4096, 1024, 14336, 128256, 32
@@ -82,7 +82,8 @@ class DecodeStack:
             L["o"].forward(self.q, out=self.o)                      # row-parallel: all-reduce inside
             ops.quant_swiglu(self.o, L["gate"].weight, L["up"].weight, out=self.h)
             L["down"].forward(self.h, out=self.d)                   # row-parallel: all-reduce inside
-        self.lm_head.forward(self.x, out=self.logits_local)
         if self.world > 1:
-            gather_from_ranks(self.logits_local, out=self.logits)
+            self.lm_head.forward_gathered(self.x, self.logits, self.exchange, local=self.logits_local)
+        else:
+            self.lm_head.forward(self.x, out=self.logits_local)
         return self.logits

@@ -123,6 +123,25 @@ def row_parallel_matmul(activation: torch.Tensor, weight: QuantTensor, rank: int
     return out
 
 
+def col_parallel_matmul_gather(activation: torch.Tensor, weight: QuantTensor, rank: int, world: int, table,
+                               out_full: torch.Tensor):
+    """Local product of a column-parallel shard fused with the gather of all ranks' slices into
+    ``out_full`` [..., world * n_local] (``b200q_col_parallel_matmul_gather``).  Returns None, having
+    launched nothing, when the shape has no fused path."""
+    act, m, k, n = _check_act("col_parallel_matmul_gather", activation, weight, True)
+    if m != 1:
+        return None
+    out_full = _out_buffer(out_full, (*activation.shape[:-1], n * world), torch.float32, act.device)
+    L = _cabi.lib()
+    with torch.cuda.device(act.device):
+        rc = L.b200q_col_parallel_matmul_gather(weight.format.format_id, act.data_ptr(), _DT[act.dtype], weight.storage.data_ptr(),
+                                                out_full.data_ptr(), m, k, n, rank, world, table, _stream())
+    if rc == _cabi.ERR_NOT_FUSED:
+        return None
+    _cabi.check(rc)
+    return out_full
+
+
 def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
                        out_dtype: torch.dtype = torch.float32, outs: Sequence[torch.Tensor] = None) -> List[torch.Tensor]:
     """One activation against several weights sharing K (q/k/v, gate/up)."""

@@ -173,6 +173,17 @@ class ColumnParallelQuantLinear:
 
     __call__ = forward
 
+    def forward_gathered(self, input: torch.Tensor, out_full: torch.Tensor, exchange: Optional["PeerExchange"] = None,
+                         local: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Local product followed by the gather of every rank's slice into row-major ``out_full``
+        [..., world * N/P].  With a ``PeerExchange`` and one activation row the product and the gather are ONE
+        kernel (the slice is pushed to all ranks over NVLink); otherwise ``forward`` + ``gather_from_ranks``."""
+        if exchange is not None and exchange.table is not None and input.is_cuda and self.bias is None:
+            y = ops.col_parallel_matmul_gather(input, self.weight, exchange.rank, exchange.world, exchange.table, out_full)
+            if y is not None:
+                return y
+        return gather_from_ranks(self.forward(input, out=local), self.group, out=out_full)
+
 
 class RowParallelQuantLinear:
     """Input features split across ranks; forward = local product, all-reduce SUM, then bias.

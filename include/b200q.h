@@ -222,6 +222,20 @@ B200Q_API int b200q_tp_free(void* buf);
 B200Q_API int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype,
                                         size_t M, size_t K, size_t N, int rank, int world, void* const* bufs, void* stream);
 
+/*
+ * Column-parallel counterpart: the local product of a row shard [n_local, K] fused with the all-gather of
+ * the logits (gather_from_ranks, src/distributed/tensor_parallel.rs:302-355, used after a column-parallel
+ * lm_head).  Every element of the local result is pushed, tagged, into column rank * n_local + i of every
+ * rank's exchange buffer; each rank then copies the assembled row [world * n_local] into `out_full`
+ * (row-major, shard r in columns [r * n_local, (r + 1) * n_local): the layout the reference's flat gather
+ * only gives for one row).  Same set-up, ordering rules and bounded waits as b200q_row_parallel_matmul;
+ * the two may alternate on one set of buffers.  M = 1, Q4_K / Q6_K, world * n_local <= 131072, f32 output;
+ * anything else returns B200Q_ERR_NOT_FUSED without launching.
+ */
+B200Q_API int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype, const void* w, void* out_full,
+                                               size_t M, size_t K, size_t n_local, int rank, int world, void* const* bufs,
+                                               void* stream);
+
 #ifdef __cplusplus
 }
 #endif

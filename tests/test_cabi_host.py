@@ -31,6 +31,15 @@ def test_header_symbols_are_exported(lib):
         assert getattr(lib, name) is not None
 
 
+def test_rust_extern_block_names_the_header_symbols():
+    # the Rust -sys crate cannot be compiled here; at least its declarations must cover the header exactly
+    hdr = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    declared = set(re.findall(r"B200Q_API\s+[\w\s\*]+?\b(b200q_\w+)\s*\(", hdr))
+    rs = open(os.path.join(ROOT, "rust", "b200q-sys", "src", "lib.rs")).read()
+    bound = set(re.findall(r"pub fn (b200q_\w+)\s*\(", rs))
+    assert bound == declared, bound ^ declared
+
+
 def test_format_tables(lib):
     for f in F:
         assert lib.b200q_block_size(f.format_id) == f.block_size

@@ -95,6 +95,59 @@ def test_row_parallel_exchange_against_staged_peer(ops, fmt, n, k):
             L.b200q_tp_free(b)
 
 
+@pytest.mark.parametrize("fmt,n_local,k", [("Q6_K", 16032, 4096), ("Q4_K", 300, 1024), ("Q6_K", 37, 512)])
+def test_col_parallel_gather_against_staged_peer(ops, fmt, n_local, k):
+    """Fused column-parallel gather (b200q_col_parallel_matmul_gather) on one GPU: rank 1's slice of the
+    assembled row is staged by the host with the right tags before the launch; rank 0 must deliver
+    [own slice | peer slice] and leave its own slice, tagged, in the peer's buffer.  The row-parallel exchange
+    alternates with it on the same buffers (both kinds share the epoch)."""
+    rt = _cudart()
+    L = _cabi.lib()
+    torch.cuda.synchronize()
+    bufs, table = [], (ctypes.c_void_p * 2)()
+    for r in range(2):
+        b, h = ctypes.c_void_p(), ctypes.create_string_buffer(_cabi.TP_HANDLE_BYTES)
+        _cabi.check(L.b200q_tp_alloc(ctypes.byref(b), h))
+        bufs.append(b.value)
+        table[r] = b.value
+    try:
+        rng = synth.rng_for(44, n_local + k)
+        f = QuantFormat.parse(fmt)
+        shards = [QuantTensor.from_bytes(synth.weight_bytes(fmt, rng, n_local, k), f, (n_local, k), device="cuda") for _ in range(2)]
+        half_bytes = 8 * 16384 * 8  # one parity half of the exchange area
+        for call in range(1, 4):
+            act = torch.from_numpy(synth.activations(rng, 1, k)).cuda()
+            y = [ops.quant_matmul(act, shards[r]) for r in range(2)]
+            torch.cuda.synchronize()
+            par = call & 1
+            staged = np.empty((n_local, 2), dtype=np.uint32)
+            staged[:, 0] = y[1].cpu().numpy().reshape(-1).view(np.uint32)
+            staged[:, 1] = call
+            _h2d(rt, bufs[0] + INBOX0 + par * half_bytes + n_local * 8, staged)   # columns [n_local, 2 n_local)
+            full = torch.full((1, 2 * n_local), float("nan"), device="cuda")
+            out = ops.col_parallel_matmul_gather(act, shards[0], 0, 2, table, full)
+            assert out is not None
+            ops.check_device_status()
+            want = torch.cat(y, dim=-1)
+            assert torch.equal(out.view(torch.int32), want.view(torch.int32)), f"call {call}"
+            pushed = _d2h(rt, bufs[1] + INBOX0 + par * half_bytes, n_local * 8).view(np.uint32).reshape(n_local, 2)
+            assert np.array_equal(pushed[:, 0], y[0].cpu().numpy().reshape(-1).view(np.uint32)) and (pushed[:, 1] == call).all()
+            ctl = _d2h(rt, bufs[0], 8).view(np.uint32)
+            assert ctl[0] == call and ctl[1] == 0
+        # shapes without a fused gather launch nothing
+        before = ops.launch_count()
+        big = QuantTensor.from_bytes(synth.weight_bytes("Q4_K", rng, 70000, 256), QuantFormat.Q4_K, (70000, 256), device="cuda")
+        a256 = torch.from_numpy(synth.activations(rng, 1, 256)).cuda()
+        assert ops.col_parallel_matmul_gather(a256, big, 0, 2, table, torch.empty(1, 140000, device="cuda")) is None
+        a2 = torch.from_numpy(synth.activations(rng, 2, k)).cuda()
+        assert ops.col_parallel_matmul_gather(a2, shards[0], 0, 2, table, torch.empty(2, 2 * n_local, device="cuda")) is None
+        assert ops.launch_count() == before
+    finally:
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.b200q_tp_free(b)
+
+
 def test_row_parallel_shapes_without_fused_path_launch_nothing(ops):
     L = _cabi.lib()
     b, h = ctypes.c_void_p(), ctypes.create_string_buffer(_cabi.TP_HANDLE_BYTES)

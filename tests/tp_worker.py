@@ -47,6 +47,21 @@ def main():
             for g in gathered:
                 assert torch.equal(g.view(torch.int32), y_fused.view(torch.int32)), "ranks disagree on the fused sum"
             assert e1 <= 2e-6 and e2 <= 2e-6, (fmt, n, k, it, e1, e2)
+    # fused column-parallel gather of logits against NCCL all-gather + strided copy (M = 1)
+    from boostr_b200.tensor_parallel import ColumnParallelQuantLinear, gather_from_ranks
+    for case, (fmt, n, k) in enumerate([("Q6_K", 128256 // 8 * world, 4096), ("Q4_K", 96 * world, 1024)]):
+        rng = synth.rng_for(78, case)
+        full = synth.weight_bytes(fmt, rng, n, k)
+        col = ColumnParallelQuantLinear.from_full(fmt, full, n, k, rank, world)
+        whole = QuantTensor.from_bytes(full, QuantFormat.parse(fmt), (n, k), device="cuda")
+        for it in range(4):
+            act = torch.from_numpy(synth.activations(rng, 1, k)).cuda()
+            fused = col.forward_gathered(act, torch.empty(1, n, device="cuda"), ex).clone()
+            plain = gather_from_ranks(col(act))
+            one = ops.quant_matmul(act, whole)
+            ops.check_device_status()
+            assert torch.equal(fused, plain), ("fused gather differs from NCCL gather", fmt, it)
+            assert torch.equal(fused, one), ("gathered logits differ from the unsharded product", fmt, it)
     # a captured decode step that contains the fused exchange (its epoch lives in device memory) replays to
     # the bits of the eager step, on every rank; M = 1 (fused) and M = 4 (product + NCCL all-reduce)
     from boostr_b200.decode_graph import DecodeGraph
