@@ -9,6 +9,7 @@
 
 #include "../../include/b200q.h"
 #include "common.cuh"
+#include "tmap.cuh"
 
 namespace b200q {
 cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, int out_dtype, cudaStream_t st, int sm_count);
@@ -46,6 +47,18 @@ std::atomic<unsigned long long> g_launches{0};
 }
 namespace b200q {
 void note_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
 }  // namespace b200q
 
 // One status word per device image of this library; kernels receive its address.

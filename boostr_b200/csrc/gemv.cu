@@ -32,6 +32,7 @@
 //   * When K is too long for one CTA's registers (K > 16 slices * chunks-per-CTA) the K-chunks are
 //     spread over gridDim.y and a second small kernel adds the partials in K order.
 #include "common.cuh"
+#include "tmap.cuh"
 
 namespace b200q {
 
@@ -60,6 +61,12 @@ struct GemvParams {
     uint32_t red_slots;   // slots in the reduction ring (3 or 4)
     uint32_t stage_off;   // byte offset of stage 0
     uint32_t rows_aligned;  // 1 when every row chunk starts and ends on a 16-byte boundary
+    // Tiled fills: the packed weights are described to the copy engine as a 3-D tensor
+    // [row_bytes / tma_w columns][N rows][tma_w bytes]; ONE copy brings the tma_cb columns of a K-chunk for all
+    // rows of a slab and lays them out column by column, [tma_cb][rows per slab][tma_w].  tma_w is a whole number
+    // of slices chosen so that consecutive rows (tma_w bytes apart) start in different shared-memory banks.
+    uint32_t use_tma;
+    uint32_t tma_w, tma_cb;
     int act_dtype, out_dtype;
     unsigned long long w_bytes;  // bytes of each weight tensor
     unsigned int* status;        // device status word (bounded-wait timeouts)
@@ -250,10 +257,10 @@ struct TileB<FMT_Q6_K, P> {
 };
 
 // ---- Q8_0 / Q4_0: every activation as P int8 pieces, x = (amax/127) * (a1 + a2/254 [+ a3/254^2]) ----
-// The lane holds the 8 consecutive elements 8t..8t+7 of each 32-block.  K order inside a block follows
-// what the weight side reads without shuffling bytes:
-//   Q8_0: the lane's two code words -> k-slots 4t..4t+3 = elements 8t..8t+3, k-slots 16+4t.. = elements 8t+4..8t+7
-//   Q4_0: byte i of the lane's word holds elements 8t+2i (low nibble) and 8t+2i+1 (high nibble)
+// K order inside a 32-block follows what the weight side reads without shuffling bytes:
+//   Q8_0: the lane's two code words are bytes 4t..4t+3 and 16+4t..16+4t+3
+//         -> k-slots 4t..4t+3 = elements 4t..4t+3, k-slots 16+4t.. = elements 16+4t..16+4t+3
+//   Q4_0: byte i of the lane's word (bytes 4t..4t+3) holds elements 8t+2i (low nibble) and 8t+2i+1 (high nibble)
 //         -> k-slots 4t..4t+3 = elements 8t+{0,2,4,6}, k-slots 16+4t.. = elements 8t+{1,3,5,7}
 constexpr float PIECE_STEP = 254.0f;
 template <int FMT, int P>
@@ -265,14 +272,24 @@ struct TileBI8 {
     __device__ __forceinline__ void build(const PrepParams& p, uint32_t slice, uint32_t m_first, uint32_t rows, int g, int t) {
         const bool on = (uint32_t)g < rows;
         const uint32_t kleft = p.K - slice * 256;  // elements of this slice that exist (ragged last slice)
-        const size_t base = (size_t)(m_first + g) * p.K + (size_t)slice * 256 + 8 * t;
+        const size_t base = (size_t)(m_first + g) * p.K + (size_t)slice * 256 + (FMT == FMT_Q8_0 ? 4 : 8) * t;
         float v[8][8];
 #pragma unroll
         for (int b = 0; b < 8; ++b) {
-            if (on && 32u * b < kleft) load_act8(p.act, p.act_dtype, base + 32 * b, v[b]);
-            else
+            if (on && 32u * b < kleft) {
+                if constexpr (FMT == FMT_Q8_0) {
+                    float lo4[4], hi4[4];
+                    load_act4(p.act, p.act_dtype, base + 32 * b, lo4);
+                    load_act4(p.act, p.act_dtype, base + 32 * b + 16, hi4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { v[b][i] = lo4[i]; v[b][4 + i] = hi4[i]; }
+                } else {
+                    load_act8(p.act, p.act_dtype, base + 32 * b, v[b]);
+                }
+            } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[b][i] = 0.f;
+            }
         }
         float amax = 0.f;
 #pragma unroll
@@ -570,17 +587,12 @@ __device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint
             uint32_t a0, a1, a2, a3;  // row g k-slots 4t.. | row g+8 | row g k-slots 16+4t.. | row g+8
             float dA = f16bits_to_f32(lds16(ra + BB * b)), dB = f16bits_to_f32(lds16(rb + BB * b));
             if constexpr (FMT == FMT_Q8_0) {
-                // block = f16 d | 32 x i8; the lane's 8 codes are bytes 8t..8t+7 (2-byte aligned): three aligned words
-                const uint8_t* pa = ra + BB * b + 2 + 8 * t;
-                const uint8_t* pb = rb + BB * b + 2 + 8 * t;
-                const uint32_t sha = (uint32_t)(reinterpret_cast<uintptr_t>(pa) & 3u) * 8u, shb = (uint32_t)(reinterpret_cast<uintptr_t>(pb) & 3u) * 8u;
-                const uint32_t* wa = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(pa) & ~(uintptr_t)3);
-                const uint32_t* wb = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(pb) & ~(uintptr_t)3);
-                const uint32_t x0 = wa[0], x1 = wa[1], x2 = wa[2], y0 = wb[0], y1 = wb[1], y2 = wb[2];
-                a0 = __funnelshift_r(x0, x1, sha);
-                a2 = __funnelshift_r(x1, x2, sha);
-                a1 = __funnelshift_r(y0, y1, shb);
-                a3 = __funnelshift_r(y1, y2, shb);
+                // block = f16 d | 32 x i8 (2-byte aligned); the lane's codes are bytes 4t..4t+3 and 16+4t..16+4t+3, so the
+                // four lanes of a row read 16 contiguous bytes per load
+                a0 = lds32_u(ra + BB * b + 2 + 4 * t);
+                a2 = lds32_u(ra + BB * b + 18 + 4 * t);
+                a1 = lds32_u(rb + BB * b + 2 + 4 * t);
+                a3 = lds32_u(rb + BB * b + 18 + 4 * t);
             } else {
                 // Q4_0 block = f16 d | 16 B; byte i = elements 2i (low nibble), 2i+1 (high); the lane's word = bytes 4t..4t+3.
                 // (w ^ 0x88..) keeps each nibble as q - 8 in 4-bit two's complement; placed in the high nibble of a byte
@@ -623,6 +635,12 @@ __device__ __forceinline__ void store_out(void* out, int dt, size_t idx, float v
     else static_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+                 : "memory");
+}
+
 // ------------------------------------------------------------------------- the kernel
 //
 // FMT    block format
@@ -645,7 +663,8 @@ constexpr int OFF_EMPTY = 8 * MAX_STAGES, OFF_ABORT = 16 * MAX_STAGES, OFF_RFULL
               OFF_REMPTY = OFF_RFULL + 8 * RED_SLOTS;
 
 template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
-__global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const __grid_constant__ CUtensorMap tmap0, const __grid_constant__ CUtensorMap tmap1,
+                                                          const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int P = fmt_pieces(FMT, MT);
     constexpr int NMAT = SWIGLU ? 2 : 1;
@@ -697,7 +716,14 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
         const uint32_t cbytes = min(p.spc * SLICE_B, p.row_bytes - coff);
         const uint32_t sdst = stage0 + stage * p.stage_bytes;
         const uint32_t bar = bar_full + 8 * stage;
-        if (p.rows_aligned) {
+        if (p.use_tma) {
+            // one lane, one copy per box; rows past the end of the tensor are filled with zeros by the copy
+            // engine and still count towards the byte total
+            if (lane == 0) {
+                mbar_expect_tx(bar, p.tma_cb * rps * p.tma_w);
+                tma_load_3d(sdst, cur.mat ? &tmap1 : &tmap0, 0, (int)r0, (int)(coff / p.tma_w), bar);
+            }
+        } else if (p.rows_aligned) {
             if (lane == 0) mbar_expect_tx(bar, nrows * cbytes);
             __syncwarp();
             for (uint32_t r = lane; r < nrows; r += 32)
@@ -767,6 +793,8 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t s = warp % p.spc;   // slice within a chunk
     const uint32_t rg = warp / p.spc;  // row group within a slab
+    // tiled fills: byte offset of row 0 of this warp's slice in a stage (column c of the chunk, then within the column)
+    const uint32_t tma_off = p.use_tma ? ((s * SLICE_B) / p.tma_w) * (16u * p.rgs) * p.tma_w + (s * SLICE_B) % p.tma_w : 0u;
 
     grid_dep_launch();  // the next kernel may begin (its weight prefetch does not depend on us)
     grid_dep_wait();    // activations written by the previous kernel are complete from here on
@@ -786,7 +814,7 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
 
     // Adds up the partial sums of slab `unit_j` (ring slot `js`) and stores the results: one
     // output per lane and pass, the slices' terms added in K order.
-    const uint32_t mcp = p.mcount <= 1 ? 1u : p.mcount <= 2 ? 2u : p.mcount <= 4 ? 4u : p.mcount <= 8 ? 8u : 16u;
+    const uint32_t mcp = p.mcount <= 1 ? 1u : p.mcount <= 2 ? 2u : p.mcount <= 4 ? 4u : p.mcount <= 8 ? 8u : p.mcount <= 16 ? 16u : 32u;
     const uint32_t mcp_log = 31 - __clz(mcp);
     auto reduce_slab = [&](uint32_t unit_j, uint32_t js, uint32_t jpar) {
         if (!dead && !mbar_wait(bar_rfull + 8 * js, jpar)) give_up(STATUS_TIMEOUT_FULL);
@@ -872,9 +900,16 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const GemvParams p) {
                     const uint32_t slice = gc * p.spc + s;
                     if (!dead && slice < p.nslices) {
                         const uint32_t coff = gc * p.spc * SLICE_B;
-                        const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + s * SLICE_B;
-                        const uint8_t* ra = sb + rowA * p.srow + ((phA + coff) & 15);
-                        const uint8_t* rb = sb + rowB * p.srow + ((phB + coff) & 15);
+                        const uint8_t *ra, *rb;
+                        if (p.use_tma) {
+                            const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + tma_off;
+                            ra = sb + rowA * p.tma_w;
+                            rb = sb + rowB * p.tma_w;
+                        } else {
+                            const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + s * SLICE_B;
+                            ra = sb + rowA * p.srow + ((phA + coff) & 15);
+                            rb = sb + rowB * p.srow + ((phB + coff) & 15);
+                        }
                         if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, M1>(B[c], ra, rb, t, acc);
                         else if constexpr (FMT == FMT_Q6_K) {
                             const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(ra) | reinterpret_cast<uintptr_t>(rb)) & 3u;
@@ -941,35 +976,39 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
+struct GemvMaps {
+    CUtensorMap m[2];
+};
+
 template <int FMT, int MT, int SL, bool M1, bool SWIGLU>
-cudaError_t launch_one(const GemvParams& p, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+cudaError_t launch_one(const GemvParams& p, const GemvMaps& maps, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     auto k = gemv_kernel<FMT, MT, SL, M1, SWIGLU>;
     static PerDeviceOnce attrs;
     cudaError_t ae = attrs.run([&] { return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024); });
     if (ae != cudaSuccess) return ae;
-    cudaError_t le = launch_pdl(k, grid, dim3(threads), smem, st, p);
+    cudaError_t le = launch_pdl(k, grid, dim3(threads), smem, st, maps.m[0], maps.m[1], p);
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 template <int FMT, bool SWIGLU>
-cudaError_t launch_gemv_fmt(const GemvParams& p, int mt, int sl, dim3 grid, int threads, size_t smem, cudaStream_t st) {
+cudaError_t launch_gemv_fmt(const GemvParams& p, const GemvMaps& maps, int mt, int sl, dim3 grid, int threads, size_t smem, cudaStream_t st) {
     constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
     const bool m1 = p.mcount == 1 && p.M == 1;
     if constexpr (KQ) {
-        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st)
-                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 1 && sl == 2) return m1 ? launch_one<FMT, 1, 2, true, SWIGLU>(p, grid, threads, smem, st)
-                                          : launch_one<FMT, 1, 2, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 1 && sl == 4) return m1 ? launch_one<FMT, 1, 4, true, SWIGLU>(p, grid, threads, smem, st)
-                                          : launch_one<FMT, 1, 4, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 4 && sl == 1) return launch_one<FMT, 4, 1, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, maps, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 1 && sl == 2) return m1 ? launch_one<FMT, 1, 2, true, SWIGLU>(p, maps, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 2, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 1 && sl == 4) return m1 ? launch_one<FMT, 1, 4, true, SWIGLU>(p, maps, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 4, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 4 && sl == 1) return launch_one<FMT, 4, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
     } else {
-        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, grid, threads, smem, st)
-                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, grid, threads, smem, st);
-        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, grid, threads, smem, st);
+        if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, maps, grid, threads, smem, st)
+                                          : launch_one<FMT, 1, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
+        if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
     }
     return cudaErrorInvalidValue;
 }
@@ -1011,6 +1050,7 @@ int gemv_tiles_per_pass(int fmt, size_t M, size_t K) {
 struct GemvPlan {
     uint32_t spc, nslices, nchunks, sl, ksplit, rgs, srow, stage_bytes, nstages, total_units, red_off, stage_off;
     uint32_t red_slot_bytes, red_slots, rows_aligned;
+    uint32_t use_tma, tma_w, tma_cb;
     size_t smem;
     int threads;
     dim3 grid;
@@ -1047,6 +1087,17 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     pl.rows_aligned = (row_bytes % 16 == 0 && (pl.spc * slice_b) % 16 == 0) ? 1u : 0u;
     pl.srow = srow;
     pl.stage_bytes = ((16 * pl.rgs * srow + 127) & ~127u) + 128;
+    // Tiled fills (one copy per stage): column width = 2 slices of Q4_K (288 B: rows 32 B apart mod 128 for the
+    // 8-byte reads), 1 slice of Q8_0 / Q4_0 (272 / 144 B: 16 B apart), 8 slices of Q6_K (1680 B, the smallest whole
+    // number of 210-byte blocks that is a multiple of 16 bytes).  Rows must be a whole number of columns.
+    const uint32_t tw = fmt == FMT_Q4_K ? 288u : fmt == FMT_Q6_K ? 1680u : slice_b;
+    pl.use_tma = 0;
+    pl.tma_w = tw;
+    pl.tma_cb = (cmax + tw - 1) / tw;
+    if (tma_available() && K % 256 == 0 && row_bytes % tw == 0 && (pl.spc * slice_b) % tw == 0 && pl.tma_cb <= 256 && 16 * pl.rgs <= 256) {
+        pl.use_tma = 1;
+        pl.stage_bytes = ((pl.tma_cb * 16 * pl.rgs * tw + 127) & ~127u) + 128;
+    }
     const int nwc = pl.spc * pl.rgs;
     pl.red_slot_bytes = (swiglu ? 2u : 1u) * nwc * mt * 4 * 32 * 4;
     const uint32_t budget = 232448 - 1024;
@@ -1117,6 +1168,28 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     default: return cudaErrorInvalidValue;
     }
     if (e != cudaSuccess) return e;
+    // tiled fills: one 3-D tensor map per weight, [row_bytes / tma_w][N][tma_w bytes as 8-byte elements]
+    GemvMaps maps{};
+    if (pl.use_tma) {
+        const uint32_t row_bytes = (uint32_t)(K / fmt_block_size(fmt) * fmt_block_bytes(fmt));
+        const cuuint64_t gdim[3] = {(cuuint64_t)(pl.tma_w / 8), (cuuint64_t)N, (cuuint64_t)(row_bytes / pl.tma_w)};
+        const cuuint64_t gstride[2] = {(cuuint64_t)row_bytes, (cuuint64_t)pl.tma_w};
+        const cuuint32_t box[3] = {pl.tma_w / 8, 16u * pl.rgs, pl.tma_cb};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const void* ws2[2] = {w0, w1 ? w1 : w0};
+        for (int i = 0; i < 2 && pl.use_tma; ++i) {
+            CUresult cr = encode_tiled()(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(ws2[i]), gdim, gstride, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) pl.use_tma = 0;  // fall back to per-row copies
+        }
+        if (!pl.use_tma) {
+            pl.stage_bytes = ((16 * pl.rgs * pl.srow + 127) & ~127u) + 128;
+            uint32_t ns = (232448u - 1024u - pl.stage_off) / pl.stage_bytes;
+            pl.nstages = ns > (uint32_t)MAX_STAGES ? (uint32_t)MAX_STAGES : ns;
+            pl.smem = pl.stage_off + (size_t)pl.nstages * pl.stage_bytes;
+        }
+    }
     const uint32_t rows_per_pass = 8u * (uint32_t)mt;
     for (size_t m0 = 0; m0 < M; m0 += rows_per_pass) {
         const uint32_t mc = (uint32_t)(M - m0 < rows_per_pass ? M - m0 : rows_per_pass);
@@ -1135,18 +1208,19 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         p.srow = pl.srow; p.stage_bytes = pl.stage_bytes; p.nstages = pl.nstages; p.total_units = pl.total_units;
         p.red_off = pl.red_off; p.stage_off = pl.stage_off;
         p.red_slot_bytes = pl.red_slot_bytes; p.red_slots = pl.red_slots; p.rows_aligned = pl.rows_aligned;
+        p.use_tma = pl.use_tma; p.tma_w = pl.tma_w; p.tma_cb = pl.tma_cb;
         p.act_dtype = act_dtype; p.out_dtype = out_dtype;
         p.w_bytes = (unsigned long long)N * p.row_bytes;
         p.status = status;
         switch (fmt) {
-        case FMT_Q4_0: e = swiglu ? launch_gemv_fmt<FMT_Q4_0, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
-                                  : launch_gemv_fmt<FMT_Q4_0, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
-        case FMT_Q8_0: e = swiglu ? launch_gemv_fmt<FMT_Q8_0, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
-                                  : launch_gemv_fmt<FMT_Q8_0, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
-        case FMT_Q4_K: e = swiglu ? launch_gemv_fmt<FMT_Q4_K, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
-                                  : launch_gemv_fmt<FMT_Q4_K, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
-        case FMT_Q6_K: e = swiglu ? launch_gemv_fmt<FMT_Q6_K, true>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
-                                  : launch_gemv_fmt<FMT_Q6_K, false>(p, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q4_0: e = swiglu ? launch_gemv_fmt<FMT_Q4_0, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q4_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q8_0: e = swiglu ? launch_gemv_fmt<FMT_Q8_0, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q8_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q4_K: e = swiglu ? launch_gemv_fmt<FMT_Q4_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q4_K, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q6_K: e = swiglu ? launch_gemv_fmt<FMT_Q6_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q6_K, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         default: return cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;

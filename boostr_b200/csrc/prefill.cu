@@ -32,6 +32,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tmap.cuh"
 
 namespace b200q {
 
@@ -572,22 +573,6 @@ __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restric
         else if (out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
         else static_cast<__half*>(out)[i] = __float2half_rn(v);
     }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
 }
 
 uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
