@@ -12,7 +12,8 @@
 #include "tmap.cuh"
 
 namespace b200q {
-cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, int out_dtype, cudaStream_t st, int sm_count);
+cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, int out_dtype, cudaStream_t st, int sm_count,
+                           unsigned int* status);
 cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
                         size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
                         unsigned int* status, bool* ws_too_small);
@@ -187,7 +188,9 @@ int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int o
     if (!w || !out) return fail(B200Q_ERR_INVALID_ARG, "dequantize: null pointer");
     if (reinterpret_cast<uintptr_t>(w) & 15) return fail(B200Q_ERR_INVALID_ARG, "dequantize: weight pointer must be 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(out) & 15) return fail(B200Q_ERR_INVALID_ARG, "dequantize: output pointer must be 16-byte aligned");
-    cudaError_t e = launch_dequant(format, w, nblocks, out, out_dtype, static_cast<cudaStream_t>(stream), sm_count_current());
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "dequantize: cannot resolve the device status word");
+    cudaError_t e = launch_dequant(format, w, nblocks, out, out_dtype, static_cast<cudaStream_t>(stream), sm_count_current(), status);
     if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA dequant kernel launch failed: %s", cudaGetErrorString(e));
     return B200Q_OK;
 }

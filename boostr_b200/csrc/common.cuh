@@ -306,6 +306,35 @@ __device__ __forceinline__ uint32_t lds32_u(const uint8_t* a) {
     return __funnelshift_r(base[0], base[1], (uint32_t)(v & 3u) * 8u);
 }
 
+// The same loads through 32-bit shared-window addresses (ld.shared): no 64-bit generic address arithmetic.
+// volatile keeps them in program order relative to the barrier waits (also volatile); it does not
+// stop the assembler from overlapping them.
+__device__ __forceinline__ uint32_t sld32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t sld16(uint32_t a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 sld64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 sld128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+// 32-bit word at a 2-byte-aligned shared address
+__device__ __forceinline__ uint32_t sld32_u(uint32_t a) {
+    const uint32_t base = a & ~3u;
+    return __funnelshift_r(sld32(base), sld32(base + 4), (a & 3u) * 8u);
+}
+
 // ------------------------------------------------------------------------------- MMA
 
 // D(16x8,s32) = A(16x32,u8,row) * B(32x8,s8,col) + C

@@ -407,10 +407,10 @@ __device__ __forceinline__ int byte_s(uint32_t x) {
 }
 
 template <int MT, bool M1>
-__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, const uint8_t* ra, const uint8_t* rb, int t,
+__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, const uint32_t ra, const uint32_t rb, int t,
                                           float (&acc)[MT][4]) {
     const int zero[4] = {0, 0, 0, 0};
-    uint4 ha = lds128(ra), hb = lds128(rb);
+    uint4 ha = sld128(ra), hb = sld128(rb);
     // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
     uint32_t sA[2], mA[2], sB[2], mB[2];
     sA[0] = ha.y & 0x3F3F3F3Fu;
@@ -432,7 +432,7 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, cons
 
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
-        uint2 qa = lds64(ra + 16 + 32 * jj + 8 * t), qb = lds64(rb + 16 + 32 * jj + 8 * t);
+        uint2 qa = sld64(ra + 16 + 32 * jj + 8 * t), qb = sld64(rb + 16 + 32 * jj + 8 * t);
         int scA0, scA1, scB0, scB1;
         if ((jj & 1) == 0) {
             scA0 = byte_u<0>(sA[jj >> 1]); scA1 = byte_u<1>(sA[jj >> 1]);
@@ -505,12 +505,16 @@ __device__ __forceinline__ int byte_s_dyn(const uint32_t (&sc)[4], int sb) {
 template <int SB>
 __device__ __forceinline__ int q6k_scale(const uint32_t (&sc)[4]) { return byte_s<SB & 3>(sc[SB >> 2]); }
 
-// ALIGNED: both slices start on a 4-byte boundary (plain 32-bit loads); otherwise they are only
-// 2-byte aligned and every word is assembled from two.
-template <int MT, bool M1, bool ALIGNED>
-__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, 0>& B, const uint8_t* ra, const uint8_t* rb, int t,
+// ALIGNED 1: both slices start on a 4-byte boundary (plain 32-bit loads); 2: both start exactly 2 bytes past one
+// (a word = two aligned loads at constant offsets and one byte permute); 0: any 2-byte alignment.
+template <int MT, bool M1, int ALIGNED>
+__device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, 0>& B, const uint32_t ra, const uint32_t rb, int t,
                                           float (&acc)[MT][4]) {
-    auto ld = [](const uint8_t* a) { return ALIGNED ? lds32(a) : lds32_u(a); };
+    auto ld = [](uint32_t a) -> uint32_t {
+        if (ALIGNED == 1) return sld32(a);
+        if (ALIGNED == 2) return __byte_perm(sld32(a - 2), sld32(a + 2), 0x5432);  // every word exactly 2 bytes off
+        return sld32_u(a);
+    };
     const int zero[4] = {0, 0, 0, 0};
     int isum[MT][4];
 #pragma unroll
@@ -554,7 +558,7 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, 0>& B, cons
             }
         }
     }
-    const float dA = f16bits_to_f32(lds16(ra + 208)), dB = f16bits_to_f32(lds16(rb + 208));
+    const float dA = f16bits_to_f32(sld16(ra + 208)), dB = f16bits_to_f32(sld16(rb + 208));
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
@@ -568,36 +572,49 @@ __device__ __forceinline__ void slice_q6k(const SliceB<FMT_Q6_K, MT, 0>& B, cons
 // Q8_0 / Q4_0 slice: per 32-block one int8 MMA per activation piece.  The accumulator starts at the bit
 // pattern of 1.5 * 2^23, so the finished integer sum S (|S| <= 32 * 128 * 127 < 2^22) reads back as the
 // float 1.5 * 2^23 + S, and S itself costs one FADD instead of a conversion.
-template <int FMT, int MT, int P, bool M1>
-__device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint8_t* ra, const uint8_t* rb, int t, uint32_t nblk,
+// ROWS4: both slices start on a 4-byte boundary (always so with tiled fills): every address is then the slice
+// address plus a compile-time constant, blocks with an odd index hold their codes word-aligned, and those of
+// even blocks sit exactly 2 bytes off, so a word is two aligned loads and one byte permute.
+template <int FMT, int MT, int P, bool M1, bool ROWS4>
+__device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint32_t ra, const uint32_t rb, int t, uint32_t nblk,
                                          float (&acc)[MT][4]) {
+    // word of a row at byte offset `off` (off = 2 mod 4 for even blocks, 0 mod 4 for odd ones when ROWS4)
+    auto word = [](uint32_t row, uint32_t off, bool aligned) -> uint32_t {
+        if (!ROWS4) return sld32_u(row + off);
+        if (aligned) return sld32(row + off);
+        return __byte_perm(sld32(row + off - 2), sld32(row + off + 2), 0x5432);
+    };
     constexpr int BB = fmt_block_bytes(FMT);
     constexpr int MAGIC_I = 0x4B400000;
     constexpr float MAGIC_F = 12582912.0f;
     const int magic[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
-    constexpr float C1 = 1.0f / PIECE_STEP, C2 = 1.0f / (PIECE_STEP * PIECE_STEP);
-    float sacc[MT][4];
+    constexpr float C1 = 1.0f / PIECE_STEP;
+    // sacc: piece 1 (offset removed per block, exact); sacc2: pieces 2.. still carrying MAGIC * d per block — their
+    // weight is 1/254 or less, so the cancellation error of removing sum(d) * MAGIC once per slice stays below 1e-6
+    float sacc[MT][4], sacc2[MT][4], dsum[2] = {0.f, 0.f};
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sacc[tl][i] = 0.f;
+        for (int i = 0; i < 4; ++i) sacc[tl][i] = sacc2[tl][i] = 0.f;
 #pragma unroll
     for (int b = 0; b < 8; ++b) {
         if ((uint32_t)b < nblk) {  // warp-uniform: ragged last slice when K % 256 != 0
             uint32_t a0, a1, a2, a3;  // row g k-slots 4t.. | row g+8 | row g k-slots 16+4t.. | row g+8
-            float dA = f16bits_to_f32(lds16(ra + BB * b)), dB = f16bits_to_f32(lds16(rb + BB * b));
+            float dA = f16bits_to_f32(sld16(ra + BB * b)), dB = f16bits_to_f32(sld16(rb + BB * b));
             if constexpr (FMT == FMT_Q8_0) {
                 // block = f16 d | 32 x i8 (2-byte aligned); the lane's codes are bytes 4t..4t+3 and 16+4t..16+4t+3, so the
                 // four lanes of a row read 16 contiguous bytes per load
-                a0 = lds32_u(ra + BB * b + 2 + 4 * t);
-                a2 = lds32_u(ra + BB * b + 18 + 4 * t);
-                a1 = lds32_u(rb + BB * b + 2 + 4 * t);
-                a3 = lds32_u(rb + BB * b + 18 + 4 * t);
+                const bool al = (b & 1) != 0;  // 34 * b + 2 is a multiple of 4 for odd b
+                a0 = word(ra, BB * b + 2 + 4 * t, al);
+                a2 = word(ra, BB * b + 18 + 4 * t, al);
+                a1 = word(rb, BB * b + 2 + 4 * t, al);
+                a3 = word(rb, BB * b + 18 + 4 * t, al);
             } else {
                 // Q4_0 block = f16 d | 16 B; byte i = elements 2i (low nibble), 2i+1 (high); the lane's word = bytes 4t..4t+3.
                 // (w ^ 0x88..) keeps each nibble as q - 8 in 4-bit two's complement; placed in the high nibble of a byte
                 // it reads as the int8 value 16 * (q - 8): the factor 16 leaves through the block scale.
-                const uint32_t wa = lds32_u(ra + BB * b + 2 + 4 * t) ^ 0x88888888u, wb = lds32_u(rb + BB * b + 2 + 4 * t) ^ 0x88888888u;
+                const bool al = (b & 1) != 0;  // 18 * b + 2 is a multiple of 4 for odd b
+                const uint32_t wa = word(ra, BB * b + 2 + 4 * t, al) ^ 0x88888888u, wb = word(rb, BB * b + 2 + 4 * t, al) ^ 0x88888888u;
                 a0 = (wa << 4) & 0xF0F0F0F0u;
                 a2 = wa & 0xF0F0F0F0u;
                 a1 = (wb << 4) & 0xF0F0F0F0u;
@@ -613,18 +630,25 @@ __device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (M1 && (i & 1)) continue;
-                    float h = __int_as_float(d[0][i]) - MAGIC_F;
-                    h = fmaf(__int_as_float(d[1][i]) - MAGIC_F, C1, h);
-                    if constexpr (P > 2) h = fmaf(__int_as_float(d[2][i]) - MAGIC_F, C2, h);
-                    sacc[tl][i] = fmaf(i < 2 ? dA : dB, h, sacc[tl][i]);
+                    const float dr = i < 2 ? dA : dB;
+                    sacc[tl][i] = fmaf(dr, __int_as_float(d[0][i]) - MAGIC_F, sacc[tl][i]);
+                    float h2 = __int_as_float(d[1][i]);
+                    if constexpr (P > 2) h2 = fmaf(__int_as_float(d[2][i]), C1, h2);  // (f2 + f3 / 254), offset MAGIC * (1 + 1/254)
+                    sacc2[tl][i] = fmaf(dr, h2, sacc2[tl][i]);
                 }
             }
+            dsum[0] += dA;
+            dsum[1] += dB;
         }
     }
+    constexpr float OFF2 = MAGIC_F * (P > 2 ? 1.0f + C1 : 1.0f);
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[tl][i] = fmaf(sacc[tl][i], B.tile[tl].scale[i & 1], acc[tl][i]);
+        for (int i = 0; i < 4; ++i) {
+            const float s2 = sacc2[tl][i] - OFF2 * dsum[i >> 1];
+            acc[tl][i] = fmaf(fmaf(s2, C1, sacc[tl][i]), B.tile[tl].scale[i & 1], acc[tl][i]);
+        }
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
@@ -900,24 +924,27 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const __grid_constant_
                     const uint32_t slice = gc * p.spc + s;
                     if (!dead && slice < p.nslices) {
                         const uint32_t coff = gc * p.spc * SLICE_B;
-                        const uint8_t *ra, *rb;
+                        uint32_t ra, rb;  // shared-window addresses of this warp's slice in rows g and g + 8
                         if (p.use_tma) {
-                            const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + tma_off;
+                            const uint32_t sb = stage0 + stage * p.stage_bytes + tma_off;
                             ra = sb + rowA * p.tma_w;
                             rb = sb + rowB * p.tma_w;
                         } else {
-                            const uint8_t* sb = smem + p.stage_off + stage * p.stage_bytes + s * SLICE_B;
+                            const uint32_t sb = stage0 + stage * p.stage_bytes + s * SLICE_B;
                             ra = sb + rowA * p.srow + ((phA + coff) & 15);
                             rb = sb + rowB * p.srow + ((phB + coff) & 15);
                         }
                         if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, M1>(B[c], ra, rb, t, acc);
                         else if constexpr (FMT == FMT_Q6_K) {
-                            const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(ra) | reinterpret_cast<uintptr_t>(rb)) & 3u;
-                            if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, M1, true>(B[c], ra, rb, t, acc);
-                            else slice_q6k<MT, M1, false>(B[c], ra, rb, t, acc);
+                            const uint32_t al = (ra | rb) & 3u;
+                            if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, M1, 1>(B[c], ra, rb, t, acc);
+                            else if (__all_sync(0xFFFFFFFFu, (ra & 3u) == 2 && (rb & 3u) == 2)) slice_q6k<MT, M1, 2>(B[c], ra, rb, t, acc);
+                            else slice_q6k<MT, M1, 0>(B[c], ra, rb, t, acc);
                         } else {
                             const uint32_t kl = p.K - slice * 256;
-                            slice_i8<FMT, MT, P, M1>(B[c], ra, rb, t, kl >= 256 ? 8u : kl / 32, acc);
+                            const uint32_t nb8 = kl >= 256 ? 8u : kl / 32;
+                            if (__all_sync(0xFFFFFFFFu, ((ra | rb) & 3u) == 0)) slice_i8<FMT, MT, P, M1, true>(B[c], ra, rb, t, nb8, acc);
+                            else slice_i8<FMT, MT, P, M1, false>(B[c], ra, rb, t, nb8, acc);
                         }
                     }
                     __syncwarp();

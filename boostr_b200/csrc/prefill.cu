@@ -589,9 +589,14 @@ cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const Pr
 
 }  // namespace
 
+// Smallest M that takes the tensor-core path; below it the memory-bound small-M kernel runs (in passes of
+// up to 32 activation rows).
+#ifndef B200Q_PREFILL_MIN_M
+#define B200Q_PREFILL_MIN_M 64
+#endif
 bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
     (void)fmt;
-    return M >= 64 && K % 64 == 0 && K % 8 == 0 && N >= 1;
+    return M >= B200Q_PREFILL_MIN_M && K % 64 == 0 && K % 8 == 0 && N >= 1;
 }
 
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
