@@ -1,4 +1,4 @@
-// Memory-bound quantized small-M kernel (2 <= M <= 32 per pass, and every M = 1 shape the decode kernels do
+// Memory-bound quantized small-M kernel (2 <= M <= 16 per pass, and every M = 1 shape the decode kernels do
 // not take) for Q4_0, Q8_0, Q4_K, Q6_K.
 //
 // Stands in for boostr's quant_gemv_*_q8_1_mwr / quant_gemv_*_f32 / fused_swiglu_*_mwr kernels
@@ -17,7 +17,7 @@
 //     run's amax), two for M 9..16 per pass (~3e-5), so the weights' int8 codes go to the tensor cores
 //     unconverted.
 //   * gemv_kernel: persistent CTAs, one per SM, 16 warps.  A warp owns one slice of a K-chunk of up to 16
-//     slices and keeps that slice's fragments for up to four 8-row tiles in registers for the whole
+//     slices and keeps that slice's fragments for one or two 8-row tiles in registers for the whole
 //     launch, so the only shared-memory traffic in the loop is the packed weights.  Slabs of 16 weight
 //     rows per warp row-group stream through a ring of stages filled by bulk copies (cp.async.bulk +
 //     mbarrier byte counts); the warps take turns requesting the refill of the stage they have just
@@ -668,7 +668,7 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 // ------------------------------------------------------------------------- the kernel
 //
 // FMT    block format
-// MT     8-row activation tiles per launch (1, 2 or 4)
+// MT     8-row activation tiles per launch (1 or 2)
 // SL     K-chunks (of up to 16 slices) one CTA walks per slab; its activation fragments for all
 //        of them stay in registers
 // SWIGLU two weights (gate, up) and out = silu(gate) * up
@@ -1031,7 +1031,6 @@ cudaError_t launch_gemv_fmt(const GemvParams& p, const GemvMaps& maps, int mt, i
                                           : launch_one<FMT, 1, 4, false, SWIGLU>(p, maps, grid, threads, smem, st);
         if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
         if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, maps, grid, threads, smem, st);
-        if (mt == 4 && sl == 1) return launch_one<FMT, 4, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
     } else {
         if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, maps, grid, threads, smem, st)
                                           : launch_one<FMT, 1, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
@@ -1061,17 +1060,18 @@ cudaError_t launch_prep_fmt(const PrepParams& pp, int mt, cudaStream_t st) {
 // (the fragments of SL chunks x MT tiles live in registers).
 int gemv_max_sl(int fmt, int mt) {
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
-    if (kq) return mt == 1 ? 4 : mt == 2 ? 2 : 1;
+    if (kq) return mt == 1 ? 4 : 2;
     return 1;
 }
 
-// 8-row tiles per pass: K-quants hold up to four (32 activation rows) when K fits one chunk, two
-// otherwise; Q4_0 / Q8_0 hold one tile of three-piece activations or two tiles of two-piece ones.
+// 8-row tiles per pass: one for M <= 8, else two (16 activation rows per pass).  Four tiles per pass were
+// measured (K-quants, K = 4096): the fragments of 32 rows leave the compiler no registers to overlap the
+// tensor-core results with their scaling, and a pass took 2.1x the time of a 16-row pass; more than 16
+// rows therefore run as consecutive 16-row passes (layer-sized weights are re-read from L2).
 int gemv_tiles_per_pass(int fmt, size_t M, size_t K) {
-    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
-    if (M <= 8) return 1;
-    if (M <= 16 || !kq) return 2;
-    return K <= 4096 ? 4 : 2;
+    (void)fmt;
+    (void)K;
+    return M <= 8 ? 1 : 2;
 }
 
 struct GemvPlan {
