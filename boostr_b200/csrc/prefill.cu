@@ -46,12 +46,15 @@ struct PrefillParams {
     uint32_t nkt;     // K / 64
     uint32_t nsa, nsb;  // ring depth of the weight (A) tiles and of the activation (B) tiles
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
-    // Work is cut into units of `ups` K steps (4 = one packed tile when packed tiles are staged, else the whole K
-    // loop); a tile has `upt` units.  CTA c walks units [c * U / P, (c + 1) * U / P) of the sequence
-    // (tile 0 unit 0, tile 0 unit 1, ...), so every SM gets the same amount of work and a tile may be shared by two
-    // neighbouring CTAs: the one that starts in the middle of a tile writes its partial accumulator to `partial`
-    // and raises `flags`, the one that began the tile adds it in before storing.
+    // Whole tiles are dealt round-robin (CTA c takes tiles c, c + P, ...: at any moment all SMs work on neighbouring
+    // tiles of one activation tile, which keeps it in L2) for the `full_waves` complete rounds.  The tiles of the last,
+    // incomplete round are cut into units of `ups` K steps (4 = one packed tile when packed tiles are staged, else the
+    // whole K loop; `upt` units per tile) and CTA c takes units [c * U / P, (c + 1) * U / P) of their sequence, so every
+    // SM gets the same share and a tile may be spread over two or three neighbouring CTAs: a CTA that starts in the
+    // middle of a tile writes its partial accumulator to `partial` and raises its flag; the CTA that began the tile
+    // adds the partial sums of its successors before storing.
     uint32_t ups, upt;
+    uint32_t full_waves;
     float* partial;        // [gridDim.x][mt][128] f32
     unsigned int* flags;   // [gridDim.x], zeroed before the launch
     int out_dtype;
@@ -62,18 +65,31 @@ struct PrefillParams {
 struct PfSeg {
     uint32_t tile, k0, k1;
 };
-// Iterates the segments of CTA `cta` of `ncta`.
+// First and one-past-last unit of CTA `cta`'s share of the last round's units.
+__device__ __forceinline__ void pf_share(const PrefillParams& p, uint32_t cta, uint32_t ncta, unsigned long long& u0, unsigned long long& u1) {
+    const unsigned long long rem_tiles = p.ntiles - (unsigned long long)p.full_waves * ncta;
+    const unsigned long long total = rem_tiles * p.upt;
+    u0 = total * cta / ncta;
+    u1 = total * (cta + 1) / ncta;
+}
+// Iterates the segments of CTA `cta` of `ncta`: its whole tiles, then its share of the last round.
 struct PfSegIter {
     unsigned long long u, u_end;
-    uint32_t ups, upt;
-    __device__ __forceinline__ PfSegIter(const PrefillParams& p, uint32_t cta, uint32_t ncta) : ups(p.ups), upt(p.upt) {
-        const unsigned long long total = (unsigned long long)p.ntiles * p.upt;
-        u = total * cta / ncta;
-        u_end = total * (cta + 1) / ncta;
+    uint32_t wave, cta, ncta, full_waves, ups, upt, nkt;
+    __device__ __forceinline__ PfSegIter(const PrefillParams& p, uint32_t cta_, uint32_t ncta_)
+        : wave(0), cta(cta_), ncta(ncta_), full_waves(p.full_waves), ups(p.ups), upt(p.upt), nkt(p.nkt) {
+        pf_share(p, cta_, ncta_, u, u_end);
     }
     __device__ __forceinline__ bool next(PfSeg& sg) {
+        if (wave < full_waves) {
+            sg.tile = wave * ncta + cta;
+            sg.k0 = 0;
+            sg.k1 = nkt;
+            ++wave;
+            return true;
+        }
         if (u >= u_end) return false;
-        sg.tile = (uint32_t)(u / upt);
+        sg.tile = full_waves * ncta + (uint32_t)(u / upt);
         const uint32_t j0 = (uint32_t)(u % upt);
         const unsigned long long left = u_end - u;
         const uint32_t j1 = left < (unsigned long long)(upt - j0) ? j0 + (uint32_t)left : upt;
@@ -430,12 +446,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 __syncwarp();
                 if (lane == 0) atomicAdd(p.flags + blockIdx.x, 1u);
             } else {
-                // K steps [0, k1): if the next CTA holds the rest of the K loop, its partial accumulator is added in.
-                // That CTA worked on it first of all, so the wait is short; it is bounded all the same.
-                const bool shared_tile = sg.k1 != p.nkt;
-                const float* src = p.partial + (size_t)(blockIdx.x + 1) * p.mt * 128;
-                if (shared_tile) {
-                    const volatile unsigned int* flag = p.flags + blockIdx.x + 1;
+                // K steps [0, k1).  If k1 stops short of the K loop, the following CTAs (one or two of them) hold the
+                // rest: each has written the partial accumulator of its first segment to its slot.  They work on it
+                // at the same time as this CTA works on its part, so the waits are short; they are bounded all the same.
+                uint32_t nsucc = 0;
+                const float* src[3] = {nullptr, nullptr, nullptr};
+                for (uint32_t kdone = sg.k1; kdone < p.nkt && ok && nsucc < 3; ++nsucc) {
+                    const uint32_t peer = blockIdx.x + 1 + nsucc;
+                    unsigned long long pu0, pu1;
+                    pf_share(p, peer, gridDim.x, pu0, pu1);
+                    const unsigned long long len = pu1 - pu0, room = (p.nkt - kdone) / p.ups;
+                    kdone += (uint32_t)(len < room ? len : room) * p.ups;
+                    const volatile unsigned int* flag = p.flags + peer;
                     uint64_t t0 = 0;
                     for (uint32_t spin = 0; *flag < 4u; ++spin) {
                         if ((spin & 63u) == 63u) {
@@ -449,8 +471,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             }
                         }
                     }
-                    __threadfence();
+                    src[nsucc] = p.partial + (size_t)peer * p.mt * 128;
                 }
+                if (nsucc) __threadfence();
                 for (uint32_t c0 = 0; c0 < p.mt && ok; c0 += 16) {
                     if (m0 + c0 >= p.M) break;  // warp-uniform
                     uint32_t v[16];
@@ -462,7 +485,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             if (m < p.M) {
                                 const size_t idx = (size_t)m * p.N + n0 + r;
                                 float f = __uint_as_float(v[i]);
-                                if (shared_tile) f += __ldcg(src + (size_t)(c0 + i) * 128 + r);
+                                for (uint32_t q = 0; q < nsucc; ++q) f += __ldcg(src[q] + (size_t)(c0 + i) * 128 + r);  // in K order
                                 if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = f;
                                 else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(f);
                                 else static_cast<__half*>(p.out)[idx] = __float2half_rn(f);
@@ -701,7 +724,7 @@ static size_t prefill_act_bytes(int fmt, int act_dtype, size_t M, size_t K) {
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
     return (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
 }
-// CTAs of a launch: one per SM, never more than tiles (so that a tile is shared by at most two CTAs)
+// CTAs of a launch: one per SM, never more than tiles
 static uint32_t prefill_grid(size_t M, size_t N, int sm_count) {
     const size_t mt = pick_mt(M), ntiles = ((N + 127) / 128) * ((M + mt - 1) / mt);
     return (uint32_t)(ntiles < (size_t)sm_count ? ntiles : (size_t)sm_count);
@@ -780,6 +803,14 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.ups = raw ? 4u : p.nkt;
     p.upt = p.nkt / p.ups;
     const uint32_t ncta = prefill_grid(M, N, sm_count);
+    p.full_waves = p.ntiles / ncta;
+    // a CTA's share of the last round must be at least a third of a tile (a tile spread over at most three CTAs);
+    // with fewer units per tile than that the last round is dealt as whole tiles too
+    const unsigned long long rem_units = (unsigned long long)(p.ntiles - p.full_waves * ncta) * p.upt;
+    if (rem_units && rem_units / ncta * 3 < p.upt) {
+        p.ups = p.nkt;
+        p.upt = 1;
+    }
     p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + act_bytes);
     p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(ws) + act_bytes + (size_t)ncta * p.mt * 128 * sizeof(float));
     {
