@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 // rest: each has written the partial accumulator of its first segment to its slot.  They work on it
                 // at the same time as this CTA works on its part, so the waits are short; they are bounded all the same.
                 uint32_t nsucc = 0;
-                const float* src[3] = {nullptr, nullptr, nullptr};
+                const float *src0 = nullptr, *src1 = nullptr, *src2 = nullptr;
                 for (uint32_t kdone = sg.k1; kdone < p.nkt && ok && nsucc < 3; ++nsucc) {
                     const uint32_t peer = blockIdx.x + 1 + nsucc;
                     unsigned long long pu0, pu1;
@@ -471,21 +471,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             }
                         }
                     }
-                    src[nsucc] = p.partial + (size_t)peer * p.mt * 128;
+                    const float* sp = p.partial + (size_t)peer * p.mt * 128;
+                    if (nsucc == 0) src0 = sp;
+                    else if (nsucc == 1) src1 = sp;
+                    else src2 = sp;
                 }
                 if (nsucc) __threadfence();
                 for (uint32_t c0 = 0; c0 < p.mt && ok; c0 += 16) {
                     if (m0 + c0 >= p.M) break;  // warp-uniform
                     uint32_t v[16];
                     tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
+                    if (nsucc) {  // rare: only the tiles of the last round that are shared with a neighbour
+                        for (uint32_t q = 0; q < nsucc; ++q) {
+                            const float* sp = q == 0 ? src0 : q == 1 ? src1 : src2;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(sp + (size_t)(c0 + i) * 128 + r));  // in K order
+                        }
+                    }
                     if (row_ok) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const uint32_t m = m0 + c0 + i;
                             if (m < p.M) {
                                 const size_t idx = (size_t)m * p.N + n0 + r;
-                                float f = __uint_as_float(v[i]);
-                                for (uint32_t q = 0; q < nsucc; ++q) f += __ldcg(src[q] + (size_t)(c0 + i) * 128 + r);  // in K order
+                                const float f = __uint_as_float(v[i]);
                                 if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = f;
                                 else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(f);
                                 else static_cast<__half*>(p.out)[idx] = __float2half_rn(f);
