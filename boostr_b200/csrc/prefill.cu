@@ -24,6 +24,9 @@
 // Measured (M = 8192, N = 14336, K = 4096): 814 TFLOP/s; with the decode arithmetic and the tile stores
 // switched off the same pipeline reaches 980 TFLOP/s, cuBLAS bf16 on the same shape 1455 TFLOP/s, so
 // the single-CTA (cta_group::1) pipeline itself, not the decode, is the larger part of the gap.
+// Output tiles are dealt round-robin, whole.  Cutting the tiles of the last, incomplete round along K (each SM an equal
+// share of K steps, partial accumulators handed to the neighbouring CTA through global memory) was built and measured:
+// it executed the same number of instructions but ran 5-8 % slower on every shape, so it was taken out again.
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code, skips the work that
 // depended on the wait and still frees its tensor memory.
 #include <cuda.h>
@@ -46,58 +49,8 @@ struct PrefillParams {
     uint32_t nkt;     // K / 64
     uint32_t nsa, nsb;  // ring depth of the weight (A) tiles and of the activation (B) tiles
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
-    // Whole tiles are dealt round-robin (CTA c takes tiles c, c + P, ...: at any moment all SMs work on neighbouring
-    // tiles of one activation tile, which keeps it in L2) for the `full_waves` complete rounds.  The tiles of the last,
-    // incomplete round are cut into units of `ups` K steps (4 = one packed tile when packed tiles are staged, else the
-    // whole K loop; `upt` units per tile) and CTA c takes units [c * U / P, (c + 1) * U / P) of their sequence, so every
-    // SM gets the same share and a tile may be spread over two or three neighbouring CTAs: a CTA that starts in the
-    // middle of a tile writes its partial accumulator to `partial` and raises its flag; the CTA that began the tile
-    // adds the partial sums of its successors before storing.
-    uint32_t ups, upt;
-    uint32_t full_waves;
-    float* partial;        // [gridDim.x][mt][128] f32
-    unsigned int* flags;   // [gridDim.x], zeroed before the launch
     int out_dtype;
     unsigned int* status;
-};
-
-// One stretch of a CTA's work: K steps [k0, k1) of `tile`.
-struct PfSeg {
-    uint32_t tile, k0, k1;
-};
-// First and one-past-last unit of CTA `cta`'s share of the last round's units.
-__device__ __forceinline__ void pf_share(const PrefillParams& p, uint32_t cta, uint32_t ncta, unsigned long long& u0, unsigned long long& u1) {
-    const unsigned long long rem_tiles = p.ntiles - (unsigned long long)p.full_waves * ncta;
-    const unsigned long long total = rem_tiles * p.upt;
-    u0 = total * cta / ncta;
-    u1 = total * (cta + 1) / ncta;
-}
-// Iterates the segments of CTA `cta` of `ncta`: its whole tiles, then its share of the last round.
-struct PfSegIter {
-    unsigned long long u, u_end;
-    uint32_t wave, cta, ncta, full_waves, ups, upt, nkt;
-    __device__ __forceinline__ PfSegIter(const PrefillParams& p, uint32_t cta_, uint32_t ncta_)
-        : wave(0), cta(cta_), ncta(ncta_), full_waves(p.full_waves), ups(p.ups), upt(p.upt), nkt(p.nkt) {
-        pf_share(p, cta_, ncta_, u, u_end);
-    }
-    __device__ __forceinline__ bool next(PfSeg& sg) {
-        if (wave < full_waves) {
-            sg.tile = wave * ncta + cta;
-            sg.k0 = 0;
-            sg.k1 = nkt;
-            ++wave;
-            return true;
-        }
-        if (u >= u_end) return false;
-        sg.tile = full_waves * ncta + (uint32_t)(u / upt);
-        const uint32_t j0 = (uint32_t)(u % upt);
-        const unsigned long long left = u_end - u;
-        const uint32_t j1 = left < (unsigned long long)(upt - j0) ? j0 + (uint32_t)left : upt;
-        sg.k0 = j0 * ups;
-        sg.k1 = j1 * ups;
-        u += j1 - j0;
-        return true;
-    }
 };
 
 namespace {
@@ -276,9 +229,9 @@ __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32
 constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OFF_EMPTY_B = 192, PF_OFF_ACC_FULL = 256,
               PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 296, PF_OFF_EMPTY_RAW = 312;
 
-// Persistent: one CTA per SM walks an equal share of the (tile, K) work (PfSegIter; consecutive tiles share an
+// Persistent: one CTA per SM walks the output tiles t = blockIdx.x, + gridDim.x, ... (consecutive CTAs share an
 // activation tile, which therefore stays in L2).  Tensor memory holds TWO accumulators, so the four epilogue warps
-// drain segment i while the MMA warp is already accumulating segment i + 1 and the rings never run dry in between.
+// drain tile i while the MMA warp is already accumulating tile i + 1 and the rings never run dry between tiles.
 template <int FMT, bool RAW_TMA>  // RAW_TMA: packed weights staged in shared memory by TMA (rows a multiple of 16 bytes)
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
@@ -299,6 +252,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;
     const uint32_t raw_tiles = sbase + 1024, a_tiles = raw_tiles + raw_bytes, b_tiles = a_tiles + p.nsa * A_TILE_BYTES;
     const uint32_t tmem_cols = 2 * p.mt;  // two accumulators of mt columns: 128, 256 or 512 (a power of two)
+    const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nsa; ++s) {
@@ -331,11 +285,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // ------------------------------------------------------------ packed weight tiles by TMA (Q4_K)
         if (RAW_TMA && !COOP && lane == 0) {
             uint32_t s = 0, par = 0;
-            PfSegIter segs(p, blockIdx.x, gridDim.x);
-            PfSeg sg;
-            while (segs.next(sg)) {
-                const uint32_t n0 = (sg.tile % p.ntn) * 128;
-                for (uint32_t j = sg.k0 >> 2; j < (sg.k1 + 3) >> 2; ++j) {
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+                const uint32_t n0 = (tile % p.ntn) * 128;
+                for (uint32_t j = 0; j < nraw; ++j) {
                     if (*dead_flag) break;
                     if (!mbar_wait(bar_empty_raw + 8 * s, par ^ 1)) {
                         *dead_flag = 1;
@@ -354,11 +306,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             uint32_t s = 0, par = 0;
-            PfSegIter segs(p, blockIdx.x, gridDim.x);
-            PfSeg sg;
-            while (segs.next(sg)) {
-                const uint32_t m0 = (sg.tile / p.ntn) * p.mt;
-                for (uint32_t kt = sg.k0; kt < sg.k1; ++kt) {
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+                const uint32_t m0 = (tile / p.ntn) * p.mt;
+                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
                     if (*dead_flag) break;
                     if (!mbar_wait(bar_empty_b + 8 * s, par ^ 1)) {
                         *dead_flag = 1;
@@ -377,11 +327,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         if (lane == 0) {
             uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
             bool ok = true;
-            PfSegIter segs(p, blockIdx.x, gridDim.x);
-            PfSeg sg;
-            for (; ok && segs.next(sg); ++it) {
+            for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
                 const uint32_t acc = it & 1, u = it >> 1;
-                // the accumulator must have been drained by the epilogue of two segments ago
+                // the accumulator must have been drained by the epilogue of two tiles ago
                 if (u > 0 && (*dead_flag || !mbar_wait(bar_acc_empty + 8 * acc, (u - 1) & 1))) {
                     if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                     *dead_flag = 1;
@@ -390,7 +338,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
-                for (uint32_t kt = sg.k0; kt < sg.k1; ++kt) {
+                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
                     if (*dead_flag || !mbar_wait(bar_full_a + 8 * sa, para) || !mbar_wait(bar_full_b + 8 * sb, parb)) {
                         if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
                         *dead_flag = 1;
@@ -401,14 +349,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     const uint32_t a_addr = a_tiles + sa * A_TILE_BYTES, b_addr = b_tiles + sb * b_tile_bytes;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_bf16(d_tmem, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, kt != sg.k0 || k != 0);
+                        tc_mma_bf16(d_tmem, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
                     // both tiles may be overwritten once these MMAs have read them
                     tc_commit(bar_empty_a + 8 * sa);
                     tc_commit(bar_empty_b + 8 * sb);
                     if (++sa == p.nsa) { sa = 0; para ^= 1; }
                     if (++sb == p.nsb) { sb = 0; parb ^= 1; }
                 }
-                if (ok) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the segment has completed
+                if (ok) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
             }
         }
     } else if (warp >= 19) {
@@ -418,11 +366,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         const uint32_t quarter = (uint32_t)warp & 3, r = quarter * 32 + lane;
         uint32_t it = 0;
         bool ok = true;
-        PfSegIter segs(p, blockIdx.x, gridDim.x);
-        PfSeg sg;
-        for (; ok && segs.next(sg); ++it) {
+        for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, u = it >> 1;
-            const uint32_t n0 = (sg.tile % p.ntn) * 128, m0 = (sg.tile / p.ntn) * p.mt;
+            const uint32_t n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt;
             if (*dead_flag || !mbar_wait(bar_acc_full + 8 * acc, u & 1)) {
                 if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_MMA);
                 *dead_flag = 1;
@@ -431,74 +377,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             }
             tc_fence_after();
             const bool row_ok = n0 + r < p.N;
-            if (sg.k0 != 0) {
-                // The K loop of this tile was begun by the previous CTA: hand the partial accumulator over
-                // ([column][row]: a warp writes 128 contiguous bytes per column) and raise the flag, one count per warp.
-                float* dst = p.partial + (size_t)blockIdx.x * p.mt * 128;
-                for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
-                    if (m0 + c0 >= p.M) break;  // warp-uniform
-                    uint32_t v[16];
-                    tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
+            for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
+                if (m0 + c0 >= p.M) break;  // warp-uniform
+                uint32_t v[16];
+                tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
+                if (row_ok) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) dst[(size_t)(c0 + i) * 128 + r] = __uint_as_float(v[i]);
-                }
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) atomicAdd(p.flags + blockIdx.x, 1u);
-            } else {
-                // K steps [0, k1).  If k1 stops short of the K loop, the following CTAs (one or two of them) hold the
-                // rest: each has written the partial accumulator of its first segment to its slot.  They work on it
-                // at the same time as this CTA works on its part, so the waits are short; they are bounded all the same.
-                uint32_t nsucc = 0;
-                const float *src0 = nullptr, *src1 = nullptr, *src2 = nullptr;
-                for (uint32_t kdone = sg.k1; kdone < p.nkt && ok && nsucc < 3; ++nsucc) {
-                    const uint32_t peer = blockIdx.x + 1 + nsucc;
-                    unsigned long long pu0, pu1;
-                    pf_share(p, peer, gridDim.x, pu0, pu1);
-                    const unsigned long long len = pu1 - pu0, room = (p.nkt - kdone) / p.ups;
-                    kdone += (uint32_t)(len < room ? len : room) * p.ups;
-                    const volatile unsigned int* flag = p.flags + peer;
-                    uint64_t t0 = 0;
-                    for (uint32_t spin = 0; *flag < 4u; ++spin) {
-                        if ((spin & 63u) == 63u) {
-                            const uint64_t now = global_timer_ns();
-                            if (t0 == 0) t0 = now;
-                            else if (now - t0 > 2000000000ull) {
-                                atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                                *dead_flag = 1;
-                                ok = false;
-                                break;
-                            }
-                        }
-                    }
-                    const float* sp = p.partial + (size_t)peer * p.mt * 128;
-                    if (nsucc == 0) src0 = sp;
-                    else if (nsucc == 1) src1 = sp;
-                    else src2 = sp;
-                }
-                if (nsucc) __threadfence();
-                for (uint32_t c0 = 0; c0 < p.mt && ok; c0 += 16) {
-                    if (m0 + c0 >= p.M) break;  // warp-uniform
-                    uint32_t v[16];
-                    tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
-                    if (nsucc) {  // rare: only the tiles of the last round that are shared with a neighbour
-                        for (uint32_t q = 0; q < nsucc; ++q) {
-                            const float* sp = q == 0 ? src0 : q == 1 ? src1 : src2;
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(sp + (size_t)(c0 + i) * 128 + r));  // in K order
-                        }
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const uint32_t m = m0 + c0 + i;
-                            if (m < p.M) {
-                                const size_t idx = (size_t)m * p.N + n0 + r;
-                                const float f = __uint_as_float(v[i]);
-                                if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = f;
-                                else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(f);
-                                else static_cast<__half*>(p.out)[idx] = __float2half_rn(f);
-                            }
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t m = m0 + c0 + i;
+                        if (m < p.M) {
+                            const size_t idx = (size_t)m * p.N + n0 + r;
+                            const float f = __uint_as_float(v[i]);
+                            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = f;
+                            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(f);
+                            else static_cast<__half*>(p.out)[idx] = __float2half_rn(f);
                         }
                     }
                 }
@@ -513,23 +405,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // kt = set, set + 2, ... of every tile
         const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
         bool ok = true;
-        // COOP: the packed tiles of this CTA's segments, counted 0, 1, 2, ... in the order they are used, are copied by
-        // all 16 dequant warps, 8 rows each, one tile ahead of its use; buffer c & 1 must have been released by every
-        // reader of tile c - 2.  `cp` walks the same segment sequence one packed tile ahead.
+        uint32_t it = 0;
+        // COOP: packed tile c (counted over all output tiles of this CTA) is copied by all 16 dequant warps, 8 rows
+        // each, one tile ahead of its use; buffer c & 1 must have been released by every reader of tile c - 2
         uint32_t next_copy = 0;
-        PfSegIter cp_segs(p, blockIdx.x, gridDim.x);
-        PfSeg cp_sg{0, 0, 0};
-        uint32_t cp_j = 0;  // next packed tile (K steps 4 cp_j ..) of cp_sg to copy; cp_sg is exhausted when 4 cp_j >= k1
-        bool cp_more = cp_segs.next(cp_sg);
-        if (cp_more) cp_j = cp_sg.k0 >> 2;
         auto copy_upto = [&](uint32_t upto) {
             for (; next_copy <= upto; ++next_copy) {
-                while (cp_more && 4 * cp_j >= cp_sg.k1) {
-                    cp_more = cp_segs.next(cp_sg);
-                    cp_j = cp_sg.k0 >> 2;
-                }
-                if (!cp_more) return;  // nothing left to copy
-                const uint32_t c = next_copy, jc = cp_j++;
+                const uint32_t c = next_copy, tc = blockIdx.x + (c / nraw) * gridDim.x, jc = c % nraw;
+                if (tc >= p.ntiles) continue;
                 const uint32_t cs = c & 1;
                 if (ok && (*dead_flag || !mbar_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1))) {
                     if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
@@ -537,7 +420,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     ok = false;
                 }
                 if (ok) {
-                    const uint32_t cn0 = (cp_sg.tile % p.ntn) * 128;
+                    const uint32_t cn0 = (tc % p.ntn) * 128;
                     uint8_t* dst = smem + 1024 + cs * RAW_TILE_BYTES;
                     unsigned short v[8][4];
 #pragma unroll
@@ -564,18 +447,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 if (lane == 0) mbar_arrive(bar_full_raw + 8 * cs);
             }
         };
-        PfSegIter segs(p, blockIdx.x, gridDim.x);
-        PfSeg sg;
-        uint32_t kbase = 0;  // K steps of the earlier segments: position of this segment in the stream the MMA warp consumes
-        uint32_t rbase = 0;  // packed tiles of the earlier segments
-        while (segs.next(sg)) {
-            const uint32_t n0 = (sg.tile % p.ntn) * 128;
+        for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
+            const uint32_t n0 = (tile % p.ntn) * 128;
             const bool row_ok = n0 + r < p.N;
             const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
-            for (uint32_t kt = sg.k0 + set; kt < sg.k1; kt += 2) {
+            for (uint32_t kt = set; kt < p.nkt; kt += 2) {
                 uint32_t o[16];
                 if constexpr (RAW_TMA) {
-                    const uint32_t jr = rbase + ((kt - sg.k0) >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
+                    const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
                     if constexpr (COOP) copy_upto(jr + 1);
                     if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1))) {
                         if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
@@ -583,26 +462,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         ok = false;
                     }
                     const uint8_t* rrow = smem + 1024 + rs * RAW_TILE_BYTES + r * RAW_PITCH;
-                    // this set's last step in the packed tile: release it
-                    const bool last_in_raw = kt + 2 >= sg.k1 || ((kt + 2) >> 2) != (kt >> 2);
                     if constexpr (FMT == FMT_Q4_K) {
                         RawQ4K cur{};
                         if (ok) cur = load_raw_q4k_smem(rrow, kt);
-                        if (last_in_raw) {
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {  // this set's last step in the tile: release it
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                         }
                         decode32_q4k(cur, kt, half, o);
                     } else if constexpr (FMT == FMT_Q6_K) {
                         if (ok) decode32_q6k<true>(rrow, kt, half, o);
-                        if (last_in_raw) {
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                         }
                     } else {
                         constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
                         if (ok) decode32_blk<FMT, true>(rrow + (2 * (kt & 3) + half) * BB, o);
-                        if (last_in_raw) {
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                         }
@@ -613,7 +490,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 if (!row_ok)
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = 0;
-                const uint32_t gk = kbase + (kt - sg.k0);  // position in the stream of K steps the MMA warp consumes
+                const uint32_t gk = it * p.nkt + kt;  // position in the stream of K steps the MMA warp consumes
                 const uint32_t s = gk % p.nsa, par = (gk / p.nsa) & 1;
                 if (ok && (*dead_flag || !mbar_wait(bar_empty_a + 8 * s, par ^ 1))) {
                     if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
@@ -632,8 +509,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
             }
-            kbase += sg.k1 - sg.k0;
-            rbase += (sg.k1 - sg.k0 + 3) >> 2;
         }
     }
     tc_fence_before();
@@ -703,6 +578,7 @@ __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restric
     }
 }
 
+uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
 
 template <int FMT, bool RAW>
 cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
@@ -726,26 +602,10 @@ bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
     return M >= B200Q_PREFILL_MIN_M && K % 64 == 0 && K % 8 == 0 && N >= 1;
 }
 
-static uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
-
-// bytes of the prepared bf16 activations (0 when the caller's bf16 activations are used as they are)
-static size_t prefill_act_bytes(int fmt, int act_dtype, size_t M, size_t K) {
+size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
+    (void)N;
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
     return (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
-}
-// CTAs of a launch: one per SM, never more than tiles
-static uint32_t prefill_grid(size_t M, size_t N, int sm_count) {
-    const size_t mt = pick_mt(M), ntiles = ((N + 127) / 128) * ((M + mt - 1) / mt);
-    return (uint32_t)(ntiles < (size_t)sm_count ? ntiles : (size_t)sm_count);
-}
-// partial accumulators exchanged between neighbouring CTAs (one [mt][128] f32 slot per CTA) + their flags
-static size_t prefill_exchange_bytes(size_t M, size_t N, int sm_count) {
-    const size_t g = prefill_grid(M, N, sm_count);
-    return g * pick_mt(M) * 128 * sizeof(float) + ((g * sizeof(unsigned int) + 255) & ~(size_t)255);
-}
-
-size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N, int sm_count) {
-    return prefill_act_bytes(fmt, act_dtype, M, K) + prefill_exchange_bytes(M, N, sm_count);
 }
 
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -754,12 +614,9 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     *ws_too_small = false;
     const void* act_bf16 = act;
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
-    const size_t act_bytes = prefill_act_bytes(fmt, act_dtype, M, K);
-    if (!ws || ws_bytes < prefill_workspace_bytes(fmt, act_dtype, M, K, N, sm_count) || (reinterpret_cast<uintptr_t>(ws) & 15)) {
-        *ws_too_small = true;
-        return cudaSuccess;
-    }
     if (act_dtype != DT_BF16 || kq) {
+        const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N);
+        if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
         const size_t n = M * K;
         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(ws);
         if (kq) {
@@ -808,24 +665,6 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.nsb = nsb;
     p.ntn = (uint32_t)((N + 127) / 128);
     p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
-    // work units: one packed tile (4 K steps) when packed tiles are staged, else a whole tile
-    p.ups = raw ? 4u : p.nkt;
-    p.upt = p.nkt / p.ups;
-    const uint32_t ncta = prefill_grid(M, N, sm_count);
-    p.full_waves = p.ntiles / ncta;
-    // a CTA's share of the last round must be at least a third of a tile (a tile spread over at most three CTAs);
-    // with fewer units per tile than that the last round is dealt as whole tiles too
-    const unsigned long long rem_units = (unsigned long long)(p.ntiles - p.full_waves * ncta) * p.upt;
-    if (rem_units && rem_units / ncta * 3 < p.upt) {
-        p.ups = p.nkt;
-        p.upt = 1;
-    }
-    p.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + act_bytes);
-    p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(ws) + act_bytes + (size_t)ncta * p.mt * 128 * sizeof(float));
-    {
-        cudaError_t me = cudaMemsetAsync(p.flags, 0, ncta * sizeof(unsigned int), st);
-        if (me != cudaSuccess) return me;
-    }
     p.out_dtype = out_dtype;
     p.status = status;
     const size_t smem = 2048 + raw_bytes + (size_t)nsa * A_TILE_BYTES + (size_t)nsb * b_tile;
@@ -858,7 +697,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
             return cudaErrorInvalidValue;
         }
     }
-    dim3 grid(ncta, 1, 1);
+    dim3 grid(p.ntiles < (uint32_t)sm_count ? p.ntiles : (uint32_t)sm_count, 1, 1);
     switch (fmt) {
     case FMT_Q4_0: return raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st);
     case FMT_Q8_0: return raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st);

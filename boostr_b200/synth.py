@@ -65,6 +65,18 @@ def q4_k_blocks(rng, nblocks: int, scale: float = 0.002) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q5_k_blocks(rng, nblocks: int, scale: float = 0.002) -> np.ndarray:
+    """Q5_K: as Q4_K plus 32 bytes of high bits (uniform), so the 5-bit codes are uniform 0..31."""
+    out = np.empty((nblocks, 176), dtype=np.uint8)
+    out[:, 0:2] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 2:4] = _fp16_scale_bytes(rng, nblocks, scale)
+    sc = rng.integers(0, 64, size=(nblocks, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, size=(nblocks, 8), dtype=np.uint8)
+    out[:, 4:16] = pack_q4k_scales(sc, mn)
+    out[:, 16:176] = rng.integers(0, 256, size=(nblocks, 160), dtype=np.uint8)
+    return out.reshape(-1)
+
+
 def q6_k_blocks(rng, nblocks: int, scale: float = 0.0005) -> np.ndarray:
     out = np.empty((nblocks, 210), dtype=np.uint8)
     out[:, 0:192] = rng.integers(0, 256, size=(nblocks, 192), dtype=np.uint8)
@@ -77,6 +89,7 @@ _GEN = {
     QuantFormat.Q4_0: q4_0_blocks,
     QuantFormat.Q8_0: q8_0_blocks,
     QuantFormat.Q4_K: q4_k_blocks,
+    QuantFormat.Q5_K: q5_k_blocks,
     QuantFormat.Q6_K: q6_k_blocks,
 }
 
@@ -100,7 +113,7 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
     f = QuantFormat.parse(fmt)
     nb = n * (k // f.block_size)
     w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device=device, generator=gen)
-    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q6_K": 0.0005}[f.name]
+    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
 
     def scale():
         return (torch.randn(nb, device=device, generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
@@ -113,6 +126,6 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
         w[:, 0:2] = scale()
     else:
         w[:, 0:2] = scale()
-        if f is QuantFormat.Q4_K:
+        if f in (QuantFormat.Q4_K, QuantFormat.Q5_K):
             w[:, 2:4] = scale()
     return QuantTensor(w.reshape(-1), f, (n, k))

@@ -45,13 +45,13 @@
 #define ORACLE_API __attribute__((visibility("default")))
 
 /* Format ids follow QuantFormat::format_id (src/quant/format.rs:204-230). */
-enum { FMT_Q4_0 = 0, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q6_K = 10 };
+enum { FMT_Q4_0 = 0, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
 
 /* block_size / block_bytes: src/quant/format.rs:81-140 */
 ORACLE_API int oracle_block_size(int fmt) {
     switch (fmt) {
     case FMT_Q4_0: case FMT_Q8_0: return 32;
-    case FMT_Q4_K: case FMT_Q6_K: return 256;
+    case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -60,6 +60,7 @@ ORACLE_API int oracle_block_bytes(int fmt) {
     case FMT_Q4_0: return 18;
     case FMT_Q8_0: return 34;
     case FMT_Q4_K: return 144;
+    case FMT_Q5_K: return 176;
     case FMT_Q6_K: return 210;
     default: return 0;
     }
@@ -158,6 +159,35 @@ static void dequant_q4k(const uint8_t *blocks, size_t nblocks, float *out) {
     }
 }
 
+/* dequant_q5k: src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:56-106.
+ * Block = f16 d | f16 dmin | 12 B scales (as Q4_K) | 32 B qh | 128 B qs.  NOTE the element order: element l of
+ * sub-block j takes nibble (l % 2) of qs[16 j + l / 2] (interleaved, 16 bytes per sub-block) and bit (idx % 8) of
+ * qh[idx / 8] with idx = 32 j + l.  This is neither ggml's Q5_K order nor the order the reference's own Q8_K dot
+ * product uses on x86 (dot_q5k_q8k_avx2order below); the restatement follows each function as it is written. */
+static void dequant_q5k(const uint8_t *blocks, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 176;
+        float d = f16_to_f32(rd16(blk));
+        float dmin = f16_to_f32(rd16(blk + 2));
+        const uint8_t *qh = blk + 16, *qs = blk + 48;
+        uint8_t scales[8], mins[8];
+        unpack_q4k_scales(blk + 4, scales, mins);
+        float *o = out + b * 256;
+        for (int j = 0; j < 8; j++) {
+            float dl = d * (float)scales[j];
+            float ml = dmin * (float)mins[j];
+            for (int l = 0; l < 32; l++) {
+                int idx = j * 32 + l;
+                int byte = qs[j * 16 + l / 2];
+                int low4 = (l % 2 == 0) ? (byte & 0x0F) : ((byte >> 4) & 0x0F);
+                int high1 = (qh[idx / 8] >> (idx % 8)) & 1;
+                float q = (float)(low4 | (high1 << 4));
+                o[idx] = dl * q - ml;
+            }
+        }
+    }
+}
+
 /* dequant_q6k: src/quant/cpu/kernels/dequant_k_quants/q6k_q8k.rs:10-56 */
 static void dequant_q6k(const uint8_t *blocks, size_t nblocks, float *out) {
     for (size_t b = 0; b < nblocks; b++) {
@@ -193,6 +223,7 @@ ORACLE_API int oracle_dequant_f32(int fmt, const uint8_t *blocks, size_t nblocks
     case FMT_Q4_0: dequant_q4_0(blocks, nblocks, out); return 0;
     case FMT_Q8_0: dequant_q8_0(blocks, nblocks, out); return 0;
     case FMT_Q4_K: dequant_q4k(blocks, nblocks, out); return 0;
+    case FMT_Q5_K: dequant_q5k(blocks, nblocks, out); return 0;
     case FMT_Q6_K: dequant_q6k(blocks, nblocks, out); return 0;
     default: return -1;
     }
@@ -456,7 +487,60 @@ static float dot_q6k_q8k_avx2(const uint8_t *act_q8k, const uint8_t *w, size_t k
 }
 #endif
 
+/* fused_dot_q5k_q8k.  The reference dispatches to its AVX2 form on x86-64 (src/quant/cpu/kernels/simd/fused_q5k_q8k_dot.rs:
+ * 27-122, dispatch :139-148); that form is what the CPU matmul computes there and what this function restates
+ * (`scalar_order` = 0).  Per chunk j of 64 elements it takes the LOW nibbles of qs[32 j .. 32 j + 32) as elements
+ * 64 j .. 64 j + 32 and the HIGH nibbles as elements 64 j + 32 .. 64 j + 64 (the Q4_K order), with high bit
+ * (qh[e / 8] >> (e % 8)) & 1 for element e, scales[2 j] / scales[2 j + 1], and the min term from the Q8_K block sums.
+ * Its scalar fallback (:151-212, `scalar_order` = 1) uses the interleaved order of dequant_q5k instead, so the two
+ * forms of the reference disagree with each other on the same bytes; integer arithmetic is exact in both. */
+static float dot_q5k_q8k(const uint8_t *act_q8k, const uint8_t *w, size_t k, int scalar_order) {
+    size_t nb = k / 256;
+    float sumf = 0.0f;
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *q5 = w + b * 176;
+        float d = f16_to_f32(rd16(q5));
+        float dmin = f16_to_f32(rd16(q5 + 2));
+        const uint8_t *qh = q5 + 16, *qs = q5 + 48;
+        uint8_t scales[8], mins[8];
+        unpack_q4k_scales(q5 + 4, scales, mins);
+        const uint8_t *a = act_q8k + b * Q8K_BLOCK_BYTES;
+        float d8;
+        memcpy(&d8, a, 4);
+        const int8_t *q8 = (const int8_t *)(a + 4);
+        const uint8_t *bs = a + 260;
+        float dall = d * d8;
+        float dmin_all = dmin * d8;
+        int32_t sumi = 0, sumi_mins = 0;
+        for (int j = 0; j < 8; j++) {
+            int32_t dot = 0;
+            for (int l = 0; l < 32; l++) {
+                int idx = j * 32 + l;
+                int low4;
+                if (scalar_order) {
+                    int byte = qs[j * 16 + l / 2];
+                    low4 = (l % 2 == 0) ? (byte & 0x0F) : ((byte >> 4) & 0x0F);
+                } else {
+                    int byte = qs[(j / 2) * 32 + l];
+                    low4 = (j & 1) ? ((byte >> 4) & 0x0F) : (byte & 0x0F);
+                }
+                int high1 = (qh[idx / 8] >> (idx % 8)) & 1;
+                dot += (low4 | (high1 << 4)) * (int32_t)q8[idx];
+            }
+            sumi += dot * (int32_t)scales[j];
+            int32_t bsum = (int32_t)(int16_t)rd16(bs + j * 4) + (int32_t)(int16_t)rd16(bs + j * 4 + 2);
+            sumi_mins += (int32_t)mins[j] * bsum;
+        }
+        float t = dall * (float)sumi - dmin_all * (float)sumi_mins;
+        sumf += t;
+    }
+    return sumf;
+}
+
+/* simd: 1 = the forms the reference runs on x86-64 (AVX2), 0 = its scalar fallbacks.  For Q4_K and Q6_K the two give
+ * identical bits; for Q5_K they are different functions of the weight bytes (see dot_q5k_q8k). */
 ORACLE_API float oracle_dot_q8k(int fmt, const uint8_t *act_q8k, const uint8_t *w, size_t k, int simd) {
+    if (fmt == FMT_Q5_K) return dot_q5k_q8k(act_q8k, w, k, simd ? 0 : 1);
 #if defined(__AVX2__)
     if (simd) return fmt == FMT_Q4_K ? dot_q4k_q8k_avx2(act_q8k, w, k) : dot_q6k_q8k_avx2(act_q8k, w, k);
 #endif
@@ -617,7 +701,7 @@ ORACLE_API int oracle_quant_matmul(int fmt, const float *act, const uint8_t *w, 
     if (k % (size_t)bs) return -2;
     if (threads <= 0) threads = 1;
     size_t row_bytes = (k / (size_t)bs) * (size_t)oracle_block_bytes(fmt);
-    int kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    int kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     size_t q8k_row = (k / 256) * Q8K_BLOCK_BYTES;
     uint8_t *aq = NULL;
     if (kq) {

@@ -279,3 +279,97 @@ def test_swiglu(oracle):
     want = g / (1 + np.exp(-g)) * u
     got = oracle.quant_swiglu("Q4_K", act, wg, wu, n)
     assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max() + 1e-9
+
+
+# ------------------------------------------------------------------ Q5_K (next-format row)
+
+
+def _q5k_block(d, dmin, sc_bytes, qh_fill, qs_fill):
+    blk = np.zeros(176, np.uint8)
+    blk[0:2] = np.array([d], np.float16).view(np.uint8)
+    blk[2:4] = np.array([dmin], np.float16).view(np.uint8)
+    blk[4:16] = sc_bytes
+    blk[16:48] = qh_fill
+    blk[48:176] = qs_fill
+    return blk
+
+
+def test_q5k_reference_known_answers(oracle):
+    # src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs: test_dequant_q5k_zero, test_dequant_q5k_known_values
+    assert np.all(oracle.dequantize_f32("Q5_K", np.zeros(176, np.uint8)) == 0)
+    sc = np.zeros(12, np.uint8)
+    sc[0:4] = 1
+    out = oracle.dequantize_f32("Q5_K", _q5k_block(1.0, 0.0, sc, 0, 0x55))
+    assert np.all(out[:128] == 5.0) and np.all(out[128:] == 0.0)
+    # high bits set for every element: 5-bit code 16 + 5 = 21
+    out = oracle.dequantize_f32("Q5_K", _q5k_block(1.0, 0.0, sc, 0xFF, 0x55))
+    assert np.all(out[:128] == 21.0)
+
+
+def test_q5k_dequant_layout_by_hand(oracle):
+    # element 32 j + l takes nibble (l % 2) of qs[16 j + l / 2] and bit (idx % 8) of qh[idx / 8] (q4k_q5k.rs:76-100)
+    rng = np.random.default_rng(5)
+    from boostr_b200 import synth
+
+    blk = synth.q5_k_blocks(rng, 3)
+    got = oracle.dequantize_f32("Q5_K", blk).reshape(3, 256)
+    for b in range(3):
+        raw = blk.reshape(3, 176)[b]
+        d = np.float32(raw[0:2].view(np.float16)[0])
+        dmin = np.float32(raw[2:4].view(np.float16)[0])
+        s = raw[4:16]
+        scales = [int(s[i] & 63) if i < 4 else int((s[i + 4] & 15) | ((s[i - 4] >> 6) << 4)) for i in range(8)]
+        mins = [int(s[i + 4] & 63) if i < 4 else int((s[i + 4] >> 4) | ((s[i] >> 6) << 4)) for i in range(8)]
+        qh, qs = raw[16:48], raw[48:176]
+        for j in range(8):
+            for l in range(32):
+                idx = 32 * j + l
+                byte = int(qs[16 * j + l // 2])
+                low = (byte & 15) if l % 2 == 0 else (byte >> 4)
+                q = low | (((int(qh[idx // 8]) >> (idx % 8)) & 1) << 4)
+                want = np.float32(np.float32(d * np.float32(scales[j])) * np.float32(q)) - np.float32(dmin * np.float32(mins[j]))
+                assert got[b, idx] == np.float32(want), (b, j, l)
+
+
+def test_q5k_q8k_dot_orders(oracle):
+    """The reference's AVX2 Q5_K x Q8_K dot (what x86-64 runs) reads the nibbles in the Q4_K order, its scalar
+    fallback in the interleaved order of its dequant: on bytes where the two orders differ they give different
+    results, and only the scalar form agrees with `activation . dequantize(weight)` to Q8_K rounding.  Both are
+    restated; the matmul oracle follows the AVX2 form."""
+    from boostr_b200 import synth
+
+    rng = np.random.default_rng(6)
+    k = 1024
+    w = synth.q5_k_blocks(rng, k // 256)
+    act = rng.standard_normal(k).astype(np.float32)
+    q8 = oracle.quantize_q8k(act)
+    simd = oracle.dot_q8k("Q5_K", q8, w, k, simd=True)
+    scal = oracle.dot_q8k("Q5_K", q8, w, k, simd=False)
+    ref = float(act.astype(np.float64) @ oracle.dequantize_f32("Q5_K", w).astype(np.float64))
+    assert abs(scal - ref) < 0.02 * abs(ref) + 1.0         # the reference's own tolerance (fused_q5k_q8k_dot.rs:288-292)
+    assert abs(simd - scal) > 1e-3                          # the two forms really are different functions
+    sc = np.zeros(12, np.uint8)
+    sc[0:4], sc[4:8], sc[8:12] = 0x03, 0x02, 0x10
+    a = ((np.arange(256) - 128) * 0.01).astype(np.float32)
+    q8 = oracle.quantize_q8k(a)
+    # when both nibbles of every byte are equal the two orders coincide
+    same = _q5k_block(1.0, 0.5, sc, 0xAA, 0x55)
+    assert oracle.dot_q8k("Q5_K", q8, same, 256, simd=True) == oracle.dot_q8k("Q5_K", q8, same, 256, simd=False)
+    # the reference's own test block (fused_q5k_q8k_dot.rs:221-247) and its tolerance, for the form x86-64 runs
+    blk = _q5k_block(1.0, 0.5, sc, 0xAA, 0x73)
+    want = float(a.astype(np.float64) @ oracle.dequantize_f32("Q5_K", blk).astype(np.float64))
+    assert abs(oracle.dot_q8k("Q5_K", q8, blk, 256, simd=True) - want) < abs(want) * 0.05 + 2.0
+
+
+def test_q5k_matmul_driver_follows_the_avx2_form(oracle):
+    from boostr_b200 import synth
+
+    rng = np.random.default_rng(7)
+    m, n, k = 3, 20, 512
+    w = synth.weight_bytes("Q5_K", rng, n, k)
+    act = rng.standard_normal((m, k)).astype(np.float32)
+    out = oracle.quant_matmul("Q5_K", act, w, n, threads=2, simd=True)
+    for i in range(m):
+        q8 = oracle.quantize_q8k(act[i])
+        for j in range(n):
+            assert out[i, j] == np.float32(oracle.dot_q8k("Q5_K", q8, w.reshape(n, -1)[j].copy(), k, simd=True))
