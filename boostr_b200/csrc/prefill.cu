@@ -56,7 +56,6 @@ struct PrefillParams {
 namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
-constexpr int A_TILE_BYTES = 128 * BK * 2;
 constexpr int PF_MAX_STAGES = 8;
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
 __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : 144; }
@@ -84,6 +83,24 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// The same with the A operand (128 rows x 16 bf16, row i in lane i, two elements per 32-bit column) in tensor memory.
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's lane (the warp covers the 32 lanes of its quarter)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -250,13 +267,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     volatile uint32_t* dead_flag = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_DEAD);
     const uint32_t b_tile_bytes = p.mt * 128;
     const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;
-    const uint32_t raw_tiles = sbase + 1024, a_tiles = raw_tiles + raw_bytes, b_tiles = a_tiles + p.nsa * A_TILE_BYTES;
-    const uint32_t tmem_cols = 2 * p.mt;  // two accumulators of mt columns: 128, 256 or 512 (a power of two)
+    const uint32_t raw_tiles = sbase + 1024, b_tiles = raw_tiles + raw_bytes;
+    // Tensor memory (all 512 columns): nacc accumulators of mt columns (two while they fit beside the weight stages,
+    // one at mt = 256), then nsa decoded weight tiles of 32 columns (128 rows x 64 bf16, two per column).
+    const uint32_t tmem_cols = 512, nacc = p.mt <= 128 ? 2u : 1u, a_col0 = nacc * p.mt;
     const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.nsa; ++s) {
-            mbar_init(bar_full_a + 8 * s, 8);  // one arrival per warp of the set that wrote the tile
+            mbar_init(bar_full_a + 8 * s, 8);  // one arrival per warp of the set that wrote the tile (to tensor memory)
             mbar_init(bar_empty_a + 8 * s, 1);
         }
         for (uint32_t s = 0; s < p.nsb; ++s) {
@@ -328,8 +347,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
-                const uint32_t acc = it & 1, u = it >> 1;
-                // the accumulator must have been drained by the epilogue of two tiles ago
+                const uint32_t acc = it % nacc, u = it / nacc;
+                // the accumulator must have been drained by the epilogue of its previous use
                 if (u > 0 && (*dead_flag || !mbar_wait(bar_acc_empty + 8 * acc, (u - 1) & 1))) {
                     if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
                     *dead_flag = 1;
@@ -346,10 +365,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = a_tiles + sa * A_TILE_BYTES, b_addr = b_tiles + sb * b_tile_bytes;
+                    const uint32_t a_tm = tmem_acc + a_col0 + 32 * sa, b_addr = b_tiles + sb * b_tile_bytes;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_bf16(d_tmem, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
+                        tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
                     // both tiles may be overwritten once these MMAs have read them
                     tc_commit(bar_empty_a + 8 * sa);
                     tc_commit(bar_empty_b + 8 * sb);
@@ -367,7 +386,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
-            const uint32_t acc = it & 1, u = it >> 1;
+            const uint32_t acc = it % nacc, u = it / nacc;
             const uint32_t n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt;
             if (*dead_flag || !mbar_wait(bar_acc_full + 8 * acc, u & 1)) {
                 if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_MMA);
@@ -497,15 +516,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     *dead_flag = 1;
                     ok = false;
                 }
-                if (ok) {
-                    uint8_t* arow = smem + 1024 + raw_bytes + s * A_TILE_BYTES + r * 128;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {  // 16-byte chunk cc of row r lives at chunk cc ^ (r & 7)
-                        const uint32_t cc = 4 * half + c;
-                        *reinterpret_cast<uint4*>(arow + ((cc ^ (r & 7)) << 4)) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-                    }
-                    fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
-                }
+                // the thread's 32 bf16 go to its own lane (= weight row) of the stage's tensor-memory tile: columns
+                // [16 half, 16 half + 16).  Executed by the whole warp (dead warps store what they hold: nobody reads it).
+                tmem_st16(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * s + 16 * half, o);
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
             }
@@ -656,8 +670,8 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     const uint32_t raw_bytes = raw ? 2u * (uint32_t)raw_tile_bytes(fmt) : 0u;
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
-    uint32_t nsa = 4;
-    uint32_t nsb = (budget - nsa * A_TILE_BYTES) / b_tile;
+    uint32_t nsa = 8;  // decoded weight tiles live in tensor memory: 8 x 32 columns
+    uint32_t nsb = budget / b_tile;
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
     if (nsa > p.nkt) nsa = p.nkt;
     if (nsb > p.nkt) nsb = p.nkt;
@@ -667,7 +681,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
     p.out_dtype = out_dtype;
     p.status = status;
-    const size_t smem = 2048 + raw_bytes + (size_t)nsa * A_TILE_BYTES + (size_t)nsb * b_tile;
+    const size_t smem = 2048 + raw_bytes + (size_t)nsb * b_tile;
 
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
