@@ -1,4 +1,4 @@
-// Dequantise packed GGUF blocks (Q4_0, Q8_0, Q4_K, Q6_K) straight to f32 / bf16 / f16 / f64.
+// Dequantise packed GGUF blocks (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
 //
 // Stands in for boostr's dequant_*_f32 kernels (src/quant/cuda/kernels/dequant.cu:18-206, one
 // thread per block, scalar stores) plus the separate cast pass of CudaClient::dequantize
@@ -116,6 +116,29 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         v[2] = fmaf(dl, byte_to_float<2>(q0), nml); v[3] = fmaf(dl, byte_to_float<3>(q0), nml);
         v[4] = fmaf(dl, byte_to_float<0>(q1), nml); v[5] = fmaf(dl, byte_to_float<1>(q1), nml);
         v[6] = fmaf(dl, byte_to_float<2>(q1), nml); v[7] = fmaf(dl, byte_to_float<3>(q1), nml);
+    } else if constexpr (FMT == FMT_Q5_K) {
+        // block = f16 d | f16 dmin | 12 B packed scales/mins (as Q4_K) | 32 B qh | 128 B qs
+        // (src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:56-106).  Element 32 j + l takes nibble (l % 2) of
+        // qs[16 j + l / 2] and bit ((32 j + l) % 8) of qh[(32 j + l) / 8]: the lane's elements 8 lane .. 8 lane + 7 are the
+        // four bytes qs[4 lane .. 4 lane + 3] (low nibble first) and the eight bits of qh[lane].
+        const int j = lane >> 2;
+        const uint4 hq = *reinterpret_cast<const uint4*>(u);
+        const uint32_t dm = hq.x, h1 = hq.y, h2 = hq.z, h3 = hq.w;
+        const float d = f16bits_to_f32(dm & 0xFFFF), dmin = f16bits_to_f32(dm >> 16);
+        const uint32_t scw = j < 4 ? (h1 & 0x3F3F3F3Fu) : ((h3 & 0x0F0F0F0Fu) | ((h1 >> 2) & 0x30303030u));
+        const uint32_t mnw = j < 4 ? (h2 & 0x3F3F3F3Fu) : (((h3 >> 4) & 0x0F0F0F0Fu) | ((h2 >> 2) & 0x30303030u));
+        const int sh8 = 8 * (j & 3);
+        const float dl = d * (float)((scw >> sh8) & 0xFF), nml = -(dmin * (float)((mnw >> sh8) & 0xFF));
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(u + 48 + 4 * lane);
+        const uint32_t hb = u[16 + lane];
+        // even elements: low nibbles + bits 0, 2, 4, 6 of hb; odd elements: high nibbles + bits 1, 3, 5, 7
+        const uint32_t be = ((hb & 1u) | ((hb & 4u) << 6) | ((hb & 16u) << 12) | ((hb & 64u) << 18)) << 4;
+        const uint32_t bo = (((hb >> 1) & 1u) | (((hb >> 1) & 4u) << 6) | (((hb >> 1) & 16u) << 12) | (((hb >> 1) & 64u) << 18)) << 4;
+        const uint32_t qe = (w & 0x0F0F0F0Fu) | be, qo = ((w >> 4) & 0x0F0F0F0Fu) | bo;
+        v[0] = fmaf(dl, byte_to_float<0>(qe), nml); v[1] = fmaf(dl, byte_to_float<0>(qo), nml);
+        v[2] = fmaf(dl, byte_to_float<1>(qe), nml); v[3] = fmaf(dl, byte_to_float<1>(qo), nml);
+        v[4] = fmaf(dl, byte_to_float<2>(qe), nml); v[5] = fmaf(dl, byte_to_float<2>(qo), nml);
+        v[6] = fmaf(dl, byte_to_float<3>(qe), nml); v[7] = fmaf(dl, byte_to_float<3>(qo), nml);
     } else {
         // Q6_K block = 128 B ql | 64 B qh | 16 x i8 scales | f16 d
         // (src/quant/cpu/kernels/dequant_k_quants/q6k_q8k.rs:10-56)
@@ -305,6 +328,7 @@ cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, in
     case FMT_Q4_0: return launch_dequant_fmt<FMT_Q4_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q8_0: return launch_dequant_fmt<FMT_Q8_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q4_K: return launch_dequant_fmt<FMT_Q4_K>(w, nblocks, out, out_dtype, st, sm_count, status);
+    case FMT_Q5_K: return launch_dequant_fmt<FMT_Q5_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q6_K: return launch_dequant_fmt<FMT_Q6_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     default: return cudaErrorInvalidValue;
     }

@@ -207,6 +207,10 @@ struct TileB<FMT_Q4_K, P> {
     }
 };
 
+// Q5_K multiplies in the same order as Q4_K (see slice_q4k): the same fragments and block sums
+template <int P>
+struct TileB<FMT_Q5_K, P> : TileB<FMT_Q4_K, P> {};
+
 // ---- Q6_K: int8 activations; sub-block sb (16 wide) uses elements 4t..4t+3 ----
 template <int P>
 struct TileB<FMT_Q6_K, P> {
@@ -406,9 +410,13 @@ __device__ __forceinline__ int byte_s(uint32_t x) {
     return r;
 }
 
-template <int MT, bool M1>
-__device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, const uint32_t ra, const uint32_t rb, int t,
+// Q4_K, and Q5_K (Q5 = true) in the element order of the reference's x86-64 dot product
+// (src/quant/cpu/kernels/simd/fused_q5k_q8k_dot.rs:27-122): the same header, scales and nibble order as Q4_K, the
+// nibbles 32 bytes further into the block, plus one high bit per element, bit (e % 8) of qh[e / 8] for element e.
+template <int MT, bool M1, bool Q5>
+__device__ __forceinline__ void slice_q4k(const SliceB<Q5 ? FMT_Q5_K : FMT_Q4_K, MT, 0>& B, const uint32_t ra, const uint32_t rb, int t,
                                           float (&acc)[MT][4]) {
+    constexpr uint32_t QS = Q5 ? 48u : 16u;  // offset of the nibble bytes
     const int zero[4] = {0, 0, 0, 0};
     uint4 ha = sld128(ra), hb = sld128(rb);
     // 6-bit scales / mins as packed bytes (unpack_q4k_q5k_scales, q4k_q5k.rs:108-122)
@@ -422,8 +430,8 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, cons
     sB[1] = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
     mB[1] = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
 
-    // 16 * sumi: low-nibble sub-blocks enter with 16 * scale, high nibbles are used unshifted (16 * q);
-    // |16 * sumi| <= 16 * 8 * 63 * 32 * 15 * 127 < 2^31
+    // Q4_K: 16 * sumi (low-nibble sub-blocks enter with 16 * scale, high nibbles are used unshifted, 16 * q);
+    // |16 * sumi| <= 16 * 8 * 63 * 32 * 15 * 127 < 2^31.  Q5_K: sumi itself (5-bit codes cannot stay in the high nibble).
     int isum[MT][4];
 #pragma unroll
     for (int tl = 0; tl < MT; ++tl)
@@ -432,7 +440,7 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, cons
 
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {  // 32 bytes: low nibbles = sub-block 2jj, high = 2jj+1
-        uint2 qa = sld64(ra + 16 + 32 * jj + 8 * t), qb = sld64(rb + 16 + 32 * jj + 8 * t);
+        uint2 qa = sld64(ra + QS + 32 * jj + 8 * t), qb = sld64(rb + QS + 32 * jj + 8 * t);
         int scA0, scA1, scB0, scB1;
         if ((jj & 1) == 0) {
             scA0 = byte_u<0>(sA[jj >> 1]); scA1 = byte_u<1>(sA[jj >> 1]);
@@ -441,10 +449,28 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, cons
             scA0 = byte_u<2>(sA[jj >> 1]); scA1 = byte_u<3>(sA[jj >> 1]);
             scB0 = byte_u<2>(sB[jj >> 1]); scB1 = byte_u<3>(sB[jj >> 1]);
         }
-        scA0 <<= 4;
-        scB0 <<= 4;
-        const uint32_t al0 = qa.x & 0x0F0F0F0Fu, al1 = qb.x & 0x0F0F0F0Fu, al2 = qa.y & 0x0F0F0F0Fu, al3 = qb.y & 0x0F0F0F0Fu;
-        const uint32_t ah0 = qa.x & 0xF0F0F0F0u, ah1 = qb.x & 0xF0F0F0F0u, ah2 = qa.y & 0xF0F0F0F0u, ah3 = qb.y & 0xF0F0F0F0u;
+        uint32_t al0, al1, al2, al3, ah0, ah1, ah2, ah3;
+        if constexpr (Q5) {
+            // the lane's elements 8t .. 8t + 7 of sub-block 2jj take the eight bits of qh[8jj + t], those of sub-block
+            // 2jj + 1 the bits of qh[8jj + 4 + t]; four bits are spread to bit 4 of four bytes by one multiplication
+            const uint2 hqa = sld64(ra + 16 + 8 * jj), hqb = sld64(rb + 16 + 8 * jj);
+            const uint32_t la = (hqa.x >> (8 * t)) & 0xFFu, ua = (hqa.y >> (8 * t)) & 0xFFu;
+            const uint32_t lb = (hqb.x >> (8 * t)) & 0xFFu, ub = (hqb.y >> (8 * t)) & 0xFFu;
+            auto spread = [](uint32_t n4) { return (n4 * 0x02040810u) & 0x10101010u; };  // n4 < 16
+            al0 = (qa.x & 0x0F0F0F0Fu) | spread(la & 15u);
+            al2 = (qa.y & 0x0F0F0F0Fu) | spread(la >> 4);
+            al1 = (qb.x & 0x0F0F0F0Fu) | spread(lb & 15u);
+            al3 = (qb.y & 0x0F0F0F0Fu) | spread(lb >> 4);
+            ah0 = ((qa.x >> 4) & 0x0F0F0F0Fu) | spread(ua & 15u);
+            ah2 = ((qa.y >> 4) & 0x0F0F0F0Fu) | spread(ua >> 4);
+            ah1 = ((qb.x >> 4) & 0x0F0F0F0Fu) | spread(ub & 15u);
+            ah3 = ((qb.y >> 4) & 0x0F0F0F0Fu) | spread(ub >> 4);
+        } else {
+            scA0 <<= 4;
+            scB0 <<= 4;
+            al0 = qa.x & 0x0F0F0F0Fu; al1 = qb.x & 0x0F0F0F0Fu; al2 = qa.y & 0x0F0F0F0Fu; al3 = qb.y & 0x0F0F0F0Fu;
+            ah0 = qa.x & 0xF0F0F0F0u; ah1 = qb.x & 0xF0F0F0F0u; ah2 = qa.y & 0xF0F0F0F0u; ah3 = qb.y & 0xF0F0F0F0u;
+        }
 #pragma unroll
         for (int tl = 0; tl < MT; ++tl) {
             int d[4];
@@ -479,7 +505,7 @@ __device__ __forceinline__ void slice_q4k(const SliceB<FMT_Q4_K, MT, 0>& B, cons
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (M1 && (i & 1)) continue;
-            const int sumi = isum[tl][i] >> 4;
+            const int sumi = Q5 ? isum[tl][i] : isum[tl][i] >> 4;
             const int summ = ml[i] + 128 * mh[i] - 4096 * (i < 2 ? sumA : sumB);
             const float d8 = B.tile[tl].d8[i & 1];
             const float dall = __fmul_rn(i < 2 ? dA : dB, d8);
@@ -934,7 +960,8 @@ __global__ void __launch_bounds__(16 * 32, 1) gemv_kernel(const __grid_constant_
                             ra = sb + rowA * p.srow + ((phA + coff) & 15);
                             rb = sb + rowB * p.srow + ((phB + coff) & 15);
                         }
-                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, M1>(B[c], ra, rb, t, acc);
+                        if constexpr (FMT == FMT_Q4_K) slice_q4k<MT, M1, false>(B[c], ra, rb, t, acc);
+                        else if constexpr (FMT == FMT_Q5_K) slice_q4k<MT, M1, true>(B[c], ra, rb, t, acc);
                         else if constexpr (FMT == FMT_Q6_K) {
                             const uint32_t al = (ra | rb) & 3u;
                             if (__all_sync(0xFFFFFFFFu, al == 0)) slice_q6k<MT, M1, 1>(B[c], ra, rb, t, acc);
@@ -1020,7 +1047,7 @@ cudaError_t launch_one(const GemvParams& p, const GemvMaps& maps, dim3 grid, int
 
 template <int FMT, bool SWIGLU>
 cudaError_t launch_gemv_fmt(const GemvParams& p, const GemvMaps& maps, int mt, int sl, dim3 grid, int threads, size_t smem, cudaStream_t st) {
-    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
+    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q5_K || FMT == FMT_Q6_K);
     const bool m1 = p.mcount == 1 && p.M == 1;
     if constexpr (KQ) {
         if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, maps, grid, threads, smem, st)
@@ -1043,7 +1070,7 @@ template <int FMT>
 cudaError_t launch_prep_fmt(const PrepParams& pp, int mt, cudaStream_t st) {
     const unsigned units = pp.nslices * pp.tiles_total;
     const dim3 grid((units + 3) / 4), block(128);
-    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q6_K);
+    constexpr bool KQ = (FMT == FMT_Q4_K || FMT == FMT_Q5_K || FMT == FMT_Q6_K);
     cudaError_t e;
     if constexpr (KQ) {
         e = launch_pdl(act_prep_kernel<FMT, 0>, grid, block, 0, st, pp);
@@ -1059,7 +1086,7 @@ cudaError_t launch_prep_fmt(const PrepParams& pp, int mt, cudaStream_t st) {
 // Largest number of K-chunks a CTA may keep activation fragments for, per format and tile count
 // (the fragments of SL chunks x MT tiles live in registers).
 int gemv_max_sl(int fmt, int mt) {
-    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     if (kq) return mt == 1 ? 4 : 2;
     return 1;
 }
@@ -1106,7 +1133,7 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     // once fall in distinct banks: Q4_K reads 8 bytes per lane (rows 32 bytes apart mod 128),
     // the other formats 4 bytes per lane (rows 16 bytes apart mod 32).
     uint32_t srow = (cmax + 19 + 15) & ~15u;
-    if (fmt == FMT_Q4_K) {
+    if (fmt == FMT_Q4_K || fmt == FMT_Q5_K) {
         while ((srow & 63) != 32) srow += 16;
     } else {
         if ((srow & 31) == 0) srow += 16;
@@ -1114,10 +1141,10 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     pl.rows_aligned = (row_bytes % 16 == 0 && (pl.spc * slice_b) % 16 == 0) ? 1u : 0u;
     pl.srow = srow;
     pl.stage_bytes = ((16 * pl.rgs * srow + 127) & ~127u) + 128;
-    // Tiled fills (one copy per stage): column width = 2 slices of Q4_K (288 B: rows 32 B apart mod 128 for the
-    // 8-byte reads), 1 slice of Q8_0 / Q4_0 (272 / 144 B: 16 B apart), 8 slices of Q6_K (1680 B, the smallest whole
+    // Tiled fills (one copy per stage): column width = 2 slices of Q4_K / Q5_K (288 / 352 B: rows 32 / 96 B apart mod
+    // 128 for the 8-byte reads), 1 slice of Q8_0 / Q4_0 (272 / 144 B: 16 B apart), 8 slices of Q6_K (1680 B, the smallest whole
     // number of 210-byte blocks that is a multiple of 16 bytes).  Rows must be a whole number of columns.
-    const uint32_t tw = fmt == FMT_Q4_K ? 288u : fmt == FMT_Q6_K ? 1680u : slice_b;
+    const uint32_t tw = fmt == FMT_Q4_K ? 288u : fmt == FMT_Q5_K ? 352u : fmt == FMT_Q6_K ? 1680u : slice_b;
     pl.use_tma = 0;
     pl.tma_w = tw;
     pl.tma_cb = (cmax + tw - 1) / tw;
@@ -1191,6 +1218,7 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     case FMT_Q4_0: e = launch_prep_fmt<FMT_Q4_0>(pp, mt, st); break;
     case FMT_Q8_0: e = launch_prep_fmt<FMT_Q8_0>(pp, mt, st); break;
     case FMT_Q4_K: e = launch_prep_fmt<FMT_Q4_K>(pp, mt, st); break;
+    case FMT_Q5_K: e = launch_prep_fmt<FMT_Q5_K>(pp, mt, st); break;
     case FMT_Q6_K: e = launch_prep_fmt<FMT_Q6_K>(pp, mt, st); break;
     default: return cudaErrorInvalidValue;
     }
@@ -1246,6 +1274,8 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
                                   : launch_gemv_fmt<FMT_Q8_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         case FMT_Q4_K: e = swiglu ? launch_gemv_fmt<FMT_Q4_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
                                   : launch_gemv_fmt<FMT_Q4_K, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q5_K: e = swiglu ? launch_gemv_fmt<FMT_Q5_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q5_K, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         case FMT_Q6_K: e = swiglu ? launch_gemv_fmt<FMT_Q6_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
                                   : launch_gemv_fmt<FMT_Q6_K, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         default: return cudaErrorInvalidValue;

@@ -58,7 +58,7 @@ namespace {
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int PF_MAX_STAGES = 8;
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
-__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : 144; }
+__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : fmt == FMT_Q5_K ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
 // multiples of 16 bytes, so TMA cannot fetch them: the dequant warps copy them themselves, coalesced, 2 bytes per lane,
 // into rows of 212 bytes (4-byte aligned blocks, conflict-free row-per-thread reads).
@@ -174,6 +174,36 @@ __device__ __forceinline__ void decode32_q4k(const RawQ4K& r, uint32_t kt, uint3
     }
 }
 
+// Elements [64*kt + 32*half, +32) of a Q5_K row in the element order of the reference's x86-64 dot product
+// (src/quant/cpu/kernels/simd/fused_q5k_q8k_dot.rs:27-122): Q4_K's nibble order, the nibbles 32 bytes further into the
+// block, plus bit (e % 8) of qh[e / 8] for element e: the 32 elements take the 32 bits of one word of qh.
+__device__ __forceinline__ void decode32_q5k(const uint8_t* blk, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
+    const uint32_t jj = kt & 3;
+    const uint4 hd = *reinterpret_cast<const uint4*>(blk);
+    const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
+    uint32_t sc, mn;
+    if (jj < 2) {
+        sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
+        mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
+    } else {
+        const uint32_t sh = 16 * (jj - 2);
+        sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
+        mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
+    }
+    const float dl = d * (float)((sc >> (8 * half)) & 0xFF);
+    const float nml = -(dmin * (float)((mn >> (8 * half)) & 0xFF));
+    const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 48 + 32 * jj), q1 = *reinterpret_cast<const uint4*>(blk + 64 + 32 * jj);
+    const uint32_t hbits = *reinterpret_cast<const uint32_t*>(blk + 16 + 8 * jj + 4 * half);
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        // word i holds elements 4i .. 4i + 3; their high bits are bits 4i .. 4i + 3 of hbits
+        const uint32_t q = ((w[i] >> (4 * half)) & 0x0F0F0F0Fu) | ((((hbits >> (4 * i)) & 15u) * 0x02040810u) & 0x10101010u);
+        o[2 * i] = pack_bf16(fmaf(dl, byte_to_float<0>(q), nml), fmaf(dl, byte_to_float<1>(q), nml));
+        o[2 * i + 1] = pack_bf16(fmaf(dl, byte_to_float<2>(q), nml), fmaf(dl, byte_to_float<3>(q), nml));
+    }
+}
+
 // One 32-element Q8_0 / Q4_0 block (2-byte aligned) as 32 bf16.  SM: the block sits in shared memory.
 template <int FMT, bool SM>
 __device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t (&o)[16]) {
@@ -232,6 +262,10 @@ template <int FMT>
 __device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
     if constexpr (FMT == FMT_Q6_K) {
         decode32_q6k<false>(row + (kt >> 2) * 210, kt, half, o);
+    } else if constexpr (FMT == FMT_Q5_K || FMT == FMT_Q4_K) {
+        // never taken: K-quant rows are whole 256-element blocks, which are always staged in shared memory
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = 0;
     } else if constexpr (FMT == FMT_Q8_0) {
         decode32_blk<FMT_Q8_0, false>(row + (2 * kt + half) * 34, o);
     } else {
@@ -315,7 +349,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
                     // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
-                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * (FMT == FMT_Q8_0 ? 136 : 144)), (int)n0, bar_full_raw + 8 * s);
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * (FMT == FMT_Q8_0 ? 136 : FMT == FMT_Q5_K ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
                     if (++s == 2) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -489,6 +523,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                         }
                         decode32_q4k(cur, kt, half, o);
+                    } else if constexpr (FMT == FMT_Q5_K) {
+                        if (ok) decode32_q5k(rrow, kt, half, o);
+                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                        }
                     } else if constexpr (FMT == FMT_Q6_K) {
                         if (ok) decode32_q6k<true>(rrow, kt, half, o);
                         if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
@@ -618,7 +658,7 @@ bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
 
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
     (void)N;
-    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
     return (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
 }
 
@@ -627,7 +667,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
                            unsigned int* status, bool* ws_too_small, char* err, size_t err_len) {
     *ws_too_small = false;
     const void* act_bf16 = act;
-    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q6_K);
+    const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     if (act_dtype != DT_BF16 || kq) {
         const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N);
         if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
@@ -702,7 +742,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
         const bool q8 = fmt == FMT_Q8_0;
         const cuuint64_t wdim[2] = {(cuuint64_t)(q8 ? p.row_bytes / 2 : p.row_bytes), (cuuint64_t)N};
         const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
-        const cuuint32_t wbox[2] = {q8 ? 136u : 144u, 128u};
+        const cuuint32_t wbox[2] = {q8 ? 136u : fmt == FMT_Q5_K ? 176u : 144u, 128u};
         cr = enc(&wmap, q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox,
                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -716,6 +756,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     case FMT_Q4_0: return raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st);
     case FMT_Q8_0: return raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st);
     case FMT_Q4_K: return launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st);
+    case FMT_Q5_K: return launch_fmt<FMT_Q5_K, true>(map, wmap, p, grid, smem, st);
     case FMT_Q6_K: return launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st);
     default: return cudaErrorInvalidValue;
     }

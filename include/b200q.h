@@ -51,6 +51,7 @@ typedef enum b200q_format {
     B200Q_Q4_0 = 0,
     B200Q_Q8_0 = 4,
     B200Q_Q4_K = 8,
+    B200Q_Q5_K = 9, /* decode shapes run through the small-M kernel; no fused row-/column-parallel exchange */
     B200Q_Q6_K = 10
 } b200q_format;
 
