@@ -34,6 +34,9 @@ SIGNATURES = {
     "b200q_quant_matmul_batch": (c_int, [c_int, POINTER(c_int), POINTER(c_void_p), POINTER(c_size_t),
                                          POINTER(c_void_p), c_void_p, c_int, c_int, c_size_t, c_size_t, c_void_p,
                                          c_size_t, c_void_p]),
+    "b200q_rmsnorm_quant_matmul_batch": (c_int, [c_int, POINTER(c_int), POINTER(c_void_p), POINTER(c_size_t), POINTER(c_void_p),
+                                                 c_void_p, c_void_p, ctypes.c_float, c_int, c_int, c_size_t, c_size_t, c_void_p,
+                                                 c_size_t, c_void_p]),
     "b200q_quant_swiglu": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                    c_size_t, c_void_p, c_size_t, c_void_p]),
     "b200q_quant_matmul_static_scratch": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t,

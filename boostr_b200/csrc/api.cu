@@ -20,13 +20,15 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
 size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count);
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu);
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
-                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status);
+                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status,
+                           const float* norm_w = nullptr, float norm_eps = 0.f);
 cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w6, size_t n6, void* out6, int out_dtype, size_t K, int sm_count,
-                                 cudaStream_t st, unsigned int* status);
+                                 cudaStream_t st, unsigned int* status, const float* norm_w = nullptr, float norm_eps = 0.f);
 cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
-                                 unsigned int* status);
+                                 unsigned int* status, const float* norm_w = nullptr, float norm_eps = 0.f);
+cudaError_t launch_rmsnorm(const void* act, int act_dtype, const float* norm_w, float eps, float* out, size_t M, size_t K, cudaStream_t st);
 cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
                                   int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm);
 bool gemv_m1_f32_supported(int fmt, size_t M, size_t K, size_t N);
@@ -230,12 +232,36 @@ int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w
     return B200Q_OK;
 }
 
-int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
-                             const void* act, int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes,
-                             void* stream) {
-    if (n_weights < 0) return fail(B200Q_ERR_INVALID_ARG, "quant_matmul_batch: negative weight count");
+}  // extern "C" (reopened below)
+
+namespace {
+// quant_matmul_batch with an optional RMSNorm prologue (norm_w == nullptr: none)
+int matmul_batch_impl(const char* op, int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
+                      const void* act, int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes, void* stream,
+                      const float* norm_w, float eps) {
+    if (n_weights < 0) return fail(B200Q_ERR_INVALID_ARG, "%s: negative weight count", op);
     if (n_weights == 0) return B200Q_OK;
-    if (!formats || !w || !N || !out) return fail(B200Q_ERR_INVALID_ARG, "quant_matmul_batch: null array");
+    if (!formats || !w || !N || !out) return fail(B200Q_ERR_INVALID_ARG, "%s: null array", op);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The decode kernels (M = 1, Q4_K / Q6_K) normalise the row themselves while they quantise it.  Every other shape
+    // gets the normalised activations from one stand-alone launch into the front of the scratch buffer.
+    bool all_fused = norm_w != nullptr;
+    for (int i = 0; i < n_weights && all_fused; ++i) all_fused = known_format(formats[i]) && gemv_m1_supported(formats[i], M, K, N[i], false);
+    if (norm_w && !all_fused) {
+        const size_t nbytes = (M * K * sizeof(float) + 255) & ~(size_t)255;
+        if (act_dtype != DT_F32 && act_dtype != DT_BF16) return fail(B200Q_ERR_UNSUPPORTED_DTYPE, "%s activation must be F32 (or BF16), got dtype id %d", op, act_dtype);
+        if (M == 0 || K == 0 || K % 8) return fail(B200Q_ERR_BAD_SHAPE, "%s: M and K must be positive and K a multiple of 8 (M=%zu K=%zu)", op, M, K);
+        if (!act || (reinterpret_cast<uintptr_t>(act) & 15)) return fail(B200Q_ERR_INVALID_ARG, "%s: activation pointer must be non-null and 16-byte aligned", op);
+        if (!ws || ws_bytes < nbytes || (reinterpret_cast<uintptr_t>(ws) & 15))
+            return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "%s: workspace of %zu bytes is too small for the normalised activations (%zu bytes)", op, ws_bytes, nbytes);
+        cudaError_t e = launch_rmsnorm(act, act_dtype, norm_w, eps, static_cast<float*>(ws), M, K, st);
+        if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA rmsnorm kernel launch failed: %s", cudaGetErrorString(e));
+        act = ws;
+        act_dtype = DT_F32;
+        ws = static_cast<uint8_t*>(ws) + nbytes;
+        ws_bytes -= nbytes;
+        norm_w = nullptr;
+    }
     for (int i = 0; i < n_weights;) {
         // decode (M = 1): runs of up to three Q4_K weights, optionally followed by one Q6_K weight (the
         // q/k/v projections of a Q4_K_M model), go out as ONE launch that streams them side by side
@@ -246,18 +272,24 @@ int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* cons
             mixed = i + run < n_weights && formats[i + run] == FMT_Q6_K && gemv_m1_supported(FMT_Q6_K, M, K, N[i + run], false);
         }
         const int total = run + (mixed ? 1 : 0);
-        if (total > 1) {
+        if (total > 1 || norm_w) {
             for (int j = 0; j < total; ++j) {
-                int rc = check_matmul_args("quant_matmul_batch", formats[i + j], act, act_dtype, w[i + j], out[i + j], out_dtype, M, K, N[i + j]);
+                int rc = check_matmul_args(op, formats[i + j], act, act_dtype, w[i + j], out[i + j], out_dtype, M, K, N[i + j]);
                 if (rc) return rc;
             }
             unsigned int* status = status_ptr_current();
-            if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul_batch: cannot resolve the device status word");
-            cudaError_t e = mixed ? launch_gemv_m1_mixed(act, act_dtype, run, w + i, N + i, out + i, w[i + run], N[i + run], out[i + run],
-                                                         out_dtype, K, sm_count_current(), static_cast<cudaStream_t>(stream), status)
-                                  : launch_gemv_m1_batch(act, act_dtype, run, w + i, N + i, out + i, nullptr, out_dtype, K,
-                                                         sm_count_current(), static_cast<cudaStream_t>(stream), status);
-            if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_matmul_batch kernel launch failed: %s", cudaGetErrorString(e));
+            if (!status) return fail(B200Q_ERR_CUDA, "%s: cannot resolve the device status word", op);
+            cudaError_t e;
+            if (mixed)
+                e = launch_gemv_m1_mixed(act, act_dtype, run, w + i, N + i, out + i, w[i + run], N[i + run], out[i + run], out_dtype, K,
+                                         sm_count_current(), st, status, norm_w, eps);
+            else if (formats[i] == FMT_Q4_K)
+                e = launch_gemv_m1_batch(act, act_dtype, run, w + i, N + i, out + i, nullptr, out_dtype, K, sm_count_current(), st, status,
+                                         norm_w, eps);
+            else  // a single fused-prologue weight of another format (Q6_K)
+                e = launch_gemv_m1(formats[i], act, act_dtype, w[i], nullptr, out[i], out_dtype, K, N[i], sm_count_current(), st, status,
+                                   norm_w, eps);
+            if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA %s kernel launch failed: %s", op, cudaGetErrorString(e));
         } else {
             int rc = b200q_quant_matmul(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream);
             if (rc) return rc;
@@ -265,6 +297,25 @@ int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* cons
         i += total;
     }
     return B200Q_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
+                             const void* act, int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes,
+                             void* stream) {
+    return matmul_batch_impl("quant_matmul_batch", n_weights, formats, w, N, out, act, act_dtype, out_dtype, M, K, ws, ws_bytes, stream,
+                             nullptr, 0.f);
+}
+
+int b200q_rmsnorm_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
+                                     const void* act, const float* norm_weight, float eps, int act_dtype, int out_dtype, size_t M,
+                                     size_t K, void* ws, size_t ws_bytes, void* stream) {
+    if (!norm_weight) return fail(B200Q_ERR_INVALID_ARG, "rmsnorm_quant_matmul_batch: null norm weight");
+    if (reinterpret_cast<uintptr_t>(norm_weight) & 15) return fail(B200Q_ERR_INVALID_ARG, "rmsnorm_quant_matmul_batch: norm weight must be 16-byte aligned");
+    return matmul_batch_impl("rmsnorm_quant_matmul_batch", n_weights, formats, w, N, out, act, act_dtype, out_dtype, M, K, ws, ws_bytes,
+                             stream, norm_weight, eps);
 }
 
 int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w_gate, const void* w_up, void* out,

@@ -34,6 +34,8 @@ struct GemvM1Params {
     uint32_t nseg;
     const uint8_t* w2;   // up-projection weight (SwiGLU variant, single segment)
     const void* act;
+    const float* norm_w; // RMSNorm prologue: the row is replaced by x * rsqrt(mean(x^2) + eps) * norm_w before it is quantised
+    float norm_eps;
     uint32_t K, N;
     uint32_t nblk;       // K / 256 (<= 16)
     uint32_t row_bytes;  // nblk * 144
@@ -117,6 +119,20 @@ __device__ __forceinline__ float quantize_block8(const float (&v)[8], uint2& pac
     return __fdiv_rn(amax, 127.0f);
 }
 
+// RMSNorm prologue.  Every warp adds the squares of the values it holds (0 for warps without a block), the 16 warp sums
+// meet in shared memory (`red`, 16 floats) and every thread adds them in warp order, so all threads hold the same
+// factor 1 / sqrt(mean(x^2) + eps).  Contains a block-wide barrier: all 512 threads call it.
+__device__ __forceinline__ float rms_factor(float local_sq, float* red, int warp, int lane, uint32_t K, float eps) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local_sq += __shfl_xor_sync(0xFFFFFFFFu, local_sq, o);
+    if (lane == 0) red[warp] = local_sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tot += red[i];
+    return 1.0f / sqrtf(tot / (float)K + eps);
+}
+
 // SWIGLU: two weights; a warp takes gate row r (lanes 0-15) and up row r (lanes 16-31) and stores
 // silu(gate . x) * (up . x)  (quant_swiglu, src/quant/traits/quant_matmul.rs:122-127).
 //
@@ -187,6 +203,21 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         if (on) load_act8(p.act, p.act_dtype, (size_t)warp * 256 + 8 * lane, v);
         const uint32_t f1 = 2 + (uint32_t)warp;  // the rest of the ring: one fill per warp
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+        if (p.norm_w) {  // uniform over the launch
+            float sq = 0.f;
+            float g[8];
+            if (on) {
+                const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + (size_t)warp * 256 + 8 * lane));
+                const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + (size_t)warp * 256 + 8 * lane) + 1);
+                g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = fmaf(v[i], v[i], sq);
+            }
+            const float rs = rms_factor(sq, reinterpret_cast<float*>(smem + 256), warp, lane, p.K, p.norm_eps);
+            if (on)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], rs), g[i]);
+        }
         if (on) {  // warp-uniform
             uint2 packed;
             int s;
@@ -335,6 +366,8 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_q4k_kernel(const __grid_consta
 struct GemvM1Q6Params {
     const uint8_t* w;
     const void* act;
+    const float* norm_w;  // RMSNorm prologue (see GemvM1Params)
+    float norm_eps;
     void* out;
     uint32_t K, N;
     uint32_t nblk;          // K / 256 (<= 64)
@@ -452,6 +485,27 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
         }
         const uint32_t f1 = 2 + (uint32_t)warp;
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+        if (p.norm_w) {  // uniform over the launch
+            float sq = 0.f;
+#pragma unroll
+            for (int j = 0; j < NCHUNK; ++j)
+                if (warp + 16 * j < p.nblk)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sq = fmaf(v[j][i], v[j][i], sq);
+            const float rs = rms_factor(sq, part, warp, lane, p.K, p.norm_eps);  // `part` is not in use yet
+            __syncthreads();                                                     // ... and is free again before the loop
+#pragma unroll
+            for (int j = 0; j < NCHUNK; ++j) {
+                const uint32_t qb = warp + 16 * j;
+                if (qb < p.nblk) {
+                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + (size_t)qb * 256 + 8 * lane));
+                    const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + (size_t)qb * 256 + 8 * lane) + 1);
+                    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[j][i] = __fmul_rn(__fmul_rn(v[j][i], rs), g[i]);
+                }
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NCHUNK; ++j) {
             const uint32_t qb = warp + 16 * j;
@@ -633,7 +687,7 @@ static size_t setup_q4k(GemvM1Params& p, size_t& smem, const void* act, int act_
     while (p.lpr < p.nblk) p.lpr *= 2;
     if (p.lpr < 2) p.lpr = 2;
     p.stage_bytes = (w_up ? 8 : 4 * (32 / p.lpr)) * p.row_bytes;  // 4 warps x rows per warp (SwiGLU: 4 gate + 4 up); multiple of 128
-    p.act_off = 256;  // [0,256) barriers
+    p.act_off = 320;  // [0,256) barriers, [256,320) the warp sums of the RMSNorm prologue
     p.stage_off = (p.act_off + 16 * ACT_STRIDE + 127) & ~127u;
     p.nstages = (uint32_t)((M1_SMEM_MAX - p.stage_off) / p.stage_bytes);
     if (p.nstages > 16) p.nstages = 16;
@@ -663,11 +717,13 @@ static cudaError_t m1_attrs() {
 }
 
 static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
-                                      size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
+                                      size_t N, int sm_count, cudaStream_t st, unsigned int* status, const float* norm_w, float norm_eps) {
     GemvM1Q6Params p;
     uint32_t nchunk;
     size_t smem;
     const size_t grid = setup_q6k(p, nchunk, smem, act, act_dtype, w, out, out_dtype, K, N, (size_t)sm_count, status);
+    p.norm_w = norm_w;
+    p.norm_eps = norm_eps;
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
@@ -680,10 +736,12 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
 // Q4_K, M = 1: `nseg` weights (1..3) sharing one activation row, each [n[i], K] with its own output.
 cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
-                                 unsigned int* status) {
+                                 unsigned int* status, const float* norm_w, float norm_eps) {
     GemvM1Params p;
     size_t smem;
     const size_t grid = setup_q4k(p, smem, act, act_dtype, nseg, w, n, out, w_up, out_dtype, K, (size_t)sm_count, status);
+    p.norm_w = norm_w;
+    p.norm_eps = norm_eps;
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = w_up ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
@@ -696,7 +754,7 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
 // divided in proportion to the packed bytes, Q6_K bytes counting 1.3x (more arithmetic per byte).
 cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w6, size_t n6, void* out6, int out_dtype, size_t K, int sm_count,
-                                 cudaStream_t st, unsigned int* status) {
+                                 cudaStream_t st, unsigned int* status, const float* norm_w, float norm_eps) {
     size_t n4 = 0;
     for (int i = 0; i < nseg; ++i) n4 += n[i];
     const double b4 = (double)n4 * 144.0, b6 = (double)n6 * 210.0 * 1.3;
@@ -709,6 +767,8 @@ cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const
     size_t smem4, smem6;
     const size_t grid4 = setup_q4k(p4, smem4, act, act_dtype, nseg, w, n, out, nullptr, out_dtype, K, (size_t)sm_count - g6, status);
     const size_t grid6 = setup_q6k(p6, nchunk, smem6, act, act_dtype, w6, out6, out_dtype, K, n6, g6, status);
+    p4.norm_w = p6.norm_w = norm_w;
+    p4.norm_eps = p6.norm_eps = norm_eps;
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = launch_pdl(gemv_m1_mixed_kernel, dim3((unsigned)(grid4 + grid6)), dim3(512), smem4 > smem6 ? smem4 : smem6, st,
@@ -744,9 +804,42 @@ cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const
 }
 
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
-                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status) {
-    if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status);
-    return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status);
+                           int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status,
+                           const float* norm_w, float norm_eps) {
+    if (fmt == FMT_Q6_K) return launch_gemv_m1_q6k(act, act_dtype, w, out, out_dtype, K, N, sm_count, st, status, norm_w, norm_eps);
+    return launch_gemv_m1_batch(act, act_dtype, 1, &w, &N, &out, w_up, out_dtype, K, sm_count, st, status, norm_w, norm_eps);
+}
+
+// Stand-alone RMSNorm (one CTA per row) for the shapes whose kernels have no fused prologue: the normalised row goes
+// to scratch as f32 and the quantized product reads it from there.  Same expression as the fused form:
+// x * (1 / sqrt(mean(x^2) + eps)) * w, squares added 8 per lane then across the warp, warp sums in warp order.
+__global__ void __launch_bounds__(512) rmsnorm_kernel(const void* __restrict__ act, int act_dtype, const float* __restrict__ norm_w, float eps,
+                                                      float* __restrict__ out, uint32_t K) {
+    __shared__ float red[16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row = blockIdx.x;
+    grid_dep_launch();
+    grid_dep_wait();
+    float sq = 0.f;
+    for (uint32_t k0 = threadIdx.x * 8; k0 < K; k0 += 512 * 8) {
+        float v[8];
+        load_act8(act, act_dtype, row * K + k0, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sq = fmaf(v[i], v[i], sq);
+    }
+    const float rs = rms_factor(sq, red, warp, lane, K, eps);
+    for (uint32_t k0 = threadIdx.x * 8; k0 < K; k0 += 512 * 8) {
+        float v[8];
+        load_act8(act, act_dtype, row * K + k0, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[row * K + k0 + i] = __fmul_rn(__fmul_rn(v[i], rs), __ldg(norm_w + k0 + i));
+    }
+}
+
+cudaError_t launch_rmsnorm(const void* act, int act_dtype, const float* norm_w, float eps, float* out, size_t M, size_t K, cudaStream_t st) {
+    cudaError_t e = launch_pdl(rmsnorm_kernel, dim3((unsigned)M), dim3(512), 0, st, act, act_dtype, norm_w, eps, out, (uint32_t)K);
+    note_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace b200q

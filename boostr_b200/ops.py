@@ -169,6 +169,36 @@ def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
     return outs
 
 
+def rmsnorm_quant_matmul_batch(activation: torch.Tensor, norm_weight: torch.Tensor, eps: float, weights: Sequence[QuantTensor],
+                               out_dtype: torch.dtype = torch.float32, outs: Sequence[torch.Tensor] = None) -> List[torch.Tensor]:
+    """RMSNorm(activation) against several weights sharing K: the attention block's input_layernorm + q/k/v
+    projections as one operator (``b200q_rmsnorm_quant_matmul_batch``).  With one activation row and Q4_K / Q6_K weights
+    the normalisation happens inside the decode kernel."""
+    if not weights:
+        return []
+    acts = [_check_act("rmsnorm_quant_matmul", activation, w, True) for w in weights]
+    act, m, k, _ = acts[0]
+    if norm_weight.dtype != torch.float32 or norm_weight.numel() != k or not norm_weight.is_cuda or not norm_weight.is_contiguous():
+        raise QuantError(f"norm weight must be a contiguous F32 CUDA tensor of {k} elements")
+    outs = [_out_buffer(None if outs is None else outs[i], (*activation.shape[:-1], a[3]), out_dtype, act.device)
+            for i, a in enumerate(acts)]
+    if m == 0:
+        return outs
+    L = _cabi.lib()
+    nw = len(weights)
+    fmts = (ctypes.c_int * nw)(*[w.format.format_id for w in weights])
+    wptr = (ctypes.c_void_p * nw)(*[w.storage.data_ptr() for w in weights])
+    ns = (ctypes.c_size_t * nw)(*[a[3] for a in acts])
+    optr = (ctypes.c_void_p * nw)(*[o.data_ptr() for o in outs])
+    with torch.cuda.device(act.device):
+        need = max(L.b200q_workspace_bytes(_cabi.OP_QUANT_MATMUL, w.format.format_id, m, k, a[3]) for w, a in zip(weights, acts))
+        need += (m * k * 4 + 255) // 256 * 256
+        ws = workspace(need, act.device)
+        _cabi.check(L.b200q_rmsnorm_quant_matmul_batch(nw, fmts, wptr, ns, optr, act.data_ptr(), norm_weight.data_ptr(), float(eps),
+                                                       _DT[act.dtype], _DT[out_dtype], m, k, ws.data_ptr(), ws.numel(), _stream()))
+    return outs
+
+
 def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: QuantTensor,
                  out_dtype: torch.dtype = torch.float32, out: torch.Tensor = None) -> torch.Tensor:
     """silu(activation x gate^T) * (activation x up^T); gate and up share N, K and format."""

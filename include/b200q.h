@@ -129,6 +129,22 @@ B200Q_API int b200q_quant_matmul_batch(int n_weights, const int* formats, const 
                                        size_t K, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * RMSNorm fused in front of quant_matmul_batch: what a LLaMA attention block does with its input,
+ * `input_layernorm` followed by the batched q/k/v projections (src/model/llama/model/blocks_attention.rs:95-99 after
+ * RmsNorm::forward, src/nn/rmsnorm.rs:40):
+ *     x' = act * (1 / sqrt(mean(act^2) + eps)) * norm_weight      (per row, f32)
+ *     out[i] = x' x dequant(w[i])^T
+ * With one activation row and Q4_K / Q6_K weights the decode kernels normalise the row while they quantise it (no extra
+ * launch, no round trip of the normalised row through memory); other shapes run one stand-alone normalisation launch
+ * into the front of `ws`, which must then hold M * K * 4 bytes (rounded up to 256) in addition to
+ * b200q_workspace_bytes.  norm_weight: K f32 values on the device, 16-byte aligned.
+ */
+B200Q_API int b200q_rmsnorm_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N,
+                                               void* const* out, const void* act, const float* norm_weight, float eps,
+                                               int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes,
+                                               void* stream);
+
+/*
  * QuantMatmulOps::quant_swiglu (src/quant/traits/quant_matmul.rs:122-127; CUDA impl
  * src/quant/cuda/quant_matmul/impl_ops.rs:337-441):
  *     out[M,N] = silu(act x Wg^T) * (act x Wu^T),   silu(x) = x / (1 + exp(-x))

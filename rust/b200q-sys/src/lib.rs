@@ -54,6 +54,10 @@ extern "C" {
     pub fn b200q_quant_matmul_batch(n_weights: c_int, formats: *const c_int, w: *const *const c_void, n: *const usize,
                                     out: *const *mut c_void, act: *const c_void, act_dtype: c_int, out_dtype: c_int,
                                     m: usize, k: usize, ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn b200q_rmsnorm_quant_matmul_batch(n_weights: c_int, formats: *const c_int, w: *const *const c_void, n: *const usize,
+                                            out: *const *mut c_void, act: *const c_void, norm_weight: *const f32, eps: f32,
+                                            act_dtype: c_int, out_dtype: c_int, m: usize, k: usize, ws: *mut c_void,
+                                            ws_bytes: usize, stream: *mut c_void) -> c_int;
     pub fn b200q_quant_swiglu(format: c_int, act: *const c_void, act_dtype: c_int, w_gate: *const c_void,
                               w_up: *const c_void, out: *mut c_void, out_dtype: c_int, m: usize, k: usize, n: usize,
                               ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> c_int;

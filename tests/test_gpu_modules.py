@@ -189,3 +189,60 @@ def test_decode_graph_replay_equals_eager(ops, m):
         runner.replay(x=torch.zeros(m + 1, 1024, device="cuda"))
     with pytest.raises(KeyError):
         runner.replay(y=torch.zeros(1, device="cuda"))
+
+
+def _rmsnorm_np(x, g, eps):
+    x = x.astype(np.float32)
+    rs = np.float32(1.0) / np.sqrt((x * x).mean(axis=-1, keepdims=True, dtype=np.float32) + np.float32(eps))
+    return (x * rs * g[None, :]).astype(np.float32)
+
+
+@pytest.mark.parametrize("k,specs", [(4096, [("Q4_K", 512), ("Q4_K", 128), ("Q6_K", 128)]), (1024, [("Q4_K", 96)]),
+                                     (8192, [("Q6_K", 64)]), (2048, [("Q6_K", 40), ("Q4_K", 33)])])
+def test_rmsnorm_prologue_decode(ops, oracle, k, specs):
+    """input_layernorm + batched projections as one operator, one activation row: the decode kernels normalise the row
+    while they quantise it.  RMSNorm itself is numr's in the reference (source absent): the comparison is against
+    x * (1 / sqrt(mean(x^2) + eps)) * w in f32 followed by the CPU path of the product; a last-bit difference in the
+    normalised row can move a Q8_K code by one, hence the 1e-3 bar.  The fused form must also equal, bit for bit, the
+    library's own unfused form (stand-alone normalisation launch, then the same product)."""
+    from boostr_b200.tensor import QuantTensor
+
+    rng = synth.rng_for(45, k + len(specs))
+    act = synth.activations(rng, 1, k) * np.float32(3.0)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    ws = [synth.weight_bytes(f, rng, n, k) for f, n in specs]
+    qts = [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)]
+    act_t, g_t = torch.from_numpy(act).cuda(), torch.from_numpy(g).cuda()
+    before = ops.launch_count()
+    outs = ops.rmsnorm_quant_matmul_batch(act_t, g_t, 1e-5, qts)
+    fused_launches = ops.launch_count() - before
+    ops.check_device_status()
+    xn = _rmsnorm_np(act, g, 1e-5)
+    for (f, n), w, o in zip(specs, ws, outs):
+        want = oracle.quant_matmul(f, xn, w, n)
+        assert rel_err(o.cpu().numpy(), want)[0] <= 1e-3, (f, n)
+    # unfused form: a Q8_0 weight in the batch has no fused prologue, so the whole batch takes the stand-alone launch
+    extra = QuantTensor.from_bytes(synth.weight_bytes("Q8_0", rng, 32, k), "Q8_0", (32, k), device="cuda")
+    before = ops.launch_count()
+    outs2 = ops.rmsnorm_quant_matmul_batch(act_t, g_t, 1e-5, qts + [extra])
+    assert ops.launch_count() - before > fused_launches
+    for a, b in zip(outs, outs2):
+        assert torch.equal(a, b)
+    want8 = oracle.quant_matmul("Q8_0", xn, extra_bytes := extra.storage.cpu().numpy(), 32)
+    assert rel_err(outs2[-1].cpu().numpy(), want8)[0] <= 1e-4
+
+
+@pytest.mark.parametrize("m", [4, 80])
+def test_rmsnorm_prologue_more_rows(ops, oracle, m):
+    rng = synth.rng_for(46, m)
+    k = 1024
+    act = synth.activations(rng, m, k)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    specs = [("Q4_K", 64), ("Q6_K", 48)]
+    ws = [synth.weight_bytes(f, rng, n, k) for f, n in specs]
+    outs = ops.rmsnorm_quant_matmul_batch(torch.from_numpy(act).cuda(), torch.from_numpy(g).cuda(), 1e-6,
+                                          [_qt(f, w, n, k) for (f, n), w in zip(specs, ws)])
+    ops.check_device_status()
+    xn = _rmsnorm_np(act, g, 1e-6)
+    for (f, n), w, o in zip(specs, ws, outs):
+        assert rel_err(o.cpu().numpy(), oracle.quant_matmul(f, xn, w, n))[0] <= (1e-2 if m >= 64 else 1e-3)
