@@ -57,6 +57,7 @@ namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int PF_MAX_STAGES = 8;
+constexpr uint32_t PF_NSA = 8;  // decoded weight tiles in tensor memory: 8 x 32 columns
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
 __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : fmt == FMT_Q5_K ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
@@ -64,6 +65,32 @@ __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 
 // into rows of 212 bytes (4-byte aligned blocks, conflict-free row-per-thread reads).
 __host__ __device__ constexpr int raw_tile_bytes(int fmt) { return (128 * raw_pitch(fmt) + 1023) & ~1023; }
 constexpr int PF_THREADS = 23 * 32;  // warps 0-15 dequant | 16 activation TMA | 17 MMA issue, TMEM | 18 packed-weight TMA | 19-22 epilogue
+
+// Bounded wait of the pipeline roles.  The fast path is one try_wait; only the slow path looks at the CTA's dead flag
+// (set by whichever warp gave up first), so a healthy pipeline never pays for the check.
+__device__ __noinline__ bool pf_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* dead) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*dead || global_timer_ns() - t0 > 2000000000ull) return false;
+        __nanosleep(40);
+    }
+}
+__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity, volatile uint32_t* dead) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return pf_wait_slow(bar, parity, dead);
+}
+// Records why a role gave up (first failure only) and marks the CTA dead.
+__device__ __noinline__ void pf_fail(volatile uint32_t* dead, unsigned int* status, unsigned int code) {
+    if (!*dead) atomicOr(status, code);
+    *dead = 1;
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -110,6 +137,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset between 8-row groups
     d |= (uint64_t)1 << 46;             // descriptor version of this architecture
     d |= (uint64_t)2 << 61;             // layout type: 128-byte swizzle
+    return d;
+}
+// The same descriptor from its low word ((addr >> 4) | 1 << 16; advancing K by 16 elements adds 2) and the constant
+// high word, without 64-bit arithmetic in the issuing thread.
+__device__ __forceinline__ uint64_t smem_desc_sw128_lo(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"((1024u >> 4) | (1u << 14) | (2u << 29)));
     return d;
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -308,7 +342,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.nsa; ++s) {
+        for (uint32_t s = 0; s < PF_NSA; ++s) {
             mbar_init(bar_full_a + 8 * s, 8);  // one arrival per warp of the set that wrote the tile (to tensor memory)
             mbar_init(bar_empty_a + 8 * s, 1);
         }
@@ -341,10 +375,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
                 const uint32_t n0 = (tile % p.ntn) * 128;
                 for (uint32_t j = 0; j < nraw; ++j) {
-                    if (*dead_flag) break;
-                    if (!mbar_wait(bar_empty_raw + 8 * s, par ^ 1)) {
-                        *dead_flag = 1;
-                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    if (!pf_wait(bar_empty_raw + 8 * s, par ^ 1, dead_flag)) {
+                        pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                         break;
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
@@ -362,10 +394,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
                 const uint32_t m0 = (tile / p.ntn) * p.mt;
                 for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                    if (*dead_flag) break;
-                    if (!mbar_wait(bar_empty_b + 8 * s, par ^ 1)) {
-                        *dead_flag = 1;
-                        atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
+                    if (!pf_wait(bar_empty_b + 8 * s, par ^ 1, dead_flag)) {
+                        pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                         break;
                     }
                     mbar_expect_tx(bar_full_b + 8 * s, b_tile_bytes);
@@ -379,34 +409,33 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
+            const uint32_t a_tm0 = tmem_acc + a_col0, b_lo0 = ((b_tiles >> 4) & 0x3FFFu) | (1u << 16), b_lo_step = b_tile_bytes >> 4;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
                 const uint32_t acc = it % nacc, u = it / nacc;
                 // the accumulator must have been drained by the epilogue of its previous use
-                if (u > 0 && (*dead_flag || !mbar_wait(bar_acc_empty + 8 * acc, (u - 1) & 1))) {
-                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    *dead_flag = 1;
+                if (u > 0 && !pf_wait(bar_acc_empty + 8 * acc, (u - 1) & 1, dead_flag)) {
+                    pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
                 for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                    if (*dead_flag || !mbar_wait(bar_full_a + 8 * sa, para) || !mbar_wait(bar_full_b + 8 * sb, parb)) {
-                        if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                        *dead_flag = 1;
+                    if (!pf_wait(bar_full_a + 8 * sa, para, dead_flag) || !pf_wait(bar_full_b + 8 * sb, parb, dead_flag)) {
+                        pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_tm = tmem_acc + a_col0 + 32 * sa, b_addr = b_tiles + sb * b_tile_bytes;
+                    const uint32_t a_tm = a_tm0 + 32 * sa, b_lo = b_lo0 + sb * b_lo_step;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128(b_addr + 32 * k), p.idesc, (kt | k) != 0);
+                        tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128_lo(b_lo + 2 * k), p.idesc, (kt | k) != 0);
                     // both tiles may be overwritten once these MMAs have read them
                     tc_commit(bar_empty_a + 8 * sa);
                     tc_commit(bar_empty_b + 8 * sb);
-                    if (++sa == p.nsa) { sa = 0; para ^= 1; }
+                    if (++sa == PF_NSA) { sa = 0; para ^= 1; }
                     if (++sb == p.nsb) { sb = 0; parb ^= 1; }
                 }
                 if (ok) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
@@ -422,9 +451,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
             const uint32_t acc = it % nacc, u = it / nacc;
             const uint32_t n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt;
-            if (*dead_flag || !mbar_wait(bar_acc_full + 8 * acc, u & 1)) {
-                if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_MMA);
-                *dead_flag = 1;
+            if (!pf_wait(bar_acc_full + 8 * acc, u & 1, dead_flag)) {
+                pf_fail(dead_flag, p.status, STATUS_TIMEOUT_MMA);
                 ok = false;
                 break;
             }
@@ -467,9 +495,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 const uint32_t c = next_copy, tc = blockIdx.x + (c / nraw) * gridDim.x, jc = c % nraw;
                 if (tc >= p.ntiles) continue;
                 const uint32_t cs = c & 1;
-                if (ok && (*dead_flag || !mbar_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1))) {
-                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    *dead_flag = 1;
+                if (ok && !pf_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1, dead_flag)) {
+                    pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
                 if (ok) {
@@ -509,9 +536,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 if constexpr (RAW_TMA) {
                     const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
                     if constexpr (COOP) copy_upto(jr + 1);
-                    if (ok && (*dead_flag || !mbar_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1))) {
-                        if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_FULL);
-                        *dead_flag = 1;
+                    if (ok && !pf_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1, dead_flag)) {
+                        pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                     }
                     const uint8_t* rrow = smem + 1024 + rs * RAW_TILE_BYTES + r * RAW_PITCH;
@@ -550,10 +576,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = 0;
                 const uint32_t gk = it * p.nkt + kt;  // position in the stream of K steps the MMA warp consumes
-                const uint32_t s = gk % p.nsa, par = (gk / p.nsa) & 1;
-                if (ok && (*dead_flag || !mbar_wait(bar_empty_a + 8 * s, par ^ 1))) {
-                    if (!*dead_flag) atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
-                    *dead_flag = 1;
+                const uint32_t s = gk % PF_NSA, par = (gk / PF_NSA) & 1;
+                if (ok && !pf_wait(bar_empty_a + 8 * s, par ^ 1, dead_flag)) {
+                    pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
                 // the thread's 32 bf16 go to its own lane (= weight row) of the stage's tensor-memory tile: columns
@@ -710,12 +735,10 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     const uint32_t raw_bytes = raw ? 2u * (uint32_t)raw_tile_bytes(fmt) : 0u;
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
-    uint32_t nsa = 8;  // decoded weight tiles live in tensor memory: 8 x 32 columns
     uint32_t nsb = budget / b_tile;
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
-    if (nsa > p.nkt) nsa = p.nkt;
     if (nsb > p.nkt) nsb = p.nkt;
-    p.nsa = nsa;
+    p.nsa = PF_NSA;
     p.nsb = nsb;
     p.ntn = (uint32_t)((N + 127) / 128);
     p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
