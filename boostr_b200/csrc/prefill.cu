@@ -97,6 +97,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  "l"(map), "r"(x), "r"(y), "r"(bar)
                  : "memory");
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -325,7 +335,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle, so that the compiler treats the role branches (and what the roles compute
+    // from kernel parameters) as warp-uniform
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B;
     const uint32_t bar_empty_a = sbase + PF_OFF_EMPTY_A, bar_empty_b = sbase + PF_OFF_EMPTY_B;
@@ -406,8 +418,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             }
         }
     } else if (warp == 17) {
-        // ------------------------------------------------------------ MMA issue (one thread)
-        if (lane == 0) {
+        // ------------------------------------------------------------ MMA issue
+        // The whole warp runs the loop and the waits, so that the stage counters and addresses are warp-uniform
+        // values; one elected lane issues the MMAs and the commits.
+        {
             uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
             const uint32_t a_tm0 = tmem_acc + a_col0, b_lo0 = ((b_tiles >> 4) & 0x3FFFu) | (1u << 16), b_lo_step = b_tile_bytes >> 4;
             bool ok = true;
@@ -415,7 +429,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 const uint32_t acc = it % nacc, u = it / nacc;
                 // the accumulator must have been drained by the epilogue of its previous use
                 if (u > 0 && !pf_wait(bar_acc_empty + 8 * acc, (u - 1) & 1, dead_flag)) {
-                    pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
+                    if (lane == 0) pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                     break;
                 }
@@ -423,22 +437,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
                 for (uint32_t kt = 0; kt < p.nkt; ++kt) {
                     if (!pf_wait(bar_full_a + 8 * sa, para, dead_flag) || !pf_wait(bar_full_b + 8 * sb, parb, dead_flag)) {
-                        pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
+                        if (lane == 0) pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     const uint32_t a_tm = a_tm0 + 32 * sa, b_lo = b_lo0 + sb * b_lo_step;
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128_lo(b_lo + 2 * k), p.idesc, (kt | k) != 0);
-                    // both tiles may be overwritten once these MMAs have read them
-                    tc_commit(bar_empty_a + 8 * sa);
-                    tc_commit(bar_empty_b + 8 * sb);
+                        for (int k = 0; k < BK / 16; ++k)
+                            tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128_lo(b_lo + 2 * k), p.idesc, (kt | k) != 0);
+                        // both tiles may be overwritten once these MMAs have read them
+                        tc_commit(bar_empty_a + 8 * sa);
+                        tc_commit(bar_empty_b + 8 * sb);
+                    }
+                    __syncwarp();
                     if (++sa == PF_NSA) { sa = 0; para ^= 1; }
                     if (++sb == p.nsb) { sb = 0; parb ^= 1; }
                 }
-                if (ok) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
+                if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
+                __syncwarp();
             }
         }
     } else if (warp >= 19) {
