@@ -11,10 +11,10 @@
 //     stored with n contiguous across lanes) while the MMA warp already accumulates tile i + 1;
 //   * activations are bf16 [M,K] (prepared once per call) and arrive by TMA (cp.async.bulk.tensor.2d,
 //     128-byte swizzle, no multicast) into their own ring;
-//   * two sets of eight dequant warps take the even and the odd K steps (64 wide); within a set two
-//     threads share a weight row, 32 elements each: they decode the packed blocks exactly in f32 (the
-//     same expressions as the dequant kernel), round once to bf16 and store into the K-major,
-//     128B-swizzled A tile of the step;
+//   * four sets of four dequant warps take the K steps (64 wide) in turn; a thread owns a weight row and
+//     decodes its 64 elements exactly in f32 (the dequant kernel's values: a byte permute and one FMA per
+//     element), rounds once to bf16 and stores them into its lane of the step's tile in tensor memory,
+//     from where the MMA reads its A operand;
 //   * Q4_K: the packed blocks themselves arrive by TMA as tiles of 128 rows x one 144-byte block (four
 //     K steps), double buffered, and are read from shared memory with conflict-free 16-byte loads
 //     (per-thread 16-byte global loads touch 32 lines per warp instruction; they kept the L1 data pipe
@@ -139,6 +139,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     uint64_t d = 0;
@@ -180,52 +191,34 @@ __device__ __forceinline__ float byte_to_float(uint32_t x) {
     return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650 | I)) - 8388608.0f;
 }
 
-// Raw bytes a thread needs for 32 elements of a Q4_K row.
-struct RawQ4K {
-    uint4 hd, q0, q1;
-};
-__device__ __forceinline__ RawQ4K load_raw_q4k_smem(const uint8_t* blk, uint32_t kt) {
-    RawQ4K r;
-    r.hd = *reinterpret_cast<const uint4*>(blk);
-    r.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (kt & 3));
-    r.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (kt & 3));
-    return r;
-}
-// Elements [64*kt + 32*half, +32) of a Q4_K row: sub-block 2*(kt&3) + half (low / high nibbles of the
-// same 32 bytes).  The expressions are those of the dequant kernel: RNE bf16 of the exact weight.
-__device__ __forceinline__ void decode32_q4k(const RawQ4K& r, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
-    const uint32_t jj = kt & 3;
-    const uint4 hd = r.hd;
-    const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
-    uint32_t sc, mn;
-    if (jj < 2) {
-        sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
-        mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
-    } else {
-        const uint32_t sh = 16 * (jj - 2);
-        sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
-        mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
-    }
-    const float dl = d * (float)((sc >> (8 * half)) & 0xFF);
-    const float nml = -(dmin * (float)((mn >> (8 * half)) & 0xFF));
-    const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t q = (w[i] >> (4 * half)) & 0x0F0F0F0Fu;
-        // dl * q is exact (17 x 4 bits), so the fused form rounds once exactly like multiply-then-subtract
-        o[2 * i] = pack_bf16(fmaf(dl, byte_to_float<0>(q), nml), fmaf(dl, byte_to_float<1>(q), nml));
-        o[2 * i + 1] = pack_bf16(fmaf(dl, byte_to_float<2>(q), nml), fmaf(dl, byte_to_float<3>(q), nml));
-    }
+// Q4_0, Q8_0 and Q6_K weights, w = s * (c - z) with an integer code c and zero point z, cost a byte permute and ONE
+// fused multiply-add each.  Byte I of x (a code c < 128) is placed in bits 16..23 of the float 2.0, which then reads
+// 2 + c / 64, and w = fma(64 s, 2 + c / 64, -(128 + z) s): the product is exact and so is the constant (s has at most
+// 18 significant bits), so the result is s * (c - z) exactly.  code_low() places codes up to 255 one byte lower
+// (2 + c / 16384) for Q8_0.  Q4_K / Q5_K (w = s * c + t with unrelated s and t) cannot use it: t - 128 s is not exact
+// in general, and a per-row test for exactness diverges within a warp and costs more than it saves (measured).
+template <int I>
+__device__ __forceinline__ float code_mid(uint32_t x) { return __uint_as_float(__byte_perm(x, 0x40000000u, 0x7044 | (I << 8))); }  // 2 + c / 64
+template <int I>
+__device__ __forceinline__ float code_low(uint32_t x) { return __uint_as_float(__byte_perm(x, 0x40000000u, 0x7404 | (I << 4))); }  // 2 + c / 16384
+template <bool SM>
+__device__ __forceinline__ uint32_t ld16(const uint8_t* p) { return SM ? (uint32_t)*reinterpret_cast<const unsigned short*>(p) : g16(p); }
+template <bool SM>
+__device__ __forceinline__ uint32_t ld32(const uint8_t* p) {  // 4 bytes at a 2-byte-aligned address
+    if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return SM ? *reinterpret_cast<const uint32_t*>(p) : __ldg(reinterpret_cast<const uint32_t*>(p));
+    return ld16<SM>(p) | (ld16<SM>(p + 2) << 16);
 }
 
-// Elements [64*kt + 32*half, +32) of a Q5_K row in the element order of the reference's x86-64 dot product
-// (src/quant/cpu/kernels/simd/fused_q5k_q8k_dot.rs:27-122): Q4_K's nibble order, the nibbles 32 bytes further into the
-// block, plus bit (e % 8) of qh[e / 8] for element e: the 32 elements take the 32 bits of one word of qh.
-__device__ __forceinline__ void decode32_q5k(const uint8_t* blk, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
-    const uint32_t jj = kt & 3;
+// The 64 elements of K step jj (0..3) of a Q4_K / Q5_K block in shared memory: sub-blocks 2 jj (low nibbles) and
+// 2 jj + 1 (high nibbles) of the same 32 bytes.  RNE bf16 of the exact f32 weight d * sc * q - dmin * m, the value
+// the dequant kernel writes.  Q5_K in the element order of the reference's x86-64 dot product
+// (src/quant/cpu/kernels/simd/fused_q5k_q8k_dot.rs:27-122): Q4_K's nibble order, the nibbles 32 bytes further into
+// the block, plus bit (e % 8) of qh[e / 8] for element e, so sub-block j takes one 32-bit word of qh.
+template <bool Q5>
+__device__ __forceinline__ void decode64_q45k(const uint8_t* blk, uint32_t jj, uint32_t (&o)[32]) {
     const uint4 hd = *reinterpret_cast<const uint4*>(blk);
     const float d = f16bits_to_f32(hd.x & 0xFFFF), dmin = f16bits_to_f32(hd.x >> 16);
-    uint32_t sc, mn;
+    uint32_t sc, mn;  // byte 0: sub-block 2 jj, byte 1: sub-block 2 jj + 1
     if (jj < 2) {
         sc = (hd.y >> (16 * jj)) & 0x3F3Fu;
         mn = (hd.z >> (16 * jj)) & 0x3F3Fu;
@@ -234,86 +227,98 @@ __device__ __forceinline__ void decode32_q5k(const uint8_t* blk, uint32_t kt, ui
         sc = ((hd.w >> sh) & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
         mn = (((hd.w >> sh) >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
     }
-    const float dl = d * (float)((sc >> (8 * half)) & 0xFF);
-    const float nml = -(dmin * (float)((mn >> (8 * half)) & 0xFF));
-    const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 48 + 32 * jj), q1 = *reinterpret_cast<const uint4*>(blk + 64 + 32 * jj);
-    const uint32_t hbits = *reinterpret_cast<const uint32_t*>(blk + 16 + 8 * jj + 4 * half);
+    constexpr uint32_t QOFF = Q5 ? 48 : 16;
+    const uint4 q0 = *reinterpret_cast<const uint4*>(blk + QOFF + 32 * jj), q1 = *reinterpret_cast<const uint4*>(blk + QOFF + 16 + 32 * jj);
+    uint2 hb = make_uint2(0, 0);
+    if constexpr (Q5) hb = *reinterpret_cast<const uint2*>(blk + 16 + 8 * jj);
     const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        // word i holds elements 4i .. 4i + 3; their high bits are bits 4i .. 4i + 3 of hbits
-        const uint32_t q = ((w[i] >> (4 * half)) & 0x0F0F0F0Fu) | ((((hbits >> (4 * i)) & 15u) * 0x02040810u) & 0x10101010u);
-        o[2 * i] = pack_bf16(fmaf(dl, byte_to_float<0>(q), nml), fmaf(dl, byte_to_float<1>(q), nml));
-        o[2 * i + 1] = pack_bf16(fmaf(dl, byte_to_float<2>(q), nml), fmaf(dl, byte_to_float<3>(q), nml));
+    for (int h = 0; h < 2; ++h) {
+        const float dl = d * byte_to_float<0>(sc >> (8 * h)), nml = -(dmin * byte_to_float<0>(mn >> (8 * h)));
+        const uint32_t hbits = h ? hb.y : hb.x;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t q = (w[i] >> (4 * h)) & 0x0F0F0F0Fu;
+            // word i holds elements 4i .. 4i + 3; their fifth bits are bits 4i .. 4i + 3 of hbits
+            if constexpr (Q5) q |= (((hbits >> (4 * i)) & 15u) * 0x02040810u) & 0x10101010u;
+            // dl * q is exact (17 x 5 bits), so the fused form rounds once exactly like multiply-then-subtract
+            o[16 * h + 2 * i] = pack_bf16(fmaf(dl, byte_to_float<0>(q), nml), fmaf(dl, byte_to_float<1>(q), nml));
+            o[16 * h + 2 * i + 1] = pack_bf16(fmaf(dl, byte_to_float<2>(q), nml), fmaf(dl, byte_to_float<3>(q), nml));
+        }
     }
 }
 
 // One 32-element Q8_0 / Q4_0 block (2-byte aligned) as 32 bf16.  SM: the block sits in shared memory.
+// Q8_0: w = d * (u - 128) with u = q + 128 placed by code_low(): fma(16384 d, 2 + u / 16384, -32896 d);
+// Q4_0: w = d * (q - 8): fma(64 d, 2 + q / 64, -136 d).  Both constants are exact (d has 11 significant bits).
 template <int FMT, bool SM>
-__device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t (&o)[16]) {
-    auto l16 = [&](const uint8_t* p) -> uint32_t { return SM ? (uint32_t)*reinterpret_cast<const unsigned short*>(p) : g16(p); };
-    auto l32 = [&](const uint8_t* p) -> uint32_t {
-        if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return SM ? *reinterpret_cast<const uint32_t*>(p) : __ldg(reinterpret_cast<const uint32_t*>(p));
-        return l16(p) | (l16(p + 2) << 16);
-    };
-    const float d = f16bits_to_f32(l16(blk));
+__device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t* o) {
+    const float d = f16bits_to_f32(ld16<SM>(blk));
     if constexpr (FMT == FMT_Q8_0) {
+        const float a = 16384.0f * d, c = -32896.0f * d;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t x = l32(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
-            o[2 * i] = pack_bf16((byte_to_float<0>(x) - 128.0f) * d, (byte_to_float<1>(x) - 128.0f) * d);
-            o[2 * i + 1] = pack_bf16((byte_to_float<2>(x) - 128.0f) * d, (byte_to_float<3>(x) - 128.0f) * d);
+            const uint32_t x = ld32<SM>(blk + 2 + 4 * i) ^ 0x80808080u;  // q + 128
+            o[2 * i] = pack_bf16(fmaf(a, code_low<0>(x), c), fmaf(a, code_low<1>(x), c));
+            o[2 * i + 1] = pack_bf16(fmaf(a, code_low<2>(x), c), fmaf(a, code_low<3>(x), c));
         }
     } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
+        const float a = 64.0f * d, c = -136.0f * d;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t x = l32(blk + 2 + 4 * i);
+            const uint32_t x = ld32<SM>(blk + 2 + 4 * i);
             const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-            o[4 * i] = pack_bf16((byte_to_float<0>(lo) - 8.0f) * d, (byte_to_float<0>(hi) - 8.0f) * d);
-            o[4 * i + 1] = pack_bf16((byte_to_float<1>(lo) - 8.0f) * d, (byte_to_float<1>(hi) - 8.0f) * d);
-            o[4 * i + 2] = pack_bf16((byte_to_float<2>(lo) - 8.0f) * d, (byte_to_float<2>(hi) - 8.0f) * d);
-            o[4 * i + 3] = pack_bf16((byte_to_float<3>(lo) - 8.0f) * d, (byte_to_float<3>(hi) - 8.0f) * d);
+            o[4 * i] = pack_bf16(fmaf(a, code_mid<0>(lo), c), fmaf(a, code_mid<0>(hi), c));
+            o[4 * i + 1] = pack_bf16(fmaf(a, code_mid<1>(lo), c), fmaf(a, code_mid<1>(hi), c));
+            o[4 * i + 2] = pack_bf16(fmaf(a, code_mid<2>(lo), c), fmaf(a, code_mid<2>(hi), c));
+            o[4 * i + 3] = pack_bf16(fmaf(a, code_mid<3>(lo), c), fmaf(a, code_mid<3>(hi), c));
         }
     }
 }
 
-// 32 elements of the Q6_K block at `blk`: K step kt of the block's four, half `half`.
-// SM: the block sits 4-byte aligned in shared memory; otherwise 2-byte aligned in global memory.
+// The 64 elements of K step jt (0..3) of the Q6_K block at `blk`: elements 128 n + 32 g + l, n = jt / 2,
+// g = 2 (jt & 1) + {0, 1}.  w = (d * sc) * (q - 32) = fma(64 s, 2 + q / 64, -160 s) with s = d * sc (18 significant
+// bits, so -160 s is exact).  SM: the block sits 4-byte aligned in shared memory; otherwise 2-byte aligned in global.
 template <bool SM>
-__device__ __forceinline__ void decode32_q6k(const uint8_t* blk, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
-    auto l8 = [&](const uint8_t* p) -> int { return SM ? (int)(signed char)*p : (int)(signed char)__ldg(p); };
-    auto l32 = [&](const uint8_t* p) -> uint32_t { return SM ? *reinterpret_cast<const uint32_t*>(p) : g32(p); };
-    const uint32_t jt = kt & 3, n = jt >> 1, g0 = (jt & 1) * 2;  // elements 128n + 32*(g0 + half) + l
-    const float d = f16bits_to_f32(SM ? (uint32_t)*reinterpret_cast<const unsigned short*>(blk + 208) : g16(blk + 208));
-    const uint32_t gq = g0 + half;
-    const uint8_t* ql = blk + 64 * n + 32 * half;  // gq & 1 == half
+__device__ __forceinline__ void decode64_q6k(const uint8_t* blk, uint32_t jt, uint32_t (&o)[32]) {
+    const uint32_t n = jt >> 1, g0 = (jt & 1) * 2;
+    const float d = f16bits_to_f32(ld16<SM>(blk + 208));
     const uint8_t* qh = blk + 128 + 32 * n;
-    const float s0 = d * (float)l8(blk + 192 + 8 * n + 2 * gq);
-    const float s1 = d * (float)l8(blk + 192 + 8 * n + 2 * gq + 1);
+    const uint32_t scw = ld16<SM>(blk + 192 + 8 * n + 2 * g0) | (ld16<SM>(blk + 192 + 8 * n + 2 * g0 + 2) << 16);  // four int8 scales
+    uint32_t hw[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t lw = l32(ql + 4 * i), hw = l32(qh + 4 * i);
-        const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
-        const uint32_t q = nib | (((hw >> (2 * gq)) & 0x03030303u) << 4);
-        const float s = i < 4 ? s0 : s1;
-        o[2 * i] = pack_bf16(s * (byte_to_float<0>(q) - 32.0f), s * (byte_to_float<1>(q) - 32.0f));
-        o[2 * i + 1] = pack_bf16(s * (byte_to_float<2>(q) - 32.0f), s * (byte_to_float<3>(q) - 32.0f));
+    for (int i = 0; i < 8; ++i) hw[i] = ld32<SM>(qh + 4 * i);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t gq = g0 + h;
+        const uint8_t* ql = blk + 64 * n + 32 * h;  // gq & 1 == h
+        const float s0 = d * (float)(int)(signed char)(scw >> (16 * h)), s1 = d * (float)(int)(signed char)(scw >> (16 * h + 8));
+        const float a0 = 64.0f * s0, c0 = -160.0f * s0, a1 = 64.0f * s1, c1 = -160.0f * s1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lw = ld32<SM>(ql + 4 * i);
+            const uint32_t nib = (g0 ? (lw >> 4) : lw) & 0x0F0F0F0Fu;
+            const uint32_t q = nib | (((hw[i] >> (2 * gq)) & 0x03030303u) << 4);
+            const float a = i < 4 ? a0 : a1, c = i < 4 ? c0 : c1;
+            o[16 * h + 2 * i] = pack_bf16(fmaf(a, code_mid<0>(q), c), fmaf(a, code_mid<1>(q), c));
+            o[16 * h + 2 * i + 1] = pack_bf16(fmaf(a, code_mid<2>(q), c), fmaf(a, code_mid<3>(q), c));
+        }
     }
 }
 
-// Elements [64*kt + 32*half, +32) of one weight row as 32 bf16 (16 packed words), other formats.
+// Elements [64 kt, 64 kt + 64) of one weight row in global memory as 64 bf16 (rows whose packed tiles are not staged).
 template <int FMT>
-__device__ __forceinline__ void decode32(const uint8_t* row, uint32_t kt, uint32_t half, uint32_t (&o)[16]) {
+__device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt, uint32_t (&o)[32]) {
     if constexpr (FMT == FMT_Q6_K) {
-        decode32_q6k<false>(row + (kt >> 2) * 210, kt, half, o);
+        decode64_q6k<false>(row + (kt >> 2) * 210, kt & 3, o);
     } else if constexpr (FMT == FMT_Q5_K || FMT == FMT_Q4_K) {
         // never taken: K-quant rows are whole 256-element blocks, which are always staged in shared memory
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = 0;
-    } else if constexpr (FMT == FMT_Q8_0) {
-        decode32_blk<FMT_Q8_0, false>(row + (2 * kt + half) * 34, o);
+        for (int i = 0; i < 32; ++i) o[i] = 0;
     } else {
-        decode32_blk<FMT_Q4_0, false>(row + (2 * kt + half) * 18, o);
+        constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
+        decode32_blk<FMT, false>(row + (2 * kt) * BB, o);
+        decode32_blk<FMT, false>(row + (2 * kt + 1) * BB, o + 16);
     }
 }
 
@@ -355,7 +360,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < PF_NSA; ++s) {
-            mbar_init(bar_full_a + 8 * s, 8);  // one arrival per warp of the set that wrote the tile (to tensor memory)
+            mbar_init(bar_full_a + 8 * s, 4);  // one arrival per warp of the set that wrote the tile (to tensor memory)
             mbar_init(bar_empty_a + 8 * s, 1);
         }
         for (uint32_t s = 0; s < p.nsb; ++s) {
@@ -500,9 +505,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         }
     } else {
         // ------------------------------------------------------------ dequant warps
-        // thread (set, half, r): weight row r of the tile, elements [32*half, 32*half+32) of the K steps
-        // kt = set, set + 2, ... of every tile
-        const uint32_t r = threadIdx.x & 127, half = (threadIdx.x >> 7) & 1, set = threadIdx.x >> 8;
+        // thread (set, r): weight row r of the tile, all 64 elements of the K steps kt = set, set + 4, ... of every
+        // tile: four sets of four warps, each taking one K step of every packed tile (one 256-element block per row)
+        const uint32_t r = threadIdx.x & 127, set = threadIdx.x >> 7;
         bool ok = true;
         uint32_t it = 0;
         // COOP: packed tile c (counted over all output tiles of this CTA) is copied by all 16 dequant warps, 8 rows
@@ -549,8 +554,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             const uint32_t n0 = (tile % p.ntn) * 128;
             const bool row_ok = n0 + r < p.N;
             const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
-            for (uint32_t kt = set; kt < p.nkt; kt += 2) {
-                uint32_t o[16];
+            for (uint32_t kt = set; kt < p.nkt; kt += 4) {
+                uint32_t o[32];
                 if constexpr (RAW_TMA) {
                     const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
                     if constexpr (COOP) copy_upto(jr + 1);
@@ -559,49 +564,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         ok = false;
                     }
                     const uint8_t* rrow = smem + 1024 + rs * RAW_TILE_BYTES + r * RAW_PITCH;
-                    if constexpr (FMT == FMT_Q4_K) {
-                        RawQ4K cur{};
-                        if (ok) cur = load_raw_q4k_smem(rrow, kt);
-                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {  // this set's last step in the tile: release it
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
-                        }
-                        decode32_q4k(cur, kt, half, o);
-                    } else if constexpr (FMT == FMT_Q5_K) {
-                        if (ok) decode32_q5k(rrow, kt, half, o);
-                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
-                        }
-                    } else if constexpr (FMT == FMT_Q6_K) {
-                        if (ok) decode32_q6k<true>(rrow, kt, half, o);
-                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
-                        }
-                    } else {
-                        constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
-                        if (ok) decode32_blk<FMT, true>(rrow + (2 * (kt & 3) + half) * BB, o);
-                        if (kt + 2 >= p.nkt || ((kt + 2) >> 2) != (kt >> 2)) {
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                    if (ok) {
+                        if constexpr (FMT == FMT_Q4_K) decode64_q45k<false>(rrow, set, o);
+                        else if constexpr (FMT == FMT_Q5_K) decode64_q45k<true>(rrow, set, o);
+                        else if constexpr (FMT == FMT_Q6_K) decode64_q6k<true>(rrow, set, o);
+                        else {
+                            constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
+                            decode32_blk<FMT, true>(rrow + (2 * set) * BB, o);
+                            decode32_blk<FMT, true>(rrow + (2 * set + 1) * BB, o + 16);
                         }
                     }
+                    // the warp's only K step in this packed tile (kt & 3 == set): release the tile
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                 } else {
-                    decode32<FMT>(wrow, kt, half, o);
+                    decode64_global<FMT>(wrow, kt, o);
                 }
-                if (!row_ok)
+                if (!row_ok || !ok)
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = 0;
+                    for (int i = 0; i < 32; ++i) o[i] = 0;
                 const uint32_t gk = it * p.nkt + kt;  // position in the stream of K steps the MMA warp consumes
                 const uint32_t s = gk % PF_NSA, par = (gk / PF_NSA) & 1;
                 if (ok && !pf_wait(bar_empty_a + 8 * s, par ^ 1, dead_flag)) {
                     pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
-                // the thread's 32 bf16 go to its own lane (= weight row) of the stage's tensor-memory tile: columns
-                // [16 half, 16 half + 16).  Executed by the whole warp (dead warps store what they hold: nobody reads it).
-                tmem_st16(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * s + 16 * half, o);
+                // the thread's 64 bf16 go to its own lane (= weight row) of the stage's tensor-memory tile, 32 columns.
+                // Executed by the whole warp (dead warps store what they hold: nobody reads it).
+                tmem_st32(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * s, o);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
