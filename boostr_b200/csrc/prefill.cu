@@ -47,7 +47,7 @@ struct PrefillParams {
     uint32_t mt;      // activation rows per tile (MMA N): 64, 128 or 256
     uint32_t idesc;   // tcgen05 instruction descriptor
     uint32_t nkt;     // K / 64
-    uint32_t nsa, nsb;  // ring depth of the weight (A) tiles and of the activation (B) tiles
+    uint32_t ns;      // ring depth: stage s = decoded weight tile s in tensor memory + activation tile s in shared memory
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
     int out_dtype;
     unsigned int* status;
@@ -57,7 +57,6 @@ namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 constexpr int PF_MAX_STAGES = 8;
-constexpr uint32_t PF_NSA = 8;  // decoded weight tiles in tensor memory: 8 x 32 columns
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
 __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : fmt == FMT_Q5_K ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
@@ -322,11 +321,9 @@ __device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt,
     }
 }
 
-// dynamic shared memory: [0,1024) barriers + TMEM base; then two packed-weight tiles (Q4_K), nsa A tiles of 16 KB,
-// nsb B tiles of mt*128 B, all 1 KB aligned.  The A and B rings are separate because they hide different latencies:
-// an activation tile is requested from L2 when its slot is released, a weight tile is written by the dequant warps
-// just in time.
-constexpr int PF_OFF_FULL_A = 0, PF_OFF_FULL_B = 64, PF_OFF_EMPTY_A = 128, PF_OFF_EMPTY_B = 192, PF_OFF_ACC_FULL = 256,
+// dynamic shared memory: [0,1024) barriers + TMEM base; then two packed-weight tiles and ns activation tiles of
+// mt*128 B, all 1 KB aligned.  Stage s pairs activation tile s with decoded weight tile s in tensor memory.
+constexpr int PF_OFF_FULL = 0, PF_OFF_EMPTY = 128, PF_OFF_ACC_FULL = 256,
               PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 296, PF_OFF_EMPTY_RAW = 312;
 
 // Persistent: one CTA per SM walks the output tiles t = blockIdx.x, + gridDim.x, ... (consecutive CTAs share an
@@ -344,8 +341,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     // from kernel parameters) as warp-uniform
     const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bar_full_a = sbase + PF_OFF_FULL_A, bar_full_b = sbase + PF_OFF_FULL_B;
-    const uint32_t bar_empty_a = sbase + PF_OFF_EMPTY_A, bar_empty_b = sbase + PF_OFF_EMPTY_B;
+    const uint32_t bar_full = sbase + PF_OFF_FULL, bar_empty = sbase + PF_OFF_EMPTY;
     const uint32_t bar_acc_full = sbase + PF_OFF_ACC_FULL, bar_acc_empty = sbase + PF_OFF_ACC_EMPTY;
     const uint32_t bar_full_raw = sbase + PF_OFF_FULL_RAW, bar_empty_raw = sbase + PF_OFF_EMPTY_RAW;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_TMEM);
@@ -359,13 +355,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < PF_NSA; ++s) {
-            mbar_init(bar_full_a + 8 * s, 4);  // one arrival per warp of the set that wrote the tile (to tensor memory)
-            mbar_init(bar_empty_a + 8 * s, 1);
-        }
-        for (uint32_t s = 0; s < p.nsb; ++s) {
-            mbar_init(bar_full_b + 8 * s, 1);
-            mbar_init(bar_empty_b + 8 * s, 1);
+        for (uint32_t s = 0; s < p.ns; ++s) {
+            // a stage is full when the four warps of a set have written the weight tile (to tensor memory) and the
+            // activation tile's bytes have landed (one more arrival, with the byte count); one wait for the MMA warp
+            mbar_init(bar_full + 8 * s, 5);
+            mbar_init(bar_empty + 8 * s, 1);  // released by the commit behind the stage's MMAs, for both producers
         }
         for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(bar_full_raw + 8 * s, COOP ? 16 : 1);  // COOP: every dequant warp copies its 8 rows
@@ -411,13 +405,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
                 const uint32_t m0 = (tile / p.ntn) * p.mt;
                 for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                    if (!pf_wait(bar_empty_b + 8 * s, par ^ 1, dead_flag)) {
+                    if (!pf_wait(bar_empty + 8 * s, par ^ 1, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                         break;
                     }
-                    mbar_expect_tx(bar_full_b + 8 * s, b_tile_bytes);
-                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full_b + 8 * s);
-                    if (++s == p.nsb) { s = 0; par ^= 1; }
+                    mbar_expect_tx(bar_full + 8 * s, b_tile_bytes);
+                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full + 8 * s);
+                    if (++s == p.ns) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
             }
@@ -427,7 +421,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // The whole warp runs the loop and the waits, so that the stage counters and addresses are warp-uniform
         // values; one elected lane issues the MMAs and the commits.
         {
-            uint32_t sa = 0, para = 0, sb = 0, parb = 0, it = 0;
+            uint32_t sa = 0, para = 0, it = 0;
             const uint32_t a_tm0 = tmem_acc + a_col0, b_lo0 = ((b_tiles >> 4) & 0x3FFFu) | (1u << 16), b_lo_step = b_tile_bytes >> 4;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
@@ -441,24 +435,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
                 for (uint32_t kt = 0; kt < p.nkt; ++kt) {
-                    if (!pf_wait(bar_full_a + 8 * sa, para, dead_flag) || !pf_wait(bar_full_b + 8 * sb, parb, dead_flag)) {
+                    if (!pf_wait(bar_full + 8 * sa, para, dead_flag)) {
                         if (lane == 0) pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_tm = a_tm0 + 32 * sa, b_lo = b_lo0 + sb * b_lo_step;
+                    const uint32_t a_tm = a_tm0 + 32 * sa, b_lo = b_lo0 + sa * b_lo_step;
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
                             tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128_lo(b_lo + 2 * k), p.idesc, (kt | k) != 0);
                         // both tiles may be overwritten once these MMAs have read them
-                        tc_commit(bar_empty_a + 8 * sa);
-                        tc_commit(bar_empty_b + 8 * sb);
+                        tc_commit(bar_empty + 8 * sa);
                     }
                     __syncwarp();
-                    if (++sa == PF_NSA) { sa = 0; para ^= 1; }
-                    if (++sb == p.nsb) { sb = 0; parb ^= 1; }
+                    if (++sa == p.ns) { sa = 0; para ^= 1; }
                 }
                 if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
                 __syncwarp();
@@ -554,6 +546,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             const uint32_t n0 = (tile % p.ntn) * 128;
             const bool row_ok = n0 + r < p.N;
             const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
+            // stage and phase of this set's K steps: position it * nkt + kt in the stream the MMA warp consumes
+            uint32_t s = (it * p.nkt + set) % p.ns, par = ((it * p.nkt + set) / p.ns) & 1;
             for (uint32_t kt = set; kt < p.nkt; kt += 4) {
                 uint32_t o[32];
                 if constexpr (RAW_TMA) {
@@ -583,9 +577,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 if (!row_ok || !ok)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = 0;
-                const uint32_t gk = it * p.nkt + kt;  // position in the stream of K steps the MMA warp consumes
-                const uint32_t s = gk % PF_NSA, par = (gk / PF_NSA) & 1;
-                if (ok && !pf_wait(bar_empty_a + 8 * s, par ^ 1, dead_flag)) {
+                if (ok && !pf_wait(bar_empty + 8 * s, par ^ 1, dead_flag)) {
                     pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
@@ -594,7 +586,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 tmem_st32(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * s, o);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full_a + 8 * s);
+                if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                s += 4;
+                while (s >= p.ns) { s -= p.ns; par ^= 1; }
             }
         }
     }
@@ -744,10 +738,9 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
     uint32_t nsb = budget / b_tile;
-    if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;
+    if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;  // tensor memory: 8 weight tiles of 32 columns
     if (nsb > p.nkt) nsb = p.nkt;
-    p.nsa = PF_NSA;
-    p.nsb = nsb;
+    p.ns = nsb;
     p.ntn = (uint32_t)((N + 127) / 128);
     p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
     p.out_dtype = out_dtype;
