@@ -35,7 +35,7 @@ bool gemv_m1_f32_supported(int fmt, size_t M, size_t K, size_t N);
 cudaError_t launch_gemv_m1_f32(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
                                size_t N, int sm_count, cudaStream_t st, unsigned int* status);
 bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
-size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N);
+size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N, int sm_count);
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                            size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
                            unsigned int* status, bool* ws_too_small, char* err, size_t err_len);
@@ -150,7 +150,7 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
     if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
     const bool swiglu = op == B200Q_OP_QUANT_SWIGLU;
     if (prefill_supported(format, M, K, N)) {
-        size_t a = prefill_workspace_bytes(format, act_dtype, M, K, N);
+        size_t a = prefill_workspace_bytes(format, act_dtype, M, K, N, sm_count_current());
         // large-M SwiGLU = two prefill GEMMs into scratch, then the gate
         if (swiglu) a += 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255);
         return a;

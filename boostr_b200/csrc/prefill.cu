@@ -49,6 +49,13 @@ struct PrefillParams {
     uint32_t nkt;     // K / 64
     uint32_t ns;      // ring depth: stage s = decoded weight tile s in tensor memory + activation tile s in shared memory
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
+    // Work distribution.  Tiles [0, nfull) are dealt whole, round-robin (nfull is a multiple of the grid).  The
+    // remaining ntail tiles (fewer than one per CTA) are, when `split`, cut along K: their ntail * gpt granules of
+    // `gran` K steps are shared evenly, CTA c taking granules [c Q / G, (c + 1) Q / G), which touches at most two
+    // tiles; a piece that is not a whole tile is written as an f32 partial tile into `part` (pieces numbered in K order) and
+    // prefill_reduce_kernel adds the pieces of each tile in K order.
+    uint32_t nfull, ntail, split, gran, gpt;
+    float* part;
     int out_dtype;
     unsigned int* status;
 };
@@ -326,9 +333,47 @@ __device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt,
 constexpr int PF_OFF_FULL = 0, PF_OFF_EMPTY = 128, PF_OFF_ACC_FULL = 256,
               PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 296, PF_OFF_EMPTY_RAW = 312;
 
-// Persistent: one CTA per SM walks the output tiles t = blockIdx.x, + gridDim.x, ... (consecutive CTAs share an
-// activation tile, which therefore stays in L2).  Tensor memory holds TWO accumulators, so the four epilogue warps
-// drain tile i while the MMA warp is already accumulating tile i + 1 and the rings never run dry between tiles.
+// One piece of work of a CTA: K steps [k0, k0 + nk) of output tile `tile`; slot < 0: the whole tile, written to the
+// output; otherwise a partial tile for the reduce kernel.
+struct PfUnit {
+    uint32_t tile, k0, nk;
+    int slot;
+};
+// The it-th unit of this CTA (every role walks the same list).
+__device__ __forceinline__ bool pf_unit(const PrefillParams& p, uint32_t it, PfUnit& u) {
+    const uint32_t t = blockIdx.x + it * gridDim.x;
+    if (t < p.nfull) {
+        u.tile = t; u.k0 = 0; u.nk = p.nkt; u.slot = -1;
+        return true;
+    }
+    const uint32_t j = it - p.nfull / gridDim.x;  // 0 or 1: piece of the tail
+    if (!p.split) {
+        if (j != 0 || blockIdx.x >= p.ntail) return false;
+        u.tile = p.nfull + blockIdx.x; u.k0 = 0; u.nk = p.nkt; u.slot = -1;
+        return true;
+    }
+    if (j > 1) return false;
+    const uint32_t Q = p.ntail * p.gpt;
+    const uint32_t a = (blockIdx.x * Q) / gridDim.x, b = ((blockIdx.x + 1) * Q) / gridDim.x;  // G * Q < 2^32 (checked by the launcher)
+    if (a >= b) return false;
+    const uint32_t t0 = a / p.gpt, e0 = min(b, (t0 + 1) * p.gpt);
+    uint32_t lo, hi, tt;
+    if (j == 0) { lo = a; hi = e0; tt = t0; }
+    else {
+        if (e0 >= b) return false;
+        lo = e0; hi = b; tt = t0 + 1;
+    }
+    u.tile = p.nfull + tt;
+    u.k0 = (lo - tt * p.gpt) * p.gran;
+    u.nk = min((hi - lo) * p.gran, p.nkt - u.k0);
+    // pieces in K order: one more at every CTA boundary and at every tile boundary (CTAs without work do not count)
+    u.slot = (u.k0 == 0 && u.nk == p.nkt) ? -1 : (int)(min(blockIdx.x, a) + tt);
+    return true;
+}
+
+// Persistent: one CTA per SM walks its work units (consecutive CTAs share an activation tile, which therefore stays
+// in L2).  Tensor memory holds TWO accumulators while they fit, so the four epilogue warps drain unit i while the MMA
+// warp is already accumulating unit i + 1 and the rings never run dry between units.
 template <int FMT, bool RAW_TMA>  // RAW_TMA: packed weights staged in shared memory by TMA (rows a multiple of 16 bytes)
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
@@ -350,9 +395,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;
     const uint32_t raw_tiles = sbase + 1024, b_tiles = raw_tiles + raw_bytes;
     // Tensor memory (all 512 columns): nacc accumulators of mt columns (two while they fit beside the weight stages,
-    // one at mt = 256), then nsa decoded weight tiles of 32 columns (128 rows x 64 bf16, two per column).
+    // one at mt = 256), then the decoded weight tiles of 32 columns (128 rows x 64 bf16, two per column).
     const uint32_t tmem_cols = 512, nacc = p.mt <= 128 ? 2u : 1u, a_col0 = nacc * p.mt;
-    const uint32_t nraw = (p.nkt + 3) / 4;  // packed tiles per output tile
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.ns; ++s) {
@@ -380,11 +424,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     const uint32_t tmem_acc = *tmem_holder;
 
     if (warp == 18) {
-        // ------------------------------------------------------------ packed weight tiles by TMA (Q4_K)
+        // ------------------------------------------------------------ packed weight tiles by TMA
         if (RAW_TMA && !COOP && lane == 0) {
             uint32_t s = 0, par = 0;
-            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-                const uint32_t n0 = (tile % p.ntn) * 128;
+            PfUnit u;
+            for (uint32_t it = 0; pf_unit(p, it, u); ++it) {
+                const uint32_t n0 = (u.tile % p.ntn) * 128, j0 = u.k0 / 4, nraw = (u.nk + 3) / 4;
                 for (uint32_t j = 0; j < nraw; ++j) {
                     if (!pf_wait(bar_empty_raw + 8 * s, par ^ 1, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
@@ -392,7 +437,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
                     // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
-                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)(j * (FMT == FMT_Q8_0 ? 136 : FMT == FMT_Q5_K ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : FMT == FMT_Q5_K ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
                     if (++s == 2) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -402,15 +447,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             uint32_t s = 0, par = 0;
-            for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-                const uint32_t m0 = (tile / p.ntn) * p.mt;
-                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+            PfUnit u;
+            for (uint32_t it = 0; pf_unit(p, it, u); ++it) {
+                const uint32_t m0 = (u.tile / p.ntn) * p.mt;
+                for (uint32_t kt = 0; kt < u.nk; ++kt) {
                     if (!pf_wait(bar_empty + 8 * s, par ^ 1, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                         break;
                     }
                     mbar_expect_tx(bar_full + 8 * s, b_tile_bytes);
-                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)(kt * BK), (int)m0, bar_full + 8 * s);
+                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)((u.k0 + kt) * BK), (int)m0, bar_full + 8 * s);
                     if (++s == p.ns) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -421,10 +467,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // The whole warp runs the loop and the waits, so that the stage counters and addresses are warp-uniform
         // values; one elected lane issues the MMAs and the commits.
         {
-            uint32_t sa = 0, para = 0, it = 0;
+            uint32_t sa = 0, para = 0;
             const uint32_t a_tm0 = tmem_acc + a_col0, b_lo0 = ((b_tiles >> 4) & 0x3FFFu) | (1u << 16), b_lo_step = b_tile_bytes >> 4;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+            PfUnit un;
+            for (uint32_t it = 0; ok && pf_unit(p, it, un); ++it) {
                 const uint32_t acc = it % nacc, u = it / nacc;
                 // the accumulator must have been drained by the epilogue of its previous use
                 if (u > 0 && !pf_wait(bar_acc_empty + 8 * acc, (u - 1) & 1, dead_flag)) {
@@ -434,7 +481,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
-                for (uint32_t kt = 0; kt < p.nkt; ++kt) {
+                for (uint32_t kt = 0; kt < un.nk; ++kt) {
                     if (!pf_wait(bar_full + 8 * sa, para, dead_flag)) {
                         if (lane == 0) pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
@@ -452,7 +499,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     __syncwarp();
                     if (++sa == p.ns) { sa = 0; para ^= 1; }
                 }
-                if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the tile has completed
+                if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);  // arrives when every MMA of the unit has completed
                 __syncwarp();
             }
         }
@@ -461,11 +508,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // lane r of the accumulator = weight row n0 + r, column c = activation row m0 + c; a warp reaches the
         // 32 lanes of its quarter (warp & 3)
         const uint32_t quarter = (uint32_t)warp & 3, r = quarter * 32 + lane;
-        uint32_t it = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x, ++it) {
+        PfUnit un;
+        for (uint32_t it = 0; ok && pf_unit(p, it, un); ++it) {
             const uint32_t acc = it % nacc, u = it / nacc;
-            const uint32_t n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt;
+            const uint32_t n0 = (un.tile % p.ntn) * 128, m0 = (un.tile / p.ntn) * p.mt;
             if (!pf_wait(bar_acc_full + 8 * acc, u & 1, dead_flag)) {
                 pf_fail(dead_flag, p.status, STATUS_TIMEOUT_MMA);
                 ok = false;
@@ -473,11 +520,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             }
             tc_fence_after();
             const bool row_ok = n0 + r < p.N;
+            float* part = un.slot >= 0 ? p.part + (size_t)un.slot * p.mt * 128 : nullptr;
             for (uint32_t c0 = 0; c0 < p.mt; c0 += 16) {
                 if (m0 + c0 >= p.M) break;  // warp-uniform
                 uint32_t v[16];
                 tmem_ld16(tmem_acc + ((quarter * 32) << 16) + acc * p.mt + c0, v);
-                if (row_ok) {
+                if (part) {
+                    // partial tile [activation row][weight row]: lanes write consecutive floats
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) part[(size_t)(c0 + i) * 128 + r] = __uint_as_float(v[i]);
+                } else if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint32_t m = m0 + c0 + i;
@@ -498,43 +550,50 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     } else {
         // ------------------------------------------------------------ dequant warps
         // thread (set, r): weight row r of the tile, all 64 elements of the K steps kt = set, set + 4, ... of every
-        // tile: four sets of four warps, each taking one K step of every packed tile (one 256-element block per row)
+        // unit: four sets of four warps, each taking one K step of every packed tile (one 256-element block per row)
         const uint32_t r = threadIdx.x & 127, set = threadIdx.x >> 7;
         bool ok = true;
-        uint32_t it = 0;
-        // COOP: packed tile c (counted over all output tiles of this CTA) is copied by all 16 dequant warps, 8 rows
-        // each, one tile ahead of its use; buffer c & 1 must have been released by every reader of tile c - 2
-        uint32_t next_copy = 0;
+        // COOP: packed tile c (counted over all units of this CTA) is copied by all 16 dequant warps, 8 rows each, one
+        // tile ahead of its use; buffer c & 1 must have been released by every reader of tile c - 2
+        uint32_t next_copy = 0, copy_it = 0, copy_base = 0;  // copy_base: first packed tile of unit copy_it
+        PfUnit cu;
+        bool cu_ok = pf_unit(p, 0, cu);
         auto copy_upto = [&](uint32_t upto) {
             for (; next_copy <= upto; ++next_copy) {
-                const uint32_t c = next_copy, tc = blockIdx.x + (c / nraw) * gridDim.x, jc = c % nraw;
-                if (tc >= p.ntiles) continue;
-                const uint32_t cs = c & 1;
+                while (cu_ok && next_copy >= copy_base + (cu.nk + 3) / 4) {
+                    copy_base += (cu.nk + 3) / 4;
+                    cu_ok = pf_unit(p, ++copy_it, cu);
+                }
+                if (!cu_ok) continue;
+                const uint32_t c = next_copy, jc = cu.k0 / 4 + (c - copy_base), cs = c & 1;
                 if (ok && !pf_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1, dead_flag)) {
                     pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
                 if (ok) {
-                    const uint32_t cn0 = (tc % p.ntn) * 128;
+                    const uint32_t cn0 = (cu.tile % p.ntn) * 128;
                     uint8_t* dst = smem + 1024 + cs * RAW_TILE_BYTES;
-                    unsigned short v[8][4];
+#pragma unroll 1
+                    for (int q0 = 0; q0 < 8; q0 += 4) {  // four rows at a time: loads first, then the stores
+                        unsigned short v[4][4];
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const uint32_t row = 8 * (uint32_t)warp + q;
-                        const unsigned short* src = reinterpret_cast<const unsigned short*>(p.w + (size_t)(cn0 + row) * p.row_bytes + (size_t)jc * 210);
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t row = 8 * (uint32_t)warp + q0 + q;
+                            const unsigned short* src = reinterpret_cast<const unsigned short*>(p.w + (size_t)(cn0 + row) * p.row_bytes + (size_t)jc * 210);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t hw = lane + 32 * i;
-                            v[q][i] = (cn0 + row < p.N && hw < 105) ? __ldg(src + hw) : (unsigned short)0;
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t hw = lane + 32 * i;
+                                v[q][i] = (cn0 + row < p.N && hw < 105) ? __ldg(src + hw) : (unsigned short)0;
+                            }
                         }
-                    }
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        unsigned short* d16 = reinterpret_cast<unsigned short*>(dst + (8 * (uint32_t)warp + q) * RAW_PITCH);
+                        for (int q = 0; q < 4; ++q) {
+                            unsigned short* d16 = reinterpret_cast<unsigned short*>(dst + (8 * (uint32_t)warp + q0 + q) * RAW_PITCH);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t hw = lane + 32 * i;
-                            if (hw < 105) d16[hw] = v[q][i];
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t hw = lane + 32 * i;
+                                if (hw < 105) d16[hw] = v[q][i];
+                            }
                         }
                     }
                 }
@@ -542,16 +601,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 if (lane == 0) mbar_arrive(bar_full_raw + 8 * cs);
             }
         };
-        for (uint32_t tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, ++it) {
-            const uint32_t n0 = (tile % p.ntn) * 128;
+        uint32_t steps_done = 0, raws_done = 0;  // K steps and packed tiles of the units before this one
+        PfUnit un;
+        for (uint32_t it = 0; pf_unit(p, it, un); ++it) {
+            const uint32_t n0 = (un.tile % p.ntn) * 128;
             const bool row_ok = n0 + r < p.N;
             const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
-            // stage and phase of this set's K steps: position it * nkt + kt in the stream the MMA warp consumes
-            uint32_t s = (it * p.nkt + set) % p.ns, par = ((it * p.nkt + set) / p.ns) & 1;
-            for (uint32_t kt = set; kt < p.nkt; kt += 4) {
+            // stage and phase of this set's K steps: position steps_done + kt in the stream the MMA warp consumes
+            uint32_t s = (steps_done + set) % p.ns, par = ((steps_done + set) / p.ns) & 1;
+            for (uint32_t kt = set; kt < un.nk; kt += 4) {
                 uint32_t o[32];
                 if constexpr (RAW_TMA) {
-                    const uint32_t jr = it * nraw + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
+                    const uint32_t jr = raws_done + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
                     if constexpr (COOP) copy_upto(jr + 1);
                     if (ok && !pf_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
@@ -572,7 +633,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
                 } else {
-                    decode64_global<FMT>(wrow, kt, o);
+                    decode64_global<FMT>(wrow, un.k0 + kt, o);
                 }
                 if (!row_ok || !ok)
 #pragma unroll
@@ -590,6 +651,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 s += 4;
                 while (s >= p.ns) { s -= p.ns; par ^= 1; }
             }
+            steps_done += un.nk;
+            raws_done += (un.nk + 3) / 4;
         }
     }
     tc_fence_before();
@@ -598,6 +661,39 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
     }
+}
+
+// Adds the partial tiles of the K-split tail tiles in K order and writes the output.  Block = (activation row of the
+// tile, tail tile), thread = weight row of the tile; the pieces of tail tile t come from the CTAs whose granule range
+// meets [t gpt, (t + 1) gpt), in CTA order, which is K order.
+__global__ void __launch_bounds__(128) prefill_reduce_kernel(const PrefillParams p, uint32_t G) {
+    __shared__ uint32_t slots[192];
+    __shared__ uint32_t nslots;
+    const uint32_t t = blockIdx.y, ml = blockIdx.x, r = threadIdx.x;
+    const uint32_t tile = p.nfull + t, n0 = (tile % p.ntn) * 128, m = (tile / p.ntn) * p.mt + ml;
+    if (m >= p.M) return;  // block-uniform
+    if (threadIdx.x == 0) {
+        const uint32_t Q = p.ntail * p.gpt, lo = t * p.gpt, hi = lo + p.gpt;
+        uint32_t c = (lo * G) / Q, n = 0;
+        while (c > 0 && (c * Q) / G > lo) --c;
+        while (((c + 1) * Q) / G <= lo) ++c;  // first CTA whose range [a, b) ends beyond lo
+        for (; c < G && n < 192; ++c) {
+            const uint32_t a = (c * Q) / G, b = ((c + 1) * Q) / G;
+            if (a >= hi) break;
+            if (a >= b) continue;
+            if (max(a, lo) == lo && min(b, hi) == hi) { n = 0; break; }  // computed whole and written by its CTA
+            slots[n++] = min(c, a) + t;  // the numbering of pf_unit()
+        }
+        nslots = n;
+    }
+    __syncthreads();
+    if (nslots == 0 || n0 + r >= p.N) return;
+    float sum = __ldcg(p.part + ((size_t)slots[0] * p.mt + ml) * 128 + r);
+    for (uint32_t i = 1; i < nslots; ++i) sum += __ldcg(p.part + ((size_t)slots[i] * p.mt + ml) * 128 + r);
+    const size_t idx = (size_t)m * p.N + n0 + r;
+    if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = sum;
+    else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(sum);
+    else static_cast<__half*>(p.out)[idx] = __float2half_rn(sum);
 }
 
 __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
@@ -683,10 +779,36 @@ bool prefill_supported(int fmt, size_t M, size_t K, size_t N) {
     return M >= B200Q_PREFILL_MIN_M && K % 64 == 0 && K % 8 == 0 && N >= 1;
 }
 
-size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N) {
-    (void)N;
+namespace {
+// How the output tiles are dealt to the CTAs (the fields of PrefillParams with the same names).
+struct PfPlan {
+    uint32_t mt, ntn, ntiles, grid, nfull, ntail, split, gran, gpt;
+    size_t part_bytes;
+};
+PfPlan pf_plan(size_t M, size_t K, size_t N, int sm_count) {
+    PfPlan pl{};
+    pl.mt = pick_mt(M);
+    pl.ntn = (uint32_t)((N + 127) / 128);
+    pl.ntiles = pl.ntn * (uint32_t)((M + pl.mt - 1) / pl.mt);
+    const uint32_t G = (uint32_t)sm_count, nkt = (uint32_t)(K / BK);
+    pl.gran = nkt % 4 == 0 ? 4u : 1u;  // whole packed tiles (256 elements) where rows consist of them
+    pl.gpt = nkt / pl.gran;
+    pl.nfull = pl.ntiles / G * G;
+    pl.ntail = pl.ntiles - pl.nfull;
+    // cut the tail along K when that at least halves it (the partial tiles and the reduce launch cost a few
+    // microseconds) and the 32-bit granule arithmetic holds
+    pl.split = pl.ntail > 0 && pl.ntail * 2 <= G && pl.gpt >= 2 && (uint64_t)(G + 1) * pl.ntail * pl.gpt < 0xFFFFFFFFull && G <= 190;
+    pl.grid = (pl.split || pl.ntiles >= G) ? G : pl.ntiles;
+    const size_t Q = (size_t)pl.ntail * pl.gpt;
+    pl.part_bytes = pl.split ? ((Q < G ? Q : G) + pl.ntail) * pl.mt * 128 * sizeof(float) : 0;
+    return pl;
+}
+}  // namespace
+
+size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N, int sm_count) {
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);  // always re-quantised (see act_q8k_to_bf16_kernel)
-    return (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
+    const size_t acts = (act_dtype == DT_BF16 && !kq) ? 0 : ((M * K * 2 + 255) & ~(size_t)255);
+    return acts + pf_plan(M, K, N, sm_count).part_bytes;
 }
 
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -695,9 +817,10 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     *ws_too_small = false;
     const void* act_bf16 = act;
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
+    const PfPlan pl = pf_plan(M, K, N, sm_count);
+    const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N, sm_count), act_bytes = need - pl.part_bytes;
+    if (need && (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15))) { *ws_too_small = true; return cudaSuccess; }
     if (act_dtype != DT_BF16 || kq) {
-        const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N);
-        if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
         const size_t n = M * K;
         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(ws);
         if (kq) {
@@ -728,7 +851,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     p.out = out;
     p.M = (uint32_t)M; p.N = (uint32_t)N; p.K = (uint32_t)K;
     p.row_bytes = (uint32_t)(K / fmt_block_size(fmt) * fmt_block_bytes(fmt));
-    p.mt = pick_mt(M);
+    p.mt = pl.mt;
     p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.mt >> 3) << 17) | ((128u >> 4) << 24);  // f32 acc, bf16 x bf16, K-major, N = mt, M = 128
     p.nkt = (uint32_t)(K / BK);
     // packed tiles by TMA need rows that are a multiple of 16 bytes and whole 256-element tiles
@@ -741,8 +864,10 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;  // tensor memory: 8 weight tiles of 32 columns
     if (nsb > p.nkt) nsb = p.nkt;
     p.ns = nsb;
-    p.ntn = (uint32_t)((N + 127) / 128);
-    p.ntiles = p.ntn * (uint32_t)((M + p.mt - 1) / p.mt);
+    p.ntn = pl.ntn;
+    p.ntiles = pl.ntiles;
+    p.nfull = pl.nfull; p.ntail = pl.ntail; p.split = pl.split; p.gran = pl.gran; p.gpt = pl.gpt;
+    p.part = pl.split ? reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + act_bytes) : nullptr;
     p.out_dtype = out_dtype;
     p.status = status;
     const size_t smem = 2048 + raw_bytes + (size_t)nsb * b_tile;
@@ -775,15 +900,22 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
             return cudaErrorInvalidValue;
         }
     }
-    dim3 grid(p.ntiles < (uint32_t)sm_count ? p.ntiles : (uint32_t)sm_count, 1, 1);
+    dim3 grid(pl.grid, 1, 1);
+    cudaError_t le;
     switch (fmt) {
-    case FMT_Q4_0: return raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st);
-    case FMT_Q8_0: return raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st);
-    case FMT_Q4_K: return launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st);
-    case FMT_Q5_K: return launch_fmt<FMT_Q5_K, true>(map, wmap, p, grid, smem, st);
-    case FMT_Q6_K: return launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st);
+    case FMT_Q4_0: le = raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q8_0: le = raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q4_K: le = launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q5_K: le = launch_fmt<FMT_Q5_K, true>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q6_K: le = launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st); break;
     default: return cudaErrorInvalidValue;
     }
+    if (le != cudaSuccess || !pl.split) return le;
+    // the K-split tail tiles: add their pieces in K order
+    const uint32_t rows = (uint32_t)(M < p.mt ? M : p.mt);
+    prefill_reduce_kernel<<<dim3(rows, pl.ntail, 1), 128, 0, st>>>(p, pl.grid);
+    note_launch();
+    return cudaGetLastError();
 }
 
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
