@@ -48,6 +48,7 @@ struct PrefillParams {
     uint32_t idesc;   // tcgen05 instruction descriptor
     uint32_t nkt;     // K / 64
     uint32_t ns;      // ring depth: stage s = decoded weight tile s in tensor memory + activation tile s in shared memory
+    uint32_t nr;      // ring depth of the packed-weight tiles (0: the rows are not staged)
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
     // Work distribution.  Tiles [0, nfull) are dealt whole, round-robin (nfull is a multiple of the grid).  The
     // remaining ntail tiles (fewer than one per CTA) are, when `split`, cut along K: their ntail * gpt granules of
@@ -312,6 +313,41 @@ __device__ __forceinline__ void decode64_q6k(const uint8_t* blk, uint32_t jt, ui
     }
 }
 
+// The same for a block staged in shared memory at byte `sh` (0 or 2) of a 4-byte-aligned slot: aligned words are loaded
+// and funnel-shifted, the same instructions for both alignments (rows of a warp differ in it).
+__device__ __forceinline__ void decode64_q6k_staged(const uint8_t* slot, uint32_t sh, uint32_t jt, uint32_t (&o)[32]) {
+    const uint32_t n = jt >> 1, g0 = (jt & 1) * 2, sb = 8 * sh;
+    const uint8_t* blk = slot + sh;
+    const float d = f16bits_to_f32(*reinterpret_cast<const unsigned short*>(blk + 208));
+    const uint32_t scw = (uint32_t)*reinterpret_cast<const unsigned short*>(blk + 192 + 8 * n + 2 * g0) |
+                         ((uint32_t)*reinterpret_cast<const unsigned short*>(blk + 192 + 8 * n + 2 * g0 + 2) << 16);  // four int8 scales
+    uint32_t hw[9];
+    const uint32_t* qh = reinterpret_cast<const uint32_t*>(slot + 128 + 32 * n);
+#pragma unroll
+    for (int i = 0; i < 9; ++i) hw[i] = qh[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hw[i] = __funnelshift_r(hw[i], hw[i + 1], sb);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t gq = g0 + h;
+        const uint32_t* ql = reinterpret_cast<const uint32_t*>(slot + 64 * n + 32 * h);  // gq & 1 == h
+        const float s0 = d * (float)(int)(signed char)(scw >> (16 * h)), s1 = d * (float)(int)(signed char)(scw >> (16 * h + 8));
+        const float a0 = 64.0f * s0, c0 = -160.0f * s0, a1 = 64.0f * s1, c1 = -160.0f * s1;
+        uint32_t lw[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) lw[i] = ql[i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t w = __funnelshift_r(lw[i], lw[i + 1], sb);
+            const uint32_t nib = (g0 ? (w >> 4) : w) & 0x0F0F0F0Fu;
+            const uint32_t q = nib | (((hw[i] >> (2 * gq)) & 0x03030303u) << 4);
+            const float a = i < 4 ? a0 : a1, c = i < 4 ? c0 : c1;
+            o[16 * h + 2 * i] = pack_bf16(fmaf(a, code_mid<0>(q), c), fmaf(a, code_mid<1>(q), c));
+            o[16 * h + 2 * i + 1] = pack_bf16(fmaf(a, code_mid<2>(q), c), fmaf(a, code_mid<3>(q), c));
+        }
+    }
+}
+
 // Elements [64 kt, 64 kt + 64) of one weight row in global memory as 64 bf16 (rows whose packed tiles are not staged).
 template <int FMT>
 __device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt, uint32_t (&o)[32]) {
@@ -331,7 +367,7 @@ __device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt,
 // dynamic shared memory: [0,1024) barriers + TMEM base; then two packed-weight tiles and ns activation tiles of
 // mt*128 B, all 1 KB aligned.  Stage s pairs activation tile s with decoded weight tile s in tensor memory.
 constexpr int PF_OFF_FULL = 0, PF_OFF_EMPTY = 128, PF_OFF_ACC_FULL = 256,
-              PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 296, PF_OFF_EMPTY_RAW = 312;
+              PF_OFF_ACC_EMPTY = 272, PF_OFF_TMEM = 288, PF_OFF_DEAD = 292, PF_OFF_FULL_RAW = 320, PF_OFF_EMPTY_RAW = 384;
 
 // One piece of work of a CTA: K steps [k0, k0 + nk) of output tile `tile`; slot < 0: the whole tile, written to the
 // output; otherwise a partial tile for the reduce kernel.
@@ -392,7 +428,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_TMEM);
     volatile uint32_t* dead_flag = reinterpret_cast<volatile uint32_t*>(smem + PF_OFF_DEAD);
     const uint32_t b_tile_bytes = p.mt * 128;
-    const uint32_t raw_bytes = RAW_TMA ? 2 * RAW_TILE_BYTES : 0;
+    const uint32_t raw_bytes = RAW_TMA ? p.nr * RAW_TILE_BYTES : 0;
     const uint32_t raw_tiles = sbase + 1024, b_tiles = raw_tiles + raw_bytes;
     // Tensor memory (all 512 columns): nacc accumulators of mt columns (two while they fit beside the weight stages,
     // one at mt = 256), then the decoded weight tiles of 32 columns (128 rows x 64 bf16, two per column).
@@ -405,9 +441,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             mbar_init(bar_full + 8 * s, 5);
             mbar_init(bar_empty + 8 * s, 1);  // released by the commit behind the stage's MMAs, for both producers
         }
-        for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(bar_full_raw + 8 * s, COOP ? 16 : 1);  // COOP: every dequant warp copies its 8 rows
+        for (uint32_t s = 0; s < p.nr; ++s) {
+            mbar_init(bar_full_raw + 8 * s, COOP ? 512 : 1);  // COOP: every dequant thread copies a share of the tile
             mbar_init(bar_empty_raw + 8 * s, 16);            // every dequant warp reads every packed tile
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
             mbar_init(bar_acc_empty + 8 * s, 4);   // the four epilogue warps
         }
@@ -438,7 +476,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
                     // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
                     tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : FMT == FMT_Q5_K ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
-                    if (++s == 2) { s = 0; par ^= 1; }
+                    if (++s == p.nr) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
             }
@@ -556,6 +594,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         // COOP: packed tile c (counted over all units of this CTA) is copied by all 16 dequant warps, 8 rows each, one
         // tile ahead of its use; buffer c & 1 must have been released by every reader of tile c - 2
         uint32_t next_copy = 0, copy_it = 0, copy_base = 0;  // copy_base: first packed tile of unit copy_it
+        uint32_t cs = 0, cpar = 0;                            // ring slot and phase of packed tile next_copy
         PfUnit cu;
         bool cu_ok = pf_unit(p, 0, cu);
         auto copy_upto = [&](uint32_t upto) {
@@ -564,44 +603,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     copy_base += (cu.nk + 3) / 4;
                     cu_ok = pf_unit(p, ++copy_it, cu);
                 }
-                if (!cu_ok) continue;
-                const uint32_t c = next_copy, jc = cu.k0 / 4 + (c - copy_base), cs = c & 1;
-                if (ok && !pf_wait(bar_empty_raw + 8 * cs, ((c >> 1) & 1) ^ 1, dead_flag)) {
+                if (!cu_ok) return;  // no further packed tiles: next_copy stays, later calls return here again
+                const uint32_t jc = cu.k0 / 4 + (next_copy - copy_base);
+                if (ok && !pf_wait(bar_empty_raw + 8 * cs, cpar ^ 1, dead_flag)) {
                     pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
                 if (ok) {
+                    // Asynchronous 4-byte copies (no registers, nothing waits here).  A block starts 2-byte aligned:
+                    // the copy starts at the 4-byte boundary at or below it, so the block lands at byte (start & 2) of
+                    // its 212-byte row and the decoder shifts.  Rows past N are zero-filled; the last word is clipped
+                    // where it would reach past the end of the tensor.
                     const uint32_t cn0 = (cu.tile % p.ntn) * 128;
-                    uint8_t* dst = smem + 1024 + cs * RAW_TILE_BYTES;
-#pragma unroll 1
-                    for (int q0 = 0; q0 < 8; q0 += 4) {  // four rows at a time: loads first, then the stores
-                        unsigned short v[4][4];
+                    const uint32_t dst = raw_tiles + cs * RAW_TILE_BYTES;
+                    const uint8_t* wend = p.w + (size_t)p.N * p.row_bytes;
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint32_t row = 8 * (uint32_t)warp + q0 + q;
-                            const unsigned short* src = reinterpret_cast<const unsigned short*>(p.w + (size_t)(cn0 + row) * p.row_bytes + (size_t)jc * 210);
+                    for (int q = 0; q < 8; ++q) {
+                        const uint32_t row = 8 * (uint32_t)warp + q;
+                        const bool in = cn0 + row < p.N;
+                        const uint8_t* blk = p.w + (size_t)(in ? cn0 + row : 0) * p.row_bytes + (size_t)jc * 210;
+                        const uint8_t* src = blk - (reinterpret_cast<uintptr_t>(blk) & 2);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const uint32_t hw = lane + 32 * i;
-                                v[q][i] = (cn0 + row < p.N && hw < 105) ? __ldg(src + hw) : (unsigned short)0;
-                            }
-                        }
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            unsigned short* d16 = reinterpret_cast<unsigned short*>(dst + (8 * (uint32_t)warp + q0 + q) * RAW_PITCH);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const uint32_t hw = lane + 32 * i;
-                                if (hw < 105) d16[hw] = v[q][i];
+                        for (int i = 0; i < 2; ++i) {
+                            const uint32_t wd = lane + 32 * i;
+                            if (wd < 53) {
+                                const uint8_t* sp = src + 4 * wd;
+                                const uint32_t nbytes = !in ? 0u : sp + 4 <= wend ? 4u : sp + 2 <= wend ? 2u : 0u;
+                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + row * RAW_PITCH + 4 * wd), "l"(in ? sp : p.w), "r"(nbytes) : "memory");
                             }
                         }
                     }
+                    // arrives on the tile's barrier once this thread's copies have landed
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_full_raw + 8 * cs) : "memory");
+                } else {
+                    mbar_arrive(bar_full_raw + 8 * cs);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_full_raw + 8 * cs);
+                if (++cs == p.nr) { cs = 0; cpar ^= 1; }
             }
         };
         uint32_t steps_done = 0, raws_done = 0;  // K steps and packed tiles of the units before this one
+        uint32_t rs = 0, rpar = 0;                // ring slot and phase of the packed tile of this set's next K step
         PfUnit un;
         for (uint32_t it = 0; pf_unit(p, it, un); ++it) {
             const uint32_t n0 = (un.tile % p.ntn) * 128;
@@ -612,9 +653,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             for (uint32_t kt = set; kt < un.nk; kt += 4) {
                 uint32_t o[32];
                 if constexpr (RAW_TMA) {
-                    const uint32_t jr = raws_done + (kt >> 2), rs = jr & 1;  // packed tile covering K steps 4j .. 4j+3
-                    if constexpr (COOP) copy_upto(jr + 1);
-                    if (ok && !pf_wait(bar_full_raw + 8 * rs, (jr >> 1) & 1, dead_flag)) {
+                    // packed tile raws_done + kt / 4 covers K steps 4j .. 4j+3; a set visits every packed tile once, in order
+                    if constexpr (COOP) copy_upto(raws_done + (kt >> 2) + p.nr - 1);
+                    if (ok && !pf_wait(bar_full_raw + 8 * rs, rpar, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                     }
@@ -622,7 +663,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     if (ok) {
                         if constexpr (FMT == FMT_Q4_K) decode64_q45k<false>(rrow, set, o);
                         else if constexpr (FMT == FMT_Q5_K) decode64_q45k<true>(rrow, set, o);
-                        else if constexpr (FMT == FMT_Q6_K) decode64_q6k<true>(rrow, set, o);
+                        else if constexpr (FMT == FMT_Q6_K) {
+                            // where the row's block sits in its 212-byte slot: the low bits of its global address
+                            const uint32_t sh = ((n0 + r) * p.row_bytes + (un.k0 / 4 + (kt >> 2)) * 210u) & 2u;
+                            decode64_q6k_staged(rrow, sh, set, o);
+                        }
                         else {
                             constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
                             decode32_blk<FMT, true>(rrow + (2 * set) * BB, o);
@@ -632,6 +677,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     // the warp's only K step in this packed tile (kt & 3 == set): release the tile
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_raw + 8 * rs);
+                    if (++rs == p.nr) { rs = 0; rpar ^= 1; }
                 } else {
                     decode64_global<FMT>(wrow, un.k0 + kt, o);
                 }
@@ -857,13 +903,19 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // packed tiles by TMA need rows that are a multiple of 16 bytes and whole 256-element tiles
     // (Q6_K's tiles are copied by the dequant warps and only need whole blocks, which the format guarantees)
     const bool raw = K % 256 == 0 && (fmt == FMT_Q6_K || p.row_bytes % 16 == 0);
-    const uint32_t raw_bytes = raw ? 2u * (uint32_t)raw_tile_bytes(fmt) : 0u;
+    const uint32_t raw_tile = raw ? (uint32_t)raw_tile_bytes(fmt) : 0u;
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
-    const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u - raw_bytes, b_tile = p.mt * 128;
-    uint32_t nsb = budget / b_tile;
+    const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u, b_tile = p.mt * 128;
+    // activation tiles first (at least two packed tiles stay), then as many packed tiles as fit: at small M the packed
+    // weights stream from HBM and the ring has to cover that latency
+    uint32_t nsb = (budget - 2 * raw_tile) / b_tile;
     if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;  // tensor memory: 8 weight tiles of 32 columns
     if (nsb > p.nkt) nsb = p.nkt;
     p.ns = nsb;
+    uint32_t nr = raw ? (budget - nsb * b_tile) / raw_tile : 0u;
+    if (nr > 8) nr = 8;
+    p.nr = nr;
+    const uint32_t raw_bytes = nr * raw_tile;
     p.ntn = pl.ntn;
     p.ntiles = pl.ntiles;
     p.nfull = pl.nfull; p.ntail = pl.ntail; p.split = pl.split; p.gran = pl.gran; p.gpt = pl.gpt;
