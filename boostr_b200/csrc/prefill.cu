@@ -47,7 +47,8 @@ struct PrefillParams {
     uint32_t mt;      // activation rows per tile (MMA N): 64, 128 or 256
     uint32_t idesc;   // tcgen05 instruction descriptor
     uint32_t nkt;     // K / 64
-    uint32_t ns;      // ring depth: stage s = decoded weight tile s in tensor memory + activation tile s in shared memory
+    uint32_t ns;      // ring depth: stage s = ks decoded weight tiles in tensor memory + ks activation tiles in shared memory
+    uint32_t ks;      // K steps (of 64) per stage, 1 or 2: at small mt the loop overhead of the MMA warp, not the MMAs, sets the pace
     uint32_t nr;      // ring depth of the packed-weight tiles (0: the rows are not staged)
     uint32_t ntn, ntiles;  // output tiles along N (128 weight rows each) and in total
     // Work distribution.  Tiles [0, nfull) are dealt whole, round-robin (nfull is a multiple of the grid).  The
@@ -64,7 +65,6 @@ struct PrefillParams {
 namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
-constexpr int PF_MAX_STAGES = 8;
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
 __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : fmt == FMT_Q5_K ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
         for (uint32_t s = 0; s < p.ns; ++s) {
             // a stage is full when the four warps of a set have written the weight tile (to tensor memory) and the
             // activation tile's bytes have landed (one more arrival, with the byte count); one wait for the MMA warp
-            mbar_init(bar_full + 8 * s, 5);
+            mbar_init(bar_full + 8 * s, 4 * p.ks + 1);
             mbar_init(bar_empty + 8 * s, 1);  // released by the commit behind the stage's MMAs, for both producers
         }
         for (uint32_t s = 0; s < p.nr; ++s) {
@@ -488,13 +488,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             PfUnit u;
             for (uint32_t it = 0; pf_unit(p, it, u); ++it) {
                 const uint32_t m0 = (u.tile / p.ntn) * p.mt;
-                for (uint32_t kt = 0; kt < u.nk; ++kt) {
+                for (uint32_t kt = 0; kt < u.nk; kt += p.ks) {
                     if (!pf_wait(bar_empty + 8 * s, par ^ 1, dead_flag)) {
                         pf_fail(dead_flag, p.status, STATUS_TIMEOUT_EMPTY);
                         break;
                     }
-                    mbar_expect_tx(bar_full + 8 * s, b_tile_bytes);
-                    tma_load_2d(b_tiles + s * b_tile_bytes, &tmap_act, (int)((u.k0 + kt) * BK), (int)m0, bar_full + 8 * s);
+                    mbar_expect_tx(bar_full + 8 * s, p.ks * b_tile_bytes);
+                    for (uint32_t i = 0; i < p.ks; ++i)
+                        tma_load_2d(b_tiles + (s * p.ks + i) * b_tile_bytes, &tmap_act, (int)((u.k0 + kt + i) * BK), (int)m0, bar_full + 8 * s);
                     if (++s == p.ns) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -519,19 +520,24 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * p.mt;
-                for (uint32_t kt = 0; kt < un.nk; ++kt) {
+                for (uint32_t kt = 0; kt < un.nk; kt += p.ks) {
                     if (!pf_wait(bar_full + 8 * sa, para, dead_flag)) {
                         if (lane == 0) pf_fail(dead_flag, p.status, STATUS_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_tm = a_tm0 + 32 * sa, b_lo = b_lo0 + sa * b_lo_step;
+                    const uint32_t a_tm = a_tm0 + 32 * p.ks * sa, b_lo = b_lo0 + p.ks * sa * b_lo_step;
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
                             tc_mma_bf16_ts(d_tmem, a_tm + 8 * k, smem_desc_sw128_lo(b_lo + 2 * k), p.idesc, (kt | k) != 0);
-                        // both tiles may be overwritten once these MMAs have read them
+                        if (p.ks == 2) {
+#pragma unroll
+                            for (int k = 0; k < BK / 16; ++k)
+                                tc_mma_bf16_ts(d_tmem, a_tm + 32 + 8 * k, smem_desc_sw128_lo(b_lo + b_lo_step + 2 * k), p.idesc, 1);
+                        }
+                        // the stage's tiles may be overwritten once these MMAs have read them
                         tc_commit(bar_empty + 8 * sa);
                     }
                     __syncwarp();
@@ -649,7 +655,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
             const bool row_ok = n0 + r < p.N;
             const uint8_t* wrow = p.w + (size_t)(row_ok ? n0 + r : 0) * p.row_bytes;
             // stage and phase of this set's K steps: position steps_done + kt in the stream the MMA warp consumes
-            uint32_t s = (steps_done + set) % p.ns, par = ((steps_done + set) / p.ns) & 1;
+            // (with two K steps per stage, units are whole multiples of four steps and a set keeps its half of the stage)
+            const uint32_t ksl = p.ks >> 1, sub = set & (p.ks - 1);
+            uint32_t s = ((steps_done + set) >> ksl) % p.ns, par = (((steps_done + set) >> ksl) / p.ns) & 1;
             for (uint32_t kt = set; kt < un.nk; kt += 4) {
                 uint32_t o[32];
                 if constexpr (RAW_TMA) {
@@ -690,11 +698,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                 }
                 // the thread's 64 bf16 go to its own lane (= weight row) of the stage's tensor-memory tile, 32 columns.
                 // Executed by the whole warp (dead warps store what they hold: nobody reads it).
-                tmem_st32(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * s, o);
+                tmem_st32(tmem_acc + ((((uint32_t)warp & 3u) * 32u) << 16) + a_col0 + 32 * (p.ks * s + sub), o);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_full + 8 * s);
-                s += 4;
+                s += 4 >> ksl;
                 while (s >= p.ns) { s -= p.ns; par ^= 1; }
             }
             steps_done += un.nk;
@@ -908,10 +916,15 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u, b_tile = p.mt * 128;
     // activation tiles first (at least two packed tiles stay), then as many packed tiles as fit: at small M the packed
     // weights stream from HBM and the ring has to cover that latency
-    uint32_t nsb = (budget - 2 * raw_tile) / b_tile;
-    if (nsb > (uint32_t)PF_MAX_STAGES) nsb = PF_MAX_STAGES;  // tensor memory: 8 weight tiles of 32 columns
+    uint32_t nsb = (budget - 2 * raw_tile) / b_tile;  // activation tiles = decoded weight tiles
+    const uint32_t tmem_tiles = (512u - (p.mt <= 128 ? 2u : 1u) * p.mt) / 32u;  // 32 columns each beside the accumulators
+    if (nsb > tmem_tiles) nsb = tmem_tiles;
+    if (nsb > 12) nsb = 12;
     if (nsb > p.nkt) nsb = p.nkt;
-    p.ns = nsb;
+    // two K steps per stage where the MMAs are short (mt <= 128) and every unit is a whole number of stages
+    p.ks = (p.mt <= 128 && p.nkt % 4 == 0 && nsb >= 4) ? 2u : 1u;
+    p.ns = nsb / p.ks;
+    nsb = p.ns * p.ks;
     uint32_t nr = raw ? (budget - nsb * b_tile) / raw_tile : 0u;
     if (nr > 8) nr = 8;
     p.nr = nr;
