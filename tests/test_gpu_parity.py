@@ -115,7 +115,8 @@ SHAPES = [
 def _bound(fmt, m):
     if fmt in ("Q4_K", "Q6_K"):
         return 2e-6  # integer dots are exact; only the order of <= 56 f32 block terms differs
-    return 1e-5 if m <= 8 else 1e-3  # fp16 hi+lo split / single fp16 rounding of activations
+    # activations as int8 pieces: three pieces (22 bits) up to 8 rows, two pieces (15 bits) above
+    return 1e-5 if m <= 8 else 1e-4
 
 
 @pytest.mark.parametrize("fmt", FMTS)
