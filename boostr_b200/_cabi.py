@@ -52,6 +52,7 @@ SIGNATURES = {
                                           c_int, c_int, POINTER(c_void_p), c_void_p]),
     "b200q_col_parallel_matmul_gather": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_size_t, c_size_t,
                                                  c_int, c_int, POINTER(c_void_p), c_void_p]),
+    "b200q_tp_all_reduce": (c_int, [c_void_p, c_size_t, c_int, c_int, POINTER(c_void_p), c_void_p]),
     "b200q_launch_count": (ctypes.c_ulonglong, []),
 }
 

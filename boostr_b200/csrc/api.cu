@@ -29,6 +29,7 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
                                  void* const* out, const void* w_up, int out_dtype, size_t K, int sm_count, cudaStream_t st,
                                  unsigned int* status, const float* norm_w = nullptr, float norm_eps = 0.f);
 cudaError_t launch_rmsnorm(const void* act, int act_dtype, const float* norm_w, float eps, float* out, size_t M, size_t K, cudaStream_t st);
+cudaError_t launch_tp_all_reduce(float* data, size_t count, const PeerComm& comm, int sm_count, cudaStream_t st, unsigned int* status);
 cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
                                   int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm);
 bool gemv_m1_f32_supported(int fmt, size_t M, size_t K, size_t N);
@@ -38,7 +39,7 @@ bool prefill_supported(int fmt, size_t M, size_t K, size_t N);
 size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_t N, int sm_count);
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                            size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
-                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len);
+                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len, bool acts_prepared);
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
                                cudaStream_t st);
 }  // namespace b200q
@@ -215,7 +216,7 @@ int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w
     if (prefill_supported(format, M, K, N)) {
         char msg[256] = "";
         e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
-                           status, &small, msg, sizeof(msg));
+                           status, &small, msg, sizeof(msg), false);
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
     } else if (gemv_m1_supported(format, M, K, N, false)) {
         e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
@@ -341,10 +342,10 @@ int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w
         const size_t rest_bytes = ws_bytes - 2 * mn;
         char msg[256] = "";
         e = launch_prefill(format, act, act_dtype, w_gate, g, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, status,
-                           &small, msg, sizeof(msg));
-        if (e == cudaSuccess && !small)
+                           &small, msg, sizeof(msg), false);
+        if (e == cudaSuccess && !small)  // the prepared activations of the first product are still in `rest`
             e = launch_prefill(format, act, act_dtype, w_up, u, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st,
-                               status, &small, msg, sizeof(msg));
+                               status, &small, msg, sizeof(msg), true);
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_swiglu: %s", msg);
         if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
     } else if (gemv_m1_supported(format, M, K, N, true)) {
@@ -533,6 +534,28 @@ int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype,
     cudaError_t e = launch_gemv_m1_rowpar(format, act, act_dtype, w, out_full, K, n_local, sm_count_current(),
                                           static_cast<cudaStream_t>(stream), status, comm);
     if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA col_parallel_matmul_gather kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+int b200q_tp_all_reduce(void* data, size_t count, int rank, int world, void* const* bufs, void* stream) {
+    if (!data || (reinterpret_cast<uintptr_t>(data) & 3)) return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: data must be a 4-byte aligned device pointer");
+    if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: rank %d of world %d (at most %u ranks)", rank, world, TP_MAX_WORLD);
+    if (!bufs) return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: null buffer table");
+    if (count == 0) return B200Q_OK;
+    if (count > TP_MAX_N)
+        return fail(B200Q_ERR_NOT_FUSED, "tp_all_reduce: %zu values exceed the exchange buffer (%u); use the communicator's all-reduce", count, TP_MAX_N);
+    PeerComm comm{};
+    comm.world = (uint32_t)world;
+    comm.rank = (uint32_t)rank;
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r]) return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: null exchange buffer of rank %d", r);
+        comm.buf[r] = static_cast<uint8_t*>(bufs[r]);
+    }
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "tp_all_reduce: cannot resolve the device status word");
+    cudaError_t e = launch_tp_all_reduce(static_cast<float*>(data), count, comm, sm_count_current(), static_cast<cudaStream_t>(stream), status);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA tp_all_reduce kernel launch failed: %s", cudaGetErrorString(e));
     return B200Q_OK;
 }
 

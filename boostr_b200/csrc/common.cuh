@@ -176,7 +176,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 //   [1024 + (((e & 1) * 8 + r) * 16384 + row) * 8]  {bits, e}: element `row` of rank r's partial row, epoch e
 // Two parities suffice: a rank can push epoch e + 2 only after it has collected e + 1 from every peer,
 // which a peer pushes after it finished collecting epoch e.
-constexpr uint32_t TP_MAX_WORLD = 8, TP_MAX_N = 16384;
+constexpr uint32_t TP_MAX_WORLD = 8, TP_MAX_N = 65536;
 constexpr size_t TP_BUF_BYTES = 1024 + 2 * (size_t)TP_MAX_WORLD * TP_MAX_N * 8;
 struct PeerComm {
     uint32_t world, rank;  // world <= 1: no exchange

@@ -842,4 +842,29 @@ cudaError_t launch_rmsnorm(const void* act, int act_dtype, const float* norm_w, 
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+// All-reduce (sum) of `count` f32 values in place over the exchange buffers, for the small messages of row-parallel
+// products that have no exchange inside their kernel (2 <= M <= 16 rows, or formats without a fused decode kernel):
+// stands in for all_reduce_tensor + sync (src/distributed/comm_utils.rs:15-39).  Each CTA pushes its share of the
+// values to every rank as tagged 8-byte stores and then adds, for the same elements, the ranks' values in rank order,
+// so all ranks hold bit-identical sums.  Every poll is bounded (tp_finish).
+__global__ void __launch_bounds__(256) tp_all_reduce_kernel(float* data, uint32_t count, const __grid_constant__ PeerComm comm,
+                                                            unsigned int* status) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const uint32_t e = tp_epoch(comm);
+    const uint32_t chunk = (count + gridDim.x - 1) / gridDim.x;
+    const uint32_t begin = min(count, blockIdx.x * chunk), end = min(count, begin + chunk);
+    for (uint32_t i = begin + threadIdx.x; i < end; i += blockDim.x) tp_push(comm, e, i, data[i]);
+    tp_finish(comm, e, begin, end, data, status);
+}
+
+cudaError_t launch_tp_all_reduce(float* data, size_t count, const PeerComm& comm, int sm_count, cudaStream_t st, unsigned int* status) {
+    unsigned grid = (unsigned)((count + 255) / 256);
+    if (grid > (unsigned)sm_count) grid = (unsigned)sm_count;
+    if (grid < 1) grid = 1;
+    cudaError_t e = launch_pdl(tp_all_reduce_kernel, dim3(grid), dim3(256), 0, st, data, (uint32_t)count, comm, status);
+    note_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 }  // namespace b200q

@@ -867,14 +867,16 @@ size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_
 
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                            size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
-                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len) {
+                           unsigned int* status, bool* ws_too_small, char* err, size_t err_len, bool acts_prepared) {
     *ws_too_small = false;
     const void* act_bf16 = act;
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     const PfPlan pl = pf_plan(M, K, N, sm_count);
     const size_t need = prefill_workspace_bytes(fmt, act_dtype, M, K, N, sm_count), act_bytes = need - pl.part_bytes;
     if (need && (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15))) { *ws_too_small = true; return cudaSuccess; }
-    if (act_dtype != DT_BF16 || kq) {
+    if ((act_dtype != DT_BF16 || kq) && acts_prepared) {
+        act_bf16 = ws;  // a previous call with the same activations and scratch left them there (gate, then up)
+    } else if (act_dtype != DT_BF16 || kq) {
         const size_t n = M * K;
         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(ws);
         if (kq) {

@@ -142,6 +142,20 @@ def col_parallel_matmul_gather(activation: torch.Tensor, weight: QuantTensor, ra
     return out_full
 
 
+def tp_all_reduce(tensor: torch.Tensor, rank: int, world: int, table) -> bool:
+    """In-place sum of a small contiguous f32 CUDA tensor over the exchange buffers (``b200q_tp_all_reduce``).
+    Returns False, having launched nothing, when the tensor does not fit (use the process group instead)."""
+    if not tensor.is_cuda or tensor.dtype != torch.float32 or not tensor.is_contiguous():
+        return False
+    L = _cabi.lib()
+    with torch.cuda.device(tensor.device):
+        rc = L.b200q_tp_all_reduce(tensor.data_ptr(), tensor.numel(), rank, world, table, _stream())
+    if rc == _cabi.ERR_NOT_FUSED:
+        return False
+    _cabi.check(rc)
+    return True
+
+
 def quant_matmul_batch(activation: torch.Tensor, weights: Sequence[QuantTensor],
                        out_dtype: torch.dtype = torch.float32, outs: Sequence[torch.Tensor] = None) -> List[torch.Tensor]:
     """One activation against several weights sharing K (q/k/v, gate/up)."""

@@ -188,9 +188,10 @@ class ColumnParallelQuantLinear:
 class RowParallelQuantLinear:
     """Input features split across ranks; forward = local product, all-reduce SUM, then bias.
 
-    With a ``PeerExchange`` the decode case (one activation row, Q4_K/Q6_K, N <= 16384) runs as ONE
-    kernel that pushes the partial row to all ranks over NVLink and adds the rows in rank order; every
-    other shape falls back to ``quant_matmul`` + the process group's all-reduce."""
+    With a ``PeerExchange`` the decode case (one activation row, Q4_K/Q6_K) runs as ONE kernel that pushes
+    the partial row to all ranks over NVLink and adds the rows in rank order; other results of up to 65536
+    values (a few rows) take ``quant_matmul`` + the exchange all-reduce kernel; larger ones ``quant_matmul``
+    + the process group's all-reduce."""
 
     def __init__(self, local_weight: QuantTensor, bias: Optional[torch.Tensor] = None, group=None,
                  exchange: Optional[PeerExchange] = None):
@@ -211,7 +212,9 @@ class RowParallelQuantLinear:
             y = ops.row_parallel_matmul(input_shard, self.weight, ex.rank, ex.world, ex.table, out=out)
         if y is None:
             y = ops.quant_matmul(input_shard, self.weight, out=out)
-            all_reduce_tensor(y, self.group)
+            # small results (a few rows) go through the exchange buffers too: one short kernel instead of a collective
+            if not (ex is not None and ex.table is not None and ops.tp_all_reduce(y, ex.rank, ex.world, ex.table)):
+                all_reduce_tensor(y, self.group)
         if self.bias is not None:
             y.add_(self.bias)
         return y

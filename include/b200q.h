@@ -226,7 +226,7 @@ B200Q_API unsigned long long b200q_launch_count(void);
  * sequence of b200q_row_parallel_matmul calls.  The buffers carry the exchange state (the epoch), so
  * one set of buffers serves one stream of calls.
  *
- * Shapes without a fused path (M > 1, formats other than Q4_K/Q6_K, N > 16384, non-f32 output) return
+ * Shapes without a fused path (M > 1, formats other than Q4_K/Q6_K, N > 65536, non-f32 output) return
  * B200Q_ERR_NOT_FUSED without launching anything: run b200q_quant_matmul and the communicator's
  * all_reduce instead.
  */
@@ -246,12 +246,22 @@ B200Q_API int b200q_row_parallel_matmul(int format, const void* act, int act_dty
  * rank's exchange buffer; each rank then copies the assembled row [world * n_local] into `out_full`
  * (row-major, shard r in columns [r * n_local, (r + 1) * n_local): the layout the reference's flat gather
  * only gives for one row).  Same set-up, ordering rules and bounded waits as b200q_row_parallel_matmul;
- * the two may alternate on one set of buffers.  M = 1, Q4_K / Q6_K, world * n_local <= 131072, f32 output;
+ * the two may alternate on one set of buffers.  M = 1, Q4_K / Q6_K, world * n_local <= 524288, f32 output;
  * anything else returns B200Q_ERR_NOT_FUSED without launching.
  */
 B200Q_API int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype, const void* w, void* out_full,
                                                size_t M, size_t K, size_t n_local, int rank, int world, void* const* bufs,
                                                void* stream);
+
+/*
+ * All-reduce (sum) of `count` f32 values in place over the same exchange buffers: the small-message stand-in for
+ * all_reduce_tensor + sync (src/distributed/comm_utils.rs:15-39) behind a row-parallel product that has no exchange
+ * inside its kernel (2 <= M rows, Q4_0 / Q8_0).  One kernel: tagged 8-byte stores to every rank, then each rank adds
+ * the ranks' values in rank order (bit-identical on all ranks), every wait bounded as above.  Same ordering rules;
+ * may alternate with the two calls above on one set of buffers.  count <= 65536, else B200Q_ERR_NOT_FUSED (nothing
+ * launched: use the communicator).
+ */
+B200Q_API int b200q_tp_all_reduce(void* data, size_t count, int rank, int world, void* const* bufs, void* stream);
 
 #ifdef __cplusplus
 }

@@ -80,4 +80,6 @@ extern "C" {
     pub fn b200q_col_parallel_matmul_gather(format: c_int, act: *const c_void, act_dtype: c_int, w: *const c_void,
                                             out_full: *mut c_void, m: usize, k: usize, n_local: usize, rank: c_int,
                                             world: c_int, bufs: *const *mut c_void, stream: *mut c_void) -> c_int;
+    pub fn b200q_tp_all_reduce(data: *mut c_void, count: usize, rank: c_int, world: c_int, bufs: *const *mut c_void,
+                               stream: *mut c_void) -> c_int;
 }

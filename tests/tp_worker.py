@@ -47,6 +47,29 @@ def main():
             for g in gathered:
                 assert torch.equal(g.view(torch.int32), y_fused.view(torch.int32)), "ranks disagree on the fused sum"
             assert e1 <= 2e-6 and e2 <= 2e-6, (fmt, n, k, it, e1, e2)
+    # several rows, and a format without a fused decode kernel: product + the exchange all-reduce kernel against
+    # product + NCCL all-reduce; bit-identical on all ranks, equal to NCCL's sum up to the order of additions
+    for case, (fmt, m, n, k) in enumerate([("Q4_K", 16, 4096, 4096), ("Q6_K", 5, 512, 2048 * world), ("Q8_0", 1, 300, 1024 * world), ("Q4_K", 64, 1024, 1024 * world)]):
+        if (k // world) % 256:
+            continue
+        rng = synth.rng_for(79, case)
+        full = synth.weight_bytes(fmt, rng, n, k)
+        viaex = RowParallelQuantLinear.from_full(fmt, full, n, k, rank, world, exchange=ex)
+        plain = RowParallelQuantLinear(viaex.weight)
+        for it in range(4):
+            act = synth.activations(rng, m, k)
+            shard = torch.from_numpy(np.ascontiguousarray(act[:, rank * (k // world):(rank + 1) * (k // world)])).cuda()
+            before = ops.launch_count()
+            y_ex = viaex(shard).clone()
+            launched = ops.launch_count() - before
+            y_nccl = plain(shard)
+            ops.check_device_status()
+            assert launched >= 2 and m * n <= 65536, (fmt, m, launched)  # the all-reduce was one of this library's kernels
+            scale = float(y_nccl.abs().max())
+            assert float((y_ex - y_nccl).abs().max()) / scale <= 2e-6, (fmt, m, it)
+            gathered = [torch.empty_like(y_ex) for _ in range(world)]
+            dist.all_gather(gathered, y_ex)
+            assert all(torch.equal(g, y_ex) for g in gathered), "ranks disagree on the exchange all-reduce"
     # fused column-parallel gather of logits against NCCL all-gather + strided copy (M = 1)
     from boostr_b200.tensor_parallel import ColumnParallelQuantLinear, gather_from_ranks
     for case, (fmt, n, k) in enumerate([("Q6_K", 128256 // 8 * world, 4096), ("Q4_K", 96 * world, 1024)]):
@@ -63,7 +86,7 @@ def main():
             assert torch.equal(fused, plain), ("fused gather differs from NCCL gather", fmt, it)
             assert torch.equal(fused, one), ("gathered logits differ from the unsharded product", fmt, it)
     # a captured decode step that contains the fused exchange (its epoch lives in device memory) replays to
-    # the bits of the eager step, on every rank; M = 1 (fused) and M = 4 (product + NCCL all-reduce)
+    # the bits of the eager step, on every rank; M = 1 (fused) and M = 4 (product + exchange all-reduce kernel)
     from boostr_b200.decode_graph import DecodeGraph
     from boostr_b200.decode_stack import DecodeStack
 
