@@ -165,6 +165,40 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
 
 }  // namespace
 
+namespace {
+// acts_prepared: the scratch already holds this activation matrix as the tensor-core path prepares it for this class
+// of formats (a previous weight of the same batch left it there)
+int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
+                      size_t K, size_t N, void* ws, size_t ws_bytes, void* stream, bool acts_prepared) {
+    int rc = check_matmul_args("quant_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int* status = status_ptr_current();
+    if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul: cannot resolve the device status word");
+    bool small = false;
+    cudaError_t e;
+    if (prefill_supported(format, M, K, N)) {
+        char msg[256] = "";
+        e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
+                           status, &small, msg, sizeof(msg), acts_prepared);
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
+    } else if (gemv_m1_supported(format, M, K, N, false)) {
+        e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else if (gemv_m1_f32_supported(format, M, K, N)) {
+        e = launch_gemv_m1_f32(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else {
+        e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
+                        st, status, &small);
+    }
+    if (small)
+        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_matmul: workspace of %zu bytes is too small, need %zu", ws_bytes,
+                    b200q_workspace_bytes(B200Q_OP_QUANT_MATMUL, format, M, K, N));
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_matmul kernel launch failed: %s", cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int b200q_version(void) { return 100; }
@@ -206,31 +240,7 @@ size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N) {
 
 int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                        size_t K, size_t N, void* ws, size_t ws_bytes, void* stream) {
-    int rc = check_matmul_args("quant_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
-    if (rc) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    unsigned int* status = status_ptr_current();
-    if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul: cannot resolve the device status word");
-    bool small = false;
-    cudaError_t e;
-    if (prefill_supported(format, M, K, N)) {
-        char msg[256] = "";
-        e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
-                           status, &small, msg, sizeof(msg), false);
-        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
-    } else if (gemv_m1_supported(format, M, K, N, false)) {
-        e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
-    } else if (gemv_m1_f32_supported(format, M, K, N)) {
-        e = launch_gemv_m1_f32(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
-    } else {
-        e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
-                        st, status, &small);
-    }
-    if (small)
-        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_matmul: workspace of %zu bytes is too small, need %zu", ws_bytes,
-                    b200q_workspace_bytes(B200Q_OP_QUANT_MATMUL, format, M, K, N));
-    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA quant_matmul kernel launch failed: %s", cudaGetErrorString(e));
-    return B200Q_OK;
+    return quant_matmul_impl(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, stream, false);
 }
 
 }  // extern "C" (reopened below)
@@ -263,6 +273,7 @@ int matmul_batch_impl(const char* op, int n_weights, const int* formats, const v
         ws_bytes -= nbytes;
         norm_w = nullptr;
     }
+    int prepared_cls = -1;
     for (int i = 0; i < n_weights;) {
         // decode (M = 1): runs of up to three Q4_K weights, optionally followed by one Q6_K weight (the
         // q/k/v projections of a Q4_K_M model), go out as ONE launch that streams them side by side
@@ -292,8 +303,13 @@ int matmul_batch_impl(const char* op, int n_weights, const int* formats, const v
                                    norm_w, eps);
             if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA %s kernel launch failed: %s", op, cudaGetErrorString(e));
         } else {
-            int rc = b200q_quant_matmul(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream);
+            // at large M the weights of a batch share the prepared activations (one preparation per class of formats)
+            const bool tc = prefill_supported(formats[i], M, K, N[i]);
+            const int cls = (formats[i] == FMT_Q4_K || formats[i] == FMT_Q5_K || formats[i] == FMT_Q6_K) ? 1 : 0;
+            int rc = quant_matmul_impl(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream,
+                                       tc && prepared_cls == cls);
             if (rc) return rc;
+            prepared_cls = tc ? cls : -1;  // another kernel family may have used the scratch for something else
         }
         i += total;
     }

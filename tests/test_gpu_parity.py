@@ -408,6 +408,22 @@ def test_prefill_swiglu(ops, oracle, fmt):
     assert rel_err(got, want)[0] <= 2e-2  # product of two 1e-2-class results
 
 
+@pytest.mark.parametrize("m", [64, 200])
+def test_prefill_batch_shares_prepared_activations(ops, m):
+    # several weights against one activation matrix at large M: the weights of a class of formats (K-quants / the
+    # others) reuse the activations the first of them prepared; every output must equal the single call's bits
+    rng = synth.rng_for(36, m)
+    k = 1024
+    act = torch.from_numpy(synth.activations(rng, m, k)).cuda()
+    spec = [("Q4_K", 512), ("Q4_K", 136), ("Q6_K", 136), ("Q8_0", 96), ("Q4_0", 64), ("Q5_K", 40), ("Q8_0", 300)]
+    ws = [_qt(f, synth.weight_bytes(f, rng, n, k), n, k) for f, n in spec]
+    outs = ops.quant_matmul_batch(act, ws)
+    ops.check_device_status()
+    for (f, n), w, o in zip(spec, ws, outs):
+        one = ops.quant_matmul(act, w)
+        assert torch.equal(o, one), (f, n)
+
+
 # ------------------------------------------------------------------ tensor-parallel shard shapes (one GPU)
 
 
