@@ -206,16 +206,27 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_f32_kernel(const __grid_consta
 // the same bar as the f32 kernel above, which stays for rows that are not whole 256-runs.
 constexpr uint32_t XB_I8 = 112;  // bytes per 32-block of the image: 3 pieces x 32 codes, 3 block sums; 7 x 16 B keeps lanes' 16-byte reads conflict-free
 
-// One 32-block of a row against the lane's own activation block held in registers: x[6 * 4] = three pieces of 32 codes
-// (Q4_0: even elements then odd elements within a piece), bs = the pieces' block sums.
+// The aligned words covering one 32-block of a row (2-byte aligned in shared memory): loaded first for several rows,
+// so that their latencies overlap, then multiplied.
 template <int FMT>
-__device__ __forceinline__ float block_dot_i8(const uint8_t* blk, const uint4 (&x)[6], const uint4& bs, float xs) {
-    const uint32_t odd = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 2);
-    const uint32_t* A = reinterpret_cast<const uint32_t*>(blk - odd);
-    const uint32_t dsel = odd ? 0x7654u : 0x5432u;
-    uint32_t prev = A[0];
-    const float d = f16bits_to_f32((odd ? prev >> 16 : prev) & 0xFFFFu);
-    int s0 = 0, s1 = 0, s2 = 0;
+struct RawBlk {
+    uint32_t a[FMT == FMT_Q8_0 ? 9 : 5];
+    uint32_t odd;
+};
+template <int FMT>
+__device__ __forceinline__ void load_blk(const uint8_t* blk, RawBlk<FMT>& r) {
+    r.odd = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 2);
+    const uint32_t* A = reinterpret_cast<const uint32_t*>(blk - r.odd);
+#pragma unroll
+    for (int i = 0; i < (FMT == FMT_Q8_0 ? 9 : 5); ++i) r.a[i] = A[i];
+}
+// One 32-block against the lane's own activation block held in registers: x[6] = three pieces of 32 codes (Q4_0: even
+// elements then odd elements within a piece), bs = the pieces' block sums.
+template <int FMT>
+__device__ __forceinline__ float block_dot_i8(const RawBlk<FMT>& r, const uint4 (&x)[6], const uint4& bs, float xs) {
+    const uint32_t dsel = r.odd ? 0x7654u : 0x5432u;
+    const float d = f16bits_to_f32((r.odd ? r.a[0] >> 16 : r.a[0]) & 0xFFFFu);
+    int s0, s1, s2;
     auto dot4 = [](const uint32_t* w, const uint4& a, int acc) {
         acc = __dp4a((int)w[0], (int)a.x, acc);
         acc = __dp4a((int)w[1], (int)a.y, acc);
@@ -225,29 +236,24 @@ __device__ __forceinline__ float block_dot_i8(const uint8_t* blk, const uint4 (&
     if constexpr (FMT == FMT_Q8_0) {
         uint32_t w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t next = A[i + 1];
-            w[i] = __byte_perm(prev, next, dsel);
-            prev = next;
-        }
-        s0 = dot4(w + 4, x[1], dot4(w, x[0], 0));
-        s1 = dot4(w + 4, x[3], dot4(w, x[2], 0));
-        s2 = dot4(w + 4, x[5], dot4(w, x[4], 0));
+        for (int i = 0; i < 8; ++i) w[i] = __byte_perm(r.a[i], r.a[i + 1], dsel);
+        // two chains of four per piece, so six independent dp4a chains
+        s0 = dot4(w, x[0], 0) + dot4(w + 4, x[1], 0);
+        s1 = dot4(w, x[2], 0) + dot4(w + 4, x[3], 0);
+        s2 = dot4(w, x[4], 0) + dot4(w + 4, x[5], 0);
     } else {
         // Q4_0: byte j = elements 2 j (low nibble), 2 j + 1 (high): low-nibble words meet the even codes of a piece,
         // high-nibble words the odd ones; q - 8 through the block sums of the pieces
         uint32_t lo[4], hi[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t next = A[i + 1];
-            const uint32_t w = __byte_perm(prev, next, dsel);
-            prev = next;
+            const uint32_t w = __byte_perm(r.a[i], r.a[i + 1], dsel);
             lo[i] = w & 0x0F0F0F0Fu;
             hi[i] = (w >> 4) & 0x0F0F0F0Fu;
         }
-        s0 = dot4(hi, x[1], dot4(lo, x[0], 0)) - 8 * (int)bs.x;
-        s1 = dot4(hi, x[3], dot4(lo, x[2], 0)) - 8 * (int)bs.y;
-        s2 = dot4(hi, x[5], dot4(lo, x[4], 0)) - 8 * (int)bs.z;
+        s0 = dot4(lo, x[0], 0) + dot4(hi, x[1], 0) - 8 * (int)bs.x;
+        s1 = dot4(lo, x[2], 0) + dot4(hi, x[3], 0) - 8 * (int)bs.y;
+        s2 = dot4(lo, x[4], 0) + dot4(hi, x[5], 0) - 8 * (int)bs.z;
     }
     constexpr float C1 = 1.0f / 254.0f;
     const float f = fmaf(fmaf((float)s2, C1, (float)s1), C1, (float)s0);
@@ -383,15 +389,29 @@ __global__ void __launch_bounds__(512, 1) gemv_m1_i8_kernel(const __grid_constan
         const uint32_t nrows = min(FR, row_end - r0);
         const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(p.w) + (size_t)r0 * p.row_bytes) & 15);
         const uint8_t* base = smem + p.stage_off + slot * p.stage_bytes + phase + (size_t)wi * cb * BB;
-        for (uint32_t rr = 0; rr < nrows && !dead; ++rr) {
-            const uint8_t* row = base + rr * p.row_bytes;
-            float tot = 0.f;
+        // four rows at a time: a row's chain (shared loads, dp4a chains, conversions, five dependent shuffles) is some
+        // 500 cycles long, and independent rows are the only parallelism a warp has (a fill holds a multiple of four)
+        for (uint32_t rr = 0; rr < nrows && !dead; rr += 4) {
+            float tot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < NB; ++j)
-                if (have[j]) tot += block_dot_i8<FMT>(row + ((uint32_t)lane + 32 * j) * BB, xr[j], xbs[j], xsc[j]);
+            for (int j = 0; j < NB; ++j) {
+                RawBlk<FMT> raw[4];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, o);
-            if (lane == 0) part[(slot * FR + rr) * 4 + wi] = tot;
+                for (int u = 0; u < 4; ++u)  // rows past the fill's last read stale bytes of the stage; never used
+                    load_blk<FMT>(base + (rr + u) * p.row_bytes + (have[j] ? (uint32_t)lane + 32 * j : 0u) * BB, raw[u]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (have[j] && rr + u < nrows) tot[u] += block_dot_i8<FMT>(raw[u], xr[j], xbs[j], xsc[j]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) tot[u] += __shfl_xor_sync(0xFFFFFFFFu, tot[u], o);
+            if (lane == 0) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (rr + u < nrows) part[(slot * FR + rr + u) * 4 + wi] = tot[u];
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
