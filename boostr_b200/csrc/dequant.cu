@@ -1,4 +1,4 @@
-// Dequantise packed GGUF blocks (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
+// Dequantise packed GGUF blocks (Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
 //
 // Stands in for boostr's dequant_*_f32 kernels (src/quant/cuda/kernels/dequant.cu:18-206, one
 // thread per block, scalar stores) plus the separate cast pass of CudaClient::dequantize
@@ -84,6 +84,20 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         v[2] = (byte_to_float<1>(lo) - 8.0f) * d; v[3] = (byte_to_float<1>(hi) - 8.0f) * d;
         v[4] = (byte_to_float<2>(lo) - 8.0f) * d; v[5] = (byte_to_float<2>(hi) - 8.0f) * d;
         v[6] = (byte_to_float<3>(lo) - 8.0f) * d; v[7] = (byte_to_float<3>(hi) - 8.0f) * d;
+    } else if constexpr (FMT == FMT_Q5_0) {
+        // block = f16 d | 32 high bits | 16 B nibbles; byte i -> elements 2i (low), 2i+1 (high); element e takes bit e of
+        // the high-bit word (src/quant/cpu/kernels/dequant_simple.rs:66-95)
+        const uint8_t* blk = u + (lane >> 2) * 22;
+        float d = f16bits_to_f32(ldg_u16(blk));
+        const uint32_t hb = (ldg_w(blk + 2) >> (8 * (lane & 3))) & 0xFFu;  // the high bits of this lane's 8 elements
+        const uint32_t w = ldg_w(blk + 6 + 4 * (lane & 3));
+        // even bits -> bit 4 of bytes 0..3 (shifts 4, 10, 16, 22; the stray products and their carries miss bits 4, 12, 20, 28)
+        const uint32_t lo = (w & 0x0F0F0F0Fu) | (((hb & 0x55u) * 0x00410410u) & 0x10101010u);
+        const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) | ((((hb >> 1) & 0x55u) * 0x00410410u) & 0x10101010u);
+        v[0] = (byte_to_float<0>(lo) - 16.0f) * d; v[1] = (byte_to_float<0>(hi) - 16.0f) * d;
+        v[2] = (byte_to_float<1>(lo) - 16.0f) * d; v[3] = (byte_to_float<1>(hi) - 16.0f) * d;
+        v[4] = (byte_to_float<2>(lo) - 16.0f) * d; v[5] = (byte_to_float<2>(hi) - 16.0f) * d;
+        v[6] = (byte_to_float<3>(lo) - 16.0f) * d; v[7] = (byte_to_float<3>(hi) - 16.0f) * d;
     } else if constexpr (FMT == FMT_Q8_0) {
         // block = f16 d | 32 x i8 (dequant_simple.rs:137-155)
         const uint8_t* blk = u + (lane >> 2) * 34;
@@ -328,6 +342,7 @@ cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, in
     case FMT_Q4_0: return launch_dequant_fmt<FMT_Q4_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q8_0: return launch_dequant_fmt<FMT_Q8_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q4_K: return launch_dequant_fmt<FMT_Q4_K>(w, nblocks, out, out_dtype, st, sm_count, status);
+    case FMT_Q5_0: return launch_dequant_fmt<FMT_Q5_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q5_K: return launch_dequant_fmt<FMT_Q5_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q6_K: return launch_dequant_fmt<FMT_Q6_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     default: return cudaErrorInvalidValue;

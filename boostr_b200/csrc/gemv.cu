@@ -353,11 +353,13 @@ template <int P>
 struct TileB<FMT_Q8_0, P> : TileBI8<FMT_Q8_0, P> {};
 template <int P>
 struct TileB<FMT_Q4_0, P> : TileBI8<FMT_Q4_0, P> {};
+template <int P>
+struct TileB<FMT_Q5_0, P> : TileBI8<FMT_Q5_0, P> {};  // Q4_0's element order: even elements in the low nibbles
 
 // pieces per activation value: K-quants none; Q4_0 / Q8_0 three while one 8-row tile is held, two beyond
-__host__ __device__ constexpr int fmt_pieces(int fmt, int mt) { return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? (mt == 1 ? 3 : 2) : 0; }
+__host__ __device__ constexpr int fmt_pieces(int fmt, int mt) { return (fmt == FMT_Q4_0 || fmt == FMT_Q5_0 || fmt == FMT_Q8_0) ? (mt == 1 ? 3 : 2) : 0; }
 __host__ __device__ constexpr int fmt_image_vectors(int fmt, int mt) {
-    return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? 4 * fmt_pieces(fmt, mt) + 1 : 5;
+    return (fmt == FMT_Q4_0 || fmt == FMT_Q5_0 || fmt == FMT_Q8_0) ? 4 * fmt_pieces(fmt, mt) + 1 : 5;
 }
 
 template <int FMT, int MT, int P>
@@ -635,6 +637,22 @@ __device__ __forceinline__ void slice_i8(const SliceB<FMT, MT, P>& B, const uint
                 a2 = word(ra, BB * b + 18 + 4 * t, al);
                 a1 = word(rb, BB * b + 2 + 4 * t, al);
                 a3 = word(rb, BB * b + 18 + 4 * t, al);
+            } else if constexpr (FMT == FMT_Q5_0) {
+                // Q5_0 block = f16 d | 32 high bits | 16 B nibbles, Q4_0's element order; element e takes bit e of the
+                // high-bit word, so the lane's eight elements take byte t of it (even bits: low-nibble elements).  The
+                // 5-bit code c goes to the top of a byte, (c << 3) ^ 0x80 = the int8 value 8 * (c - 16); the factor 8
+                // leaves through the block scale.  (22 * b + 6 and 22 * b + 2 are multiples of 4 for odd b.)
+                const bool al = (b & 1) != 0;
+                const uint32_t wa = word(ra, BB * b + 6 + 4 * t, al), wb = word(rb, BB * b + 6 + 4 * t, al);
+                const uint32_t ha = (word(ra, BB * b + 2, al) >> (8 * t)) & 0xFFu, hb = (word(rb, BB * b + 2, al) >> (8 * t)) & 0xFFu;
+                // even bits of the byte -> bit 7 of bytes 0..3 (shifts 7, 13, 19, 25; stray products and their carries miss those bits)
+                auto top = [](uint32_t bits) { return ((bits & 0x55u) * 0x02082080u) & 0x80808080u; };
+                a0 = (((wa << 3) & 0x78787878u) | top(ha)) ^ 0x80808080u;
+                a2 = (((wa >> 1) & 0x78787878u) | top(ha >> 1)) ^ 0x80808080u;
+                a1 = (((wb << 3) & 0x78787878u) | top(hb)) ^ 0x80808080u;
+                a3 = (((wb >> 1) & 0x78787878u) | top(hb >> 1)) ^ 0x80808080u;
+                dA *= 0.125f;
+                dB *= 0.125f;
             } else {
                 // Q4_0 block = f16 d | 16 B; byte i = elements 2i (low nibble), 2i+1 (high); the lane's word = bytes 4t..4t+3.
                 // (w ^ 0x88..) keeps each nibble as q - 8 in 4-bit two's complement; placed in the high nibble of a byte
@@ -1216,6 +1234,7 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     cudaError_t e;
     switch (fmt) {
     case FMT_Q4_0: e = launch_prep_fmt<FMT_Q4_0>(pp, mt, st); break;
+    case FMT_Q5_0: e = launch_prep_fmt<FMT_Q5_0>(pp, mt, st); break;
     case FMT_Q8_0: e = launch_prep_fmt<FMT_Q8_0>(pp, mt, st); break;
     case FMT_Q4_K: e = launch_prep_fmt<FMT_Q4_K>(pp, mt, st); break;
     case FMT_Q5_K: e = launch_prep_fmt<FMT_Q5_K>(pp, mt, st); break;
@@ -1270,6 +1289,8 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
         switch (fmt) {
         case FMT_Q4_0: e = swiglu ? launch_gemv_fmt<FMT_Q4_0, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
                                   : launch_gemv_fmt<FMT_Q4_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
+        case FMT_Q5_0: e = swiglu ? launch_gemv_fmt<FMT_Q5_0, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
+                                  : launch_gemv_fmt<FMT_Q5_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         case FMT_Q8_0: e = swiglu ? launch_gemv_fmt<FMT_Q8_0, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)
                                   : launch_gemv_fmt<FMT_Q8_0, false>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st); break;
         case FMT_Q4_K: e = swiglu ? launch_gemv_fmt<FMT_Q4_K, true>(p, maps, mt, pl.sl, pl.grid, pl.threads, pl.smem, st)

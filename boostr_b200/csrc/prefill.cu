@@ -66,7 +66,7 @@ namespace {
 
 constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle row of bf16
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
-__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : fmt == FMT_Q5_K ? 176 : 144; }
+__host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : (fmt == FMT_Q5_K || fmt == FMT_Q5_0) ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
 // multiples of 16 bytes, so TMA cannot fetch them: the dequant warps copy them themselves, coalesced, 2 bytes per lane,
 // into rows of 212 bytes (4-byte aligned blocks, conflict-free row-per-thread reads).
@@ -269,6 +269,22 @@ __device__ __forceinline__ void decode32_blk(const uint8_t* blk, uint32_t* o) {
             o[2 * i] = pack_bf16(fmaf(a, code_low<0>(x), c), fmaf(a, code_low<1>(x), c));
             o[2 * i + 1] = pack_bf16(fmaf(a, code_low<2>(x), c), fmaf(a, code_low<3>(x), c));
         }
+    } else if constexpr (FMT == FMT_Q5_0) {
+        // f16 d | 32 high bits | 16 B nibbles (Q4_0's element order; element e takes bit e of the high-bit word):
+        // w = d * (c - 16) = fma(64 d, 2 + c / 64, -144 d)
+        const float a = 64.0f * d, c = -144.0f * d;
+        const uint32_t qh = ld32<SM>(blk + 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t x = ld32<SM>(blk + 6 + 4 * i), hb = (qh >> (8 * i)) & 0xFFu;
+            // even bits of hb -> bit 4 of bytes 0..3 (shifts 4, 10, 16, 22; stray products and their carries miss those bits)
+            const uint32_t lo = (x & 0x0F0F0F0Fu) | (((hb & 0x55u) * 0x00410410u) & 0x10101010u);
+            const uint32_t hi = ((x >> 4) & 0x0F0F0F0Fu) | ((((hb >> 1) & 0x55u) * 0x00410410u) & 0x10101010u);
+            o[4 * i] = pack_bf16(fmaf(a, code_mid<0>(lo), c), fmaf(a, code_mid<0>(hi), c));
+            o[4 * i + 1] = pack_bf16(fmaf(a, code_mid<1>(lo), c), fmaf(a, code_mid<1>(hi), c));
+            o[4 * i + 2] = pack_bf16(fmaf(a, code_mid<2>(lo), c), fmaf(a, code_mid<2>(hi), c));
+            o[4 * i + 3] = pack_bf16(fmaf(a, code_mid<3>(lo), c), fmaf(a, code_mid<3>(hi), c));
+        }
     } else {  // Q4_0: byte i = elements 2i (low nibble), 2i+1 (high)
         const float a = 64.0f * d, c = -136.0f * d;
 #pragma unroll
@@ -358,7 +374,7 @@ __device__ __forceinline__ void decode64_global(const uint8_t* row, uint32_t kt,
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = 0;
     } else {
-        constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
+        constexpr uint32_t BB = fmt_block_bytes(FMT);
         decode32_blk<FMT, false>(row + (2 * kt) * BB, o);
         decode32_blk<FMT, false>(row + (2 * kt + 1) * BB, o + 16);
     }
@@ -475,7 +491,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
                     // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
-                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : FMT == FMT_Q5_K ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : (FMT == FMT_Q5_K || FMT == FMT_Q5_0) ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
                     if (++s == p.nr) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -677,7 +693,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                             decode64_q6k_staged(rrow, sh, set, o);
                         }
                         else {
-                            constexpr uint32_t BB = FMT == FMT_Q8_0 ? 34 : 18;
+                            constexpr uint32_t BB = fmt_block_bytes(FMT);
                             decode32_blk<FMT, true>(rrow + (2 * set) * BB, o);
                             decode32_blk<FMT, true>(rrow + (2 * set + 1) * BB, o + 16);
                         }
@@ -958,7 +974,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
         const bool q8 = fmt == FMT_Q8_0;
         const cuuint64_t wdim[2] = {(cuuint64_t)(q8 ? p.row_bytes / 2 : p.row_bytes), (cuuint64_t)N};
         const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
-        const cuuint32_t wbox[2] = {q8 ? 136u : fmt == FMT_Q5_K ? 176u : 144u, 128u};
+        const cuuint32_t wbox[2] = {q8 ? 136u : (fmt == FMT_Q5_K || fmt == FMT_Q5_0) ? 176u : 144u, 128u};
         cr = enc(&wmap, q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox,
                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -971,6 +987,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     cudaError_t le;
     switch (fmt) {
     case FMT_Q4_0: le = raw ? launch_fmt<FMT_Q4_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q4_0, false>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q5_0: le = raw ? launch_fmt<FMT_Q5_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q5_0, false>(map, wmap, p, grid, smem, st); break;
     case FMT_Q8_0: le = raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st); break;
     case FMT_Q4_K: le = launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st); break;
     case FMT_Q5_K: le = launch_fmt<FMT_Q5_K, true>(map, wmap, p, grid, smem, st); break;

@@ -43,6 +43,14 @@ def q8_0_blocks(rng, nblocks: int, scale: float = 0.004) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q5_0_blocks(rng, nblocks: int, scale: float = 0.01) -> np.ndarray:
+    """Q5_0: f16 d, 32 high bits, 16 bytes of nibbles, all uniform, so the 5-bit codes are uniform 0..31."""
+    out = np.empty((nblocks, 22), dtype=np.uint8)
+    out[:, 0:2] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 2:22] = rng.integers(0, 256, size=(nblocks, 20), dtype=np.uint8)
+    return out.reshape(-1)
+
+
 def pack_q4k_scales(scales: np.ndarray, mins: np.ndarray) -> np.ndarray:
     """[nb,8] 6-bit scales and mins -> [nb,12] packed bytes."""
     s = scales.astype(np.uint8)
@@ -90,6 +98,7 @@ _GEN = {
     QuantFormat.Q8_0: q8_0_blocks,
     QuantFormat.Q4_K: q4_k_blocks,
     QuantFormat.Q5_K: q5_k_blocks,
+    QuantFormat.Q5_0: q5_0_blocks,
     QuantFormat.Q6_K: q6_k_blocks,
 }
 
@@ -113,7 +122,7 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
     f = QuantFormat.parse(fmt)
     nb = n * (k // f.block_size)
     w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device=device, generator=gen)
-    c = {"Q4_0": 0.02, "Q8_0": 0.004, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
+    c = {"Q4_0": 0.02, "Q5_0": 0.01, "Q8_0": 0.004, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
 
     def scale():
         return (torch.randn(nb, device=device, generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)

@@ -49,6 +49,7 @@ typedef enum b200q_status {
 /* Block formats; values are QuantFormat::format_id (src/quant/format.rs:204-230). */
 typedef enum b200q_format {
     B200Q_Q4_0 = 0,
+    B200Q_Q5_0 = 2, /* 22-byte blocks (src/quant/format.rs:114); all row counts through the small-M kernel and, from 64 rows, the tensor-core path */
     B200Q_Q8_0 = 4,
     B200Q_Q4_K = 8,
     B200Q_Q5_K = 9, /* decode shapes run through the small-M kernel; no fused row-/column-parallel exchange */

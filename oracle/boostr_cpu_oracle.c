@@ -45,12 +45,12 @@
 #define ORACLE_API __attribute__((visibility("default")))
 
 /* Format ids follow QuantFormat::format_id (src/quant/format.rs:204-230). */
-enum { FMT_Q4_0 = 0, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
+enum { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
 
 /* block_size / block_bytes: src/quant/format.rs:81-140 */
 ORACLE_API int oracle_block_size(int fmt) {
     switch (fmt) {
-    case FMT_Q4_0: case FMT_Q8_0: return 32;
+    case FMT_Q4_0: case FMT_Q5_0: case FMT_Q8_0: return 32;
     case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
     default: return 0;
     }
@@ -58,6 +58,7 @@ ORACLE_API int oracle_block_size(int fmt) {
 ORACLE_API int oracle_block_bytes(int fmt) {
     switch (fmt) {
     case FMT_Q4_0: return 18;
+    case FMT_Q5_0: return 22;
     case FMT_Q8_0: return 34;
     case FMT_Q4_K: return 144;
     case FMT_Q5_K: return 176;
@@ -107,6 +108,25 @@ static void dequant_q4_0(const uint8_t *blocks, size_t nblocks, float *out) {
         for (int i = 0; i < 16; i++) {
             int lo = (int)(qs[i] & 0x0F) - 8;
             int hi = (int)((qs[i] >> 4) & 0x0F) - 8;
+            o[2 * i] = (float)lo * d;
+            o[2 * i + 1] = (float)hi * d;
+        }
+    }
+}
+
+/* dequant_q5_0: src/quant/cpu/kernels/dequant_simple.rs:66-95.  Block = f16 d | 32 high bits | 16 bytes of nibbles;
+ * element 2 i = low nibble of byte i, element 2 i + 1 = its high nibble (boostr's interleaved order, as for Q4_0),
+ * and element e takes bit e of the high-bit word; value = (5-bit code - 16) * d. */
+static void dequant_q5_0(const uint8_t *blocks, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 22;
+        float d = f16_to_f32(rd16(blk));
+        uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+        const uint8_t *qs = blk + 6;
+        float *o = out + b * 32;
+        for (int i = 0; i < 16; i++) {
+            int lo = (int)((qs[i] & 0x0F) | (((qh >> (2 * i)) & 1u) << 4)) - 16;
+            int hi = (int)(((qs[i] >> 4) & 0x0F) | (((qh >> (2 * i + 1)) & 1u) << 4)) - 16;
             o[2 * i] = (float)lo * d;
             o[2 * i + 1] = (float)hi * d;
         }
@@ -221,6 +241,7 @@ static void dequant_q6k(const uint8_t *blocks, size_t nblocks, float *out) {
 ORACLE_API int oracle_dequant_f32(int fmt, const uint8_t *blocks, size_t nblocks, float *out) {
     switch (fmt) {
     case FMT_Q4_0: dequant_q4_0(blocks, nblocks, out); return 0;
+    case FMT_Q5_0: dequant_q5_0(blocks, nblocks, out); return 0;
     case FMT_Q8_0: dequant_q8_0(blocks, nblocks, out); return 0;
     case FMT_Q4_K: dequant_q4k(blocks, nblocks, out); return 0;
     case FMT_Q5_K: dequant_q5k(blocks, nblocks, out); return 0;

@@ -373,3 +373,50 @@ def test_q5k_matmul_driver_follows_the_avx2_form(oracle):
         q8 = oracle.quantize_q8k(act[i])
         for j in range(n):
             assert out[i, j] == np.float32(oracle.dot_q8k("Q5_K", q8, w.reshape(n, -1)[j].copy(), k, simd=True))
+
+
+# ------------------------------------------------------------------ Q5_0 (src/quant/cpu/kernels/dequant_simple.rs:66-95)
+
+
+def _q5_0_block(d, qh_fill, qs_fill):
+    blk = np.zeros(22, dtype=np.uint8)
+    blk[0:2] = f16b(d)
+    blk[2:6] = qh_fill
+    blk[6:22] = qs_fill
+    return blk
+
+
+def test_q5_0_known_values(oracle):  # dequant_simple.rs:230-257
+    out = oracle.dequantize_f32("Q5_0", _q5_0_block(1.0, 0, 0))
+    assert np.allclose(out, -16.0)
+    out = oracle.dequantize_f32("Q5_0", _q5_0_block(1.0, 0xFF, 0))  # every high bit set, nibbles 0: code 16 -> 0
+    assert np.allclose(out, 0.0)
+
+
+def test_q5_0_order_and_numpy_model(oracle):
+    # element 2 i = low nibble of byte i, element 2 i + 1 = its high nibble, element e takes bit e of the high-bit word
+    rng = np.random.default_rng(50)
+    w = synth.weight_bytes("Q5_0", rng, 7, 96)
+    got = oracle.dequantize_f32("Q5_0", w)
+    blocks = w.reshape(-1, 22)
+    d = blocks[:, 0:2].copy().view(np.float16).astype(np.float32)[:, 0]
+    qh = blocks[:, 2:6].copy().view(np.uint32)[:, 0]
+    qs = blocks[:, 6:22]
+    nib = np.empty((blocks.shape[0], 32), dtype=np.int32)
+    nib[:, 0::2] = qs & 15
+    nib[:, 1::2] = qs >> 4
+    hb = (qh[:, None] >> np.arange(32, dtype=np.uint32)[None, :]) & 1
+    want = ((nib | (hb.astype(np.int32) << 4)) - 16).astype(np.float32) * d[:, None]
+    assert np.array_equal(got.reshape(-1, 32).view(np.uint32), want.view(np.uint32))
+
+
+def test_q5_0_matmul_is_dequant_times_f32(oracle):
+    # Q5_0 takes the dequantised-row path of quant_matmul_f32 (src/quant/cpu/kernels/quant_matmul.rs:193-209)
+    rng = np.random.default_rng(51)
+    m, n, k = 3, 9, 128
+    w = synth.weight_bytes("Q5_0", rng, n, k)
+    act = synth.activations(rng, m, k)
+    got = oracle.quant_matmul("Q5_0", act, w, n, threads=2)
+    deq = oracle.dequantize_f32("Q5_0", w).reshape(n, k).astype(np.float64)
+    want = act.astype(np.float64) @ deq.T
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
