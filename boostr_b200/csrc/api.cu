@@ -40,6 +40,10 @@ size_t prefill_workspace_bytes(int fmt, int act_dtype, size_t M, size_t K, size_
 cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                            size_t K, size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st,
                            unsigned int* status, bool* ws_too_small, char* err, size_t err_len, bool acts_prepared);
+bool kq_generic_supported(int fmt, size_t M, size_t K, size_t N);
+size_t kq_generic_workspace_bytes(size_t M, size_t K);
+cudaError_t launch_kq_generic(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
+                              size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, bool* ws_too_small);
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
                                cudaStream_t st);
 }  // namespace b200q
@@ -99,12 +103,13 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-bool known_format(int f) { return f == FMT_Q4_0 || f == FMT_Q5_0 || f == FMT_Q8_0 || f == FMT_Q4_K || f == FMT_Q5_K || f == FMT_Q6_K; }
+bool known_format(int f) { return f == FMT_Q4_0 || f == FMT_Q5_0 || f == FMT_Q8_0 || f == FMT_Q2_K || f == FMT_Q4_K || f == FMT_Q5_K || f == FMT_Q6_K; }
 const char* format_name(int f) {
     switch (f) {
     case FMT_Q4_0: return "Q4_0";
     case FMT_Q8_0: return "Q8_0";
     case FMT_Q4_K: return "Q4_K";
+    case FMT_Q2_K: return "Q2_K";
     case FMT_Q5_0: return "Q5_0";
     case FMT_Q5_K: return "Q5_K";
     case FMT_Q6_K: return "Q6_K";
@@ -151,6 +156,8 @@ int check_matmul_args(const char* op, int format, const void* act, int act_dtype
 size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, size_t N) {
     if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
     const bool swiglu = op == B200Q_OP_QUANT_SWIGLU;
+    if (kq_generic_supported(format, M, K, N))  // formats without a tuned kernel: the Q8_K image (+ gate and up for SwiGLU)
+        return kq_generic_workspace_bytes(M, K) + (swiglu ? 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255) : 0);
     if (prefill_supported(format, M, K, N)) {
         size_t a = prefill_workspace_bytes(format, act_dtype, M, K, N, sm_count_current());
         // large-M SwiGLU = two prefill GEMMs into scratch, then the gate
@@ -178,7 +185,9 @@ int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w,
     if (!status) return fail(B200Q_ERR_CUDA, "quant_matmul: cannot resolve the device status word");
     bool small = false;
     cudaError_t e;
-    if (prefill_supported(format, M, K, N)) {
+    if (kq_generic_supported(format, M, K, N)) {
+        e = launch_kq_generic(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st, &small);
+    } else if (prefill_supported(format, M, K, N)) {
         char msg[256] = "";
         e = launch_prefill(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st,
                            status, &small, msg, sizeof(msg), acts_prepared);
@@ -350,7 +359,18 @@ int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w
         return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_swiglu: workspace of %zu bytes is too small, need %zu", ws_bytes, need);
     bool small = false;
     cudaError_t e;
-    if (prefill_supported(format, M, K, N)) {
+    if (kq_generic_supported(format, M, K, N)) {
+        // two products into f32 scratch (the second finds the Q8_K image again, it is rebuilt: same bytes), then the gate
+        const size_t mn = (M * N * sizeof(float) + 255) & ~(size_t)255;
+        float* g = static_cast<float*>(ws);
+        float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + mn);
+        uint8_t* rest = static_cast<uint8_t*>(ws) + 2 * mn;
+        const size_t rest_bytes = ws_bytes - 2 * mn;
+        e = launch_kq_generic(format, act, act_dtype, w_gate, g, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, &small);
+        if (e == cudaSuccess && !small)
+            e = launch_kq_generic(format, act, act_dtype, w_up, u, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, &small);
+        if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
+    } else if (prefill_supported(format, M, K, N)) {
         // two tensor-core GEMMs into f32 scratch, then silu(gate) * up
         const size_t mn = (M * N * sizeof(float) + 255) & ~(size_t)255;
         float* g = static_cast<float*>(ws);

@@ -1,4 +1,4 @@
-// Dequantise packed GGUF blocks (Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
+// Dequantise packed GGUF blocks (Q4_0, Q5_0, Q8_0, Q2_K, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
 //
 // Stands in for boostr's dequant_*_f32 kernels (src/quant/cuda/kernels/dequant.cu:18-206, one
 // thread per block, scalar stores) plus the separate cast pass of CudaClient::dequantize
@@ -108,6 +108,22 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         v[2] = (byte_to_float<2>(w0) - 128.0f) * d; v[3] = (byte_to_float<3>(w0) - 128.0f) * d;
         v[4] = (byte_to_float<0>(w1) - 128.0f) * d; v[5] = (byte_to_float<1>(w1) - 128.0f) * d;
         v[6] = (byte_to_float<2>(w1) - 128.0f) * d; v[7] = (byte_to_float<3>(w1) - 128.0f) * d;
+    } else if constexpr (FMT == FMT_Q2_K) {
+        // block = 16 scale bytes (low nibble scale, high nibble min) | 64 B of 2-bit codes | f16 d | f16 dmin; element
+        // e = 128 n + 32 g + 16 h + l takes bits 2g..2g+1 of byte 32 n + 16 h + l and scale byte e / 16
+        // (src/quant/cpu/kernels/dequant_k_quants/q2k_q3k.rs:13-58).  d * sc * q is exact, so the fused form rounds once
+        // exactly like the reference's multiply-then-subtract.
+        const int n = lane >> 4, g = (lane >> 2) & 3, h = (lane >> 1) & 1;
+        const uint32_t dm = *reinterpret_cast<const uint32_t*>(u + 80);
+        const float d = f16bits_to_f32(dm & 0xFFFF), dmin = f16bits_to_f32(dm >> 16);
+        const uint32_t sc = u[lane >> 1];
+        const float dl = d * (float)(sc & 15u), nml = -(dmin * (float)(sc >> 4));
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(u + 16 + 32 * n + 16 * h + 8 * (lane & 1));  // blocks are 4-byte aligned
+        const uint32_t q0 = (w[0] >> (2 * g)) & 0x03030303u, q1 = (w[1] >> (2 * g)) & 0x03030303u;
+        v[0] = fmaf(dl, byte_to_float<0>(q0), nml); v[1] = fmaf(dl, byte_to_float<1>(q0), nml);
+        v[2] = fmaf(dl, byte_to_float<2>(q0), nml); v[3] = fmaf(dl, byte_to_float<3>(q0), nml);
+        v[4] = fmaf(dl, byte_to_float<0>(q1), nml); v[5] = fmaf(dl, byte_to_float<1>(q1), nml);
+        v[6] = fmaf(dl, byte_to_float<2>(q1), nml); v[7] = fmaf(dl, byte_to_float<3>(q1), nml);
     } else if constexpr (FMT == FMT_Q4_K) {
         // block = f16 d | f16 dmin | 12 B packed 6-bit scales/mins | 128 B nibbles
         // (src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:10-47, :108-122)
@@ -342,6 +358,7 @@ cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, in
     case FMT_Q4_0: return launch_dequant_fmt<FMT_Q4_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q8_0: return launch_dequant_fmt<FMT_Q8_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q4_K: return launch_dequant_fmt<FMT_Q4_K>(w, nblocks, out, out_dtype, st, sm_count, status);
+    case FMT_Q2_K: return launch_dequant_fmt<FMT_Q2_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q5_0: return launch_dequant_fmt<FMT_Q5_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q5_K: return launch_dequant_fmt<FMT_Q5_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q6_K: return launch_dequant_fmt<FMT_Q6_K>(w, nblocks, out, out_dtype, st, sm_count, status);

@@ -51,6 +51,15 @@ def q5_0_blocks(rng, nblocks: int, scale: float = 0.01) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q2_k_blocks(rng, nblocks: int, scale: float = 0.01) -> np.ndarray:
+    """Q2_K: 16 scale bytes (4-bit scale, 4-bit min), 64 bytes of 2-bit codes, f16 d, f16 dmin; all fields uniform."""
+    out = np.empty((nblocks, 84), dtype=np.uint8)
+    out[:, 0:80] = rng.integers(0, 256, size=(nblocks, 80), dtype=np.uint8)
+    out[:, 80:82] = _fp16_scale_bytes(rng, nblocks, scale)
+    out[:, 82:84] = _fp16_scale_bytes(rng, nblocks, scale)
+    return out.reshape(-1)
+
+
 def pack_q4k_scales(scales: np.ndarray, mins: np.ndarray) -> np.ndarray:
     """[nb,8] 6-bit scales and mins -> [nb,12] packed bytes."""
     s = scales.astype(np.uint8)
@@ -99,6 +108,7 @@ _GEN = {
     QuantFormat.Q4_K: q4_k_blocks,
     QuantFormat.Q5_K: q5_k_blocks,
     QuantFormat.Q5_0: q5_0_blocks,
+    QuantFormat.Q2_K: q2_k_blocks,
     QuantFormat.Q6_K: q6_k_blocks,
 }
 
@@ -122,12 +132,15 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
     f = QuantFormat.parse(fmt)
     nb = n * (k // f.block_size)
     w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device=device, generator=gen)
-    c = {"Q4_0": 0.02, "Q5_0": 0.01, "Q8_0": 0.004, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
+    c = {"Q4_0": 0.02, "Q5_0": 0.01, "Q8_0": 0.004, "Q2_K": 0.01, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
 
     def scale():
         return (torch.randn(nb, device=device, generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
 
-    if f is QuantFormat.Q6_K:
+    if f is QuantFormat.Q2_K:
+        w[:, 80:82] = scale()
+        w[:, 82:84] = scale()
+    elif f is QuantFormat.Q6_K:
         w[:, 192:208] = torch.randint(-64, 64, (nb, 16), dtype=torch.int8, device=device, generator=gen).view(torch.uint8)
         w[:, 208:210] = scale()
     elif f is QuantFormat.Q8_0:

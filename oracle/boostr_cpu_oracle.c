@@ -45,13 +45,13 @@
 #define ORACLE_API __attribute__((visibility("default")))
 
 /* Format ids follow QuantFormat::format_id (src/quant/format.rs:204-230). */
-enum { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
+enum { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q2_K = 6, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
 
 /* block_size / block_bytes: src/quant/format.rs:81-140 */
 ORACLE_API int oracle_block_size(int fmt) {
     switch (fmt) {
     case FMT_Q4_0: case FMT_Q5_0: case FMT_Q8_0: return 32;
-    case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
+    case FMT_Q2_K: case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -60,6 +60,7 @@ ORACLE_API int oracle_block_bytes(int fmt) {
     case FMT_Q4_0: return 18;
     case FMT_Q5_0: return 22;
     case FMT_Q8_0: return 34;
+    case FMT_Q2_K: return 84;
     case FMT_Q4_K: return 144;
     case FMT_Q5_K: return 176;
     case FMT_Q6_K: return 210;
@@ -235,6 +236,34 @@ static void dequant_q6k(const uint8_t *blocks, size_t nblocks, float *out) {
     }
 }
 
+/* dequant_q2k: src/quant/cpu/kernels/dequant_k_quants/q2k_q3k.rs:13-58.  Block = 16 scale bytes (low nibble: sub-block
+ * scale, high nibble: sub-block min) | 64 bytes of 2-bit codes | f16 d | f16 dmin.  Element e = 128 n + 32 g + 16 h + l
+ * takes bits 2 g .. 2 g + 1 of byte 32 n + 16 h + l and the scale byte e / 16; value = d * sc * q - dmin * m (the
+ * product and the subtraction each rounded, as the reference writes them). */
+static void dequant_q2k(const uint8_t *blocks, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 84;
+        const uint8_t *sc = blk, *qs = blk + 16;
+        float d = f16_to_f32(rd16(blk + 80)), dmin = f16_to_f32(rd16(blk + 82));
+        float *o = out + b * 256;
+        int y = 0, is = 0;
+        for (int n = 0; n < 2; n++) {
+            const uint8_t *q = qs + 32 * n;
+            for (int shift = 0; shift < 8; shift += 2) {
+                for (int h = 0; h < 2; h++) {
+                    float dl = d * (float)(sc[is] & 0x0F);
+                    float ml = dmin * (float)(sc[is] >> 4);
+                    is++;
+                    for (int l = 0; l < 16; l++) {
+                        volatile float p = dl * (float)((q[16 * h + l] >> shift) & 3);  /* no contraction into an FMA */
+                        o[y++] = p - ml;
+                    }
+                }
+            }
+        }
+    }
+}
+
 /* dequant_row_f32 (src/quant/cpu/kernels/quant_matmul.rs:378-407) restricted to the
  * four formats on the path; also the body of CpuClient::dequantize
  * (src/quant/cpu/dequant.rs:91-115). Returns 0, or -1 for an unknown format. */
@@ -243,6 +272,7 @@ ORACLE_API int oracle_dequant_f32(int fmt, const uint8_t *blocks, size_t nblocks
     case FMT_Q4_0: dequant_q4_0(blocks, nblocks, out); return 0;
     case FMT_Q5_0: dequant_q5_0(blocks, nblocks, out); return 0;
     case FMT_Q8_0: dequant_q8_0(blocks, nblocks, out); return 0;
+    case FMT_Q2_K: dequant_q2k(blocks, nblocks, out); return 0;
     case FMT_Q4_K: dequant_q4k(blocks, nblocks, out); return 0;
     case FMT_Q5_K: dequant_q5k(blocks, nblocks, out); return 0;
     case FMT_Q6_K: dequant_q6k(blocks, nblocks, out); return 0;
@@ -558,10 +588,52 @@ static float dot_q5k_q8k(const uint8_t *act_q8k, const uint8_t *w, size_t k, int
     return sumf;
 }
 
+/* fused_dot_q2k_q8k: src/quant/cpu/kernels/simd/fused_q2k_q8k_dot.rs:152-214 (scalar) and :28-137 (AVX2: the same
+ * integers through maddubs / madd).  Per block: summs = sum_j bsums[j] * (sc[j] >> 4) over the sixteen 16-wide sums of
+ * the activation block, isum = sum_j (sc[j] & 15) * sum_l q * a, sumf += (d * d8) * isum - (dmin * d8) * summs. */
+static float dot_q2k_q8k(const uint8_t *act_q8k, const uint8_t *w, size_t k) {
+    size_t nb = k / 256;
+    float sumf = 0.0f;
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = w + b * 84;
+        const uint8_t *sc = blk, *qs = blk + 16;
+        float d = f16_to_f32(rd16(blk + 80)), dmin = f16_to_f32(rd16(blk + 82));
+        const uint8_t *a = act_q8k + b * Q8K_BLOCK_BYTES;
+        float d8;
+        memcpy(&d8, a, 4);
+        const int8_t *q8 = (const int8_t *)(a + 4);
+        const uint8_t *bs = a + 260;
+        float dall = d * d8, dmin_all = dmin * d8;
+        int32_t summs = 0;
+        for (int j = 0; j < 16; j++) {
+            int16_t v;
+            memcpy(&v, bs + 2 * j, 2);
+            summs += (int32_t)v * (int32_t)(sc[j] >> 4);
+        }
+        int32_t isum = 0;
+        int is = 0, off = 0;
+        for (int n = 0; n < 2; n++) {
+            const uint8_t *q = qs + 32 * n;
+            for (int shift = 0; shift < 8; shift += 2) {
+                for (int h = 0; h < 2; h++) {
+                    int32_t isuml = 0;
+                    for (int l = 0; l < 16; l++) isuml += (int32_t)q8[off + 16 * h + l] * (int32_t)((q[16 * h + l] >> shift) & 3);
+                    isum += (int32_t)(sc[is++] & 0x0F) * isuml;
+                }
+                off += 32;
+            }
+        }
+        volatile float t1 = dall * (float)isum, t2 = dmin_all * (float)summs;  /* no contraction */
+        sumf += t1 - t2;
+    }
+    return sumf;
+}
+
 /* simd: 1 = the forms the reference runs on x86-64 (AVX2), 0 = its scalar fallbacks.  For Q4_K and Q6_K the two give
  * identical bits; for Q5_K they are different functions of the weight bytes (see dot_q5k_q8k). */
 ORACLE_API float oracle_dot_q8k(int fmt, const uint8_t *act_q8k, const uint8_t *w, size_t k, int simd) {
     if (fmt == FMT_Q5_K) return dot_q5k_q8k(act_q8k, w, k, simd ? 0 : 1);
+    if (fmt == FMT_Q2_K) return dot_q2k_q8k(act_q8k, w, k);  /* the AVX2 form computes the same integers */
 #if defined(__AVX2__)
     if (simd) return fmt == FMT_Q4_K ? dot_q4k_q8k_avx2(act_q8k, w, k) : dot_q6k_q8k_avx2(act_q8k, w, k);
 #endif
@@ -722,7 +794,7 @@ ORACLE_API int oracle_quant_matmul(int fmt, const float *act, const uint8_t *w, 
     if (k % (size_t)bs) return -2;
     if (threads <= 0) threads = 1;
     size_t row_bytes = (k / (size_t)bs) * (size_t)oracle_block_bytes(fmt);
-    int kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
+    int kq = (fmt == FMT_Q2_K || fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     size_t q8k_row = (k / 256) * Q8K_BLOCK_BYTES;
     uint8_t *aq = NULL;
     if (kq) {

@@ -420,3 +420,74 @@ def test_q5_0_matmul_is_dequant_times_f32(oracle):
     deq = oracle.dequantize_f32("Q5_0", w).reshape(n, k).astype(np.float64)
     want = act.astype(np.float64) @ deq.T
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+
+# ------------------------------------------------------------------ Q2_K (dequant_k_quants/q2k_q3k.rs:13-58, simd/fused_q2k_q8k_dot.rs)
+
+
+def _q2k_numpy(w):
+    """Independent restatement: element e = 128 n + 32 g + 16 h + l <- bits 2g..2g+1 of qs[32 n + 16 h + l], scale byte e // 16."""
+    blocks = w.reshape(-1, 84)
+    sc, qs = blocks[:, 0:16].astype(np.int32), blocks[:, 16:80].astype(np.int32)
+    d = blocks[:, 80:82].copy().view(np.float16).astype(np.float32)[:, 0]
+    dmin = blocks[:, 82:84].copy().view(np.float16).astype(np.float32)[:, 0]
+    e = np.arange(256)
+    n, g, h, l = e // 128, (e % 128) // 32, (e % 32) // 16, e % 16
+    q = (qs[:, 32 * n + 16 * h + l] >> (2 * g)) & 3
+    s = sc[:, e // 16]
+    dl = d[:, None] * (s & 15).astype(np.float32)
+    ml = dmin[:, None] * (s >> 4).astype(np.float32)
+    return (dl * q.astype(np.float32)).astype(np.float32) - ml, q, s
+
+
+def test_q2k_dequant_matches_numpy_model(oracle):
+    rng = np.random.default_rng(60)
+    w = synth.weight_bytes("Q2_K", rng, 5, 512)
+    got = oracle.dequantize_f32("Q2_K", w).reshape(-1, 256)
+    want, _, _ = _q2k_numpy(w)
+    assert np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32))
+
+
+def test_q2k_zero_and_simple_blocks(oracle):
+    blk = np.zeros(84, np.uint8)
+    assert np.all(oracle.dequantize_f32("Q2_K", blk) == 0.0)
+    blk[80:82] = f16b(1.0)   # d
+    blk[82:84] = f16b(0.5)   # dmin
+    blk[0:16] = 0x21         # scale 1, min 2
+    blk[16:80] = 0xFF        # every code 3
+    assert np.all(oracle.dequantize_f32("Q2_K", blk) == 3.0 - 1.0)
+
+
+@pytest.mark.parametrize("mk", [(1, 256), (3, 1024)])
+def test_q2k_q8k_dot_vs_f32_reference_tolerance(oracle, mk):  # fused_q2k_q8k_dot.rs:224-286: 2 % + 1.0
+    m, k = mk
+    rng = np.random.default_rng(61)
+    n = 7
+    w = synth.weight_bytes("Q2_K", rng, n, k)
+    act = synth.activations(rng, m, k)
+    got = oracle.quant_matmul("Q2_K", act, w, n, threads=2)
+    ref = act.astype(np.float64) @ oracle.dequantize_f32("Q2_K", w).reshape(n, k).astype(np.float64).T
+    assert np.all(np.abs(got - ref) <= 0.02 * np.abs(ref) + 1.0)
+    # and tightly against an integer restatement of the same formula on the quantised activations
+    _, q, s = _q2k_numpy(w)
+    q = q.reshape(n, k // 256, 256)
+    s = s.reshape(n, k // 256, 256)
+    blocks = w.reshape(n, k // 256, 84)
+    d = blocks[:, :, 80:82].copy().view(np.float16).astype(np.float32)[:, :, 0]
+    dmin = blocks[:, :, 82:84].copy().view(np.float16).astype(np.float32)[:, :, 0]
+    a = act.reshape(m, k // 256, 256)
+    amax = np.abs(a).max(axis=2)
+    idv = np.where(amax != 0, np.float32(127.0) / amax, 0).astype(np.float32)
+    codes = np.clip(np.rint((a * idv[:, :, None]).astype(np.float32)), -128, 127).astype(np.int64)
+    d8 = (amax / np.float32(127.0)).astype(np.float32)
+    want = np.zeros((m, n), np.float32)
+    for i in range(m):
+        for j in range(n):
+            acc = np.float32(0)
+            for b in range(k // 256):
+                isum = int(((s[j, b] & 15) * q[j, b] * codes[i, b]).sum())
+                summs = int(((s[j, b] >> 4) * codes[i, b]).sum())
+                t = np.float32(np.float32(d[j, b] * d8[i, b]) * np.float32(isum)) - np.float32(np.float32(dmin[j, b] * d8[i, b]) * np.float32(summs))
+                acc = np.float32(acc + np.float32(t))
+            want[i, j] = acc
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
