@@ -103,13 +103,14 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-bool known_format(int f) { return f == FMT_Q4_0 || f == FMT_Q5_0 || f == FMT_Q8_0 || f == FMT_Q2_K || f == FMT_Q4_K || f == FMT_Q5_K || f == FMT_Q6_K; }
+bool known_format(int f) { return f == FMT_Q4_0 || f == FMT_Q5_0 || f == FMT_Q8_0 || f == FMT_Q2_K || f == FMT_Q3_K || f == FMT_Q4_K || f == FMT_Q5_K || f == FMT_Q6_K; }
 const char* format_name(int f) {
     switch (f) {
     case FMT_Q4_0: return "Q4_0";
     case FMT_Q8_0: return "Q8_0";
     case FMT_Q4_K: return "Q4_K";
     case FMT_Q2_K: return "Q2_K";
+    case FMT_Q3_K: return "Q3_K";
     case FMT_Q5_0: return "Q5_0";
     case FMT_Q5_K: return "Q5_K";
     case FMT_Q6_K: return "Q6_K";

@@ -13,7 +13,7 @@
 namespace b200q {
 
 // Block formats (QuantFormat::format_id of the reference).
-enum : int { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q2_K = 6, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
+enum : int { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q2_K = 6, FMT_Q3_K = 7, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
 enum : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_F64 = 3 };
 
 // Device status word (one per device, owned by the C-ABI translation unit and handed to
@@ -23,7 +23,7 @@ enum : unsigned { STATUS_TIMEOUT_FULL = 1u, STATUS_TIMEOUT_EMPTY = 2u, STATUS_TI
 
 __host__ __device__ constexpr int fmt_block_size(int f) { return (f == FMT_Q4_0 || f == FMT_Q5_0 || f == FMT_Q8_0) ? 32 : 256; }
 __host__ __device__ constexpr int fmt_block_bytes(int f) {
-    return f == FMT_Q4_0 ? 18 : f == FMT_Q5_0 ? 22 : f == FMT_Q8_0 ? 34 : f == FMT_Q2_K ? 84 : f == FMT_Q4_K ? 144 : f == FMT_Q5_K ? 176 : f == FMT_Q6_K ? 210 : 0;
+    return f == FMT_Q4_0 ? 18 : f == FMT_Q5_0 ? 22 : f == FMT_Q8_0 ? 34 : f == FMT_Q2_K ? 84 : f == FMT_Q3_K ? 110 : f == FMT_Q4_K ? 144 : f == FMT_Q5_K ? 176 : f == FMT_Q6_K ? 210 : 0;
 }
 // Bytes of one 256-element run of a row ("slice"): the unit one warp of the small-M kernel owns.
 __host__ __device__ constexpr int fmt_slice_bytes(int f) { return fmt_block_bytes(f) * (256 / fmt_block_size(f)); }

@@ -1,4 +1,4 @@
-// Dequantise packed GGUF blocks (Q4_0, Q5_0, Q8_0, Q2_K, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
+// Dequantise packed GGUF blocks (Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K) straight to f32 / bf16 / f16 / f64.
 //
 // Stands in for boostr's dequant_*_f32 kernels (src/quant/cuda/kernels/dequant.cu:18-206, one
 // thread per block, scalar stores) plus the separate cast pass of CudaClient::dequantize
@@ -124,6 +124,24 @@ __device__ __forceinline__ void decode8(const uint8_t* u, int lane, float (&v)[8
         v[2] = fmaf(dl, byte_to_float<2>(q0), nml); v[3] = fmaf(dl, byte_to_float<3>(q0), nml);
         v[4] = fmaf(dl, byte_to_float<0>(q1), nml); v[5] = fmaf(dl, byte_to_float<1>(q1), nml);
         v[6] = fmaf(dl, byte_to_float<2>(q1), nml); v[7] = fmaf(dl, byte_to_float<3>(q1), nml);
+    } else if constexpr (FMT == FMT_Q3_K) {
+        // block = 32 B high-bit masks | 64 B of 2-bit codes | 12 B packed 6-bit scales | f16 d (2-byte aligned); element
+        // e = 128 n + 32 g + 16 h + l: low bits 2g..2g+1 of qs[32 n + 16 h + l], high bit 4 n + g of hmask[16 h + l], a
+        // clear high bit subtracts 4; scale e / 16 (src/quant/cpu/kernels/dequant_k_quants/q2k_q3k.rs:64-144).
+        // (d * scale) * (code - 4) is exact in f32.
+        const int n = lane >> 4, g = (lane >> 2) & 3, h = (lane >> 1) & 1, j = lane >> 1;
+        const float d = f16bits_to_f32(ldg_u16(u + 108));
+        const uint32_t low4 = ((uint32_t)u[96 + (j & 7)] >> (4 * (j >> 3))) & 15u, high2 = ((uint32_t)u[104 + (j & 3)] >> (2 * (j >> 2))) & 3u;
+        const float dl = d * (float)((int)(low4 | (high2 << 4)) - 32);
+        const uint8_t* qp = u + 32 + 32 * n + 16 * h + 8 * (lane & 1);
+        const uint8_t* hp = u + 16 * h + 8 * (lane & 1);
+        const uint32_t q0 = (ldg_w(qp) >> (2 * g)) & 0x03030303u, q1 = (ldg_w(qp + 4) >> (2 * g)) & 0x03030303u;
+        const uint32_t h0 = (ldg_w(hp) >> (4 * n + g)) & 0x01010101u, h1 = (ldg_w(hp + 4) >> (4 * n + g)) & 0x01010101u;
+        const uint32_t c0 = q0 | (h0 << 2), c1 = q1 | (h1 << 2);  // codes 0..7
+        v[0] = dl * (byte_to_float<0>(c0) - 4.0f); v[1] = dl * (byte_to_float<1>(c0) - 4.0f);
+        v[2] = dl * (byte_to_float<2>(c0) - 4.0f); v[3] = dl * (byte_to_float<3>(c0) - 4.0f);
+        v[4] = dl * (byte_to_float<0>(c1) - 4.0f); v[5] = dl * (byte_to_float<1>(c1) - 4.0f);
+        v[6] = dl * (byte_to_float<2>(c1) - 4.0f); v[7] = dl * (byte_to_float<3>(c1) - 4.0f);
     } else if constexpr (FMT == FMT_Q4_K) {
         // block = f16 d | f16 dmin | 12 B packed 6-bit scales/mins | 128 B nibbles
         // (src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:10-47, :108-122)
@@ -359,6 +377,7 @@ cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, in
     case FMT_Q8_0: return launch_dequant_fmt<FMT_Q8_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q4_K: return launch_dequant_fmt<FMT_Q4_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q2_K: return launch_dequant_fmt<FMT_Q2_K>(w, nblocks, out, out_dtype, st, sm_count, status);
+    case FMT_Q3_K: return launch_dequant_fmt<FMT_Q3_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q5_0: return launch_dequant_fmt<FMT_Q5_0>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q5_K: return launch_dequant_fmt<FMT_Q5_K>(w, nblocks, out, out_dtype, st, sm_count, status);
     case FMT_Q6_K: return launch_dequant_fmt<FMT_Q6_K>(w, nblocks, out, out_dtype, st, sm_count, status);

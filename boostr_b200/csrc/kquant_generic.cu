@@ -1,8 +1,9 @@
-// Quantized matmul for the K-quant formats that have no tuned kernel yet (Q2_K): correct on every shape, not fast.
+// Quantized matmul for the K-quant formats that have no tuned kernel yet (Q2_K, Q3_K): correct on every shape, not fast.
 //
 // boostr's CPU path for these formats (src/quant/cpu/kernels/quant_matmul.rs:107-135) quantises each activation row to
 // Q8_K (src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98) and takes an integer dot product per 256-block
-// (src/quant/cpu/kernels/simd/fused_q2k_q8k_dot.rs:152-214): sumf += (d * d8) * isum - (dmin * d8) * summs.  The
+// (src/quant/cpu/kernels/simd/fused_q2k_q8k_dot.rs:152-214, fused_q3k_q8k_dot.rs:33-205 in the form x86-64 runs):
+// sumf += (d * d8) * isum - (dmin * d8) * summs (Q3_K: no min term).  The
 // integer sums are exact and the blocks are added in K order without FMA contraction, so the result has the CPU's bits.
 //
 //   * kq_act_prep_kernel: one warp per (activation row, 256-block) writes the Q8_K block in the CPU's own layout
@@ -99,6 +100,33 @@ __device__ __forceinline__ LaneBlk load_lane_blk<FMT_Q2_K>(const uint8_t* blk, i
     return r;
 }
 
+// Q3_K (q2k_q3k.rs:64-144): low two bits as Q2_K from the 64 code bytes at offset 32, the high bit 4 n + g of
+// hmask[16 h + l], a clear high bit subtracts 4; sixteen 6-bit scales minus 32, no min term.  Blocks (110 bytes) are only
+// 2-byte aligned.  The codes minus 4 leave as signed bytes.
+template <>
+__device__ __forceinline__ LaneBlk load_lane_blk<FMT_Q3_K>(const uint8_t* blk, int lane) {
+    LaneBlk r;
+    const int n = lane >> 4, g = (lane >> 2) & 3, h = (lane >> 1) & 1, j = lane >> 1;
+    auto w32 = [](const uint8_t* p) {
+        const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
+        return (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
+    };
+    const uint8_t* qp = blk + 32 + 32 * n + 16 * h + 8 * (lane & 1);
+    const uint8_t* hp = blk + 16 * h + 8 * (lane & 1);
+    const uint32_t c0 = ((w32(qp) >> (2 * g)) & 0x03030303u) | (((w32(hp) >> (4 * n + g)) & 0x01010101u) << 2);
+    const uint32_t c1 = ((w32(qp + 4) >> (2 * g)) & 0x03030303u) | (((w32(hp + 4) >> (4 * n + g)) & 0x01010101u) << 2);
+    // per byte c - 4 in two's complement: the set top bit keeps the subtraction inside its byte
+    r.q0 = ((c0 | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
+    r.q1 = ((c1 | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
+    const uint32_t low4 = ((uint32_t)__ldg(blk + 96 + (j & 7)) >> (4 * (j >> 3))) & 15u;
+    const uint32_t high2 = ((uint32_t)__ldg(blk + 104 + (j & 3)) >> (2 * (j >> 2))) & 3u;
+    r.sc = (int)(low4 | (high2 << 4)) - 32;
+    r.mn = 0;
+    r.d = f16bits_to_f32(__ldg(reinterpret_cast<const unsigned short*>(blk + 108)));
+    r.dmin = 0.f;
+    return r;
+}
+
 constexpr int KQ_MC = 8;  // activation rows per pass
 
 template <int FMT>
@@ -151,7 +179,7 @@ __global__ void __launch_bounds__(256) kq_generic_kernel(const KqParams p) {
 
 }  // namespace
 
-bool kq_generic_supported(int fmt, size_t M, size_t K, size_t N) { return fmt == FMT_Q2_K && M >= 1 && N >= 1 && K % 256 == 0; }
+bool kq_generic_supported(int fmt, size_t M, size_t K, size_t N) { return (fmt == FMT_Q2_K || fmt == FMT_Q3_K) && M >= 1 && N >= 1 && K % 256 == 0; }
 
 size_t kq_generic_workspace_bytes(size_t M, size_t K) { return (M * (K / 256) * Q8K_BYTES + 255) & ~(size_t)255; }
 
@@ -179,8 +207,9 @@ cudaError_t launch_kq_generic(int fmt, const void* act, int act_dtype, const voi
     p.out_dtype = out_dtype;
     size_t g2 = (N + 7) / 8;
     if (g2 > (size_t)sm_count * 8) g2 = (size_t)sm_count * 8;
-    if (fmt != FMT_Q2_K) return cudaErrorInvalidValue;
-    kq_generic_kernel<FMT_Q2_K><<<(unsigned)g2, 256, 0, st>>>(p);
+    if (fmt == FMT_Q2_K) kq_generic_kernel<FMT_Q2_K><<<(unsigned)g2, 256, 0, st>>>(p);
+    else if (fmt == FMT_Q3_K) kq_generic_kernel<FMT_Q3_K><<<(unsigned)g2, 256, 0, st>>>(p);
+    else return cudaErrorInvalidValue;
     note_launch();
     return cudaGetLastError();
 }

@@ -1,7 +1,7 @@
 """Block formats of the quantized-linear path.
 
 Mirrors ``QuantFormat`` (src/quant/format.rs:23-230) for the GGUF formats this library
-implements: Q4_0, Q5_0, Q8_0, Q2_K, Q4_K, Q5_K and Q6_K.  Blocks are packed along the last (K) axis of a row-major tensor and
+implements: Q4_0, Q5_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K and Q6_K.  Blocks are packed along the last (K) axis of a row-major tensor and
 rows carry no padding (src/quant/format.rs:5-20).
 """
 from __future__ import annotations
@@ -19,6 +19,7 @@ class QuantFormat(enum.Enum):
     Q5_0 = 2
     Q8_0 = 4
     Q2_K = 6
+    Q3_K = 7
     Q4_K = 8
     Q5_K = 9
     Q6_K = 10
@@ -29,11 +30,11 @@ class QuantFormat(enum.Enum):
 
     @property
     def block_bytes(self) -> int:  # src/quant/format.rs:110-140
-        return {QuantFormat.Q4_0: 18, QuantFormat.Q5_0: 22, QuantFormat.Q8_0: 34, QuantFormat.Q2_K: 84, QuantFormat.Q4_K: 144, QuantFormat.Q5_K: 176, QuantFormat.Q6_K: 210}[self]
+        return {QuantFormat.Q4_0: 18, QuantFormat.Q5_0: 22, QuantFormat.Q8_0: 34, QuantFormat.Q2_K: 84, QuantFormat.Q3_K: 110, QuantFormat.Q4_K: 144, QuantFormat.Q5_K: 176, QuantFormat.Q6_K: 210}[self]
 
     @property
     def ggml_type_id(self) -> int:  # src/quant/format.rs:174-200
-        return {QuantFormat.Q4_0: 2, QuantFormat.Q5_0: 6, QuantFormat.Q8_0: 8, QuantFormat.Q2_K: 10, QuantFormat.Q4_K: 12, QuantFormat.Q5_K: 13, QuantFormat.Q6_K: 14}[self]
+        return {QuantFormat.Q4_0: 2, QuantFormat.Q5_0: 6, QuantFormat.Q8_0: 8, QuantFormat.Q2_K: 10, QuantFormat.Q3_K: 11, QuantFormat.Q4_K: 12, QuantFormat.Q5_K: 13, QuantFormat.Q6_K: 14}[self]
 
     @property
     def format_id(self) -> int:
@@ -61,6 +62,6 @@ class QuantFormat(enum.Enum):
         if isinstance(x, cls):
             return x
         if isinstance(x, str):
-            key = x.upper().replace("Q2K", "Q2_K").replace("Q4K", "Q4_K").replace("Q5K", "Q5_K").replace("Q6K", "Q6_K")
+            key = x.upper().replace("Q2K", "Q2_K").replace("Q3K", "Q3_K").replace("Q4K", "Q4_K").replace("Q5K", "Q5_K").replace("Q6K", "Q6_K")
             return cls[key]
         return cls(int(x))

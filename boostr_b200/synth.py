@@ -60,6 +60,14 @@ def q2_k_blocks(rng, nblocks: int, scale: float = 0.01) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q3_k_blocks(rng, nblocks: int, scale: float = 0.002) -> np.ndarray:
+    """Q3_K: 32 B high-bit masks, 64 B of 2-bit codes, 12 B packed 6-bit scales, f16 d; all fields uniform."""
+    out = np.empty((nblocks, 110), dtype=np.uint8)
+    out[:, 0:108] = rng.integers(0, 256, size=(nblocks, 108), dtype=np.uint8)
+    out[:, 108:110] = _fp16_scale_bytes(rng, nblocks, scale)
+    return out.reshape(-1)
+
+
 def pack_q4k_scales(scales: np.ndarray, mins: np.ndarray) -> np.ndarray:
     """[nb,8] 6-bit scales and mins -> [nb,12] packed bytes."""
     s = scales.astype(np.uint8)
@@ -109,6 +117,7 @@ _GEN = {
     QuantFormat.Q5_K: q5_k_blocks,
     QuantFormat.Q5_0: q5_0_blocks,
     QuantFormat.Q2_K: q2_k_blocks,
+    QuantFormat.Q3_K: q3_k_blocks,
     QuantFormat.Q6_K: q6_k_blocks,
 }
 
@@ -132,7 +141,7 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
     f = QuantFormat.parse(fmt)
     nb = n * (k // f.block_size)
     w = torch.randint(0, 256, (nb, f.block_bytes), dtype=torch.uint8, device=device, generator=gen)
-    c = {"Q4_0": 0.02, "Q5_0": 0.01, "Q8_0": 0.004, "Q2_K": 0.01, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
+    c = {"Q4_0": 0.02, "Q5_0": 0.01, "Q8_0": 0.004, "Q2_K": 0.01, "Q3_K": 0.002, "Q4_K": 0.002, "Q5_K": 0.002, "Q6_K": 0.0005}[f.name]
 
     def scale():
         return (torch.randn(nb, device=device, generator=gen).abs() * c).to(torch.float16).view(torch.uint8).reshape(nb, 2)
@@ -140,6 +149,8 @@ def device_weight(fmt, n: int, k: int, gen, device="cuda"):
     if f is QuantFormat.Q2_K:
         w[:, 80:82] = scale()
         w[:, 82:84] = scale()
+    elif f is QuantFormat.Q3_K:
+        w[:, 108:110] = scale()
     elif f is QuantFormat.Q6_K:
         w[:, 192:208] = torch.randint(-64, 64, (nb, 16), dtype=torch.int8, device=device, generator=gen).view(torch.uint8)
         w[:, 208:210] = scale()

@@ -52,6 +52,7 @@ typedef enum b200q_format {
     B200Q_Q5_0 = 2, /* 22-byte blocks (src/quant/format.rs:114); all row counts through the small-M kernel and, from 64 rows, the tensor-core path */
     B200Q_Q8_0 = 4,
     B200Q_Q2_K = 6, /* dequantize at full speed; matmul through a generic integer-dot kernel (exact CPU numerics, not tuned) */
+    B200Q_Q3_K = 7, /* as Q2_K */
     B200Q_Q4_K = 8,
     B200Q_Q5_K = 9, /* decode shapes run through the small-M kernel; no fused row-/column-parallel exchange */
     B200Q_Q6_K = 10

@@ -45,13 +45,13 @@
 #define ORACLE_API __attribute__((visibility("default")))
 
 /* Format ids follow QuantFormat::format_id (src/quant/format.rs:204-230). */
-enum { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q2_K = 6, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
+enum { FMT_Q4_0 = 0, FMT_Q5_0 = 2, FMT_Q8_0 = 4, FMT_Q2_K = 6, FMT_Q3_K = 7, FMT_Q4_K = 8, FMT_Q5_K = 9, FMT_Q6_K = 10 };
 
 /* block_size / block_bytes: src/quant/format.rs:81-140 */
 ORACLE_API int oracle_block_size(int fmt) {
     switch (fmt) {
     case FMT_Q4_0: case FMT_Q5_0: case FMT_Q8_0: return 32;
-    case FMT_Q2_K: case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
+    case FMT_Q2_K: case FMT_Q3_K: case FMT_Q4_K: case FMT_Q5_K: case FMT_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -61,6 +61,7 @@ ORACLE_API int oracle_block_bytes(int fmt) {
     case FMT_Q5_0: return 22;
     case FMT_Q8_0: return 34;
     case FMT_Q2_K: return 84;
+    case FMT_Q3_K: return 110;
     case FMT_Q4_K: return 144;
     case FMT_Q5_K: return 176;
     case FMT_Q6_K: return 210;
@@ -264,6 +265,41 @@ static void dequant_q2k(const uint8_t *blocks, size_t nblocks, float *out) {
     }
 }
 
+/* unpack_q3k_scales: src/quant/cpu/kernels/dequant_k_quants/q2k_q3k.rs:115-144.  Sixteen 6-bit scales from 12 bytes:
+ * low four bits from the nibbles of bytes 0..7, high two bits from the bit pairs of bytes 8..11; value - 32. */
+static void unpack_q3k_scales(const uint8_t *sc, int8_t *out) {
+    for (int j = 0; j < 16; j++) {
+        int low4 = (sc[j & 7] >> (4 * (j >> 3))) & 15;
+        int high2 = (sc[8 + (j & 3)] >> (2 * (j >> 2))) & 3;
+        out[j] = (int8_t)((low4 | (high2 << 4)) - 32);
+    }
+}
+
+/* The 3-bit code minus 4 of element e = 128 n + 32 g + 16 h + l of a Q3_K block: two low bits from qs[32 n + 16 h + l]
+ * (bits 2g..2g+1), the high bit from hmask[16 h + l] (bit 4 n + g); a clear high bit subtracts 4
+ * (q2k_q3k.rs:64-110). */
+static inline int q3k_code(const uint8_t *blk, int e) {
+    int n = e >> 7, g = (e >> 5) & 3, hl = e & 31;
+    int low2 = (blk[32 + 32 * n + hl] >> (2 * g)) & 3;
+    int hbit = (blk[hl] >> (4 * n + g)) & 1;
+    return low2 - (hbit ? 0 : 4);
+}
+
+/* dequant_q3k: src/quant/cpu/kernels/dequant_k_quants/q2k_q3k.rs:64-110.  Block = 32 B high-bit masks | 64 B of 2-bit
+ * codes | 12 B packed scales | f16 d; value = (d * scale[e / 16]) * (code - 4). */
+static void dequant_q3k(const uint8_t *blocks, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = blocks + b * 110;
+        int8_t scales[16];
+        unpack_q3k_scales(blk + 96, scales);
+        float d = f16_to_f32(rd16(blk + 108));
+        for (int e = 0; e < 256; e++) {
+            float dl = d * (float)scales[e >> 4];
+            out[b * 256 + e] = dl * (float)q3k_code(blk, e);
+        }
+    }
+}
+
 /* dequant_row_f32 (src/quant/cpu/kernels/quant_matmul.rs:378-407) restricted to the
  * four formats on the path; also the body of CpuClient::dequantize
  * (src/quant/cpu/dequant.rs:91-115). Returns 0, or -1 for an unknown format. */
@@ -273,6 +309,7 @@ ORACLE_API int oracle_dequant_f32(int fmt, const uint8_t *blocks, size_t nblocks
     case FMT_Q5_0: dequant_q5_0(blocks, nblocks, out); return 0;
     case FMT_Q8_0: dequant_q8_0(blocks, nblocks, out); return 0;
     case FMT_Q2_K: dequant_q2k(blocks, nblocks, out); return 0;
+    case FMT_Q3_K: dequant_q3k(blocks, nblocks, out); return 0;
     case FMT_Q4_K: dequant_q4k(blocks, nblocks, out); return 0;
     case FMT_Q5_K: dequant_q5k(blocks, nblocks, out); return 0;
     case FMT_Q6_K: dequant_q6k(blocks, nblocks, out); return 0;
@@ -629,10 +666,42 @@ static float dot_q2k_q8k(const uint8_t *act_q8k, const uint8_t *w, size_t k) {
     return sumf;
 }
 
+/* fused_dot_q3k_q8k.  scalar_form = 0: the AVX2 form x86-64 runs (src/quant/cpu/kernels/simd/fused_q3k_q8k_dot.rs:33-205):
+ * one integer sum per block, sumf += (d * d8) * isum.  scalar_form = 1: the scalar fallback (:225-292), which keeps eight
+ * float accumulators (element index mod 8) across blocks and adds them at the end.  Same integers, different f32 sums. */
+static float dot_q3k_q8k(const uint8_t *act_q8k, const uint8_t *w, size_t k, int scalar_form) {
+    size_t nb = k / 256;
+    float sumf = 0.0f, sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = w + b * 110;
+        int8_t scales[16];
+        unpack_q3k_scales(blk + 96, scales);
+        float d_all = f16_to_f32(rd16(blk + 108));
+        const uint8_t *a = act_q8k + b * Q8K_BLOCK_BYTES;
+        float d8;
+        memcpy(&d8, a, 4);
+        const int8_t *q8 = (const int8_t *)(a + 4);
+        float d = d_all * d8;
+        int32_t aux32[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int e = 0; e < 256; e++) aux32[e & 7] += (int32_t)scales[e >> 4] * ((int32_t)q8[e] * q3k_code(blk, e));
+        if (scalar_form) {
+            for (int l = 0; l < 8; l++) sums[l] += d * (float)aux32[l];
+        } else {
+            int32_t isum = 0;
+            for (int l = 0; l < 8; l++) isum += aux32[l];
+            sumf += d * (float)isum;
+        }
+    }
+    if (scalar_form)
+        for (int l = 0; l < 8; l++) sumf += sums[l];
+    return sumf;
+}
+
 /* simd: 1 = the forms the reference runs on x86-64 (AVX2), 0 = its scalar fallbacks.  For Q4_K and Q6_K the two give
  * identical bits; for Q5_K they are different functions of the weight bytes (see dot_q5k_q8k). */
 ORACLE_API float oracle_dot_q8k(int fmt, const uint8_t *act_q8k, const uint8_t *w, size_t k, int simd) {
     if (fmt == FMT_Q5_K) return dot_q5k_q8k(act_q8k, w, k, simd ? 0 : 1);
+    if (fmt == FMT_Q3_K) return dot_q3k_q8k(act_q8k, w, k, simd ? 0 : 1);
     if (fmt == FMT_Q2_K) return dot_q2k_q8k(act_q8k, w, k);  /* the AVX2 form computes the same integers */
 #if defined(__AVX2__)
     if (simd) return fmt == FMT_Q4_K ? dot_q4k_q8k_avx2(act_q8k, w, k) : dot_q6k_q8k_avx2(act_q8k, w, k);
@@ -794,7 +863,7 @@ ORACLE_API int oracle_quant_matmul(int fmt, const float *act, const uint8_t *w, 
     if (k % (size_t)bs) return -2;
     if (threads <= 0) threads = 1;
     size_t row_bytes = (k / (size_t)bs) * (size_t)oracle_block_bytes(fmt);
-    int kq = (fmt == FMT_Q2_K || fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
+    int kq = (fmt == FMT_Q2_K || fmt == FMT_Q3_K || fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
     size_t q8k_row = (k / 256) * Q8K_BLOCK_BYTES;
     uint8_t *aq = NULL;
     if (kq) {

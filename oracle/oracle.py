@@ -17,8 +17,8 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-FMT_Q4_0, FMT_Q5_0, FMT_Q8_0, FMT_Q2_K, FMT_Q4_K, FMT_Q5_K, FMT_Q6_K = 0, 2, 4, 6, 8, 9, 10
-FORMATS = {"Q4_0": FMT_Q4_0, "Q5_0": FMT_Q5_0, "Q8_0": FMT_Q8_0, "Q2_K": FMT_Q2_K, "Q4_K": FMT_Q4_K, "Q5_K": FMT_Q5_K, "Q6_K": FMT_Q6_K}
+FMT_Q4_0, FMT_Q5_0, FMT_Q8_0, FMT_Q2_K, FMT_Q3_K, FMT_Q4_K, FMT_Q5_K, FMT_Q6_K = 0, 2, 4, 6, 7, 8, 9, 10
+FORMATS = {"Q4_0": FMT_Q4_0, "Q5_0": FMT_Q5_0, "Q8_0": FMT_Q8_0, "Q2_K": FMT_Q2_K, "Q3_K": FMT_Q3_K, "Q4_K": FMT_Q4_K, "Q5_K": FMT_Q5_K, "Q6_K": FMT_Q6_K}
 Q8K_BLOCK_BYTES = 292
 
 _libs: dict[str, ctypes.CDLL] = {}

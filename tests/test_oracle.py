@@ -491,3 +491,73 @@ def test_q2k_q8k_dot_vs_f32_reference_tolerance(oracle, mk):  # fused_q2k_q8k_do
                 acc = np.float32(acc + np.float32(t))
             want[i, j] = acc
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# ------------------------------------------------------------------ Q3_K (dequant_k_quants/q2k_q3k.rs:64-144, simd/fused_q3k_q8k_dot.rs)
+
+
+def _q3k_numpy(w):
+    blocks = w.reshape(-1, 110)
+    hm, qs, sc = blocks[:, 0:32].astype(np.int32), blocks[:, 32:96].astype(np.int32), blocks[:, 96:108]
+    d = blocks[:, 108:110].copy().view(np.float16).astype(np.float32)[:, 0]
+    # the reference's u32 unpacking, word by word (q2k_q3k.rs:115-144)
+    aux = sc.copy().view(np.uint32).astype(np.uint64)
+    a0, a1, tmp = aux[:, 0], aux[:, 1], aux[:, 2]
+    k1, k2 = 0x03030303, 0x0F0F0F0F
+    words = np.stack([(a0 & k2) | ((tmp & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4),
+                      ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)], axis=1).astype(np.uint32)
+    scales = words.view(np.uint8).reshape(-1, 16).astype(np.int32) - 32
+    e = np.arange(256)
+    n, g, hl = e // 128, (e % 128) // 32, e % 32
+    low2 = (qs[:, 32 * n + hl] >> (2 * g)) & 3
+    hbit = (hm[:, hl] >> (4 * n + g)) & 1
+    code = low2 - np.where(hbit != 0, 0, 4)
+    return d, scales, code
+
+
+def test_q3k_dequant_matches_numpy_model(oracle):
+    rng = np.random.default_rng(62)
+    w = synth.weight_bytes("Q3_K", rng, 5, 512)
+    got = oracle.dequantize_f32("Q3_K", w).reshape(-1, 256)
+    d, scales, code = _q3k_numpy(w)
+    want = (d[:, None] * scales[:, np.arange(256) // 16].astype(np.float32)).astype(np.float32) * code.astype(np.float32)
+    assert np.array_equal(got.view(np.uint32), want.astype(np.float32).view(np.uint32))
+
+
+def test_q3k_simple_blocks(oracle):
+    blk = np.zeros(110, np.uint8)
+    assert np.all(oracle.dequantize_f32("Q3_K", blk) == 0.0)
+    blk[108:110] = f16b(1.0)
+    blk[0:32] = 0xFF          # every high bit set: nothing subtracted
+    blk[32:96] = 0xFF         # low bits 3
+    blk[96:104] = 0x11        # low four bits of every scale: 1
+    blk[104:108] = 0xAA       # high two bits: 2 -> scale (1 | 32) - 32 = 1
+    assert np.all(oracle.dequantize_f32("Q3_K", blk) == 3.0)
+
+
+def test_q3k_q8k_dot_forms(oracle):
+    rng = np.random.default_rng(63)
+    m, n, k = 2, 6, 768
+    w = synth.weight_bytes("Q3_K", rng, n, k)
+    act = synth.activations(rng, m, k)
+    got = oracle.quant_matmul("Q3_K", act, w, n, threads=2)                 # the AVX2 form
+    ref = act.astype(np.float64) @ oracle.dequantize_f32("Q3_K", w).reshape(n, k).astype(np.float64).T
+    assert np.all(np.abs(got - ref) <= 0.02 * np.abs(ref) + 1.0)            # fused_q3k_q8k_dot.rs:300-364
+    d, scales, code = _q3k_numpy(w)
+    d, scales, code = d.reshape(n, -1), scales.reshape(n, -1, 16), code.reshape(n, -1, 256)
+    a = act.reshape(m, k // 256, 256)
+    amax = np.abs(a).max(axis=2)
+    idv = np.where(amax != 0, np.float32(127.0) / amax, 0).astype(np.float32)
+    codes8 = np.clip(np.rint((a * idv[:, :, None]).astype(np.float32)), -128, 127).astype(np.int64)
+    d8 = (amax / np.float32(127.0)).astype(np.float32)
+    want = np.zeros((m, n), np.float32)
+    for i in range(m):
+        for j in range(n):
+            acc = np.float32(0)
+            for b in range(k // 256):
+                isum = int((scales[j, b][np.arange(256) // 16] * code[j, b] * codes8[i, b]).sum())
+                acc = np.float32(acc + np.float32(np.float32(d[j, b] * d8[i, b]) * np.float32(isum)))
+            want[i, j] = acc
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    scalar = oracle.quant_matmul("Q3_K", act, w, n, threads=2, simd=False)  # eight float lanes: close, not equal in general
+    assert np.abs(scalar - got).max() <= 1e-5 * np.abs(got).max()
