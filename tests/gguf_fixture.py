@@ -20,7 +20,7 @@ def write_gguf(path, layers=2, alignment=None):
     import gguf
     from gguf import GGMLQuantizationType as T
 
-    qt = {"Q4_0": T.Q4_0, "Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "Q6_K": T.Q6_K}
+    qt = {"Q4_0": T.Q4_0, "Q5_0": T.Q5_0, "Q8_0": T.Q8_0, "Q2_K": T.Q2_K, "Q3_K": T.Q3_K, "Q4_K": T.Q4_K, "Q5_K": T.Q5_K, "Q6_K": T.Q6_K}
     rng = synth.rng_for(60, layers)
     w = gguf.GGUFWriter(path, "llama")
     w.add_uint32("llama.block_count", layers)
@@ -43,6 +43,9 @@ def write_gguf(path, layers=2, alignment=None):
         w.add_tensor(f"blk.{li}.attn_q.bias", rng.standard_normal(HID, dtype=np.float32))
     w.add_tensor("output_norm.weight", rng.standard_normal(HID, dtype=np.float32).astype(np.float16))
     add("output.weight", "Q6_K", VOC, HID)
+    # one tensor of every other format the library reads (expert-style names: they map to names of their own)
+    for i, fmt in enumerate(("Q4_0", "Q5_0", "Q2_K", "Q3_K", "Q5_K")):
+        add(f"blk.0.ffn_gate.{i}.weight", fmt, 64, HID)
     w.write_header_to_file()
     w.write_kv_data_to_file()
     w.write_tensors_to_file()
