@@ -129,7 +129,8 @@ def test_gguf_load_and_forward(ops, oracle, tmp_path):
     rng = synth.rng_for(43)
     lin = G.load_llama_linears(path)
     assert set(lin) == {"lm_head"} | {f"model.layers.0.{s}" for s in (
-        "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")}
+        "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")} | {
+        f"model.layers.0.block_sparse_moe.experts.{i}.gate_proj" for i in range(5)}  # one tensor of every other format
     assert lin["model.layers.0.self_attn.q_proj"].bias is not None   # attn_q.bias rides along
     for m in (1, 6):
         for gname, (fmt, n, k, b) in packed.items():
