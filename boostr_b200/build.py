@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJDIR = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200q.so")
-SOURCES = ["api.cu", "dequant.cu", "gemv.cu", "gemv_m1.cu", "gemv_m1_f32.cu", "kquant_generic.cu", "prefill.cu"]
+SOURCES = ["api.cu", "dequant.cu", "gemv.cu", "gemv_m1.cu", "gemv_m1_f32.cu", "kquant_generic.cu", "prefill.cu", "smallm_i8.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -46,6 +46,11 @@ cudaError_t launch_kq_generic(int fmt, const void* act, int act_dtype, const voi
                               size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, bool* ws_too_small);
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
                                cudaStream_t st);
+bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N);
+size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count);
+cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
+                             size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status,
+                             bool* ws_too_small, char* err, size_t err_len, bool acts_prepared);
 }  // namespace b200q
 
 using namespace b200q;
@@ -169,7 +174,12 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
     if (gemv_m1_supported(format, M, K, N, swiglu)) return 0;
     if (!swiglu && gemv_m1_f32_supported(format, M, K, N)) return 0;
     // small-M kernel: the activation image, plus split-K partial sums when K is long
-    return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
+    size_t need = gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
+    if (!swiglu && smallm_i8_supported(format, M, K, N)) {
+        const size_t b = smallm_i8_workspace_bytes(M, K, N, sm_count_current());
+        if (b > need) need = b;
+    }
+    return need;
 }
 
 }  // namespace
@@ -197,6 +207,11 @@ int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w,
         e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
     } else if (gemv_m1_f32_supported(format, M, K, N)) {
         e = launch_gemv_m1_f32(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else if (getenv("B200Q_I8") && smallm_i8_supported(format, M, K, N)) {
+        char msg[256] = "";
+        e = launch_smallm_i8(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st, status, &small, msg,
+                             sizeof(msg), false);
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
     } else {
         e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
                         st, status, &small);

@@ -1,0 +1,769 @@
+// Small-M quantized matmul (2 <= M <= 32) for Q4_K on the 5th-generation tensor cores' INTEGER path:
+//   out[M,N] = act[M,K] x W[N,K]^T  with boostr's CPU arithmetic (activations quantised to Q8_K,
+//   src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98; per 256-block (d*d8)*sumi - (dmin*d8)*sumi_mins with exact
+//   integer sums, src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172).
+//
+// The mma.sync kernel (gemv.cu) spends ~540 warp instructions per (16 weight rows x 256 K x 16 activation rows) and is
+// bound by instruction issue, not by memory.  Here ONE tcgen05.mma.kind::i8 (128 weight rows x MP activation rows x
+// 32 K) computes the integer dot products of a whole 32-wide sub-block for 128 rows, and the per-sub-block scales are
+// applied by the warps that drain the accumulator:
+//   * tile = 128 weight rows (the MMA's M = the 128 lanes of tensor memory); the activations are the B operand,
+//     MP = 16 or 32 rows (MMA N); every 32-wide sub-block j of a 256-block gets its OWN accumulator columns
+//     [MP j, MP j + MP), so no scale has to enter the tensor core;
+//   * packed weight blocks arrive by TMA as tiles of 128 rows x 144 bytes (conflict-free 16-byte reads, one thread
+//     per row); four decode warps turn the nibbles into bytes and write them as the K-major, 128-byte-swizzled A
+//     operand in shared memory (two tiles of 128 rows x 128 codes per block), and leave the row's 6-bit scales,
+//     mins, d and dmin in a small ring for the drain;
+//   * the activations are quantised once per call (i8_act_prep_kernel) into an int8 image [M][K] that TMA brings in
+//     as the B operand, plus the Q8_K scales and the 32-wide block sums the min term needs;
+//   * one thread issues the 8 MMAs of a block; four drain warps (one thread per weight row) read the 8 x MP integer
+//     sums from tensor memory, form sumi = sum_j sc_j dot_j and sumi_mins = sum_j m_j bsum_j in integers and add the
+//     block's term to f32 accumulators in registers, blocks in K order;
+//   * work = (tile, block) pairs dealt to the CTAs as equal contiguous ranges, so a range may cut a tile along K: such
+//     pieces go to scratch as f32 partial tiles and a small second kernel adds them in K order (a tile that one CTA
+//     owns whole is written directly and has the CPU's bits; a cut tile differs from it by f32 rounding only).
+// Every mbarrier wait is bounded; on a timeout the CTA records a status code and still frees its tensor memory.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "common.cuh"
+#include "tmap.cuh"
+
+namespace b200q {
+
+struct I8Params {
+    const uint8_t* w;
+    void* out;
+    float* part;          // [slot][MP][128] f32 pieces of cut tiles
+    unsigned int* cnt;    // [ntiles] pieces of a cut tile that have been written; 0 between calls
+    const uint8_t* aux;   // [nblk][aux_bytes(MP)]: per block the eight int16 sums of 32 codes of every activation row, then the rows' Q8_K scales
+    uint32_t M, N, K;
+    uint32_t MP;          // activation rows of the MMA (16 or 32)
+    uint32_t nblk;        // K / 256
+    uint32_t ntiles;      // ceil(N / 128)
+    uint32_t Q;           // ntiles * nblk (tile, block) pairs
+    uint32_t unit;        // pairs are dealt in items of `unit` pairs: 1, or nblk (whole tiles: nothing is cut)
+    uint32_t qbase, qrem; // items / grid and items % grid: CTA c takes items [c qbase + min(c, qrem), ...)
+    uint32_t ns;          // ring depth of operand stages (one 256-block each)
+    uint32_t nr;          // ring depth of packed-weight tiles
+    uint32_t nsc;         // ring depth of the scale records
+    uint32_t idesc;
+    int out_dtype;
+    unsigned int* status;
+#ifdef I8_TRACE
+    long long* dbg;  // [cta][role][8] cycle counters
+#endif
+};
+
+namespace {
+
+#ifdef I8_TRACE
+#define TR_DECL long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t = clock64();
+#define TR(k) { const long long tr_n = clock64(); tr[k] += tr_n - tr_t; tr_t = tr_n; }
+#define TR_OUT(role) if (lane == 0) { for (int k = 0; k < 8; ++k) p.dbg[(blockIdx.x * 4 + role) * 8 + k] = tr[k]; }
+#else
+#define TR_DECL
+#define TR(k)
+#define TR_OUT(role) {}
+#endif
+
+constexpr int DEC_WARPS = 8, DRAIN_WARPS = 8;  // decode: sets of four warps; drain: groups of four warps
+constexpr int I8_THREADS = (DEC_WARPS + DRAIN_WARPS + 3) * 32;  // decode | drain | packed-weight TMA | activation TMA | MMA issue, TMEM
+constexpr int W_RAW = DEC_WARPS + DRAIN_WARPS, W_ACT = W_RAW + 1, W_MMA = W_RAW + 2;
+constexpr uint32_t RAW_PITCH = 144, RAW_TILE = 128 * RAW_PITCH;  // 18432 = 18 x 1024
+constexpr uint32_t A_ATOM = 128 * 128;                            // 128 rows x 128 codes
+constexpr uint32_t SC_WORDS = 5;                                  // d|dmin, 8 scales, 8 mins
+constexpr uint32_t SC_REC = 128 * SC_WORDS * 4;                  // the 128 row records of a block
+constexpr uint32_t SC_SLOT = SC_REC + 32 * 20;                    // + the activation side of the block (aux_bytes(32))
+__host__ __device__ constexpr uint32_t aux_bytes(uint32_t MP) { return MP * 20; }  // per block: MP x 8 int16 block sums | MP x f32 d8
+// barriers (8 bytes each) at the start of dynamic shared memory
+constexpr int OFF_FULL = 0, OFF_EMPTY = 64, OFF_RAW_FULL = 128, OFF_RAW_EMPTY = 192, OFF_ACC_FULL = 256, OFF_ACC_EMPTY = 272,
+              OFF_SC_FULL = 320, OFF_TMEM = 448, OFF_DEAD = 452, OFF_RED = 456, OFF_LAST = 464, OFF_NSLOT = 472, OFF_SLOTS = 512,
+              OFF_SC = 1024;  // OFF_SLOTS: two lists of 64 slots
+
+__device__ __noinline__ bool i8_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* dead) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 8; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*dead || global_timer_ns() - t0 > 2000000000ull) return false;
+        __nanosleep(40);
+    }
+}
+__device__ __forceinline__ bool i8_wait(uint32_t bar, uint32_t parity, volatile uint32_t* dead) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return i8_wait_slow(bar, parity, dead);
+}
+__device__ __noinline__ void i8_fail(volatile uint32_t* dead, unsigned int* status, unsigned int code) {
+    if (!*dead) atomicOr(status, code);
+    *dead = 1;
+}
+__device__ __forceinline__ void tma2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit_to(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[128 x N] (int32, tensor memory) = A[128 x 32] (int8, shared) x B[N x 32]^T (int8, shared); never accumulates:
+// every sub-block has its own columns
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+        : "memory");
+}
+// K-major operand tile with 128-byte swizzle (rows of 128 bytes, 8-row groups 1024 bytes apart), from the low word
+// ((addr >> 4) | 1 << 16; 32 bytes further along K adds 2)
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"((1024u >> 4) | (1u << 14) | (2u << 29)));
+    return d;
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); }
+// 16 consecutive 32-bit columns of this thread's lane; the caller waits (tmem_ld_wait) before using them
+__device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8_async(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld4_async(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// One piece of work of a CTA: blocks [b0, b0 + nb) of tile `tile`; slot < 0: the whole tile, written to the output.
+struct I8Unit {
+    uint32_t tile, b0, nb;
+    int slot;
+};
+// First (tile, block) pair of CTA c: the first qrem CTAs take one item more than the others
+__device__ __forceinline__ uint32_t i8_range_begin(const I8Params& p, uint32_t c) { return (c * p.qbase + min(c, p.qrem)) * p.unit; }
+// The CTA whose range holds pair x
+__device__ __forceinline__ uint32_t i8_cta_of(const I8Params& p, uint32_t x) {
+    const uint32_t y = x / p.unit, big = p.qrem * (p.qbase + 1);
+    return y < big ? y / (p.qbase + 1) : p.qrem + (y - big) / p.qbase;
+}
+// The it-th unit of this CTA (every role walks the same list): the CTA's range cut at the tile boundaries
+__device__ __forceinline__ bool i8_unit(const I8Params& p, uint32_t it, I8Unit& u) {
+    const uint32_t a = i8_range_begin(p, blockIdx.x), b = i8_range_begin(p, blockIdx.x + 1);
+    const uint32_t t = a / p.nblk + it;
+    const uint32_t lo = max(a, t * p.nblk), hi = min(b, (t + 1) * p.nblk);
+    if (t >= p.ntiles || lo >= hi) return false;
+    u.tile = t;
+    u.b0 = lo - t * p.nblk;
+    u.nb = hi - lo;
+    u.slot = u.nb == p.nblk ? -1 : (int)(2 * blockIdx.x + (it == 0 ? 0u : 1u));
+    return true;
+}
+
+template <int I>
+__device__ __forceinline__ int ubyte(uint32_t x) { return (int)__byte_perm(x, 0u, 0x4440 | I); }
+
+template <int MP>
+__global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __grid_constant__ CUtensorMap tmap_act,
+                                                                      const __grid_constant__ CUtensorMap tmap_w, const I8Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // the launch reserves 1 KB of slack
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + OFF_FULL, bar_empty = sbase + OFF_EMPTY, bar_raw_full = sbase + OFF_RAW_FULL,
+                   bar_raw_empty = sbase + OFF_RAW_EMPTY, bar_acc_full = sbase + OFF_ACC_FULL, bar_acc_empty = sbase + OFF_ACC_EMPTY,
+                   bar_sc_full = sbase + OFF_SC_FULL;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM);
+    volatile uint32_t* dead = reinterpret_cast<volatile uint32_t*>(smem + OFF_DEAD);
+    constexpr uint32_t NACC = 2, ACC_COLS = 8 * MP, TMEM_COLS = NACC * ACC_COLS < 32 ? 32 : NACC * ACC_COLS;  // 256 or 512
+    constexpr uint32_t B_ATOM = MP * 128, STAGE = 2 * A_ATOM + 2 * B_ATOM;
+    // shared memory: barriers | scale records | packed tiles | operand stages (A atom 0, A atom 1, B atom 0, B atom 1)
+    const uint32_t sc_off = OFF_SC, raw_off = (sc_off + p.nsc * SC_SLOT + 1023u) & ~1023u, st_off = raw_off + p.nr * RAW_TILE;
+
+    constexpr int MH = MP / (DRAIN_WARPS / 4);  // activation rows of a drain warp
+    const uint32_t drain_warps = 4 * min((uint32_t)DRAIN_WARPS / 4, (p.M + MH - 1) / MH);
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.ns; ++s) {
+            mbar_init(bar_full + 8 * s, 5);   // the four decode warps of a set + the activation copy (with its byte count)
+            mbar_init(bar_empty + 8 * s, 1);  // the commit behind the block's MMAs
+        }
+        for (uint32_t s = 0; s < p.nr; ++s) {
+            mbar_init(bar_raw_full + 8 * s, 1);
+            mbar_init(bar_raw_empty + 8 * s, 4);
+        }
+        for (uint32_t s = 0; s < NACC; ++s) {
+            mbar_init(bar_acc_full + 8 * s, 1);
+            mbar_init(bar_acc_empty + 8 * s, drain_warps);  // the drain warps that have activation rows
+        }
+        for (uint32_t s = 0; s < p.nsc; ++s) mbar_init(bar_sc_full + 8 * s, 5);  // four decode warps write the records, one copy brings the activation side
+        mbar_init(sbase + OFF_RED, drain_warps);  // they meet here around the hand-over of a cut tile
+        *dead = 0;
+        mbar_fence_init();
+    }
+    if (warp == W_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + OFF_TMEM), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_before();
+    __syncthreads();
+    tc_after();
+    const uint32_t tmem = *tmem_holder;
+    grid_dep_launch();
+
+    if (warp == W_RAW) {
+        // ------------------------------------------------------------ packed weight tiles (do not depend on the previous kernel)
+        if (lane == 0) {
+            uint32_t s = 0, par = 0;
+            I8Unit u;
+            for (uint32_t it = 0; i8_unit(p, it, u) && !*dead; ++it) {
+                for (uint32_t j = 0; j < u.nb; ++j) {
+                    if (!i8_wait(bar_raw_empty + 8 * s, par ^ 1, dead)) {
+                        i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                        break;
+                    }
+                    mbar_expect_tx(bar_raw_full + 8 * s, RAW_TILE);
+                    tma2d(sbase + raw_off + s * RAW_TILE, &tmap_w, (int)((u.b0 + j) * RAW_PITCH), (int)(u.tile * 128), bar_raw_full + 8 * s);
+                    if (++s == p.nr) { s = 0; par ^= 1; }
+                }
+            }
+        }
+    } else if (warp == W_ACT) {
+        // ------------------------------------------------------------ activation codes (written by the previous kernel)
+        if (lane == 0) {
+            grid_dep_wait();
+            uint32_t s = 0, par = 0, i = 0;
+            I8Unit u;
+            for (uint32_t it = 0; i8_unit(p, it, u) && !*dead; ++it) {
+                for (uint32_t j = 0; j < u.nb; ++j, ++i) {
+                    if (!i8_wait(bar_empty + 8 * s, par ^ 1, dead)) {
+                        i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                        break;
+                    }
+                    const uint32_t b0 = sbase + st_off + s * STAGE + 2 * A_ATOM;
+                    mbar_expect_tx(bar_full + 8 * s, 2 * B_ATOM);
+                    tma2d(b0, &tmap_act, (int)((u.b0 + j) * 256), 0, bar_full + 8 * s);
+                    tma2d(b0 + B_ATOM, &tmap_act, (int)((u.b0 + j) * 256 + 128), 0, bar_full + 8 * s);
+                    // block sums and scales of the activation rows, next to the row records (same life time)
+                    const uint32_t q = i % p.nsc;
+                    mbar_expect_tx(bar_sc_full + 8 * q, aux_bytes(MP));
+                    bulk_g2s(sbase + sc_off + q * SC_SLOT + SC_REC, p.aux + (size_t)(u.b0 + j) * aux_bytes(MP), aux_bytes(MP), bar_sc_full + 8 * q);
+                    if (++s == p.ns) { s = 0; par ^= 1; }
+                }
+            }
+        }
+    } else if (warp == W_MMA) {
+        // ------------------------------------------------------------ MMA issue: 8 sub-blocks, 8 column groups
+        uint32_t s = 0, par = 0, i = 0;
+        bool ok = true;
+        I8Unit u;
+        TR_DECL
+        for (uint32_t it = 0; ok && i8_unit(p, it, u); ++it) {
+            for (uint32_t j = 0; j < u.nb; ++j, ++i) {
+                const uint32_t buf = i % NACC, use = i / NACC;
+                TR(0)
+                if (!i8_wait(bar_full + 8 * s, par, dead)) {
+                    if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                    ok = false;
+                    break;
+                }
+                TR(1)
+                if (use > 0 && !i8_wait(bar_acc_empty + 8 * buf, (use - 1) & 1, dead)) {
+                    if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    ok = false;
+                    break;
+                }
+                TR(2)
+                tc_after();
+                if (elect_one_lane()) {
+                    const uint32_t a_lo = desc_lo(sbase + st_off + s * STAGE), b_lo = desc_lo(sbase + st_off + s * STAGE + 2 * A_ATOM);
+                    const uint32_t d0 = tmem + buf * ACC_COLS;
+#pragma unroll
+                    for (uint32_t sb = 0; sb < 8; ++sb)
+                        tc_mma_i8(d0 + MP * sb, desc_sw128(a_lo + (sb >> 2) * (A_ATOM >> 4) + 2 * (sb & 3)),
+                                  desc_sw128(b_lo + (sb >> 2) * (B_ATOM >> 4) + 2 * (sb & 3)), p.idesc);
+                    tc_commit_to(bar_empty + 8 * s);         // the stage may be overwritten once these MMAs have read it
+                    tc_commit_to(bar_acc_full + 8 * buf);    // and the sums are complete
+                }
+                __syncwarp();
+                TR(3)
+                if (++s == p.ns) { s = 0; par ^= 1; }
+            }
+        }
+        TR_OUT(0)
+    } else if (warp < DEC_WARPS) {
+        // ------------------------------------------------------------ decode: nibbles -> int8 A operand, one thread per row
+        // the sets of four warps take the CTA's blocks in turn, so DEC_WARPS / 4 blocks are in work at a time
+        const uint32_t r = threadIdx.x & 127, set = threadIdx.x >> 7;
+        const uint32_t row_sw = (r >> 3) * 1024 + (r & 7) * 128, x7 = r & 7;
+        bool ok = true;
+        I8Unit u;
+        uint32_t i = 0;
+        TR_DECL
+        for (uint32_t it = 0; i8_unit(p, it, u); ++it) {
+            const bool row_ok = u.tile * 128 + r < p.N;
+            for (uint32_t j = 0; j < u.nb; ++j, ++i) {
+                if (i % (DEC_WARPS / 4) != set) continue;
+                const uint32_t rs = i % p.nr, rpar = (i / p.nr) & 1, s = i % p.ns, par = (i / p.ns) & 1;
+                TR(0)
+                if (ok && !i8_wait(bar_raw_full + 8 * rs, rpar, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                    ok = false;
+                }
+                TR(1)
+                const uint4* src = reinterpret_cast<const uint4*>(smem + raw_off + rs * RAW_TILE + r * RAW_PITCH);
+                uint4 h = make_uint4(0, 0, 0, 0), q[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) q[k] = make_uint4(0, 0, 0, 0);
+                if (ok && row_ok) {
+                    h = src[0];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) q[k] = src[1 + k];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
+                TR(2)
+                if (ok && !i8_wait(bar_empty + 8 * s, par ^ 1, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    ok = false;
+                }
+                TR(3)
+                // 16 nibble bytes q[k] = bytes 16k .. 16k+15 of qs: low nibbles -> sub-block 2 (k / 2), codes 16 (k & 1) ..;
+                // high nibbles -> sub-block 2 (k / 2) + 1.  Sub-block sb sits at bytes 32 sb .. of the 256-byte operand
+                // row: 16-byte chunk c = 2 sb + (k & 1) -> tile (c / 8), chunk (c % 8) ^ (row % 8) of the swizzled row.
+                uint8_t* a0 = smem + st_off + s * STAGE + row_sw;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t c_lo = 4 * (k >> 1) + (k & 1), c_hi = c_lo + 2;
+                    const uint4 lo = make_uint4(q[k].x & 0x0F0F0F0Fu, q[k].y & 0x0F0F0F0Fu, q[k].z & 0x0F0F0F0Fu, q[k].w & 0x0F0F0F0Fu);
+                    const uint4 hi = make_uint4((q[k].x >> 4) & 0x0F0F0F0Fu, (q[k].y >> 4) & 0x0F0F0F0Fu, (q[k].z >> 4) & 0x0F0F0F0Fu,
+                                                (q[k].w >> 4) & 0x0F0F0F0Fu);
+                    *reinterpret_cast<uint4*>(a0 + (c_lo >> 3) * A_ATOM + (((c_lo & 7) ^ x7) << 4)) = lo;
+                    *reinterpret_cast<uint4*>(a0 + (c_hi >> 3) * A_ATOM + (((c_hi & 7) ^ x7) << 4)) = hi;
+                }
+                // the row's record for the drain: d | dmin, the 6-bit scales and mins as bytes (unpack_q4k_q5k_scales,
+                // src/quant/cpu/kernels/dequant_k_quants/q4k_q5k.rs:108-122)
+                uint32_t* rec = reinterpret_cast<uint32_t*>(smem + sc_off + (i % p.nsc) * SC_SLOT) + r * SC_WORDS;
+                rec[0] = h.x;
+                rec[1] = h.y & 0x3F3F3F3Fu;
+                rec[2] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+                rec[3] = h.z & 0x3F3F3F3Fu;
+                rec[4] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+                proxy_fence();  // the operand bytes are read by the tensor core (async proxy)
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_full + 8 * s);
+                    mbar_arrive(bar_sc_full + 8 * (i % p.nsc));
+                }
+                TR(4)
+            }
+        }
+        if (warp == 0) TR_OUT(1)
+    } else {
+        // ------------------------------------------------------------ drain: integer sums -> scaled f32 terms
+        // DRAIN_WARPS / 4 warps per quarter of the rows: a thread owns one weight row and MH of the activation rows (warps
+        // whose rows do not exist have nothing to do).  The CTA's pairs are the contiguous range [xa, xb): pair x =
+        // block x % nblk of tile x / nblk.
+        const uint32_t quarter = (uint32_t)warp & 3, r = quarter * 32 + lane, m_lo = (((uint32_t)warp - DEC_WARPS) >> 2) * MH;
+        const bool rows_exist = m_lo < p.M;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        const uint32_t xa = i8_range_begin(p, blockIdx.x), xb = i8_range_begin(p, blockIdx.x + 1);
+        const uint32_t bar_red = sbase + OFF_RED;
+        volatile uint32_t* last_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_LAST);   // [2]
+        volatile uint32_t* nslot = reinterpret_cast<volatile uint32_t*>(smem + OFF_NSLOT);      // [2]
+        volatile uint32_t* slot_list = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOTS);  // [2][64]
+        grid_dep_wait();  // the output and the scratch may still be in use by the previous kernel
+        uint32_t red_phase = 0;
+        bool ok = true;
+        auto store_out = [&](uint32_t n, uint32_t m, float v) {
+            const size_t idx = (size_t)m * p.N + n;
+            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = v;
+            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
+            else static_cast<__half*>(p.out)[idx] = __float2half_rn(v);
+        };
+        // the drain warps meet (bounded: a warp that gave up marks the CTA dead and the others leave too)
+        auto meet = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_red);
+            if (!i8_wait(bar_red, red_phase & 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                ok = false;
+            }
+            ++red_phase;
+        };
+        // pieces of cut tiles this CTA has written: its first tile (0) and / or its last one (1)
+        bool have[2] = {false, false};
+        uint32_t cut_tile[2] = {0, 0};
+        float acc[MH];
+#pragma unroll
+        for (int m = 0; m < MH; ++m) acc[m] = 0.f;
+        TR_DECL
+        for (uint32_t x = xa; x < xb && ok && rows_exist; ++x) {
+            TR(0)
+            const uint32_t i = x - xa, buf = i % NACC, use = i / NACC, q = i % p.nsc;
+            const uint32_t tile = x / p.nblk, blk = x - tile * p.nblk;
+            if (!i8_wait(bar_sc_full + 8 * q, (i / p.nsc) & 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                ok = false;
+                break;
+            }
+            TR(1)
+            const uint8_t* slot = smem + sc_off + q * SC_SLOT;
+            const uint32_t* rec = reinterpret_cast<const uint32_t*>(slot) + r * SC_WORDS;
+            const uint32_t hd = rec[0], s0 = rec[1], s1 = rec[2], m0 = rec[3], m1 = rec[4];
+            const uint4* bsum = reinterpret_cast<const uint4*>(slot + SC_REC) + m_lo;
+            const float* d8s = reinterpret_cast<const float*>(slot + SC_REC + MP * 16) + m_lo;
+            const int sc[8] = {ubyte<0>(s0), ubyte<1>(s0), ubyte<2>(s0), ubyte<3>(s0), ubyte<0>(s1), ubyte<1>(s1), ubyte<2>(s1), ubyte<3>(s1)};
+            TR(2)
+            if (!i8_wait(bar_acc_full + 8 * buf, use & 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_MMA);
+                ok = false;
+                break;
+            }
+            TR(3)
+            tc_after();
+            const uint32_t t0 = tmem + lane_addr + buf * ACC_COLS + m_lo;
+            constexpr int GB = MH <= 8 ? 4 : 2;  // sub-blocks whose loads are in flight together
+            uint32_t v[GB][MH];
+            auto issue_loads = [&](int g) {
+#pragma unroll
+                for (int k = 0; k < GB; ++k) {
+                    if constexpr (MH == 16) tmem_ld16_async(t0 + MP * (GB * g + k), v[k]);
+                    else if constexpr (MH == 8) tmem_ld8_async(t0 + MP * (GB * g + k), v[k]);
+                    else tmem_ld4_async(t0 + MP * (GB * g + k), v[k]);
+                }
+            };
+            issue_loads(0);
+            // everything that does not need the integer sums, while the first loads are on their way
+            const float d = f16bits_to_f32(hd & 0xFFFF), dmin = f16bits_to_f32(hd >> 16);
+            float dall[MH], mterm[MH];
+#pragma unroll
+            for (int m = 0; m < MH; ++m) {
+                const uint4 bs = bsum[m];
+                const float d8 = d8s[m];
+                const int summ = __dp2a_lo((int)bs.x, (int)m0, __dp2a_hi((int)bs.y, (int)m0, __dp2a_lo((int)bs.z, (int)m1, __dp2a_hi((int)bs.w, (int)m1, 0))));
+                dall[m] = __fmul_rn(d, d8);
+                mterm[m] = __fmul_rn(__fmul_rn(dmin, d8), (float)summ);
+            }
+            int sumi[MH];
+#pragma unroll
+            for (int m = 0; m < MH; ++m) sumi[m] = 0;
+#pragma unroll
+            for (int g = 0; g < 8 / GB; ++g) {
+                tmem_ld_wait();
+#pragma unroll
+                for (int k = 0; k < GB; ++k)
+#pragma unroll
+                    for (int m = 0; m < MH; ++m) sumi[m] += sc[GB * g + k] * (int)v[k][m];
+                if (g + 1 < 8 / GB) issue_loads(g + 1);
+            }
+            tc_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);  // the MMA warp may reuse the columns
+            TR(4)
+#pragma unroll
+            for (int m = 0; m < MH; ++m) acc[m] = __fadd_rn(acc[m], __fsub_rn(__fmul_rn(dall[m], (float)sumi[m]), mterm[m]));
+            TR(5)
+            if (blk + 1 != p.nblk && x + 1 != xb) continue;
+            // ---- the CTA's last block of this tile
+            const uint32_t n = tile * 128 + r;
+            const bool whole = (tile * p.nblk >= xa) && ((tile + 1) * p.nblk <= xb);
+            if (whole) {
+                if (n < p.N)
+#pragma unroll
+                    for (int m = 0; m < MH; ++m)
+                        if (m_lo + m < p.M) store_out(n, m_lo + m, acc[m]);
+            } else {
+                // a piece of a cut tile goes to scratch; the hand-over follows when all blocks are done
+                const uint32_t which = tile == xa / p.nblk ? 0u : 1u;
+                float* part = p.part + ((size_t)(2 * blockIdx.x + which) * MP + m_lo) * 128;
+#pragma unroll
+                for (int m = 0; m < MH; ++m) part[m * 128 + r] = acc[m];
+                have[which] = true;
+                cut_tile[which] = tile;
+            }
+#pragma unroll
+            for (int m = 0; m < MH; ++m) acc[m] = 0.f;
+            TR(6)
+        }
+        // ---- cut tiles: whoever writes a tile's last piece adds all of them, in K order, and stores the rows
+        if (ok && rows_exist && (have[0] || have[1])) {
+            meet();  // every drain thread's pieces are written
+            if (ok && warp == DEC_WARPS && lane == 0) {
+                uint32_t old[2] = {0, 0}, np[2] = {0, 0};
+#pragma unroll
+                for (uint32_t which = 0; which < 2; ++which) {
+                    if (!have[which]) continue;
+                    // the CTAs whose ranges meet the tile's pairs [x0, x1), in order
+                    const uint32_t tile = cut_tile[which], x0 = tile * p.nblk, x1 = x0 + p.nblk, G = gridDim.x;
+                    uint32_t k = 0;
+                    for (uint32_t cc = i8_cta_of(p, x0); cc < G && k < 64; ++cc) {
+                        const uint32_t a = i8_range_begin(p, cc);
+                        if (a >= x1) break;
+                        slot_list[64 * which + k++] = 2 * cc + (tile == a / p.nblk ? 0u : 1u);
+                    }
+                    nslot[which] = np[which] = k;
+                    // release: the pieces (seen through the meeting) are visible to whoever reads the count; acquire: the
+                    // pieces counted before are visible here.  The two counts are on their way together.
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old[which]) : "l"(p.cnt + tile) : "memory");
+                }
+#pragma unroll
+                for (uint32_t which = 0; which < 2; ++which) {
+                    const bool last = have[which] && old[which] + 1 == np[which];
+                    if (last) p.cnt[cut_tile[which]] = 0;  // ready for the next call
+                    last_flag[which] = last ? 1u : 0u;
+                }
+            }
+            meet();
+            for (uint32_t which = 0; ok && which < 2; ++which) {
+                if (!have[which] || !last_flag[which]) continue;
+                const uint32_t ns = nslot[which], n = cut_tile[which] * 128 + r;
+                float tot[MH];
+                for (uint32_t k0 = 0; k0 < ns; k0 += 4) {
+                    float v[4][MH];
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        if (k0 + k < ns) {
+                            const float* src = p.part + ((size_t)slot_list[64 * which + k0 + k] * MP + m_lo) * 128 + r;
+#pragma unroll
+                            for (int m = 0; m < MH; ++m) v[k][m] = __ldcg(src + m * 128);
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        if (k0 + k < ns) {
+#pragma unroll
+                            for (int m = 0; m < MH; ++m) tot[m] = k0 + k == 0 ? v[k][m] : __fadd_rn(tot[m], v[k][m]);
+                        }
+                    }
+                }
+                if (n < p.N)
+#pragma unroll
+                    for (int m = 0; m < MH; ++m)
+                        if (m_lo + m < p.M) store_out(n, m_lo + m, tot[m]);
+            }
+            TR(7)
+        }
+        if (warp == DEC_WARPS) TR_OUT(2)
+    }
+    tc_before();
+    __syncthreads();
+    if (warp == W_MMA) {
+        tc_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// One warp per (activation row, 256-block): Q8_K codes (quantize_act_q8k.rs:26-98: d = amax / 127, id = 127 / amax,
+// round half to even) into the int8 image [M][K]; the eight sums of 32 codes and the scale go to the block's record in
+// `aux` (aux_bytes).  Also clears the piece counters of the main kernel.
+template <typename InT>
+__global__ void __launch_bounds__(256) i8_act_prep_kernel(const InT* __restrict__ act, uint8_t* __restrict__ codes, uint8_t* __restrict__ aux,
+                                                          unsigned int* __restrict__ cnt, uint32_t ntiles, uint32_t M, uint32_t nblk,
+                                                          uint32_t MP) {
+    const int lane = threadIdx.x & 31;
+    grid_dep_launch();
+    grid_dep_wait();  // the activations may be the previous kernel's output; the image may still be read by it
+    for (uint32_t t = blockIdx.x * 256 + threadIdx.x; t < ntiles; t += gridDim.x * 256) cnt[t] = 0;  // piece counters of the cut tiles
+    const uint32_t run = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (run >= M * nblk) return;
+    const uint32_t m = run / nblk, b = run % nblk;
+    float v[8];
+    const size_t base = (size_t)run * 256 + 8 * lane;  // row m, block b of [M][K]
+    if constexpr (sizeof(InT) == 4) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(act + base)), y = __ldg(reinterpret_cast<const float4*>(act + base) + 1);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    } else {
+        const uint4 rr = __ldg(reinterpret_cast<const uint4*>(act + base));
+        v[0] = __uint_as_float(rr.x << 16); v[1] = __uint_as_float(rr.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(rr.y << 16); v[3] = __uint_as_float(rr.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(rr.z << 16); v[5] = __uint_as_float(rr.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(rr.w << 16); v[7] = __uint_as_float(rr.w & 0xFFFF0000u);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+    int c[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        c[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], id))));
+        s += c[i];
+    }
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        w0 |= (uint32_t)(c[i] & 0xFF) << (8 * i);
+        w1 |= (uint32_t)(c[4 + i] & 0xFF) << (8 * i);
+    }
+    *reinterpret_cast<uint2*>(codes + base) = make_uint2(w0, w1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 32 codes = four lanes
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    uint8_t* ab = aux + (size_t)b * aux_bytes(MP);
+    if ((lane & 3) == 0) reinterpret_cast<short*>(ab)[m * 8 + (lane >> 2)] = (short)s;
+    if (lane == 0) reinterpret_cast<float*>(ab + MP * 16)[m] = __fdiv_rn(amax, 127.0f);
+}
+
+#ifdef I8_TRACE
+long long* g_i8_dbg = nullptr;
+#endif
+struct I8Layout {
+    uint32_t MP, nblk, ntiles, Q, grid, unit;
+    size_t codes_bytes, aux_off, part_off, cnt_off, total;
+};
+I8Layout i8_layout(size_t M, size_t K, size_t N, int sm_count) {
+    I8Layout l{};
+    l.MP = M <= 16 ? 16u : 32u;
+    l.nblk = (uint32_t)(K / 256);
+    l.ntiles = (uint32_t)((N + 127) / 128);
+    l.Q = l.ntiles * l.nblk;
+    // Whole tiles per CTA (nothing to hand over) unless cutting the tiles along K shortens the longest CTA by more than
+    // the hand-over costs (about eight blocks' worth of time).
+    const uint32_t G = (uint32_t)sm_count;
+    const uint32_t whole_cost = (l.ntiles + G - 1) / G * l.nblk, cut_cost = (l.Q + G - 1) / G + 8;
+    l.unit = whole_cost <= cut_cost ? l.nblk : 1u;
+    const uint32_t items = l.Q / l.unit;
+    l.grid = items < G ? items : G;
+    l.codes_bytes = (M * K + 255) & ~(size_t)255;
+    l.aux_off = l.codes_bytes;
+    l.part_off = l.aux_off + (((size_t)l.nblk * aux_bytes(l.MP) + 255) & ~(size_t)255);
+    l.cnt_off = l.part_off + (size_t)2 * l.grid * l.MP * 128 * 4;
+    l.total = l.cnt_off + (((size_t)l.ntiles * 4 + 255) & ~(size_t)255);
+    return l;
+}
+
+}  // namespace
+
+// Shapes the integer tensor-core kernel takes: Q4_K, 2 <= M <= 32, whole 256-blocks, rows a multiple of 16 bytes
+// (always so: 144-byte blocks), N * K small enough for 32-bit pair counts.
+bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N) {
+    return fmt == FMT_Q4_K && M >= 2 && M <= 32 && K % 256 == 0 && K >= 256 && K / 256 <= 64 && N >= 1 && (N + 127) / 128 * (K / 256) < (1u << 30);
+}
+size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count) { return i8_layout(M, K, N, sm_count).total; }
+
+// acts_prepared: a previous call with the same activations and scratch left the image there (gate, then up).
+cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
+                             size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status,
+                             bool* ws_too_small, char* err, size_t err_len, bool acts_prepared) {
+    (void)fmt;
+    *ws_too_small = false;
+    const I8Layout l = i8_layout(M, K, N, sm_count);
+    if (!ws || ws_bytes < l.total || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    uint8_t* codes = base;
+    uint8_t* aux = base + l.aux_off;
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(base + l.cnt_off);
+    if (!acts_prepared) {
+        const uint32_t runs = (uint32_t)M * l.nblk;
+        const dim3 pg((runs + 7) / 8);
+        cudaError_t e = act_dtype == DT_F32
+                            ? launch_pdl(i8_act_prep_kernel<float>, pg, dim3(256), 0, st, static_cast<const float*>(act), codes, aux, cnt, l.ntiles, (uint32_t)M, l.nblk, l.MP)
+                            : launch_pdl(i8_act_prep_kernel<__nv_bfloat16>, pg, dim3(256), 0, st, static_cast<const __nv_bfloat16*>(act), codes, aux, cnt,
+                                         l.ntiles, (uint32_t)M, l.nblk, l.MP);
+        note_launch();
+        if (e != cudaSuccess) return e;
+    }
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled is not available from this driver");
+        return cudaErrorNotSupported;
+    }
+    I8Params p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.out = out;
+    p.part = reinterpret_cast<float*>(base + l.part_off);
+    p.cnt = cnt;
+    p.aux = aux;
+    p.M = (uint32_t)M; p.N = (uint32_t)N; p.K = (uint32_t)K;
+    p.MP = l.MP; p.nblk = l.nblk; p.ntiles = l.ntiles; p.Q = l.Q;
+    p.unit = l.unit;
+    p.qbase = (l.Q / l.unit) / l.grid; p.qrem = (l.Q / l.unit) % l.grid;
+    // int32 accumulator, signed 8-bit x signed 8-bit, both K-major, N = MP, M = 128
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((p.MP >> 3) << 17) | ((128u >> 4) << 24);
+    p.out_dtype = out_dtype;
+    p.status = status;
+#ifdef I8_TRACE
+    static long long* dbg = nullptr;
+    if (!dbg) cudaMalloc(&dbg, 256 * 4 * 8 * sizeof(long long));
+    p.dbg = dbg;
+    g_i8_dbg = dbg;
+#endif
+    const uint32_t stage = 2 * A_ATOM + 2 * p.MP * 128;
+    p.ns = 3;
+    p.nsc = p.ns + 2 + 2;
+    const uint32_t fixed = 1024 + ((p.nsc * SC_SLOT + 1023u) & ~1023u) + p.ns * stage;
+    p.nr = (232448u - 1024u - 1024u - fixed) / RAW_TILE;
+    if (p.nr > 6) p.nr = 6;
+    const size_t smem = 1024 + fixed + (size_t)p.nr * RAW_TILE;
+
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap amap, wmap;
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+        const cuuint64_t gstride[1] = {(cuuint64_t)K};
+        const cuuint32_t box[2] = {128u, p.MP};
+        CUresult cr = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, codes, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (activation image %p, K=%zu, M=%zu)", (int)cr, (void*)codes, K, M);
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        const uint32_t row_bytes = l.nblk * 144;
+        const cuuint64_t gdim[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
+        const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+        const cuuint32_t box[2] = {RAW_PITCH, 128u};
+        CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (weight pointer %p, row bytes %u, N=%zu)", (int)cr, w, row_bytes, N);
+            return cudaErrorInvalidValue;
+        }
+    }
+    static PerDeviceOnce attrs;
+    cudaError_t e = attrs.run([] {
+        cudaError_t a = cudaFuncSetAttribute(smallm_i8_q4k_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (a == cudaSuccess) a = cudaFuncSetAttribute(smallm_i8_q4k_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        return a;
+    });
+    if (e != cudaSuccess) return e;
+    e = p.MP == 16 ? launch_pdl(smallm_i8_q4k_kernel<16>, dim3(l.grid), dim3(I8_THREADS), smem, st, amap, wmap, p)
+                   : launch_pdl(smallm_i8_q4k_kernel<32>, dim3(l.grid), dim3(I8_THREADS), smem, st, amap, wmap, p);
+    note_launch();
+    if (e != cudaSuccess) return e;
+    return cudaGetLastError();
+}
+
+#ifdef I8_TRACE
+extern "C" __attribute__((visibility("default"))) int b200q_i8_trace(long long* host) {
+    return g_i8_dbg ? (int)cudaMemcpy(host, g_i8_dbg, 256 * 4 * 8 * sizeof(long long), cudaMemcpyDeviceToHost) : -1;
+}
+#endif
+}  // namespace b200q
