@@ -47,6 +47,7 @@ cudaError_t launch_kq_generic(int fmt, const void* act, int act_dtype, const voi
 cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, int out_dtype, size_t n, int sm_count,
                                cudaStream_t st);
 bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N);
+bool smallm_i8_preferred(int fmt, size_t M, size_t K, size_t N, int sm_count);
 size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count);
 cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
                              size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status,
@@ -174,12 +175,9 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
     if (gemv_m1_supported(format, M, K, N, swiglu)) return 0;
     if (!swiglu && gemv_m1_f32_supported(format, M, K, N)) return 0;
     // small-M kernel: the activation image, plus split-K partial sums when K is long
-    size_t need = gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
-    if (!swiglu && smallm_i8_supported(format, M, K, N)) {
-        const size_t b = smallm_i8_workspace_bytes(M, K, N, sm_count_current());
-        if (b > need) need = b;
-    }
-    return need;
+    if (smallm_i8_preferred(format, M, K, N, sm_count_current()))  // integer tensor-core kernel (+ gate and up for SwiGLU)
+        return smallm_i8_workspace_bytes(M, K, N, sm_count_current()) + (swiglu ? 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255) : 0);
+    return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
 }
 
 }  // namespace
@@ -207,7 +205,7 @@ int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w,
         e = launch_gemv_m1(format, act, act_dtype, w, nullptr, out, out_dtype, K, N, sm_count_current(), st, status);
     } else if (gemv_m1_f32_supported(format, M, K, N)) {
         e = launch_gemv_m1_f32(format, act, act_dtype, w, out, out_dtype, K, N, sm_count_current(), st, status);
-    } else if (getenv("B200Q_I8") && smallm_i8_supported(format, M, K, N)) {
+    } else if (smallm_i8_preferred(format, M, K, N, sm_count_current())) {
         char msg[256] = "";
         e = launch_smallm_i8(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st, status, &small, msg,
                              sizeof(msg), false);
@@ -403,6 +401,21 @@ int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w
         if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
     } else if (gemv_m1_supported(format, M, K, N, true)) {
         e = launch_gemv_m1(format, act, act_dtype, w_gate, w_up, out, out_dtype, K, N, sm_count_current(), st, status);
+    } else if (smallm_i8_preferred(format, M, K, N, sm_count_current())) {
+        // two integer tensor-core products into f32 scratch (the second reuses the quantised activations), then the gate
+        const size_t mn = (M * N * sizeof(float) + 255) & ~(size_t)255;
+        float* g = static_cast<float*>(ws);
+        float* u = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + mn);
+        uint8_t* rest = static_cast<uint8_t*>(ws) + 2 * mn;
+        const size_t rest_bytes = ws_bytes - 2 * mn;
+        char msg[256] = "";
+        e = launch_smallm_i8(format, act, act_dtype, w_gate, g, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, status, &small, msg,
+                             sizeof(msg), false);
+        if (e == cudaSuccess && !small)
+            e = launch_smallm_i8(format, act, act_dtype, w_up, u, DT_F32, M, K, N, rest, rest_bytes, sm_count_current(), st, status, &small, msg,
+                                 sizeof(msg), true);
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_swiglu: %s", msg);
+        if (e == cudaSuccess && !small) e = launch_swiglu_gate(g, u, out, out_dtype, M * N, sm_count_current(), st);
     } else {
         e = launch_gemv(format, act, act_dtype, w_gate, w_up, out, out_dtype, M, K, N, ws, ws_bytes, true, sm_count_current(),
                         st, status, &small);

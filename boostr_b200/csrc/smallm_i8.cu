@@ -3,25 +3,29 @@
 //   src/quant/cpu/kernels/simd/quantize_act_q8k.rs:26-98; per 256-block (d*d8)*sumi - (dmin*d8)*sumi_mins with exact
 //   integer sums, src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172).
 //
-// The mma.sync kernel (gemv.cu) spends ~540 warp instructions per (16 weight rows x 256 K x 16 activation rows) and is
-// bound by instruction issue, not by memory.  Here ONE tcgen05.mma.kind::i8 (128 weight rows x MP activation rows x
-// 32 K) computes the integer dot products of a whole 32-wide sub-block for 128 rows, and the per-sub-block scales are
-// applied by the warps that drain the accumulator:
+// The mma.sync kernel (gemv.cu) spends ~540 warp instructions per (16 weight rows x 256 K x 16 activation rows), is bound
+// by instruction issue, and takes more than 16 activation rows in several passes over the weights.  Here ONE
+// tcgen05.mma.kind::i8 (128 weight rows x MP activation rows x 32 K) computes the integer dot products of a whole
+// 32-wide sub-block for 128 rows, and the per-sub-block scales are applied by the warps that drain the accumulator:
 //   * tile = 128 weight rows (the MMA's M = the 128 lanes of tensor memory); the activations are the B operand,
 //     MP = 16 or 32 rows (MMA N); every 32-wide sub-block j of a 256-block gets its OWN accumulator columns
-//     [MP j, MP j + MP), so no scale has to enter the tensor core;
+//     [MP j, MP j + MP), so no scale has to enter the tensor core; tensor memory holds two such accumulators;
 //   * packed weight blocks arrive by TMA as tiles of 128 rows x 144 bytes (conflict-free 16-byte reads, one thread
-//     per row); four decode warps turn the nibbles into bytes and write them as the K-major, 128-byte-swizzled A
-//     operand in shared memory (two tiles of 128 rows x 128 codes per block), and leave the row's 6-bit scales,
-//     mins, d and dmin in a small ring for the drain;
+//     per row); two sets of four decode warps, taking the blocks in turn, split the nibbles into bytes and write them
+//     as the K-major, 128-byte-swizzled A operand in shared memory (two tiles of 128 rows x 128 codes per block), and
+//     leave the row's 6-bit scales, mins, d and dmin in a small ring of records for the drain;
 //   * the activations are quantised once per call (i8_act_prep_kernel) into an int8 image [M][K] that TMA brings in
-//     as the B operand, plus the Q8_K scales and the 32-wide block sums the min term needs;
-//   * one thread issues the 8 MMAs of a block; four drain warps (one thread per weight row) read the 8 x MP integer
-//     sums from tensor memory, form sumi = sum_j sc_j dot_j and sumi_mins = sum_j m_j bsum_j in integers and add the
-//     block's term to f32 accumulators in registers, blocks in K order;
-//   * work = (tile, block) pairs dealt to the CTAs as equal contiguous ranges, so a range may cut a tile along K: such
-//     pieces go to scratch as f32 partial tiles and a small second kernel adds them in K order (a tile that one CTA
-//     owns whole is written directly and has the CPU's bits; a cut tile differs from it by f32 rounding only).
+//     as the B operand; the Q8_K scales and the 32-wide block sums the min term needs travel beside the records;
+//   * one thread issues the 8 MMAs of a block; two teams of eight drain warps, one per accumulator (a thread owns a
+//     weight row and half of the activation rows), read the 8 x MP integer sums from tensor memory, form
+//     sumi = sum_j sc_j dot_j and sumi_mins = sum_j m_j bsum_j in integers and the block's f32 term; the running f32
+//     sums pass from team to team through shared memory, so the blocks are still added in K order;
+//   * work = (tile, block) pairs dealt to the CTAs as equal contiguous ranges.  Where the matrix has enough tiles the
+//     ranges are whole tiles and the result has the CPU's bits.  Otherwise a range may cut a tile along K: such pieces
+//     go to scratch as f32 partial tiles and the CTA that writes a tile's last piece (a counter per tile) adds them in
+//     K order; a cut tile differs from the CPU's bits by f32 rounding only (the grouping of the sum).
+// What bounds it: the drain is ~200 instructions per (weight row, 8 activation rows, block), about 2600 warp
+// instructions per (128 rows x 256 K x 16 activation rows) for the whole CTA against ~4300 in the mma.sync kernel.
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code and still frees its tensor memory.
 #include <cuda.h>
 
@@ -51,24 +55,12 @@ struct I8Params {
     uint32_t idesc;
     int out_dtype;
     unsigned int* status;
-#ifdef I8_TRACE
-    long long* dbg;  // [cta][role][8] cycle counters
-#endif
 };
 
 namespace {
 
-#ifdef I8_TRACE
-#define TR_DECL long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tr_t = clock64();
-#define TR(k) { const long long tr_n = clock64(); tr[k] += tr_n - tr_t; tr_t = tr_n; }
-#define TR_OUT(role) if (lane == 0) { for (int k = 0; k < 8; ++k) p.dbg[(blockIdx.x * 4 + role) * 8 + k] = tr[k]; }
-#else
-#define TR_DECL
-#define TR(k)
-#define TR_OUT(role) {}
-#endif
 
-constexpr int DEC_WARPS = 8, DRAIN_WARPS = 8;  // decode: sets of four warps; drain: groups of four warps
+constexpr int DEC_WARPS = 8, DRAIN_WARPS = 16;  // decode: two sets of four warps; drain: two teams of eight warps
 constexpr int I8_THREADS = (DEC_WARPS + DRAIN_WARPS + 3) * 32;  // decode | drain | packed-weight TMA | activation TMA | MMA issue, TMEM
 constexpr int W_RAW = DEC_WARPS + DRAIN_WARPS, W_ACT = W_RAW + 1, W_MMA = W_RAW + 2;
 constexpr uint32_t RAW_PITCH = 144, RAW_TILE = 128 * RAW_PITCH;  // 18432 = 18 x 1024
@@ -79,7 +71,7 @@ constexpr uint32_t SC_SLOT = SC_REC + 32 * 20;                    // + the activ
 __host__ __device__ constexpr uint32_t aux_bytes(uint32_t MP) { return MP * 20; }  // per block: MP x 8 int16 block sums | MP x f32 d8
 // barriers (8 bytes each) at the start of dynamic shared memory
 constexpr int OFF_FULL = 0, OFF_EMPTY = 64, OFF_RAW_FULL = 128, OFF_RAW_EMPTY = 192, OFF_ACC_FULL = 256, OFF_ACC_EMPTY = 272,
-              OFF_SC_FULL = 320, OFF_TMEM = 448, OFF_DEAD = 452, OFF_RED = 456, OFF_LAST = 464, OFF_NSLOT = 472, OFF_SLOTS = 512,
+              OFF_SC_FULL = 320, OFF_TMEM = 448, OFF_DEAD = 452, OFF_RED = 456, OFF_LAST = 464, OFF_NSLOT = 472, OFF_XFER = 480, OFF_SLOTS = 512,
               OFF_SC = 1024;  // OFF_SLOTS: two lists of 64 slots
 
 __device__ __noinline__ bool i8_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* dead) {
@@ -155,9 +147,6 @@ __device__ __forceinline__ void tmem_ld8_async(uint32_t taddr, uint32_t (&r)[8])
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_ld4_async(uint32_t taddr, uint32_t (&r)[4]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // One piece of work of a CTA: blocks [b0, b0 + nb) of tile `tile`; slot < 0: the whole tile, written to the output.
@@ -202,11 +191,13 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
     volatile uint32_t* dead = reinterpret_cast<volatile uint32_t*>(smem + OFF_DEAD);
     constexpr uint32_t NACC = 2, ACC_COLS = 8 * MP, TMEM_COLS = NACC * ACC_COLS < 32 ? 32 : NACC * ACC_COLS;  // 256 or 512
     constexpr uint32_t B_ATOM = MP * 128, STAGE = 2 * A_ATOM + 2 * B_ATOM;
-    // shared memory: barriers | scale records | packed tiles | operand stages (A atom 0, A atom 1, B atom 0, B atom 1)
-    const uint32_t sc_off = OFF_SC, raw_off = (sc_off + p.nsc * SC_SLOT + 1023u) & ~1023u, st_off = raw_off + p.nr * RAW_TILE;
+    // shared memory: barriers | scale records | exchange buffer of the drain teams | packed tiles | operand stages (A atom
+    // 0, A atom 1, B atom 0, B atom 1)
+    const uint32_t sc_off = OFF_SC, x_off = sc_off + p.nsc * SC_SLOT, raw_off = (x_off + 128 * MP * 4 + 1023u) & ~1023u,
+                   st_off = raw_off + p.nr * RAW_TILE;
 
-    constexpr int MH = MP / (DRAIN_WARPS / 4);  // activation rows of a drain warp
-    const uint32_t drain_warps = 4 * min((uint32_t)DRAIN_WARPS / 4, (p.M + MH - 1) / MH);
+    constexpr int MH = MP / 2;  // activation rows of a drain warp: a team is 2 groups of 4 warps
+    const uint32_t team_warps = 4 * min(2u, (p.M + MH - 1) / MH);  // warps of a team whose activation rows exist
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.ns; ++s) {
             mbar_init(bar_full + 8 * s, 5);   // the four decode warps of a set + the activation copy (with its byte count)
@@ -218,10 +209,11 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
         }
         for (uint32_t s = 0; s < NACC; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
-            mbar_init(bar_acc_empty + 8 * s, drain_warps);  // the drain warps that have activation rows
+            mbar_init(bar_acc_empty + 8 * s, team_warps);  // the team that drains this accumulator
+            mbar_init(sbase + OFF_XFER + 8 * s, team_warps);  // the team's running sums are in the exchange buffer
         }
         for (uint32_t s = 0; s < p.nsc; ++s) mbar_init(bar_sc_full + 8 * s, 5);  // four decode warps write the records, one copy brings the activation side
-        mbar_init(sbase + OFF_RED, drain_warps);  // they meet here around the hand-over of a cut tile
+        mbar_init(sbase + OFF_RED, 2 * team_warps);  // both teams meet here around the hand-over of a cut tile
         *dead = 0;
         mbar_fence_init();
     }
@@ -281,23 +273,19 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
         uint32_t s = 0, par = 0, i = 0;
         bool ok = true;
         I8Unit u;
-        TR_DECL
         for (uint32_t it = 0; ok && i8_unit(p, it, u); ++it) {
             for (uint32_t j = 0; j < u.nb; ++j, ++i) {
                 const uint32_t buf = i % NACC, use = i / NACC;
-                TR(0)
                 if (!i8_wait(bar_full + 8 * s, par, dead)) {
                     if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
                     ok = false;
                     break;
                 }
-                TR(1)
                 if (use > 0 && !i8_wait(bar_acc_empty + 8 * buf, (use - 1) & 1, dead)) {
                     if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                     break;
                 }
-                TR(2)
                 tc_after();
                 if (elect_one_lane()) {
                     const uint32_t a_lo = desc_lo(sbase + st_off + s * STAGE), b_lo = desc_lo(sbase + st_off + s * STAGE + 2 * A_ATOM);
@@ -310,11 +298,9 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
                     tc_commit_to(bar_acc_full + 8 * buf);    // and the sums are complete
                 }
                 __syncwarp();
-                TR(3)
                 if (++s == p.ns) { s = 0; par ^= 1; }
             }
         }
-        TR_OUT(0)
     } else if (warp < DEC_WARPS) {
         // ------------------------------------------------------------ decode: nibbles -> int8 A operand, one thread per row
         // the sets of four warps take the CTA's blocks in turn, so DEC_WARPS / 4 blocks are in work at a time
@@ -323,18 +309,15 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
         bool ok = true;
         I8Unit u;
         uint32_t i = 0;
-        TR_DECL
         for (uint32_t it = 0; i8_unit(p, it, u); ++it) {
             const bool row_ok = u.tile * 128 + r < p.N;
             for (uint32_t j = 0; j < u.nb; ++j, ++i) {
                 if (i % (DEC_WARPS / 4) != set) continue;
                 const uint32_t rs = i % p.nr, rpar = (i / p.nr) & 1, s = i % p.ns, par = (i / p.ns) & 1;
-                TR(0)
                 if (ok && !i8_wait(bar_raw_full + 8 * rs, rpar, dead)) {
                     i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
                     ok = false;
                 }
-                TR(1)
                 const uint4* src = reinterpret_cast<const uint4*>(smem + raw_off + rs * RAW_TILE + r * RAW_PITCH);
                 uint4 h = make_uint4(0, 0, 0, 0), q[8];
 #pragma unroll
@@ -346,12 +329,10 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
-                TR(2)
                 if (ok && !i8_wait(bar_empty + 8 * s, par ^ 1, dead)) {
                     i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
                     ok = false;
                 }
-                TR(3)
                 // 16 nibble bytes q[k] = bytes 16k .. 16k+15 of qs: low nibbles -> sub-block 2 (k / 2), codes 16 (k & 1) ..;
                 // high nibbles -> sub-block 2 (k / 2) + 1.  Sub-block sb sits at bytes 32 sb .. of the 256-byte operand
                 // row: 16-byte chunk c = 2 sb + (k & 1) -> tile (c / 8), chunk (c % 8) ^ (row % 8) of the swizzled row.
@@ -379,23 +360,24 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
                     mbar_arrive(bar_full + 8 * s);
                     mbar_arrive(bar_sc_full + 8 * (i % p.nsc));
                 }
-                TR(4)
             }
         }
-        if (warp == 0) TR_OUT(1)
     } else {
         // ------------------------------------------------------------ drain: integer sums -> scaled f32 terms
-        // DRAIN_WARPS / 4 warps per quarter of the rows: a thread owns one weight row and MH of the activation rows (warps
-        // whose rows do not exist have nothing to do).  The CTA's pairs are the contiguous range [xa, xb): pair x =
-        // block x % nblk of tile x / nblk.
-        const uint32_t quarter = (uint32_t)warp & 3, r = quarter * 32 + lane, m_lo = (((uint32_t)warp - DEC_WARPS) >> 2) * MH;
+        // Two teams of eight warps take the CTA's blocks in turn (team = block index & 1 = accumulator), so the latencies
+        // of two blocks overlap.  In a team, a thread owns one weight row (two warps per quarter of the rows) and MH of
+        // the activation rows; warps whose rows do not exist have nothing to do.  The f32 sums still grow block by block,
+        // in K order: the running sums of a tile pass from team to team through a buffer in shared memory.
+        // The CTA's pairs are the contiguous range [xa, xb): pair x = block x % nblk of tile x / nblk.
+        const uint32_t dw = (uint32_t)warp - DEC_WARPS, team = dw >> 3, quarter = dw & 3, r = quarter * 32 + lane, m_lo = ((dw >> 2) & 1) * MH;
         const bool rows_exist = m_lo < p.M;
         const uint32_t lane_addr = (quarter * 32) << 16;
         const uint32_t xa = i8_range_begin(p, blockIdx.x), xb = i8_range_begin(p, blockIdx.x + 1);
-        const uint32_t bar_red = sbase + OFF_RED;
+        const uint32_t bar_red = sbase + OFF_RED, bar_x = sbase + OFF_XFER;
         volatile uint32_t* last_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_LAST);   // [2]
         volatile uint32_t* nslot = reinterpret_cast<volatile uint32_t*>(smem + OFF_NSLOT);      // [2]
         volatile uint32_t* slot_list = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOTS);  // [2][64]
+        float* xch = reinterpret_cast<float*>(smem + x_off) + m_lo * 128 + r;                   // [activation row][weight row]
         grid_dep_wait();  // the output and the scratch may still be in use by the previous kernel
         uint32_t red_phase = 0;
         bool ok = true;
@@ -415,80 +397,80 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
             }
             ++red_phase;
         };
-        // pieces of cut tiles this CTA has written: its first tile (0) and / or its last one (1)
-        bool have[2] = {false, false};
-        uint32_t cut_tile[2] = {0, 0};
-        float acc[MH];
-#pragma unroll
-        for (int m = 0; m < MH; ++m) acc[m] = 0.f;
-        TR_DECL
-        for (uint32_t x = xa; x < xb && ok && rows_exist; ++x) {
-            TR(0)
-            const uint32_t i = x - xa, buf = i % NACC, use = i / NACC, q = i % p.nsc;
+        // pieces of cut tiles this CTA writes: of its first tile (0) and / or of its last one (1)
+        const uint32_t t_first = xa / p.nblk, t_last = xb > xa ? (xb - 1) / p.nblk : t_first;
+        const bool have[2] = {xb > xa && (xa != t_first * p.nblk || xb < (t_first + 1) * p.nblk), t_last != t_first && xb != (t_last + 1) * p.nblk};
+        const uint32_t cut_tile[2] = {t_first, t_last};
+        for (uint32_t x = xa + team; x < xb && ok && rows_exist; x += 2) {
+            const uint32_t i = x - xa, buf = team, use = i >> 1, q = i % p.nsc;
             const uint32_t tile = x / p.nblk, blk = x - tile * p.nblk;
             if (!i8_wait(bar_sc_full + 8 * q, (i / p.nsc) & 1, dead)) {
                 i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
                 ok = false;
                 break;
             }
-            TR(1)
             const uint8_t* slot = smem + sc_off + q * SC_SLOT;
             const uint32_t* rec = reinterpret_cast<const uint32_t*>(slot) + r * SC_WORDS;
             const uint32_t hd = rec[0], s0 = rec[1], s1 = rec[2], m0 = rec[3], m1 = rec[4];
             const uint4* bsum = reinterpret_cast<const uint4*>(slot + SC_REC) + m_lo;
             const float* d8s = reinterpret_cast<const float*>(slot + SC_REC + MP * 16) + m_lo;
             const int sc[8] = {ubyte<0>(s0), ubyte<1>(s0), ubyte<2>(s0), ubyte<3>(s0), ubyte<0>(s1), ubyte<1>(s1), ubyte<2>(s1), ubyte<3>(s1)};
-            TR(2)
             if (!i8_wait(bar_acc_full + 8 * buf, use & 1, dead)) {
                 i8_fail(dead, p.status, STATUS_TIMEOUT_MMA);
                 ok = false;
                 break;
             }
-            TR(3)
             tc_after();
             const uint32_t t0 = tmem + lane_addr + buf * ACC_COLS + m_lo;
-            constexpr int GB = MH <= 8 ? 4 : 2;  // sub-blocks whose loads are in flight together
-            uint32_t v[GB][MH];
-            auto issue_loads = [&](int g) {
-#pragma unroll
-                for (int k = 0; k < GB; ++k) {
-                    if constexpr (MH == 16) tmem_ld16_async(t0 + MP * (GB * g + k), v[k]);
-                    else if constexpr (MH == 8) tmem_ld8_async(t0 + MP * (GB * g + k), v[k]);
-                    else tmem_ld4_async(t0 + MP * (GB * g + k), v[k]);
-                }
-            };
-            issue_loads(0);
-            // everything that does not need the integer sums, while the first loads are on their way
-            const float d = f16bits_to_f32(hd & 0xFFFF), dmin = f16bits_to_f32(hd >> 16);
-            float dall[MH], mterm[MH];
-#pragma unroll
-            for (int m = 0; m < MH; ++m) {
-                const uint4 bs = bsum[m];
-                const float d8 = d8s[m];
-                const int summ = __dp2a_lo((int)bs.x, (int)m0, __dp2a_hi((int)bs.y, (int)m0, __dp2a_lo((int)bs.z, (int)m1, __dp2a_hi((int)bs.w, (int)m1, 0))));
-                dall[m] = __fmul_rn(d, d8);
-                mterm[m] = __fmul_rn(__fmul_rn(dmin, d8), (float)summ);
-            }
+            constexpr int GB = 2;  // sub-blocks whose loads are in flight together
             int sumi[MH];
 #pragma unroll
             for (int m = 0; m < MH; ++m) sumi[m] = 0;
 #pragma unroll
             for (int g = 0; g < 8 / GB; ++g) {
+                uint32_t v[GB][MH];
+#pragma unroll
+                for (int k = 0; k < GB; ++k) {
+                    if constexpr (MH == 16) tmem_ld16_async(t0 + MP * (GB * g + k), v[k]);
+                    else tmem_ld8_async(t0 + MP * (GB * g + k), v[k]);
+                }
                 tmem_ld_wait();
 #pragma unroll
                 for (int k = 0; k < GB; ++k)
 #pragma unroll
                     for (int m = 0; m < MH; ++m) sumi[m] += sc[GB * g + k] * (int)v[k][m];
-                if (g + 1 < 8 / GB) issue_loads(g + 1);
             }
             tc_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);  // the MMA warp may reuse the columns
-            TR(4)
+            // the block's terms: (d d8) sumi - (dmin d8) sum_j m_j bsum_j
+            const float d = f16bits_to_f32(hd & 0xFFFF), dmin = f16bits_to_f32(hd >> 16);
+            float term[MH];
 #pragma unroll
-            for (int m = 0; m < MH; ++m) acc[m] = __fadd_rn(acc[m], __fsub_rn(__fmul_rn(dall[m], (float)sumi[m]), mterm[m]));
-            TR(5)
-            if (blk + 1 != p.nblk && x + 1 != xb) continue;
+            for (int m = 0; m < MH; ++m) {
+                const uint4 bs = bsum[m];
+                const float d8 = d8s[m];
+                const int summ = __dp2a_lo((int)bs.x, (int)m0, __dp2a_hi((int)bs.y, (int)m0, __dp2a_lo((int)bs.z, (int)m1, __dp2a_hi((int)bs.w, (int)m1, 0))));
+                term[m] = __fsub_rn(__fmul_rn(__fmul_rn(d, d8), (float)sumi[m]), __fmul_rn(__fmul_rn(dmin, d8), (float)summ));
+            }
+            // the running sums after the previous block (the other team's); every block waits for its predecessor, so the
+            // teams never drift apart by more than one block
+            const bool first_of_tile = blk == 0 || x == xa;
+            if (i > 0 && !i8_wait(bar_x + 8 * (team ^ 1), ((i - 1) >> 1) & 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                ok = false;
+                break;
+            }
+            if (!first_of_tile)
+#pragma unroll
+                for (int m = 0; m < MH; ++m) term[m] = __fadd_rn(xch[m * 128], term[m]);
+            const bool last_of_tile = blk + 1 == p.nblk || x + 1 == xb;
+            if (!last_of_tile)
+#pragma unroll
+                for (int m = 0; m < MH; ++m) xch[m * 128] = term[m];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_x + 8 * team);
+            if (!last_of_tile) continue;
             // ---- the CTA's last block of this tile
             const uint32_t n = tile * 128 + r;
             const bool whole = (tile * p.nblk >= xa) && ((tile + 1) * p.nblk <= xb);
@@ -496,19 +478,14 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
                 if (n < p.N)
 #pragma unroll
                     for (int m = 0; m < MH; ++m)
-                        if (m_lo + m < p.M) store_out(n, m_lo + m, acc[m]);
+                        if (m_lo + m < p.M) store_out(n, m_lo + m, term[m]);
             } else {
                 // a piece of a cut tile goes to scratch; the hand-over follows when all blocks are done
-                const uint32_t which = tile == xa / p.nblk ? 0u : 1u;
+                const uint32_t which = tile == t_first ? 0u : 1u;
                 float* part = p.part + ((size_t)(2 * blockIdx.x + which) * MP + m_lo) * 128;
 #pragma unroll
-                for (int m = 0; m < MH; ++m) part[m * 128 + r] = acc[m];
-                have[which] = true;
-                cut_tile[which] = tile;
+                for (int m = 0; m < MH; ++m) part[m * 128 + r] = term[m];
             }
-#pragma unroll
-            for (int m = 0; m < MH; ++m) acc[m] = 0.f;
-            TR(6)
         }
         // ---- cut tiles: whoever writes a tile's last piece adds all of them, in K order, and stores the rows
         if (ok && rows_exist && (have[0] || have[1])) {
@@ -539,36 +516,25 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q4k_kernel(const __gr
                 }
             }
             meet();
+            // the rows of a tile are shared out over both teams: team t adds the activation rows of its parity
             for (uint32_t which = 0; ok && which < 2; ++which) {
                 if (!have[which] || !last_flag[which]) continue;
                 const uint32_t ns = nslot[which], n = cut_tile[which] * 128 + r;
-                float tot[MH];
-                for (uint32_t k0 = 0; k0 < ns; k0 += 4) {
-                    float v[4][MH];
+                for (uint32_t m = m_lo + team; m < m_lo + MH && m < p.M; m += 2) {
+                    float tot = 0.f;
+                    for (uint32_t k0 = 0; k0 < ns; k0 += 8) {
+                        float v[8];
 #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {
-                        if (k0 + k < ns) {
-                            const float* src = p.part + ((size_t)slot_list[64 * which + k0 + k] * MP + m_lo) * 128 + r;
+                        for (uint32_t k = 0; k < 8; ++k)
+                            if (k0 + k < ns) v[k] = __ldcg(p.part + ((size_t)slot_list[64 * which + k0 + k] * MP + m) * 128 + r);
 #pragma unroll
-                            for (int m = 0; m < MH; ++m) v[k][m] = __ldcg(src + m * 128);
-                        }
+                        for (uint32_t k = 0; k < 8; ++k)
+                            if (k0 + k < ns) tot = k0 + k == 0 ? v[k] : __fadd_rn(tot, v[k]);
                     }
-#pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {
-                        if (k0 + k < ns) {
-#pragma unroll
-                            for (int m = 0; m < MH; ++m) tot[m] = k0 + k == 0 ? v[k][m] : __fadd_rn(tot[m], v[k][m]);
-                        }
-                    }
+                    if (n < p.N) store_out(n, m, tot);
                 }
-                if (n < p.N)
-#pragma unroll
-                    for (int m = 0; m < MH; ++m)
-                        if (m_lo + m < p.M) store_out(n, m_lo + m, tot[m]);
             }
-            TR(7)
         }
-        if (warp == DEC_WARPS) TR_OUT(2)
     }
     tc_before();
     __syncthreads();
@@ -630,9 +596,6 @@ __global__ void __launch_bounds__(256) i8_act_prep_kernel(const InT* __restrict_
     if (lane == 0) reinterpret_cast<float*>(ab + MP * 16)[m] = __fdiv_rn(amax, 127.0f);
 }
 
-#ifdef I8_TRACE
-long long* g_i8_dbg = nullptr;
-#endif
 struct I8Layout {
     uint32_t MP, nblk, ntiles, Q, grid, unit;
     size_t codes_bytes, aux_off, part_off, cnt_off, total;
@@ -666,6 +629,15 @@ bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N) {
     return fmt == FMT_Q4_K && M >= 2 && M <= 32 && K % 256 == 0 && K >= 256 && K / 256 <= 64 && N >= 1 && (N + 127) / 128 * (K / 256) < (1u << 30);
 }
 size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count) { return i8_layout(M, K, N, sm_count).total; }
+// Where it beats the mma.sync kernel (measured): matrices with enough 128-row tiles to give every SM whole tiles
+// (nothing to hand over), from 8 activation rows on; and every shape above 16 rows, which the mma.sync kernel takes
+// in two passes over the weights.
+bool smallm_i8_preferred(int fmt, size_t M, size_t K, size_t N, int sm_count) {
+    if (!smallm_i8_supported(fmt, M, K, N)) return false;
+    if (M > 16) return true;
+    const I8Layout l = i8_layout(M, K, N, sm_count);
+    return M >= 8 && l.unit == l.nblk && l.ntiles >= (uint32_t)sm_count * 3 / 4;
+}
 
 // acts_prepared: a previous call with the same activations and scratch left the image there (gate, then up).
 cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
@@ -708,16 +680,10 @@ cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((p.MP >> 3) << 17) | ((128u >> 4) << 24);
     p.out_dtype = out_dtype;
     p.status = status;
-#ifdef I8_TRACE
-    static long long* dbg = nullptr;
-    if (!dbg) cudaMalloc(&dbg, 256 * 4 * 8 * sizeof(long long));
-    p.dbg = dbg;
-    g_i8_dbg = dbg;
-#endif
     const uint32_t stage = 2 * A_ATOM + 2 * p.MP * 128;
     p.ns = 3;
     p.nsc = p.ns + 2 + 2;
-    const uint32_t fixed = 1024 + ((p.nsc * SC_SLOT + 1023u) & ~1023u) + p.ns * stage;
+    const uint32_t fixed = 1024 + ((p.nsc * SC_SLOT + 128 * p.MP * 4 + 1023u) & ~1023u) + p.ns * stage;
     p.nr = (232448u - 1024u - 1024u - fixed) / RAW_TILE;
     if (p.nr > 6) p.nr = 6;
     const size_t smem = 1024 + fixed + (size_t)p.nr * RAW_TILE;
@@ -761,9 +727,4 @@ cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void
     return cudaGetLastError();
 }
 
-#ifdef I8_TRACE
-extern "C" __attribute__((visibility("default"))) int b200q_i8_trace(long long* host) {
-    return g_i8_dbg ? (int)cudaMemcpy(host, g_i8_dbg, 256 * 4 * 8 * sizeof(long long), cudaMemcpyDeviceToHost) : -1;
-}
-#endif
 }  // namespace b200q

@@ -1,0 +1,144 @@
+"""The integer tensor-core small-M kernel (Q4_K, csrc/smallm_i8.cu) against the CPU oracle.
+
+It takes every Q4_K product with 17..32 activation rows and, from 8 rows on, the matrices with enough 128-row tiles for
+whole tiles per SM.  Bars: the integer sums are exact and the f32 block terms are added in K order, so a matrix that is
+dealt in whole tiles has the oracle's BITS at any K the oracle adds in one chain (K <= 4096); a matrix whose tiles are
+cut along K differs by the grouping of at most 56 f32 terms (<= 2e-6 of the largest output)."""
+import os
+
+import numpy as np
+import pytest
+
+from boostr_b200 import synth
+from boostr_b200.format import QuantFormat as F
+from util import describe_mismatch, rel_err, seed_of
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from boostr_b200 import ops as o
+
+    return o
+
+
+def _qt(w, n, k):
+    from boostr_b200.tensor import QuantTensor
+
+    return QuantTensor.from_bytes(w, F.Q4_K, (n, k), device="cuda")
+
+
+def _threads():
+    return os.cpu_count() or 8
+
+
+# whole tiles per SM: 111 tiles and more on a 148-SM part, 8..16 rows; and every row count above 16
+WHOLE = [(8, 14336, 4096), (16, 14336, 4096), (13, 14250, 2048), (32, 19000, 1024), (17, 128 * 148, 256)]
+# tiles cut along K (few tiles, or long K), ragged N, a single row of weights
+CUT = [(17, 50, 1024), (24, 4096, 14336), (32, 1024, 4096), (20, 4096, 4096), (31, 1, 256), (18, 129, 512), (32, 300, 16384)]
+
+
+@pytest.mark.parametrize("m,n,k", WHOLE)
+def test_whole_tiles_have_the_oracles_bits(ops, oracle, m, n, k):
+    rng = synth.rng_for(91, seed_of(m, n, k))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 777.0, device="cuda")
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(w, n, k), out=flat[guard:guard + m * n].view(m, n)).cpu().numpy()
+    ops.check_device_status()
+    assert (flat[:guard] == 777.0).all() and (flat[guard + m * n:] == 777.0).all(), "guard regions were written"
+    want = oracle.quant_matmul("Q4_K", act, w, n, threads=_threads())
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), describe_mismatch(got, want)
+
+
+@pytest.mark.parametrize("m,n,k", CUT)
+def test_cut_tiles(ops, oracle, m, n, k):
+    rng = synth.rng_for(92, seed_of(m, n, k))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 777.0, device="cuda")
+    x = torch.from_numpy(act).cuda()
+    qt = _qt(w, n, k)
+    got = ops.quant_matmul(x, qt, out=flat[guard:guard + m * n].view(m, n)).cpu().numpy()
+    ops.check_device_status()
+    assert (flat[:guard] == 777.0).all() and (flat[guard + m * n:] == 777.0).all(), "guard regions were written"
+    want = oracle.quant_matmul("Q4_K", act, w, n, threads=_threads())
+    e_max, e_rms = rel_err(got, want)
+    assert np.isfinite(got).all()
+    assert e_max <= 2e-6, f"M={m} N={n} K={k}: {e_max:.3e} (rms {e_rms:.3e})\n" + describe_mismatch(got, want)
+    # the per-tile counters are back at zero: a second and a third call give the same bits
+    for _ in range(2):
+        again = ops.quant_matmul(x, qt).cpu().numpy()
+        assert np.array_equal(again.view(np.uint32), got.view(np.uint32))
+    ops.check_device_status()
+
+
+def test_bf16_activations_and_16bit_outputs(ops, oracle):
+    m, n, k = 24, 700, 2048
+    rng = synth.rng_for(93, 1)
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    xb = torch.from_numpy(act).cuda().to(torch.bfloat16)
+    act_bf = xb.float().cpu().numpy()
+    want = oracle.quant_matmul("Q4_K", act_bf, w, n, threads=_threads())
+    qt = _qt(w, n, k)
+    got = ops.quant_matmul(xb, qt, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(got, want)[0] <= 2e-6
+    for dt, tol in ((torch.bfloat16, 2 ** -8), (torch.float16, 2 ** -10)):
+        g16 = ops.quant_matmul(xb, qt, out_dtype=dt).float().cpu().numpy()
+        assert rel_err(g16, want)[0] <= tol, dt
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 14336, 4096), (32, 512, 1024), (19, 1000, 4096)])
+def test_swiglu(ops, oracle, m, n, k):
+    rng = synth.rng_for(94, seed_of(m, n, k))
+    act = synth.activations(rng, m, k)
+    wg = synth.weight_bytes("Q4_K", rng, n, k)
+    wu = synth.weight_bytes("Q4_K", rng, n, k)
+    got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _qt(wg, n, k), _qt(wu, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_swiglu("Q4_K", act, wg, wu, n, threads=_threads())
+    e_max, _ = rel_err(got, want)
+    assert e_max <= 1e-5, f"{e_max:.3e}\n" + describe_mismatch(got, want)
+
+
+def test_zero_rows_and_a_zero_activation_row(ops, oracle):
+    # an all-zero activation row quantises with d8 = 0 and must give exact zeros, beside ordinary rows
+    m, n, k = 20, 260, 1024
+    rng = synth.rng_for(95, 2)
+    act = synth.activations(rng, m, k)
+    act[7] = 0.0
+    w = synth.weight_bytes("Q4_K", rng, n, k)
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), _qt(w, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_matmul("Q4_K", act, w, n, threads=4)
+    assert (got[7] == 0.0).all()
+    assert rel_err(got, want)[0] <= 2e-6
+
+
+def test_graph_replay_is_bitwise_identical(ops):
+    m, n, k = 32, 2048, 4096
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(9)
+    w = synth.device_weight("Q4_K", n, k, gen)
+    x = torch.randn(m, k, device="cuda", generator=gen)
+    y = torch.empty(m, n, device="cuda")
+    ref = ops.quant_matmul(x, w).clone()
+    for _ in range(2):
+        ops.quant_matmul(x, w, out=y)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.quant_matmul(x, w, out=y)
+    for _ in range(3):
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref)
+    ops.check_device_status()
