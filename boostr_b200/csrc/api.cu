@@ -48,7 +48,7 @@ cudaError_t launch_swiglu_gate(const float* gate, const float* up, void* out, in
                                cudaStream_t st);
 bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N);
 bool smallm_i8_preferred(int fmt, size_t M, size_t K, size_t N, int sm_count);
-size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count);
+size_t smallm_i8_workspace_bytes(int fmt, size_t M, size_t K, size_t N, int sm_count);
 cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
                              size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status,
                              bool* ws_too_small, char* err, size_t err_len, bool acts_prepared);
@@ -176,7 +176,7 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
     if (!swiglu && gemv_m1_f32_supported(format, M, K, N)) return 0;
     // small-M kernel: the activation image, plus split-K partial sums when K is long
     if (smallm_i8_preferred(format, M, K, N, sm_count_current()))  // integer tensor-core kernel (+ gate and up for SwiGLU)
-        return smallm_i8_workspace_bytes(M, K, N, sm_count_current()) + (swiglu ? 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255) : 0);
+        return smallm_i8_workspace_bytes(format, M, K, N, sm_count_current()) + (swiglu ? 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255) : 0);
     return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
 }
 

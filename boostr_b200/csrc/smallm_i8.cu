@@ -596,6 +596,360 @@ __global__ void __launch_bounds__(256) i8_act_prep_kernel(const InT* __restrict_
     if (lane == 0) reinterpret_cast<float*>(ab + MP * 16)[m] = __fdiv_rn(amax, 127.0f);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Q8_0 (f32 activations on boostr's CPU path: dequantised row . f32 dot, src/quant/cpu/kernels/quant_matmul.rs:193-209).
+// The weight codes are int8 already; every activation is P int8 PIECES, x = amax/127 (a1 + a2/254 [+ a3/254^2]) with amax
+// over its 256-run (P = 3 up to 8 rows: ~1e-7 of the run's amax; P = 2 above: ~3e-5), stacked as P x MP rows of the B
+// operand.  One MMA per 32-block (128 weight rows x P MP x 32) leaves the block's integer sums of every piece in its
+// own columns; the drain converts them, weighs the pieces, multiplies by the block's d and adds in f32.  Same pipeline
+// as above with two differences: an accumulator holds the four blocks of half a 256-run (one 128-byte operand tile), so
+// a stage feeds two accumulators; and nothing here has to have the CPU's bits, so the drain teams keep their own sums
+// (MP = 16: team = half-run; MP = 32: all drain warps on every accumulator, a quarter of the rows each) and only whole
+// tiles are dealt (no hand-over).
+struct Q8Params {
+    const uint8_t* w;
+    void* out;
+    const float* scale;   // [nblk256][MP] amax / 127 of (256-run, activation row)
+    uint32_t M, N, K;
+    uint32_t nblk;        // K / 256
+    uint32_t ntiles;      // ceil(N / 128)
+    uint32_t ns, nr, nsc;
+    uint32_t idesc;
+    int out_dtype;
+    unsigned int* status;
+};
+constexpr uint32_t Q8_RAW_PITCH = 272, Q8_RAW_TILE = 128 * Q8_RAW_PITCH;  // 34816 = 34 x 1024
+constexpr uint32_t Q8_REC_WORDS = 4;                                       // the eight f16 d of a row's 256-run
+constexpr uint32_t Q8_REC = 128 * Q8_REC_WORDS * 4;
+constexpr uint32_t Q8_SLOT = Q8_REC + 32 * 4;                              // + the activation rows' scales of the run
+constexpr float Q8_STEP = 254.0f;
+
+// tile t of the CTA's share: whole tiles, round-robin
+template <int MP, int P>
+__global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __grid_constant__ CUtensorMap tmap_act,
+                                                                       const __grid_constant__ CUtensorMap tmap_w, const Q8Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + OFF_FULL, bar_empty = sbase + OFF_EMPTY, bar_raw_full = sbase + OFF_RAW_FULL,
+                   bar_raw_empty = sbase + OFF_RAW_EMPTY, bar_acc_full = sbase + OFF_ACC_FULL, bar_acc_empty = sbase + OFF_ACC_EMPTY,
+                   bar_sc_full = sbase + OFF_SC_FULL, bar_x = sbase + OFF_XFER;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM);
+    volatile uint32_t* dead = reinterpret_cast<volatile uint32_t*>(smem + OFF_DEAD);
+    constexpr uint32_t NB = P * MP;                      // MMA N: the pieces' rows
+    constexpr uint32_t ACC_COLS = 4 * NB;                // four 32-blocks
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS <= 256 ? 256 : 512;
+    constexpr uint32_t B_ATOM = NB * 128, STAGE = 2 * A_ATOM + 2 * B_ATOM;
+    constexpr int MH = 8;                                // activation rows of a drain thread
+    constexpr bool TEAMS = MP == 16;                     // two teams of eight warps, one per half-run; else four groups of four warps
+    const uint32_t sc_off = OFF_SC, x_off = sc_off + p.nsc * Q8_SLOT, raw_off = (x_off + 128 * 16 * 4 + 1023u) & ~1023u,
+                   st_off = raw_off + p.nr * Q8_RAW_TILE;
+    // drain warps whose activation rows exist, per accumulator
+    const uint32_t groups = min((uint32_t)MP / MH, (p.M + MH - 1) / MH), acc_warps = 4 * groups;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.ns; ++s) {
+            mbar_init(bar_full + 8 * s, 5);   // the four decode warps of a set + the activation copy
+            mbar_init(bar_empty + 8 * s, 1);  // the commit behind the stage's second group of MMAs
+        }
+        for (uint32_t s = 0; s < p.nr; ++s) {
+            mbar_init(bar_raw_full + 8 * s, 1);
+            mbar_init(bar_raw_empty + 8 * s, 4);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar_acc_full + 8 * s, 1);
+            mbar_init(bar_acc_empty + 8 * s, acc_warps);
+        }
+        mbar_init(bar_x, acc_warps);      // MP = 16: the second team's sums of a tile are in the exchange buffer
+        mbar_init(bar_x + 8, acc_warps);  // ... and the first team has taken them
+        for (uint32_t s = 0; s < p.nsc; ++s) mbar_init(bar_sc_full + 8 * s, 5);
+        *dead = 0;
+        mbar_fence_init();
+    }
+    if (warp == W_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + OFF_TMEM), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_before();
+    __syncthreads();
+    tc_after();
+    const uint32_t tmem = *tmem_holder;
+    grid_dep_launch();
+    // the CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; block i of the CTA = block i % nblk of its (i / nblk)-th tile
+    const uint32_t my_tiles = p.ntiles > blockIdx.x ? (p.ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+    const uint32_t nblocks = my_tiles * p.nblk;
+
+    if (warp == W_RAW) {
+        if (lane == 0) {
+            for (uint32_t i = 0; i < nblocks && !*dead; ++i) {
+                const uint32_t s = i % p.nr, par = (i / p.nr) & 1, tile = blockIdx.x + (i / p.nblk) * gridDim.x, blk = i % p.nblk;
+                if (!i8_wait(bar_raw_empty + 8 * s, par ^ 1, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    break;
+                }
+                mbar_expect_tx(bar_raw_full + 8 * s, Q8_RAW_TILE);
+                tma2d(sbase + raw_off + s * Q8_RAW_TILE, &tmap_w, (int)(blk * 136), (int)(tile * 128), bar_raw_full + 8 * s);  // x in 16-bit units
+            }
+        }
+    } else if (warp == W_ACT) {
+        if (lane == 0) {
+            grid_dep_wait();
+            for (uint32_t i = 0; i < nblocks && !*dead; ++i) {
+                const uint32_t s = i % p.ns, par = (i / p.ns) & 1, blk = i % p.nblk, q = i % p.nsc;
+                if (!i8_wait(bar_empty + 8 * s, par ^ 1, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    break;
+                }
+                const uint32_t b0 = sbase + st_off + s * STAGE + 2 * A_ATOM;
+                mbar_expect_tx(bar_full + 8 * s, 2 * B_ATOM);
+                tma2d(b0, &tmap_act, (int)(blk * 256), 0, bar_full + 8 * s);
+                tma2d(b0 + B_ATOM, &tmap_act, (int)(blk * 256 + 128), 0, bar_full + 8 * s);
+                mbar_expect_tx(bar_sc_full + 8 * q, MP * 4);
+                bulk_g2s(sbase + sc_off + q * Q8_SLOT + Q8_REC, p.scale + (size_t)blk * MP, MP * 4, bar_sc_full + 8 * q);
+            }
+        }
+    } else if (warp == W_MMA) {
+        // ------------------------------------------------------------ MMA issue: per stage two accumulators of four blocks
+        bool ok = true;
+        for (uint32_t i = 0; ok && i < nblocks; ++i) {
+            const uint32_t s = i % p.ns, par = (i / p.ns) & 1;
+            if (!i8_wait(bar_full + 8 * s, par, dead)) {
+                if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                break;
+            }
+            for (uint32_t h = 0; h < 2; ++h) {  // accumulator h = half-run h of the block: use number i of this accumulator
+                if (i > 0 && !i8_wait(bar_acc_empty + 8 * h, (i - 1) & 1, dead)) {
+                    if (lane == 0) i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    ok = false;
+                    break;
+                }
+                tc_after();
+                if (elect_one_lane()) {
+                    const uint32_t a_lo = desc_lo(sbase + st_off + s * STAGE + h * A_ATOM), b_lo = desc_lo(sbase + st_off + s * STAGE + 2 * A_ATOM + h * B_ATOM);
+#pragma unroll
+                    for (uint32_t b = 0; b < 4; ++b) tc_mma_i8(tmem + h * ACC_COLS + NB * b, desc_sw128(a_lo + 2 * b), desc_sw128(b_lo + 2 * b), p.idesc);
+                    if (h == 1) tc_commit_to(bar_empty + 8 * s);
+                    tc_commit_to(bar_acc_full + 8 * h);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < DEC_WARPS) {
+        // ------------------------------------------------------------ decode: copy the codes into the A operand, one thread per row
+        // Raw row of a 256-run: eight blocks of 34 bytes (f16 d | 32 x i8) = 68 words.  The codes of block b start at byte
+        // 34 b + 2: on a word boundary for odd b, two bytes past one for even b (a word = two neighbours and a byte permute).
+        const uint32_t r = threadIdx.x & 127, set = threadIdx.x >> 7;
+        const uint32_t row_sw = (r >> 3) * 1024 + (r & 7) * 128, x7 = r & 7;
+        bool ok = true;
+        for (uint32_t i = set; i < nblocks; i += DEC_WARPS / 4) {
+            const uint32_t rs = i % p.nr, rpar = (i / p.nr) & 1, s = i % p.ns, par = (i / p.ns) & 1;
+            const bool row_ok = (blockIdx.x + (i / p.nblk) * gridDim.x) * 128 + r < p.N;
+            if (ok && !i8_wait(bar_raw_full + 8 * rs, rpar, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                ok = false;
+            }
+            if (ok && !i8_wait(bar_empty + 8 * s, par ^ 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                ok = false;
+            }
+            const uint4* src = reinterpret_cast<const uint4*>(smem + raw_off + rs * Q8_RAW_TILE + r * Q8_RAW_PITCH);
+            uint8_t* a0 = smem + st_off + s * STAGE + row_sw;
+            uint32_t dd[8];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                constexpr int K0[8] = {0, 9, 17, 26, 34, 43, 51, 60};  // first word that holds codes of block b
+                const int q0 = (K0[b] - (b & 1)) / 4, off = K0[b] - 4 * q0;  // three 16-byte loads from word 4 q0 cover d and the codes
+                uint32_t a[12];
+                if (ok && row_ok) {
+                    const uint4 u0 = src[q0], u1 = src[q0 + 1], u2 = src[q0 + 2];
+                    a[0] = u0.x; a[1] = u0.y; a[2] = u0.z; a[3] = u0.w; a[4] = u1.x; a[5] = u1.y; a[6] = u1.z; a[7] = u1.w;
+                    a[8] = u2.x; a[9] = u2.y; a[10] = u2.z; a[11] = u2.w;
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 12; ++k) a[k] = 0;
+                }
+                uint32_t o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = (b & 1) ? a[off + j] : __byte_perm(a[off + j], a[off + j + 1], 0x5432);
+                dd[b] = (b & 1) ? a[off - 1] >> 16 : a[off] & 0xFFFFu;
+                // block b = bytes 32 b .. of the 256-byte operand row: 16-byte chunks 2 b, 2 b + 1 -> tile b / 4
+                uint8_t* at = a0 + (b >> 2) * A_ATOM;
+                *reinterpret_cast<uint4*>(at + ((((2 * b) & 7) ^ x7) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(at + ((((2 * b + 1) & 7) ^ x7) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);
+            uint32_t* rec = reinterpret_cast<uint32_t*>(smem + sc_off + (i % p.nsc) * Q8_SLOT) + r * Q8_REC_WORDS;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) rec[k] = dd[2 * k] | (dd[2 * k + 1] << 16);
+            proxy_fence();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_full + 8 * s);
+                mbar_arrive(bar_sc_full + 8 * (i % p.nsc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ drain
+        const uint32_t dw = (uint32_t)warp - DEC_WARPS, quarter = dw & 3, r = quarter * 32 + lane;
+        const uint32_t team = TEAMS ? dw >> 3 : 0u, m_lo = (TEAMS ? (dw >> 2) & 1 : dw >> 2) * MH;
+        const bool rows_exist = m_lo < p.M;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        float* xch = reinterpret_cast<float*>(smem + x_off) + m_lo * 128 + r;
+        grid_dep_wait();
+        bool ok = true;
+        float acc[MH];
+#pragma unroll
+        for (int m = 0; m < MH; ++m) acc[m] = 0.f;
+        constexpr float C1 = 1.0f / Q8_STEP;
+        for (uint32_t i = 0; i < nblocks && ok && rows_exist; ++i) {
+            const uint32_t q = i % p.nsc, blk = i % p.nblk, tl = i / p.nblk;
+            if (!i8_wait(bar_sc_full + 8 * q, (i / p.nsc) & 1, dead)) {
+                i8_fail(dead, p.status, STATUS_TIMEOUT_FULL);
+                ok = false;
+                break;
+            }
+            const uint8_t* slot = smem + sc_off + q * Q8_SLOT;
+            const uint32_t* rec = reinterpret_cast<const uint32_t*>(slot) + r * Q8_REC_WORDS;
+            const float* scl = reinterpret_cast<const float*>(slot + Q8_REC) + m_lo;
+#pragma unroll
+            for (uint32_t hh = 0; hh < (TEAMS ? 1u : 2u); ++hh) {
+                const uint32_t h = TEAMS ? team : hh;
+                const uint32_t d01 = rec[2 * h], d23 = rec[2 * h + 1];
+                const float db[4] = {f16bits_to_f32(d01 & 0xFFFF), f16bits_to_f32(d01 >> 16), f16bits_to_f32(d23 & 0xFFFF), f16bits_to_f32(d23 >> 16)};
+                if (!i8_wait(bar_acc_full + 8 * h, i & 1, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tc_after();
+                float sacc[MH], sacc2[MH];
+#pragma unroll
+                for (int m = 0; m < MH; ++m) sacc[m] = sacc2[m] = 0.f;
+                const uint32_t t0 = tmem + lane_addr + h * ACC_COLS + m_lo;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    uint32_t v[P][MH];
+#pragma unroll
+                    for (int pc = 0; pc < P; ++pc) tmem_ld8_async(t0 + NB * b + MP * pc, v[pc]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int m = 0; m < MH; ++m) {
+                        float h2 = (float)(int)v[1][m];
+                        if constexpr (P > 2) h2 = fmaf((float)(int)v[2][m], C1, h2);
+                        sacc[m] = fmaf(db[b], (float)(int)v[0][m], sacc[m]);
+                        sacc2[m] = fmaf(db[b], h2, sacc2[m]);
+                    }
+                }
+                tc_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * h);
+#pragma unroll
+                for (int m = 0; m < MH; ++m) acc[m] = fmaf(fmaf(sacc2[m], C1, sacc[m]), scl[m], acc[m]);
+            }
+            if (!ok || blk + 1 != p.nblk) continue;
+            // ---- the tile is complete
+            const uint32_t n = (blockIdx.x + tl * gridDim.x) * 128 + r;
+            if (TEAMS && team == 1) {
+                // hand the second half-runs' sums to the first team (the buffer is free once it has taken the last tile's)
+                if (tl > 0 && !i8_wait(bar_x + 8, (tl - 1) & 1, dead)) {
+                    i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int m = 0; m < MH; ++m) xch[m * 128] = acc[m];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_x);
+            } else {
+                if (TEAMS) {
+                    if (!i8_wait(bar_x, tl & 1, dead)) {
+                        i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int m = 0; m < MH; ++m) acc[m] += xch[m * 128];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_x + 8);
+                }
+                if (n < p.N)
+#pragma unroll
+                    for (int m = 0; m < MH; ++m) {
+                        if (m_lo + m < p.M) {
+                            const size_t idx = (size_t)(m_lo + m) * p.N + n;
+                            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = acc[m];
+                            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc[m]);
+                            else static_cast<__half*>(p.out)[idx] = __float2half_rn(acc[m]);
+                        }
+                    }
+            }
+#pragma unroll
+            for (int m = 0; m < MH; ++m) acc[m] = 0.f;
+        }
+    }
+    tc_before();
+    __syncthreads();
+    if (warp == W_MMA) {
+        tc_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// One warp per (activation row, 256-run): the run's amax / 127 into scale[run][row] and every value as P int8 pieces,
+// x = amax/127 (a1 + a2/254 + a3/254^2), piece pc of row m into row pc MP + m of the image [P MP][K]; rows that do not
+// exist are written as zeros (the B operand reads all MP rows of a piece).
+template <typename InT, int P>
+__global__ void __launch_bounds__(256) q8_act_prep_kernel(const InT* __restrict__ act, uint8_t* __restrict__ img, float* __restrict__ scale,
+                                                          uint32_t M, uint32_t K, uint32_t MP) {
+    const int lane = threadIdx.x & 31;
+    grid_dep_launch();
+    grid_dep_wait();
+    const uint32_t nblk = K / 256, run = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (run >= MP * nblk) return;
+    const uint32_t m = run / nblk, b = run % nblk;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    if (m < M) {
+        const size_t base = (size_t)m * K + (size_t)b * 256 + 8 * lane;
+        if constexpr (sizeof(InT) == 4) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(act + base)), y = __ldg(reinterpret_cast<const float4*>(act + base) + 1);
+            v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+        } else {
+            const uint4 rr = __ldg(reinterpret_cast<const uint4*>(act + base));
+            v[0] = __uint_as_float(rr.x << 16); v[1] = __uint_as_float(rr.x & 0xFFFF0000u);
+            v[2] = __uint_as_float(rr.y << 16); v[3] = __uint_as_float(rr.y & 0xFFFF0000u);
+            v[4] = __uint_as_float(rr.z << 16); v[5] = __uint_as_float(rr.z & 0xFFFF0000u);
+            v[6] = __uint_as_float(rr.w << 16); v[7] = __uint_as_float(rr.w & 0xFFFF0000u);
+        }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float id = amax != 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+    uint32_t w[P][2];
+#pragma unroll
+    for (int pc = 0; pc < P; ++pc) w[pc][0] = w[pc][1] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float rr = __fmul_rn(v[i], id);  // |rr| <= 127 (+ one rounding)
+#pragma unroll
+        for (int pc = 0; pc < P; ++pc) {
+            const int c = max(-127, min(127, (int)rintf(rr)));
+            w[pc][i >> 2] |= (uint32_t)(c & 0xFF) << (8 * (i & 3));
+            rr = __fmul_rn(__fsub_rn(rr, (float)c), Q8_STEP);  // remainder in [-0.5, 0.5] -> [-127, 127]
+        }
+    }
+#pragma unroll
+    for (int pc = 0; pc < P; ++pc)
+        *reinterpret_cast<uint2*>(img + ((size_t)(pc * MP + m) * K + (size_t)b * 256 + 8 * lane)) = make_uint2(w[pc][0], w[pc][1]);
+    if (lane == 0) scale[(size_t)b * MP + m] = m < M ? __fdiv_rn(amax, 127.0f) : 0.f;
+}
+
 struct I8Layout {
     uint32_t MP, nblk, ntiles, Q, grid, unit;
     size_t codes_bytes, aux_off, part_off, cnt_off, total;
@@ -621,19 +975,125 @@ I8Layout i8_layout(size_t M, size_t K, size_t N, int sm_count) {
     return l;
 }
 
+struct Q8Layout {
+    uint32_t MP, P, nblk, ntiles, grid;
+    size_t img_bytes, scale_off, total;
+};
+Q8Layout q8_layout(size_t M, size_t K, size_t N, int sm_count) {
+    Q8Layout l{};
+    (void)M;
+    l.MP = 32u;  // 17..32 rows
+    l.P = 2u;
+    l.nblk = (uint32_t)(K / 256);
+    l.ntiles = (uint32_t)((N + 127) / 128);
+    l.grid = l.ntiles < (uint32_t)sm_count ? l.ntiles : (uint32_t)sm_count;
+    l.img_bytes = ((size_t)l.P * l.MP * K + 255) & ~(size_t)255;
+    l.scale_off = l.img_bytes;
+    l.total = l.scale_off + (((size_t)l.nblk * l.MP * 4 + 255) & ~(size_t)255);
+    return l;
+}
+
+template <int MP, int P>
+cudaError_t launch_q8_kernel(const CUtensorMap& amap, const CUtensorMap& wmap, const Q8Params& p, uint32_t grid, size_t smem, cudaStream_t st) {
+    static PerDeviceOnce attrs;
+    cudaError_t e = attrs.run([] { return cudaFuncSetAttribute(smallm_i8_q8_0_kernel<MP, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+    if (e != cudaSuccess) return e;
+    return launch_pdl(smallm_i8_q8_0_kernel<MP, P>, dim3(grid), dim3(I8_THREADS), smem, st, amap, wmap, p);
+}
+
+cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K, size_t N, void* ws,
+                               size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status, bool* ws_too_small, char* err,
+                               size_t err_len, bool acts_prepared) {
+    *ws_too_small = false;
+    const Q8Layout l = q8_layout(M, K, N, sm_count);
+    if (!ws || ws_bytes < l.total || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    float* scale = reinterpret_cast<float*>(base + l.scale_off);
+    if (!acts_prepared) {
+        const dim3 pg((l.MP * l.nblk + 7) / 8);
+        cudaError_t e;
+        if (act_dtype == DT_F32)
+            e = launch_pdl(q8_act_prep_kernel<float, 2>, pg, dim3(256), 0, st, static_cast<const float*>(act), base, scale, (uint32_t)M, (uint32_t)K, l.MP);
+        else
+            e = launch_pdl(q8_act_prep_kernel<__nv_bfloat16, 2>, pg, dim3(256), 0, st, static_cast<const __nv_bfloat16*>(act), base, scale, (uint32_t)M,
+                           (uint32_t)K, l.MP);
+        note_launch();
+        if (e != cudaSuccess) return e;
+    }
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled is not available from this driver");
+        return cudaErrorNotSupported;
+    }
+    Q8Params p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.out = out;
+    p.scale = scale;
+    p.M = (uint32_t)M; p.N = (uint32_t)N; p.K = (uint32_t)K;
+    p.nblk = l.nblk; p.ntiles = l.ntiles;
+    const uint32_t NB = l.P * l.MP;
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((NB >> 3) << 17) | ((128u >> 4) << 24);  // int32 <- s8 x s8, K-major, N = P MP, M = 128
+    p.out_dtype = out_dtype;
+    p.status = status;
+    const uint32_t stage = 2 * A_ATOM + 2 * NB * 128;
+    p.ns = 2;
+    p.nsc = p.ns + 2 + 2;
+    const uint32_t fixed = 1024 + ((p.nsc * Q8_SLOT + 128 * 16 * 4 + 1023u) & ~1023u) + p.ns * stage;
+    p.nr = (232448u - 1024u - 1024u - fixed) / Q8_RAW_TILE;
+    if (p.nr > 4) p.nr = 4;
+    const size_t smem = 1024 + fixed + (size_t)p.nr * Q8_RAW_TILE;
+
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap amap, wmap;
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)NB};
+        const cuuint64_t gstride[1] = {(cuuint64_t)K};
+        const cuuint32_t box[2] = {128u, NB};
+        CUresult cr = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (activation image %p, K=%zu, rows %u)", (int)cr, (void*)base, K, NB);
+            return cudaErrorInvalidValue;
+        }
+    }
+    {
+        // packed rows as 16-bit units (a box dimension holds at most 256 elements): 136 units = the 272 bytes of a 256-run
+        const uint32_t row_bytes = l.nblk * 272;
+        const cuuint64_t gdim[2] = {(cuuint64_t)(row_bytes / 2), (cuuint64_t)N};
+        const cuuint64_t gstride[1] = {(cuuint64_t)row_bytes};
+        const cuuint32_t box[2] = {136u, 128u};
+        CUresult cr = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(w), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d (weight pointer %p, row bytes %u, N=%zu)", (int)cr, w, row_bytes, N);
+            return cudaErrorInvalidValue;
+        }
+    }
+    cudaError_t e = launch_q8_kernel<32, 2>(amap, wmap, p, l.grid, smem, st);
+    note_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 }  // namespace
 
-// Shapes the integer tensor-core kernel takes: Q4_K, 2 <= M <= 32, whole 256-blocks, rows a multiple of 16 bytes
-// (always so: 144-byte blocks), N * K small enough for 32-bit pair counts.
+// Shapes the integer tensor-core kernels take.  Q4_K: 2 <= M <= 32, whole 256-blocks (rows are multiples of 16 bytes:
+// 144-byte blocks), pair counts within 32 bits.  Q8_0: 17 <= M <= 32 (up to 16 rows the mma.sync kernel is as fast: the
+// kernel is written for 16 rows and for three pieces as well, but only the instance that is used is built), K a multiple
+// of 256 (rows of whole 272-byte runs), whole tiles only.
 bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N) {
-    return fmt == FMT_Q4_K && M >= 2 && M <= 32 && K % 256 == 0 && K >= 256 && K / 256 <= 64 && N >= 1 && (N + 127) / 128 * (K / 256) < (1u << 30);
+    if (M < 2 || M > 32 || K % 256 != 0 || K < 256 || N < 1 || (N + 127) / 128 * (K / 256) >= (1u << 30)) return false;
+    return (fmt == FMT_Q8_0 && M > 16) || (fmt == FMT_Q4_K && K / 256 <= 64);
 }
-size_t smallm_i8_workspace_bytes(size_t M, size_t K, size_t N, int sm_count) { return i8_layout(M, K, N, sm_count).total; }
-// Where it beats the mma.sync kernel (measured): matrices with enough 128-row tiles to give every SM whole tiles
-// (nothing to hand over), from 8 activation rows on; and every shape above 16 rows, which the mma.sync kernel takes
-// in two passes over the weights.
+size_t smallm_i8_workspace_bytes(int fmt, size_t M, size_t K, size_t N, int sm_count) {
+    return fmt == FMT_Q8_0 ? q8_layout(M, K, N, sm_count).total : i8_layout(M, K, N, sm_count).total;
+}
+// Where they beat the mma.sync kernel (measured).  Q4_K: matrices with enough 128-row tiles to give every SM whole tiles
+// (nothing to hand over), from 8 activation rows on; and every shape above 16 rows, which the mma.sync kernel takes in
+// two passes over the weights.  Q8_0: above 16 rows (one pass over the weights instead of two), matrices with enough
+// tiles to occupy half of the SMs (only whole tiles are dealt).
 bool smallm_i8_preferred(int fmt, size_t M, size_t K, size_t N, int sm_count) {
     if (!smallm_i8_supported(fmt, M, K, N)) return false;
+    if (fmt == FMT_Q8_0) return M > 16 && (N + 127) / 128 >= (size_t)sm_count / 2;
     if (M > 16) return true;
     const I8Layout l = i8_layout(M, K, N, sm_count);
     return M >= 8 && l.unit == l.nblk && l.ntiles >= (uint32_t)sm_count * 3 / 4;
@@ -643,7 +1103,8 @@ bool smallm_i8_preferred(int fmt, size_t M, size_t K, size_t N, int sm_count) {
 cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K,
                              size_t N, void* ws, size_t ws_bytes, int sm_count, cudaStream_t st, unsigned int* status,
                              bool* ws_too_small, char* err, size_t err_len, bool acts_prepared) {
-    (void)fmt;
+    if (fmt == FMT_Q8_0)
+        return launch_smallm_q8_0(act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count, st, status, ws_too_small, err, err_len, acts_prepared);
     *ws_too_small = false;
     const I8Layout l = i8_layout(M, K, N, sm_count);
     if (!ws || ws_bytes < l.total || (reinterpret_cast<uintptr_t>(ws) & 15)) { *ws_too_small = true; return cudaSuccess; }

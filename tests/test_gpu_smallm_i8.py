@@ -1,6 +1,6 @@
-"""The integer tensor-core small-M kernel (Q4_K, csrc/smallm_i8.cu) against the CPU oracle.
+"""The integer tensor-core small-M kernels (csrc/smallm_i8.cu: Q4_K, and Q8_0 above 16 rows) against the CPU oracle.
 
-It takes every Q4_K product with 17..32 activation rows and, from 8 rows on, the matrices with enough 128-row tiles for
+The Q4_K kernel takes every Q4_K product with 17..32 activation rows and, from 8 rows on, the matrices with enough 128-row tiles for
 whole tiles per SM.  Bars: the integer sums are exact and the f32 block terms are added in K order, so a matrix that is
 dealt in whole tiles has the oracle's BITS at any K the oracle adds in one chain (K <= 4096); a matrix whose tiles are
 cut along K differs by the grouping of at most 56 f32 terms (<= 2e-6 of the largest output)."""
@@ -142,3 +142,49 @@ def test_graph_replay_is_bitwise_identical(ops):
         torch.cuda.synchronize()
         assert torch.equal(y, ref)
     ops.check_device_status()
+
+
+# ------------------------------------------------------------------ Q8_0, 17..32 activation rows
+# f32 activations on the CPU path; here two int8 pieces per value (relative error ~3e-5 of a 256-run's amax): the bar of
+# the small-M kernel above 8 rows, 1e-4 of the largest output.
+
+def _q8(w, n, k):
+    from boostr_b200.tensor import QuantTensor
+
+    return QuantTensor.from_bytes(w, F.Q8_0, (n, k), device="cuda")
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 11008, 4096), (17, 9600, 512), (24, 74 * 128 + 5, 1024), (31, 20000, 256)])
+def test_q8_0_above_16_rows(ops, oracle, m, n, k):
+    rng = synth.rng_for(96, seed_of(m, n, k))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes("Q8_0", rng, n, k)
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 555.0, device="cuda")
+    x = torch.from_numpy(act).cuda()
+    qt = _q8(w, n, k)
+    got = ops.quant_matmul(x, qt, out=flat[guard:guard + m * n].view(m, n)).cpu().numpy()
+    ops.check_device_status()
+    assert (flat[:guard] == 555.0).all() and (flat[guard + m * n:] == 555.0).all(), "guard regions were written"
+    want = oracle.quant_matmul("Q8_0", act, w, n, threads=_threads())
+    e_max, e_rms = rel_err(got, want)
+    assert np.isfinite(got).all()
+    assert e_max <= 1e-4, f"M={m} N={n} K={k}: {e_max:.3e} (rms {e_rms:.3e})\n" + describe_mismatch(got, want)
+    again = ops.quant_matmul(x, qt).cpu().numpy()
+    assert np.array_equal(again.view(np.uint32), got.view(np.uint32))
+
+
+def test_q8_0_swiglu_and_bf16(ops, oracle):
+    m, n, k = 20, 9728, 1024
+    rng = synth.rng_for(97, 3)
+    act = synth.activations(rng, m, k)
+    wg = synth.weight_bytes("Q8_0", rng, n, k)
+    wu = synth.weight_bytes("Q8_0", rng, n, k)
+    got = ops.quant_swiglu(torch.from_numpy(act).cuda(), _q8(wg, n, k), _q8(wu, n, k)).cpu().numpy()
+    ops.check_device_status()
+    want = oracle.quant_swiglu("Q8_0", act, wg, wu, n, threads=_threads())
+    assert rel_err(got, want)[0] <= 4e-4
+    xb = torch.from_numpy(act).cuda().to(torch.bfloat16)
+    want_b = oracle.quant_matmul("Q8_0", xb.float().cpu().numpy(), wg, n, threads=_threads())
+    got_b = ops.quant_matmul(xb, _q8(wg, n, k)).cpu().numpy()
+    assert rel_err(got_b, want_b)[0] <= 1e-4
