@@ -188,3 +188,33 @@ def test_q8_0_swiglu_and_bf16(ops, oracle):
     want_b = oracle.quant_matmul("Q8_0", xb.float().cpu().numpy(), wg, n, threads=_threads())
     got_b = ops.quant_matmul(xb, _q8(wg, n, k)).cpu().numpy()
     assert rel_err(got_b, want_b)[0] <= 1e-4
+
+
+@pytest.mark.parametrize("fmt,m,n,k", [("Q4_K", 16, 14336, 4096), ("Q4_K", 32, 4096, 4096), ("Q4_K", 24, 4096, 14336), ("Q8_0", 32, 11008, 4096),
+                                       ("Q4_K", 17, 1024, 4096)])
+def test_many_replays_keep_their_bits_and_never_time_out(ops, fmt, m, n, k):
+    # back-to-back launches (the next call's kernels start under programmatic dependent launch while this one drains):
+    # every replay must reproduce the first result and no bounded wait may give up
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    ws = [synth.device_weight(fmt, n, k, gen) for _ in range(4)]
+    x = torch.randn(m, k, device="cuda", generator=gen)
+    y = torch.empty(m, n, device="cuda")
+    ref = ops.quant_matmul(x, ws[-1]).clone()
+
+    def run():
+        for w in ws:
+            ops.quant_matmul(x, w, out=y)
+
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    for it in range(100):
+        g.replay()
+        if it % 20 == 19:
+            torch.cuda.synchronize()
+            assert torch.equal(y, ref)
+    torch.cuda.synchronize()
+    ops.check_device_status()
