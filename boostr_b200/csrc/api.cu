@@ -159,6 +159,8 @@ int check_matmul_args(const char* op, int format, const void* act, int act_dtype
     return B200Q_OK;
 }
 
+bool i8_in_passes(int format, size_t M, size_t K, size_t N);
+
 // Scratch bytes of one call with activations of `act_dtype` (the public query assumes F32).
 size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, size_t N) {
     if (!known_format(format) || M == 0 || K == 0 || N == 0 || K % fmt_block_size(format)) return 0;
@@ -177,12 +179,38 @@ size_t workspace_need(int op, int format, int act_dtype, size_t M, size_t K, siz
     // small-M kernel: the activation image, plus split-K partial sums when K is long
     if (smallm_i8_preferred(format, M, K, N, sm_count_current()))  // integer tensor-core kernel (+ gate and up for SwiGLU)
         return smallm_i8_workspace_bytes(format, M, K, N, sm_count_current()) + (swiglu ? 2 * ((M * N * sizeof(float) + 255) & ~(size_t)255) : 0);
+    if (!swiglu && i8_in_passes(format, M, K, N)) {  // passes of 32 rows; a last pass of one row uses the mma.sync kernel's scratch
+        const size_t a = smallm_i8_workspace_bytes(format, 32, K, N, sm_count_current()), b = gemv_workspace_bytes(format, 1, K, N, false, sm_count_current());
+        return a > b ? a : b;
+    }
     return gemv_workspace_bytes(format, M, K, N, swiglu, sm_count_current());
 }
 
 }  // namespace
 
 namespace {
+// 33..63 activation rows that do not take the bf16 tensor-core path go through the integer tensor-core kernels in passes of
+// up to 32 rows (the mma.sync kernel would take passes of 16).
+bool i8_in_passes(int format, size_t M, size_t K, size_t N) {
+    return M > 32 && M < 64 && !prefill_supported(format, M, K, N) && smallm_i8_preferred(format, 32, K, N, sm_count_current());
+}
+size_t dtype_bytes(int dt) { return dt == DT_F32 ? 4 : dt == DT_F64 ? 8 : 2; }
+cudaError_t launch_i8_passes(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K, size_t N,
+                             void* ws, size_t ws_bytes, cudaStream_t st, unsigned int* status, bool* small, char* msg, size_t msg_len) {
+    cudaError_t e = cudaSuccess;
+    for (size_t m0 = 0; m0 < M && e == cudaSuccess && !*small; m0 += 32) {
+        const size_t rows = M - m0 < 32 ? M - m0 : 32;
+        const void* a = static_cast<const uint8_t*>(act) + m0 * K * dtype_bytes(act_dtype);
+        void* o = static_cast<uint8_t*>(out) + m0 * N * dtype_bytes(out_dtype);
+        if (rows >= 2 && smallm_i8_supported(format, rows, K, N))
+            e = launch_smallm_i8(format, a, act_dtype, w, o, out_dtype, rows, K, N, ws, ws_bytes, sm_count_current(), st, status, small, msg, msg_len,
+                                 false);
+        else  // a last pass of one row (or of a row count the kernels do not take): the mma.sync kernel
+            e = launch_gemv(format, a, act_dtype, w, nullptr, o, out_dtype, rows, K, N, ws, ws_bytes, false, sm_count_current(), st, status, small);
+    }
+    return e;
+}
+
 // acts_prepared: the scratch already holds this activation matrix as the tensor-core path prepares it for this class
 // of formats (a previous weight of the same batch left it there)
 int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
@@ -209,6 +237,10 @@ int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w,
         char msg[256] = "";
         e = launch_smallm_i8(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, sm_count_current(), st, status, &small, msg,
                              sizeof(msg), false);
+        if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
+    } else if (i8_in_passes(format, M, K, N)) {
+        char msg[256] = "";
+        e = launch_i8_passes(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, st, status, &small, msg, sizeof(msg));
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
     } else {
         e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),

@@ -218,3 +218,26 @@ def test_many_replays_keep_their_bits_and_never_time_out(ops, fmt, m, n, k):
             assert torch.equal(y, ref)
     torch.cuda.synchronize()
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("fmt,m,n,k,tol", [("Q4_K", 40, 14336, 4096, 0.0), ("Q4_K", 63, 700, 1024, 2e-6), ("Q4_K", 33, 19000, 512, 0.0), ("Q8_0", 48, 11008, 1024, 1e-4),
+                                           ("Q8_0", 33, 9600, 512, 1e-4)])
+def test_33_to_63_rows_in_passes_of_32(ops, oracle, fmt, m, n, k, tol):
+    # the bf16 tensor-core path starts at 64 rows; below it these rows go through the integer kernels in passes of up to 32
+    # (a last pass of one row through the mma.sync kernel)
+    from boostr_b200.tensor import QuantTensor
+
+    rng = synth.rng_for(98, seed_of(fmt, m, n, k))
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)
+    guard = 4096
+    flat = torch.full((2 * guard + m * n,), 333.0, device="cuda")
+    qt = QuantTensor.from_bytes(w, F.parse(fmt), (n, k), device="cuda")
+    got = ops.quant_matmul(torch.from_numpy(act).cuda(), qt, out=flat[guard:guard + m * n].view(m, n)).cpu().numpy()
+    ops.check_device_status()
+    assert (flat[:guard] == 333.0).all() and (flat[guard + m * n:] == 333.0).all(), "guard regions were written"
+    want = oracle.quant_matmul(fmt, act, w, n, threads=_threads())
+    if tol == 0.0:
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), describe_mismatch(got, want)
+    else:
+        assert rel_err(got, want)[0] <= tol, describe_mismatch(got, want)
