@@ -597,19 +597,19 @@ __global__ void __launch_bounds__(256) i8_act_prep_kernel(const InT* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Q8_0 (f32 activations on boostr's CPU path: dequantised row . f32 dot, src/quant/cpu/kernels/quant_matmul.rs:193-209).
-// The weight codes are int8 already; every activation is P int8 PIECES, x = amax/127 (a1 + a2/254 [+ a3/254^2]) with amax
-// over its 256-run (P = 3 up to 8 rows: ~1e-7 of the run's amax; P = 2 above: ~3e-5), stacked as P x MP rows of the B
-// operand.  One MMA per 32-block (128 weight rows x P MP x 32) leaves the block's integer sums of every piece in its
-// own columns; the drain converts them, weighs the pieces, multiplies by the block's d and adds in f32.  Same pipeline
-// as above with two differences: an accumulator holds the four blocks of half a 256-run (one 128-byte operand tile), so
-// a stage feeds two accumulators; and nothing here has to have the CPU's bits, so the drain teams keep their own sums
-// (MP = 16: team = half-run; MP = 32: all drain warps on every accumulator, a quarter of the rows each) and only whole
-// tiles are dealt (no hand-over).
+// Q8_0, 17..32 activation rows (f32 activations on boostr's CPU path: dequantised row . f32 dot,
+// src/quant/cpu/kernels/quant_matmul.rs:193-209).  The weight codes are int8 already; every activation is two int8
+// PIECES, x = amax/127 (a1 + a2/254) with amax over its 256-run (~3e-5 of the run's amax), stacked as 2 x 32 rows of the
+// B operand.  One MMA per 32-block (128 weight rows x 64 x 32) leaves the block's integer sums of both pieces in its own
+// columns; the drain converts them, weighs the pieces, multiplies by the block's d and adds in f32.  Same pipeline as
+// above with these differences: an accumulator holds the four blocks of half a 256-run (one 128-byte operand tile, 256
+// columns), so a stage feeds both accumulators and each is reused every block; all sixteen drain warps work on every
+// accumulator (four groups of four warps, 8 activation rows each) and keep their sums in registers for the whole tile;
+// only whole tiles are dealt (no hand-over).
 struct Q8Params {
     const uint8_t* w;
     void* out;
-    const float* scale;   // [nblk256][MP] amax / 127 of (256-run, activation row)
+    const float* scale;   // [nblk256][32] amax / 127 of (256-run, activation row)
     uint32_t M, N, K;
     uint32_t nblk;        // K / 256
     uint32_t ntiles;      // ceil(N / 128)
@@ -624,8 +624,6 @@ constexpr uint32_t Q8_REC = 128 * Q8_REC_WORDS * 4;
 constexpr uint32_t Q8_SLOT = Q8_REC + 32 * 4;                              // + the activation rows' scales of the run
 constexpr float Q8_STEP = 254.0f;
 
-// tile t of the CTA's share: whole tiles, round-robin
-template <int MP, int P>
 __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                        const __grid_constant__ CUtensorMap tmap_w, const Q8Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -634,17 +632,16 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full = sbase + OFF_FULL, bar_empty = sbase + OFF_EMPTY, bar_raw_full = sbase + OFF_RAW_FULL,
                    bar_raw_empty = sbase + OFF_RAW_EMPTY, bar_acc_full = sbase + OFF_ACC_FULL, bar_acc_empty = sbase + OFF_ACC_EMPTY,
-                   bar_sc_full = sbase + OFF_SC_FULL, bar_x = sbase + OFF_XFER;
+                   bar_sc_full = sbase + OFF_SC_FULL;
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM);
     volatile uint32_t* dead = reinterpret_cast<volatile uint32_t*>(smem + OFF_DEAD);
+    constexpr uint32_t MP = 32, P = 2;                   // activation rows of the MMA, pieces per activation
     constexpr uint32_t NB = P * MP;                      // MMA N: the pieces' rows
     constexpr uint32_t ACC_COLS = 4 * NB;                // four 32-blocks
-    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS <= 256 ? 256 : 512;
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;         // 512
     constexpr uint32_t B_ATOM = NB * 128, STAGE = 2 * A_ATOM + 2 * B_ATOM;
     constexpr int MH = 8;                                // activation rows of a drain thread
-    constexpr bool TEAMS = MP == 16;                     // two teams of eight warps, one per half-run; else four groups of four warps
-    const uint32_t sc_off = OFF_SC, x_off = sc_off + p.nsc * Q8_SLOT, raw_off = (x_off + 128 * 16 * 4 + 1023u) & ~1023u,
-                   st_off = raw_off + p.nr * Q8_RAW_TILE;
+    const uint32_t sc_off = OFF_SC, raw_off = (sc_off + p.nsc * Q8_SLOT + 1023u) & ~1023u, st_off = raw_off + p.nr * Q8_RAW_TILE;
     // drain warps whose activation rows exist, per accumulator
     const uint32_t groups = min((uint32_t)MP / MH, (p.M + MH - 1) / MH), acc_warps = 4 * groups;
 
@@ -661,8 +658,6 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
             mbar_init(bar_acc_full + 8 * s, 1);
             mbar_init(bar_acc_empty + 8 * s, acc_warps);
         }
-        mbar_init(bar_x, acc_warps);      // MP = 16: the second team's sums of a tile are in the exchange buffer
-        mbar_init(bar_x + 8, acc_warps);  // ... and the first team has taken them
         for (uint32_t s = 0; s < p.nsc; ++s) mbar_init(bar_sc_full + 8 * s, 5);
         *dead = 0;
         mbar_fence_init();
@@ -791,12 +786,10 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
             }
         }
     } else {
-        // ------------------------------------------------------------ drain
-        const uint32_t dw = (uint32_t)warp - DEC_WARPS, quarter = dw & 3, r = quarter * 32 + lane;
-        const uint32_t team = TEAMS ? dw >> 3 : 0u, m_lo = (TEAMS ? (dw >> 2) & 1 : dw >> 2) * MH;
+        // ------------------------------------------------------------ drain: four groups of four warps, 8 activation rows each
+        const uint32_t dw = (uint32_t)warp - DEC_WARPS, quarter = dw & 3, r = quarter * 32 + lane, m_lo = (dw >> 2) * MH;
         const bool rows_exist = m_lo < p.M;
         const uint32_t lane_addr = (quarter * 32) << 16;
-        float* xch = reinterpret_cast<float*>(smem + x_off) + m_lo * 128 + r;
         grid_dep_wait();
         bool ok = true;
         float acc[MH];
@@ -814,8 +807,7 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
             const uint32_t* rec = reinterpret_cast<const uint32_t*>(slot) + r * Q8_REC_WORDS;
             const float* scl = reinterpret_cast<const float*>(slot + Q8_REC) + m_lo;
 #pragma unroll
-            for (uint32_t hh = 0; hh < (TEAMS ? 1u : 2u); ++hh) {
-                const uint32_t h = TEAMS ? team : hh;
+            for (uint32_t h = 0; h < 2; ++h) {  // the two half-runs of the block
                 const uint32_t d01 = rec[2 * h], d23 = rec[2 * h + 1];
                 const float db[4] = {f16bits_to_f32(d01 & 0xFFFF), f16bits_to_f32(d01 >> 16), f16bits_to_f32(d23 & 0xFFFF), f16bits_to_f32(d23 >> 16)};
                 if (!i8_wait(bar_acc_full + 8 * h, i & 1, dead)) {
@@ -832,14 +824,12 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
                 for (int b = 0; b < 4; ++b) {
                     uint32_t v[P][MH];
 #pragma unroll
-                    for (int pc = 0; pc < P; ++pc) tmem_ld8_async(t0 + NB * b + MP * pc, v[pc]);
+                    for (int pc = 0; pc < (int)P; ++pc) tmem_ld8_async(t0 + NB * b + MP * pc, v[pc]);
                     tmem_ld_wait();
 #pragma unroll
                     for (int m = 0; m < MH; ++m) {
-                        float h2 = (float)(int)v[1][m];
-                        if constexpr (P > 2) h2 = fmaf((float)(int)v[2][m], C1, h2);
                         sacc[m] = fmaf(db[b], (float)(int)v[0][m], sacc[m]);
-                        sacc2[m] = fmaf(db[b], h2, sacc2[m]);
+                        sacc2[m] = fmaf(db[b], (float)(int)v[1][m], sacc2[m]);
                     }
                 }
                 tc_before();
@@ -851,40 +841,16 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
             if (!ok || blk + 1 != p.nblk) continue;
             // ---- the tile is complete
             const uint32_t n = (blockIdx.x + tl * gridDim.x) * 128 + r;
-            if (TEAMS && team == 1) {
-                // hand the second half-runs' sums to the first team (the buffer is free once it has taken the last tile's)
-                if (tl > 0 && !i8_wait(bar_x + 8, (tl - 1) & 1, dead)) {
-                    i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
-                    ok = false;
-                    break;
-                }
+            if (n < p.N)
 #pragma unroll
-                for (int m = 0; m < MH; ++m) xch[m * 128] = acc[m];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_x);
-            } else {
-                if (TEAMS) {
-                    if (!i8_wait(bar_x, tl & 1, dead)) {
-                        i8_fail(dead, p.status, STATUS_TIMEOUT_EMPTY);
-                        ok = false;
-                        break;
+                for (int m = 0; m < MH; ++m) {
+                    if (m_lo + m < p.M) {
+                        const size_t idx = (size_t)(m_lo + m) * p.N + n;
+                        if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = acc[m];
+                        else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc[m]);
+                        else static_cast<__half*>(p.out)[idx] = __float2half_rn(acc[m]);
                     }
-#pragma unroll
-                    for (int m = 0; m < MH; ++m) acc[m] += xch[m * 128];
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_x + 8);
                 }
-                if (n < p.N)
-#pragma unroll
-                    for (int m = 0; m < MH; ++m) {
-                        if (m_lo + m < p.M) {
-                            const size_t idx = (size_t)(m_lo + m) * p.N + n;
-                            if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = acc[m];
-                            else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc[m]);
-                            else static_cast<__half*>(p.out)[idx] = __float2half_rn(acc[m]);
-                        }
-                    }
-            }
 #pragma unroll
             for (int m = 0; m < MH; ++m) acc[m] = 0.f;
         }
@@ -993,12 +959,11 @@ Q8Layout q8_layout(size_t M, size_t K, size_t N, int sm_count) {
     return l;
 }
 
-template <int MP, int P>
 cudaError_t launch_q8_kernel(const CUtensorMap& amap, const CUtensorMap& wmap, const Q8Params& p, uint32_t grid, size_t smem, cudaStream_t st) {
     static PerDeviceOnce attrs;
-    cudaError_t e = attrs.run([] { return cudaFuncSetAttribute(smallm_i8_q8_0_kernel<MP, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
+    cudaError_t e = attrs.run([] { return cudaFuncSetAttribute(smallm_i8_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448); });
     if (e != cudaSuccess) return e;
-    return launch_pdl(smallm_i8_q8_0_kernel<MP, P>, dim3(grid), dim3(I8_THREADS), smem, st, amap, wmap, p);
+    return launch_pdl(smallm_i8_q8_0_kernel, dim3(grid), dim3(I8_THREADS), smem, st, amap, wmap, p);
 }
 
 cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M, size_t K, size_t N, void* ws,
@@ -1038,7 +1003,7 @@ cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, vo
     const uint32_t stage = 2 * A_ATOM + 2 * NB * 128;
     p.ns = 2;
     p.nsc = p.ns + 2 + 2;
-    const uint32_t fixed = 1024 + ((p.nsc * Q8_SLOT + 128 * 16 * 4 + 1023u) & ~1023u) + p.ns * stage;
+    const uint32_t fixed = 1024 + ((p.nsc * Q8_SLOT + 1023u) & ~1023u) + p.ns * stage;
     p.nr = (232448u - 1024u - 1024u - fixed) / Q8_RAW_TILE;
     if (p.nr > 4) p.nr = 4;
     const size_t smem = 1024 + fixed + (size_t)p.nr * Q8_RAW_TILE;
@@ -1069,7 +1034,7 @@ cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, vo
             return cudaErrorInvalidValue;
         }
     }
-    cudaError_t e = launch_q8_kernel<32, 2>(amap, wmap, p, l.grid, smem, st);
+    cudaError_t e = launch_q8_kernel(amap, wmap, p, l.grid, smem, st);
     note_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -1077,8 +1042,7 @@ cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, vo
 }  // namespace
 
 // Shapes the integer tensor-core kernels take.  Q4_K: 2 <= M <= 32, whole 256-blocks (rows are multiples of 16 bytes:
-// 144-byte blocks), pair counts within 32 bits.  Q8_0: 17 <= M <= 32 (up to 16 rows the mma.sync kernel is as fast: the
-// kernel is written for 16 rows and for three pieces as well, but only the instance that is used is built), K a multiple
+// 144-byte blocks), pair counts within 32 bits.  Q8_0: 17 <= M <= 32 (up to 16 rows the mma.sync kernel is as fast), K a multiple
 // of 256 (rows of whole 272-byte runs), whole tiles only.
 bool smallm_i8_supported(int fmt, size_t M, size_t K, size_t N) {
     if (M < 2 || M > 32 || K % 256 != 0 || K < 256 || N < 1 || (N + 127) / 128 * (K / 256) >= (1u << 30)) return false;
