@@ -99,7 +99,8 @@ B200Q_API int b200q_dequantize(int format, const void* w, size_t nblocks, void* 
 /*
  * Scratch bytes b200q_quant_matmul / b200q_quant_swiglu need for this shape with F32 activations:
  * 0 for the decode shapes (one activation row); the prepared activation image for 2 <= M < 64 (a few
- * hundred KB) and for the tensor-core path (2 bytes per activation), plus split-K partial sums when K
+ * hundred KB; the integer tensor-core kernels for Q4_K / Q8_0 add up to ~5 MB of f32 pieces of tiles cut
+ * along K) and for the bf16 tensor-core path (2 bytes per activation), plus split-K partial sums when K
  * is long.  `ws` must be 16-byte aligned.  Scratch contents need no initialisation and carry nothing
  * between calls, but calls that may overlap on the GPU must not share one scratch buffer.
  * Returns 0 as well when the arguments are invalid; the op itself reports the error.
