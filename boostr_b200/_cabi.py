@@ -39,6 +39,9 @@ SIGNATURES = {
                                                  c_size_t, c_void_p]),
     "b200q_quant_swiglu": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                    c_size_t, c_void_p, c_size_t, c_void_p]),
+    "b200q_mlp_workspace_bytes": (c_size_t, [c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t]),
+    "b200q_quant_mlp": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_size_t,
+                                c_size_t, c_size_t, c_void_p, c_size_t, c_void_p]),
     "b200q_quant_matmul_static_scratch": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                                   c_size_t, c_void_p]),
     "b200q_shard_pack": (c_int, [c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_int, c_void_p, c_size_t]),

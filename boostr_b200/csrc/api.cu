@@ -457,6 +457,27 @@ int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w
     return B200Q_OK;
 }
 
+size_t b200q_mlp_workspace_bytes(int format_gate_up, int format_down, size_t M, size_t K, size_t n_ff, size_t n_out) {
+    const size_t a = workspace_need(B200Q_OP_QUANT_SWIGLU, format_gate_up, DT_F32, M, K, n_ff);
+    const size_t b = workspace_need(B200Q_OP_QUANT_MATMUL, format_down, DT_F32, M, n_ff, n_out);
+    return ((M * n_ff * sizeof(float) + 255) & ~(size_t)255) + (a > b ? a : b);
+}
+
+int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void* w_up, int format_down, const void* w_down, const void* act,
+                    int act_dtype, void* out, int out_dtype, size_t M, size_t K, size_t n_ff, size_t n_out, void* ws, size_t ws_bytes,
+                    void* stream) {
+    const size_t hid = (M * n_ff * sizeof(float) + 255) & ~(size_t)255;
+    if (!ws || ws_bytes < hid || (reinterpret_cast<uintptr_t>(ws) & 15))
+        return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_mlp: workspace of %zu bytes is too small, need %zu", ws_bytes,
+                    b200q_mlp_workspace_bytes(format_gate_up, format_down, M, K, n_ff, n_out));
+    float* h = static_cast<float*>(ws);
+    uint8_t* rest = static_cast<uint8_t*>(ws) + hid;
+    const size_t rest_bytes = ws_bytes - hid;
+    int rc = b200q_quant_swiglu(format_gate_up, act, act_dtype, w_gate, w_up, h, DT_F32, M, K, n_ff, rest, rest_bytes, stream);
+    if (rc) return rc;
+    return quant_matmul_impl(format_down, h, DT_F32, w_down, out, out_dtype, M, n_ff, n_out, rest, rest_bytes, stream, false);
+}
+
 int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, int rank, int world, void* dst,
                      size_t dst_bytes) {
     if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "shard_pack: unsupported format id %d", format);

@@ -233,6 +233,29 @@ def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: 
     return out
 
 
+def quant_mlp(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: QuantTensor, down_weight: QuantTensor,
+              out_dtype: torch.dtype = torch.float32, out: torch.Tensor = None) -> torch.Tensor:
+    """down(silu(activation x gate^T) * (activation x up^T)): the feed-forward block of a quantized layer
+    (src/model/llama/model/blocks_mlp.rs:38-46) as one call; the hidden state stays in scratch."""
+    if gate_weight.format != up_weight.format or tuple(gate_weight.shape) != tuple(up_weight.shape):
+        raise QuantError("quant_mlp: gate and up weights must have the same format and shape")
+    act, m, k, n_ff = _check_act("quant_mlp", activation, gate_weight, True)
+    if len(down_weight.shape) != 2 or down_weight.shape[1] != n_ff:
+        raise QuantError(f"quant_mlp: down weight {tuple(down_weight.shape)} does not take a hidden state of {n_ff}")
+    n_out = down_weight.shape[0]
+    out = _out_buffer(out, (*activation.shape[:-1], n_out), out_dtype, act.device)
+    if m == 0:
+        return out
+    L = _cabi.lib()
+    with torch.cuda.device(act.device):
+        need = L.b200q_mlp_workspace_bytes(gate_weight.format.format_id, down_weight.format.format_id, m, k, n_ff, n_out)
+        ws = workspace(need, act.device)
+        _cabi.check(L.b200q_quant_mlp(gate_weight.format.format_id, gate_weight.storage.data_ptr(), up_weight.storage.data_ptr(),
+                                      down_weight.format.format_id, down_weight.storage.data_ptr(), act.data_ptr(), _DT[act.dtype],
+                                      out.data_ptr(), _DT[out_dtype], m, k, n_ff, n_out, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
 def launch_count() -> int:
     """Kernel launches issued by the library so far in this process."""
     return int(_cabi.lib().b200q_launch_count())

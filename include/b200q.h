@@ -159,6 +159,22 @@ B200Q_API int b200q_quant_swiglu(int format, const void* act, int act_dtype, con
                                  void* stream);
 
 /*
+ * The feed-forward block of a quantized layer, down(silu(gate x) * (up x))
+ * (src/model/llama/model/blocks_mlp.rs:38-46: `quant_swiglu` followed by the down projection's
+ * `forward`), as ONE call: activation [M, K] -> hidden [M, n_ff] (f32, kept in `ws`) -> out [M, n_out].
+ * The gate and up weights are [n_ff, K] of `format_gate_up`, the down weight [n_out, n_ff] of
+ * `format_down` (a Q4_K_M file mixes them: Q4_K gate/up, Q6_K or Q4_K down).  The two products run
+ * back to back under programmatic dependent launch (the second streams its weights while the first
+ * drains); the hidden state never goes back to the caller.  Results are those of b200q_quant_swiglu
+ * followed by b200q_quant_matmul, bit for bit.  b200q_mlp_workspace_bytes gives the scratch for F32
+ * activations: the hidden state plus what the two products need.
+ */
+B200Q_API size_t b200q_mlp_workspace_bytes(int format_gate_up, int format_down, size_t M, size_t K, size_t n_ff, size_t n_out);
+B200Q_API int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void* w_up, int format_down, const void* w_down,
+                              const void* act, int act_dtype, void* out, int out_dtype, size_t M, size_t K, size_t n_ff,
+                              size_t n_out, void* ws, size_t ws_bytes, void* stream);
+
+/*
  * quant_matmul for callers that cannot hand over scratch memory.  (No counterpart in boostr:
  * its CUDA backend always has numr's allocator at hand.)
  *

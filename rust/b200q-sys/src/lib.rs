@@ -61,6 +61,12 @@ extern "C" {
     pub fn b200q_quant_swiglu(format: c_int, act: *const c_void, act_dtype: c_int, w_gate: *const c_void,
                               w_up: *const c_void, out: *mut c_void, out_dtype: c_int, m: usize, k: usize, n: usize,
                               ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn b200q_mlp_workspace_bytes(format_gate_up: c_int, format_down: c_int, m: usize, k: usize, n_ff: usize,
+                                     n_out: usize) -> usize;
+    pub fn b200q_quant_mlp(format_gate_up: c_int, w_gate: *const c_void, w_up: *const c_void, format_down: c_int,
+                           w_down: *const c_void, act: *const c_void, act_dtype: c_int, out: *mut c_void, out_dtype: c_int,
+                           m: usize, k: usize, n_ff: usize, n_out: usize, ws: *mut c_void, ws_bytes: usize,
+                           stream: *mut c_void) -> c_int;
     pub fn b200q_quant_matmul_static_scratch(format: c_int, act: *const c_void, act_dtype: c_int, w: *const c_void,
                                              out: *mut c_void, out_dtype: c_int, m: usize, k: usize, n: usize,
                                              stream: *mut c_void) -> c_int;

@@ -104,6 +104,38 @@ pub fn quant_swiglu(client: &CudaClient, activation: &Tensor<CudaRuntime>, gate:
     Ok(out)
 }
 
+/// The feed-forward block `down(silu(gate x) * (up x))` of `src/model/llama/model/blocks_mlp.rs:38-46` as one call
+/// (the hidden state stays in the library's scratch).  Falls back to the two separate ops for formats libb200q does not serve.
+pub fn quant_mlp(client: &CudaClient, activation: &Tensor<CudaRuntime>, gate: &QuantTensor<CudaRuntime>, up: &QuantTensor<CudaRuntime>,
+                 down: &QuantTensor<CudaRuntime>) -> Result<Tensor<CudaRuntime>> {
+    if gate.format() != up.format() || gate.shape() != up.shape() {
+        return Err(Error::QuantError { reason: "quant_mlp: gate and up weights must have the same format and shape".into() });
+    }
+    let (m, k, n_ff, _) = validate("quant_mlp", activation, gate)?;
+    let dshape = down.shape();
+    if dshape.len() != 2 || dshape[1] != n_ff {
+        return Err(Error::QuantError { reason: format!("quant_mlp: down weight {:?} does not take a hidden state of {}", dshape, n_ff) });
+    }
+    let (Some(fgu), Some(fd)) = (format_id(gate.format()), format_id(down.format())) else {
+        let h = quant_swiglu(client, activation, gate, up)?;
+        return quant_matmul(client, &h, down);
+    };
+    let n_out = dshape[0];
+    let act = activation.contiguous()?;
+    let mut out_shape = activation.shape().to_vec();
+    *out_shape.last_mut().unwrap() = n_out;
+    let out = Tensor::<CudaRuntime>::empty(&out_shape, DType::F32, activation.device());
+    let ws_bytes = unsafe { b200q_sys::b200q_mlp_workspace_bytes(fgu, fd, m, k, n_ff, n_out) };
+    let ws = scratch(ws_bytes, activation);
+    check(unsafe {
+        b200q_sys::b200q_quant_mlp(fgu, gate.storage().ptr() as *const c_void, up.storage().ptr() as *const c_void, fd,
+                                   down.storage().ptr() as *const c_void, act.ptr() as *const c_void, b200q_sys::B200Q_F32,
+                                   out.ptr() as *mut c_void, b200q_sys::B200Q_F32, m, k, n_ff, n_out, ptr_or_null(&ws), ws_bytes,
+                                   stream_of(client))
+    })?;
+    Ok(out)
+}
+
 /// For a host that must not allocate at the call site (see `b200q_quant_matmul_static_scratch` in the header):
 /// same result as `quant_matmul`, scratch inside the library, calls on one device must not overlap.
 pub fn quant_matmul_no_alloc(client: &CudaClient, activation: &Tensor<CudaRuntime>, weight: &QuantTensor<CudaRuntime>,
