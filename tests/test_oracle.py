@@ -561,3 +561,82 @@ def test_q3k_q8k_dot_forms(oracle):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     scalar = oracle.quant_matmul("Q3_K", act, w, n, threads=2, simd=False)  # eight float lanes: close, not equal in general
     assert np.abs(scalar - got).max() <= 1e-5 * np.abs(got).max()
+
+
+# ---- independent numpy restatements of the two Q8_K integer dot products, bit for bit against the C oracle ----
+def _f16(b2):
+    return np.frombuffer(bytes(b2), dtype=np.float16)[0].astype(np.float32)
+
+
+def _q8k_numpy(x):
+    """quantize_act_q8k.rs:26-98 for one row: per 256-block d8 (f32), 256 int8 codes, 16 sums of 16."""
+    out = []
+    for b in range(len(x) // 256):
+        xb = x[256 * b:256 * b + 256]
+        amax = np.float32(np.abs(xb).max())
+        if amax == 0:
+            out.append((np.float32(0), np.zeros(256, np.int32)))
+            continue
+        idv = np.float32(127.0) / amax
+        codes = np.clip(np.rint(xb * idv), -128, 127).astype(np.int32)
+        out.append((amax / np.float32(127.0), codes))
+    return out
+
+
+def _dot_q4k_numpy(row, q8):
+    """fused_q4k_q8k_dot.rs:111-172: sumf += (d*d8)*sumi - (dmin*d8)*sumi_mins, block after block, no FMA."""
+    acc = np.float32(0)
+    for b, (d8, a) in enumerate(q8):
+        blk = row[144 * b:144 * b + 144]
+        d, dmin = _f16(blk[0:2]), _f16(blk[2:4])
+        s = blk[4:16].astype(np.int32)
+        sc = [s[j] & 63 if j < 4 else (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4) for j in range(8)]
+        mn = [s[j + 4] & 63 if j < 4 else (s[j + 4] >> 4) | ((s[j] >> 6) << 4) for j in range(8)]
+        qs = blk[16:144].astype(np.int32)
+        sumi = 0
+        summ = 0
+        for jj in range(4):
+            lo, hi = qs[32 * jj:32 * jj + 32] & 0xF, qs[32 * jj:32 * jj + 32] >> 4
+            sumi += int(sc[2 * jj]) * int((lo * a[64 * jj:64 * jj + 32]).sum()) + int(sc[2 * jj + 1]) * int((hi * a[64 * jj + 32:64 * jj + 64]).sum())
+            summ += int(mn[2 * jj]) * int(a[64 * jj:64 * jj + 32].sum()) + int(mn[2 * jj + 1]) * int(a[64 * jj + 32:64 * jj + 64].sum())
+        term = (d * d8) * np.float32(sumi) - (dmin * d8) * np.float32(summ)
+        acc = np.float32(acc + term)
+    return acc
+
+
+def _dot_q6k_numpy(row, q8):
+    """fused_q6k_q8k_dot.rs:170-224: sumf += (d*d8)*sum_sb sc_sb * sum (q-32) a."""
+    acc = np.float32(0)
+    for b, (d8, a) in enumerate(q8):
+        blk = row[210 * b:210 * b + 210]
+        ql, qh = blk[0:128].astype(np.int32), blk[128:192].astype(np.int32)
+        sc = blk[192:208].view(np.int8).astype(np.int32)
+        d = _f16(blk[208:210])
+        sumi = 0
+        for n in range(2):
+            for g in range(4):
+                src = ql[64 * n + 32 * (g & 1):64 * n + 32 * (g & 1) + 32]
+                nib = (src & 0xF) if g < 2 else (src >> 4)
+                q = (nib | (((qh[32 * n:32 * n + 32] >> (2 * g)) & 3) << 4)) - 32
+                e0 = 128 * n + 32 * g
+                for half in range(2):
+                    sumi += int(sc[8 * n + 2 * g + half]) * int((q[16 * half:16 * half + 16] * a[e0 + 16 * half:e0 + 16 * half + 16]).sum())
+        acc = np.float32(acc + (d * d8) * np.float32(sumi))
+    return acc
+
+
+@pytest.mark.parametrize("fmt,dot", [("Q4_K", _dot_q4k_numpy), ("Q6_K", _dot_q6k_numpy)])
+@pytest.mark.parametrize("simd", [True, False])
+def test_kquant_dots_match_an_independent_numpy_restatement_bit_for_bit(oracle, fmt, dot, simd):
+    m, n, k = 2, 6, 1024
+    rng = synth.rng_for(41, 7 if fmt == "Q4_K" else 8)
+    act = synth.activations(rng, m, k)
+    w = synth.weight_bytes(fmt, rng, n, k)  # the BASELINE distributions of the two formats
+    got = oracle.quant_matmul(fmt, act, w, n, threads=1, simd=simd)
+    rb = k // 256 * (144 if fmt == "Q4_K" else 210)
+    want = np.empty((m, n), np.float32)
+    for i in range(m):
+        q8 = _q8k_numpy(act[i])
+        for j in range(n):
+            want[i, j] = dot(w[rb * j:rb * j + rb], q8)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (got, want)
