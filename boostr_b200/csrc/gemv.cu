@@ -1075,7 +1075,6 @@ cudaError_t launch_gemv_fmt(const GemvParams& p, const GemvMaps& maps, int mt, i
         if (mt == 1 && sl == 4) return m1 ? launch_one<FMT, 1, 4, true, SWIGLU>(p, maps, grid, threads, smem, st)
                                           : launch_one<FMT, 1, 4, false, SWIGLU>(p, maps, grid, threads, smem, st);
         if (mt == 2 && sl == 1) return launch_one<FMT, 2, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
-        if (mt == 2 && sl == 2) return launch_one<FMT, 2, 2, false, SWIGLU>(p, maps, grid, threads, smem, st);
     } else {
         if (mt == 1 && sl == 1) return m1 ? launch_one<FMT, 1, 1, true, SWIGLU>(p, maps, grid, threads, smem, st)
                                           : launch_one<FMT, 1, 1, false, SWIGLU>(p, maps, grid, threads, smem, st);
@@ -1101,12 +1100,14 @@ cudaError_t launch_prep_fmt(const PrepParams& pp, int mt, cudaStream_t st) {
 
 }  // namespace
 
-// Largest number of K-chunks a CTA may keep activation fragments for, per format and tile count
-// (the fragments of SL chunks x MT tiles live in registers).
-int gemv_max_sl(int fmt, int mt) {
+// K-chunks a CTA walks per slab (their activation fragments live in registers); the others are spread over
+// gridDim.y.  Measured on 4096 x 14336 and the like: one chunk per CTA and a wider K split beats two or four chunks
+// per CTA at every row count (Q6_K M = 16: 24.5 us against 33.7, where two chunks also spill; Q5_K M = 16: 23.3 / 29.3;
+// Q4_K M = 3: 15.5 / 17.1); only single-tile launches over many rows (14336 x 8192, M = 1) are 5 % faster with more
+// chunks per CTA, so those keep them.
+int gemv_max_sl(int fmt, int mt, size_t N) {
     const bool kq = (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K);
-    if (kq) return mt == 1 ? 4 : 2;
-    return 1;
+    return (kq && mt == 1 && N >= 8192) ? 4 : 1;
 }
 
 // 8-row tiles per pass: one for M <= 8, else two (16 activation rows per pass).  Four tiles per pass were
@@ -1135,7 +1136,7 @@ bool gemv_plan(int fmt, uint32_t K, uint32_t N, int mt, bool swiglu, int sm_coun
     pl.nslices = (K + 255) / 256;
     pl.spc = pl.nslices < 16 ? pl.nslices : 16;
     pl.nchunks = (pl.nslices + pl.spc - 1) / pl.spc;
-    const uint32_t maxsl = gemv_max_sl(fmt, mt);
+    const uint32_t maxsl = gemv_max_sl(fmt, mt, N);
     uint32_t sl = pl.nchunks < maxsl ? pl.nchunks : maxsl;
     if (sl == 3) sl = 4;  // instantiated values: 1, 2, 4
     pl.sl = sl;
