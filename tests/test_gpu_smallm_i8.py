@@ -36,7 +36,7 @@ def _threads():
 
 
 # whole tiles per SM: 111 tiles and more on a 148-SM part, 8..16 rows; and every row count above 16
-WHOLE = [(8, 14336, 4096), (16, 14336, 4096), (13, 14250, 2048), (32, 19000, 1024), (17, 128 * 148, 256)]
+WHOLE = [(8, 14336, 4096), (16, 14336, 4096), (13, 14250, 2048), (32, 19000, 1024), (17, 128 * 148, 256), (16, 128256, 4096)]
 # tiles cut along K (few tiles, or long K), ragged N, a single row of weights
 CUT = [(17, 50, 1024), (24, 4096, 14336), (32, 1024, 4096), (20, 4096, 4096), (31, 1, 256), (18, 129, 512), (32, 300, 16384)]
 
