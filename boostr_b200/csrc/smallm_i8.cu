@@ -1004,7 +1004,7 @@ cudaError_t launch_smallm_q8_0(const void* act, int act_dtype, const void* w, vo
     p.ns = 2;
     p.nsc = p.ns + 2 + 2;
     const uint32_t fixed = 1024 + ((p.nsc * Q8_SLOT + 1023u) & ~1023u) + p.ns * stage;
-    p.nr = (232448u - 1024u - 1024u - fixed) / Q8_RAW_TILE;
+    p.nr = ((232448u - 1024u - 1024u - fixed) / Q8_RAW_TILE) & ~1u;  // even: see launch_smallm_i8
     if (p.nr > 4) p.nr = 4;
     const size_t smem = 1024 + fixed + (size_t)p.nr * Q8_RAW_TILE;
 
@@ -1109,7 +1109,11 @@ cudaError_t launch_smallm_i8(int fmt, const void* act, int act_dtype, const void
     p.ns = 3;
     p.nsc = p.ns + 2 + 2;
     const uint32_t fixed = 1024 + ((p.nsc * SC_SLOT + 128 * p.MP * 4 + 1023u) & ~1023u) + p.ns * stage;
-    p.nr = (232448u - 1024u - 1024u - fixed) / RAW_TILE;
+    // The ring of packed tiles must have an EVEN depth: block i lives in slot i % nr and is read by decode set i & 1, so with
+    // an even depth a slot always belongs to one set and that set sees every phase of the slot's barrier.  With an odd depth
+    // the sets would alternate on a slot, a set would wait for phase k having last seen phase k - 2, and a parity wait cannot
+    // tell those apart when the fill in between is late (fills may complete out of order).
+    p.nr = ((232448u - 1024u - 1024u - fixed) / RAW_TILE) & ~1u;
     if (p.nr > 6) p.nr = 6;
     const size_t smem = 1024 + fixed + (size_t)p.nr * RAW_TILE;
 
