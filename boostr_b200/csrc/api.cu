@@ -16,7 +16,7 @@ cudaError_t launch_dequant(int fmt, const void* w, size_t nblocks, void* out, in
                            unsigned int* status);
 cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
                         size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
-                        unsigned int* status, bool* ws_too_small);
+                        unsigned int* status, bool* ws_too_small, bool image_ready = false);
 size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count);
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu);
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
@@ -211,8 +211,19 @@ cudaError_t launch_i8_passes(int format, const void* act, int act_dtype, const v
     return e;
 }
 
-// acts_prepared: the scratch already holds this activation matrix as the tensor-core path prepares it for this class
-// of formats (a previous weight of the same batch left it there)
+// Which prepared form of the activations (in scratch) a product reads; -1: none that another weight of a batch could
+// share.  The bf16 tensor-core path prepares one form per class of formats (K-quants: Q8_K round trip; others: bf16);
+// the mma.sync small-M kernel one image per format (Q5_K reads Q4_K's).
+int prepared_class(int format, size_t M, size_t K, size_t N) {
+    if (kq_generic_supported(format, M, K, N)) return -1;
+    if (prefill_supported(format, M, K, N)) return (format == FMT_Q4_K || format == FMT_Q5_K || format == FMT_Q6_K) ? 101 : 100;
+    if (gemv_m1_supported(format, M, K, N, false) || gemv_m1_f32_supported(format, M, K, N)) return -1;
+    if (smallm_i8_preferred(format, M, K, N, sm_count_current()) || i8_in_passes(format, M, K, N)) return -1;
+    return 200 + (format == FMT_Q5_K ? FMT_Q4_K : format);
+}
+
+// acts_prepared: the scratch already holds this activation matrix in the form this product reads (prepared_class): a
+// previous weight of the same batch left it there
 int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                       size_t K, size_t N, void* ws, size_t ws_bytes, void* stream, bool acts_prepared) {
     int rc = check_matmul_args("quant_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
@@ -244,7 +255,7 @@ int quant_matmul_impl(int format, const void* act, int act_dtype, const void* w,
         if (e != cudaSuccess && msg[0]) return fail(B200Q_ERR_CUDA, "quant_matmul: %s", msg);
     } else {
         e = launch_gemv(format, act, act_dtype, w, nullptr, out, out_dtype, M, K, N, ws, ws_bytes, false, sm_count_current(),
-                        st, status, &small);
+                        st, status, &small, acts_prepared);
     }
     if (small)
         return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_matmul: workspace of %zu bytes is too small, need %zu", ws_bytes,
@@ -359,13 +370,12 @@ int matmul_batch_impl(const char* op, int n_weights, const int* formats, const v
                                    norm_w, eps);
             if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "CUDA %s kernel launch failed: %s", op, cudaGetErrorString(e));
         } else {
-            // at large M the weights of a batch share the prepared activations (one preparation per class of formats)
-            const bool tc = prefill_supported(formats[i], M, K, N[i]);
-            const int cls = (formats[i] == FMT_Q4_K || formats[i] == FMT_Q5_K || formats[i] == FMT_Q6_K) ? 1 : 0;
+            // the weights of a batch share the prepared activations where consecutive ones read the same form of them
+            const int cls = prepared_class(formats[i], M, K, N[i]);
             int rc = quant_matmul_impl(formats[i], act, act_dtype, w[i], out[i], out_dtype, M, K, N[i], ws, ws_bytes, stream,
-                                       tc && prepared_cls == cls);
+                                       cls >= 0 && prepared_cls == cls);
             if (rc) return rc;
-            prepared_cls = tc ? cls : -1;  // another kernel family may have used the scratch for something else
+            prepared_cls = cls;  // -1: another kernel family may have used the scratch for something else
         }
         i += total;
     }

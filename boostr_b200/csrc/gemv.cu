@@ -1210,10 +1210,11 @@ size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, 
     return need;
 }
 
-// out[M,N] = act[M,K] x W^T for any M: one activation-image launch, then passes of up to 8 * MT activation rows.
+// out[M,N] = act[M,K] x W^T for any M: one activation-image launch (none when the image is there already), then passes of up
+// to 8 * MT activation rows.
 cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0, const void* w1, void* out, int out_dtype,
                         size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, bool swiglu, int sm_count, cudaStream_t st,
-                        unsigned int* status, bool* ws_too_small) {
+                        unsigned int* status, bool* ws_too_small, bool image_ready) {
     *ws_too_small = false;
     const int mt = gemv_tiles_per_pass(fmt, M, K);  // one geometry for every pass, so split-K partials line up
     GemvPlan pl;
@@ -1232,7 +1233,9 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
     pp.nslices = pl.nslices;
     pp.tiles_total = (uint32_t)((M + 7) / 8);
     pp.act_dtype = act_dtype;
-    cudaError_t e;
+    // image_ready: the previous weight of a batch (same activations, same image format, same scratch) left the image there
+    cudaError_t e = cudaSuccess;
+    if (!image_ready)
     switch (fmt) {
     case FMT_Q4_0: e = launch_prep_fmt<FMT_Q4_0>(pp, mt, st); break;
     case FMT_Q5_0: e = launch_prep_fmt<FMT_Q5_0>(pp, mt, st); break;

@@ -271,6 +271,33 @@ def test_quant_matmul_batch_mixed_formats(ops, oracle):
         assert rel_err(o.cpu().numpy(), want)[0] < 2e-6
 
 
+@pytest.mark.parametrize("m", [3, 16, 40])
+def test_small_m_batch_shares_the_activation_image(ops, m):
+    # q, k (Q4_K), a Q5_K weight (reads the Q4_K image), v (Q6_K: its own image), then Q8_0 twice: consecutive weights of one
+    # image format take ONE preparation launch; every output must have the bits of the separate call
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(17)
+    k = 2048
+    specs = [("Q4_K", 384), ("Q4_K", 96), ("Q5_K", 160), ("Q6_K", 96), ("Q8_0", 200), ("Q8_0", 72)]
+    ws = [synth.device_weight(f, n, k, gen) for f, n in specs]
+    x = torch.randn(m, k, device="cuda", generator=gen)
+    single = []
+    n_single = 0
+    for w in ws:
+        before = ops.launch_count()
+        single.append(ops.quant_matmul(x, w).clone())
+        n_single += ops.launch_count() - before
+    before = ops.launch_count()
+    outs = ops.quant_matmul_batch(x, ws)
+    n_batch = ops.launch_count() - before
+    ops.check_device_status()
+    for a, b in zip(outs, single):
+        assert torch.equal(a, b)
+    # the images of weights 2, 3 and 6 were there already; at 40 rows the Q4_K weights take the integer tensor-core kernels
+    # (their own image per call), so only the second Q8_0 weight finds its image
+    assert n_batch == n_single - (3 if m <= 32 else 1), (n_batch, n_single)
+
+
 # ------------------------------------------------------------------ BASELINE shapes
 
 
