@@ -68,8 +68,10 @@ constexpr int BK = 64;          // K elements per stage = one 128-byte swizzle r
 // packed-weight tiles staged by TMA: 128 rows x the bytes of 256 elements (four K steps)
 __host__ __device__ constexpr int raw_pitch(int fmt) { return fmt == FMT_Q8_0 ? 272 : fmt == FMT_Q6_K ? 212 : (fmt == FMT_Q5_K || fmt == FMT_Q5_0) ? 176 : 144; }
 // tile bytes rounded up to 1 KB (the operand tiles behind them must stay 1 KB aligned).  Q6_K blocks (210 B) are not
-// multiples of 16 bytes, so TMA cannot fetch them: the dequant warps copy them themselves, coalesced, 2 bytes per lane,
-// into rows of 212 bytes (4-byte aligned blocks, conflict-free row-per-thread reads).
+// multiples of 16 bytes: where the ROWS are (K a multiple of 2048) TMA fetches the 240 bytes from the 16-byte boundary below
+// the block (prefill_kernel's Q6BOX; measured 1.4-2.0x the speed of the copy below: M = 2048, 14336 x 4096: 371 -> 229 us);
+// otherwise the dequant warps copy the blocks themselves with 4-byte asynchronous copies into rows of 212 bytes (4-byte
+// aligned blocks, conflict-free row-per-thread reads).
 __host__ __device__ constexpr int raw_tile_bytes(int fmt) { return (128 * raw_pitch(fmt) + 1023) & ~1023; }
 constexpr int PF_THREADS = 23 * 32;  // warps 0-15 dequant | 16 activation TMA | 17 MMA issue, TMEM | 18 packed-weight TMA | 19-22 epilogue
 
@@ -426,11 +428,15 @@ __device__ __forceinline__ bool pf_unit(const PrefillParams& p, uint32_t it, PfU
 // Persistent: one CTA per SM walks its work units (consecutive CTAs share an activation tile, which therefore stays
 // in L2).  Tensor memory holds TWO accumulators while they fit, so the four epilogue warps drain unit i while the MMA
 // warp is already accumulating unit i + 1 and the rings never run dry between units.
-template <int FMT, bool RAW_TMA>  // RAW_TMA: packed weights staged in shared memory by TMA (rows a multiple of 16 bytes)
+// RAW_TMA: packed weights staged in shared memory (by TMA where the rows are multiples of 16 bytes).  Q6BOX (Q6_K with rows
+// that are multiples of 16 bytes, i.e. K a multiple of 2048): the 210-byte block comes by TMA as the 240 bytes from the
+// 16-byte boundary below it, so it sits (210 b mod 16) bytes into every row of the tile; otherwise the dequant warps copy
+// Q6_K tiles themselves with 4-byte asynchronous copies.
+template <int FMT, bool RAW_TMA, bool Q6BOX = false>
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_constant__ CUtensorMap tmap_act,
                                                                 const __grid_constant__ CUtensorMap tmap_w, const PrefillParams p) {
-    constexpr uint32_t RAW_PITCH = raw_pitch(FMT), RAW_TILE_BYTES = raw_tile_bytes(FMT);
-    constexpr bool COOP = RAW_TMA && FMT == FMT_Q6_K;  // packed tiles copied by the dequant warps instead of TMA
+    constexpr uint32_t RAW_PITCH = Q6BOX ? 240u : (uint32_t)raw_pitch(FMT), RAW_TILE_BYTES = Q6BOX ? 128u * 240u : (uint32_t)raw_tile_bytes(FMT);
+    constexpr bool COOP = RAW_TMA && FMT == FMT_Q6_K && !Q6BOX;  // packed tiles copied by the dequant warps instead of TMA
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzled operand tiles need 1024-byte alignment; the launch reserves 1 KB of slack for this
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -491,7 +497,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                     }
                     mbar_expect_tx(bar_full_raw + 8 * s, RAW_TILE_BYTES);
                     // x in elements of the tensor map: bytes for the 144-byte formats, 16-bit units for Q8_0
-                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : (FMT == FMT_Q5_K || FMT == FMT_Q5_0) ? 176 : 144)), (int)n0, bar_full_raw + 8 * s);
+                    const int x = Q6BOX ? (int)(((j0 + j) * 210u) & ~15u)
+                                        : (int)((j0 + j) * (FMT == FMT_Q8_0 ? 136 : (FMT == FMT_Q5_K || FMT == FMT_Q5_0) ? 176 : 144));
+                    tma_load_2d(raw_tiles + s * RAW_TILE_BYTES, &tmap_w, x, (int)n0, bar_full_raw + 8 * s);
                     if (++s == p.nr) { s = 0; par ^= 1; }
                 }
                 if (*dead_flag) break;
@@ -688,9 +696,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
                         if constexpr (FMT == FMT_Q4_K) decode64_q45k<false>(rrow, set, o);
                         else if constexpr (FMT == FMT_Q5_K) decode64_q45k<true>(rrow, set, o);
                         else if constexpr (FMT == FMT_Q6_K) {
-                            // where the row's block sits in its 212-byte slot: the low bits of its global address
-                            const uint32_t sh = ((n0 + r) * p.row_bytes + (un.k0 / 4 + (kt >> 2)) * 210u) & 2u;
-                            decode64_q6k_staged(rrow, sh, set, o);
+                            if constexpr (Q6BOX) {
+                                // the block sits `off` bytes into the row's 240: words from the 4-byte boundary below, the
+                                // remaining 0 or 2 bytes through the decoder's shift
+                                const uint32_t off = ((un.k0 / 4 + (kt >> 2)) * 210u) & 15u;
+                                decode64_q6k_staged(rrow + (off & ~3u), off & 2u, set, o);
+                            } else {
+                                // where the row's block sits in its 212-byte slot: the low bits of its global address
+                                const uint32_t sh = ((n0 + r) * p.row_bytes + (un.k0 / 4 + (kt >> 2)) * 210u) & 2u;
+                                decode64_q6k_staged(rrow, sh, set, o);
+                            }
                         }
                         else {
                             constexpr uint32_t BB = fmt_block_bytes(FMT);
@@ -838,12 +853,12 @@ __global__ void __launch_bounds__(256) swiglu_gate_kernel(const float* __restric
 
 uint32_t pick_mt(size_t M) { return M >= 256 ? 256u : M > 64 ? 128u : 64u; }
 
-template <int FMT, bool RAW>
+template <int FMT, bool RAW, bool Q6BOX = false>
 cudaError_t launch_fmt(const CUtensorMap& map, const CUtensorMap& wmap, const PrefillParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     static PerDeviceOnce attrs;
-    cudaError_t ae = attrs.run([] { return cudaFuncSetAttribute(prefill_kernel<FMT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024); });
+    cudaError_t ae = attrs.run([] { return cudaFuncSetAttribute(prefill_kernel<FMT, RAW, Q6BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024); });
     if (ae != cudaSuccess) return ae;
-    prefill_kernel<FMT, RAW><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
+    prefill_kernel<FMT, RAW, Q6BOX><<<grid, PF_THREADS, smem, st>>>(map, wmap, p);
     note_launch();
     return cudaGetLastError();
 }
@@ -940,7 +955,8 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // packed tiles by TMA need rows that are a multiple of 16 bytes and whole 256-element tiles
     // (Q6_K's tiles are copied by the dequant warps and only need whole blocks, which the format guarantees)
     const bool raw = K % 256 == 0 && (fmt == FMT_Q6_K || p.row_bytes % 16 == 0);
-    const uint32_t raw_tile = raw ? (uint32_t)raw_tile_bytes(fmt) : 0u;
+    const bool q6box = raw && fmt == FMT_Q6_K && p.row_bytes % 16 == 0;  // K a multiple of 2048
+    const uint32_t raw_tile = !raw ? 0u : q6box ? 128u * 240u : (uint32_t)raw_tile_bytes(fmt);
     // the paths that still fetch packed bytes with loads keep ~30 KB of the SM's 256 KB as L1
     const uint32_t budget = (raw ? 232448u - 1024u : 200704u) - 2048u, b_tile = p.mt * 128;
     // activation tiles first (at least two packed tiles stay), then as many packed tiles as fit: at small M the packed
@@ -981,11 +997,11 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     // packed weights as a matrix [N, row_bytes]: tiles of 128 rows x the bytes of 256 elements (bytes for the
     // 144-byte formats, 16-bit units for Q8_0's 272 bytes: a box dimension holds at most 256 elements)
     CUtensorMap wmap = map;
-    if (raw && fmt != FMT_Q6_K) {
+    if (raw && (fmt != FMT_Q6_K || q6box)) {
         const bool q8 = fmt == FMT_Q8_0;
         const cuuint64_t wdim[2] = {(cuuint64_t)(q8 ? p.row_bytes / 2 : p.row_bytes), (cuuint64_t)N};
         const cuuint64_t wstride[1] = {(cuuint64_t)p.row_bytes};
-        const cuuint32_t wbox[2] = {q8 ? 136u : (fmt == FMT_Q5_K || fmt == FMT_Q5_0) ? 176u : 144u, 128u};
+        const cuuint32_t wbox[2] = {q6box ? 240u : q8 ? 136u : (fmt == FMT_Q5_K || fmt == FMT_Q5_0) ? 176u : 144u, 128u};
         cr = enc(&wmap, q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), wdim, wstride, wbox,
                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1002,7 +1018,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     case FMT_Q8_0: le = raw ? launch_fmt<FMT_Q8_0, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q8_0, false>(map, wmap, p, grid, smem, st); break;
     case FMT_Q4_K: le = launch_fmt<FMT_Q4_K, true>(map, wmap, p, grid, smem, st); break;
     case FMT_Q5_K: le = launch_fmt<FMT_Q5_K, true>(map, wmap, p, grid, smem, st); break;
-    case FMT_Q6_K: le = launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st); break;
+    case FMT_Q6_K: le = q6box ? launch_fmt<FMT_Q6_K, true, true>(map, wmap, p, grid, smem, st) : launch_fmt<FMT_Q6_K, true>(map, wmap, p, grid, smem, st); break;
     default: return cudaErrorInvalidValue;
     }
     if (le != cudaSuccess || !pl.split) return le;
