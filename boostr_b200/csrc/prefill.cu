@@ -748,15 +748,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kernel(const __grid_con
     }
 }
 
-// Adds the partial tiles of the K-split tail tiles in K order and writes the output.  Block = (activation row of the
-// tile, tail tile), thread = weight row of the tile; the pieces of tail tile t come from the CTAs whose granule range
+// Adds the partial tiles of the K-split tail tiles in K order and writes the output.  Block = (eight activation rows of
+// the tile, tail tile), thread = weight row of the tile; the pieces of tail tile t come from the CTAs whose granule range
 // meets [t gpt, (t + 1) gpt), in CTA order, which is K order.
+constexpr uint32_t PF_RED_ROWS = 8;
 __global__ void __launch_bounds__(128) prefill_reduce_kernel(const PrefillParams p, uint32_t G) {
     __shared__ uint32_t slots[192];
     __shared__ uint32_t nslots;
-    const uint32_t t = blockIdx.y, ml = blockIdx.x, r = threadIdx.x;
-    const uint32_t tile = p.nfull + t, n0 = (tile % p.ntn) * 128, m = (tile / p.ntn) * p.mt + ml;
-    if (m >= p.M) return;  // block-uniform
+    const uint32_t t = blockIdx.y, ml0 = blockIdx.x * PF_RED_ROWS, r = threadIdx.x;
+    const uint32_t tile = p.nfull + t, n0 = (tile % p.ntn) * 128, m0 = (tile / p.ntn) * p.mt + ml0;
+    if (m0 >= p.M) return;  // block-uniform
     if (threadIdx.x == 0) {
         const uint32_t Q = p.ntail * p.gpt, lo = t * p.gpt, hi = lo + p.gpt;
         uint32_t c = (lo * G) / Q, n = 0;
@@ -772,24 +773,38 @@ __global__ void __launch_bounds__(128) prefill_reduce_kernel(const PrefillParams
         nslots = n;
     }
     __syncthreads();
-    if (nslots == 0 || n0 + r >= p.N) return;
-    // eight pieces' loads are in flight together (a tile of a small matrix is cut into up to ~20 pieces: one load at a
-    // time was 20 L2 round trips); the additions stay in K order
-    float sum = 0.f;
     const uint32_t ns = nslots;
-    for (uint32_t i0 = 0; i0 < ns; i0 += 8) {
-        float v[8];
+    if (ns == 0 || n0 + r >= p.N) return;
+    // four pieces x eight rows of loads are in flight together (a tile of a small matrix is cut into up to ~20 pieces: one
+    // load at a time was 20 L2 round trips); the additions stay in K order
+    float sum[PF_RED_ROWS];
+    for (uint32_t i0 = 0; i0 < ns; i0 += 4) {
+        float v[4][PF_RED_ROWS];
 #pragma unroll
-        for (uint32_t i = 0; i < 8; ++i)
-            if (i0 + i < ns) v[i] = __ldcg(p.part + ((size_t)slots[i0 + i] * p.mt + ml) * 128 + r);
+        for (uint32_t i = 0; i < 4; ++i) {
+            if (i0 + i < ns) {
+                const float* src = p.part + ((size_t)slots[i0 + i] * p.mt + ml0) * 128 + r;
 #pragma unroll
-        for (uint32_t i = 0; i < 8; ++i)
-            if (i0 + i < ns) sum = i0 + i == 0 ? v[i] : sum + v[i];
+                for (uint32_t j = 0; j < PF_RED_ROWS; ++j) v[i][j] = __ldcg(src + j * 128);  // rows up to mt exist in every piece
+            }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            if (i0 + i < ns) {
+#pragma unroll
+                for (uint32_t j = 0; j < PF_RED_ROWS; ++j) sum[j] = i0 + i == 0 ? v[i][j] : sum[j] + v[i][j];
+            }
+        }
     }
-    const size_t idx = (size_t)m * p.N + n0 + r;
-    if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = sum;
-    else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(sum);
-    else static_cast<__half*>(p.out)[idx] = __float2half_rn(sum);
+#pragma unroll
+    for (uint32_t j = 0; j < PF_RED_ROWS; ++j) {
+        const uint32_t m = m0 + j;
+        if (m >= p.M) break;
+        const size_t idx = (size_t)m * p.N + n0 + r;
+        if (p.out_dtype == DT_F32) static_cast<float*>(p.out)[idx] = sum[j];
+        else if (p.out_dtype == DT_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(sum[j]);
+        else static_cast<__half*>(p.out)[idx] = __float2half_rn(sum[j]);
+    }
 }
 
 __global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, size_t n) {
@@ -1024,7 +1039,7 @@ cudaError_t launch_prefill(int fmt, const void* act, int act_dtype, const void* 
     if (le != cudaSuccess || !pl.split) return le;
     // the K-split tail tiles: add their pieces in K order
     const uint32_t rows = (uint32_t)(M < p.mt ? M : p.mt);
-    prefill_reduce_kernel<<<dim3(rows, pl.ntail, 1), 128, 0, st>>>(p, pl.grid);
+    prefill_reduce_kernel<<<dim3((rows + PF_RED_ROWS - 1) / PF_RED_ROWS, pl.ntail, 1), 128, 0, st>>>(p, pl.grid);
     note_launch();
     return cudaGetLastError();
 }
