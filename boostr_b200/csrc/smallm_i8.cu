@@ -816,9 +816,9 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
                     break;
                 }
                 tc_after();
-                float sacc[MH], sacc2[MH];
+                float sacc[MH];
 #pragma unroll
-                for (int m = 0; m < MH; ++m) sacc[m] = sacc2[m] = 0.f;
+                for (int m = 0; m < MH; ++m) sacc[m] = 0.f;
                 const uint32_t t0 = tmem + lane_addr + h * ACC_COLS + m_lo;
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
@@ -826,17 +826,15 @@ __global__ void __launch_bounds__(I8_THREADS, 1) smallm_i8_q8_0_kernel(const __g
 #pragma unroll
                     for (int pc = 0; pc < (int)P; ++pc) tmem_ld8_async(t0 + NB * b + MP * pc, v[pc]);
                     tmem_ld_wait();
+                    // the two pieces meet as integers, 254 a1 + a2 (|.| < 2^28), so a block costs one conversion and one FMA
 #pragma unroll
-                    for (int m = 0; m < MH; ++m) {
-                        sacc[m] = fmaf(db[b], (float)(int)v[0][m], sacc[m]);
-                        sacc2[m] = fmaf(db[b], (float)(int)v[1][m], sacc2[m]);
-                    }
+                    for (int m = 0; m < MH; ++m) sacc[m] = fmaf(db[b], (float)(254 * (int)v[0][m] + (int)v[1][m]), sacc[m]);
                 }
                 tc_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * h);
 #pragma unroll
-                for (int m = 0; m < MH; ++m) acc[m] = fmaf(fmaf(sacc2[m], C1, sacc[m]), scl[m], acc[m]);
+                for (int m = 0; m < MH; ++m) acc[m] = fmaf(sacc[m], scl[m] * C1, acc[m]);
             }
             if (!ok || blk + 1 != p.nblk) continue;
             // ---- the tile is complete
