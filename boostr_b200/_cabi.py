@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200q_mlp_workspace_bytes": (c_size_t, [c_int, c_int, c_size_t, c_size_t, c_size_t, c_size_t]),
     "b200q_quant_mlp": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_size_t,
                                 c_size_t, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "b200q_prefetch_next": (c_int, [c_int, c_int, POINTER(c_int), POINTER(c_void_p), POINTER(c_size_t), c_size_t]),
     "b200q_quant_matmul_static_scratch": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                                   c_size_t, c_void_p]),
     "b200q_shard_pack": (c_int, [c_int, c_void_p, c_size_t, c_size_t, c_int, c_int, c_int, c_void_p, c_size_t]),

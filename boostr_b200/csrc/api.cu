@@ -19,6 +19,10 @@ cudaError_t launch_gemv(int fmt, const void* act, int act_dtype, const void* w0,
                         unsigned int* status, bool* ws_too_small, bool image_ready = false);
 size_t gemv_workspace_bytes(int fmt, size_t M, size_t K, size_t N, bool swiglu, int sm_count);
 bool gemv_m1_supported(int fmt, size_t M, size_t K, size_t N, bool swiglu);
+bool m1_next_set(bool swiglu, int n_weights, const int* formats, const void* const* w, const size_t* N, size_t K, int sm_count);
+void m1_next_clear();
+void m1_next_stash();
+void m1_next_unstash();
 cudaError_t launch_gemv_m1(int fmt, const void* act, int act_dtype, const void* w, const void* w_up, void* out,
                            int out_dtype, size_t K, size_t N, int sm_count, cudaStream_t st, unsigned int* status,
                            const float* norm_w = nullptr, float norm_eps = 0.f);
@@ -100,6 +104,10 @@ unsigned int* status_ptr_current() {
 }
 
 thread_local char t_err[512] = "";
+
+struct NextScope {
+    ~NextScope() { m1_next_clear(); }
+};
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -286,6 +294,7 @@ int b200q_storage_bytes(int format, size_t numel, size_t* out_bytes) {
 }
 
 int b200q_dequantize(int format, const void* w, size_t nblocks, void* out, int out_dtype, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     if (!known_format(format)) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "dequantize: unsupported format id %d", format);
     if (out_dtype != DT_F32 && out_dtype != DT_BF16 && out_dtype != DT_F16 && out_dtype != DT_F64)
         return fail(B200Q_ERR_UNSUPPORTED_DTYPE, "dequantize target must be float, got dtype id %d", out_dtype);
@@ -307,6 +316,7 @@ size_t b200q_workspace_bytes(int op, int format, size_t M, size_t K, size_t N) {
 
 int b200q_quant_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                        size_t K, size_t N, void* ws, size_t ws_bytes, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     return quant_matmul_impl(format, act, act_dtype, w, out, out_dtype, M, K, N, ws, ws_bytes, stream, false);
 }
 
@@ -388,6 +398,7 @@ extern "C" {
 int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
                              const void* act, int act_dtype, int out_dtype, size_t M, size_t K, void* ws, size_t ws_bytes,
                              void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     return matmul_batch_impl("quant_matmul_batch", n_weights, formats, w, N, out, act, act_dtype, out_dtype, M, K, ws, ws_bytes, stream,
                              nullptr, 0.f);
 }
@@ -395,6 +406,7 @@ int b200q_quant_matmul_batch(int n_weights, const int* formats, const void* cons
 int b200q_rmsnorm_quant_matmul_batch(int n_weights, const int* formats, const void* const* w, const size_t* N, void* const* out,
                                      const void* act, const float* norm_weight, float eps, int act_dtype, int out_dtype, size_t M,
                                      size_t K, void* ws, size_t ws_bytes, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     if (!norm_weight) return fail(B200Q_ERR_INVALID_ARG, "rmsnorm_quant_matmul_batch: null norm weight");
     if (reinterpret_cast<uintptr_t>(norm_weight) & 15) return fail(B200Q_ERR_INVALID_ARG, "rmsnorm_quant_matmul_batch: norm weight must be 16-byte aligned");
     return matmul_batch_impl("rmsnorm_quant_matmul_batch", n_weights, formats, w, N, out, act, act_dtype, out_dtype, M, K, ws, ws_bytes,
@@ -403,6 +415,7 @@ int b200q_rmsnorm_quant_matmul_batch(int n_weights, const int* formats, const vo
 
 int b200q_quant_swiglu(int format, const void* act, int act_dtype, const void* w_gate, const void* w_up, void* out,
                        int out_dtype, size_t M, size_t K, size_t N, void* ws, size_t ws_bytes, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     int rc = check_matmul_args("quant_swiglu", format, act, act_dtype, w_gate, out, out_dtype, M, K, N);
     if (rc) return rc;
     if (!w_up) return fail(B200Q_ERR_INVALID_ARG, "quant_swiglu: null pointer");
@@ -476,6 +489,7 @@ size_t b200q_mlp_workspace_bytes(int format_gate_up, int format_down, size_t M, 
 int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void* w_up, int format_down, const void* w_down, const void* act,
                     int act_dtype, void* out, int out_dtype, size_t M, size_t K, size_t n_ff, size_t n_out, void* ws, size_t ws_bytes,
                     void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     const size_t hid = (M * n_ff * sizeof(float) + 255) & ~(size_t)255;
     if (!ws || ws_bytes < hid || (reinterpret_cast<uintptr_t>(ws) & 15))
         return fail(B200Q_ERR_WORKSPACE_TOO_SMALL, "quant_mlp: workspace of %zu bytes is too small, need %zu", ws_bytes,
@@ -483,9 +497,26 @@ int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void* w_up, in
     float* h = static_cast<float*>(ws);
     uint8_t* rest = static_cast<uint8_t*>(ws) + hid;
     const size_t rest_bytes = ws_bytes - hid;
+    // the gate/up launch pulls the head of the down-projection into L2 while it drains; the caller's own hint is for the
+    // launch after the down-projection
+    m1_next_stash();
+    if (M == 1) m1_next_set(false, 1, &format_down, &w_down, &n_out, n_ff, sm_count_current());
     int rc = b200q_quant_swiglu(format_gate_up, act, act_dtype, w_gate, w_up, h, DT_F32, M, K, n_ff, rest, rest_bytes, stream);
+    m1_next_unstash();
     if (rc) return rc;
     return quant_matmul_impl(format_down, h, DT_F32, w_down, out, out_dtype, M, n_ff, n_out, rest, rest_bytes, stream, false);
+}
+
+int b200q_prefetch_next(int op, int n_weights, const int* formats, const void* const* w, const size_t* N, size_t K) {
+    m1_next_clear();
+    if (op != B200Q_OP_QUANT_MATMUL && op != B200Q_OP_QUANT_SWIGLU) return fail(B200Q_ERR_INVALID_ARG, "prefetch_next: unknown operation %d", op);
+    if (n_weights < 1 || !formats || !w || !N) return fail(B200Q_ERR_INVALID_ARG, "prefetch_next: null array or no weights");
+    for (int i = 0; i < n_weights; ++i) {
+        if (!known_format(formats[i])) return fail(B200Q_ERR_UNSUPPORTED_FORMAT, "prefetch_next: unsupported format id %d", formats[i]);
+        if (!w[i] || (reinterpret_cast<uintptr_t>(w[i]) & 15)) return fail(B200Q_ERR_INVALID_ARG, "prefetch_next: weight pointer must be non-null and 16-byte aligned");
+    }
+    m1_next_set(op == B200Q_OP_QUANT_SWIGLU, n_weights, formats, w, N, K, sm_count_current());  // false: no kernel would use it
+    return B200Q_OK;
 }
 
 int b200q_shard_pack(int format, const void* src, size_t N, size_t K, int dim, int rank, int world, void* dst,
@@ -554,6 +585,7 @@ extern "C" {
 
 int b200q_quant_matmul_static_scratch(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype,
                                       size_t M, size_t K, size_t N, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     int rc = check_matmul_args("quant_matmul_static_scratch", format, act, act_dtype, w, out, out_dtype, M, K, N);
     if (rc) return rc;
     const size_t need = workspace_need(B200Q_OP_QUANT_MATMUL, format, act_dtype, M, K, N);
@@ -614,6 +646,7 @@ int b200q_tp_free(void* buf) {
 
 int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t M,
                               size_t K, size_t N, int rank, int world, void* const* bufs, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     int rc = check_matmul_args("row_parallel_matmul", format, act, act_dtype, w, out, out_dtype, M, K, N);
     if (rc) return rc;
     if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
@@ -639,6 +672,7 @@ int b200q_row_parallel_matmul(int format, const void* act, int act_dtype, const 
 
 int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype, const void* w, void* out_full, size_t M, size_t K,
                                      size_t n_local, int rank, int world, void* const* bufs, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     int rc = check_matmul_args("col_parallel_matmul_gather", format, act, act_dtype, w, out_full, DT_F32, M, K, n_local);
     if (rc) return rc;
     if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
@@ -667,6 +701,7 @@ int b200q_col_parallel_matmul_gather(int format, const void* act, int act_dtype,
 }
 
 int b200q_tp_all_reduce(void* data, size_t count, int rank, int world, void* const* bufs, void* stream) {
+    NextScope next_scope;  // a hint about the following launch lives for one call
     if (!data || (reinterpret_cast<uintptr_t>(data) & 3)) return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: data must be a 4-byte aligned device pointer");
     if (world < 1 || world > (int)TP_MAX_WORLD || rank < 0 || rank >= world)
         return fail(B200Q_ERR_INVALID_ARG, "tp_all_reduce: rank %d of world %d (at most %u ranks)", rank, world, TP_MAX_WORLD);

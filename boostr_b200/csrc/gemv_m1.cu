@@ -25,6 +25,23 @@
 
 namespace b200q {
 
+
+// Where the launch AFTER this one starts to read, so that this launch can pull those bytes into L2 while its
+// own ring drains.  A space is the virtual row range of up to three weights (or gate + up) that the next
+// launch's CTAs cta0 .. cta0 + ncta - 1 divide into runs of rows_per_cta rows; CTA c of this launch
+// prefetches the first `head` bytes of the run of CTA c of the next one.
+struct NextSpace {
+    const uint8_t* w[3];
+    const uint8_t* w2;  // second weight with the same geometry (up-projection), or null
+    uint32_t seg_end[3];
+    uint32_t nseg, row_bytes, rows_per_cta, cta0, ncta;
+};
+struct NextHint {
+    NextSpace sp[2];
+    uint32_t nsp;   // 0: nothing to prefetch
+    uint32_t head;  // bytes per CTA and weight
+};
+
 struct GemvM1Params {
     // Up to three weights that share the activation row (q/k/v-style batches) form one virtual row
     // space [0, N): segment s covers rows [seg_end[s-1], seg_end[s]) and writes its own output.
@@ -47,6 +64,7 @@ struct GemvM1Params {
     int act_dtype, out_dtype;
     unsigned int* status;
     PeerComm comm;  // row-parallel shard: push the partial row to every rank and add them up (single weight, f32 out)
+    NextHint next;
 };
 
 namespace {
@@ -64,10 +82,12 @@ __device__ __forceinline__ uint32_t dp4a_u8u8(uint32_t a, uint32_t b, uint32_t c
 template <int I>
 __device__ __forceinline__ int ubyte(uint32_t x) { return (int)__byte_perm(x, 0u, 0x4440 | I); }
 
-// shared-memory image of the quantised activation row, per 256-block b (stride 288 B):
+// shared-memory image of the quantised activation row, per 256-block b (stride 400 B):
 //   [0,256)   int8 codes   [256,264) (bsum_j + 4096) & 127, j = 0..7   [264,272) (bsum_j + 4096) >> 7
 //   [272,276) f32 d8
-constexpr int ACT_STRIDE = 288;
+// Every lane copies its block of the image into registers with 16-byte loads, 16 different blocks per warp.  The
+// stride is 16 bytes past a multiple of 128, so the eight lanes of a quarter-warp hit all 32 banks once.
+constexpr int ACT_STRIDE = 400;
 
 // Loads 8 consecutive activation values of this lane (f32 or bf16 source).
 __device__ __forceinline__ void load_act8(const void* act, int act_dtype, size_t base, float (&v)[8]) {
@@ -117,6 +137,34 @@ __device__ __forceinline__ float quantize_block8(const float (&v)[8], uint2& pac
     packed.y = prmt(prmt(c[4], c[5], 0x0040u), prmt(c[6], c[7], 0x0040u), 0x5410u);
     s = dp4a_s8s8(packed.x, 0x01010101u, dp4a_s8s8(packed.y, 0x01010101u, 0));
     return __fdiv_rn(amax, 127.0f);
+}
+
+// One lane: L2 prefetch of [ptr, ptr + len), shrunk to 16-byte boundaries (the bulk form wants both).
+__device__ __forceinline__ void l2_prefetch(const uint8_t* ptr, uint32_t len) {
+    const uint32_t skip = (uint32_t)(-(intptr_t)reinterpret_cast<uintptr_t>(ptr)) & 15u;
+    if (len < skip + 16) return;
+    const uint32_t n = (len - skip) & ~15u;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr + skip), "r"(n) : "memory");
+}
+
+// One lane of CTA `cta`: the head of the matching CTA's rows in the next launch goes to L2.  Called once the
+// last fill of this CTA is on its way, so the prefetch queues behind every byte this launch still needs and
+// fills the time in which this launch drains and the next one starts up.
+__device__ __forceinline__ void prefetch_next(const NextHint& h, uint32_t cta) {
+    for (uint32_t s = 0; s < h.nsp; ++s) {
+        const NextSpace& sp = h.sp[s];
+        const uint32_t c = cta - sp.cta0;
+        if (c >= sp.ncta) continue;
+        const uint32_t r0 = c * sp.rows_per_cta;
+        uint32_t sg = 0, seg_begin = 0;
+        while (sg + 1 < sp.nseg && r0 >= sp.seg_end[sg]) seg_begin = sp.seg_end[sg++];
+        if (r0 >= sp.seg_end[sg]) continue;
+        const uint32_t rows = min(sp.seg_end[sg] - r0, sp.rows_per_cta);
+        const size_t off = (size_t)(r0 - seg_begin) * sp.row_bytes;
+        const uint32_t len = (uint32_t)min((size_t)h.head, (size_t)rows * sp.row_bytes);
+        l2_prefetch(sp.w[sg] + off, len);
+        if (sp.w2) l2_prefetch(sp.w2 + off, len);
+    }
 }
 
 // RMSNorm prologue.  Every warp adds the squares of the values it holds (0 for warps without a block), the 16 warp sums
@@ -203,6 +251,7 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
         if (on) load_act8(p.act, p.act_dtype, (size_t)warp * 256 + 8 * lane, v);
         const uint32_t f1 = 2 + (uint32_t)warp;  // the rest of the ring: one fill per warp
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+        if (warp == 15 && lane == 0 && nfill <= p.nstages) prefetch_next(p.next, blockIdx.x);  // the whole range is on its way
         if (p.norm_w) {  // uniform over the launch
             float sq = 0.f;
             float g[8];
@@ -329,7 +378,10 @@ __device__ __forceinline__ void q4k_body(const GemvM1Params& p, const uint32_t c
                 dead = true;
                 atomicOr(p.status, STATUS_TIMEOUT_EMPTY);
             }
-            if (!dead && lane == 0) issue_fill(f + p.nstages, slot);
+            if (!dead && lane == 0) {
+                issue_fill(f + p.nstages, slot);
+                if (f + p.nstages + 1 == nfill) prefetch_next(p.next, blockIdx.x);
+            }
         }
         slot += 4;
         if (slot >= p.nstages) {
@@ -380,10 +432,15 @@ struct GemvM1Q6Params {
     int act_dtype, out_dtype;
     unsigned int* status;
     PeerComm comm;  // row-parallel shard: push the partial row to every rank and add them up (f32 out)
+    NextHint next;
 };
 
-// activation image per 256-block (stride 304 B): [0,256) int8 codes | [256,288) 16 x int16 sums of 16 | [288,292) f32 d8
-constexpr int ACT6_STRIDE = 304;
+// activation image per 256-block (stride 416 B), one 144-byte record per 128-element half n:
+//   [144 n, 144 n + 128) int8 codes | [144 n + 128, 144 n + 144) 8 x int16 sums of 16;   [288,292) f32 d8
+// Lane (b, n) copies record n of block b into registers with 16-byte loads; with the records 36 words apart and
+// the blocks 8 words past a multiple of 32, the eight lanes of a quarter-warp hit all 32 banks once.
+constexpr int ACT6_STRIDE = 416, ACT6_HALF = 144, ACT6_SUMS = 128, ACT6_SUMS_HALF = 144;
+// half n: codes at ACT6_HALF * n, sums at ACT6_SUMS + ACT6_SUMS_HALF * n
 
 template <int I>
 __device__ __forceinline__ int sbyte(uint32_t x) {
@@ -485,6 +542,7 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
         }
         const uint32_t f1 = 2 + (uint32_t)warp;
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
+        if (warp == 15 && lane == 0 && nfill <= p.nstages) prefetch_next(p.next, blockIdx.x);
         if (p.norm_w) {  // uniform over the launch
             float sq = 0.f;
 #pragma unroll
@@ -514,9 +572,10 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
                 int s;
                 const float d8 = quantize_block8(v[j], packed, s);
                 uint8_t* blk = act_s + qb * ACT6_STRIDE;
-                *reinterpret_cast<uint2*>(blk + 8 * lane) = packed;
+                const int hn = lane >> 4;  // the half this lane's 8 values belong to
+                *reinterpret_cast<uint2*>(blk + ACT6_HALF * hn + 8 * (lane & 15)) = packed;
                 s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);  // 16 elements = 2 lanes
-                if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + 256 + 2 * (lane >> 1)) = (short)s;
+                if ((lane & 1) == 0) *reinterpret_cast<short*>(blk + ACT6_SUMS + ACT6_SUMS_HALF * hn + 2 * ((lane >> 1) & 7)) = (short)s;
                 if (lane == 0) *reinterpret_cast<float*>(blk + 288) = d8;
             }
         }
@@ -536,10 +595,10 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
         const uint8_t* blk = act_s + gblk * ACT6_STRIDE;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            uint4 q = *reinterpret_cast<const uint4*>(blk + 128 * n + 16 * i);
+            uint4 q = *reinterpret_cast<const uint4*>(blk + ACT6_HALF * n + 16 * i);
             a[4 * i] = q.x; a[4 * i + 1] = q.y; a[4 * i + 2] = q.z; a[4 * i + 3] = q.w;
         }
-        uint4 q = *reinterpret_cast<const uint4*>(blk + 256 + 16 * n);
+        uint4 q = *reinterpret_cast<const uint4*>(blk + ACT6_SUMS + ACT6_SUMS_HALF * n);
         bs[0] = q.x; bs[1] = q.y; bs[2] = q.z; bs[3] = q.w;
         d8 = *reinterpret_cast<const float*>(blk + 288);
     }
@@ -593,7 +652,10 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
                 store_row(r0 + lane, tot);
             }
             __syncwarp();
-            if (!dead && refill && lane == 0) issue_fill(f + p.nstages, slot);
+            if (!dead && refill && lane == 0) {
+                issue_fill(f + p.nstages, slot);
+                if (f + p.nstages + 1 == nfill) prefetch_next(p.next, blockIdx.x);
+            }
         }
         slot += 4;
         if (slot >= p.nstages) {
@@ -716,6 +778,117 @@ static cudaError_t m1_attrs() {
     });
 }
 
+// Number of CTAs that stream the Q6_K weight of a mixed launch: the SMs are divided in proportion to the
+// packed bytes, Q6_K bytes counting 1.3x (more arithmetic per byte).
+static size_t mixed_q6k_ctas(size_t n4, size_t n6, int sm_count) {
+    const double b4 = (double)n4 * 144.0, b6 = (double)n6 * 210.0 * 1.3;
+    size_t g6 = (size_t)((double)sm_count * b6 / (b4 + b6) + 0.5);
+    if (g6 < 1) g6 = 1;
+    if (g6 > (size_t)sm_count - 1) g6 = (size_t)sm_count - 1;
+    return g6;
+}
+
+// ---- the hint about the launch after the next one (see NextHint) ----
+namespace {
+thread_local NextHint t_next = {};   // taken by the next M = 1 launch of this thread
+thread_local NextHint t_stash = {};
+NextHint take_next() {
+    const NextHint h = t_next;
+    t_next.nsp = 0;
+    return h;
+}
+void space_of(NextSpace& sp, const GemvM1Params& p, size_t grid, size_t cta0) {
+    sp = NextSpace{};
+    for (int i = 0; i < 3; ++i) {
+        sp.w[i] = p.w[i];
+        sp.seg_end[i] = p.seg_end[i];
+    }
+    sp.w2 = p.w2;
+    sp.nseg = p.nseg;
+    sp.row_bytes = p.row_bytes;
+    sp.rows_per_cta = p.rows_per_cta;
+    sp.cta0 = (uint32_t)cta0;
+    sp.ncta = (uint32_t)grid;
+}
+void space_of(NextSpace& sp, const GemvM1Q6Params& p, size_t grid, size_t cta0) {
+    sp = NextSpace{};
+    sp.w[0] = p.w;
+    sp.seg_end[0] = p.N;
+    sp.nseg = 1;
+    sp.row_bytes = p.row_bytes;
+    sp.rows_per_cta = p.rows_per_cta;
+    sp.cta0 = (uint32_t)cta0;
+    sp.ncta = (uint32_t)grid;
+}
+}  // namespace
+
+void m1_next_clear() { t_next.nsp = 0; }
+void m1_next_stash() {
+    t_stash = t_next;
+    t_next.nsp = 0;
+}
+void m1_next_unstash() {
+    t_next = t_stash;
+    t_stash.nsp = 0;
+}
+
+// Describes the first launch of the coming single-row operation (the same choices as the dispatch makes):
+// `n_weights` weights [N[i], K] sharing the activation row, or gate and up of a SwiGLU.  Returns false, and
+// leaves no hint, when that operation would not run on the kernels of this file.
+bool m1_next_set(bool swiglu, int n_weights, const int* formats, const void* const* w, const size_t* N, size_t K, int sm_count) {
+    t_next.nsp = 0;
+    if (n_weights < 1 || !formats || !w || !N || sm_count < 2) return false;
+    for (int i = 0; i < n_weights && i < 4; ++i)
+        if (!w[i] || N[i] == 0 || N[i] > 0x7FFFFFFFu) return false;
+    // Bytes per CTA: what the memory system delivers to one SM while a launch drains and the next one starts up
+    // (about 2 us at 1/148 of the HBM rate); measured flat between 80 and 104 KB, worse outside.
+    constexpr uint32_t head_bytes = 96u * 1024u;
+    NextHint h = {};
+    h.head = head_bytes;
+    void* const no_out[3] = {nullptr, nullptr, nullptr};
+    size_t smem;
+    if (swiglu) {
+        if (n_weights != 2 || formats[0] != FMT_Q4_K || formats[1] != FMT_Q4_K || N[0] != N[1] || !gemv_m1_supported(FMT_Q4_K, 1, K, N[0], true))
+            return false;
+        GemvM1Params p;
+        const size_t grid = setup_q4k(p, smem, nullptr, DT_F32, 1, w, N, no_out, w[1], DT_F32, K, (size_t)sm_count, nullptr);
+        space_of(h.sp[0], p, grid, 0);
+        h.nsp = 1;
+        h.head = head_bytes / 2;
+    } else if (formats[0] == FMT_Q4_K && gemv_m1_supported(FMT_Q4_K, 1, K, N[0], false)) {
+        int run = 1;
+        while (run < 3 && run < n_weights && formats[run] == FMT_Q4_K) ++run;
+        const bool mixed = run < n_weights && formats[run] == FMT_Q6_K && gemv_m1_supported(FMT_Q6_K, 1, K, N[run], false);
+        GemvM1Params p4;
+        if (mixed) {
+            size_t n4 = 0;
+            for (int i = 0; i < run; ++i) n4 += N[i];
+            const size_t g6 = mixed_q6k_ctas(n4, N[run], sm_count);
+            GemvM1Q6Params p6;
+            uint32_t nchunk;
+            const size_t grid4 = setup_q4k(p4, smem, nullptr, DT_F32, run, w, N, no_out, nullptr, DT_F32, K, (size_t)sm_count - g6, nullptr);
+            const size_t grid6 = setup_q6k(p6, nchunk, smem, nullptr, DT_F32, w[run], nullptr, DT_F32, K, N[run], g6, nullptr);
+            space_of(h.sp[0], p4, grid4, 0);
+            space_of(h.sp[1], p6, grid6, grid4);
+            h.nsp = 2;
+        } else {
+            const size_t grid = setup_q4k(p4, smem, nullptr, DT_F32, run, w, N, no_out, nullptr, DT_F32, K, (size_t)sm_count, nullptr);
+            space_of(h.sp[0], p4, grid, 0);
+            h.nsp = 1;
+        }
+    } else if (formats[0] == FMT_Q6_K && gemv_m1_supported(FMT_Q6_K, 1, K, N[0], false)) {
+        GemvM1Q6Params p6;
+        uint32_t nchunk;
+        const size_t grid = setup_q6k(p6, nchunk, smem, nullptr, DT_F32, w[0], nullptr, DT_F32, K, N[0], (size_t)sm_count, nullptr);
+        space_of(h.sp[0], p6, grid, 0);
+        h.nsp = 1;
+    } else {
+        return false;
+    }
+    t_next = h;
+    return true;
+}
+
 static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void* w, void* out, int out_dtype, size_t K,
                                       size_t N, int sm_count, cudaStream_t st, unsigned int* status, const float* norm_w, float norm_eps) {
     GemvM1Q6Params p;
@@ -724,6 +897,7 @@ static cudaError_t launch_gemv_m1_q6k(const void* act, int act_dtype, const void
     const size_t grid = setup_q6k(p, nchunk, smem, act, act_dtype, w, out, out_dtype, K, N, (size_t)sm_count, status);
     p.norm_w = norm_w;
     p.norm_eps = norm_eps;
+    p.next = take_next();
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
@@ -742,6 +916,7 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
     const size_t grid = setup_q4k(p, smem, act, act_dtype, nseg, w, n, out, w_up, out_dtype, K, (size_t)sm_count, status);
     p.norm_w = norm_w;
     p.norm_eps = norm_eps;
+    p.next = take_next();
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = w_up ? launch_pdl(gemv_m1_q4k_kernel<true>, dim3((unsigned)grid), dim3(512), smem, st, p)
@@ -750,17 +925,13 @@ cudaError_t launch_gemv_m1_batch(const void* act, int act_dtype, int nseg, const
     return le != cudaSuccess ? le : cudaGetLastError();
 }
 
-// `nseg` Q4_K weights plus one Q6_K weight [n6, K] on the same activation row, one launch.  The SMs are
-// divided in proportion to the packed bytes, Q6_K bytes counting 1.3x (more arithmetic per byte).
+// `nseg` Q4_K weights plus one Q6_K weight [n6, K] on the same activation row, one launch.
 cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const void* const* w, const size_t* n,
                                  void* const* out, const void* w6, size_t n6, void* out6, int out_dtype, size_t K, int sm_count,
                                  cudaStream_t st, unsigned int* status, const float* norm_w, float norm_eps) {
     size_t n4 = 0;
     for (int i = 0; i < nseg; ++i) n4 += n[i];
-    const double b4 = (double)n4 * 144.0, b6 = (double)n6 * 210.0 * 1.3;
-    size_t g6 = (size_t)((double)sm_count * b6 / (b4 + b6) + 0.5);
-    if (g6 < 1) g6 = 1;
-    if (g6 > (size_t)sm_count - 1) g6 = (size_t)sm_count - 1;
+    const size_t g6 = mixed_q6k_ctas(n4, n6, sm_count);
     GemvM1Params p4;
     GemvM1Q6Params p6;
     uint32_t nchunk;
@@ -769,6 +940,7 @@ cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const
     const size_t grid6 = setup_q6k(p6, nchunk, smem6, act, act_dtype, w6, out6, out_dtype, K, n6, g6, status);
     p4.norm_w = p6.norm_w = norm_w;
     p4.norm_eps = p6.norm_eps = norm_eps;
+    p4.next = p6.next = take_next();
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le = launch_pdl(gemv_m1_mixed_kernel, dim3((unsigned)(grid4 + grid6)), dim3(512), smem4 > smem6 ? smem4 : smem6, st,
@@ -781,6 +953,7 @@ cudaError_t launch_gemv_m1_mixed(const void* act, int act_dtype, int nseg, const
 // lands in `out` (f32), all in this one launch.
 cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const void* w, void* out, size_t K, size_t N,
                                   int sm_count, cudaStream_t st, unsigned int* status, const PeerComm& comm) {
+    const NextHint next = take_next();
     cudaError_t e = m1_attrs();
     if (e != cudaSuccess) return e;
     cudaError_t le;
@@ -790,14 +963,16 @@ cudaError_t launch_gemv_m1_rowpar(int fmt, const void* act, int act_dtype, const
         uint32_t nchunk;
         const size_t grid = setup_q6k(p, nchunk, smem, act, act_dtype, w, out, DT_F32, K, N, (size_t)sm_count, status);
         p.comm = comm;
-        le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
+        p.next = next;
+            le = nchunk == 1   ? launch_pdl(gemv_m1_q6k_kernel<1>, dim3((unsigned)grid), dim3(512), smem, st, p)
              : nchunk == 2 ? launch_pdl(gemv_m1_q6k_kernel<2>, dim3((unsigned)grid), dim3(512), smem, st, p)
                            : launch_pdl(gemv_m1_q6k_kernel<4>, dim3((unsigned)grid), dim3(512), smem, st, p);
     } else {
         GemvM1Params p;
         const size_t grid = setup_q4k(p, smem, act, act_dtype, 1, &w, &N, &out, nullptr, DT_F32, K, (size_t)sm_count, status);
         p.comm = comm;
-        le = launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
+        p.next = next;
+            le = launch_pdl(gemv_m1_q4k_kernel<false>, dim3((unsigned)grid), dim3(512), smem, st, p);
     }
     note_launch();
     return le != cudaSuccess ? le : cudaGetLastError();

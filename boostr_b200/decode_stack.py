@@ -66,6 +66,7 @@ class DecodeStack:
         self.logits_local = torch.empty(m, vocab // p, **f32)
         self.logits = torch.empty(m, vocab, **f32) if p > 1 else self.logits_local
         self.exchange: Optional[PeerExchange] = None
+        self.prefetch = True  # tell each call which weights follow it (ops.prefetch_next)
         self.bytes_local = sum(L[n].weight.storage_bytes() for L in self.layers for n, *_ in self.spec) + \
             self.lm_head.weight.storage_bytes()
 
@@ -77,11 +78,19 @@ class DecodeStack:
             L["down"].exchange = exchange
 
     def step(self) -> torch.Tensor:
-        for L in self.layers:
+        # single-row decode: every call is told which weights come after it, so its launch ends by pulling their head
+        # into L2 (a hint only; it is baked into a captured graph like any other argument)
+        hint = ops.prefetch_next if self.m == 1 and self.prefetch else (lambda *a, **k: None)
+        for i, L in enumerate(self.layers):
+            hint([L["o"].weight])
             QuantLinear.forward_batch(L["qkv"], self.x, outs=[self.q, self.k, self.v])   # column-parallel
+            hint([L["gate"].weight, L["up"].weight], swiglu=True)
             L["o"].forward(self.q, out=self.o)                      # row-parallel: all-reduce inside
+            hint([L["down"].weight])
             ops.quant_swiglu(self.o, L["gate"].weight, L["up"].weight, out=self.h)
+            hint([l.weight for l in self.layers[i + 1]["qkv"]] if i + 1 < len(self.layers) else [self.lm_head.weight])
             L["down"].forward(self.h, out=self.d)                   # row-parallel: all-reduce inside
+        hint([l.weight for l in self.layers[0]["qkv"]])             # the next step starts there
         if self.world > 1:
             self.lm_head.forward_gathered(self.x, self.logits, self.exchange, local=self.logits_local)
         else:

@@ -233,6 +233,21 @@ def quant_swiglu(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: 
     return out
 
 
+def prefetch_next(weights: Sequence[QuantTensor], swiglu: bool = False) -> None:
+    """Hint for a single-row decode loop (``b200q_prefetch_next``): ``weights`` are those of the operation AFTER the next
+    call — several weights sharing one activation row, or ``[gate, up]`` with ``swiglu=True``.  The next call pulls the
+    head of those weights into L2 while it drains.  Purely a performance hint; results never depend on it."""
+    if not weights:
+        return
+    nw = len(weights)
+    k = weights[0].shape[-1]
+    fmts = (ctypes.c_int * nw)(*[w.format.format_id for w in weights])
+    wptr = (ctypes.c_void_p * nw)(*[w.storage.data_ptr() for w in weights])
+    ns = (ctypes.c_size_t * nw)(*[w.shape[0] for w in weights])
+    with torch.cuda.device(weights[0].storage.device):
+        _cabi.check(_cabi.lib().b200q_prefetch_next(_cabi.OP_QUANT_SWIGLU if swiglu else _cabi.OP_QUANT_MATMUL, nw, fmts, wptr, ns, k))
+
+
 def quant_mlp(activation: torch.Tensor, gate_weight: QuantTensor, up_weight: QuantTensor, down_weight: QuantTensor,
               out_dtype: torch.dtype = torch.float32, out: torch.Tensor = None) -> torch.Tensor:
     """down(silu(activation x gate^T) * (activation x up^T)): the feed-forward block of a quantized layer

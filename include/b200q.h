@@ -175,6 +175,26 @@ B200Q_API int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void
                               size_t n_out, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * Optional hint for a decode loop (single activation row), where every launch is short and the time
+ * between the last byte of one weight and the first byte of the next is a visible share of the step.
+ * (No counterpart in boostr, whose decode step launches its kernels back to back,
+ * src/model/llama/model/forward_graph.rs:22-73; results never depend on the hint.)
+ *
+ * The call describes the operation that will FOLLOW the next call this thread makes:
+ * B200Q_OP_QUANT_MATMUL with `n_weights` weights [N[i], K] that share one activation row (as in
+ * b200q_quant_matmul / b200q_quant_matmul_batch), or B200Q_OP_QUANT_SWIGLU with w[0] = gate and
+ * w[1] = up, both [N[0], K].  The next call, when it is a single-row product of a format with a
+ * streaming decode kernel (Q4_K, Q6_K), then spends its last microseconds pulling the first ~100 KB
+ * that each SM of the following launch will read into L2, so that launch starts from L2 instead of
+ * from idle HBM.  The hint lives for exactly one call (any b200q compute call consumes or drops it)
+ * and is dropped at once when the described operation has no such kernel.  The weight pointers
+ * must stay valid device memory until the call that consumed the hint has finished on its stream;
+ * under stream capture the hint is baked into the captured launch, so the same holds for every replay.
+ * b200q_quant_mlp places the hint for its own down-projection itself.
+ */
+B200Q_API int b200q_prefetch_next(int op, int n_weights, const int* formats, const void* const* w, const size_t* N, size_t K);
+
+/*
  * quant_matmul for callers that cannot hand over scratch memory.  (No counterpart in boostr:
  * its CUDA backend always has numr's allocator at hand.)
  *

@@ -67,6 +67,9 @@ extern "C" {
                            w_down: *const c_void, act: *const c_void, act_dtype: c_int, out: *mut c_void, out_dtype: c_int,
                            m: usize, k: usize, n_ff: usize, n_out: usize, ws: *mut c_void, ws_bytes: usize,
                            stream: *mut c_void) -> c_int;
+    /// Decode-loop hint: describes the operation AFTER the next call (its weights' head goes to L2 while that call drains).
+    pub fn b200q_prefetch_next(op: c_int, n_weights: c_int, formats: *const c_int, w: *const *const c_void, n: *const usize,
+                               k: usize) -> c_int;
     pub fn b200q_quant_matmul_static_scratch(format: c_int, act: *const c_void, act_dtype: c_int, w: *const c_void,
                                              out: *mut c_void, out_dtype: c_int, m: usize, k: usize, n: usize,
                                              stream: *mut c_void) -> c_int;

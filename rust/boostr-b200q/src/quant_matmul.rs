@@ -136,6 +136,26 @@ pub fn quant_mlp(client: &CudaClient, activation: &Tensor<CudaRuntime>, gate: &Q
     Ok(out)
 }
 
+/// Decode-loop hint (`b200q_prefetch_next`): `weights` are those of the operation AFTER the next call made by this thread:
+/// several weights sharing one activation row, or `[gate, up]` with `swiglu`.  The next call, when it is a single-row
+/// product, pulls the head of those weights into L2 while it drains.  A hint only: results never depend on it, and a
+/// weight of a format libb200q does not serve simply drops it.  The weights must outlive the call that consumes the hint.
+pub fn prefetch_next(weights: &[&QuantTensor<CudaRuntime>], swiglu: bool) -> Result<()> {
+    if weights.is_empty() {
+        return Ok(());
+    }
+    let mut formats = Vec::with_capacity(weights.len());
+    for w in weights {
+        let Some(f) = format_id(w.format()) else { return Ok(()) };
+        formats.push(f);
+    }
+    let ptrs: Vec<*const c_void> = weights.iter().map(|w| w.storage().ptr() as *const c_void).collect();
+    let ns: Vec<usize> = weights.iter().map(|w| w.shape()[0]).collect();
+    let k = *weights[0].shape().last().unwrap();
+    let op = if swiglu { b200q_sys::B200Q_OP_QUANT_SWIGLU } else { b200q_sys::B200Q_OP_QUANT_MATMUL };
+    check(unsafe { b200q_sys::b200q_prefetch_next(op, weights.len() as c_int, formats.as_ptr(), ptrs.as_ptr(), ns.as_ptr(), k) })
+}
+
 /// For a host that must not allocate at the call site (see `b200q_quant_matmul_static_scratch` in the header):
 /// same result as `quant_matmul`, scratch inside the library, calls on one device must not overlap.
 pub fn quant_matmul_no_alloc(client: &CudaClient, activation: &Tensor<CudaRuntime>, weight: &QuantTensor<CudaRuntime>,
