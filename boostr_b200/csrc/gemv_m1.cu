@@ -526,7 +526,8 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
         mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 15 && lane < 2 && (uint32_t)lane < nfill) issue_fill(lane, lane);
+    const uint32_t early = NCHUNK > 1 ? p.nstages : 2u;
+    if (warp == 15 && (uint32_t)lane < early && (uint32_t)lane < nfill) issue_fill(lane, lane);
     grid_dep_launch();
     grid_dep_wait();
     const bool tp = p.comm.world > 1;
@@ -540,7 +541,7 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
             const uint32_t qb = warp + 16 * j;
             if (qb < p.nblk) load_act8(p.act, p.act_dtype, (size_t)qb * 256 + 8 * lane, v[j]);
         }
-        const uint32_t f1 = 2 + (uint32_t)warp;
+        const uint32_t f1 = early + (uint32_t)warp;
         if (lane == 0 && f1 < p.nstages && f1 < nfill) issue_fill(f1, f1);
         if (warp == 15 && lane == 0 && nfill <= p.nstages) prefetch_next(p.next, blockIdx.x);
         if (p.norm_w) {  // uniform over the launch
