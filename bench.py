@@ -155,9 +155,9 @@ class ClockSampler:
 # --------------------------------------------------------------------------- GPU arm
 
 # DRAM bytes (read + written) of one launch of the dominant kernel at one GPU, from the ncu capture
-# summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.262 MB, dram__bytes_write.sum 2 KB.
+# summarised in profiles/gemv_m1_q6k_down.md: dram__bytes_read.sum 48.276 MB, dram__bytes_write.sum 0 (the 16 KB of output stay in L2).
 # A K-split shard streams proportionally fewer bytes, so the figure is scaled by the shard's packed bytes.
-NCU_TRAFFIC_DOWN_1GPU = 48_264_148
+NCU_TRAFFIC_DOWN_1GPU = 48_275_700
 NCU_ALGORITHMIC_DOWN_1GPU = 4096 * 56 * 210
 REGION_REPEATS = 30
 
@@ -193,7 +193,9 @@ def time_kernel_family(stack, torch, ops):
     outs = torch.empty(stack.m, ws[0].shape[0], device="cuda")
 
     def run():
-        for w in ws:
+        for i, w in enumerate(ws):
+            if stack.m == 1:
+                ops.prefetch_next([ws[(i + 1) % len(ws)]])  # as in the decode step: each call knows which weights follow
             ops.quant_matmul(x, w, out=outs)
 
     med, lo, hi = timed_graph(torch, run, reps=20)
