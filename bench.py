@@ -362,6 +362,7 @@ def run_ours(args):
     m = args.m
     pk = peaks()
     stack = DecodeStack(m, rank, world)
+    stack.prefetch = not args.no_prefetch_hint
     torch.cuda.synchronize()
     log("stack built")
     # kernel-family and per-configuration timings run before any process group exists (one-GPU figures on
@@ -619,6 +620,8 @@ def main():
                     help="row-parallel all-reduce at N > 1: fused into the GEMV kernel over peer memory, or NCCL")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-per-config", action="store_true", help="skip the per-configuration kernel timings")
+    ap.add_argument("--no-prefetch-hint", action="store_true",
+                    help="decode step without b200q_prefetch_next (each call told which weights follow it); for A/B runs")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
