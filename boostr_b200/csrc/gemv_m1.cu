@@ -18,6 +18,10 @@
 //     one AND each (high nibbles stay in place and are divided out of the integer sum), 6-bit
 //     scales and mins unpacked with a handful of byte-parallel logic ops, the min term through
 //     byte-split block sums; then 16 lanes add their block terms with shuffles.
+//   * a decode step is a chain of such launches, each short, so the time between one launch's last byte and
+//     the next one's first byte counts: kernels start under programmatic dependent launch and send their
+//     first fills before the grid dependency resolves, and a launch that has been told which weights follow
+//     (NextHint) ends by pulling the head of those weights into L2.
 // Integer sums are exact and each block contributes (d*d8)*sumi - (dmin*d8)*summ as in
 // fused_dot_q4k_q8k (src/quant/cpu/kernels/simd/fused_q4k_q8k_dot.rs:111-172); only the order in
 // which the K/256 block terms are added differs from the CPU loop (pairwise instead of serial).
@@ -518,8 +522,10 @@ __device__ __forceinline__ void q6k_body(const GemvM1Q6Params& p, const uint32_t
                         nrows * p.row_bytes, p.w + (size_t)p.N * p.row_bytes, bar_full + 8 * slot);
     };
 
-    // two fills leave before the grid dependency is resolved, the rest of the ring after the
-    // activation loads (responses return in request order)
+    // Short rows: two fills leave before the grid dependency is resolved, the rest of the ring after the
+    // activation loads (responses return in request order, so loads behind a full ring would wait for it).
+    // Long rows (several warps per row, eight activation loads per lane): the whole ring leaves first.  This
+    // kernel's end is set by when its weights arrive, and fills slip in between the many loads anyway.
     if (warp == 15 && (uint32_t)lane < p.nstages) {
         mbar_init(bar_full + 8 * lane, 1);
         mbar_init(bar_empty + 8 * lane, 4);
