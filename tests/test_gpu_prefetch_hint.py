@@ -32,11 +32,15 @@ def weights():
         "down": synth.device_weight("Q6_K", 4096, 14336, gen),   # four K-chunks
         "down2": synth.device_weight("Q6_K", 600, 8192, gen),    # two K-chunks
         "short": synth.device_weight("Q4_K", 37, 1024, gen),     # fewer rows than SMs, short rows
+        "o_shard8": synth.device_weight("Q4_K", 4096, 512, gen),     # row-parallel shards of an 8-rank group: two and
+        "down_shard8": synth.device_weight("Q6_K", 4096, 1792, gen),  # seven blocks per row
         "q8": synth.device_weight("Q8_0", 512, 4096, gen),       # no streaming decode kernel: the hint is dropped
         "x4096": torch.randn(1, 4096, device="cuda", generator=gen),
         "x14336": torch.randn(1, 14336, device="cuda", generator=gen),
         "x8192": torch.randn(1, 8192, device="cuda", generator=gen),
         "x1024": torch.randn(1, 1024, device="cuda", generator=gen),
+        "x512": torch.randn(1, 512, device="cuda", generator=gen),
+        "x1792": torch.randn(1, 1792, device="cuda", generator=gen),
     }
     return w
 
@@ -50,6 +54,8 @@ NEXT = {
     "mixed": (["q", "k", "v"], False),
     "swiglu": (["gate", "up"], True),
     "short": (["short"], False),
+    "shard_q4k": (["o_shard8"], False),
+    "shard_q6k": (["down_shard8"], False),
     "unusable": (["q8"], False),
 }
 
@@ -60,6 +66,8 @@ CALLS = {
     "matmul_q6k_2chunks": lambda o, w: [o.quant_matmul(w["x8192"], w["down2"])],
     "matmul_q6k_1chunk": lambda o, w: [o.quant_matmul(w["x4096"], w["v"])],
     "matmul_short": lambda o, w: [o.quant_matmul(w["x1024"], w["short"])],
+    "matmul_shard_q4k": lambda o, w: [o.quant_matmul(w["x512"], w["o_shard8"])],
+    "matmul_shard_q6k": lambda o, w: [o.quant_matmul(w["x1792"], w["down_shard8"])],
     "batch_mixed": lambda o, w: o.quant_matmul_batch(w["x4096"], [w["q"], w["k"], w["v"]]),
     "batch_q4k": lambda o, w: o.quant_matmul_batch(w["x4096"], [w["q"], w["k"]]),
     "swiglu": lambda o, w: [o.quant_swiglu(w["x4096"], w["gate"], w["up"])],
