@@ -799,9 +799,12 @@ static size_t mixed_q6k_ctas(size_t n4, size_t n6, int sm_count) {
 namespace {
 thread_local NextHint t_next = {};   // taken by the next M = 1 launch of this thread
 thread_local NextHint t_stash = {};
+thread_local int t_next_device = -1;  // the device that was current when the hint was given: its weights live there
 NextHint take_next() {
-    const NextHint h = t_next;
+    NextHint h = t_next;
     t_next.nsp = 0;
+    int dev = -1;
+    if (h.nsp && (cudaGetDevice(&dev) != cudaSuccess || dev != t_next_device)) h.nsp = 0;  // a launch on another device drops it
     return h;
 }
 void space_of(NextSpace& sp, const GemvM1Params& p, size_t grid, size_t cta0) {
@@ -892,6 +895,7 @@ bool m1_next_set(bool swiglu, int n_weights, const int* formats, const void* con
     } else {
         return false;
     }
+    if (cudaGetDevice(&t_next_device) != cudaSuccess) return false;
     t_next = h;
     return true;
 }

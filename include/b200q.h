@@ -187,7 +187,8 @@ B200Q_API int b200q_quant_mlp(int format_gate_up, const void* w_gate, const void
  * streaming decode kernel (Q4_K, Q6_K), then spends its last microseconds pulling the first ~100 KB
  * that each SM of the following launch will read into L2, so that launch starts from L2 instead of
  * from idle HBM.  The hint lives for exactly one call (any b200q compute call consumes or drops it)
- * and is dropped at once when the described operation has no such kernel.  The weight pointers
+ * and is dropped at once when the described operation has no such kernel, or when the consuming
+ * call runs on another device than the one current at the time of the hint.  The weight pointers
  * must stay valid device memory until the call that consumed the hint has finished on its stream;
  * under stream capture the hint is baked into the captured launch, so the same holds for every replay.
  * b200q_quant_mlp places the hint for its own down-projection itself.
