@@ -76,6 +76,23 @@ def test_validation_fails_before_launch(lib):
     assert lib.b200q_dequantize(F.Q8_0.format_id, fake, 0, fake, 0, None) == _cabi.OK  # empty tensor: nothing to do
 
 
+def test_prefetch_hint_validation_needs_no_device(lib):
+    fm = (ctypes.c_int * 2)(F.Q4_K.format_id, F.Q4_K.format_id)
+    wp = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    ns = (ctypes.c_size_t * 2)(512, 512)
+    assert lib.b200q_prefetch_next(5, 1, fm, wp, ns, 4096) == _cabi.ERR_INVALID_ARG and b"unknown operation" in lib.b200q_last_error()
+    assert lib.b200q_prefetch_next(_cabi.OP_QUANT_MATMUL, 0, fm, wp, ns, 4096) == _cabi.ERR_INVALID_ARG
+    assert lib.b200q_prefetch_next(_cabi.OP_QUANT_MATMUL, 2, fm, None, ns, 4096) == _cabi.ERR_INVALID_ARG
+    bad = (ctypes.c_int * 1)(3)
+    assert lib.b200q_prefetch_next(_cabi.OP_QUANT_MATMUL, 1, bad, wp, ns, 4096) == _cabi.ERR_UNSUPPORTED_FORMAT
+    odd = (ctypes.c_void_p * 1)(0x1008)
+    assert lib.b200q_prefetch_next(_cabi.OP_QUANT_MATMUL, 1, fm, odd, ns, 4096) == _cabi.ERR_INVALID_ARG
+    # a well-formed hint on a machine without a usable device is dropped, not an error: nothing will consume it
+    assert lib.b200q_prefetch_next(_cabi.OP_QUANT_SWIGLU, 2, fm, wp, ns, 4096) == _cabi.OK
+    # ... and any compute call ends a hint's life: on a machine WITH a device the made-up pointers above must not survive
+    assert lib.b200q_dequantize(F.Q8_0.format_id, ctypes.c_void_p(0x1000), 0, ctypes.c_void_p(0x1000), 0, None) == _cabi.OK
+
+
 @pytest.mark.parametrize("fmt", list(F))
 @pytest.mark.parametrize("world", [1, 2, 4])
 def test_shard_pack_matches_numpy(lib, fmt, world):
